@@ -1,0 +1,570 @@
+// Collective kernels for sm_100a: all-gather, equal all-to-all, broadcast, reduce-scatter,
+// one-shot and two-shot all-reduce, profile probe.  See coll_kernels.cuh for the scheme.
+//
+// Conventions used by every body below
+//   * blocks [0, producers) push tiles into peers' windows (or into peers' registered output
+//     when zeroCopy), the remaining blocks consume tiles that land in this rank's window;
+//   * tile t of source s lands at  DataHalf(dst) + s * pairStride + t * tileBytes  and is
+//     announced by flag plane A slot  s * FLAGS_PER_PAIR + t  holding (epoch, t + 1);
+//   * a launch never wraps its rings: the host splits larger messages into several launches,
+//     each with a fresh epoch and the other data half, and the done-epoch guard in the
+//     prologue keeps a fast rank from overwriting a half that a slow peer still reads;
+//   * reductions accumulate in rank order 0..R-1 in fp32 (integers natively), so every rank
+//     computes bit-identical results and results do not depend on arrival order
+//     (the reference needs a separate deterministic variant for that: lccl_op.h:188-203).
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "coll_kernels.cuh"
+#include "device/tilexr_perf_trace.cuh"
+#include "device/tilexr_rma.cuh"
+#include "device/tilexr_sync.cuh"
+
+namespace TileXR {
+
+using namespace tilexr;
+
+namespace {
+
+constexpr int FLAG_PLANE_A = TILEXR_FLAG_DATA_BASE;
+constexpr int FLAG_PLANE_B = TILEXR_FLAG_ACK_BASE;
+
+struct BlockCtx {
+    Waiter w;
+    PerfScope perf;
+    int rank;
+    int ranks;
+};
+
+__device__ __forceinline__ uint8_t *RingSlot(const CollArgs &a, int dst, int src, uint32_t tile, uint32_t epoch,
+                                             uint32_t plane)
+{
+    return DataHalf(a.comm, dst, epoch) + static_cast<uint64_t>(src) * a.pairStride +
+           (static_cast<uint64_t>(plane) * a.tiles + tile) * a.tileBytes;
+}
+
+__device__ __forceinline__ uint32_t TileLen(uint64_t sliceLen, uint32_t tile, uint32_t tileBytes)
+{
+    const uint64_t begin = static_cast<uint64_t>(tile) * tileBytes;
+    if (begin >= sliceLen) return 0;
+    const uint64_t left = sliceLen - begin;
+    return static_cast<uint32_t>(left < tileBytes ? left : tileBytes);
+}
+
+// After a block has stored a tile for `peer`: make the stores visible, then raise the flag.
+// Called by ONE thread per peer, after a __syncthreads() that joined the storing threads.
+__device__ __forceinline__ void RaiseTileFlag(const CollArgs &a, int peer, int plane, int src, uint32_t tile, uint32_t epoch)
+{
+    SetFlag(FlagSlot(a.comm, peer, plane + static_cast<int64_t>(src) * TILEXR_FLAGS_PER_PAIR + tile), epoch, tile + 1);
+}
+
+__device__ __forceinline__ bool WaitTileFlag(BlockCtx &c, const CollArgs &a, int plane, int src, uint32_t tile)
+{
+    const int64_t slot = plane + static_cast<int64_t>(src) * TILEXR_FLAGS_PER_PAIR + tile;
+    return WaitFlagGE(c.w, FlagSlot(a.comm, c.rank, slot), tile + 1, src, slot);
+}
+
+// Where rank `peer` receives bytes that belong at `offset` of ITS output buffer.
+__device__ __forceinline__ uint8_t *PeerOut(const CollArgs &a, int peer, uint64_t offset)
+{
+    return a.comm->registryPtr->regions[a.outHandle].peerBase[peer] + a.outOffset + offset;
+}
+
+// ---- element-wise reduction of 16-byte vectors ---------------------------------------------------
+
+template <typename T>
+struct Elem;
+template <>
+struct Elem<float> {
+    typedef float Acc;
+    static __device__ __forceinline__ float up(float v) { return v; }
+    static __device__ __forceinline__ float down(float v) { return v; }
+};
+template <>
+struct Elem<__half> {
+    typedef float Acc;
+    static __device__ __forceinline__ float up(__half v) { return __half2float(v); }
+    static __device__ __forceinline__ __half down(float v) { return __float2half_rn(v); }
+};
+template <>
+struct Elem<__nv_bfloat16> {
+    typedef float Acc;
+    static __device__ __forceinline__ float up(__nv_bfloat16 v) { return __bfloat162float(v); }
+    static __device__ __forceinline__ __nv_bfloat16 down(float v) { return __float2bfloat16_rn(v); }
+};
+#define TXR_INT_ELEM(T)                                                    \
+    template <>                                                            \
+    struct Elem<T> {                                                       \
+        typedef T Acc;                                                     \
+        static __device__ __forceinline__ T up(T v) { return v; }          \
+        static __device__ __forceinline__ T down(T v) { return v; }        \
+    };
+TXR_INT_ELEM(int8_t)
+TXR_INT_ELEM(int16_t)
+TXR_INT_ELEM(int32_t)
+TXR_INT_ELEM(int64_t)
+
+template <typename A>
+__device__ __forceinline__ A Combine(A x, A y, int op)
+{
+    switch (op) {
+        case TILEXR_REDUCE_PROD: return x * y;
+        case TILEXR_REDUCE_MAX: return x > y ? x : y;
+        case TILEXR_REDUCE_MIN: return x < y ? x : y;
+        default: return x + y;
+    }
+}
+
+// One tile: dst[i] = reduce over sources s = 0..ranks-1 of src_s[i], in that order.
+// `srcOf(s)` yields the base pointer of source s for this tile.
+template <typename T, typename SrcFn>
+__device__ __forceinline__ void ReduceTile(uint8_t *dst, uint8_t *dst2, SrcFn srcOf, int ranks, uint32_t bytes, int op)
+{
+    typedef typename Elem<T>::Acc Acc;
+    constexpr int N = 16 / sizeof(T);
+    const uint32_t vecs = bytes / 16;
+    bool aligned = (reinterpret_cast<uintptr_t>(dst) & 15u) == 0 && (dst2 == nullptr || (reinterpret_cast<uintptr_t>(dst2) & 15u) == 0);
+    for (int s = 0; s < ranks; ++s) aligned = aligned && (reinterpret_cast<uintptr_t>(srcOf(s)) & 15u) == 0;
+    uint32_t doneBytes = 0;
+    if (aligned) {
+        for (uint32_t i = threadIdx.x; i < vecs; i += blockDim.x) {
+            Acc acc[N];
+            {
+                const Vec16 v = ld_vec16_stream(srcOf(0) + i * 16ull);
+                const T *e = reinterpret_cast<const T *>(&v);
+#pragma unroll
+                for (int k = 0; k < N; ++k) acc[k] = Elem<T>::up(e[k]);
+            }
+            for (int s = 1; s < ranks; ++s) {
+                const Vec16 v = ld_vec16_stream(srcOf(s) + i * 16ull);
+                const T *e = reinterpret_cast<const T *>(&v);
+#pragma unroll
+                for (int k = 0; k < N; ++k) acc[k] = Combine<Acc>(acc[k], Elem<T>::up(e[k]), op);
+            }
+            Vec16 r;
+            T *e = reinterpret_cast<T *>(&r);
+#pragma unroll
+            for (int k = 0; k < N; ++k) e[k] = Elem<T>::down(acc[k]);
+            st_vec16(dst + i * 16ull, r);
+            if (dst2 != nullptr) st_vec16(dst2 + i * 16ull, r);
+        }
+        doneBytes = vecs * 16;
+    }
+    // ragged tail, or everything when a pointer is not 16-byte aligned
+    const uint32_t elems = (bytes - doneBytes) / sizeof(T);
+    for (uint32_t i = threadIdx.x; i < elems; i += blockDim.x) {
+        const uint64_t off = doneBytes + static_cast<uint64_t>(i) * sizeof(T);
+        Acc acc = Elem<T>::up(*reinterpret_cast<const T *>(srcOf(0) + off));
+        for (int s = 1; s < ranks; ++s) acc = Combine<Acc>(acc, Elem<T>::up(*reinterpret_cast<const T *>(srcOf(s) + off)), op);
+        const T r = Elem<T>::down(acc);
+        *reinterpret_cast<T *>(dst + off) = r;
+        if (dst2 != nullptr) *reinterpret_cast<T *>(dst2 + off) = r;
+    }
+}
+
+template <typename SrcFn>
+__device__ __forceinline__ void ReduceTileByType(int dtype, uint8_t *dst, uint8_t *dst2, SrcFn srcOf, int ranks,
+                                                 uint32_t bytes, int op)
+{
+    switch (dtype) {
+        case TILEXR_DATA_TYPE_FP32: ReduceTile<float>(dst, dst2, srcOf, ranks, bytes, op); break;
+        case TILEXR_DATA_TYPE_FP16: ReduceTile<__half>(dst, dst2, srcOf, ranks, bytes, op); break;
+        case TILEXR_DATA_TYPE_BFP16: ReduceTile<__nv_bfloat16>(dst, dst2, srcOf, ranks, bytes, op); break;
+        case TILEXR_DATA_TYPE_INT8: ReduceTile<int8_t>(dst, dst2, srcOf, ranks, bytes, op); break;
+        case TILEXR_DATA_TYPE_INT16: ReduceTile<int16_t>(dst, dst2, srcOf, ranks, bytes, op); break;
+        case TILEXR_DATA_TYPE_INT32: ReduceTile<int32_t>(dst, dst2, srcOf, ranks, bytes, op); break;
+        case TILEXR_DATA_TYPE_INT64: ReduceTile<int64_t>(dst, dst2, srcOf, ranks, bytes, op); break;
+        default: break;
+    }
+}
+
+// Reads a tile once and stores it to up to `nDst` destinations (peers' windows plus an
+// optional local copy), four 16-byte vectors in flight per thread.
+__device__ __forceinline__ void FanOutTile(uint8_t *const *dsts, int nDst, const uint8_t *src, uint32_t bytes)
+{
+    bool aligned = (reinterpret_cast<uintptr_t>(src) & 15u) == 0;
+    for (int d = 0; d < nDst; ++d) aligned = aligned && (reinterpret_cast<uintptr_t>(dsts[d]) & 15u) == 0;
+    if (!aligned) {
+        for (int d = 0; d < nDst; ++d) CopyLanes(dsts[d], src, bytes, threadIdx.x, blockDim.x);
+        return;
+    }
+    const uint32_t vecs = bytes / 16;
+    const uint32_t stride = blockDim.x;
+    uint32_t i = threadIdx.x;
+    for (; i + 3 * stride < vecs; i += 4 * stride) {
+        const Vec16 v0 = ld_vec16_stream(src + i * 16ull);
+        const Vec16 v1 = ld_vec16_stream(src + (i + stride) * 16ull);
+        const Vec16 v2 = ld_vec16_stream(src + (i + 2 * stride) * 16ull);
+        const Vec16 v3 = ld_vec16_stream(src + (i + 3 * stride) * 16ull);
+        for (int d = 0; d < nDst; ++d) {
+            uint8_t *p = dsts[d];
+            st_vec16(p + i * 16ull, v0);
+            st_vec16(p + (i + stride) * 16ull, v1);
+            st_vec16(p + (i + 2 * stride) * 16ull, v2);
+            st_vec16(p + (i + 3 * stride) * 16ull, v3);
+        }
+    }
+    for (; i < vecs; i += stride) {
+        const Vec16 v = ld_vec16_stream(src + i * 16ull);
+        for (int d = 0; d < nDst; ++d) st_vec16(dsts[d] + i * 16ull, v);
+    }
+    for (uint32_t b = vecs * 16 + threadIdx.x; b < bytes; b += blockDim.x) {
+        const uint8_t v = src[b];
+        for (int d = 0; d < nDst; ++d) dsts[d][b] = v;
+    }
+}
+
+__device__ __forceinline__ bool Prologue(BlockCtx &c, const CollArgs &a)
+{
+    c.rank = a.comm->rank;
+    c.ranks = a.comm->rankSize;
+    c.perf.stats = nullptr;
+    if (threadIdx.x == 0) {
+        c.perf = PerfInit(a.perfTrace, c.rank, blockIdx.x);
+        PerfStageBegin(c.perf, TILEXR_PERF_KERNEL_TOTAL);
+        PerfStageBegin(c.perf, TILEXR_PERF_POST_SYNC);
+    }
+    const bool ok = KernelPrologue(c.w, a.comm, a.magic, a.opType, static_cast<int64_t>(a.sliceBytes), true);
+    if (threadIdx.x == 0) PerfStageEnd(c.perf, TILEXR_PERF_POST_SYNC);
+    return ok;
+}
+
+__device__ __forceinline__ void Epilogue(BlockCtx &c, const CollArgs &a, bool ok)
+{
+    KernelEpilogue(c.w, ok);
+    if (threadIdx.x == 0) PerfStageEnd(c.perf, TILEXR_PERF_KERNEL_TOTAL, a.sliceBytes);
+}
+
+// ---- all-gather / all-to-all / broadcast -----------------------------------------------------------
+
+__device__ void PushBody(const CollArgs &a)
+{
+    __shared__ uint8_t *sDst[TILEXR_MAX_RANK_SIZE + 1];
+    BlockCtx c;
+    bool ok = Prologue(c, a);
+    const int rank = c.rank;
+    const int R = c.ranks;
+    const uint32_t epoch = c.w.epoch;
+    const uint64_t S = a.sliceBytes;
+    const bool isProducer = blockIdx.x < a.producers;
+
+    if (ok && isProducer) {
+        if (a.kind == COLL_ALL_TO_ALL) {
+            // item (tile, k): slice for peer (rank+1+k) % R; k == R-1 is the local slice
+            const uint64_t items = static_cast<uint64_t>(a.tiles) * R;
+            for (uint64_t it = blockIdx.x; it < items; it += a.producers) {
+                const uint32_t t = static_cast<uint32_t>(it / R);
+                const int peer = (rank + 1 + static_cast<int>(it % R)) % R;
+                const uint32_t n = TileLen(S, t, a.tileBytes);
+                const uint8_t *src = a.in + static_cast<uint64_t>(peer) * a.sliceStride + static_cast<uint64_t>(t) * a.tileBytes;
+                uint8_t *dst;
+                if (peer == rank) {
+                    dst = a.out + static_cast<uint64_t>(rank) * a.sliceStride + static_cast<uint64_t>(t) * a.tileBytes;
+                } else if (a.zeroCopy) {
+                    dst = PeerOut(a, peer, static_cast<uint64_t>(rank) * a.sliceStride + static_cast<uint64_t>(t) * a.tileBytes);
+                } else {
+                    dst = RingSlot(a, peer, rank, t, epoch, 0);
+                }
+                if (threadIdx.x == 0) PerfStageBegin(c.perf, TILEXR_PERF_LOCAL_INPUT_TO_IPC);
+                if (dst != src) CopyLanes(dst, src, n, threadIdx.x, blockDim.x);
+                __syncthreads();
+                if (threadIdx.x == 0) {
+                    if (peer != rank) RaiseTileFlag(a, peer, FLAG_PLANE_A, rank, t, epoch);
+                    PerfStageEnd(c.perf, TILEXR_PERF_LOCAL_INPUT_TO_IPC, n);
+                }
+            }
+        } else if (a.kind == COLL_ALL_GATHER || rank == a.root) {
+            const bool gather = a.kind == COLL_ALL_GATHER;
+            for (uint32_t t = blockIdx.x; t < a.tiles; t += a.producers) {
+                const uint32_t n = TileLen(S, t, a.tileBytes);
+                const uint64_t tileOff = static_cast<uint64_t>(t) * a.tileBytes;
+                const uint8_t *src = a.in + tileOff;
+                __syncthreads();   // sDst of the previous tile is no longer read
+                if (static_cast<int>(threadIdx.x) < R) {
+                    const int peer = threadIdx.x;
+                    uint8_t *dst;
+                    if (peer == rank) {
+                        dst = gather ? a.out + static_cast<uint64_t>(rank) * a.sliceStride + tileOff : nullptr;
+                        if (dst == src) dst = nullptr;   // in-place all-gather
+                    } else if (a.zeroCopy) {
+                        dst = PeerOut(a, peer, (gather ? static_cast<uint64_t>(rank) * a.sliceStride : 0) + tileOff);
+                    } else {
+                        dst = RingSlot(a, peer, rank, t, epoch, 0);
+                    }
+                    sDst[peer] = dst;
+                }
+                __syncthreads();
+                // compact the destination list (every thread computes the same list)
+                uint8_t *dsts[8];
+                if (threadIdx.x == 0) PerfStageBegin(c.perf, TILEXR_PERF_LOCAL_INPUT_TO_IPC);
+                for (int base = 0; base < R; base += 8) {
+                    int nd = 0;
+                    for (int k = 0; k < 8 && base + k < R; ++k) {
+                        // start at rank+1 so that ranks do not all hit the same peer first
+                        uint8_t *d = sDst[(rank + 1 + base + k) % R];
+                        if (d != nullptr) dsts[nd++] = d;
+                    }
+                    if (nd > 0) FanOutTile(dsts, nd, src, n);
+                }
+                __syncthreads();
+                if (static_cast<int>(threadIdx.x) < R && static_cast<int>(threadIdx.x) != rank) {
+                    RaiseTileFlag(a, threadIdx.x, FLAG_PLANE_A, rank, t, epoch);
+                }
+                if (threadIdx.x == 0) PerfStageEnd(c.perf, TILEXR_PERF_LOCAL_INPUT_TO_IPC, static_cast<uint64_t>(n) * (R - 1));
+            }
+        }
+    } else if (ok) {
+        // consumers: tiles that other ranks push into this rank's window
+        const uint32_t consumers = gridDim.x - a.producers;
+        const uint32_t me = blockIdx.x - a.producers;
+        const bool bcast = a.kind == COLL_BROADCAST;
+        const int nSrc = bcast ? (rank == a.root ? 0 : 1) : R - 1;
+        const uint64_t items = static_cast<uint64_t>(a.tiles) * nSrc;
+        for (uint64_t it = me; it < items && ok; it += consumers) {
+            const uint32_t t = static_cast<uint32_t>(it / nSrc);
+            const int src = bcast ? a.root : (rank + 1 + static_cast<int>(it % nSrc)) % R;
+            const uint32_t n = TileLen(S, t, a.tileBytes);
+            bool got = true;
+            if (threadIdx.x == 0) {
+                PerfStageBegin(c.perf, TILEXR_PERF_FLAG_POLL_WAIT);
+                got = WaitTileFlag(c, a, FLAG_PLANE_A, src, t);
+                PerfStageEnd(c.perf, TILEXR_PERF_FLAG_POLL_WAIT);
+            }
+            ok = BlockBroadcastOk(got);
+            if (ok && !a.zeroCopy) {
+                if (threadIdx.x == 0) PerfStageBegin(c.perf, TILEXR_PERF_PEER_IPC_TO_OUTPUT);
+                uint8_t *dst = a.out + (bcast ? 0 : static_cast<uint64_t>(src) * a.sliceStride) + static_cast<uint64_t>(t) * a.tileBytes;
+                CopyLanes(dst, RingSlot(a, rank, src, t, epoch, 0), n, threadIdx.x, blockDim.x);
+                if (threadIdx.x == 0) PerfStageEnd(c.perf, TILEXR_PERF_PEER_IPC_TO_OUTPUT, n);
+            }
+        }
+    }
+    Epilogue(c, a, ok);
+}
+
+// ---- reduce-scatter / one-shot all-reduce -----------------------------------------------------------
+
+__device__ void ReduceBody(const CollArgs &a)
+{
+    __shared__ uint8_t *sDst[TILEXR_MAX_RANK_SIZE + 1];
+    BlockCtx c;
+    bool ok = Prologue(c, a);
+    const int rank = c.rank;
+    const int R = c.ranks;
+    const uint32_t epoch = c.w.epoch;
+    const uint64_t S = a.sliceBytes;
+    const bool scatter = a.kind == COLL_REDUCE_SCATTER;
+
+    if (ok && blockIdx.x < a.producers) {
+        if (scatter) {
+            const uint64_t items = static_cast<uint64_t>(a.tiles) * (R - 1);
+            for (uint64_t it = blockIdx.x; it < items; it += a.producers) {
+                const uint32_t t = static_cast<uint32_t>(it / (R - 1));
+                const int peer = (rank + 1 + static_cast<int>(it % (R - 1))) % R;
+                const uint32_t n = TileLen(S, t, a.tileBytes);
+                const uint8_t *src = a.in + static_cast<uint64_t>(peer) * a.sliceStride + static_cast<uint64_t>(t) * a.tileBytes;
+                CopyLanes(RingSlot(a, peer, rank, t, epoch, 0), src, n, threadIdx.x, blockDim.x);
+                __syncthreads();
+                if (threadIdx.x == 0) RaiseTileFlag(a, peer, FLAG_PLANE_A, rank, t, epoch);
+            }
+        } else {
+            for (uint32_t t = blockIdx.x; t < a.tiles; t += a.producers) {
+                const uint32_t n = TileLen(S, t, a.tileBytes);
+                const uint8_t *src = a.in + static_cast<uint64_t>(t) * a.tileBytes;
+                __syncthreads();
+                if (static_cast<int>(threadIdx.x) < R) {
+                    sDst[threadIdx.x] = static_cast<int>(threadIdx.x) == rank ? nullptr : RingSlot(a, threadIdx.x, rank, t, epoch, 0);
+                }
+                __syncthreads();
+                uint8_t *dsts[8];
+                for (int base = 0; base < R; base += 8) {
+                    int nd = 0;
+                    for (int k = 0; k < 8 && base + k < R; ++k) {
+                        uint8_t *d = sDst[(rank + 1 + base + k) % R];
+                        if (d != nullptr) dsts[nd++] = d;
+                    }
+                    if (nd > 0) FanOutTile(dsts, nd, src, n);
+                }
+                __syncthreads();
+                if (static_cast<int>(threadIdx.x) < R && static_cast<int>(threadIdx.x) != rank) {
+                    RaiseTileFlag(a, threadIdx.x, FLAG_PLANE_A, rank, t, epoch);
+                }
+            }
+        }
+    } else if (ok) {
+        const uint32_t consumers = gridDim.x - a.producers;
+        const uint32_t me = blockIdx.x - a.producers;
+        const uint8_t *own = a.in + (scatter ? static_cast<uint64_t>(rank) * a.sliceStride : 0);
+        for (uint32_t t = me; t < a.tiles && ok; t += consumers) {
+            const uint32_t n = TileLen(S, t, a.tileBytes);
+            bool got = true;
+            if (static_cast<int>(threadIdx.x) < R && static_cast<int>(threadIdx.x) != rank) {
+                got = WaitTileFlag(c, a, FLAG_PLANE_A, threadIdx.x, t);
+            }
+            ok = BlockBroadcastOk(got);
+            if (!ok) break;
+            const uint64_t tileOff = static_cast<uint64_t>(t) * a.tileBytes;
+            auto srcOf = [&](int s) -> const uint8_t * {
+                return s == rank ? own + tileOff : RingSlot(a, rank, s, t, epoch, 0);
+            };
+            ReduceTileByType(a.dtype, a.out + tileOff, nullptr, srcOf, R, n, a.reduceOp);
+        }
+    }
+    Epilogue(c, a, ok);
+}
+
+// ---- two-shot all-reduce ------------------------------------------------------------------------------
+// Rank r owns slice r = bytes [r*sliceBytes, min((r+1)*sliceBytes, totalBytes)).
+//   pushers   : send tile t of slice p to owner p                       (plane A, ring plane 0)
+//   reducers  : owner reduces tile t of its slice in rank order, writes it to its own output
+//               and pushes the reduced tile to every peer               (plane B, ring plane 1)
+//   gatherers : copy reduced tiles of the other slices into the output
+
+__device__ __forceinline__ uint64_t SliceLen(const CollArgs &a, int r)
+{
+    const uint64_t begin = static_cast<uint64_t>(r) * a.sliceBytes;
+    if (begin >= a.totalBytes) return 0;
+    const uint64_t left = a.totalBytes - begin;
+    return left < a.sliceBytes ? left : a.sliceBytes;
+}
+
+__device__ void TwoShotBody(const CollArgs &a)
+{
+    __shared__ uint8_t *sDst[TILEXR_MAX_RANK_SIZE + 1];
+    BlockCtx c;
+    bool ok = Prologue(c, a);
+    const int rank = c.rank;
+    const int R = c.ranks;
+    const uint32_t epoch = c.w.epoch;
+    const uint64_t S = a.sliceBytes;
+
+    if (ok && blockIdx.x < a.producers) {
+        const uint64_t items = static_cast<uint64_t>(a.tiles) * (R - 1);
+        for (uint64_t it = blockIdx.x; it < items; it += a.producers) {
+            const uint32_t t = static_cast<uint32_t>(it / (R - 1));
+            const int peer = (rank + 1 + static_cast<int>(it % (R - 1))) % R;
+            const uint32_t n = TileLen(SliceLen(a, peer), t, a.tileBytes);
+            const uint8_t *src = a.in + static_cast<uint64_t>(peer) * S + static_cast<uint64_t>(t) * a.tileBytes;
+            if (n > 0) CopyLanes(RingSlot(a, peer, rank, t, epoch, 0), src, n, threadIdx.x, blockDim.x);
+            __syncthreads();
+            if (threadIdx.x == 0) RaiseTileFlag(a, peer, FLAG_PLANE_A, rank, t, epoch);
+        }
+    } else if (ok && blockIdx.x < a.producers + a.reducers) {
+        const uint32_t me = blockIdx.x - a.producers;
+        const uint64_t myLen = SliceLen(a, rank);
+        for (uint32_t t = me; t < a.tiles && ok; t += a.reducers) {
+            const uint32_t n = TileLen(myLen, t, a.tileBytes);
+            const uint64_t tileOff = static_cast<uint64_t>(t) * a.tileBytes;
+            bool got = true;
+            if (static_cast<int>(threadIdx.x) < R && static_cast<int>(threadIdx.x) != rank) {
+                got = WaitTileFlag(c, a, FLAG_PLANE_A, threadIdx.x, t);
+            }
+            ok = BlockBroadcastOk(got);
+            if (!ok) break;
+            if (n > 0) {
+                auto srcOf = [&](int s) -> const uint8_t * {
+                    return s == rank ? a.in + static_cast<uint64_t>(rank) * S + tileOff : RingSlot(a, rank, s, t, epoch, 0);
+                };
+                // The reduced tile goes to this rank's output and to a staging slot in this
+                // rank's own ring plane 1, from where it fans out to the peers.
+                uint8_t *stage = RingSlot(a, rank, rank, t, epoch, 1);
+                ReduceTileByType(a.dtype, a.out + static_cast<uint64_t>(rank) * S + tileOff, stage, srcOf, R, n, a.reduceOp);
+                __syncthreads();
+                if (static_cast<int>(threadIdx.x) < R) {
+                    const int peer = threadIdx.x;
+                    sDst[peer] = peer == rank ? nullptr
+                                 : a.zeroCopy ? PeerOut(a, peer, static_cast<uint64_t>(rank) * S + tileOff)
+                                              : RingSlot(a, peer, rank, t, epoch, 1);
+                }
+                __syncthreads();
+                uint8_t *dsts[8];
+                for (int base = 0; base < R; base += 8) {
+                    int nd = 0;
+                    for (int k = 0; k < 8 && base + k < R; ++k) {
+                        uint8_t *d = sDst[(rank + 1 + base + k) % R];
+                        if (d != nullptr) dsts[nd++] = d;
+                    }
+                    if (nd > 0) FanOutTile(dsts, nd, stage, n);
+                }
+            }
+            __syncthreads();
+            if (static_cast<int>(threadIdx.x) < R && static_cast<int>(threadIdx.x) != rank) {
+                RaiseTileFlag(a, threadIdx.x, FLAG_PLANE_B, rank, t, epoch);
+            }
+        }
+    } else if (ok) {
+        const uint32_t first = a.producers + a.reducers;
+        const uint32_t gatherers = gridDim.x - first;
+        const uint32_t me = blockIdx.x - first;
+        const uint64_t items = static_cast<uint64_t>(a.tiles) * (R - 1);
+        for (uint64_t it = me; it < items && ok; it += gatherers) {
+            const uint32_t t = static_cast<uint32_t>(it / (R - 1));
+            const int src = (rank + 1 + static_cast<int>(it % (R - 1))) % R;
+            const uint32_t n = TileLen(SliceLen(a, src), t, a.tileBytes);
+            bool got = true;
+            if (threadIdx.x == 0) got = WaitTileFlag(c, a, FLAG_PLANE_B, src, t);
+            ok = BlockBroadcastOk(got);
+            if (ok && !a.zeroCopy && n > 0) {
+                CopyLanes(a.out + static_cast<uint64_t>(src) * S + static_cast<uint64_t>(t) * a.tileBytes,
+                          RingSlot(a, rank, src, t, epoch, 1), n, threadIdx.x, blockDim.x);
+            }
+        }
+    }
+    Epilogue(c, a, ok);
+}
+
+// ---- profile probe --------------------------------------------------------------------------------------
+// A local copy that walks through every profiler stage and touches no peer memory
+// (reference: kernels/lcal_profile_probe.cce:54-116).
+
+__device__ void ProbeBody(const CollArgs &a)
+{
+    BlockCtx c;
+    c.rank = a.comm->rank;
+    c.ranks = a.comm->rankSize;
+    c.w = MakeWaiter(a.comm, a.magic, blockIdx.x);
+    c.perf.stats = nullptr;
+    if (threadIdx.x == 0) {
+        c.perf = PerfInit(a.perfTrace, c.rank, blockIdx.x);
+        PerfStageBegin(c.perf, TILEXR_PERF_KERNEL_TOTAL);
+        PerfStageBegin(c.perf, TILEXR_PERF_POST_SYNC);
+        PerfStageEnd(c.perf, TILEXR_PERF_POST_SYNC);
+        PerfStageBegin(c.perf, TILEXR_PERF_CHUNK_TOTAL);
+    }
+    const uint64_t per = ((a.sliceBytes + gridDim.x - 1) / gridDim.x + 15) & ~15ull;
+    const uint64_t begin = per * blockIdx.x;
+    const uint64_t n = begin >= a.sliceBytes ? 0 : (a.sliceBytes - begin < per ? a.sliceBytes - begin : per);
+    if (threadIdx.x == 0) PerfStageBegin(c.perf, TILEXR_PERF_LOCAL_INPUT_TO_IPC);
+    CopyLanes(a.out + begin, a.in + begin, n, threadIdx.x, blockDim.x);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        PerfStageEnd(c.perf, TILEXR_PERF_LOCAL_INPUT_TO_IPC, n);
+        PerfStageBegin(c.perf, TILEXR_PERF_FLAG_POLL_WAIT);
+        PerfStageEnd(c.perf, TILEXR_PERF_FLAG_POLL_WAIT);
+        PerfStageBegin(c.perf, TILEXR_PERF_PEER_IPC_TO_OUTPUT);
+        PerfStageEnd(c.perf, TILEXR_PERF_PEER_IPC_TO_OUTPUT, 0);
+        PerfStageBegin(c.perf, TILEXR_PERF_CHUNK_BARRIER);
+        PerfStageEnd(c.perf, TILEXR_PERF_CHUNK_BARRIER);
+        PerfStageEnd(c.perf, TILEXR_PERF_CHUNK_TOTAL, n);
+        PerfStageEnd(c.perf, TILEXR_PERF_KERNEL_TOTAL, n);
+        if (blockIdx.x == 0) {
+            a.comm->dfx[TILEXR_DFX_MAGIC] = a.magic;
+            a.comm->dfx[TILEXR_DFX_OP] = TILEXR_OP_PROFILE_PROBE;
+            a.comm->dfx[TILEXR_DFX_RUN_STATUS] = TILEXR_RUN_FINISHED;
+        }
+    }
+}
+
+TILEXR_DEFINE_KERNEL(TileXRPushTiles, CollArgs, PushBody, COLL_BLOCK_THREADS)
+TILEXR_DEFINE_KERNEL(TileXRReduceTiles, CollArgs, ReduceBody, COLL_BLOCK_THREADS)
+TILEXR_DEFINE_KERNEL(TileXRAllReduceTwoShot, CollArgs, TwoShotBody, COLL_BLOCK_THREADS)
+TILEXR_DEFINE_KERNEL(TileXRProfileProbeKernel, CollArgs, ProbeBody, COLL_BLOCK_THREADS)
+
+} // namespace
+
+const KernelEntry &PushKernelEntry() { return TileXRPushTilesEntry; }
+const KernelEntry &ReduceKernelEntry() { return TileXRReduceTilesEntry; }
+const KernelEntry &TwoShotKernelEntry() { return TileXRAllReduceTwoShotEntry; }
+const KernelEntry &ProbeKernelEntry() { return TileXRProfileProbeKernelEntry; }
+
+} // namespace TileXR

@@ -1,0 +1,643 @@
+#include "comm.h"
+
+#include <algorithm>
+#include <cerrno>
+#include <cstdlib>
+#include <cstring>
+#include <ctime>
+#include <fcntl.h>
+#include <map>
+#include <sys/mman.h>
+#include <sys/stat.h>
+#include <unistd.h>
+
+#include "tilexr_log.h"
+
+namespace TileXR {
+
+#define TXR_CUDA(call)                                                                              \
+    do {                                                                                            \
+        cudaError_t e_ = (call);                                                                    \
+        if (e_ != cudaSuccess) {                                                                    \
+            TILEXR_LOG(ERROR) << #call << " failed: " << cudaGetErrorString(e_);                    \
+            return TILEXR_ERROR_RUNTIME;                                                            \
+        }                                                                                           \
+    } while (0)
+
+namespace {
+
+uint64_t HashString(const std::string &s)
+{
+    uint64_t h = 1469598103934665603ull;
+    for (unsigned char c : s) {
+        h ^= c;
+        h *= 1099511628211ull;
+    }
+    return h;
+}
+
+long EnvLong(const char *name, long fallback)
+{
+    const char *v = std::getenv(name);
+    if (v == nullptr || *v == '\0') return fallback;
+    char *end = nullptr;
+    const long x = std::strtol(v, &end, 10);
+    return (*end == '\0') ? x : fallback;
+}
+
+// What every rank tells the others at bring-up.
+struct PeerInfo {
+    int32_t device;
+    int32_t pid;
+    uint64_t hostHash;
+    uint64_t rawPtr;
+    uint64_t windowBytes;
+    uint32_t knobs;
+    uint32_t bufferMB;
+    uint64_t timeoutNs;
+    cudaIpcMemHandle_t handle;
+};
+
+struct RegionInfo {
+    int32_t pid;
+    int32_t device;
+    uint64_t rawPtr;      // address of the registered range in the owner's address space
+    uint64_t offset;      // of the range inside its allocation
+    uint64_t bytes;
+    uint32_t handleIndex;
+    uint32_t valid;
+    cudaIpcMemHandle_t handle;
+};
+
+typedef int (*CuMemGetAddressRangeFn)(unsigned long long *, size_t *, unsigned long long);
+
+int AllocationBase(const void *ptr, uint8_t **base, size_t *size)
+{
+    static CuMemGetAddressRangeFn fn = [] {
+        void *f = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuMemGetAddressRange", &f, cudaEnableDefault, &q) != cudaSuccess) f = nullptr;
+        return reinterpret_cast<CuMemGetAddressRangeFn>(f);
+    }();
+    if (fn == nullptr) return TILEXR_ERROR_RUNTIME;
+    unsigned long long b = 0;
+    size_t s = 0;
+    if (fn(&b, &s, reinterpret_cast<unsigned long long>(ptr)) != 0) return TILEXR_ERROR_RUNTIME;
+    *base = reinterpret_cast<uint8_t *>(b);
+    *size = s;
+    return TILEXR_SUCCESS;
+}
+
+} // namespace
+
+uint64_t DefaultWaitTimeoutNs()
+{
+    const long ms = EnvLong("TILEXR_WAIT_TIMEOUT_MS", 10000);
+    return static_cast<uint64_t>(ms > 0 ? ms : 10000) * 1000000ull;
+}
+
+TileXRComm::TileXRComm(int rank, int rankSize, const InitOptions &opt) : rank_(rank), rankSize_(rankSize), opt_(opt)
+{
+    waitTimeoutNs_ = DefaultWaitTimeoutNs();
+    regions_.resize(TILEXR_MAX_REGISTERED_REGIONS);
+    profiles_.resize(16);
+    registry_.magic = TILEXR_REGISTRY_MAGIC;
+    registry_.version = 1;
+    registry_.rankSize = static_cast<uint32_t>(rankSize);
+    registry_.regionCount = 0;
+    if (std::getenv("LCCL_DETERMINISTIC") != nullptr && EnvLong("LCCL_DETERMINISTIC", 0) != 0) {
+        knobFlags_ |= TILEXR_FLAG_DETERMINISTIC;
+    }
+    if (EnvLong("TILEXR_ENABLE_SDMA", 1) != 0) knobFlags_ |= TILEXR_FLAG_LOCAL_COPY;
+    if (EnvLong("TILEXR_ENABLE_UDMA", 1) != 0 && !opt.memoryOnly) knobFlags_ |= TILEXR_FLAG_RMA;
+}
+
+TileXRComm::~TileXRComm()
+{
+    const bool gpu = !isHostMemory();
+    if (gpu && device_ >= 0) cudaSetDevice(device_);
+    for (size_t h = 0; h < regions_.size(); ++h) {
+        if (regions_[h].live) Unregister(static_cast<TileXRUDMAMemHandle>(h));
+    }
+    if (gpu) {
+        for (void *p : ipcOpened_) cudaIpcCloseMemHandle(p);
+        if (devArgs_ != nullptr) cudaFree(devArgs_);
+        if (devRegistry_ != nullptr) cudaFree(devRegistry_);
+        if (localCopyWorkspace_ != nullptr) cudaFree(localCopyWorkspace_);
+        if (window_ != nullptr) cudaFree(window_);
+        if (copyStream_ != nullptr) cudaStreamDestroy(copyStream_);
+        if (copyEventIn_ != nullptr) cudaEventDestroy(copyEventIn_);
+        if (copyEventOut_ != nullptr) cudaEventDestroy(copyEventOut_);
+        delete hostArgs_;
+    } else {
+        for (int r = 0; r < static_cast<int>(peerWindows_.size()); ++r) {
+            if (peerWindows_[r] != nullptr) munmap(peerWindows_[r], windowBytes_);
+        }
+        if (!shmNames_.empty()) shm_unlink(shmNames_[rank_].c_str());
+        delete hostArgs_;
+    }
+}
+
+int TileXRComm::AllocateWindow()
+{
+    const size_t dataBytes = static_cast<size_t>(opt_.bufferMB) << 20;
+    windowBytes_ = static_cast<size_t>(TILEXR_WIN_DATA_OFFSET) + dataBytes;
+    if (isHostMemory()) {
+        // every rank derives the segment names from a job id that rank 0 drew
+        uint64_t mine = (static_cast<uint64_t>(getpid()) << 32) ^ static_cast<uint64_t>(time(nullptr)) ^
+                        reinterpret_cast<uintptr_t>(this);
+        std::vector<uint64_t> ids(rankSize_);
+        if (exchange_->AllGather(&mine, ids.data(), sizeof(mine)) != TILEXR_SUCCESS) return TILEXR_ERROR_INTERNAL;
+        const uint64_t job = ids[0];
+        shmNames_.resize(rankSize_);
+        for (int r = 0; r < rankSize_; ++r) {
+            char name[96];
+            std::snprintf(name, sizeof(name), "/tilexr-%016llx-d%d-r%d", static_cast<unsigned long long>(job),
+                          opt_.commDomain, r);
+            shmNames_[r] = name;
+        }
+        shm_unlink(shmNames_[rank_].c_str());
+        const int fd = shm_open(shmNames_[rank_].c_str(), O_CREAT | O_RDWR | O_EXCL, 0600);
+        if (fd < 0) {
+            TILEXR_LOG(ERROR) << "shm_open " << shmNames_[rank_] << ": " << std::strerror(errno);
+            return TILEXR_ERROR_INTERNAL;
+        }
+        if (ftruncate(fd, static_cast<off_t>(windowBytes_)) != 0) {
+            close(fd);
+            return TILEXR_ERROR_INTERNAL;
+        }
+        void *p = mmap(nullptr, windowBytes_, PROT_READ | PROT_WRITE, MAP_SHARED, fd, 0);
+        close(fd);
+        if (p == MAP_FAILED) return TILEXR_ERROR_INTERNAL;
+        window_ = static_cast<uint8_t *>(p);
+        // fresh shared memory is zero filled; touch only the control and flag areas
+        std::memset(window_, 0, static_cast<size_t>(TILEXR_WIN_DATA_OFFSET));
+        return TILEXR_SUCCESS;
+    }
+    TXR_CUDA(cudaMalloc(reinterpret_cast<void **>(&window_), windowBytes_));
+    // flags and control words must start at zero; the data halves need no initial value
+    TXR_CUDA(cudaMemset(window_, 0, static_cast<size_t>(TILEXR_WIN_DATA_OFFSET)));
+    TXR_CUDA(cudaDeviceSynchronize());
+    return TILEXR_SUCCESS;
+}
+
+int TileXRComm::AgreeOnKnobs()
+{
+    struct Knobs {
+        uint32_t flags;
+        uint32_t bufferMB;
+        uint64_t timeoutNs;
+        int32_t memoryOnly;
+        int32_t domain;
+    } mine{knobFlags_, static_cast<uint32_t>(opt_.bufferMB), waitTimeoutNs_, opt_.memoryOnly ? 1 : 0, opt_.commDomain};
+    std::vector<Knobs> all(rankSize_);
+    int ret = exchange_->AllGather(&mine, all.data(), sizeof(Knobs));
+    if (ret != TILEXR_SUCCESS) return ret;
+    for (int r = 0; r < rankSize_; ++r) {
+        if (std::memcmp(&all[r], &mine, sizeof(Knobs)) != 0) {
+            TILEXR_LOG(ERROR) << "rank " << r << " was started with different TILEXR_*/LCCL_* settings or buffer size "
+                              << "than rank " << rank_ << "; every rank must agree";
+            return TILEXR_ERROR_PARA_CHECK_FAIL;
+        }
+    }
+    return TILEXR_SUCCESS;
+}
+
+int TileXRComm::MapHostMemoryWindows()
+{
+    int ret = exchange_->Barrier();   // every rank created its segment
+    if (ret != TILEXR_SUCCESS) return ret;
+    peerWindows_.assign(rankSize_, nullptr);
+    for (int r = 0; r < rankSize_; ++r) {
+        if (r == rank_) {
+            peerWindows_[r] = window_;
+            continue;
+        }
+        const int fd = shm_open(shmNames_[r].c_str(), O_RDWR, 0600);
+        if (fd < 0) {
+            TILEXR_LOG(ERROR) << "cannot open window of rank " << r << ": " << std::strerror(errno);
+            return TILEXR_ERROR_INTERNAL;
+        }
+        void *p = mmap(nullptr, windowBytes_, PROT_READ | PROT_WRITE, MAP_SHARED, fd, 0);
+        close(fd);
+        if (p == MAP_FAILED) return TILEXR_ERROR_INTERNAL;
+        peerWindows_[r] = static_cast<uint8_t *>(p);
+    }
+    return exchange_->Barrier();
+}
+
+int TileXRComm::ExchangeWindows()
+{
+    PeerInfo mine{};
+    mine.device = device_;
+    mine.pid = static_cast<int32_t>(getpid());
+    mine.hostHash = HashString(SockExchange::ReadBootId());
+    mine.rawPtr = reinterpret_cast<uint64_t>(window_);
+    mine.windowBytes = windowBytes_;
+    if (opt_.mode == CommMode::PROCESS) {
+        TXR_CUDA(cudaIpcGetMemHandle(&mine.handle, window_));
+    }
+    std::vector<PeerInfo> all(rankSize_);
+    int ret = exchange_->AllGather(&mine, all.data(), sizeof(PeerInfo));
+    if (ret != TILEXR_SUCCESS) return ret;
+    peerWindows_.assign(rankSize_, nullptr);
+    for (int i = 0; i < rankSize_; ++i) {
+        const int r = (rank_ + i) % rankSize_;
+        const PeerInfo &p = all[r];
+        if (r == rank_) {
+            peerWindows_[r] = window_;
+            continue;
+        }
+        if (p.hostHash != mine.hostHash) {
+            TILEXR_LOG(ERROR) << "rank " << r << " runs on another host; this build maps peers inside one NVSwitch "
+                              << "node only";
+            return TILEXR_ERROR_NOT_SUPPORT;
+        }
+        if (p.windowBytes != windowBytes_) return TILEXR_ERROR_PARA_CHECK_FAIL;
+        if (p.pid == mine.pid) {
+            if (p.device != device_) {
+                int can = 0;
+                TXR_CUDA(cudaDeviceCanAccessPeer(&can, device_, p.device));
+                if (!can) {
+                    TILEXR_LOG(ERROR) << "device " << device_ << " cannot access device " << p.device;
+                    return TILEXR_ERROR_NOT_SUPPORT;
+                }
+                cudaError_t e = cudaDeviceEnablePeerAccess(p.device, 0);
+                if (e != cudaSuccess && e != cudaErrorPeerAccessAlreadyEnabled) {
+                    TILEXR_LOG(ERROR) << "cudaDeviceEnablePeerAccess: " << cudaGetErrorString(e);
+                    return TILEXR_ERROR_RUNTIME;
+                }
+                cudaGetLastError();
+            }
+            peerWindows_[r] = reinterpret_cast<uint8_t *>(p.rawPtr);
+        } else {
+            void *mapped = nullptr;
+            TXR_CUDA(cudaIpcOpenMemHandle(&mapped, p.handle, cudaIpcMemLazyEnablePeerAccess));
+            ipcOpened_.push_back(mapped);
+            peerWindows_[r] = static_cast<uint8_t *>(mapped);
+        }
+    }
+    return exchange_->Barrier();
+}
+
+void TileXRComm::FillCommArgs()
+{
+    CommArgs &a = *hostArgs_;
+    std::memset(&a, 0, sizeof(a));
+    a.rank = rank_;
+    a.localRank = rank_;
+    a.rankSize = rankSize_;
+    a.localRankSize = rankSize_;
+    a.commDomain = opt_.commDomain;
+    a.peerMemBytes = windowBytes_;
+    a.dataHalfBytes = ((static_cast<uint64_t>(opt_.bufferMB) << 20) / 2) & ~static_cast<uint64_t>(255);
+    a.waitTimeoutNs = waitTimeoutNs_;
+    a.extraFlag = knobFlags_ | TILEXR_FLAG_P2P;
+    if (opt_.memoryOnly) a.extraFlag |= TILEXR_FLAG_MEMORY_ONLY;
+    if (opt_.mode == CommMode::THREAD || opt_.mode == CommMode::EMULATED) a.extraFlag |= TILEXR_FLAG_SAME_PROCESS;
+    if (opt_.mode == CommMode::EMULATED) a.extraFlag |= TILEXR_FLAG_EMULATED;
+    if (opt_.mode == CommMode::HOST_MEMORY) {
+        a.extraFlag |= TILEXR_FLAG_HOST_MEMORY;
+        a.extraFlag &= ~static_cast<uint32_t>(TILEXR_FLAG_LOCAL_COPY);
+    }
+    for (int r = 0; r < rankSize_; ++r) {
+        a.peerMems[r] = peerWindows_[r];
+        a.signalMems[r] = peerWindows_[r] + TILEXR_CTRL_SIGNAL_OFFSET;
+    }
+    a.localCopyWorkspace = localCopyWorkspace_;
+    a.registryPtr = devRegistry_;
+}
+
+int TileXRComm::SyncCommArgs()
+{
+    if (isHostMemory()) return TILEXR_SUCCESS;   // hostArgs_ is what the CPU kernels read
+    TXR_CUDA(cudaMemcpy(devArgs_, hostArgs_, offsetof(CommArgs, dfx), cudaMemcpyHostToDevice));
+    return TILEXR_SUCCESS;
+}
+
+int TileXRComm::Init(std::unique_ptr<Exchange> exchange)
+{
+    if (rankSize_ <= 0 || rankSize_ > TILEXR_MAX_RANK_SIZE || rank_ < 0 || rank_ >= rankSize_ || opt_.bufferMB < 2) {
+        TILEXR_LOG(ERROR) << "bad communicator shape rank=" << rank_ << " rankSize=" << rankSize_
+                          << " bufferMB=" << opt_.bufferMB;
+        return TILEXR_ERROR_PARA_CHECK_FAIL;
+    }
+    exchange_ = std::move(exchange);
+    int ret = AgreeOnKnobs();
+    if (ret != TILEXR_SUCCESS) return ret;
+    hostArgs_ = new CommArgs();
+    if (isHostMemory()) {
+        ret = AllocateWindow();
+        if (ret != TILEXR_SUCCESS) return ret;
+        ret = MapHostMemoryWindows();
+        if (ret != TILEXR_SUCCESS) return ret;
+        FillCommArgs();
+        devArgs_ = nullptr;
+        initialized_ = true;
+        return TILEXR_SUCCESS;
+    }
+    TXR_CUDA(cudaGetDevice(&device_));
+    ret = AllocateWindow();
+    if (ret != TILEXR_SUCCESS) return ret;
+    ret = ExchangeWindows();
+    if (ret != TILEXR_SUCCESS) return ret;
+    TXR_CUDA(cudaMalloc(reinterpret_cast<void **>(&devArgs_), sizeof(CommArgs)));
+    TXR_CUDA(cudaMemset(devArgs_, 0, sizeof(CommArgs)));
+    TXR_CUDA(cudaMalloc(reinterpret_cast<void **>(&devRegistry_), sizeof(TileXRRegistry)));
+    TXR_CUDA(cudaMemcpy(devRegistry_, &registry_, sizeof(TileXRRegistry), cudaMemcpyHostToDevice));
+    TXR_CUDA(cudaMalloc(&localCopyWorkspace_, 4096));
+    TXR_CUDA(cudaStreamCreateWithFlags(&copyStream_, cudaStreamNonBlocking));
+    TXR_CUDA(cudaEventCreateWithFlags(&copyEventIn_, cudaEventDisableTiming));
+    TXR_CUDA(cudaEventCreateWithFlags(&copyEventOut_, cudaEventDisableTiming));
+    FillCommArgs();
+    ret = SyncCommArgs();
+    if (ret != TILEXR_SUCCESS) return ret;
+    initialized_ = true;
+    TILEXR_LOG(INFO) << "rank " << rank_ << "/" << rankSize_ << " ready on device " << device_ << ", window "
+                     << (windowBytes_ >> 20) << " MiB";
+    return exchange_->Barrier();
+}
+
+int TileXRComm::InitInWorld(std::shared_ptr<EmulatedWorld> world, int device)
+{
+    world_ = std::move(world);
+    device_ = device;
+    hostArgs_ = new CommArgs();
+    TXR_CUDA(cudaSetDevice(device_));
+    int ret = AllocateWindow();
+    if (ret != TILEXR_SUCCESS) return ret;
+    world_->comms[rank_] = this;
+    return TILEXR_SUCCESS;
+}
+
+int TileXRComm::FinishWorldInit()
+{
+    TXR_CUDA(cudaSetDevice(device_));
+    peerWindows_.assign(rankSize_, nullptr);
+    for (int r = 0; r < rankSize_; ++r) {
+        TileXRComm *peer = world_->comms[r];
+        if (peer == nullptr || peer->window_ == nullptr) return TILEXR_ERROR_INTERNAL;
+        if (peer->device_ != device_) {
+            cudaError_t e = cudaDeviceEnablePeerAccess(peer->device_, 0);
+            if (e != cudaSuccess && e != cudaErrorPeerAccessAlreadyEnabled) return TILEXR_ERROR_RUNTIME;
+            cudaGetLastError();
+        }
+        peerWindows_[r] = peer->window_;
+    }
+    TXR_CUDA(cudaMalloc(reinterpret_cast<void **>(&devArgs_), sizeof(CommArgs)));
+    TXR_CUDA(cudaMemset(devArgs_, 0, sizeof(CommArgs)));
+    TXR_CUDA(cudaMalloc(reinterpret_cast<void **>(&devRegistry_), sizeof(TileXRRegistry)));
+    TXR_CUDA(cudaMemcpy(devRegistry_, &registry_, sizeof(TileXRRegistry), cudaMemcpyHostToDevice));
+    TXR_CUDA(cudaMalloc(&localCopyWorkspace_, 4096));
+    TXR_CUDA(cudaStreamCreateWithFlags(&copyStream_, cudaStreamNonBlocking));
+    TXR_CUDA(cudaEventCreateWithFlags(&copyEventIn_, cudaEventDisableTiming));
+    TXR_CUDA(cudaEventCreateWithFlags(&copyEventOut_, cudaEventDisableTiming));
+    FillCommArgs();
+    int ret = SyncCommArgs();
+    if (ret != TILEXR_SUCCESS) return ret;
+    initialized_ = true;
+    return TILEXR_SUCCESS;
+}
+
+// ---- registry -------------------------------------------------------------------------------
+
+int TileXRComm::UploadRegistry()
+{
+    uint32_t count = 0;
+    for (uint32_t h = 0; h < regions_.size(); ++h) {
+        const RegionRecord &rec = regions_[h];
+        registry_.regions[h].bytes = rec.live ? rec.bytes : 0;
+        registry_.regions[h].localBase = rec.live ? rec.localBase : nullptr;
+        registry_.regions[h].peerBase = rec.live ? rec.devPeerBase : nullptr;
+        if (rec.live) count = h + 1;
+    }
+    registry_.regionCount = count;
+    hostArgs_->registrationGeneration += 1;
+    if (isHostMemory()) return TILEXR_SUCCESS;
+    TXR_CUDA(cudaMemcpy(devRegistry_, &registry_, sizeof(TileXRRegistry), cudaMemcpyHostToDevice));
+    return SyncCommArgs();
+}
+
+int EmulatedWorld::TryFinalizeRegion(TileXRUDMAMemHandle handle)
+{
+    for (TileXRComm *c : comms) {
+        if (c == nullptr || !c->regions()[handle].live) return TILEXR_SUCCESS;   // not everyone yet
+    }
+    const size_t bytes = comms[0]->regions()[handle].bytes;
+    for (TileXRComm *c : comms) {
+        if (c->regions()[handle].bytes != bytes) {
+            TILEXR_LOG(ERROR) << "ranks registered different sizes under handle " << handle;
+            return TILEXR_ERROR_PARA_CHECK_FAIL;
+        }
+    }
+    for (TileXRComm *c : comms) {
+        RegionRecord &rec = c->regions()[handle];
+        rec.peerBase.resize(rankSize);
+        for (int r = 0; r < rankSize; ++r) rec.peerBase[r] = comms[r]->regions()[handle].localBase;
+        if (cudaMemcpy(rec.devPeerBase, rec.peerBase.data(), sizeof(uint8_t *) * rankSize, cudaMemcpyHostToDevice) !=
+            cudaSuccess) {
+            return TILEXR_ERROR_RUNTIME;
+        }
+        int ret = c->UploadRegistry();
+        if (ret != TILEXR_SUCCESS) return ret;
+    }
+    return TILEXR_SUCCESS;
+}
+
+int TileXRComm::Register(uint8_t *ptr, size_t bytes, bool owned, TileXRUDMAMemHandle *handle)
+{
+    if (!initialized_) return TILEXR_ERROR_NOT_INITIALIZED;
+    if (ptr == nullptr || bytes == 0 || handle == nullptr) return TILEXR_ERROR_PARA_CHECK_FAIL;
+    if ((hostArgs_->extraFlag & TILEXR_FLAG_RMA) == 0) return TILEXR_ERROR_NOT_SUPPORT;
+    uint32_t h = 0;
+    while (h < regions_.size() && regions_[h].live) ++h;
+    if (h == regions_.size()) {
+        TILEXR_LOG(ERROR) << "all " << regions_.size() << " registration slots are in use";
+        return TILEXR_ERROR_INTERNAL;
+    }
+    RegionRecord rec;
+    rec.live = true;
+    rec.ownedAllocation = owned;
+    rec.localBase = ptr;
+    rec.bytes = bytes;
+    rec.peerBase.assign(rankSize_, nullptr);
+    rec.peerBase[rank_] = ptr;
+
+    if (isHostMemory()) {
+        TILEXR_LOG(ERROR) << "host-memory communicators register only memory from TileXRSymmAlloc";
+        return TILEXR_ERROR_NOT_SUPPORT;
+    }
+    TXR_CUDA(cudaSetDevice(device_));
+    TXR_CUDA(cudaMalloc(reinterpret_cast<void **>(&rec.devPeerBase), sizeof(uint8_t *) * rankSize_));
+
+    if (isEmulated()) {
+        regions_[h] = rec;
+        *handle = h;
+        return world_->TryFinalizeRegion(h);
+    }
+
+    RegionInfo mine{};
+    mine.pid = static_cast<int32_t>(getpid());
+    mine.device = device_;
+    mine.rawPtr = reinterpret_cast<uint64_t>(ptr);
+    mine.bytes = bytes;
+    mine.handleIndex = h;
+    mine.valid = 1;
+    if (opt_.mode == CommMode::PROCESS) {
+        uint8_t *base = nullptr;
+        size_t allocBytes = 0;
+        if (AllocationBase(ptr, &base, &allocBytes) != TILEXR_SUCCESS) {
+            mine.valid = 0;
+        } else {
+            mine.offset = static_cast<uint64_t>(ptr - base);
+            if (cudaIpcGetMemHandle(&mine.handle, base) != cudaSuccess) {
+                cudaGetLastError();
+                mine.valid = 0;
+            }
+        }
+    }
+    std::vector<RegionInfo> all(rankSize_);
+    int ret = exchange_->AllGather(&mine, all.data(), sizeof(RegionInfo));
+    if (ret != TILEXR_SUCCESS) return ret;
+    for (int r = 0; r < rankSize_; ++r) {
+        if (!all[r].valid || all[r].bytes != bytes || all[r].handleIndex != h) {
+            TILEXR_LOG(ERROR) << "registration mismatch with rank " << r << " (valid=" << all[r].valid
+                              << " bytes=" << all[r].bytes << " slot=" << all[r].handleIndex << ")";
+            cudaFree(rec.devPeerBase);
+            return TILEXR_ERROR_PARA_CHECK_FAIL;
+        }
+    }
+    for (int r = 0; r < rankSize_; ++r) {
+        if (r == rank_) continue;
+        if (all[r].pid == mine.pid) {
+            rec.peerBase[r] = reinterpret_cast<uint8_t *>(all[r].rawPtr);
+        } else {
+            void *mapped = nullptr;
+            cudaError_t e = cudaIpcOpenMemHandle(&mapped, all[r].handle, cudaIpcMemLazyEnablePeerAccess);
+            if (e != cudaSuccess) {
+                TILEXR_LOG(ERROR) << "cannot map region of rank " << r << ": " << cudaGetErrorString(e);
+                for (void *p : rec.ipcOpened) cudaIpcCloseMemHandle(p);
+                cudaFree(rec.devPeerBase);
+                return TILEXR_ERROR_RUNTIME;
+            }
+            rec.ipcOpened.push_back(mapped);
+            rec.peerBase[r] = static_cast<uint8_t *>(mapped) + all[r].offset;
+        }
+    }
+    TXR_CUDA(cudaMemcpy(rec.devPeerBase, rec.peerBase.data(), sizeof(uint8_t *) * rankSize_, cudaMemcpyHostToDevice));
+    regions_[h] = rec;
+    *handle = h;
+    ret = UploadRegistry();
+    if (ret != TILEXR_SUCCESS) return ret;
+    return exchange_->Barrier();
+}
+
+int TileXRComm::Unregister(TileXRUDMAMemHandle handle)
+{
+    if (handle >= regions_.size() || !regions_[handle].live) return TILEXR_ERROR_NOT_FOUND;
+    RegionRecord &rec = regions_[handle];
+    if (!isHostMemory()) {
+        cudaSetDevice(device_);
+        for (void *p : rec.ipcOpened) cudaIpcCloseMemHandle(p);
+        if (rec.devPeerBase != nullptr) cudaFree(rec.devPeerBase);
+        if (rec.ownedAllocation && rec.localBase != nullptr) cudaFree(rec.localBase);
+    }
+    rec = RegionRecord();
+    if (initialized_) UploadRegistry();
+    return TILEXR_SUCCESS;
+}
+
+int TileXRComm::FindRegistration(const void *ptr, size_t bytes, TileXRUDMAMemHandle *handle, uint64_t *offset) const
+{
+    const uint8_t *p = static_cast<const uint8_t *>(ptr);
+    for (uint32_t h = 0; h < regions_.size(); ++h) {
+        const RegionRecord &rec = regions_[h];
+        if (!rec.live || rec.peerBase.empty() || rec.peerBase[(rank_ + 1) % rankSize_] == nullptr) continue;
+        if (p >= rec.localBase && p + bytes <= rec.localBase + rec.bytes) {
+            if (handle != nullptr) *handle = h;
+            if (offset != nullptr) *offset = static_cast<uint64_t>(p - rec.localBase);
+            return TILEXR_SUCCESS;
+        }
+    }
+    return TILEXR_ERROR_NOT_FOUND;
+}
+
+// ---- status ---------------------------------------------------------------------------------
+
+int TileXRComm::DeviceStatus(int *status)
+{
+    if (!initialized_) return TILEXR_ERROR_NOT_INITIALIZED;
+    if (!isHostMemory()) {
+        TXR_CUDA(cudaSetDevice(device_));
+        TXR_CUDA(cudaMemcpy(hostArgs_->dfx, devArgs_->dfx, sizeof(hostArgs_->dfx), cudaMemcpyDeviceToHost));
+    }
+    *status = static_cast<int>(hostArgs_->dfx[TILEXR_DFX_FAIL_CODE]);
+    return TILEXR_SUCCESS;
+}
+
+int TileXRComm::ResetStatus()
+{
+    if (!initialized_) return TILEXR_ERROR_NOT_INITIALIZED;
+    if (isHostMemory()) {
+        std::memset(hostArgs_->dfx, 0, sizeof(hostArgs_->dfx));
+        std::memset(window_, 0, TILEXR_CTRL_DONE_WORD * 8);
+    } else {
+        TXR_CUDA(cudaSetDevice(device_));
+        TXR_CUDA(cudaDeviceSynchronize());
+        TXR_CUDA(cudaMemset(devArgs_->dfx, 0, sizeof(hostArgs_->dfx)));
+        TXR_CUDA(cudaMemset(window_, 0, TILEXR_CTRL_DONE_WORD * 8));
+        TXR_CUDA(cudaDeviceSynchronize());
+    }
+    return isEmulated() ? TILEXR_SUCCESS : HostBarrier();
+}
+
+int TileXRComm::HostBarrier()
+{
+    if (exchange_ == nullptr) return TILEXR_SUCCESS;
+    return exchange_->Barrier();
+}
+
+void TileXRComm::PrintDfx()
+{
+    int status = 0;
+    if (DeviceStatus(&status) != TILEXR_SUCCESS) return;
+    const int64_t *d = hostArgs_->dfx;
+    const char *run = d[TILEXR_DFX_RUN_STATUS] == TILEXR_RUN_STARTED    ? "running"
+                      : d[TILEXR_DFX_RUN_STATUS] == TILEXR_RUN_FINISHED ? "finished"
+                      : d[TILEXR_DFX_RUN_STATUS] == TILEXR_RUN_FAILED   ? "FAILED"
+                                                                        : "idle";
+    std::ostringstream os;
+    os << "DFX rank " << rank_ << ": last op " << TileXROpName(static_cast<int>(d[TILEXR_DFX_OP])) << " magic "
+       << d[TILEXR_DFX_MAGIC] << " count " << d[TILEXR_DFX_COUNT_ARG] << " state " << run << " launches "
+       << d[TILEXR_DFX_LAUNCHES];
+    if (d[TILEXR_DFX_FAIL_CODE] != 0) {
+        os << " | failure code " << d[TILEXR_DFX_FAIL_CODE] << " block " << d[TILEXR_DFX_FAIL_BLOCK] << " peer "
+           << d[TILEXR_DFX_FAIL_PEER] << " slot " << d[TILEXR_DFX_FAIL_SLOT] << " expected 0x" << std::hex
+           << d[TILEXR_DFX_FAIL_EXPECTED] << " observed 0x" << d[TILEXR_DFX_FAIL_OBSERVED];
+    }
+    // DFX is asked for explicitly, so it is printed at any log level
+    std::lock_guard<std::mutex> lock(LogMutex());
+    std::fprintf(stdout, "[TileXR] %s\n", os.str().c_str());
+    std::fflush(stdout);
+}
+
+int TileXRComm::LocalCopyAsync(void *dst, const void *src, size_t bytes, cudaStream_t stream)
+{
+    if (!initialized_) return TILEXR_ERROR_NOT_INITIALIZED;
+    if (isHostMemory()) {
+        std::memcpy(dst, src, bytes);
+        return TILEXR_SUCCESS;
+    }
+    if ((hostArgs_->extraFlag & TILEXR_FLAG_LOCAL_COPY) == 0) {
+        TXR_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, stream));
+        return TILEXR_SUCCESS;
+    }
+    TXR_CUDA(cudaEventRecord(copyEventIn_, stream));
+    TXR_CUDA(cudaStreamWaitEvent(copyStream_, copyEventIn_, 0));
+    TXR_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, copyStream_));
+    TXR_CUDA(cudaEventRecord(copyEventOut_, copyStream_));
+    TXR_CUDA(cudaStreamWaitEvent(stream, copyEventOut_, 0));
+    return TILEXR_SUCCESS;
+}
+
+} // namespace TileXR

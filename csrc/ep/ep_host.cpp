@@ -1,0 +1,525 @@
+// Host side of the expert-parallel library: shape validation, window layout, launch.
+// Validation rules follow the reference's memory route (src/ep/host/ep_dispatch_memory_host.cpp:44-107,
+// ep_memory_layout.cpp:67-306) where they still apply on this hardware.
+#include <algorithm>
+#include <cstdlib>
+#include <cstring>
+
+#include "ep_kernels.cuh"
+#include "tilexr_ep.h"
+#include "tilexr_log.h"
+
+using namespace TileXR;
+using namespace TileXREp;
+
+namespace {
+
+uint64_t Align(uint64_t v, uint64_t a) { return (v + a - 1) / a * a; }
+
+long EnvLong(const char *name, long fallback)
+{
+    const char *v = std::getenv(name);
+    if (v == nullptr || *v == '\0') return fallback;
+    char *end = nullptr;
+    const long x = std::strtol(v, &end, 10);
+    return *end == '\0' ? x : fallback;
+}
+
+bool DispatchLayout(int64_t h, int64_t numExperts, int64_t rankSize, int64_t maxRecvRows, int64_t quantMode,
+                    int64_t elemSize, int64_t grid, bool zeroCopy, EpDispatchWindow *win)
+{
+    if (h <= 0 || numExperts <= 0 || rankSize <= 0 || maxRecvRows <= 0 || grid <= 0) return false;
+    const bool quant = quantMode == TILEXR_EP_QUANT_FP8_1X128;
+    win->rowBytes = static_cast<uint32_t>(quant ? h : h * elemSize);
+    win->scaleRowBytes = quant ? static_cast<uint32_t>(h / 128 * 4) : 0;
+    uint64_t off = 0;
+    win->payloadOff = off;
+    if (!zeroCopy) off = Align(off + static_cast<uint64_t>(maxRecvRows) * win->rowBytes, 256);
+    win->scalesOff = off;
+    off = Align(off + static_cast<uint64_t>(maxRecvRows) * win->scaleRowBytes, 256);
+    win->assistOff = off;
+    off = Align(off + static_cast<uint64_t>(maxRecvRows) * 16, 256);
+    win->countOff = off;
+    off = Align(off + static_cast<uint64_t>(rankSize) * numExperts * 4, 256);
+    win->blockCountOff = off;
+    off = Align(off + static_cast<uint64_t>(grid) * numExperts * 4, 256);
+    win->totalBytes = off;
+    return true;
+}
+
+struct Ctx {
+    TileXRCommArgs *hostArgs = nullptr;
+    GM_ADDR devArgs = nullptr;
+    int rank = 0, rankSize = 0;
+};
+
+int Prepare(TileXRCommPtr comm, Ctx *c)
+{
+    if (comm == nullptr) return TILEXR_ERROR_NOT_INITIALIZED;
+    int ret = TileXRGetCommArgsHost(comm, &c->hostArgs);
+    if (ret != TILEXR_SUCCESS) return ret;
+    ret = TileXRGetCommArgsDev(comm, &c->devArgs);
+    if (ret != TILEXR_SUCCESS) return ret;
+    if (c->hostArgs->extraFlag & TILEXR_FLAG_HOST_MEMORY) return TILEXR_ERROR_NOT_SUPPORT;
+    c->rank = c->hostArgs->rank;
+    c->rankSize = c->hostArgs->rankSize;
+    return TILEXR_SUCCESS;
+}
+
+int ValidateShape(int64_t bs, int64_t h, int64_t topK, int64_t moeExpertNum, int rankSize, int dtype)
+{
+    if (dtype != TILEXR_DATA_TYPE_FP16 && dtype != TILEXR_DATA_TYPE_BFP16) {
+        TILEXR_LOG(ERROR) << "EP: x must be fp16 or bf16";
+        return TILEXR_ERROR_PARA_CHECK_FAIL;
+    }
+    if (bs <= 0 || h <= 0 || topK <= 0 || moeExpertNum <= 0) {
+        TILEXR_LOG(ERROR) << "EP: bs, h, topK and moeExpertNum must be positive";
+        return TILEXR_ERROR_PARA_CHECK_FAIL;
+    }
+    if (topK > EP_MAX_TOPK || topK > moeExpertNum || moeExpertNum > EP_MAX_EXPERTS) {
+        TILEXR_LOG(ERROR) << "EP: topK <= " << EP_MAX_TOPK << ", topK <= experts <= " << EP_MAX_EXPERTS << " required";
+        return TILEXR_ERROR_PARA_CHECK_FAIL;
+    }
+    if (moeExpertNum % rankSize != 0) {
+        TILEXR_LOG(ERROR) << "EP: " << moeExpertNum << " experts do not divide over " << rankSize << " ranks";
+        return TILEXR_ERROR_PARA_CHECK_FAIL;
+    }
+    if ((h * 2) % 16 != 0) {
+        TILEXR_LOG(ERROR) << "EP: hidden size must be a multiple of 8 elements";
+        return TILEXR_ERROR_PARA_CHECK_FAIL;
+    }
+    if (bs * topK > TILEXR_FLAG_OP_SLOTS) {
+        TILEXR_LOG(ERROR) << "EP: bs*topK exceeds the " << TILEXR_FLAG_OP_SLOTS << " slot flags of a window";
+        return TILEXR_ERROR_PARA_CHECK_FAIL;
+    }
+    return TILEXR_SUCCESS;
+}
+
+} // namespace
+
+extern "C" {
+
+uint64_t TileXREpDispatchWindowBytes(int64_t bs, int64_t h, int64_t topK, int64_t moeExpertNum, int64_t rankSize,
+                                     int64_t maxRecvRows, int64_t quantMode, int64_t elemSize, int64_t grid, int zeroCopy)
+{
+    (void)bs;
+    (void)topK;
+    EpDispatchWindow win;
+    if (!DispatchLayout(h, moeExpertNum, rankSize, maxRecvRows, quantMode, elemSize, grid, zeroCopy != 0, &win)) return 0;
+    return win.totalBytes;
+}
+
+uint64_t TileXREpCombineWindowBytes(int64_t bs, int64_t h, int64_t topK, int64_t elemSize)
+{
+    if (bs <= 0 || h <= 0 || topK <= 0 || elemSize <= 0) return 0;
+    return static_cast<uint64_t>(bs) * topK * h * elemSize;
+}
+
+int TileXRMoeEpDispatchFused(const TileXREpDispatchParams *p, TileXRCommPtr comm, TileXRStream stream)
+{
+    Ctx c;
+    int ret = Prepare(comm, &c);
+    if (ret != TILEXR_SUCCESS) return ret;
+    if (p == nullptr || p->x == nullptr || p->expandXOut == nullptr || p->assistInfoForCombineOut == nullptr ||
+        p->expertTokenNumsOut == nullptr || p->sendCountsOut == nullptr) {
+        TILEXR_LOG(ERROR) << "EP dispatch: null tensor";
+        return TILEXR_ERROR_PARA_CHECK_FAIL;
+    }
+    if ((p->expertIds == nullptr) == (p->gateLogits == nullptr)) {
+        TILEXR_LOG(ERROR) << "EP dispatch: give either expertIds or gateLogits";
+        return TILEXR_ERROR_PARA_CHECK_FAIL;
+    }
+    if (p->gateLogits != nullptr && (p->topkIdsOut == nullptr || p->topkWeightsOut == nullptr)) {
+        TILEXR_LOG(ERROR) << "EP dispatch: fused routing needs topkIdsOut and topkWeightsOut";
+        return TILEXR_ERROR_PARA_CHECK_FAIL;
+    }
+    ret = ValidateShape(p->bs, p->h, p->topK, p->moeExpertNum, c.rankSize, p->dtype);
+    if (ret != TILEXR_SUCCESS) return ret;
+    if (p->quantMode != TILEXR_EP_QUANT_NONE && p->quantMode != TILEXR_EP_QUANT_FP8_1X128) {
+        TILEXR_LOG(ERROR) << "EP dispatch: quantMode " << p->quantMode << " is not fused into dispatch (use NONE or FP8_1X128; "
+                          << "MXFP8 is available as TileXRMxfp8Quant)";
+        return TILEXR_ERROR_NOT_SUPPORT;
+    }
+    if (p->quantMode == TILEXR_EP_QUANT_FP8_1X128) {
+        if (p->dynamicScalesOut == nullptr || p->h % 512 != 0 || p->h > EP_FP8_MAX_H) {
+            TILEXR_LOG(ERROR) << "EP dispatch: fp8 mode needs dynamicScalesOut and h a multiple of 512 up to " << EP_FP8_MAX_H;
+            return TILEXR_ERROR_PARA_CHECK_FAIL;
+        }
+    }
+    if (p->activeMaskType != TILEXR_EP_ACTIVE_MASK_NONE && p->xActiveMask == nullptr) return TILEXR_ERROR_PARA_CHECK_FAIL;
+    if (p->activeMaskType < 0 || p->activeMaskType > TILEXR_EP_ACTIVE_MASK_EXPERT) return TILEXR_ERROR_PARA_CHECK_FAIL;
+    if (p->maxRecvRows <= 0) return TILEXR_ERROR_PARA_CHECK_FAIL;
+
+    // grid: one block per ~8 tokens per warp-set, capped by what can be co-resident
+    const int ranksPerDevice = (c.hostArgs->extraFlag & TILEXR_FLAG_EMULATED) ? c.rankSize : 1;
+    const int64_t wantBlocks = std::max<int64_t>(1, std::min<int64_t>((p->bs + 15) / 16, EnvLong("TILEXR_EP_BLOCKS", 128)));
+    unsigned grid = static_cast<unsigned>(wantBlocks);
+    uint32_t tokensPerBlock = 0;
+    size_t smem = 0;
+    for (;;) {
+        tokensPerBlock = static_cast<uint32_t>((p->bs + grid - 1) / grid);
+        if (static_cast<int64_t>(tokensPerBlock) * p->topK > EP_MAX_ROUTES_PER_BLOCK) {
+            TILEXR_LOG(ERROR) << "EP dispatch: " << tokensPerBlock << " tokens per block exceed the per-block route table; "
+                              << "raise TILEXR_EP_BLOCKS";
+            return TILEXR_ERROR_NOT_SUPPORT;
+        }
+        smem = EpDispatchSmemBytes(static_cast<int>(p->moeExpertNum), static_cast<int>(tokensPerBlock * p->topK));
+        unsigned maxGrid = 0;
+        ret = MaxCooperativeGrid(comm, EpDispatchKernelEntry(), EP_BLOCK_THREADS, smem, ranksPerDevice, &maxGrid);
+        if (ret != TILEXR_SUCCESS) return ret;
+        if (maxGrid == 0) return TILEXR_ERROR_NOT_SUPPORT;
+        if (grid <= maxGrid) break;
+        grid = maxGrid;
+    }
+    grid = static_cast<unsigned>((p->bs + tokensPerBlock - 1) / tokensPerBlock);
+
+    const size_t elemSize = TileXRDataTypeSize(p->dtype);
+    const bool quant = p->quantMode == TILEXR_EP_QUANT_FP8_1X128;
+    const uint64_t outBytes = static_cast<uint64_t>(p->maxRecvRows) * (quant ? p->h : p->h * elemSize);
+    TileXRUDMAMemHandle handle = 0;
+    uint64_t regionOffset = 0;
+    const bool zeroCopy = EnvLong("TILEXR_EP_ZERO_COPY", 1) != 0 &&
+                          TileXRFindRegistration(comm, p->expandXOut, outBytes, &handle, &regionOffset) == TILEXR_SUCCESS;
+
+    EpDispatchArgs a;
+    std::memset(&a, 0, sizeof(a));
+    if (!DispatchLayout(p->h, p->moeExpertNum, c.rankSize, p->maxRecvRows, p->quantMode, elemSize, grid, zeroCopy, &a.win)) {
+        return TILEXR_ERROR_PARA_CHECK_FAIL;
+    }
+    if (a.win.totalBytes > c.hostArgs->dataHalfBytes) {
+        TILEXR_LOG(ERROR) << "EP dispatch needs " << a.win.totalBytes << " bytes of window per half, the communicator has "
+                          << c.hostArgs->dataHalfBytes << "; create it with a larger buffer or register expandXOut";
+        return TILEXR_ERROR_PARA_CHECK_FAIL;
+    }
+    a.x = static_cast<const uint8_t *>(p->x);
+    a.expertIds = p->expertIds;
+    a.gateLogits = p->gateLogits;
+    a.selectionBias = p->selectionBias;
+    a.activeMask = reinterpret_cast<const uint8_t *>(p->xActiveMask);
+    a.topkIdsOut = p->topkIdsOut;
+    a.topkWeightsOut = p->topkWeightsOut;
+    a.expandXOut = static_cast<uint8_t *>(p->expandXOut);
+    a.dynamicScalesOut = p->dynamicScalesOut;
+    a.assistOut = p->assistInfoForCombineOut;
+    a.expertTokenNumsOut = p->expertTokenNumsOut;
+    a.sendCountsOut = p->sendCountsOut;
+    a.recvTotalOut = p->recvTotalOut;
+    a.comm = reinterpret_cast<CommArgs *>(c.devArgs);
+    a.bs = static_cast<int32_t>(p->bs);
+    a.h = static_cast<int32_t>(p->h);
+    a.topK = static_cast<int32_t>(p->topK);
+    a.numExperts = static_cast<int32_t>(p->moeExpertNum);
+    a.expertsPerRank = static_cast<int32_t>(p->moeExpertNum / c.rankSize);
+    a.maskType = static_cast<int32_t>(p->activeMaskType);
+    a.quantMode = static_cast<int32_t>(p->quantMode);
+    a.scoreFunc = static_cast<int32_t>(p->scoreFunc);
+    a.renormalize = static_cast<int32_t>(p->renormalize);
+    a.tokenNumsType = static_cast<int32_t>(p->expertTokenNumsType);
+    a.routedScale = p->routedScalingFactor == 0.f ? 1.0f : p->routedScalingFactor;
+    a.maxRecvRows = static_cast<uint32_t>(p->maxRecvRows);
+    a.tokensPerBlock = tokensPerBlock;
+    a.elemSize = static_cast<uint32_t>(elemSize);
+    a.isBf16 = p->dtype == TILEXR_DATA_TYPE_BFP16 ? 1u : 0u;
+    a.zeroCopy = zeroCopy ? 1u : 0u;
+    a.outHandle = handle;
+    a.outOffset = regionOffset;
+    int64_t magic = 0;
+    ret = TileXRCommNextMagic(comm, &magic);
+    if (ret != TILEXR_SUCCESS) return ret;
+    a.magic = magic;
+    LaunchConfig cfg{grid, EP_BLOCK_THREADS, smem, true};
+    return LaunchKernel(comm, EpDispatchKernelEntry(), &a, cfg, stream);
+}
+
+int TileXRMoeEpCombineFused(const TileXREpCombineParams *p, TileXRCommPtr comm, TileXRStream stream)
+{
+    Ctx c;
+    int ret = Prepare(comm, &c);
+    if (ret != TILEXR_SUCCESS) return ret;
+    if (p == nullptr || p->expertOut == nullptr || p->assistInfoForCombine == nullptr || p->sendCounts == nullptr ||
+        p->yOut == nullptr) {
+        TILEXR_LOG(ERROR) << "EP combine: null tensor";
+        return TILEXR_ERROR_PARA_CHECK_FAIL;
+    }
+    ret = ValidateShape(p->bs, p->h, p->topK, p->moeExpertNum, c.rankSize, p->dtype);
+    if (ret != TILEXR_SUCCESS) return ret;
+    if (p->activeMaskType != TILEXR_EP_ACTIVE_MASK_NONE && p->xActiveMask == nullptr) return TILEXR_ERROR_PARA_CHECK_FAIL;
+    const uint64_t need = TileXREpCombineWindowBytes(p->bs, p->h, p->topK, 2);
+    if (need > c.hostArgs->dataHalfBytes) {
+        TILEXR_LOG(ERROR) << "EP combine needs " << need << " bytes of window per half, the communicator has "
+                          << c.hostArgs->dataHalfBytes;
+        return TILEXR_ERROR_PARA_CHECK_FAIL;
+    }
+    EpCombineArgs a;
+    std::memset(&a, 0, sizeof(a));
+    a.expertOut = static_cast<const uint8_t *>(p->expertOut);
+    a.assist = p->assistInfoForCombine;
+    a.sendCounts = p->sendCounts;
+    a.expertIds = p->expertIds;
+    a.expertScales = p->expertScales;
+    a.activeMask = reinterpret_cast<const uint8_t *>(p->xActiveMask);
+    a.sharedExpertX = static_cast<const uint8_t *>(p->sharedExpertX);
+    a.yOut = static_cast<uint8_t *>(p->yOut);
+    a.comm = reinterpret_cast<CommArgs *>(c.devArgs);
+    a.bs = static_cast<int32_t>(p->bs);
+    a.h = static_cast<int32_t>(p->h);
+    a.topK = static_cast<int32_t>(p->topK);
+    a.numExperts = static_cast<int32_t>(p->moeExpertNum);
+    a.expertsPerRank = static_cast<int32_t>(p->moeExpertNum / c.rankSize);
+    a.maskType = static_cast<int32_t>(p->activeMaskType);
+    a.rowBytes = static_cast<uint32_t>(p->h * 2);
+    a.isBf16 = p->dtype == TILEXR_DATA_TYPE_BFP16 ? 1u : 0u;
+    a.sendCountEntries = static_cast<uint32_t>(p->moeExpertNum / c.rankSize * c.rankSize);
+    int64_t magic = 0;
+    ret = TileXRCommNextMagic(comm, &magic);
+    if (ret != TILEXR_SUCCESS) return ret;
+    a.magic = magic;
+    const int ranksPerDevice = (c.hostArgs->extraFlag & TILEXR_FLAG_EMULATED) ? c.rankSize : 1;
+    unsigned maxGrid = 0;
+    ret = MaxCooperativeGrid(comm, EpCombineKernelEntry(), EP_BLOCK_THREADS, 0, ranksPerDevice, &maxGrid);
+    if (ret != TILEXR_SUCCESS) return ret;
+    const int64_t want = std::min<int64_t>(EnvLong("TILEXR_EP_BLOCKS", 128), std::max<int64_t>(1, (p->bs * p->topK + 15) / 16));
+    const unsigned grid = static_cast<unsigned>(std::max<int64_t>(1, std::min<int64_t>(want, maxGrid)));
+    LaunchConfig cfg{grid, EP_BLOCK_THREADS, 0, true};
+    return LaunchKernel(comm, EpCombineKernelEntry(), &a, cfg, stream);
+}
+
+// ---- reference-shaped wrappers -----------------------------------------------------------------------------
+
+int TileXRMoeEpDispatchMemoryV2(void *x, int32_t *expertIds, void *scales, bool *xActiveMask, int64_t activeMaskType,
+                                void *expertScales, TileXRCommPtr comm, int64_t bs, int64_t h, int64_t topK,
+                                int64_t moeExpertNum, int64_t epWorldSize, int64_t epRankId, int64_t tpWorldSize,
+                                int64_t tpRankId, int64_t expertShardType, int64_t sharedExpertNum,
+                                int64_t sharedExpertRankNum, int64_t quantMode, int64_t globalBs,
+                                int64_t expertTokenNumsType, void *expandXOut, void *dynamicScalesOut,
+                                int32_t *assistInfoForCombineOut, int64_t *expertTokenNumsOut, int32_t *sendCountsOut,
+                                int32_t *tpRecvCountsOut, void *expandScalesOut, TileXRDataType dtype,
+                                TileXRDataType expandXOutDtype, TileXRStream stream)
+{
+    (void)expertScales;
+    (void)tpRankId;
+    (void)expertShardType;
+    (void)tpRecvCountsOut;
+    (void)expandScalesOut;
+    Ctx c;
+    int ret = Prepare(comm, &c);
+    if (ret != TILEXR_SUCCESS) return ret;
+    if (scales != nullptr) {
+        TILEXR_LOG(ERROR) << "EP dispatch: static scales are not supported (the reference rejects them too)";
+        return TILEXR_ERROR_NOT_SUPPORT;
+    }
+    if (tpWorldSize > 1) {
+        TILEXR_LOG(ERROR) << "EP dispatch: tpWorldSize must be 1";
+        return TILEXR_ERROR_NOT_SUPPORT;
+    }
+    if (sharedExpertNum != 0 || sharedExpertRankNum != 0) {
+        TILEXR_LOG(ERROR) << "EP dispatch: dedicated shared-expert ranks are not supported; add the shared expert's "
+                          << "output through sharedExpertX in combine";
+        return TILEXR_ERROR_NOT_SUPPORT;
+    }
+    if (epWorldSize != c.rankSize || epRankId != c.rank) return TILEXR_ERROR_PARA_CHECK_FAIL;
+    if (globalBs != 0 && globalBs != bs * c.rankSize) {
+        TILEXR_LOG(ERROR) << "EP dispatch: globalBs must be bs * epWorldSize";
+        return TILEXR_ERROR_PARA_CHECK_FAIL;
+    }
+    if (quantMode != TILEXR_EP_QUANT_NONE && expandXOutDtype != TILEXR_DATA_TYPE_FP8E4M3) return TILEXR_ERROR_PARA_CHECK_FAIL;
+    TileXREpDispatchParams p;
+    std::memset(&p, 0, sizeof(p));
+    p.x = x;
+    p.expertIds = expertIds;
+    p.xActiveMask = xActiveMask;
+    p.activeMaskType = activeMaskType;
+    p.bs = bs;
+    p.h = h;
+    p.topK = topK;
+    p.moeExpertNum = moeExpertNum;
+    p.quantMode = quantMode;
+    p.expertTokenNumsType = expertTokenNumsType;
+    p.maxRecvRows = bs * c.rankSize * std::min<int64_t>(topK, moeExpertNum / c.rankSize);   // worst case, as the reference sizes it
+    p.expandXOut = expandXOut;
+    p.dynamicScalesOut = static_cast<float *>(dynamicScalesOut);
+    p.assistInfoForCombineOut = assistInfoForCombineOut;
+    p.expertTokenNumsOut = expertTokenNumsOut;
+    p.sendCountsOut = sendCountsOut;
+    p.dtype = dtype;
+    return TileXRMoeEpDispatchFused(&p, comm, stream);
+}
+
+int TileXRMoeEpDispatchMemory(void *x, int32_t *expertIds, TileXRCommPtr comm, int64_t bs, int64_t h, int64_t topK,
+                              int64_t moeExpertNum, void *expandXOut, int64_t *expertTokenNumsOut, int32_t *sendCountsOut,
+                              int32_t *assistInfoForCombineOut, TileXRDataType dtype, TileXRStream stream)
+{
+    Ctx c;
+    int ret = Prepare(comm, &c);
+    if (ret != TILEXR_SUCCESS) return ret;
+    return TileXRMoeEpDispatchMemoryV2(x, expertIds, nullptr, nullptr, TILEXR_EP_ACTIVE_MASK_NONE, nullptr, comm, bs, h, topK,
+                                       moeExpertNum, c.rankSize, c.rank, 1, 0, 0, 0, 0, TILEXR_EP_QUANT_NONE, bs * c.rankSize,
+                                       TILEXR_EP_TOKEN_NUMS_COUNT, expandXOut, nullptr, assistInfoForCombineOut,
+                                       expertTokenNumsOut, sendCountsOut, nullptr, nullptr, dtype, dtype, stream);
+}
+
+// The reference's slot-window ("MVP") route has the same observable semantics as its memory
+// route; both names run the same kernels here.
+int TileXRMoeEpDispatch(void *x, int32_t *expertIds, TileXRCommPtr comm, int64_t bs, int64_t h, int64_t topK,
+                        int64_t moeExpertNum, void *expandXOut, int64_t *expertTokenNumsOut, int32_t *epRecvCountsOut,
+                        int32_t *assistInfoForCombineOut, TileXRDataType dtype, TileXRStream stream)
+{
+    return TileXRMoeEpDispatchMemory(x, expertIds, comm, bs, h, topK, moeExpertNum, expandXOut, expertTokenNumsOut,
+                                     epRecvCountsOut, assistInfoForCombineOut, dtype, stream);
+}
+
+int TileXRMoeEpDispatchV2(void *x, int32_t *expertIds, void *scales, bool *xActiveMask, void *expertScales,
+                          TileXRCommPtr comm, int64_t bs, int64_t h, int64_t topK, int64_t moeExpertNum,
+                          int64_t epWorldSize, int64_t epRankId, int64_t tpWorldSize, int64_t tpRankId,
+                          int64_t expertShardType, int64_t sharedExpertNum, int64_t sharedExpertRankNum, int64_t quantMode,
+                          int64_t globalBs, int64_t expertTokenNumsType, void *expandXOut, void *dynamicScalesOut,
+                          int32_t *assistInfoForCombineOut, int64_t *expertTokenNumsOut, int32_t *epRecvCountsOut,
+                          int32_t *tpRecvCountsOut, void *expandScalesOut, void *workspace, TileXRDataType dtype,
+                          TileXRStream stream)
+{
+    (void)workspace;
+    return TileXRMoeEpDispatchMemoryV2(x, expertIds, scales, xActiveMask,
+                                       xActiveMask != nullptr ? TILEXR_EP_ACTIVE_MASK_TOKEN : TILEXR_EP_ACTIVE_MASK_NONE,
+                                       expertScales, comm, bs, h, topK, moeExpertNum, epWorldSize, epRankId, tpWorldSize,
+                                       tpRankId, expertShardType, sharedExpertNum, sharedExpertRankNum, quantMode, globalBs,
+                                       expertTokenNumsType, expandXOut, dynamicScalesOut, assistInfoForCombineOut,
+                                       expertTokenNumsOut, epRecvCountsOut, tpRecvCountsOut, expandScalesOut, dtype,
+                                       quantMode == TILEXR_EP_QUANT_NONE ? dtype : TILEXR_DATA_TYPE_FP8E4M3, stream);
+}
+
+int TileXRMoeEpCombineMemoryV2(void *expertOut, int32_t *assistInfoForCombine, int32_t *sendCounts, float *expertScales,
+                               bool *xActiveMask, int64_t activeMaskType, void *sharedExpertX, TileXRCommPtr comm,
+                               int64_t bs, int64_t h, int64_t topK, int64_t moeExpertNum, int64_t epWorldSize,
+                               int64_t epRankId, int64_t tpWorldSize, int64_t tpRankId, int64_t expertShardType,
+                               int64_t sharedExpertNum, int64_t sharedExpertRankNum, int64_t quantMode, int64_t globalBs,
+                               void *yOut, TileXRDataType dtype, TileXRStream stream)
+{
+    (void)tpRankId;
+    (void)expertShardType;
+    (void)globalBs;
+    Ctx c;
+    int ret = Prepare(comm, &c);
+    if (ret != TILEXR_SUCCESS) return ret;
+    if (tpWorldSize > 1 || sharedExpertNum != 0 || sharedExpertRankNum != 0) return TILEXR_ERROR_NOT_SUPPORT;
+    if (quantMode != TILEXR_EP_QUANT_NONE) {
+        TILEXR_LOG(ERROR) << "EP combine: rows travel in their own dtype; communication quantisation is not supported";
+        return TILEXR_ERROR_NOT_SUPPORT;
+    }
+    if (epWorldSize != c.rankSize || epRankId != c.rank) return TILEXR_ERROR_PARA_CHECK_FAIL;
+    TileXREpCombineParams p;
+    std::memset(&p, 0, sizeof(p));
+    p.expertOut = expertOut;
+    p.assistInfoForCombine = assistInfoForCombine;
+    p.sendCounts = sendCounts;
+    p.expertScales = expertScales;
+    p.xActiveMask = xActiveMask;
+    p.activeMaskType = activeMaskType;
+    p.sharedExpertX = sharedExpertX;
+    p.bs = bs;
+    p.h = h;
+    p.topK = topK;
+    p.moeExpertNum = moeExpertNum;
+    p.yOut = yOut;
+    p.dtype = dtype;
+    return TileXRMoeEpCombineFused(&p, comm, stream);
+}
+
+int TileXRMoeEpCombineMemory(void *expertOut, int32_t *assistInfoForCombine, int32_t *epRecvCounts, TileXRCommPtr comm,
+                             int64_t bs, int64_t h, int64_t topK, int64_t moeExpertNum, void *yOut, TileXRDataType dtype,
+                             TileXRStream stream)
+{
+    Ctx c;
+    int ret = Prepare(comm, &c);
+    if (ret != TILEXR_SUCCESS) return ret;
+    return TileXRMoeEpCombineMemoryV2(expertOut, assistInfoForCombine, epRecvCounts, nullptr, nullptr,
+                                      TILEXR_EP_ACTIVE_MASK_NONE, nullptr, comm, bs, h, topK, moeExpertNum, c.rankSize, c.rank,
+                                      1, 0, 0, 0, 0, TILEXR_EP_QUANT_NONE, bs * c.rankSize, yOut, dtype, stream);
+}
+
+int TileXRMoeEpCombine(void *expertOut, int32_t *assistInfoForCombine, int32_t *epRecvCounts, TileXRCommPtr comm,
+                       int64_t bs, int64_t h, int64_t topK, int64_t moeExpertNum, void *yOut, TileXRDataType dtype,
+                       TileXRStream stream)
+{
+    return TileXRMoeEpCombineMemory(expertOut, assistInfoForCombine, epRecvCounts, comm, bs, h, topK, moeExpertNum, yOut, dtype,
+                                    stream);
+}
+
+int TileXRMoeEpCombineV2(void *expertOut, int32_t *assistInfoForCombine, int32_t *epRecvCounts, TileXRCommPtr comm,
+                         int64_t bs, int64_t h, int64_t topK, int64_t moeExpertNum, void *yOut, void *workspace,
+                         TileXRDataType dtype, TileXRStream stream)
+{
+    (void)workspace;
+    return TileXRMoeEpCombineMemory(expertOut, assistInfoForCombine, epRecvCounts, comm, bs, h, topK, moeExpertNum, yOut, dtype,
+                                    stream);
+}
+
+// ---- stand-alone ops ------------------------------------------------------------------------------------------
+
+int TileXRMoeRoutingTopK(const float *gateLogits, const float *selectionBias, int64_t bs, int64_t moeExpertNum,
+                         int64_t topK, int64_t scoreFunc, int64_t renormalize, float routedScalingFactor,
+                         int32_t *topkIdsOut, float *topkWeightsOut, TileXRStream stream)
+{
+    if (gateLogits == nullptr || topkIdsOut == nullptr || topkWeightsOut == nullptr || bs <= 0 || moeExpertNum <= 0 ||
+        moeExpertNum > EP_MAX_EXPERTS || topK <= 0 || topK > EP_MAX_TOPK || topK > moeExpertNum ||
+        (scoreFunc != TILEXR_EP_SCORE_SOFTMAX && scoreFunc != TILEXR_EP_SCORE_SIGMOID)) {
+        return TILEXR_ERROR_PARA_CHECK_FAIL;
+    }
+    RoutingArgs a{gateLogits, selectionBias, topkIdsOut, topkWeightsOut, static_cast<int32_t>(bs),
+                  static_cast<int32_t>(moeExpertNum), static_cast<int32_t>(topK), static_cast<int32_t>(scoreFunc),
+                  static_cast<int32_t>(renormalize), routedScalingFactor == 0.f ? 1.0f : routedScalingFactor};
+    return LaunchRoutingTopK(a, stream);
+}
+
+static bool HalfType(int dtype) { return dtype == TILEXR_DATA_TYPE_FP16 || dtype == TILEXR_DATA_TYPE_BFP16; }
+
+int TileXRFp8Quant1x128(const void *x, int64_t rows, int64_t h, TileXRDataType dtype, void *yOut, float *scalesOut,
+                        TileXRStream stream)
+{
+    if (x == nullptr || yOut == nullptr || scalesOut == nullptr || rows <= 0 || h <= 0 || h % 128 != 0 || !HalfType(dtype)) {
+        return TILEXR_ERROR_PARA_CHECK_FAIL;
+    }
+    return LaunchFp8Quant1x128(x, rows, h, dtype == TILEXR_DATA_TYPE_BFP16, yOut, scalesOut, stream);
+}
+
+int TileXRFp8Dequant1x128(const void *y, const float *scales, int64_t rows, int64_t h, TileXRDataType dtype, void *xOut,
+                          TileXRStream stream)
+{
+    if (y == nullptr || xOut == nullptr || scales == nullptr || rows <= 0 || h <= 0 || h % 128 != 0 || !HalfType(dtype)) {
+        return TILEXR_ERROR_PARA_CHECK_FAIL;
+    }
+    return LaunchFp8Dequant1x128(y, scales, rows, h, dtype == TILEXR_DATA_TYPE_BFP16, xOut, stream);
+}
+
+int TileXRMxfp8Quant(const void *x, int64_t rows, int64_t h, TileXRDataType dtype, TileXRDataType fp8Type, void *yOut,
+                     uint8_t *scalesOut, TileXRStream stream)
+{
+    if (x == nullptr || yOut == nullptr || scalesOut == nullptr || rows <= 0 || h <= 0 || !HalfType(dtype) ||
+        (fp8Type != TILEXR_DATA_TYPE_FP8E4M3 && fp8Type != TILEXR_DATA_TYPE_FP8E5M2)) {
+        return TILEXR_ERROR_PARA_CHECK_FAIL;
+    }
+    return LaunchMxfp8Quant(x, rows, h, dtype == TILEXR_DATA_TYPE_BFP16, fp8Type == TILEXR_DATA_TYPE_FP8E5M2, yOut, scalesOut,
+                            stream);
+}
+
+int TileXRMxfp8Dequant(const void *y, const uint8_t *scales, int64_t rows, int64_t h, TileXRDataType fp8Type,
+                       TileXRDataType dtype, void *xOut, TileXRStream stream)
+{
+    if (y == nullptr || xOut == nullptr || scales == nullptr || rows <= 0 || h <= 0 || !HalfType(dtype) ||
+        (fp8Type != TILEXR_DATA_TYPE_FP8E4M3 && fp8Type != TILEXR_DATA_TYPE_FP8E5M2)) {
+        return TILEXR_ERROR_PARA_CHECK_FAIL;
+    }
+    return LaunchMxfp8Dequant(y, scales, rows, h, fp8Type == TILEXR_DATA_TYPE_FP8E5M2, dtype == TILEXR_DATA_TYPE_BFP16, xOut,
+                              stream);
+}
+
+int TileXRRmsNorm(const void *x, void *residualInOut, const void *gamma, float eps, int64_t rows, int64_t h,
+                  TileXRDataType dtype, void *yOut, TileXRStream stream)
+{
+    if (x == nullptr || gamma == nullptr || yOut == nullptr || rows <= 0 || h <= 0 || h % 8 != 0 || h > 16384 ||
+        !HalfType(dtype)) {
+        return TILEXR_ERROR_PARA_CHECK_FAIL;
+    }
+    return LaunchRmsNorm(x, residualInOut, gamma, eps, rows, h, dtype == TILEXR_DATA_TYPE_BFP16, yOut, stream);
+}
+
+} // extern "C"

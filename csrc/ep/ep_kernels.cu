@@ -1,0 +1,802 @@
+// Expert-parallel dispatch and combine for sm_100a, plus the local hot ops around them
+// (routing top-k, block-scaled fp8 quantisation, MXFP8, RMSNorm).
+//
+// Dispatch, one cooperative kernel per rank:
+//   1. every block takes a contiguous range of tokens, routes them (top-k over the gate logits,
+//      or reads the given expert ids and masks), and ranks its routes per expert in (token, k)
+//      order; per-block expert counts go to a scratch table;
+//   2. after one barrier among the rank's blocks, block 0 sums the table and pushes the rank's
+//      count vector to every peer (an all-gather of R x E integers).  With everybody's counts
+//      each rank computes, for itself as a sender, the exact row at which each of its routes
+//      lands in the destination's expert-major / source-major layout: rows are placed at their
+//      FINAL position by the sender, the receiver never sorts or compacts;
+//   3. a warp per token quantises the row once (fp8 e4m3, one fp32 scale per 128 elements, kept
+//      in registers) and stores it to each destination together with its scales and the assist
+//      tuple; when the block is done it raises one flag per destination;
+//   4. the receiver waits for the flags of every sender block and copies rows, scales and
+//      tuples from its window to the output tensors (rows are skipped when the output tensor
+//      is registered and was written directly).
+// The reference reaches the same layout with worst-case regions per (source, expert) and a
+// receiver-side compaction (src/ep/kernels/tilexr_ep_dispatch_memory_kernel.h:666-708,
+// 903-1140, 1190-1317); at 4096 tokens x 8 routes that needs gigabytes of window, hence the
+// count-first placement here.
+//
+// Combine: a warp per received row pushes it to slot (token, k) of the source's window and
+// raises that slot's flag; a warp per token waits for its K flags and accumulates
+// weight_k * row_k in fp32 in k order, then rounds once.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+
+#include <cstdio>
+#include <cuda_runtime_api.h>
+
+#include "device/tilexr_rma.cuh"
+#include "device/tilexr_sync.cuh"
+#include "ep_kernels.cuh"
+#include "tilexr_ep.h"
+
+namespace TileXR {
+
+using namespace tilexr;
+
+namespace {
+
+constexpr float FP8_E4M3_MAX = 448.0f;
+constexpr float FP8_AMAX_FLOOR = 1e-4f;
+
+__device__ __forceinline__ float WarpMax(float v)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+__device__ __forceinline__ float WarpSum(float v)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// 8 halfs/bfloats packed in 16 bytes -> 8 floats
+__device__ __forceinline__ void Unpack8(const Vec16 &v, bool bf16, float *f)
+{
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        if (bf16) {
+            f[2 * i] = __uint_as_float(w[i] << 16);
+            f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        } else {
+            const __half2 h2 = *reinterpret_cast<const __half2 *>(&w[i]);
+            const float2 f2 = __half22float2(h2);
+            f[2 * i] = f2.x;
+            f[2 * i + 1] = f2.y;
+        }
+    }
+}
+
+__device__ __forceinline__ Vec16 Pack8(const float *f, bool bf16)
+{
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        if (bf16) {
+            const __nv_bfloat162 b = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+            w[i] = *reinterpret_cast<const uint32_t *>(&b);
+        } else {
+            const __half2 h2 = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+            w[i] = *reinterpret_cast<const uint32_t *>(&h2);
+        }
+    }
+    return Vec16{w[0], w[1], w[2], w[3]};
+}
+
+__device__ __forceinline__ uint32_t Fp8x4(float a, float b, float c, float d)
+{
+    const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+    const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
+    return lo | (hi << 16);
+}
+
+// ---- routing: one warp scores one token and picks its top-k -------------------------------------------
+// Lane l owns experts l, l+32, ...  Selection is by score (+ optional bias), ties go to the
+// lower expert id; the gate weight is the unbiased score, optionally renormalised over the
+// selected experts and multiplied by `routedScale`.
+__device__ __forceinline__ void RouteToken(const float *logits, const float *bias, int numExperts, int topK, int scoreFunc,
+                                           int renormalize, float routedScale, int lane, int32_t *idsOut, float *weightsOut)
+{
+    constexpr int PER_LANE = EP_MAX_EXPERTS / 32;
+    float score[PER_LANE];
+    float sel[PER_LANE];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < PER_LANE; ++j) {
+        const int e = j * 32 + lane;
+        score[j] = e < numExperts ? logits[e] : -INFINITY;
+        mx = fmaxf(mx, score[j]);
+    }
+    if (scoreFunc == TileXREp::TILEXR_EP_SCORE_SOFTMAX) {
+        mx = WarpMax(mx);
+        float sum = 0.f;
+#pragma unroll
+        for (int j = 0; j < PER_LANE; ++j) {
+            const int e = j * 32 + lane;
+            score[j] = e < numExperts ? expf(score[j] - mx) : 0.f;
+            sum += score[j];
+        }
+        sum = WarpSum(sum);
+        const float inv = 1.0f / sum;
+#pragma unroll
+        for (int j = 0; j < PER_LANE; ++j) score[j] *= inv;
+    } else {
+#pragma unroll
+        for (int j = 0; j < PER_LANE; ++j) {
+            const int e = j * 32 + lane;
+            score[j] = e < numExperts ? 1.0f / (1.0f + expf(-score[j])) : 0.f;
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < PER_LANE; ++j) {
+        const int e = j * 32 + lane;
+        sel[j] = e < numExperts ? score[j] + (bias != nullptr ? bias[e] : 0.f) : -INFINITY;
+    }
+    float myWeight = 0.f;   // lane k keeps the k-th pick
+    int myId = -1;
+    float total = 0.f;
+    for (int k = 0; k < topK; ++k) {
+        float best = -INFINITY;
+        int bestE = 0x7fffffff;
+        float bestScore = 0.f;
+#pragma unroll
+        for (int j = 0; j < PER_LANE; ++j) {
+            const int e = j * 32 + lane;
+            if (sel[j] > best) {   // ascending e within a lane: first maximum wins the tie
+                best = sel[j];
+                bestE = e;
+                bestScore = score[j];
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oe = __shfl_xor_sync(0xffffffffu, bestE, o);
+            const float os = __shfl_xor_sync(0xffffffffu, bestScore, o);
+            if (ob > best || (ob == best && oe < bestE)) {
+                best = ob;
+                bestE = oe;
+                bestScore = os;
+            }
+        }
+        if ((bestE & 31) == lane) {
+#pragma unroll
+            for (int j = 0; j < PER_LANE; ++j) {
+                if (j == (bestE >> 5)) sel[j] = -INFINITY;
+            }
+        }
+        if (lane == k) {
+            myWeight = bestScore;
+            myId = bestE;
+        }
+        total += bestScore;
+    }
+    if (lane < topK) {
+        float w = myWeight;
+        if (renormalize) w = w / total;
+        w *= routedScale;
+        idsOut[lane] = myId;
+        weightsOut[lane] = w;
+    }
+}
+
+__global__ void __launch_bounds__(256) RoutingTopKKernel(const RoutingArgs a)
+{
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) / 32;
+    const int lane = threadIdx.x & 31;
+    if (warp >= a.bs) return;
+    RouteToken(a.gateLogits + static_cast<int64_t>(warp) * a.numExperts, a.selectionBias, a.numExperts, a.topK, a.scoreFunc,
+               a.renormalize, a.routedScale, lane, a.topkIdsOut + static_cast<int64_t>(warp) * a.topK,
+               a.topkWeightsOut + static_cast<int64_t>(warp) * a.topK);
+}
+
+// ---- dispatch ---------------------------------------------------------------------------------------------
+
+struct DispatchSmem {
+    int32_t *routeExpert;   // [routesPerBlock]  expert id or -1
+    int32_t *routeRank;     // [routesPerBlock]  rank among the block's routes to the same expert
+    int32_t *hist;          // [E] routes of this block per expert
+    int32_t *blockBase;     // [E] routes of earlier blocks per expert
+    int32_t *total;         // [E] routes of all sources per expert
+    int32_t *dstRow;        // [E] first row, at the owner, of (expert, this source)
+    float *scaleStage;      // [EP_WARPS][64]
+};
+
+__device__ __forceinline__ DispatchSmem CarveSmem(uint8_t *base, int numExperts, int routesPerBlock)
+{
+    DispatchSmem s;
+    s.routeExpert = reinterpret_cast<int32_t *>(base);
+    s.routeRank = s.routeExpert + routesPerBlock;
+    s.hist = s.routeRank + routesPerBlock;
+    s.blockBase = s.hist + numExperts;
+    s.total = s.blockBase + numExperts;
+    s.dstRow = s.total + numExperts;
+    s.scaleStage = reinterpret_cast<float *>(s.dstRow + numExperts);
+    return s;
+}
+
+__device__ void EpDispatchBody(const EpDispatchArgs &a)
+{
+    extern __shared__ __align__(16) uint8_t smemRaw[];
+    Waiter w;
+    bool ok = KernelPrologue(w, a.comm, a.magic, TILEXR_OP_EP_DISPATCH, a.bs, true);
+    CommArgs *comm = a.comm;
+    const int rank = comm->rank;
+    const int R = comm->rankSize;
+    const int E = a.numExperts;
+    const int K = a.topK;
+    const int G = gridDim.x;
+    const int tid = threadIdx.x;
+    const int lane = tid & 31;
+    const int warp = tid >> 5;
+    const uint32_t epoch = w.epoch;
+    const int routesPerBlock = static_cast<int>(a.tokensPerBlock) * K;
+    DispatchSmem sm = CarveSmem(smemRaw, E, routesPerBlock);
+    uint8_t *myHalf = DataHalf(comm, rank, epoch);
+    int32_t *blockCounts = reinterpret_cast<int32_t *>(myHalf + a.win.blockCountOff);
+    const int32_t *countMatrix = reinterpret_cast<const int32_t *>(myHalf + a.win.countOff);
+
+    const int t0 = min(a.bs, static_cast<int>(blockIdx.x * a.tokensPerBlock));
+    const int t1 = min(a.bs, t0 + static_cast<int>(a.tokensPerBlock));
+    const int nTok = t1 - t0;
+    const int nRoutes = nTok * K;
+
+    // ---- 1. route, rank, count --------------------------------------------------------------------
+    for (int e = tid; e < E; e += blockDim.x) sm.hist[e] = 0;
+    for (int i = warp; i < nTok; i += EP_WARPS) {
+        const int t = t0 + i;
+        if (a.gateLogits != nullptr) {
+            RouteToken(a.gateLogits + static_cast<int64_t>(t) * E, a.selectionBias, E, K, a.scoreFunc, a.renormalize,
+                       a.routedScale, lane, a.topkIdsOut + static_cast<int64_t>(t) * K,
+                       a.topkWeightsOut + static_cast<int64_t>(t) * K);
+            __syncwarp();
+        }
+        if (lane < K) {
+            const int32_t *ids = a.gateLogits != nullptr ? a.topkIdsOut : a.expertIds;
+            int e = ids[static_cast<int64_t>(t) * K + lane];
+            if (e < 0 || e >= E) e = -1;
+            if (a.maskType == TileXREp::TILEXR_EP_ACTIVE_MASK_TOKEN && a.activeMask[t] == 0) e = -1;
+            if (a.maskType == TileXREp::TILEXR_EP_ACTIVE_MASK_EXPERT && a.activeMask[static_cast<int64_t>(t) * K + lane] == 0) e = -1;
+            sm.routeExpert[i * K + lane] = e;
+            if (a.gateLogits == nullptr && a.topkIdsOut != nullptr) a.topkIdsOut[static_cast<int64_t>(t) * K + lane] = e;
+        }
+    }
+    __syncthreads();
+    for (int i = tid; i < nRoutes; i += blockDim.x) {
+        const int e = sm.routeExpert[i];
+        int r = 0;
+        if (e >= 0) {
+            for (int j = 0; j < i; ++j) r += (sm.routeExpert[j] == e) ? 1 : 0;
+            atomicAdd(&sm.hist[e], 1);
+        }
+        sm.routeRank[i] = r;
+    }
+    __syncthreads();
+    for (int e = tid; e < E; e += blockDim.x) blockCounts[static_cast<int64_t>(blockIdx.x) * E + e] = sm.hist[e];
+    ok = GridBarrier(w, 0) && ok;
+
+    // ---- 2. publish this rank's counts, learn everybody's ----------------------------------------------
+    if (ok && blockIdx.x == 0) {
+        for (int e = tid; e < E; e += blockDim.x) {
+            int c = 0;
+            for (int b = 0; b < G; ++b) c += blockCounts[static_cast<int64_t>(b) * E + e];
+            for (int i = 0; i < R; ++i) {
+                const int peer = (rank + i) % R;
+                reinterpret_cast<int32_t *>(DataHalf(comm, peer, epoch) + a.win.countOff)[static_cast<int64_t>(rank) * E + e] = c;
+            }
+        }
+        __syncthreads();
+        if (tid < R) {
+            SetFlag(FlagSlot(comm, tid, TILEXR_FLAG_OP_BASE + static_cast<int64_t>(rank) * TILEXR_FLAGS_PER_PAIR + EP_COUNT_FLAG_SLOT),
+                    epoch, 1);
+        }
+    }
+    for (int e = tid; e < E; e += blockDim.x) {
+        int c = 0;
+        for (int b = 0; b < static_cast<int>(blockIdx.x); ++b) c += blockCounts[static_cast<int64_t>(b) * E + e];
+        sm.blockBase[e] = c;
+    }
+    {
+        bool got = true;
+        if (ok && tid < R) {
+            const int64_t slot = TILEXR_FLAG_OP_BASE + static_cast<int64_t>(tid) * TILEXR_FLAGS_PER_PAIR + EP_COUNT_FLAG_SLOT;
+            got = WaitFlagGE(w, FlagSlot(comm, rank, slot), 1, tid, slot);
+        }
+        ok = BlockBroadcastOk(got) && ok;
+    }
+    if (ok) {
+        for (int e = tid; e < E; e += blockDim.x) {
+            int c = 0;
+            for (int s = 0; s < R; ++s) c += countMatrix[static_cast<int64_t>(s) * E + e];
+            sm.total[e] = c;
+        }
+        __syncthreads();
+        for (int e = tid; e < E; e += blockDim.x) {
+            const int first = (e / a.expertsPerRank) * a.expertsPerRank;
+            int row = 0;
+            for (int p = first; p < e; ++p) row += sm.total[p];
+            for (int s = 0; s < rank; ++s) row += countMatrix[static_cast<int64_t>(s) * E + e];
+            sm.dstRow[e] = row;
+        }
+        // Every rank sees the same counts, so every rank reaches the same verdict on overflow.
+        bool fits = true;
+        if (tid < R) {
+            int64_t rows = 0;
+            for (int e = tid * a.expertsPerRank; e < (tid + 1) * a.expertsPerRank; ++e) rows += sm.total[e];
+            fits = rows <= static_cast<int64_t>(a.maxRecvRows);
+            if (!fits) RaiseFailure(w, TILEXR_DEV_BAD_ARGUMENT, tid, 0, a.maxRecvRows, static_cast<uint64_t>(rows));
+        }
+        ok = BlockBroadcastOk(fits);
+    }
+
+    // ---- 3. send ----------------------------------------------------------------------------------------
+    if (ok) {
+        const bool bf16 = a.isBf16 != 0;
+        const bool quant = a.quantMode == TileXREp::TILEXR_EP_QUANT_FP8_1X128;
+        const int chunks = a.h / 16;             // 16 elements per lane and iteration (fp8 path)
+        const int iters = (chunks + 31) / 32;
+        float *stage = sm.scaleStage + warp * 64;
+        for (int i = warp; i < nTok; i += EP_WARPS) {
+            const int t = t0 + i;
+            const uint8_t *row = a.x + static_cast<int64_t>(t) * a.h * a.elemSize;
+            bool any = false;
+            for (int k = 0; k < K; ++k) any = any || sm.routeExpert[i * K + k] >= 0;
+            if (!any) continue;
+            constexpr int MAX_ITERS = EP_FP8_MAX_H / 512;
+            uint4 q[MAX_ITERS];
+            if (quant) {
+#pragma unroll
+                for (int it = 0; it < MAX_ITERS; ++it) {
+                    if (it < iters) {
+                        const int c = it * 32 + lane;
+                        float f[16];
+                        if (c < chunks) {
+                            Unpack8(ld_vec16(row + static_cast<int64_t>(c) * 32), bf16, f);
+                            Unpack8(ld_vec16(row + static_cast<int64_t>(c) * 32 + 16), bf16, f + 8);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) f[j] = 0.f;
+                        }
+                        float amax = 0.f;
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(f[j]));
+                        // 128 elements = 8 consecutive lanes
+                        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+                        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+                        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+                        amax = fmaxf(amax, FP8_AMAX_FLOOR);
+                        const float inv = FP8_E4M3_MAX / amax;
+                        if ((lane & 7) == 0 && c < chunks) stage[it * 4 + (lane >> 3)] = amax / FP8_E4M3_MAX;
+                        q[it].x = Fp8x4(f[0] * inv, f[1] * inv, f[2] * inv, f[3] * inv);
+                        q[it].y = Fp8x4(f[4] * inv, f[5] * inv, f[6] * inv, f[7] * inv);
+                        q[it].z = Fp8x4(f[8] * inv, f[9] * inv, f[10] * inv, f[11] * inv);
+                        q[it].w = Fp8x4(f[12] * inv, f[13] * inv, f[14] * inv, f[15] * inv);
+                    }
+                }
+                __syncwarp();
+            }
+            for (int k = 0; k < K; ++k) {
+                const int e = sm.routeExpert[i * K + k];
+                if (e < 0) continue;
+                const int dst = e / a.expertsPerRank;
+                const uint32_t r = static_cast<uint32_t>(sm.dstRow[e] + sm.blockBase[e] + sm.routeRank[i * K + k]);
+                uint8_t *half = DataHalf(comm, dst, epoch);
+                uint8_t *payload = a.zeroCopy
+                                       ? comm->registryPtr->regions[a.outHandle].peerBase[dst] + a.outOffset +
+                                             static_cast<uint64_t>(r) * a.win.rowBytes
+                                       : half + a.win.payloadOff + static_cast<uint64_t>(r) * a.win.rowBytes;
+                if (quant) {
+#pragma unroll
+                    for (int it = 0; it < MAX_ITERS; ++it) {
+                        if (it < iters) {
+                            const int c = it * 32 + lane;
+                            if (c < chunks) st_vec16(payload + static_cast<int64_t>(c) * 16, Vec16{q[it].x, q[it].y, q[it].z, q[it].w});
+                        }
+                    }
+                    uint8_t *scales = half + a.win.scalesOff + static_cast<uint64_t>(r) * a.win.scaleRowBytes;
+                    const int scaleVecs = a.win.scaleRowBytes / 16;
+                    if (lane < scaleVecs) {
+                        st_vec16(scales + lane * 16, *reinterpret_cast<const Vec16 *>(stage + lane * 4));
+                    }
+                } else {
+                    CopyLanes(payload, row, a.win.rowBytes, lane, 32);
+                }
+                if (lane == 0) {
+                    st_vec16(half + a.win.assistOff + static_cast<uint64_t>(r) * 16,
+                             Vec16{static_cast<uint32_t>(rank), static_cast<uint32_t>(t), static_cast<uint32_t>(k),
+                                   static_cast<uint32_t>(e)});
+                }
+            }
+            __syncwarp();
+        }
+    }
+    __syncthreads();
+    if (ok && tid < R) {
+        SetFlag(FlagSlot(comm, tid, TILEXR_FLAG_OP_BASE + static_cast<int64_t>(rank) * TILEXR_FLAGS_PER_PAIR + blockIdx.x), epoch, 1);
+    }
+
+    // ---- 4. receive ---------------------------------------------------------------------------------------
+    {
+        bool got = true;
+        if (ok && tid < R) {
+            for (int b = 0; b < G && got; ++b) {
+                const int64_t slot = TILEXR_FLAG_OP_BASE + static_cast<int64_t>(tid) * TILEXR_FLAGS_PER_PAIR + b;
+                got = WaitFlagGE(w, FlagSlot(comm, rank, slot), 1, tid, slot);
+            }
+        }
+        ok = BlockBroadcastOk(got) && ok;
+    }
+    if (ok) {
+        const int firstLocal = rank * a.expertsPerRank;
+        int64_t rows = 0;
+        for (int e = firstLocal; e < firstLocal + a.expertsPerRank; ++e) rows += sm.total[e];
+        const int64_t perBlock = (rows + G - 1) / G;
+        const int64_t r0 = min(rows, perBlock * blockIdx.x);
+        const int64_t n = min(rows - r0, perBlock);
+        if (n > 0) {
+            if (!a.zeroCopy) {
+                CopyLanes(a.expandXOut + r0 * a.win.rowBytes, myHalf + a.win.payloadOff + r0 * a.win.rowBytes,
+                          n * a.win.rowBytes, tid, blockDim.x);
+            }
+            if (a.quantMode == TileXREp::TILEXR_EP_QUANT_FP8_1X128 && a.dynamicScalesOut != nullptr) {
+                CopyLanes(reinterpret_cast<uint8_t *>(a.dynamicScalesOut) + r0 * a.win.scaleRowBytes,
+                          myHalf + a.win.scalesOff + r0 * a.win.scaleRowBytes, n * a.win.scaleRowBytes, tid, blockDim.x);
+            }
+            CopyLanes(reinterpret_cast<uint8_t *>(a.assistOut) + r0 * 16, myHalf + a.win.assistOff + r0 * 16, n * 16, tid,
+                      blockDim.x);
+        }
+        if (blockIdx.x == 0) {
+            if (tid == 0) {
+                int64_t running = 0;
+                for (int le = 0; le < a.expertsPerRank; ++le) {
+                    const int e = firstLocal + le;
+                    for (int s = 0; s < R; ++s) {
+                        running += countMatrix[static_cast<int64_t>(s) * E + e];
+                        a.sendCountsOut[le * R + s] = static_cast<int32_t>(running);
+                    }
+                    a.expertTokenNumsOut[le] =
+                        a.tokenNumsType == TileXREp::TILEXR_EP_TOKEN_NUMS_COUNT ? static_cast<int64_t>(sm.total[e]) : running;
+                }
+                if (a.recvTotalOut != nullptr) *a.recvTotalOut = static_cast<int32_t>(running);
+            }
+        }
+    }
+    KernelEpilogue(w, ok);
+}
+
+// ---- combine -----------------------------------------------------------------------------------------------
+
+__device__ void EpCombineBody(const EpCombineArgs &a)
+{
+    Waiter w;
+    bool ok = KernelPrologue(w, a.comm, a.magic, TILEXR_OP_EP_COMBINE, a.bs, true);
+    CommArgs *comm = a.comm;
+    const int rank = comm->rank;
+    const int K = a.topK;
+    const int lane = threadIdx.x & 31;
+    const int warpsPerBlock = blockDim.x >> 5;
+    const int64_t gwarp = static_cast<int64_t>(blockIdx.x) * warpsPerBlock + (threadIdx.x >> 5);
+    const int64_t nWarps = static_cast<int64_t>(gridDim.x) * warpsPerBlock;
+    const uint32_t epoch = w.epoch;
+    const bool bf16 = a.isBf16 != 0;
+
+    if (ok) {
+        // ---- send every processed row back to slot (token, k) of its source ------------------------------
+        const int64_t rows = a.sendCounts[a.sendCountEntries - 1];
+        for (int64_t r = gwarp; r < rows; r += nWarps) {
+            const Vec16 tuple = ld_vec16(a.assist + r * 4);
+            const int src = static_cast<int>(tuple.x);
+            const int64_t slot = static_cast<int64_t>(tuple.y) * K + tuple.z;
+            if (src < 0 || src >= comm->rankSize || slot < 0 || slot >= static_cast<int64_t>(a.bs) * K) continue;
+            uint8_t *dst = DataHalf(comm, src, epoch) + slot * a.rowBytes;
+            CopyLanes(dst, a.expertOut + r * a.rowBytes, a.rowBytes, lane, 32);
+            __syncwarp();
+            if (lane == 0) SetFlag(FlagSlot(comm, src, TILEXR_FLAG_OP_BASE + slot), epoch, 1);
+        }
+        // ---- reduce this rank's tokens ------------------------------------------------------------------------
+        const uint8_t *half = DataHalf(comm, rank, epoch);
+        const int vecs = a.rowBytes / 16;
+        for (int64_t t = gwarp; t < a.bs && w.ok(); t += nWarps) {
+            int e = -1;
+            float wk = 0.f;
+            if (lane < K) {
+                e = a.expertIds != nullptr ? a.expertIds[t * K + lane] : 0;
+                if (e >= a.numExperts) e = -1;
+                if (a.maskType == TileXREp::TILEXR_EP_ACTIVE_MASK_TOKEN && a.activeMask[t] == 0) e = -1;
+                if (a.maskType == TileXREp::TILEXR_EP_ACTIVE_MASK_EXPERT && a.activeMask[t * K + lane] == 0) e = -1;
+                wk = a.expertScales != nullptr ? a.expertScales[t * K + lane] : 1.0f;
+                if (e >= 0) {
+                    const int64_t slot = t * K + lane;
+                    WaitFlagGE(w, FlagSlot(comm, rank, TILEXR_FLAG_OP_BASE + slot), 1, e / a.expertsPerRank, slot);
+                }
+            }
+            const bool good = __all_sync(0xffffffffu, w.ok());
+            if (!good) {
+                if (w.ok()) w.status = TILEXR_DEV_ABORTED;
+                break;
+            }
+            const uint32_t active = __ballot_sync(0xffffffffu, e >= 0);
+            uint8_t *y = a.yOut + t * a.rowBytes;
+            for (int v = lane; v < vecs; v += 32) {
+                float acc[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+                for (int k = 0; k < K; ++k) {
+                    const float wgt = __shfl_sync(0xffffffffu, wk, k);
+                    if ((active >> k) & 1u) {
+                        float f[8];
+                        Unpack8(ld_vec16_stream(half + (t * K + k) * a.rowBytes + v * 16), bf16, f);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) acc[j] = fmaf(wgt, f[j], acc[j]);
+                    }
+                }
+                if (a.sharedExpertX != nullptr) {
+                    float f[8];
+                    Unpack8(ld_vec16(a.sharedExpertX + t * a.rowBytes + v * 16), bf16, f);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) acc[j] += f[j];
+                }
+                st_vec16(y + v * 16, Pack8(acc, bf16));
+            }
+        }
+        ok = w.ok();
+    }
+    ok = BlockBroadcastOk(ok);
+    KernelEpilogue(w, ok);
+}
+
+TILEXR_DEFINE_KERNEL(TileXREpDispatchKernel, EpDispatchArgs, EpDispatchBody, EP_BLOCK_THREADS)
+TILEXR_DEFINE_KERNEL(TileXREpCombineKernel, EpCombineArgs, EpCombineBody, EP_BLOCK_THREADS)
+
+// ---- stand-alone quantisation and norm kernels ---------------------------------------------------------------
+
+// One warp per row; lane handles 16 elements per iteration, a 128-element block is 8 lanes.
+__global__ void __launch_bounds__(256) Fp8Quant1x128Kernel(const uint8_t *x, int64_t rows, int h, int bf16, uint8_t *y, float *scales)
+{
+    const int64_t row = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) / 32;
+    const int lane = threadIdx.x & 31;
+    if (row >= rows) return;
+    const int chunks = h / 16;
+    const uint8_t *src = x + row * h * 2;
+    for (int c0 = 0; c0 < chunks; c0 += 32) {
+        const int c = c0 + lane;
+        float f[16];
+        if (c < chunks) {
+            Unpack8(ld_vec16(src + static_cast<int64_t>(c) * 32), bf16 != 0, f);
+            Unpack8(ld_vec16(src + static_cast<int64_t>(c) * 32 + 16), bf16 != 0, f + 8);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) f[j] = 0.f;
+        }
+        float amax = 0.f;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(f[j]));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+        amax = fmaxf(amax, FP8_AMAX_FLOOR);
+        const float inv = FP8_E4M3_MAX / amax;
+        if (c < chunks) {
+            if ((lane & 7) == 0) scales[row * (h / 128) + c / 8] = amax / FP8_E4M3_MAX;
+            Vec16 q;
+            q.x = Fp8x4(f[0] * inv, f[1] * inv, f[2] * inv, f[3] * inv);
+            q.y = Fp8x4(f[4] * inv, f[5] * inv, f[6] * inv, f[7] * inv);
+            q.z = Fp8x4(f[8] * inv, f[9] * inv, f[10] * inv, f[11] * inv);
+            q.w = Fp8x4(f[12] * inv, f[13] * inv, f[14] * inv, f[15] * inv);
+            st_vec16(y + row * h + static_cast<int64_t>(c) * 16, q);
+        }
+    }
+}
+
+__global__ void __launch_bounds__(256) Fp8Dequant1x128Kernel(const uint8_t *y, const float *scales, int64_t rows, int h, int bf16, uint8_t *x)
+{
+    const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;   // one thread per 8 elements
+    const int per = h / 8;
+    if (idx >= rows * per) return;
+    const int64_t row = idx / per;
+    const int c = static_cast<int>(idx % per);
+    const uint2 raw = *reinterpret_cast<const uint2 *>(y + row * h + static_cast<int64_t>(c) * 8);
+    const float s = scales[row * (h / 128) + c / 16];
+    float f[8];
+    const uint32_t w[2] = {raw.x, raw.y};
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const __half2_raw h2 = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>((w[i] >> (16 * j)) & 0xffffu), __NV_E4M3);
+            const float2 f2 = __half22float2(*reinterpret_cast<const __half2 *>(&h2));
+            f[i * 4 + j * 2] = f2.x * s;
+            f[i * 4 + j * 2 + 1] = f2.y * s;
+        }
+    }
+    st_vec16(x + (row * h + static_cast<int64_t>(c) * 8) * 2, Pack8(f, bf16 != 0));
+}
+
+// MXFP8: 32-element blocks share an E8M0 exponent 2^(floor(log2(amax)) - emax), emax = 8 for
+// e4m3 and 15 for e5m2; elements are x / 2^exp rounded to nearest even with saturation.
+__global__ void __launch_bounds__(256) Mxfp8QuantKernel(const uint8_t *x, int64_t rows, int h, int bf16, int e5m2, uint8_t *y, uint8_t *scales)
+{
+    const int blocksPerRow = (h + 31) / 32;
+    const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;   // one thread per 32-element block
+    if (idx >= rows * blocksPerRow) return;
+    const int64_t row = idx / blocksPerRow;
+    const int b = static_cast<int>(idx % blocksPerRow);
+    const int n = min(32, h - b * 32);
+    float f[32];
+    float amax = 0.f;
+    for (int j = 0; j < 32; ++j) {
+        float v = 0.f;
+        if (j < n) {
+            const uint16_t raw = *reinterpret_cast<const uint16_t *>(x + (row * h + b * 32 + j) * 2);
+            v = bf16 ? __uint_as_float(static_cast<uint32_t>(raw) << 16) : __half2float(*reinterpret_cast<const __half *>(&raw));
+        }
+        f[j] = v;
+        amax = fmaxf(amax, fabsf(v));
+    }
+    const int emax = e5m2 ? 15 : 8;
+    int exp = 0;
+    if (amax > 0.f) {
+        exp = static_cast<int>((__float_as_uint(amax) >> 23) & 0xff) - 127 - emax;   // floor(log2(amax)) - emax
+        if ((__float_as_uint(amax) >> 23) == 0) exp = -126 - emax;                    // subnormal input
+    } else {
+        exp = -127;
+    }
+    exp = max(-127, min(127, exp));
+    scales[row * blocksPerRow + b] = static_cast<uint8_t>(exp + 127);
+    const float inv = exp2f(static_cast<float>(-exp));
+    for (int j = 0; j < n; ++j) {
+        const float v = f[j] * inv;
+        const __nv_fp8_storage_t q = __nv_cvt_float_to_fp8(v, __NV_SATFINITE, e5m2 ? __NV_E5M2 : __NV_E4M3);
+        y[row * h + b * 32 + j] = q;
+    }
+}
+
+__global__ void __launch_bounds__(256) Mxfp8DequantKernel(const uint8_t *y, const uint8_t *scales, int64_t rows, int h, int e5m2, int bf16, uint8_t *x)
+{
+    const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (idx >= rows * h) return;
+    const int64_t row = idx / h;
+    const int col = static_cast<int>(idx % h);
+    const int blocksPerRow = (h + 31) / 32;
+    const float s = exp2f(static_cast<float>(static_cast<int>(scales[row * blocksPerRow + col / 32]) - 127));
+    const __half_raw hr = __nv_cvt_fp8_to_halfraw(y[idx], e5m2 ? __NV_E5M2 : __NV_E4M3);
+    const float v = __half2float(*reinterpret_cast<const __half *>(&hr)) * s;
+    if (bf16) {
+        const __nv_bfloat16 o = __float2bfloat16_rn(v);
+        *reinterpret_cast<__nv_bfloat16 *>(x + idx * 2) = o;
+    } else {
+        *reinterpret_cast<__half *>(x + idx * 2) = __float2half_rn(v);
+    }
+}
+
+// One block per row.  The row stays in registers between the two passes.
+__global__ void __launch_bounds__(256) RmsNormKernel(const uint8_t *x, uint8_t *residual, const uint8_t *gamma, float eps, int h, int bf16, uint8_t *y)
+{
+    __shared__ float partial[8];
+    const int64_t row = blockIdx.x;
+    const int vecs = h / 8;
+    constexpr int MAX_VECS = 8;   // 256 threads x 8 vectors x 8 elements = 16384 columns
+    float vals[MAX_VECS][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAX_VECS; ++i) {
+        const int v = i * 256 + threadIdx.x;
+        if (v < vecs) {
+            Unpack8(ld_vec16(x + (row * h + static_cast<int64_t>(v) * 8) * 2), bf16 != 0, vals[i]);
+            if (residual != nullptr) {
+                float r[8];
+                Unpack8(ld_vec16(residual + (row * h + static_cast<int64_t>(v) * 8) * 2), bf16 != 0, r);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) vals[i][j] += r[j];
+                // the sum, rounded to the storage type, is both the new residual and the norm input
+                const Vec16 packed = Pack8(vals[i], bf16 != 0);
+                st_vec16(residual + (row * h + static_cast<int64_t>(v) * 8) * 2, packed);
+                Unpack8(packed, bf16 != 0, vals[i]);
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) ss += vals[i][j] * vals[i][j];
+        }
+    }
+    ss = WarpSum(ss);
+    if ((threadIdx.x & 31) == 0) partial[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) tot += partial[i];
+    const float rstd = rsqrtf(tot / static_cast<float>(h) + eps);
+#pragma unroll
+    for (int i = 0; i < MAX_VECS; ++i) {
+        const int v = i * 256 + threadIdx.x;
+        if (v < vecs) {
+            float g[8];
+            Unpack8(ld_vec16(gamma + static_cast<int64_t>(v) * 16), bf16 != 0, g);
+            float o[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o[j] = vals[i][j] * rstd * g[j];
+            st_vec16(y + (row * h + static_cast<int64_t>(v) * 8) * 2, Pack8(o, bf16 != 0));
+        }
+    }
+}
+
+int CheckLaunch(const char *what)
+{
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        fprintf(stderr, "[TileXR] %s launch failed: %s\n", what, cudaGetErrorString(e));
+        return TILEXR_ERROR_RUNTIME;
+    }
+    return TILEXR_SUCCESS;
+}
+
+} // namespace
+
+const KernelEntry &EpDispatchKernelEntry() { return TileXREpDispatchKernelEntry; }
+const KernelEntry &EpCombineKernelEntry() { return TileXREpCombineKernelEntry; }
+
+size_t EpDispatchSmemBytes(int numExperts, int routesPerBlock)
+{
+    return static_cast<size_t>(routesPerBlock) * 8 + static_cast<size_t>(numExperts) * 16 + EP_WARPS * 64 * sizeof(float);
+}
+
+int LaunchRoutingTopK(const RoutingArgs &args, void *stream)
+{
+    const int warpsPerBlock = 8;
+    const unsigned grid = static_cast<unsigned>((args.bs + warpsPerBlock - 1) / warpsPerBlock);
+    RoutingTopKKernel<<<grid, warpsPerBlock * 32, 0, static_cast<cudaStream_t>(stream)>>>(args);
+    return CheckLaunch("routing top-k");
+}
+
+int LaunchFp8Quant1x128(const void *x, int64_t rows, int64_t h, bool bf16, void *y, float *scales, void *stream)
+{
+    const unsigned grid = static_cast<unsigned>((rows + 7) / 8);
+    Fp8Quant1x128Kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const uint8_t *>(x), rows, static_cast<int>(h),
+                                                                              bf16 ? 1 : 0, static_cast<uint8_t *>(y), scales);
+    return CheckLaunch("fp8 quant");
+}
+
+int LaunchFp8Dequant1x128(const void *y, const float *scales, int64_t rows, int64_t h, bool bf16, void *x, void *stream)
+{
+    const int64_t n = rows * (h / 8);
+    const unsigned grid = static_cast<unsigned>((n + 255) / 256);
+    Fp8Dequant1x128Kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const uint8_t *>(y), scales, rows,
+                                                                                static_cast<int>(h), bf16 ? 1 : 0, static_cast<uint8_t *>(x));
+    return CheckLaunch("fp8 dequant");
+}
+
+int LaunchMxfp8Quant(const void *x, int64_t rows, int64_t h, bool bf16, bool e5m2, void *y, uint8_t *scales, void *stream)
+{
+    const int64_t n = rows * ((h + 31) / 32);
+    const unsigned grid = static_cast<unsigned>((n + 255) / 256);
+    Mxfp8QuantKernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const uint8_t *>(x), rows, static_cast<int>(h),
+                                                                           bf16 ? 1 : 0, e5m2 ? 1 : 0, static_cast<uint8_t *>(y), scales);
+    return CheckLaunch("mxfp8 quant");
+}
+
+int LaunchMxfp8Dequant(const void *y, const uint8_t *scales, int64_t rows, int64_t h, bool e5m2, bool bf16, void *x, void *stream)
+{
+    const int64_t n = rows * h;
+    const unsigned grid = static_cast<unsigned>((n + 255) / 256);
+    Mxfp8DequantKernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const uint8_t *>(y), scales, rows,
+                                                                             static_cast<int>(h), e5m2 ? 1 : 0, bf16 ? 1 : 0,
+                                                                             static_cast<uint8_t *>(x));
+    return CheckLaunch("mxfp8 dequant");
+}
+
+int LaunchRmsNorm(const void *x, void *residual, const void *gamma, float eps, int64_t rows, int64_t h, bool bf16, void *y, void *stream)
+{
+    RmsNormKernel<<<static_cast<unsigned>(rows), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint8_t *>(x), static_cast<uint8_t *>(residual), static_cast<const uint8_t *>(gamma), eps,
+        static_cast<int>(h), bf16 ? 1 : 0, static_cast<uint8_t *>(y));
+    return CheckLaunch("rmsnorm");
+}
+
+} // namespace TileXR

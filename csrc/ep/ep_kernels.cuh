@@ -1,0 +1,106 @@
+// Argument blocks of the expert-parallel kernels and the window layout they agree on.
+#ifndef TILEXR_EP_KERNELS_CUH
+#define TILEXR_EP_KERNELS_CUH
+
+#include <stdint.h>
+
+#include "tilexr_comm_args.h"
+#include "tilexr_launch.h"
+
+namespace TileXR {
+
+constexpr unsigned EP_BLOCK_THREADS = 512;
+constexpr unsigned EP_WARPS = EP_BLOCK_THREADS / 32;
+constexpr int EP_MAX_EXPERTS = 1024;
+constexpr int EP_MAX_TOPK = 32;
+constexpr int EP_MAX_ROUTES_PER_BLOCK = 4096;
+constexpr int EP_FP8_MAX_H = 8192;      // register-resident quantised row: 16 x 512 elements
+constexpr uint32_t EP_COUNT_FLAG_SLOT = TILEXR_FLAGS_PER_PAIR - 1;   // "my expert counts are published"
+
+// Where a dispatch puts things inside one data half of the DESTINATION's window.  Identical
+// on every rank; computed by EpDispatchLayout() on the host.
+struct EpDispatchWindow {
+    uint64_t payloadOff;      // [maxRecvRows][rowBytes]           (unused when zeroCopy)
+    uint64_t scalesOff;       // [maxRecvRows][scaleRowBytes]
+    uint64_t assistOff;       // [maxRecvRows][16]
+    uint64_t countOff;        // [rankSize][numExperts] int32: routes of source s for expert e
+    uint64_t blockCountOff;   // [grid][numExperts] int32, local scratch of the sender
+    uint64_t totalBytes;
+    uint32_t rowBytes;
+    uint32_t scaleRowBytes;
+};
+
+struct EpDispatchArgs {
+    const uint8_t *x;
+    const int32_t *expertIds;
+    const float *gateLogits;
+    const float *selectionBias;
+    const uint8_t *activeMask;
+    int32_t *topkIdsOut;
+    float *topkWeightsOut;
+    uint8_t *expandXOut;
+    float *dynamicScalesOut;
+    int32_t *assistOut;
+    int64_t *expertTokenNumsOut;
+    int32_t *sendCountsOut;
+    int32_t *recvTotalOut;
+    CommArgs *comm;
+    int64_t magic;
+    EpDispatchWindow win;
+    int32_t bs, h, topK, numExperts, expertsPerRank;
+    int32_t maskType, quantMode, scoreFunc, renormalize, tokenNumsType;
+    float routedScale;
+    uint32_t maxRecvRows;
+    uint32_t tokensPerBlock;
+    uint32_t elemSize;
+    uint32_t isBf16;
+    uint32_t zeroCopy;
+    uint32_t outHandle;
+    uint64_t outOffset;
+};
+
+struct EpCombineArgs {
+    const uint8_t *expertOut;
+    const int32_t *assist;
+    const int32_t *sendCounts;       // last entry = rows to send back
+    const int32_t *expertIds;
+    const float *expertScales;
+    const uint8_t *activeMask;
+    const uint8_t *sharedExpertX;
+    uint8_t *yOut;
+    CommArgs *comm;
+    int64_t magic;
+    int32_t bs, h, topK, numExperts, expertsPerRank;
+    int32_t maskType;
+    uint32_t rowBytes;
+    uint32_t isBf16;
+    uint32_t sendCountEntries;
+};
+
+struct RoutingArgs {
+    const float *gateLogits;
+    const float *selectionBias;
+    int32_t *topkIdsOut;
+    float *topkWeightsOut;
+    int32_t bs, numExperts, topK, scoreFunc, renormalize;
+    float routedScale;
+};
+
+const KernelEntry &EpDispatchKernelEntry();
+const KernelEntry &EpCombineKernelEntry();
+
+// Plain (non communicating) kernels, launched directly.
+int LaunchRoutingTopK(const RoutingArgs &args, void *stream);
+int LaunchFp8Quant1x128(const void *x, int64_t rows, int64_t h, bool bf16, void *y, float *scales, void *stream);
+int LaunchFp8Dequant1x128(const void *y, const float *scales, int64_t rows, int64_t h, bool bf16, void *x, void *stream);
+int LaunchMxfp8Quant(const void *x, int64_t rows, int64_t h, bool bf16, bool e5m2, void *y, uint8_t *scales, void *stream);
+int LaunchMxfp8Dequant(const void *y, const uint8_t *scales, int64_t rows, int64_t h, bool e5m2, bool bf16, void *x,
+                       void *stream);
+int LaunchRmsNorm(const void *x, void *residual, const void *gamma, float eps, int64_t rows, int64_t h, bool bf16, void *y,
+                  void *stream);
+
+size_t EpDispatchSmemBytes(int numExperts, int routesPerBlock);
+
+} // namespace TileXR
+
+#endif

@@ -1,0 +1,91 @@
+// Device-initiated local copy (global -> global on the same GPU) that does not occupy the
+// calling block's threads: one thread drives a TMA pipeline global -> shared -> global and
+// the rest of the block keeps computing.  Counterpart of the reference's SDMA device API
+// (src/include/tilexr_sdma.h:43-100: SDMACopyNbi returns an event handle, SDMAWait joins it,
+// and both degrade to a synchronous path when the engine is not available).
+//
+// The host-initiated form of the same transport is a copy-engine `cudaMemcpyAsync` on a side
+// stream (TileXRLocalCopyAsync in tilexr_api.h).
+#ifndef TILEXR_LOCAL_COPY_CUH
+#define TILEXR_LOCAL_COPY_CUH
+
+#include "tilexr_rma.cuh"
+
+namespace tilexr {
+
+constexpr uint32_t LOCAL_COPY_STAGE_BYTES = 32 * 1024;
+constexpr uint32_t LOCAL_COPY_STAGES = 2;
+
+#if defined(__CUDACC__)
+
+// Shared-memory footprint of one copy lane; place it in dynamic shared memory, 128-byte aligned.
+struct alignas(128) LocalCopyLane {
+    uint8_t stage[LOCAL_COPY_STAGES][LOCAL_COPY_STAGE_BYTES];
+    uint64_t full[LOCAL_COPY_STAGES];
+    uint32_t phase[LOCAL_COPY_STAGES];
+    uint32_t ready;
+};
+
+struct LocalCopyEvent {
+    int status;          // RMA_OK, RMA_MISALIGNED (nothing copied) or RMA_TIMEOUT
+    uint32_t groups;     // bulk groups committed by the issuing thread
+};
+
+// One thread of the block calls this once before the first copy on `lane`.
+__device__ __forceinline__ void LocalCopyLaneInit(LocalCopyLane *lane)
+{
+    for (uint32_t s = 0; s < LOCAL_COPY_STAGES; ++s) {
+        MbarInit(&lane->full[s], 1);
+        lane->phase[s] = 0;
+    }
+    lane->ready = 1;
+    MbarInitFence();
+}
+
+// Issued by ONE thread.  Addresses 16-byte aligned, bytes a multiple of 16; otherwise nothing
+// is copied and the event says RMA_MISALIGNED so the caller can use CopyLanes instead.
+// `channelGroup` is accepted for parity with the reference API; lanes are chosen by the caller.
+__device__ __forceinline__ LocalCopyEvent LocalCopyNbi(const CommArgs *args, LocalCopyLane *lane, void *dst,
+                                                       const void *src, uint64_t bytes, uint32_t channelGroup = 0)
+{
+    (void)channelGroup;
+    LocalCopyEvent ev{RMA_OK, 0};
+    if ((args->extraFlag & TileXR::TILEXR_FLAG_LOCAL_COPY) == 0 ||
+        ((reinterpret_cast<uintptr_t>(dst) | reinterpret_cast<uintptr_t>(src) | bytes) & 15u) != 0) {
+        ev.status = RMA_MISALIGNED;
+        return ev;
+    }
+    uint64_t done = 0;
+    uint32_t s = 0;
+    while (done < bytes) {
+        const uint32_t n = static_cast<uint32_t>(bytes - done < LOCAL_COPY_STAGE_BYTES ? bytes - done : LOCAL_COPY_STAGE_BYTES);
+        // the store that last read this stage must have finished reading shared memory
+        BulkWaitRead<LOCAL_COPY_STAGES - 1>();
+        MbarExpectTx(&lane->full[s], n);
+        BulkLoadToSmem(lane->stage[s], reinterpret_cast<const uint8_t *>(src) + done, n, &lane->full[s]);
+        if (!MbarWait(&lane->full[s], lane->phase[s], args->waitTimeoutNs)) {
+            ev.status = RMA_TIMEOUT;
+            break;
+        }
+        lane->phase[s] ^= 1u;
+        BulkStoreFromSmem(reinterpret_cast<uint8_t *>(dst) + done, lane->stage[s], n);
+        BulkCommit();
+        ev.groups++;
+        done += n;
+        s = (s + 1) % LOCAL_COPY_STAGES;
+    }
+    return ev;
+}
+
+// Joins the copy: all bytes are written and visible to the calling thread afterwards.
+__device__ __forceinline__ bool LocalCopyWait(const LocalCopyEvent &ev)
+{
+    BulkWait<0>();
+    return ev.status == RMA_OK;
+}
+
+#endif // __CUDACC__
+
+} // namespace tilexr
+
+#endif // TILEXR_LOCAL_COPY_CUH

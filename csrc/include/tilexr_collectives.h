@@ -1,0 +1,57 @@
+// Collectives library: all-gather, equal all-to-all, all-reduce, reduce-scatter, broadcast
+// and the profile probe, issued as kernels on the caller's stream.  Same entry points as the
+// reference (src/include/tilexr_collectives.h:23-40).  Differences worth knowing:
+//   * all four reduce operators are implemented (the reference host accepts SUM only);
+//   * all-to-all works for any rank count (the reference needs an even count on one topology);
+//   * when the receive buffer lies inside a registered region (TileXRUDMARegister or
+//     TileXRSymmAlloc on every rank, same offset) peers write into it directly and the
+//     staging copy through the window is skipped.
+#ifndef TILEXR_COLLECTIVES_H
+#define TILEXR_COLLECTIVES_H
+
+#include "tilexr_api.h"
+#include "tilexr_types.h"
+
+#ifdef __cplusplus
+#define TXR_DT TileXR::TileXRDataType
+#define TXR_OP TileXR::TileXRReduceOp
+extern "C" {
+#else
+#define TXR_DT enum TileXRDataType
+#define TXR_OP enum TileXRReduceOp
+#endif
+
+int TileXRAllGather(void *sendBuf, void *recvBuf, int64_t sendCount, TXR_DT dataType, TileXRCommPtr comm,
+                    TileXRStream stream);
+int TileXRAllToAll(void *sendBuf, void *recvBuf, int64_t sendCount /* per peer */, TXR_DT dataType, TileXRCommPtr comm,
+                   TileXRStream stream);
+int TileXRAllReduce(void *sendBuf, void *recvBuf, int64_t count, TXR_DT dataType, TXR_OP op, TileXRCommPtr comm,
+                    TileXRStream stream);
+int TileXRReduceScatter(void *sendBuf, void *recvBuf, int64_t recvCount, TXR_DT dataType, TXR_OP op, TileXRCommPtr comm,
+                        TileXRStream stream);
+int TileXRBroadcast(void *buf, int64_t count, TXR_DT dataType, int root, TileXRCommPtr comm, TileXRStream stream);
+int TileXRProfileProbe(void *sendBuf, void *recvBuf, int64_t count, TXR_DT dataType, TileXRCommPtr comm,
+                       TileXRStream stream);
+
+// How a call would be split into launches; pure host arithmetic, exposed for tests and tools.
+typedef struct TileXRCollPlanInfo {
+    int32_t kind;            // CollKind
+    uint32_t launches;       // kernel launches the call needs
+    uint32_t tileBytes;
+    uint32_t tilesPerLaunch; // tiles per (source, destination) pair in the first launch
+    uint32_t producers;
+    uint32_t reducers;
+    uint32_t consumers;
+    uint32_t grid;
+    uint64_t bytesPerLaunch; // slice bytes covered by one launch
+} TileXRCollPlanInfo;
+int TileXRCollectivePlan(int opType, int64_t count, int dataType, int rankSize, uint64_t dataHalfBytes,
+                         unsigned maxGrid, TileXRCollPlanInfo *info);
+
+#ifdef __cplusplus
+}
+#endif
+#undef TXR_DT
+#undef TXR_OP
+
+#endif // TILEXR_COLLECTIVES_H

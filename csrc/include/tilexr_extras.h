@@ -1,0 +1,7 @@
+// Umbrella header of the libraries that sit beside the core, collectives and EP headers.
+#ifndef TILEXR_EXTRAS_H
+#define TILEXR_EXTRAS_H
+
+#include "tilexr_hostsim.h"
+
+#endif

@@ -1,0 +1,37 @@
+// CPU execution of the tile-flag protocols over a host-memory communicator
+// (TileXRCommInitRankHostMemory): windows are POSIX shared memory, one process per rank, and
+// the "kernels" below run on the calling thread using the very same flag / epoch / reuse-guard
+// primitives as the CUDA kernels (device/tilexr_sync.cuh compiled for the host).  This is the
+// no-GPU plumbing mode: it exercises bootstrap, window mapping, magic epochs, bounded waits and
+// the expert-parallel placement rules between real processes.
+#ifndef TILEXR_HOSTSIM_H
+#define TILEXR_HOSTSIM_H
+
+#include "tilexr_api.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// All-gather of `bytes` per rank in tiles of `tileBytes`, each tile announced by its own
+// magic-tagged flag; consumers copy a tile as soon as its flag shows up.
+int TileXRHostAllGather(const void *send, void *recv, uint64_t bytes, uint32_t tileBytes, TileXRCommPtr comm);
+int TileXRHostAllReduceSumF32(const float *send, float *recv, uint64_t count, TileXRCommPtr comm);
+
+// fp32 expert-parallel dispatch / combine with the semantics of tilexr_ep.h.
+int TileXRHostEpDispatch(const float *x, const int32_t *expertIds, int64_t bs, int64_t h, int64_t topK,
+                         int64_t moeExpertNum, int64_t maxRecvRows, float *expandXOut, int32_t *assistOut,
+                         int64_t *expertTokenNumsOut, int32_t *sendCountsOut, int32_t *recvTotalOut, TileXRCommPtr comm);
+int TileXRHostEpCombine(const float *expertOut, const int32_t *assist, int32_t rows, const int32_t *expertIds,
+                        const float *expertScales, int64_t bs, int64_t h, int64_t topK, int64_t moeExpertNum, float *yOut,
+                        TileXRCommPtr comm);
+
+// Test hook: the next host kernel of this process skips raising its flags, so that peers run
+// into their wait budget (failure-detection tests make the failure on the host).
+int TileXRHostInjectSkipFlags(int enable);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif

@@ -1,0 +1,140 @@
+// Basic enums shared by every TileXR-B200 library: status codes, element types,
+// reduction operators and operator ids.  Numeric values follow the reference ABI
+// (src/include/tilexr_types.h:17-25, 60-127) so existing callers keep their constants.
+#ifndef TILEXR_TYPES_H
+#define TILEXR_TYPES_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+namespace TileXR {
+#endif
+
+enum TileXRStatus {
+    TILEXR_SUCCESS = 0,
+    TILEXR_ERROR_NOT_INITIALIZED = -1,
+    TILEXR_ERROR_RUNTIME = -2,          // a CUDA runtime / driver call failed (reference: MKIRT)
+    TILEXR_ERROR_PARA_CHECK_FAIL = -3,
+    TILEXR_ERROR_INTERNAL = -4,
+    TILEXR_ERROR_TIMEOUT = -5,
+    TILEXR_ERROR_NOT_SUPPORT = -6,
+    TILEXR_ERROR_NOT_FOUND = -7,
+};
+#define TILEXR_ERROR_MKIRT TILEXR_ERROR_RUNTIME
+
+enum TileXRDataType {
+    TILEXR_DATA_TYPE_INT8 = 0,
+    TILEXR_DATA_TYPE_INT16 = 1,
+    TILEXR_DATA_TYPE_INT32 = 2,
+    TILEXR_DATA_TYPE_FP16 = 3,
+    TILEXR_DATA_TYPE_FP32 = 4,
+    TILEXR_DATA_TYPE_INT64 = 5,
+    TILEXR_DATA_TYPE_UINT64 = 6,
+    TILEXR_DATA_TYPE_UINT8 = 7,
+    TILEXR_DATA_TYPE_UINT16 = 8,
+    TILEXR_DATA_TYPE_UINT32 = 9,
+    TILEXR_DATA_TYPE_FP64 = 10,
+    TILEXR_DATA_TYPE_BFP16 = 11,
+    TILEXR_DATA_TYPE_INT128 = 12,
+    TILEXR_DATA_TYPE_HIF8 = 14,
+    TILEXR_DATA_TYPE_FP8E4M3 = 15,
+    TILEXR_DATA_TYPE_FP8E5M2 = 16,
+    TILEXR_DATA_TYPE_FP8E8M0 = 17,
+    TILEXR_DATA_TYPE_NVFP4 = 18,        // Blackwell addition, two e2m1 values per byte
+    TILEXR_DATA_TYPE_RESERVED = 255
+};
+
+enum TileXRReduceOp {
+    TILEXR_REDUCE_SUM = 0,
+    TILEXR_REDUCE_PROD = 1,
+    TILEXR_REDUCE_MAX = 2,
+    TILEXR_REDUCE_MIN = 3,
+    TILEXR_REDUCE_RESERVED = 255
+};
+
+// Operator ids.  Ids >= 100 are the compute+collective fusions; the reference keeps only
+// their names, this runtime implements ALL_GATHER_MATMUL and MATMUL_REDUCE_SCATTER.
+enum TileXROpType {
+    TILEXR_OP_ALL_REDUCE = 1,
+    TILEXR_OP_REDUCE_SCATTER = 2,
+    TILEXR_OP_ALL_GATHER = 3,
+    TILEXR_OP_BROADCAST = 4,
+    TILEXR_OP_ALL2ALL = 5,
+    TILEXR_OP_ALL2ALL_V_C = 6,
+    TILEXR_OP_GATHER = 7,
+    TILEXR_OP_LOCAL_REDUCE = 8,
+    TILEXR_OP_SEND = 9,
+    TILEXR_OP_RECV = 10,
+    TILEXR_OP_PROFILE_PROBE = 11,
+    TILEXR_OP_ALL_REDUCE_RMSNORM = 12,  // all-reduce + residual add + RMSNorm
+    TILEXR_OP_EP_DISPATCH = 20,
+    TILEXR_OP_EP_COMBINE = 21,
+    TILEXR_OP_MOONEP_PLANNING = 30,
+    TILEXR_OP_MOONEP_DISPATCH = 31,
+    TILEXR_OP_MOONEP_PREFETCH = 32,
+    TILEXR_OP_MOONEP_COMBINE = 33,
+    TILEXR_OP_MOONEP_REDUCE_GRAD = 34,
+    TILEXR_OP_PURE_MATMUL = 101,
+    TILEXR_OP_MATMUL_ALL_REDUCE = 102,
+    TILEXR_OP_MATMUL_REDUCE_SCATTER = 103,
+    TILEXR_OP_ALL_GATHER_MATMUL = 104,
+    TILEXR_OP_BANDWIDTH = 201,
+};
+
+static inline size_t TileXRDataTypeSize(int dtype)
+{
+    switch (dtype) {
+        case TILEXR_DATA_TYPE_INT8: case TILEXR_DATA_TYPE_UINT8: case TILEXR_DATA_TYPE_HIF8:
+        case TILEXR_DATA_TYPE_FP8E4M3: case TILEXR_DATA_TYPE_FP8E5M2: case TILEXR_DATA_TYPE_FP8E8M0:
+            return 1;
+        case TILEXR_DATA_TYPE_INT16: case TILEXR_DATA_TYPE_UINT16: case TILEXR_DATA_TYPE_FP16:
+        case TILEXR_DATA_TYPE_BFP16:
+            return 2;
+        case TILEXR_DATA_TYPE_INT32: case TILEXR_DATA_TYPE_UINT32: case TILEXR_DATA_TYPE_FP32:
+            return 4;
+        case TILEXR_DATA_TYPE_INT64: case TILEXR_DATA_TYPE_UINT64: case TILEXR_DATA_TYPE_FP64:
+            return 8;
+        case TILEXR_DATA_TYPE_INT128:
+            return 16;
+        default:
+            return 0;
+    }
+}
+
+static inline const char *TileXROpName(int op)
+{
+    switch (op) {
+        case TILEXR_OP_ALL_REDUCE: return "TileXRAllReduce";
+        case TILEXR_OP_REDUCE_SCATTER: return "TileXRReduceScatter";
+        case TILEXR_OP_ALL_GATHER: return "TileXRAllGather";
+        case TILEXR_OP_BROADCAST: return "TileXRBroadcast";
+        case TILEXR_OP_ALL2ALL: return "TileXRAll2All";
+        case TILEXR_OP_ALL2ALL_V_C: return "TileXRAll2AllVC";
+        case TILEXR_OP_GATHER: return "TileXRGather";
+        case TILEXR_OP_LOCAL_REDUCE: return "TileXRLocalReduce";
+        case TILEXR_OP_SEND: return "TileXRSend";
+        case TILEXR_OP_RECV: return "TileXRRecv";
+        case TILEXR_OP_PROFILE_PROBE: return "TileXRProfileProbe";
+        case TILEXR_OP_ALL_REDUCE_RMSNORM: return "TileXRAllReduceRmsNorm";
+        case TILEXR_OP_EP_DISPATCH: return "TileXRMoeEpDispatch";
+        case TILEXR_OP_EP_COMBINE: return "TileXRMoeEpCombine";
+        case TILEXR_OP_MOONEP_PLANNING: return "TileXRMoonEpPlanning";
+        case TILEXR_OP_MOONEP_DISPATCH: return "TileXRMoonEpDispatch";
+        case TILEXR_OP_MOONEP_PREFETCH: return "TileXRMoonEpPrefetchWeight";
+        case TILEXR_OP_MOONEP_COMBINE: return "TileXRMoonEpCombine";
+        case TILEXR_OP_MOONEP_REDUCE_GRAD: return "TileXRMoonEpReduceGrad";
+        case TILEXR_OP_PURE_MATMUL: return "TileXRPureMatmul";
+        case TILEXR_OP_MATMUL_ALL_REDUCE: return "TileXRMatmulAllReduce";
+        case TILEXR_OP_MATMUL_REDUCE_SCATTER: return "TileXRMatmulReduceScatter";
+        case TILEXR_OP_ALL_GATHER_MATMUL: return "TileXRAllGatherMatmul";
+        case TILEXR_OP_BANDWIDTH: return "TileXRBandwidthTest";
+        default: return "TileXRUnknown";
+    }
+}
+
+#ifdef __cplusplus
+} // namespace TileXR
+#endif
+
+#endif // TILEXR_TYPES_H

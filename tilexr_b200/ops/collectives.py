@@ -1,0 +1,69 @@
+"""Collectives on torch tensors (current CUDA stream).
+
+Each function issues kernels and returns without synchronising, like the C API
+(csrc/include/tilexr_collectives.h).  Output tensors that live in registered memory
+(``Comm.symm_empty`` / ``Comm.register``) are written by the peers directly.
+"""
+from __future__ import annotations
+
+import enum
+from typing import Optional
+
+import torch
+
+from .. import _C
+
+
+class ReduceOp(enum.IntEnum):
+    SUM = 0
+    PROD = 1
+    MAX = 2
+    MIN = 3
+
+
+def all_gather(comm, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    x = x.contiguous()
+    if out is None:
+        out = torch.empty((comm.world_size,) + tuple(x.shape), dtype=x.dtype, device=x.device)
+    _C.all_gather(comm, x, out)
+    return out
+
+
+def all_to_all(comm, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Equal split along dim 0: chunk p of ``x`` goes to rank p."""
+    x = x.contiguous()
+    if out is None:
+        out = torch.empty_like(x)
+    _C.all_to_all(comm, x, out)
+    return out
+
+
+def all_reduce(comm, x: torch.Tensor, op: ReduceOp = ReduceOp.SUM, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    x = x.contiguous()
+    if out is None:
+        out = torch.empty_like(x)
+    _C.all_reduce(comm, x, out, int(op))
+    return out
+
+
+def reduce_scatter(comm, x: torch.Tensor, op: ReduceOp = ReduceOp.SUM, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``x`` holds world_size equal chunks along dim 0; returns the reduction of chunk ``rank``."""
+    x = x.contiguous()
+    if out is None:
+        shape = list(x.shape)
+        shape[0] //= comm.world_size
+        out = torch.empty(shape, dtype=x.dtype, device=x.device)
+    _C.reduce_scatter(comm, x, out, int(op))
+    return out
+
+
+def broadcast(comm, x: torch.Tensor, root: int = 0) -> torch.Tensor:
+    _C.broadcast(comm, x, root)
+    return x
+
+
+def profile_probe(comm, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    if out is None:
+        out = torch.empty_like(x)
+    _C.profile_probe(comm, x.contiguous(), out)
+    return out

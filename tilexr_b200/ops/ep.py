@@ -1,0 +1,53 @@
+"""Expert-parallel dispatch / combine on torch tensors.
+
+``dispatch`` returns a :class:`DispatchResult`; pass it to ``combine`` together with the
+expert outputs.  Semantics are those of csrc/include/tilexr_ep.h.
+"""
+from __future__ import annotations
+
+import dataclasses
+from typing import Optional
+
+import torch
+
+from .. import _C
+
+QUANT_NONE = 0
+QUANT_FP8_1X128 = 5
+TOKEN_NUMS_PREFIX = 0
+TOKEN_NUMS_COUNT = 1
+
+
+@dataclasses.dataclass
+class DispatchResult:
+    expand_x: torch.Tensor            # [max_recv_rows, h]
+    dynamic_scales: Optional[torch.Tensor]
+    assist: torch.Tensor              # [max_recv_rows, 4] int32 {src_rank, token, k, expert}
+    expert_token_nums: torch.Tensor   # [experts_per_rank] int64
+    send_counts: torch.Tensor         # [experts_per_rank * world] int32, running sum
+    recv_total: torch.Tensor          # [1] int32
+    topk_ids: torch.Tensor            # [bs, k] int32 (negative = inactive)
+    topk_weights: torch.Tensor        # [bs, k] fp32 (only meaningful with fused routing)
+    bs: int
+    top_k: int
+    num_experts: int
+
+
+def dispatch(comm, x: torch.Tensor, *, num_experts: int, top_k: int, expert_ids: Optional[torch.Tensor] = None,
+             gate_logits: Optional[torch.Tensor] = None, selection_bias: Optional[torch.Tensor] = None,
+             active_mask: Optional[torch.Tensor] = None, quant_mode: int = QUANT_NONE, score_func: int = 0,
+             renormalize: bool = True, routed_scale: float = 1.0, token_nums_type: int = TOKEN_NUMS_COUNT,
+             max_recv_rows: Optional[int] = None, expand_x_out: Optional[torch.Tensor] = None) -> DispatchResult:
+    bs = x.shape[0]
+    if max_recv_rows is None:
+        max_recv_rows = bs * comm.world_size * min(top_k, num_experts // comm.world_size)
+    out = _C.ep_dispatch(comm, x, expert_ids, gate_logits, selection_bias, active_mask, top_k, num_experts, quant_mode,
+                         score_func, renormalize, routed_scale, token_nums_type, max_recv_rows, expand_x_out)
+    return DispatchResult(*out, bs=bs, top_k=top_k, num_experts=num_experts)
+
+
+def combine(comm, expert_out: torch.Tensor, d: DispatchResult, *, expert_scales: Optional[torch.Tensor] = None,
+            active_mask: Optional[torch.Tensor] = None, shared_expert_x: Optional[torch.Tensor] = None,
+            y_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    return _C.ep_combine(comm, expert_out, d.assist, d.send_counts, d.topk_ids, expert_scales, active_mask, shared_expert_x,
+                         d.bs, d.top_k, d.num_experts, y_out)
