@@ -1,0 +1,344 @@
+#!/usr/bin/env python
+"""Headline benchmark: expert-parallel dispatch + combine of a DeepSeek-V3 shaped MoE block.
+
+Per rank: 4096 tokens x hidden 7168 (bf16), 256 routed experts (256/N per GPU), sigmoid top-8
+routing with renormalised weights done inside the dispatch kernel, tokens transported as fp8
+e4m3 with 1x128 fp32 scales, combine in bf16 with the gate-weighted fp32 reduction.  One step =
+dispatch -> fp8-to-bf16 dequantisation of the received rows (the stand-in for the expert FFN,
+so that combine gets real rows) -> combine.  Weak scaling: tokens per GPU stay fixed.
+
+    python bench.py --gpus 1
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+        --master-port 29511 bench.py --gpus 8 --steps 20 --warmup 5
+
+Rank 0 prints one JSON line.  `value` is tokens per second through dispatch+combine, summed
+over all GPUs; `ms_per_step` is the device time of one step, max over ranks.  `--impl nccl`
+runs the same workload with torch ops + NCCL all_to_all_single (the baseline this repository
+is measured against); `--impl reference` reports why the Ascend-only reference cannot run.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import socket
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+# Ascend950 model replay of the same shape (S 4096, K 8, H 7168, EP8): dispatch fwd 2646 us +
+# combine fwd 3021 us per 4096 tokens per rank (reference file
+# tools/moonep/model_replay_meta/model-replay-s4096-k8-h7168-ep8-r8/performance.json).
+PUBLISHED_TOKENS_PER_S_PER_RANK = 4096 / ((2646 + 3021) * 1e-6)
+
+
+def parse_args():
+    p = argparse.ArgumentParser()
+    p.add_argument("--gpus", type=int, default=1)
+    p.add_argument("--steps", type=int, default=20)
+    p.add_argument("--warmup", type=int, default=5)
+    p.add_argument("--impl", default="tilexr", choices=["tilexr", "nccl", "reference"])
+    p.add_argument("--tokens", type=int, default=4096)
+    p.add_argument("--hidden", type=int, default=7168)
+    p.add_argument("--experts", type=int, default=256)
+    p.add_argument("--topk", type=int, default=8)
+    p.add_argument("--no-e2e", action="store_true")
+    return p.parse_args()
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons through NVML (read-only) while the benchmark runs."""
+
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
+
+    def __init__(self, device_index: int):
+        self.device_index = device_index
+        self.samples = []          # (time, sm_mhz, reasons bitmask)
+        self.stop_flag = threading.Event()
+        self.thread = None
+        self.max_mhz = None
+        self.windows = []
+
+    def start(self):
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self.nvml = pynvml
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(self.device_index)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self.nvml = None
+            return
+        self.thread = threading.Thread(target=self._loop, daemon=True)
+        self.thread.start()
+
+    def _loop(self):
+        nv = self.nvml
+        while not self.stop_flag.is_set():
+            try:
+                mhz = float(nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM))
+                reasons = int(nv.nvmlDeviceGetCurrentClocksEventReasons(self.handle))
+                self.samples.append((time.time(), mhz, reasons))
+            except Exception:
+                pass
+            time.sleep(0.002)
+
+    def mark(self, t0: float, t1: float):
+        """A timed region; only samples inside marked regions are reported."""
+        self.windows.append((t0, t1))
+
+    def stop(self):
+        self.stop_flag.set()
+        if self.thread is not None:
+            self.thread.join(timeout=2)
+        inside = [s for s in self.samples if any(a <= s[0] <= b for a, b in self.windows)]
+        if not inside:
+            inside = self.samples
+        if not inside:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0}
+        mask = 0
+        for s in inside:
+            mask |= s[2]
+        reasons = sorted(name for bit, name in self.REASONS.items() if mask & bit)
+        return {"sm_mhz": statistics.median(s[1] for s in inside), "sm_max_mhz": self.max_mhz, "reasons": reasons,
+                "samples": len(inside)}
+
+
+def physical_device_index(local_rank: int) -> int:
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        try:
+            return int(vis.split(",")[local_rank])
+        except (ValueError, IndexError):
+            return local_rank
+    return local_rank
+
+
+def free_port() -> int:
+    with socket.socket(socket.AF_INET, socket.SOCK_STREAM) as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def reference_unavailable():
+    print(json.dumps({
+        "impl": "reference",
+        "unavailable": "the reference builds only for Huawei Ascend (CANN toolchain, AICore kernels); it has no "
+                       "setup.py/pyproject.toml and no CUDA path, so it cannot be installed or run on a B200",
+    }))
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        reference_unavailable()
+        return 0
+
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("launch with torch.distributed.run --nproc-per-node N for --gpus N > 1")
+        args.gpus = world
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+
+    import tilexr_b200 as txr
+    from tilexr_b200.models import ExpertParallelMoE, MoEConfig
+    from tilexr_b200.ops import ep, quant
+
+    T, H, E, K = args.tokens, args.hidden, args.experts, args.topk
+    cap = int(T * K * 1.125) // 128 * 128 if world > 1 else T * K
+    steps, warmup = args.steps, max(args.warmup, 3)
+
+    g = torch.Generator(device="cpu").manual_seed(20260 + rank)
+    n_buf = 4     # 4 x 58.7 MB of tokens rotate, so the inputs of consecutive steps exceed the 126 MB L2
+    x_host = [torch.randn(T, H, generator=g).to(torch.bfloat16).pin_memory() for _ in range(n_buf)]
+    logit_host = [torch.randn(T, E, generator=g).pin_memory() for _ in range(n_buf)]
+    x_dev = [t.to(dev) for t in x_host]
+    logit_dev = [t.to(dev) for t in logit_host]
+
+    cfg = MoEConfig(hidden=H, ffn=0, num_experts=E, top_k=K, score_func=quant.SCORE_SIGMOID, renormalize=True,
+                    fp8_dispatch=True)
+
+    if args.impl == "tilexr":
+        if world > 1:
+            comm = txr.init_from_torch_distributed(buffer_mb=1024)
+        else:
+            comm = txr.init_process(0, 1, comm_id=f"127.0.0.1:{free_port()}", buffer_mb=1024, device=local_rank)
+        layer = ExpertParallelMoE(comm, cfg, device=dev, with_experts=False)
+        recv = comm.symm_empty([cap, H], torch.float8_e4m3fn)     # peers store received rows here directly
+
+        def step(i):
+            return layer(x_dev[i % n_buf], gate_logits=logit_dev[i % n_buf], max_recv_rows=cap, expand_x_out=recv)
+
+        def step_parts(i, ev):
+            x, lg = x_dev[i % n_buf], logit_dev[i % n_buf]
+            ev[0].record()
+            d = ep.dispatch(comm, x, gate_logits=lg, num_experts=E, top_k=K, quant_mode=ep.QUANT_FP8_1X128,
+                            score_func=quant.SCORE_SIGMOID, renormalize=True, max_recv_rows=cap, expand_x_out=recv)
+            ev[1].record()
+            rows = quant.fp8_dequant_1x128(d.expand_x, d.dynamic_scales, torch.bfloat16)
+            ev[2].record()
+            y = ep.combine(comm, rows, d, expert_scales=d.topk_weights)
+            ev[3].record()
+            return y
+    else:
+        from tilexr_b200.tools.nccl_baseline import NcclMoEBaseline
+
+        comm = None
+        base = NcclMoEBaseline(world, rank, E, K, dev)
+
+        def step(i):
+            return base.step(x_dev[i % n_buf], logit_dev[i % n_buf])
+
+        def step_parts(i, ev):
+            return base.step(x_dev[i % n_buf], logit_dev[i % n_buf], ev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(v: float) -> float:
+        if world == 1:
+            return v
+        t = torch.tensor([v], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def check():
+        if comm is not None and comm.device_status() != 0:
+            comm.print_dfx()
+            raise SystemExit("a device-side wait gave up; see the DFX line above")
+
+    # ---- device-timed loop --------------------------------------------------------------------------
+    for i in range(warmup):
+        step(i)
+    barrier()
+    check()
+    sampler = ClockSampler(physical_device_index(local_rank))
+    sampler.start()
+    launches0 = txr.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    wall0 = time.time()
+    e0.record()
+    for i in range(steps):
+        y = step(i)
+    e1.record()
+    barrier()
+    sampler.mark(wall0, time.time())
+    launches = txr.launch_count() - launches0
+    ms_per_step = max_over_ranks(e0.elapsed_time(e1) / steps)
+    check()
+
+    # per-phase medians (separate pass, not the headline)
+    parts = []
+    for i in range(min(steps, 10)):
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+        step_parts(i, ev)
+        torch.cuda.synchronize()
+        parts.append([ev[j].elapsed_time(ev[j + 1]) * 1000 for j in range(3)])
+    phase_us = [max_over_ranks(statistics.median(p[j] for p in parts)) for j in range(3)]
+    barrier()
+
+    # ---- end to end: pinned host inputs in, scalar result out, every step -----------------------------
+    e2e = None
+    if not args.no_e2e:
+        xin = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+        lin = torch.empty(T, E, dtype=torch.float32, device=dev)
+        result_host = torch.empty(1, dtype=torch.float32).pin_memory()
+
+        def e2e_step(i):
+            xin.copy_(x_host[i % n_buf], non_blocking=True)
+            lin.copy_(logit_host[i % n_buf], non_blocking=True)
+            if args.impl == "tilexr":
+                yy = layer(xin, gate_logits=lin, max_recv_rows=cap, expand_x_out=recv)
+            else:
+                yy = base.step(xin, lin)
+            result_host.copy_(yy[0, :1].float(), non_blocking=True)
+
+        for i in range(3):
+            e2e_step(i)
+        barrier()
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        wall0 = time.time()
+        s0.record()
+        for i in range(steps):
+            e2e_step(i)
+        s1.record()
+        barrier()
+        sampler.mark(wall0, time.time())
+        e2e_ms = max_over_ranks(s0.elapsed_time(s1) / steps)
+        e2e = {
+            "value": T * world / (e2e_ms * 1e-3),
+            "unit": "tokens/s",
+            "ms_per_step": e2e_ms,
+            "h2d_bytes_per_step": x_host[0].numel() * 2 + logit_host[0].numel() * 4,
+            "d2h_bytes_per_step": 4,
+        }
+        check()
+    clocks = sampler.stop()
+
+    value = T * world / (ms_per_step * 1e-3)
+    route_bytes = H + H // 128 * 4 + 16                 # fp8 row + scales + assist tuple
+    remote = (world - 1) / world
+    out = {
+        "metric": "ep_dispatch_combine_tokens_per_s",
+        "value": value,
+        "unit": "tokens/s",
+        "impl": args.impl,
+        "n_gpus": world,
+        "steps": steps,
+        "warmup": warmup,
+        "ms_per_step": ms_per_step,
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": value / (PUBLISHED_TOKENS_PER_S_PER_RANK * world),
+        "baseline_note": "published: Ascend950 EP8 model replay, dispatch fwd 2646 us + combine fwd 3021 us per 4096 tokens/rank",
+        "dtype": "fp8 e4m3 (1x128 scales) dispatch, bf16 combine",
+        "data": "synthetic: seeded N(0,1) tokens and gate logits, no weights needed (identity expert)",
+        "config": {
+            "model": "DeepSeek-V3 MoE block (EP dispatch+combine)",
+            "tokens_per_rank": T, "global_batch": T * world, "seq_len": 1, "hidden": H, "experts": E, "top_k": K,
+            "parallelism": f"ep{world}",
+            "l2": f"inputs rotate over {n_buf} buffers of {x_host[0].numel() * 2 / 1e6:.1f} MB (> 126 MB L2 in total)",
+            "recv_capacity_rows": cap,
+        },
+        "phases_us": {"dispatch": phase_us[0], "dequant_standin": phase_us[1], "combine": phase_us[2]},
+        "nvlink_GBps_per_gpu": {
+            "dispatch": T * K * remote * route_bytes / (phase_us[0] * 1e-6) / 1e9 if world > 1 else 0.0,
+            "combine": T * K * remote * H * 2 / (phase_us[2] * 1e-6) / 1e9 if world > 1 else 0.0,
+        },
+        "clocks": clocks,
+        "gpu_launches": int(launches),
+    }
+    if e2e is not None:
+        out["e2e"] = e2e
+    if rank == 0:
+        print(json.dumps(out))
+    if comm is not None:
+        comm.destroy()
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -87,6 +87,7 @@ int IssueWorldLaunch(EmulatedWorld *world, std::vector<PendingLaunch *> &perRank
 } // namespace
 
 uint64_t LaunchCount() { return g_launches.load(); }
+void NoteLaunch() { g_launches.fetch_add(1); }
 
 int LaunchKernel(TileXRCommPtr commPtr, const KernelEntry &kernel, const void *args, const LaunchConfig &cfg,
                  TileXRStream streamPtr)

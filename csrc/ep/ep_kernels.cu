@@ -734,6 +734,7 @@ int CheckLaunch(const char *what)
         fprintf(stderr, "[TileXR] %s launch failed: %s\n", what, cudaGetErrorString(e));
         return TILEXR_ERROR_RUNTIME;
     }
+    NoteLaunch();
     return TILEXR_SUCCESS;
 }
 

@@ -40,6 +40,8 @@ int LaunchKernel(TileXRCommPtr comm, const KernelEntry &kernel, const void *args
 
 // Number of kernels this library launched since the process started (all communicators).
 uint64_t LaunchCount();
+// Called by code that launches a kernel directly (local ops without a communicator).
+void NoteLaunch();
 
 // Largest grid of `kernel` that can be co-resident on the communicator's device.
 int MaxCooperativeGrid(TileXRCommPtr comm, const KernelEntry &kernel, unsigned block, size_t smemBytes, int ranksPerDevice,

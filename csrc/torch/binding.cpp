@@ -63,6 +63,20 @@ void RequireContiguous(const at::Tensor &t, const char *name)
     TORCH_CHECK(t.is_contiguous(), name, " must be contiguous");
 }
 
+// Launches on an emulated world are deferred until the group ends, so tensors handed to an op
+// inside a group must outlive the call: they are parked here until group_end.
+thread_local int g_groupDepth = 0;
+thread_local std::vector<at::Tensor> g_groupKeep;
+
+void Keep(const at::Tensor &t)
+{
+    if (g_groupDepth > 0 && t.defined()) g_groupKeep.push_back(t);
+}
+void Keep(const c10::optional<at::Tensor> &t)
+{
+    if (t.has_value()) Keep(*t);
+}
+
 // Exchange over a torch Store: every rank publishes its bytes under a per-call key.
 struct StoreExchangeCtx {
     c10::intrusive_ptr<c10d::Store> store;
@@ -253,6 +267,8 @@ void AllGather(const CommPtr &c, const at::Tensor &in, at::Tensor out)
 {
     RequireContiguous(in, "input");
     RequireContiguous(out, "output");
+    Keep(in);
+    Keep(out);
     TORCH_CHECK(out.numel() == in.numel() * c->rankSize() && out.scalar_type() == in.scalar_type(), "all_gather: bad output");
     Check(TileXRAllGather(in.data_ptr(), out.data_ptr(), in.numel(), ToDtype(in.scalar_type()), c->ptr(), StreamOf(in)),
           "TileXRAllGather");
@@ -262,6 +278,8 @@ void AllToAll(const CommPtr &c, const at::Tensor &in, at::Tensor out)
 {
     RequireContiguous(in, "input");
     RequireContiguous(out, "output");
+    Keep(in);
+    Keep(out);
     TORCH_CHECK(out.numel() == in.numel() && in.numel() % c->rankSize() == 0 && out.scalar_type() == in.scalar_type(),
                 "all_to_all: sizes must match and divide by the rank count");
     Check(TileXRAllToAll(in.data_ptr(), out.data_ptr(), in.numel() / c->rankSize(), ToDtype(in.scalar_type()), c->ptr(),
@@ -273,6 +291,8 @@ void AllReduce(const CommPtr &c, const at::Tensor &in, at::Tensor out, int op)
 {
     RequireContiguous(in, "input");
     RequireContiguous(out, "output");
+    Keep(in);
+    Keep(out);
     TORCH_CHECK(out.numel() == in.numel() && out.scalar_type() == in.scalar_type(), "all_reduce: bad output");
     Check(TileXRAllReduce(in.data_ptr(), out.data_ptr(), in.numel(), ToDtype(in.scalar_type()),
                           static_cast<TileXR::TileXRReduceOp>(op), c->ptr(), StreamOf(in)),
@@ -283,6 +303,8 @@ void ReduceScatter(const CommPtr &c, const at::Tensor &in, at::Tensor out, int o
 {
     RequireContiguous(in, "input");
     RequireContiguous(out, "output");
+    Keep(in);
+    Keep(out);
     TORCH_CHECK(in.numel() == out.numel() * c->rankSize() && out.scalar_type() == in.scalar_type(), "reduce_scatter: bad output");
     Check(TileXRReduceScatter(in.data_ptr(), out.data_ptr(), out.numel(), ToDtype(in.scalar_type()),
                               static_cast<TileXR::TileXRReduceOp>(op), c->ptr(), StreamOf(in)),
@@ -292,6 +314,7 @@ void ReduceScatter(const CommPtr &c, const at::Tensor &in, at::Tensor out, int o
 void Broadcast(const CommPtr &c, at::Tensor buf, int root)
 {
     RequireContiguous(buf, "buffer");
+    Keep(buf);
     Check(TileXRBroadcast(buf.data_ptr(), buf.numel(), ToDtype(buf.scalar_type()), root, c->ptr(), StreamOf(buf)),
           "TileXRBroadcast");
 }
@@ -300,6 +323,8 @@ void ProfileProbe(const CommPtr &c, const at::Tensor &in, at::Tensor out)
 {
     RequireContiguous(in, "input");
     RequireContiguous(out, "output");
+    Keep(in);
+    Keep(out);
     TORCH_CHECK(out.nbytes() >= in.nbytes(), "profile_probe: output too small");
     Check(TileXRProfileProbe(in.data_ptr(), out.data_ptr(), in.numel(), ToDtype(in.scalar_type()), c->ptr(), StreamOf(in)),
           "TileXRProfileProbe");
@@ -335,6 +360,11 @@ py::tuple EpDispatch(const CommPtr &c, const at::Tensor &x, const c10::optional<
 {
     RequireContiguous(x, "x");
     TORCH_CHECK(x.dim() == 2 && x.is_cuda(), "x must be a 2-D CUDA tensor");
+    Keep(x);
+    Keep(expertIds);
+    Keep(gateLogits);
+    Keep(selectionBias);
+    Keep(activeMask);
     const int64_t bs = x.size(0), h = x.size(1);
     const int R = c->rankSize();
     const int64_t localExperts = numExperts / R;
@@ -387,6 +417,7 @@ py::tuple EpDispatch(const CommPtr &c, const at::Tensor &x, const c10::optional<
     p.sendCountsOut = sendCounts.data_ptr<int32_t>();
     p.recvTotalOut = recvTotal.data_ptr<int32_t>();
     p.dtype = ToDtype(x.scalar_type());
+    for (const at::Tensor &t : {expandX, scales, assist, tokenNums, sendCounts, recvTotal, topkIds, topkWeights}) Keep(t);
     Check(TileXRMoeEpDispatchFused(&p, c->ptr(), StreamOf(x)), "TileXRMoeEpDispatchFused");
     return py::make_tuple(expandX, quant ? py::cast(scales) : py::none(), assist, tokenNums, sendCounts, recvTotal, topkIds,
                           topkWeights);
@@ -399,6 +430,13 @@ at::Tensor EpCombine(const CommPtr &c, const at::Tensor &expertOut, const at::Te
 {
     RequireContiguous(expertOut, "expert_out");
     TORCH_CHECK(expertOut.dim() == 2 && expertOut.is_cuda(), "expert_out must be a 2-D CUDA tensor");
+    Keep(expertOut);
+    Keep(assist);
+    Keep(sendCounts);
+    Keep(expertIds);
+    Keep(expertScales);
+    Keep(activeMask);
+    Keep(sharedExpertX);
     const int64_t h = expertOut.size(1);
     at::Tensor y = yOut.has_value() && yOut->defined() ? *yOut : at::empty({bs, h}, expertOut.options());
     TileXREpCombineParams p;
@@ -419,6 +457,7 @@ at::Tensor EpCombine(const CommPtr &c, const at::Tensor &expertOut, const at::Te
     p.moeExpertNum = numExperts;
     p.yOut = y.data_ptr();
     p.dtype = ToDtype(expertOut.scalar_type());
+    Keep(y);
     Check(TileXRMoeEpCombineFused(&p, c->ptr(), StreamOf(expertOut)), "TileXRMoeEpCombineFused");
     return y;
 }
@@ -544,8 +583,16 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m)
     m.def("init_host_memory", &InitHostMemory, py::arg("rank"), py::arg("world_size"), py::arg("comm_id") = "",
           py::arg("domain") = 0, py::arg("buffer_mb") = 64);
     m.def("init_emulated", &InitEmulated, py::arg("world_size"), py::arg("device") = 0, py::arg("buffer_mb") = 64);
-    m.def("group_start", [] { Check(TileXRGroupStart(), "TileXRGroupStart"); });
-    m.def("group_end", [] { Check(TileXRGroupEnd(), "TileXRGroupEnd"); });
+    m.def("group_start", [] {
+        Check(TileXRGroupStart(), "TileXRGroupStart");
+        g_groupDepth += 1;
+    });
+    m.def("group_end", [] {
+        if (g_groupDepth > 0) g_groupDepth -= 1;
+        const int status = TileXRGroupEnd();
+        if (g_groupDepth == 0) g_groupKeep.clear();   // the launches are enqueued: stream order protects the memory now
+        Check(status, "TileXRGroupEnd");
+    });
     m.def("launch_count", [] { return TileXR::LaunchCount(); });
     m.def("all_gather", &AllGather);
     m.def("all_to_all", &AllToAll);

@@ -1,0 +1,179 @@
+"""Expert-parallel dispatch / combine and the local hot ops against fp32 PyTorch references."""
+import pytest
+import torch
+
+from conftest import require_cuda
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def txr():
+    require_cuda()
+    import tilexr_b200
+
+    return tilexr_b200
+
+
+@pytest.mark.parametrize("score_func,renorm,bias", [(0, True, False), (1, True, False), (1, False, True)])
+def test_routing_topk(txr, score_func, renorm, bias):
+    from tilexr_b200.utils import oracle
+
+    g = torch.Generator().manual_seed(0)
+    logits = torch.randn(333, 256, generator=g)
+    b = torch.randn(256, generator=g) * 0.1 if bias else None
+    ids, w = txr.quant.routing_topk(logits.cuda(), 8, score_func, renorm, 2.5, None if b is None else b.cuda())
+    rids, rw = oracle.routing_topk_ref(logits, 8, score_func, renorm, 2.5, b)
+    assert torch.equal(ids.cpu(), rids)
+    assert torch.allclose(w.cpu(), rw, rtol=1e-5, atol=1e-7)
+
+
+def test_fp8_quant_1x128_matches_reference(txr):
+    from tilexr_b200.utils import oracle
+
+    g = torch.Generator().manual_seed(1)
+    x = (torch.randn(257, 7168, generator=g) * 3).to(torch.bfloat16)
+    x[5] = 0       # an all-zero row hits the amax floor
+    q, s = txr.quant.fp8_quant_1x128(x.cuda())
+    rq, rs = oracle.fp8_quant_1x128_ref(x)
+    assert torch.equal(s.cpu(), rs)
+    assert torch.equal(q.cpu().view(torch.uint8), rq.view(torch.uint8))
+    back = txr.quant.fp8_dequant_1x128(q, s, torch.bfloat16)
+    ref_back = oracle.fp8_dequant_1x128_ref(rq, rs).to(torch.bfloat16)
+    assert torch.equal(back.cpu(), ref_back)
+    rel = (back.cpu().float() - x.float()).abs().max() / x.float().abs().max()
+    assert rel < 0.07
+
+
+@pytest.mark.parametrize("e5m2", [False, True])
+def test_mxfp8_matches_reference(txr, e5m2):
+    from tilexr_b200.utils import oracle
+
+    g = torch.Generator().manual_seed(2)
+    x = (torch.randn(64, 1000, generator=g) * torch.logspace(-3, 3, 1000)).to(torch.float16)
+    q, s = txr.quant.mxfp8_quant(x.cuda(), e5m2)
+    rq, rs = oracle.mxfp8_quant_ref(x, e5m2)
+    assert torch.equal(s.cpu(), rs)
+    assert torch.equal(q.cpu().view(torch.uint8), rq.view(torch.uint8))
+    back = txr.quant.mxfp8_dequant(q, s, torch.float16)
+    assert torch.allclose(back.cpu().float(), oracle.mxfp8_dequant_ref(rq, rs).to(torch.float16).float(), rtol=0, atol=0)
+
+
+@pytest.mark.parametrize("with_residual", [False, True])
+def test_rmsnorm(txr, with_residual):
+    from tilexr_b200.utils import oracle
+
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(37, 8192, generator=g).to(torch.bfloat16)
+    gamma = (1 + 0.1 * torch.randn(8192, generator=g)).to(torch.bfloat16)
+    res = torch.randn(37, 8192, generator=g).to(torch.bfloat16) if with_residual else None
+    res_dev = res.cuda() if with_residual else None
+    y = txr.quant.rmsnorm(x.cuda(), gamma.cuda(), 1e-6, res_dev)
+    ry, rres = oracle.rmsnorm_ref(x, gamma, 1e-6, res)
+    assert torch.allclose(y.cpu().float(), ry.float(), rtol=2e-2, atol=2e-2)
+    assert (y.cpu().float() - ry.float()).abs().mean() < 2e-3
+    if with_residual:
+        assert torch.equal(res_dev.cpu(), rres)
+
+
+def _ep_case(txr, ranks, bs, h, experts, top_k, quant, fused_routing, masks=False, zero_copy=False, dtype=torch.bfloat16):
+    from tilexr_b200.ops import ep
+    from tilexr_b200.utils import oracle
+
+    world = txr.init_emulated_world(ranks, device=0, buffer_mb=128)
+    g = torch.Generator().manual_seed(11)
+    xs = [torch.randn(bs, h, generator=g).to(dtype) for _ in range(ranks)]
+    logits = [torch.randn(bs, experts, generator=g) for _ in range(ranks)]
+    routed = [oracle.routing_topk_ref(l, top_k, 1, True, 1.0) for l in logits]
+    ids = [r[0] for r in routed]
+    ws = [r[1] for r in routed]
+    mask = None
+    if masks:
+        mask = [(torch.rand(bs, generator=g) > 0.3) for _ in range(ranks)]
+    max_rows = bs * ranks * min(top_k, experts // ranks)
+    outs = world.symm_empty((max_rows, h), torch.float8_e4m3fn if quant else dtype) if zero_copy else [None] * ranks
+    for _ in range(2):
+        def call(c, r):
+            kw = dict(num_experts=experts, top_k=top_k, quant_mode=ep.QUANT_FP8_1X128 if quant else ep.QUANT_NONE,
+                      score_func=1, renormalize=True, max_recv_rows=max_rows, expand_x_out=outs[r],
+                      active_mask=None if mask is None else mask[r].cuda())
+            if fused_routing:
+                return ep.dispatch(c, xs[r].cuda(), gate_logits=logits[r].cuda(), **kw)
+            return ep.dispatch(c, xs[r].cuda(), expert_ids=ids[r].cuda(), **kw)
+        res = world.run(call)
+        world.check()
+    ref = oracle.ep_dispatch_ref(xs, ids, experts, mask)
+    expert_outs = []
+    for r in range(ranks):
+        d = res[r]
+        n = int(d.recv_total.item())
+        assert n == len(ref[r]["rows"])
+        assert torch.equal(d.assist[:n].cpu(), ref[r]["assist"])
+        assert torch.equal(d.expert_token_nums.cpu(), ref[r]["token_nums"])
+        assert torch.equal(d.send_counts.cpu(), ref[r]["send_counts"])
+        if fused_routing:
+            assert torch.equal(d.topk_ids.cpu(), ids[r])
+            assert torch.allclose(d.topk_weights.cpu(), ws[r], rtol=1e-5, atol=1e-7)
+        if quant:
+            rq, rs = oracle.fp8_quant_1x128_ref(ref[r]["expand_x"]) if n else (None, None)
+            if n:
+                assert torch.equal(d.expand_x[:n].cpu().view(torch.uint8), rq.view(torch.uint8))
+                assert torch.equal(d.dynamic_scales[:n].cpu(), rs)
+            rows = txr.quant.fp8_dequant_1x128(d.expand_x, d.dynamic_scales, dtype)
+        else:
+            assert torch.equal(d.expand_x[:n].cpu(), ref[r]["expand_x"])
+            rows = d.expand_x
+        # stand-in expert: scale by (1 + local expert index / 8)
+        e_local = (d.assist[:, 3] % (experts // ranks)).clamp(min=0).float().cuda()
+        out = (rows.float() * (1 + e_local / 8).unsqueeze(1)).to(dtype)
+        expert_outs.append(out)
+
+    ys = world.run(lambda c, r: ep.combine(c, expert_outs[r], res[r], expert_scales=ws[r].cuda(),
+                                           active_mask=None if mask is None else mask[r].cuda()))
+    world.check()
+    ref_outs = [expert_outs[r][: len(ref[r]["rows"])].cpu() for r in range(ranks)]
+    yref = oracle.ep_combine_ref(ref, ref_outs, ids, ws, dtype)
+    for r in range(ranks):
+        got = ys[r].cpu().float()
+        want = yref[r].float()
+        if mask is not None:
+            want = want * mask[r].unsqueeze(1).float()
+        assert torch.allclose(got, want, rtol=2e-2, atol=2e-2), (got - want).abs().max()
+        assert (got - want).abs().mean() < 1e-3
+    world.destroy()
+
+
+def test_ep_bf16_explicit_ids(txr):
+    _ep_case(txr, ranks=4, bs=48, h=256, experts=16, top_k=2, quant=False, fused_routing=False)
+
+
+def test_ep_fp8_fused_routing(txr):
+    _ep_case(txr, ranks=4, bs=40, h=1024, experts=32, top_k=4, quant=True, fused_routing=True)
+
+
+def test_ep_token_mask(txr):
+    _ep_case(txr, ranks=2, bs=33, h=512, experts=8, top_k=2, quant=True, fused_routing=False, masks=True)
+
+
+def test_ep_zero_copy_output(txr):
+    _ep_case(txr, ranks=4, bs=64, h=512, experts=16, top_k=4, quant=True, fused_routing=True, zero_copy=True)
+
+
+def test_ep_eight_ranks_fp16(txr):
+    _ep_case(txr, ranks=8, bs=24, h=512, experts=64, top_k=8, quant=False, fused_routing=True, dtype=torch.float16)
+
+
+def test_ep_overflow_is_reported_not_written(txr):
+    from tilexr_b200.ops import ep
+
+    world = txr.init_emulated_world(2, device=0, buffer_mb=64)
+    x = [torch.randn(16, 256).to(torch.bfloat16).cuda() for _ in range(2)]
+    ids = [torch.zeros(16, 2, dtype=torch.int32).cuda() for _ in range(2)]     # every route to expert 0
+    ids[0][:, 1] = 1
+    ids[1][:, 1] = 1
+    world.run(lambda c, r: ep.dispatch(c, x[r], expert_ids=ids[r], num_experts=4, top_k=2, max_recv_rows=8))
+    torch.cuda.synchronize()
+    assert all(c.device_status() == 4 for c in world.comms)      # TILEXR_DEV_BAD_ARGUMENT on every rank
+    for c in world.comms:
+        c.reset_status()
+    world.destroy()

@@ -1,0 +1,85 @@
+"""One process per GPU over NVLink peer mappings (CUDA IPC), bootstrapped by the library's own
+TCP exchange.  Needs at least two GPUs; on a one-GPU box the emulated-world tests cover the
+same kernels."""
+import os
+import traceback
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+from conftest import free_port
+
+pytestmark = pytest.mark.gpu
+
+
+def _worker(rank, world, port, q):
+    try:
+        os.environ["TILEXR_WAIT_TIMEOUT_MS"] = "5000"
+        torch.cuda.set_device(rank)
+        import tilexr_b200 as txr
+        from tilexr_b200.ops import ep
+        from tilexr_b200.utils import oracle
+
+        comm = txr.init_process(rank, world, comm_id=f"127.0.0.1:{port}", buffer_mb=128, device=rank)
+        gens = [torch.Generator().manual_seed(100 + r) for r in range(world)]
+        xs = [torch.randn(1 << 18, generator=g).to(torch.bfloat16) for g in gens]
+        mine = xs[rank].cuda()
+        for _ in range(3):
+            ag = txr.all_gather(comm, mine)
+            ar = txr.all_reduce(comm, mine)
+            a2a = txr.all_to_all(comm, mine)
+            rs = txr.reduce_scatter(comm, mine)
+        sym = comm.symm_empty([world, 1 << 18], torch.bfloat16)
+        txr.all_gather(comm, mine, out=sym)
+        b = mine.clone()
+        txr.broadcast(comm, b, root=world - 1)
+        torch.cuda.synchronize()
+        assert comm.device_status() == 0
+        assert torch.equal(ag.cpu().reshape(-1), oracle.all_gather_ref(xs))
+        assert torch.equal(sym.cpu().reshape(-1), oracle.all_gather_ref(xs))
+        full = oracle.all_reduce_ref(xs)
+        assert torch.equal(ar.cpu(), full)
+        assert torch.equal(a2a.cpu(), oracle.all_to_all_ref(xs)[rank])
+        n = (1 << 18) // world
+        assert torch.equal(rs.cpu(), full[rank * n:(rank + 1) * n])
+        assert torch.equal(b.cpu(), xs[world - 1])
+
+        bs, h, E, K = 64, 1024, 8 * world, 4
+        tok = [torch.randn(bs, h, generator=g).to(torch.bfloat16) for g in gens]
+        logits = [torch.randn(bs, E, generator=g) for g in gens]
+        routed = [oracle.routing_topk_ref(l, K, 1, True) for l in logits]
+        d = ep.dispatch(comm, tok[rank].cuda(), gate_logits=logits[rank].cuda(), num_experts=E, top_k=K,
+                        quant_mode=ep.QUANT_FP8_1X128, score_func=1)
+        rows = txr.quant.fp8_dequant_1x128(d.expand_x, d.dynamic_scales, torch.bfloat16)
+        y = ep.combine(comm, rows, d, expert_scales=d.topk_weights)
+        torch.cuda.synchronize()
+        assert comm.device_status() == 0
+        ref = oracle.ep_dispatch_ref(tok, [r[0] for r in routed], E)[rank]
+        cnt = int(d.recv_total.item())
+        assert cnt == len(ref["rows"])
+        assert torch.equal(d.assist[:cnt].cpu(), ref["assist"])
+        # identity expert: y ~= sum_k w_k * dequant(quant(x)) ~= x
+        err = (y.cpu().float() - tok[rank].float()).abs().max().item()
+        assert err < 0.35, err
+        comm.destroy()
+        q.put((rank, "ok"))
+    except Exception:
+        q.put((rank, traceback.format_exc()))
+
+
+def test_process_per_gpu_collectives_and_ep():
+    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    world = min(torch.cuda.device_count(), 4)
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=240) for _ in procs]
+    for p in procs:
+        p.join(timeout=30)
+    for rank, status in results:
+        assert status == "ok", f"rank {rank}:\n{status}"

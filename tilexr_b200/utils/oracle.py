@@ -40,9 +40,10 @@ def fp8_quant_1x128_ref(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     rows, h = xf.shape
     g = xf.view(rows, h // 128, 128)
     amax = g.abs().amax(dim=-1).clamp_min(AMAX_FLOOR)
-    inv = (FP8_MAX / amax).unsqueeze(-1)
+    # tensor / tensor: a true IEEE division (scalar / tensor is reciprocal-then-multiply in torch)
+    inv = (torch.full_like(amax, FP8_MAX) / amax).unsqueeze(-1)
     q = (g * inv).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn).view(rows, h)
-    return q, amax / FP8_MAX
+    return q, amax / torch.full_like(amax, FP8_MAX)
 
 
 def fp8_dequant_1x128_ref(q: torch.Tensor, scales: torch.Tensor) -> torch.Tensor:
