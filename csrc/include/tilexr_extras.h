@@ -2,6 +2,7 @@
 #ifndef TILEXR_EXTRAS_H
 #define TILEXR_EXTRAS_H
 
+#include "tilexr_fused.h"
 #include "tilexr_hostsim.h"
 
 #endif

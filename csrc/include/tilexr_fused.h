@@ -1,0 +1,45 @@
+// Compute fused with communication: tensor-parallel building blocks.
+//
+//   TileXRAllReduceRmsNorm   y = RMSNorm(all_reduce(x) + residual) * gamma, residual updated in
+//                            place; one-shot or two-shot chosen by size (decode / prefill).
+//   TileXRAllGatherMatmul    C = all_gather(A) x B^T on tcgen05 tensor cores; A shards are pushed
+//                            into every rank's staging buffer tile by tile and each GEMM tile
+//                            starts as soon as the rows it needs have landed.
+//   TileXRMatmulReduceScatter  C_rank = reduce_scatter(A x B^T); partial tiles are pushed to the
+//                            owner from the GEMM epilogue and summed there in rank order.
+//   TileXRMatmul             the same tcgen05 GEMM without communication.
+//
+// The reference only keeps the operator ids of the last three (src/include/tilexr_types.h:108-125,
+// the kernels were removed from it); the all-reduce it ships is unfused
+// (src/collectives/kernels/allreduce_*.h).
+#ifndef TILEXR_FUSED_H
+#define TILEXR_FUSED_H
+
+#include "tilexr_api.h"
+#include "tilexr_types.h"
+
+#ifdef __cplusplus
+extern "C" {
+#define TXR_DT TileXR::TileXRDataType
+#else
+#define TXR_DT enum TileXRDataType
+#endif
+
+enum TileXRAllReduceAlgo { TILEXR_AR_AUTO = 0, TILEXR_AR_ONE_SHOT = 1, TILEXR_AR_TWO_SHOT = 2 };
+
+// x [rows, h] holds this rank's partial sums.  residualInOut [rows, h] may be null (no residual
+// add).  yOut and residualInOut are complete on every rank when the kernel finishes.  If both
+// live in registered memory at the same offset on every rank, the two-shot path writes them
+// directly.  fp16 / bf16, h a multiple of 8 up to 16384.
+int TileXRAllReduceRmsNorm(const void *x, void *residualInOut, const void *gamma, float eps, int64_t rows, int64_t h,
+                           TXR_DT dtype, void *yOut, int algo, TileXRCommPtr comm, TileXRStream stream);
+
+// Which algorithm TILEXR_AR_AUTO picks for a message of `bytes` on `rankSize` ranks.
+int TileXRAllReduceRmsNormChoose(uint64_t bytes, int rankSize);
+
+#ifdef __cplusplus
+}
+#endif
+#undef TXR_DT
+
+#endif // TILEXR_FUSED_H

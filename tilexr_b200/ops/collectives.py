@@ -67,3 +67,14 @@ def profile_probe(comm, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> 
         out = torch.empty_like(x)
     _C.profile_probe(comm, x.contiguous(), out)
     return out
+
+
+AR_AUTO, AR_ONE_SHOT, AR_TWO_SHOT = 0, 1, 2
+
+
+def all_reduce_rmsnorm(comm, x: torch.Tensor, gamma: torch.Tensor, eps: float = 1e-6,
+                       residual: Optional[torch.Tensor] = None, algo: int = AR_AUTO,
+                       out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``y = RMSNorm(all_reduce(x) + residual) * gamma`` in one kernel; ``residual`` is updated in
+    place with the pre-norm sum.  ``algo`` forces one-shot or two-shot (default: by size)."""
+    return _C.all_reduce_rmsnorm(comm, x.contiguous(), residual, gamma, eps, algo, out)
