@@ -1,0 +1,288 @@
+// Host side of the tcgen05 GEMM family: tensor-map construction, tiling, launch.
+#include <algorithm>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+
+#include <cuda.h>
+#include <cuda_runtime_api.h>
+
+#include "gemm_kernels.cuh"
+#include "tilexr_fused.h"
+#include "tilexr_log.h"
+
+using namespace TileXR;
+
+namespace {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn EncodeTiled()
+{
+    static EncodeTiledFn fn = [] {
+        void *f = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess) f = nullptr;
+        return reinterpret_cast<EncodeTiledFn>(f);
+    }();
+    return fn;
+}
+
+long EnvLong(const char *name, long fallback)
+{
+    const char *v = std::getenv(name);
+    if (v == nullptr || *v == '\0') return fallback;
+    char *end = nullptr;
+    const long x = std::strtol(v, &end, 10);
+    return *end == '\0' ? x : fallback;
+}
+
+// Row-major [rows, cols] 16-bit matrix, box = boxRows x 64 columns, 128-byte swizzle.
+int MakeMap(CUtensorMap *map, const void *base, int64_t rows, int64_t cols, int boxRows, bool bf16)
+{
+    EncodeTiledFn fn = EncodeTiled();
+    if (fn == nullptr) {
+        TILEXR_LOG(ERROR) << "cuTensorMapEncodeTiled is not available from this driver";
+        return TILEXR_ERROR_RUNTIME;
+    }
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * 2};
+    const cuuint32_t box[2] = {GEMM_BK, static_cast<cuuint32_t>(boxRows)};
+    const cuuint32_t elemStrides[2] = {1, 1};
+    const CUresult r = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+                          const_cast<void *>(base), dims, strides, box, elemStrides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        TILEXR_LOG(ERROR) << "cuTensorMapEncodeTiled failed with " << static_cast<int>(r) << " for a " << rows << "x" << cols
+                          << " matrix at " << base;
+        return TILEXR_ERROR_RUNTIME;
+    }
+    return TILEXR_SUCCESS;
+}
+
+int CheckShape(const void *a, const void *b, const void *c, int64_t m, int64_t n, int64_t k, int dtype)
+{
+    if (a == nullptr || b == nullptr || c == nullptr || m <= 0 || n <= 0 || k <= 0) return TILEXR_ERROR_PARA_CHECK_FAIL;
+    if (dtype != TILEXR_DATA_TYPE_FP16 && dtype != TILEXR_DATA_TYPE_BFP16) {
+        TILEXR_LOG(ERROR) << "matmul: fp16 or bf16 only";
+        return TILEXR_ERROR_PARA_CHECK_FAIL;
+    }
+    if (k % 8 != 0 || n % 8 != 0) {
+        TILEXR_LOG(ERROR) << "matmul: K and N must be multiples of 8 (16-byte rows for TMA and vector stores)";
+        return TILEXR_ERROR_PARA_CHECK_FAIL;
+    }
+    if ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(c)) & 15u) {
+        TILEXR_LOG(ERROR) << "matmul: operands must be 16-byte aligned";
+        return TILEXR_ERROR_PARA_CHECK_FAIL;
+    }
+    return TILEXR_SUCCESS;
+}
+
+int SmCount(int *sms)
+{
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return TILEXR_ERROR_RUNTIME;
+    if (cudaDeviceGetAttribute(sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return TILEXR_ERROR_RUNTIME;
+    return TILEXR_SUCCESS;
+}
+
+const KernelEntry &GemmEntry()
+{
+    static const KernelEntry e = {GemmKernelSingle(), GemmKernelEmulated(), sizeof(GemmArgs), "TileXRGemmTcgen05"};
+    return e;
+}
+
+void FillTiling(GemmArgs *g, int64_t m, int64_t n, int64_t k)
+{
+    g->M = static_cast<int32_t>(m);
+    g->N = static_cast<int32_t>(n);
+    g->K = static_cast<int32_t>(k);
+    g->mBlocks = static_cast<int32_t>((m + GEMM_BM - 1) / GEMM_BM);
+    g->nBlocks = static_cast<int32_t>((n + GEMM_BN - 1) / GEMM_BN);
+    g->kBlocks = static_cast<int32_t>((k + GEMM_BK - 1) / GEMM_BK);
+}
+
+} // namespace
+
+extern "C" {
+
+int TileXRMatmul(const void *a, const void *b, void *c, int64_t m, int64_t n, int64_t k, TileXRDataType dtype,
+                 int32_t *status, TileXRStream stream)
+{
+    int ret = CheckShape(a, b, c, m, n, k, dtype);
+    if (ret != TILEXR_SUCCESS) return ret;
+    const bool bf16 = dtype == TILEXR_DATA_TYPE_BFP16;
+    GemmArgs g;
+    std::memset(&g, 0, sizeof(g));
+    ret = MakeMap(&g.tmapA, a, m, k, GEMM_BM, bf16);
+    if (ret != TILEXR_SUCCESS) return ret;
+    ret = MakeMap(&g.tmapB, b, n, k, GEMM_BN, bf16);
+    if (ret != TILEXR_SUCCESS) return ret;
+    g.tmapALocal = g.tmapA;
+    g.c = static_cast<uint8_t *>(c);
+    g.status = status;
+    g.mode = GEMM_PLAIN;
+    g.isBf16 = bf16 ? 1u : 0u;
+    FillTiling(&g, m, n, k);
+    int sms = 0;
+    ret = SmCount(&sms);
+    if (ret != TILEXR_SUCCESS) return ret;
+    const int tiles = g.mBlocks * g.nBlocks;
+    const unsigned grid = static_cast<unsigned>(std::max(1, std::min<int>(tiles, static_cast<int>(EnvLong("TILEXR_GEMM_CTAS", sms)))));
+    static std::once_flag once;
+    std::call_once(once, [] {
+        cudaFuncSetAttribute(GemmKernelSingle(), cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(GEMM_SMEM_BYTES));
+        cudaFuncSetAttribute(GemmKernelEmulated(), cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(GEMM_SMEM_BYTES));
+    });
+    void *params[] = {&g};
+    const cudaError_t e = cudaLaunchKernel(GemmKernelSingle(), dim3(grid), dim3(GEMM_THREADS), params, GEMM_SMEM_BYTES,
+                                           static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) {
+        TILEXR_LOG(ERROR) << "matmul launch failed: " << cudaGetErrorString(e);
+        cudaGetLastError();
+        return TILEXR_ERROR_RUNTIME;
+    }
+    NoteLaunch();
+    return TILEXR_SUCCESS;
+}
+
+static int FusedCommon(TileXRCommPtr comm, TileXRCommArgs **hostArgs, GM_ADDR *devArgs)
+{
+    if (comm == nullptr) return TILEXR_ERROR_NOT_INITIALIZED;
+    int ret = TileXRGetCommArgsHost(comm, hostArgs);
+    if (ret != TILEXR_SUCCESS) return ret;
+    ret = TileXRGetCommArgsDev(comm, devArgs);
+    if (ret != TILEXR_SUCCESS) return ret;
+    if ((*hostArgs)->extraFlag & TILEXR_FLAG_HOST_MEMORY) return TILEXR_ERROR_NOT_SUPPORT;
+    return TILEXR_SUCCESS;
+}
+
+static int FusedGrid(TileXRCommPtr comm, const TileXRCommArgs *hostArgs, unsigned *grid)
+{
+    const int ranksPerDevice = (hostArgs->extraFlag & TILEXR_FLAG_EMULATED) ? hostArgs->rankSize : 1;
+    unsigned maxGrid = 0;
+    int ret = MaxCooperativeGrid(comm, GemmEntry(), GEMM_THREADS, GEMM_SMEM_BYTES, ranksPerDevice, &maxGrid);
+    if (ret != TILEXR_SUCCESS) return ret;
+    if (maxGrid < 2) {
+        TILEXR_LOG(ERROR) << "fused GEMM needs at least two co-resident CTAs per rank";
+        return TILEXR_ERROR_NOT_SUPPORT;
+    }
+    *grid = static_cast<unsigned>(std::min<long>(maxGrid, EnvLong("TILEXR_GEMM_CTAS", maxGrid)));
+    return TILEXR_SUCCESS;
+}
+
+int TileXRAllGatherMatmul(const void *aShard, void *aStaging, const void *b, void *c, int64_t shardRows, int64_t n, int64_t k,
+                          TileXRDataType dtype, TileXRCommPtr comm, TileXRStream stream)
+{
+    TileXRCommArgs *hostArgs = nullptr;
+    GM_ADDR devArgs = nullptr;
+    int ret = FusedCommon(comm, &hostArgs, &devArgs);
+    if (ret != TILEXR_SUCCESS) return ret;
+    const int R = hostArgs->rankSize;
+    const int64_t m = shardRows * R;
+    ret = CheckShape(aShard, b, c, m, n, k, dtype);
+    if (ret != TILEXR_SUCCESS) return ret;
+    if (aStaging == nullptr || shardRows % GEMM_BM != 0) {
+        TILEXR_LOG(ERROR) << "all-gather matmul: shardRows must be a multiple of " << GEMM_BM << " and a staging buffer is required";
+        return TILEXR_ERROR_PARA_CHECK_FAIL;
+    }
+    TileXRUDMAMemHandle handle = 0;
+    uint64_t offset = 0;
+    if (TileXRFindRegistration(comm, aStaging, static_cast<size_t>(m) * k * 2, &handle, &offset) != TILEXR_SUCCESS) {
+        TILEXR_LOG(ERROR) << "all-gather matmul: the staging buffer must be registered on every rank (TileXRSymmAlloc)";
+        return TILEXR_ERROR_PARA_CHECK_FAIL;
+    }
+    const bool bf16 = dtype == TILEXR_DATA_TYPE_BFP16;
+    GemmArgs g;
+    std::memset(&g, 0, sizeof(g));
+    ret = MakeMap(&g.tmapA, aStaging, m, k, GEMM_BM, bf16);
+    if (ret != TILEXR_SUCCESS) return ret;
+    ret = MakeMap(&g.tmapALocal, aShard, shardRows, k, GEMM_BM, bf16);
+    if (ret != TILEXR_SUCCESS) return ret;
+    ret = MakeMap(&g.tmapB, b, n, k, GEMM_BN, bf16);
+    if (ret != TILEXR_SUCCESS) return ret;
+    g.c = static_cast<uint8_t *>(c);
+    g.aLocal = static_cast<const uint8_t *>(aShard);
+    g.comm = reinterpret_cast<CommArgs *>(devArgs);
+    g.mode = GEMM_ALL_GATHER;
+    g.isBf16 = bf16 ? 1u : 0u;
+    FillTiling(&g, m, n, k);
+    g.shardRows = static_cast<int32_t>(shardRows);
+    g.blocksPerShard = static_cast<int32_t>(shardRows / GEMM_BM);
+    g.kChunks = std::max(1, std::min<int>(GEMM_MAX_K_CHUNKS, std::min<int>(g.kBlocks, (TILEXR_FLAGS_PER_PAIR - 1) / g.blocksPerShard)));
+    g.kBlocksPerChunk = (g.kBlocks + g.kChunks - 1) / g.kChunks;
+    g.kChunks = (g.kBlocks + g.kBlocksPerChunk - 1) / g.kBlocksPerChunk;
+    if (g.blocksPerShard * g.kChunks >= TILEXR_FLAGS_PER_PAIR) {
+        TILEXR_LOG(ERROR) << "all-gather matmul: " << shardRows << " rows per rank exceed the per-pair flag space";
+        return TILEXR_ERROR_NOT_SUPPORT;
+    }
+    g.stageHandle = handle;
+    g.stageOffset = offset;
+    unsigned grid = 0;
+    ret = FusedGrid(comm, hostArgs, &grid);
+    if (ret != TILEXR_SUCCESS) return ret;
+    g.commBlocks = R > 1 ? static_cast<uint32_t>(std::max<long>(1, std::min<long>(grid / 2, EnvLong("TILEXR_AG_GEMM_COMM_CTAS", std::max(2u, grid / 10))))) : 0;
+    int64_t magic = 0;
+    ret = TileXRCommNextMagic(comm, &magic);
+    if (ret != TILEXR_SUCCESS) return ret;
+    g.magic = magic;
+    LaunchConfig cfg{grid, GEMM_THREADS, GEMM_SMEM_BYTES, true};
+    return LaunchKernel(comm, GemmEntry(), &g, cfg, stream);
+}
+
+int TileXRMatmulReduceScatter(const void *a, const void *b, void *partialStaging, void *out, int64_t shardRows, int64_t n,
+                              int64_t k, TileXRDataType dtype, TileXRCommPtr comm, TileXRStream stream)
+{
+    TileXRCommArgs *hostArgs = nullptr;
+    GM_ADDR devArgs = nullptr;
+    int ret = FusedCommon(comm, &hostArgs, &devArgs);
+    if (ret != TILEXR_SUCCESS) return ret;
+    const int R = hostArgs->rankSize;
+    const int64_t m = shardRows * R;
+    ret = CheckShape(a, b, out, m, n, k, dtype);
+    if (ret != TILEXR_SUCCESS) return ret;
+    if (partialStaging == nullptr || shardRows % GEMM_BM != 0) {
+        TILEXR_LOG(ERROR) << "matmul reduce-scatter: shardRows must be a multiple of " << GEMM_BM << " and a staging buffer is required";
+        return TILEXR_ERROR_PARA_CHECK_FAIL;
+    }
+    TileXRUDMAMemHandle handle = 0;
+    uint64_t offset = 0;
+    if (TileXRFindRegistration(comm, partialStaging, static_cast<size_t>(m) * n * 2, &handle, &offset) != TILEXR_SUCCESS) {
+        TILEXR_LOG(ERROR) << "matmul reduce-scatter: the staging buffer must be registered on every rank (TileXRSymmAlloc)";
+        return TILEXR_ERROR_PARA_CHECK_FAIL;
+    }
+    const bool bf16 = dtype == TILEXR_DATA_TYPE_BFP16;
+    GemmArgs g;
+    std::memset(&g, 0, sizeof(g));
+    ret = MakeMap(&g.tmapA, a, m, k, GEMM_BM, bf16);
+    if (ret != TILEXR_SUCCESS) return ret;
+    g.tmapALocal = g.tmapA;
+    ret = MakeMap(&g.tmapB, b, n, k, GEMM_BN, bf16);
+    if (ret != TILEXR_SUCCESS) return ret;
+    g.c = static_cast<uint8_t *>(out);
+    g.comm = reinterpret_cast<CommArgs *>(devArgs);
+    g.mode = GEMM_REDUCE_SCATTER;
+    g.isBf16 = bf16 ? 1u : 0u;
+    FillTiling(&g, m, n, k);
+    g.shardRows = static_cast<int32_t>(shardRows);
+    g.blocksPerShard = static_cast<int32_t>(shardRows / GEMM_BM);
+    if (static_cast<int64_t>(g.blocksPerShard) * g.nBlocks >= TILEXR_FLAGS_PER_PAIR) {
+        TILEXR_LOG(ERROR) << "matmul reduce-scatter: " << g.blocksPerShard * g.nBlocks << " tiles per owner exceed the per-pair flag space";
+        return TILEXR_ERROR_NOT_SUPPORT;
+    }
+    g.stageHandle = handle;
+    g.stageOffset = offset;
+    unsigned grid = 0;
+    ret = FusedGrid(comm, hostArgs, &grid);
+    if (ret != TILEXR_SUCCESS) return ret;
+    int64_t magic = 0;
+    ret = TileXRCommNextMagic(comm, &magic);
+    if (ret != TILEXR_SUCCESS) return ret;
+    g.magic = magic;
+    LaunchConfig cfg{grid, GEMM_THREADS, GEMM_SMEM_BYTES, true};
+    return LaunchKernel(comm, GemmEntry(), &g, cfg, stream);
+}
+
+} // extern "C"

@@ -1,0 +1,58 @@
+// Argument block of the tcgen05 GEMM family (plain, all-gather -> GEMM, GEMM -> reduce-scatter).
+#ifndef TILEXR_GEMM_KERNELS_CUH
+#define TILEXR_GEMM_KERNELS_CUH
+
+#include <cuda.h>
+#include <stdint.h>
+
+#include "tilexr_comm_args.h"
+#include "tilexr_launch.h"
+
+namespace TileXR {
+
+constexpr int GEMM_BM = 128;        // rows of C per tile  = UMMA M
+constexpr int GEMM_BN = 256;        // columns of C per tile = UMMA N
+constexpr int GEMM_BK = 64;         // K per pipeline stage = one 128-byte swizzle row of bf16
+constexpr int GEMM_UMMA_K = 16;     // K of one tcgen05.mma for 16-bit inputs
+constexpr int GEMM_STAGES = 4;
+constexpr unsigned GEMM_THREADS = 192;   // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-5: epilogue
+constexpr uint32_t GEMM_STAGE_A_BYTES = GEMM_BM * GEMM_BK * 2;
+constexpr uint32_t GEMM_STAGE_B_BYTES = GEMM_BN * GEMM_BK * 2;
+constexpr uint32_t GEMM_STAGE_BYTES = GEMM_STAGE_A_BYTES + GEMM_STAGE_B_BYTES;
+constexpr size_t GEMM_SMEM_BYTES = 1024 /* alignment slack */ + GEMM_STAGES * GEMM_STAGE_BYTES + 256 /* barriers */;
+constexpr int GEMM_MAX_K_CHUNKS = 4;     // all-gather flags per 128-row block
+
+enum GemmMode : int32_t {
+    GEMM_PLAIN = 0,
+    GEMM_ALL_GATHER = 1,      // A is gathered: local shard + staging filled by peers
+    GEMM_REDUCE_SCATTER = 2,  // C is reduce-scattered: partial tiles pushed to the row owner
+};
+
+struct GemmArgs {
+    CUtensorMap tmapA;        // A [M, K] row-major (all-gather: the staging buffer [R * shardRows, K])
+    CUtensorMap tmapALocal;   // all-gather: this rank's shard [shardRows, K]
+    CUtensorMap tmapB;        // B [N, K] row-major (the weight; C = A x B^T)
+    uint8_t *c;               // plain / all-gather: C [M, N]; reduce-scatter: out [shardRows, N]
+    const uint8_t *aLocal;    // all-gather: shard to push to the peers
+    CommArgs *comm;
+    int32_t *status;          // device int, set non-zero when a pipeline wait gave up
+    int64_t magic;
+    int32_t mode;
+    int32_t M, N, K;          // M = rows of the whole product (R * shardRows in the fused modes)
+    int32_t mBlocks, nBlocks, kBlocks;
+    int32_t shardRows;        // rows per rank in the fused modes
+    int32_t blocksPerShard;   // shardRows / GEMM_BM
+    int32_t kChunks;          // all-gather: flags per row block
+    int32_t kBlocksPerChunk;
+    uint32_t commBlocks;      // all-gather: leading CTAs that only push
+    uint32_t stageHandle;     // registry handle of the staging buffer (A staging or partial-C staging)
+    uint64_t stageOffset;
+    uint32_t isBf16;
+};
+
+const void *GemmKernelSingle();
+const void *GemmKernelEmulated();
+
+} // namespace TileXR
+
+#endif

@@ -34,6 +34,26 @@ enum TileXRAllReduceAlgo { TILEXR_AR_AUTO = 0, TILEXR_AR_ONE_SHOT = 1, TILEXR_AR
 int TileXRAllReduceRmsNorm(const void *x, void *residualInOut, const void *gamma, float eps, int64_t rows, int64_t h,
                            TXR_DT dtype, void *yOut, int algo, TileXRCommPtr comm, TileXRStream stream);
 
+// C[M,N] = A[M,K] x B[N,K]^T on tcgen05 tensor cores; fp16 or bf16, K and N multiples of 8,
+// all pointers 16-byte aligned.  `status` (device int32, may be null) is set non-zero if a
+// pipeline wait inside the kernel gave up.
+int TileXRMatmul(const void *a, const void *b, void *c, int64_t m, int64_t n, int64_t k, TXR_DT dtype, int32_t *status,
+                 TileXRStream stream);
+
+// C[R*shardRows, N] = all_gather(aShard)[R*shardRows, K] x B[N,K]^T.  `aStaging` is a registered
+// buffer of R*shardRows*K elements at the same offset on every rank (TileXRSymmAlloc): the
+// kernel pushes aShard into every peer's staging buffer and multiplies as rows arrive.  Row
+// blocks of rank r's shard occupy rows [r*shardRows, (r+1)*shardRows) of C and of the staging
+// buffer.  shardRows must be a multiple of 128.
+int TileXRAllGatherMatmul(const void *aShard, void *aStaging, const void *b, void *c, int64_t shardRows, int64_t n, int64_t k,
+                          TXR_DT dtype, TileXRCommPtr comm, TileXRStream stream);
+
+// out[shardRows, N] = rows [rank*shardRows, ...) of sum over ranks of A_r[R*shardRows, K_r] x B_r[N, K_r]^T.
+// `partialStaging` is a registered buffer of R*shardRows*N elements at the same offset on every
+// rank; partial tiles travel in the 16-bit output type and are summed in rank order in fp32.
+int TileXRMatmulReduceScatter(const void *a, const void *b, void *partialStaging, void *out, int64_t shardRows, int64_t n,
+                              int64_t k, TXR_DT dtype, TileXRCommPtr comm, TileXRStream stream);
+
 // Which algorithm TILEXR_AR_AUTO picks for a message of `bytes` on `rankSize` ranks.
 int TileXRAllReduceRmsNormChoose(uint64_t bytes, int rankSize);
 

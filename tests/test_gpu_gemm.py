@@ -1,0 +1,76 @@
+"""tcgen05 GEMM and its all-gather / reduce-scatter fusions against an fp32 PyTorch matmul."""
+import pytest
+import torch
+
+from conftest import require_cuda
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def txr():
+    require_cuda()
+    import tilexr_b200
+
+    return tilexr_b200
+
+
+def _close(got, want, k):
+    got, want = got.float().cpu(), want.float().cpu()
+    tol = 2e-2 * max(1.0, (k ** 0.5) / 8)
+    assert torch.allclose(got, want, rtol=2e-2, atol=tol), (got - want).abs().max()
+    assert (got - want).abs().mean() < 0.02 * want.abs().mean() + 1e-3
+
+
+@pytest.mark.parametrize("m,n,k,dtype", [
+    (128, 256, 64, torch.bfloat16),
+    (512, 512, 256, torch.bfloat16),
+    (300, 264, 200, torch.bfloat16),        # ragged in every dimension
+    (2048, 2048, 1024, torch.float16),
+    (1024, 7168, 2048, torch.bfloat16),     # more tiles than SMs: both accumulator buffers, ring wrap
+])
+def test_matmul(txr, m, n, k, dtype):
+    g = torch.Generator().manual_seed(m + n + k)
+    a = (torch.randn(m, k, generator=g) * 0.5).to(dtype).cuda()
+    b = (torch.randn(n, k, generator=g) * 0.5).to(dtype).cuda()
+    for _ in range(2):
+        c = txr.gemm.matmul(a, b)
+    torch.cuda.synchronize()
+    _close(c, a.float() @ b.float().t(), k)
+
+
+@pytest.mark.parametrize("ranks,shard_rows,n,k", [(2, 128, 256, 256), (2, 256, 512, 1024), (4, 128, 768, 512)])
+def test_all_gather_matmul(txr, ranks, shard_rows, n, k):
+    world = txr.init_emulated_world(ranks, device=0, buffer_mb=16)
+    g = torch.Generator().manual_seed(7)
+    shards = [(torch.randn(shard_rows, k, generator=g) * 0.5).to(torch.bfloat16).cuda() for _ in range(ranks)]
+    bs = [(torch.randn(n, k, generator=g) * 0.5).to(torch.bfloat16).cuda() for _ in range(ranks)]
+    staging = world.symm_empty((ranks * shard_rows, k), torch.bfloat16)
+    full = torch.cat(shards).float()
+    for _ in range(3):
+        outs = world.run(lambda c, r: txr.gemm.all_gather_matmul(c, shards[r], bs[r], staging[r]))
+        world.check()
+    for r in range(ranks):
+        _close(outs[r], full @ bs[r].float().t(), k)
+    world.destroy()
+
+
+@pytest.mark.parametrize("ranks,shard_rows,n,k", [(2, 128, 256, 128), (2, 256, 512, 512), (4, 128, 512, 256)])
+def test_matmul_reduce_scatter(txr, ranks, shard_rows, n, k):
+    world = txr.init_emulated_world(ranks, device=0, buffer_mb=16)
+    g = torch.Generator().manual_seed(9)
+    m = ranks * shard_rows
+    a = [(torch.randn(m, k, generator=g) * 0.5).to(torch.bfloat16).cuda() for _ in range(ranks)]
+    b = [(torch.randn(n, k, generator=g) * 0.5).to(torch.bfloat16).cuda() for _ in range(ranks)]
+    staging = world.symm_empty((m, n), torch.bfloat16)
+    # partial products travel as bf16 and are summed in rank order in fp32
+    partial = [(a[r].float() @ b[r].float().t()).to(torch.bfloat16).float() for r in range(ranks)]
+    want = partial[0]
+    for p in partial[1:]:
+        want = want + p
+    for _ in range(3):
+        outs = world.run(lambda c, r: txr.gemm.matmul_reduce_scatter(c, a[r], b[r], staging[r]))
+        world.check()
+    for r in range(ranks):
+        _close(outs[r], want[r * shard_rows:(r + 1) * shard_rows], k * ranks)
+    world.destroy()

@@ -1,4 +1,4 @@
 """Tensor-level operators backed by the native kernels."""
-from . import collectives, ep, quant
+from . import collectives, ep, gemm, quant
 
-__all__ = ["collectives", "ep", "quant"]
+__all__ = ["collectives", "ep", "gemm", "quant"]
