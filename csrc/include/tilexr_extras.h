@@ -4,5 +4,6 @@
 
 #include "tilexr_fused.h"
 #include "tilexr_hostsim.h"
+#include "tilexr_moonep.h"
 
 #endif

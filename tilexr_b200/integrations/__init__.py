@@ -1,0 +1,1 @@
+"""Framework integrations: MoonEP-compatible buffer, vLLM communicator patch."""

@@ -1,0 +1,278 @@
+"""MoonEP-compatible torch facade over the native five-stage kernels.
+
+``Buffer`` keeps the call signatures of the reference's compatibility layer
+(integrations/moonep_torch/tilexr_moonep/compat.py:135-501) so that training code written
+against it runs unchanged; ``TileXRMoonEPBuffer`` is the native facade with real remote weight
+prefetch and owner-pull gradient reduction (torch_api.py:591-1808).  Differences: there is no
+host synchronisation between planning and dispatch (every later stage checks ``plan.status`` on
+the device), and the dispatch outputs are persistent symmetric tensors that peers write
+directly, so ``dispatch`` returns views that stay valid until the next ``dispatch``.
+"""
+from __future__ import annotations
+
+import dataclasses
+from typing import Callable, Optional
+
+import torch
+
+from .. import _C
+from ..ops import collectives
+
+
+@dataclasses.dataclass
+class MoonEPCommPlan:
+    dst: torch.Tensor
+    experts_to_copy: torch.Tensor
+    zero_fill_ranges: torch.Tensor
+    remote_stats: torch.Tensor
+    N: int
+    R: int
+    E: int
+    B: int
+    NvS: int
+    K: int
+    dup_groups: Optional[torch.Tensor] = None
+    dup_loffs: Optional[torch.Tensor] = None
+    dup_counts: Optional[torch.Tensor] = None
+    status: Optional[torch.Tensor] = None
+    dst_local: Optional[torch.Tensor] = None
+    cu_seqlens: Optional[torch.Tensor] = None
+
+    def clone(self) -> "MoonEPCommPlan":
+        def c(t):
+            return None if t is None else t.clone()
+
+        return MoonEPCommPlan(c(self.dst), c(self.experts_to_copy), c(self.zero_fill_ranges), c(self.remote_stats), self.N,
+                              self.R, self.E, self.B, self.NvS, self.K, c(self.dup_groups), c(self.dup_loffs),
+                              c(self.dup_counts), c(self.status), c(self.dst_local), c(self.cu_seqlens))
+
+    def as_dict(self) -> dict:
+        return {"dst": self.dst, "experts_to_copy": self.experts_to_copy, "zero_fill_ranges": self.zero_fill_ranges,
+                "remote_stats": self.remote_stats, "dup_counts": self.dup_counts, "status": self.status,
+                "dst_local": self.dst_local, "cu_seqlens": self.cu_seqlens, "N": self.N, "R": self.R, "E": self.E,
+                "B": self.B, "NvS": self.NvS, "K": self.K}
+
+    @staticmethod
+    def from_dict(d: dict) -> "MoonEPCommPlan":
+        return MoonEPCommPlan(d["dst"], d["experts_to_copy"], d["zero_fill_ranges"], d["remote_stats"], d["N"], d["R"], d["E"],
+                              d["B"], d["NvS"], d["K"], None, None, d["dup_counts"], d["status"], d["dst_local"], d["cu_seqlens"])
+
+
+@dataclasses.dataclass
+class ProjectionBuffers:
+    """gate / up / down as ``[E/R + B, ...]`` tensors in symmetric memory: rows ``[0, E/R)`` are the
+    rank's own experts, rows ``E/R + b`` the prefetch slots."""
+    gate: torch.Tensor
+    up: torch.Tensor
+    down: torch.Tensor
+
+
+class TileXRMoonEPBuffer:
+    """Native facade: planning, dispatch, prefetch_weight, combine, reduce_grad, forward, backward."""
+
+    def __init__(self, comm, S: int, H: int, K: int, E: int, token_padding: int = 128, B: Optional[int] = None,
+                 dtype=torch.bfloat16):
+        self.comm = comm
+        self.S, self.H, self.K, self.E = S, H, K, E
+        self.R = comm.world_size
+        if E % self.R != 0:
+            raise ValueError("E must divide by the number of ranks")
+        self.B = E // self.R if B is None else B
+        self.token_padding = token_padding
+        self.NvS = S * K + (token_padding - 1) * 2 * (E // self.R)
+        self.dtype = dtype
+        self._poisoned = False
+        # persistent receive tensors: peers write into them directly
+        self.hidden_nvsh = comm.symm_empty([self.NvS, H], dtype)
+        self.weights_nvs = comm.symm_empty([self.NvS], torch.float32)
+        self._grad_nvsh = None
+
+    # -- stages ------------------------------------------------------------------------------------
+    def planning(self, topk_experts_sk: torch.Tensor, tokens_per_expert: Optional[torch.Tensor] = None) -> MoonEPCommPlan:
+        self._check_alive()
+        topk = topk_experts_sk.to(torch.int32).contiguous()
+        return MoonEPCommPlan.from_dict(_C.moonep_planning(self.comm, topk, self.E, self.B, self.token_padding))
+
+    def dispatch(self, hidden_sh: torch.Tensor, route_weights_sk: Optional[torch.Tensor], plan: MoonEPCommPlan,
+                 out: Optional[torch.Tensor] = None):
+        self._check_alive()
+        hidden_out = self.hidden_nvsh if out is None else out
+        w_out = self.weights_nvs if route_weights_sk is not None else None
+        _C.moonep_dispatch(self.comm, plan.as_dict(), hidden_sh.contiguous(),
+                           None if route_weights_sk is None else route_weights_sk.float().contiguous(), hidden_out, w_out)
+        return hidden_out, w_out
+
+    def register_projection_buffers(self, rows_gate, rows_up, rows_down, dtype=torch.bfloat16) -> ProjectionBuffers:
+        L = self.E // self.R
+        mk = lambda shape: self.comm.symm_empty([L + self.B] + list(shape), dtype)
+        return ProjectionBuffers(mk(rows_gate), mk(rows_up), mk(rows_down))
+
+    def prefetch_weight(self, plan: MoonEPCommPlan, projections: ProjectionBuffers) -> None:
+        self._check_alive()
+        _C.moonep_prefetch_weight(self.comm, plan.as_dict(), projections.gate, projections.up, projections.down)
+
+    def combine(self, plan: MoonEPCommPlan, hidden_nvsh: torch.Tensor, route_weights_nvs: Optional[torch.Tensor] = None):
+        self._check_alive()
+        hidden_sh = torch.empty(self.S, hidden_nvsh.shape[1], dtype=hidden_nvsh.dtype, device=hidden_nvsh.device)
+        w_sk = None
+        if route_weights_nvs is not None:
+            w_sk = torch.empty(self.S, self.K, dtype=torch.float32, device=hidden_nvsh.device)
+        _C.moonep_combine(self.comm, plan.as_dict(), hidden_nvsh.contiguous(), route_weights_nvs, hidden_sh, w_sk)
+        return hidden_sh, w_sk
+
+    def prepare_reduce_grad(self, projections: ProjectionBuffers) -> ProjectionBuffers:
+        """Gradient tensors must be fp32 and symmetric; returns zero-filled ones of the right shape."""
+        L = self.E // self.R
+        mk = lambda t: self.comm.symm_empty([L + self.B] + list(t.shape[1:]), torch.float32).zero_()
+        return ProjectionBuffers(mk(projections.gate), mk(projections.up), mk(projections.down))
+
+    def reduce_grad(self, plan: MoonEPCommPlan, grads: ProjectionBuffers) -> None:
+        self._check_alive()
+        _C.moonep_reduce_grad(self.comm, plan.as_dict(), grads.gate, grads.up, grads.down)
+
+    # -- composed flows -------------------------------------------------------------------------------
+    def forward(self, hidden, route_weights, topk_experts, tokens_per_expert, projections: Optional[ProjectionBuffers],
+                expert_forward: Callable, apply_route_weights: bool = True):
+        plan = self.planning(topk_experts, tokens_per_expert)
+        rows, w = self.dispatch(hidden, route_weights, plan)
+        if projections is not None:
+            self.prefetch_weight(plan, projections)
+        out = expert_forward(rows, plan.cu_seqlens, projections)
+        if apply_route_weights and w is not None:
+            out = (out.float() * w.unsqueeze(1)).to(out.dtype)
+        y, _ = self.combine(plan, out)
+        return y, plan
+
+    def backward(self, grad_output, plan: MoonEPCommPlan, expert_backward: Callable, grads: Optional[ProjectionBuffers] = None):
+        if self._grad_nvsh is None or self._grad_nvsh.dtype != grad_output.dtype:
+            self._grad_nvsh = self.comm.symm_empty([self.NvS, self.H], grad_output.dtype)
+        rows, _ = self.dispatch(grad_output, None, plan, out=self._grad_nvsh)
+        grad_rows = expert_backward(rows, plan.cu_seqlens)
+        gx, _ = self.combine(plan, grad_rows)
+        if grads is not None:
+            self.reduce_grad(plan, grads)
+        return gx
+
+    # -- housekeeping ------------------------------------------------------------------------------------
+    def check_pending_status(self, plan: Optional[MoonEPCommPlan] = None) -> None:
+        """Call after a stream synchronisation: raises if a stage gave up on the device."""
+        status = self.comm.device_status()
+        plan_status = int(plan.status.item()) if plan is not None and plan.status is not None else 0
+        if status != 0 or plan_status != 0:
+            self._poisoned = True
+            self.comm.print_dfx()
+            raise RuntimeError(f"MoonEP stage failed: device status {status}, plan status {plan_status}")
+
+    def synchronize(self) -> None:
+        torch.cuda.synchronize()
+        self.check_pending_status()
+
+    quiesce = synchronize
+
+    def _check_alive(self):
+        if self._poisoned:
+            raise RuntimeError("this MoonEP buffer saw a failed stage; create a new one")
+
+    def close(self) -> None:
+        self._poisoned = True
+
+
+class Buffer:
+    """Drop-in for the MoonEP ``Buffer``: same constructor and method signatures."""
+
+    def __init__(self, S, H, K, E, num_ep_ranks, num_sms=None, token_padding=128, B=None, group=None,
+                 comm_stream_priority=-1, enable_pdl=True, explicitly_destroy=False, comm=None, dtype=torch.bfloat16):
+        if comm is None:
+            import torch.distributed as dist
+
+            from ..parallel.comm import init_from_torch_distributed
+
+            if not dist.is_initialized():
+                raise RuntimeError("Buffer needs an initialised torch.distributed (or pass comm=)")
+            pg = group if group is not None else dist.group.WORLD
+            if dist.get_world_size(pg) != num_ep_ranks:
+                raise ValueError("group size must equal num_ep_ranks")
+            need = max(S * K * H * 2 + S * K * 4, 64 << 20)
+            comm = init_from_torch_distributed(pg, buffer_mb=int(2 * need / (1 << 20)) + 16)
+        if comm.world_size != num_ep_ranks:
+            raise ValueError("communicator size must equal num_ep_ranks")
+        self.num_sms = 32 if num_sms is None else num_sms
+        self.explicitly_destroy = explicitly_destroy
+        self.native = TileXRMoonEPBuffer(comm, S, H, K, E, token_padding, B, dtype)
+        self.S, self.H, self.K, self.E, self.R = S, H, K, E, num_ep_ranks
+        self.B = self.native.B
+
+    def dispatch(self, hidden_sh, route_weights_sk=None, topk_experts_sk=None, tokens_per_expert=None, plan=None,
+                 async_finish=False, *, inter_rank_sync=True, zero_copy=False):
+        if not inter_rank_sync or zero_copy:
+            raise NotImplementedError("inter_rank_sync=False and zero_copy=True are not supported")
+        if plan is None:
+            if topk_experts_sk is None:
+                raise ValueError("a fresh dispatch needs topk_experts_sk")
+            plan = self.native.planning(topk_experts_sk, tokens_per_expert)
+        rows, w = self.native.dispatch(hidden_sh, route_weights_sk, plan)
+        out = (rows, w, plan.cu_seqlens, plan)
+        if async_finish:
+            ev = torch.cuda.Event()
+            ev.record()
+            out = out + (ev,)
+        return out
+
+    def prefetch_weight(self, plan, async_finish=False, *, full_gate_weight, full_up_weight, full_down_weight):
+        """Every rank holds all E experts in rows [0, E); rows [E, E+B) receive this rank's
+        borrowed experts (a local copy, as in the reference's compatibility layer)."""
+        idx = plan.experts_to_copy[self.native.comm.rank].long()
+        valid = idx >= 0
+        src = idx.clamp(min=0)
+        for t in (full_gate_weight, full_up_weight, full_down_weight):
+            rows = t.index_select(0, src)
+            rows[~valid] = 0
+            t[self.E:self.E + self.B].copy_(rows)
+        if async_finish:
+            ev = torch.cuda.Event()
+            ev.record()
+            return ev
+        return None
+
+    def combine(self, plan, hidden_nvsh, route_weights_nvs=None, async_finish=False, inter_rank_sync=True, *, zero_copy=False):
+        if not inter_rank_sync or zero_copy:
+            raise NotImplementedError("inter_rank_sync=False and zero_copy=True are not supported")
+        y, w = self.native.combine(plan, hidden_nvsh, route_weights_nvs)
+        ev = None
+        if async_finish:
+            ev = torch.cuda.Event()
+            ev.record()
+        return y, w, ev
+
+    def reduce_grad(self, plan, async_finish=False, *, full_gate_grad, full_up_grad, full_down_grad, gate_reduce_buffer,
+                    up_reduce_buffer, down_reduce_buffer):
+        """Slot rows [E, E+B) of every rank are gathered into the ``[R, B, ...]`` reduce buffers and
+        each owner adds the rows of its experts in ascending (rank, slot) order."""
+        comm = self.native.comm
+        L = self.E // self.R
+        etc = plan.experts_to_copy
+        for grad, buf in ((full_gate_grad, gate_reduce_buffer), (full_up_grad, up_reduce_buffer),
+                          (full_down_grad, down_reduce_buffer)):
+            collectives.all_gather(comm, grad[self.E:self.E + self.B].contiguous(), out=buf)
+            owner_rows = (etc >= comm.rank * L) & (etc < (comm.rank + 1) * L)
+            rr, bb = owner_rows.nonzero(as_tuple=True)
+            for r, b in zip(rr.tolist(), bb.tolist()):
+                if r == comm.rank:
+                    continue
+                grad[int(etc[r, b])] += buf[r, b]
+            grad[self.E:self.E + self.B].zero_()
+        if async_finish:
+            ev = torch.cuda.Event()
+            ev.record()
+            return ev
+        return None
+
+    def destroy(self):
+        self.native.close()
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.destroy()
+        return False
