@@ -5,5 +5,6 @@
 #include "tilexr_fused.h"
 #include "tilexr_hostsim.h"
 #include "tilexr_moonep.h"
+#include "../checker/checker.h"
 
 #endif

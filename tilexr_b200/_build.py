@@ -157,9 +157,27 @@ def build_binding(verbose: bool = True) -> Path:
     return out
 
 
+def build_checker_cli(verbose: bool = True) -> Path:
+    """The stand-alone protocol checker (no CUDA, no torch)."""
+    (PKG / "bin").mkdir(parents=True, exist_ok=True)
+    out = PKG / "bin" / "tilexr_checker"
+    srcs = [CSRC / "checker" / "checker.cpp", CSRC / "checker" / "cli" / "checker_cli.cpp"]
+    newest = max([p.stat().st_mtime for p in srcs] + [(CSRC / "checker" / "checker.h").stat().st_mtime])
+    if out.exists() and out.stat().st_mtime >= newest:
+        return out
+    cmd = ["g++", "-std=c++17", "-O2", "-Wall", f"-I{CSRC / 'checker'}", *map(str, srcs), "-o", str(out)]
+    if verbose:
+        print("  cc+ld", out.relative_to(ROOT), flush=True)
+    proc = subprocess.run(cmd, capture_output=True, text=True)
+    if proc.returncode != 0:
+        raise RuntimeError(f"checker build failed: {proc.stdout}\n{proc.stderr}")
+    return out
+
+
 def build_all(verbose: bool = True):
     lib = build_library(verbose)
     ext = build_binding(verbose)
+    build_checker_cli(verbose)
     return lib, ext
 
 
