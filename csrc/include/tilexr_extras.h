@@ -5,6 +5,7 @@
 #include "tilexr_fused.h"
 #include "tilexr_hostsim.h"
 #include "tilexr_moonep.h"
+#include "tilexr_probes.h"
 #include "../checker/checker.h"
 
 #endif
