@@ -1,0 +1,70 @@
+"""Architectural invariants checked on the source text (the reference keeps the same kind of
+guards: tests/comm/unit/test_tilexr_source_guards.cpp, tests/collectives/unit/
+test_tilexr_collectives_kernel_ownership.cpp)."""
+import re
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent.parent
+CSRC = ROOT / "csrc"
+
+
+def _sources(*suffixes):
+    return [p for p in CSRC.rglob("*") if p.suffix in suffixes]
+
+
+def test_no_cluster_multicast_loads_anywhere():
+    # remote memory must never be read by a TMA load with cluster multicast; the tree has none at all
+    for p in _sources(".cu", ".cuh", ".h", ".cpp", ".inc"):
+        text = p.read_text()
+        assert "multicast::cluster" not in text.replace("tcgen05.commit", ""), p
+        assert "MemcpyBatchAsync" not in text, p
+
+
+def test_operator_libraries_do_not_reach_into_the_core_runtime():
+    # collectives / ep / gemm / moonep consume the C API and the launch service only
+    for sub in ("collectives", "ep", "gemm", "moonep", "hostsim"):
+        for p in (CSRC / sub).glob("*"):
+            if p.suffix in (".cu", ".cpp", ".cuh", ".h"):
+                text = p.read_text()
+                assert '#include "comm.h"' not in text and "sock_exchange.h" not in text, p
+
+
+def test_every_device_spin_is_bounded():
+    # a `while`/`for(;;)` that polls memory must sit next to a deadline or poll-count check
+    pattern = re.compile(r"(for \(;;\)|while \([^)]*ld_(acquire|relaxed|vec16_volatile)[^)]*\))")
+    for p in _sources(".cu", ".cuh"):
+        text = p.read_text()
+        for m in pattern.finditer(text):
+            window = text[m.start(): m.start() + 900]
+            if m.group(0).startswith("for") and not re.search(r"ld_(acquire|relaxed|vec16_volatile)|MbarTryWait", window[:500]):
+                continue      # a host or integer loop, not a memory poll
+            assert ("deadline" in window or "budget" in window or "polls" in window), f"{p}: unbounded spin near offset {m.start()}"
+
+
+def test_no_trap_or_device_assert():
+    for p in _sources(".cu", ".cuh"):
+        text = p.read_text()
+        assert "__trap" not in text, p
+        assert not re.search(r"(?<!static_)assert\(", text), p
+
+
+def test_kernels_target_blackwell_features_where_claimed():
+    gemm = (CSRC / "gemm" / "gemm_tcgen05.cu").read_text()
+    for needle in ("tcgen05.mma", "tcgen05.alloc", "tcgen05.ld", "tcgen05.commit", "cp.async.bulk.tensor.2d"):
+        assert needle in gemm
+    assert "wgmma" not in gemm and "mma.sync" not in gemm
+    # the fused kernels touch peer memory in the same kernel as the tensor-core tiles
+    assert "peerBase[" in gemm and "WaitFlagGE" in gemm
+
+
+def test_public_headers_cite_the_reference():
+    for name in ("tilexr_api.h", "tilexr_collectives.h", "tilexr_ep.h", "tilexr_moonep.h", "tilexr_perf_trace.h"):
+        assert "src/" in (CSRC / "include" / name).read_text(), name
+
+
+def test_no_build_note_names_in_sources():
+    banned = ("SURVEY", "VERDICT", "ADVICE.md", "DESIGN.md", "BASELINE.md", "gpurun", "/root/")
+    for p in list(_sources(".cu", ".cuh", ".h", ".cpp", ".inc")) + list((ROOT / "tilexr_b200").rglob("*.py")):
+        text = p.read_text()
+        for b in banned:
+            assert b not in text, f"{p} mentions {b}"
