@@ -25,7 +25,6 @@ import socket
 import statistics
 import subprocess
 import sys
-import threading
 import time
 from pathlib import Path
 
@@ -50,66 +49,72 @@ def parse_args():
     p.add_argument("--experts", type=int, default=256)
     p.add_argument("--topk", type=int, default=8)
     p.add_argument("--no-e2e", action="store_true")
+    p.add_argument("--debug-steps", action="store_true", help="print every timed step's device time to stderr")
+    p.add_argument("--clock-interval-ms", type=float, default=2.0, help="NVML sampling interval")
+    p.add_argument("--stage-profile", default="", metavar="DIR",
+                   help="after the timed loop, run two more steps under the in-kernel stage profiler and write its "
+                        "reports to DIR (the stage table goes to stderr)")
     return p.parse_args()
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons through NVML (read-only) while the benchmark runs."""
+    """Reads SM clocks and clock-event reasons through NVML (read-only) during the timed regions.
+
+    The launching thread samples after it has queued all steps of a region, while the device is still working
+    through them, until the region's end event has completed.  A background sampler is not used: NVML queries
+    issued while the host was still launching delayed the launches by milliseconds and starved the GPU.
+    """
 
     REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
 
-    def __init__(self, device_index: int):
+    def __init__(self, device_index: int, interval_s: float = 0.002):
         self.device_index = device_index
-        self.samples = []          # (time, sm_mhz, reasons bitmask)
-        self.stop_flag = threading.Event()
-        self.thread = None
+        self.interval_s = interval_s
+        self.samples = []          # (sm_mhz, reasons bitmask)
         self.max_mhz = None
-        self.windows = []
+        self.nvml = None
 
     def start(self):
         try:
             import pynvml
 
             pynvml.nvmlInit()
-            self.nvml = pynvml
             self.handle = pynvml.nvmlDeviceGetHandleByIndex(self.device_index)
             self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+            self.nvml = pynvml
+            self._read()             # the first call of each query takes milliseconds: keep it out of the regions
         except Exception:
             self.nvml = None
-            return
-        self.thread = threading.Thread(target=self._loop, daemon=True)
-        self.thread.start()
 
-    def _loop(self):
+    def _read(self):
         nv = self.nvml
-        while not self.stop_flag.is_set():
-            try:
-                mhz = float(nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM))
-                reasons = int(nv.nvmlDeviceGetCurrentClocksEventReasons(self.handle))
-                self.samples.append((time.time(), mhz, reasons))
-            except Exception:
-                pass
-            time.sleep(0.002)
+        return (float(nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM)),
+                int(nv.nvmlDeviceGetCurrentClocksEventReasons(self.handle)))
 
-    def mark(self, t0: float, t1: float):
-        """A timed region; only samples inside marked regions are reported."""
-        self.windows.append((t0, t1))
+    def sample_until(self, end_event):
+        """Samples until `end_event` (recorded after the last queued step) has completed; at least once."""
+        if self.nvml is None:
+            return
+        while True:
+            done = end_event.query()
+            try:
+                if not done or not self.samples:
+                    self.samples.append(self._read())
+            except Exception:
+                return
+            if done:
+                return
+            time.sleep(self.interval_s)
 
     def stop(self):
-        self.stop_flag.set()
-        if self.thread is not None:
-            self.thread.join(timeout=2)
-        inside = [s for s in self.samples if any(a <= s[0] <= b for a, b in self.windows)]
-        if not inside:
-            inside = self.samples
-        if not inside:
+        if not self.samples:
             return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0}
         mask = 0
-        for s in inside:
-            mask |= s[2]
+        for s in self.samples:
+            mask |= s[1]
         reasons = sorted(name for bit, name in self.REASONS.items() if mask & bit)
-        return {"sm_mhz": statistics.median(s[1] for s in inside), "sm_max_mhz": self.max_mhz, "reasons": reasons,
-                "samples": len(inside)}
+        return {"sm_mhz": statistics.median(s[0] for s in self.samples), "sm_max_mhz": self.max_mhz, "reasons": reasons,
+                "samples": len(self.samples)}
 
 
 def physical_device_index(local_rank: int) -> int:
@@ -227,23 +232,35 @@ def main():
             comm.print_dfx()
             raise SystemExit("a device-side wait gave up; see the DFX line above")
 
+    # NVML is brought up before the warm-up steps so that its first, slow queries are long over
+    sampler = ClockSampler(physical_device_index(local_rank), args.clock_interval_ms / 1000.0)
+    sampler.start()
+
     # ---- device-timed loop --------------------------------------------------------------------------
     for i in range(warmup):
         step(i)
     barrier()
     check()
-    sampler = ClockSampler(physical_device_index(local_rank))
-    sampler.start()
     launches0 = txr.launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
-    wall0 = time.time()
+    marks = [torch.cuda.Event(enable_timing=True) for _ in range(steps)] if args.debug_steps else None
+    host0 = time.perf_counter()
     e0.record()
     for i in range(steps):
         y = step(i)
+        if marks is not None:
+            marks[i].record()
     e1.record()
+    host_issue_ms = (time.perf_counter() - host0) * 1e3 / steps
+    sampler.sample_until(e1)
     barrier()
-    sampler.mark(wall0, time.time())
+    if marks is not None and rank == 0:
+        prev, line = e0, []
+        for m in marks:
+            line.append(f"{prev.elapsed_time(m) * 1e3:.0f}")
+            prev = m
+        print("per-step device us: " + " ".join(line), file=sys.stderr)
     launches = txr.launch_count() - launches0
     ms_per_step = max_over_ranks(e0.elapsed_time(e1) / steps)
     check()
@@ -257,6 +274,16 @@ def main():
         parts.append([ev[j].elapsed_time(ev[j + 1]) * 1000 for j in range(3)])
     phase_us = [max_over_ranks(statistics.median(p[j] for p in parts)) for j in range(3)]
     barrier()
+
+    if args.stage_profile and args.impl == "tilexr":
+        from tilexr_b200.utils.stage_profile import format_summaries, stage_profile
+
+        with stage_profile(args.stage_profile):
+            for i in range(2):
+                step(i)
+        barrier()
+        if rank == 0:
+            print(format_summaries(args.stage_profile), file=sys.stderr)
 
     # ---- end to end: pinned host inputs in, scalar result out, every step -----------------------------
     e2e = None
@@ -278,13 +305,12 @@ def main():
             e2e_step(i)
         barrier()
         s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        wall0 = time.time()
         s0.record()
         for i in range(steps):
             e2e_step(i)
         s1.record()
+        sampler.sample_until(s1)
         barrier()
-        sampler.mark(wall0, time.time())
         e2e_ms = max_over_ranks(s0.elapsed_time(s1) / steps)
         e2e = {
             "value": T * world / (e2e_ms * 1e-3),
@@ -328,6 +354,7 @@ def main():
         },
         "clocks": clocks,
         "gpu_launches": int(launches),
+        "host_issue_ms_per_step": round(host_issue_ms, 4),
     }
     if e2e is not None:
         out["e2e"] = e2e

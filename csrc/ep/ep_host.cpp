@@ -6,6 +6,7 @@
 #include <cstring>
 
 #include "ep_kernels.cuh"
+#include "../collectives/perf_trace_session.h"
 #include "tilexr_ep.h"
 #include "tilexr_log.h"
 
@@ -40,7 +41,7 @@ bool DispatchLayout(int64_t h, int64_t numExperts, int64_t rankSize, int64_t max
     win->assistOff = off;
     off = Align(off + static_cast<uint64_t>(maxRecvRows) * 16, 256);
     win->countOff = off;
-    off = Align(off + static_cast<uint64_t>(rankSize) * numExperts * 4, 256);
+    off = Align(off + (static_cast<uint64_t>(rankSize) * numExperts + rankSize) * 4, 256);
     win->blockCountOff = off;
     off = Align(off + static_cast<uint64_t>(grid) * numExperts * 4, 256);
     win->totalBytes = off;
@@ -115,6 +116,8 @@ uint64_t TileXREpCombineWindowBytes(int64_t bs, int64_t h, int64_t topK, int64_t
     return static_cast<uint64_t>(bs) * topK * h * elemSize;
 }
 
+uint64_t TileXREpAbiStamp(void) { return TILEXR_EP_ABI_STAMP; }
+
 int TileXRMoeEpDispatchFused(const TileXREpDispatchParams *p, TileXRCommPtr comm, TileXRStream stream)
 {
     Ctx c;
@@ -152,7 +155,7 @@ int TileXRMoeEpDispatchFused(const TileXREpDispatchParams *p, TileXRCommPtr comm
 
     // grid: one block per ~8 tokens per warp-set, capped by what can be co-resident
     const int ranksPerDevice = (c.hostArgs->extraFlag & TILEXR_FLAG_EMULATED) ? c.rankSize : 1;
-    const int64_t wantBlocks = std::max<int64_t>(1, std::min<int64_t>((p->bs + 15) / 16, EnvLong("TILEXR_EP_BLOCKS", 128)));
+    const int64_t wantBlocks = std::max<int64_t>(1, std::min<int64_t>((p->bs + 15) / 16, EnvLong("TILEXR_EP_BLOCKS", 296)));
     unsigned grid = static_cast<unsigned>(wantBlocks);
     uint32_t tokensPerBlock = 0;
     size_t smem = 0;
@@ -223,10 +226,17 @@ int TileXRMoeEpDispatchFused(const TileXREpDispatchParams *p, TileXRCommPtr comm
     a.zeroCopy = zeroCopy ? 1u : 0u;
     a.outHandle = handle;
     a.outOffset = regionOffset;
+    a.routeRowsOut = p->routeRowsOut;
     int64_t magic = 0;
     ret = TileXRCommNextMagic(comm, &magic);
     if (ret != TILEXR_SUCCESS) return ret;
     a.magic = magic;
+    {
+        PerfLaunchInfo info{static_cast<uint32_t>(TILEXR_OP_EP_DISPATCH), static_cast<uint32_t>(p->dtype),
+                            static_cast<uint32_t>(c.rank), static_cast<uint32_t>(c.rankSize), grid,
+                            static_cast<uint64_t>(p->bs) * p->h * elemSize};
+        a.perfTrace = PerfTracePrepareLaunch(info, stream);
+    }
     LaunchConfig cfg{grid, EP_BLOCK_THREADS, smem, true};
     return LaunchKernel(comm, EpDispatchKernelEntry(), &a, cfg, stream);
 }
@@ -270,6 +280,7 @@ int TileXRMoeEpCombineFused(const TileXREpCombineParams *p, TileXRCommPtr comm, 
     a.rowBytes = static_cast<uint32_t>(p->h * 2);
     a.isBf16 = p->dtype == TILEXR_DATA_TYPE_BFP16 ? 1u : 0u;
     a.sendCountEntries = static_cast<uint32_t>(p->moeExpertNum / c.rankSize * c.rankSize);
+    a.routeRows = p->expertIds != nullptr ? p->routeRows : nullptr;
     int64_t magic = 0;
     ret = TileXRCommNextMagic(comm, &magic);
     if (ret != TILEXR_SUCCESS) return ret;
@@ -278,8 +289,14 @@ int TileXRMoeEpCombineFused(const TileXREpCombineParams *p, TileXRCommPtr comm, 
     unsigned maxGrid = 0;
     ret = MaxCooperativeGrid(comm, EpCombineKernelEntry(), EP_BLOCK_THREADS, 0, ranksPerDevice, &maxGrid);
     if (ret != TILEXR_SUCCESS) return ret;
-    const int64_t want = std::min<int64_t>(EnvLong("TILEXR_EP_BLOCKS", 128), std::max<int64_t>(1, (p->bs * p->topK + 15) / 16));
+    const int64_t want = std::min<int64_t>(EnvLong("TILEXR_EP_BLOCKS", 296), std::max<int64_t>(1, (p->bs * p->topK + 15) / 16));
     const unsigned grid = static_cast<unsigned>(std::max<int64_t>(1, std::min<int64_t>(want, maxGrid)));
+    {
+        PerfLaunchInfo info{static_cast<uint32_t>(TILEXR_OP_EP_COMBINE), static_cast<uint32_t>(p->dtype),
+                            static_cast<uint32_t>(c.rank), static_cast<uint32_t>(c.rankSize), grid,
+                            static_cast<uint64_t>(p->bs) * a.rowBytes};
+        a.perfTrace = PerfTracePrepareLaunch(info, stream);
+    }
     LaunchConfig cfg{grid, EP_BLOCK_THREADS, 0, true};
     return LaunchKernel(comm, EpCombineKernelEntry(), &a, cfg, stream);
 }

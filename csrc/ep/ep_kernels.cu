@@ -31,6 +31,7 @@
 #include <cstdio>
 #include <cuda_runtime_api.h>
 
+#include "device/tilexr_perf_trace.cuh"
 #include "device/tilexr_rma.cuh"
 #include "device/tilexr_sync.cuh"
 #include "ep_kernels.cuh"
@@ -103,10 +104,10 @@ __device__ __forceinline__ uint32_t Fp8x4(float a, float b, float c, float d)
 // Lane l owns experts l, l+32, ...  Selection is by score (+ optional bias), ties go to the
 // lower expert id; the gate weight is the unbiased score, optionally renormalised over the
 // selected experts and multiplied by `routedScale`.
-__device__ __forceinline__ void RouteToken(const float *logits, const float *bias, int numExperts, int topK, int scoreFunc,
-                                           int renormalize, float routedScale, int lane, int32_t *idsOut, float *weightsOut)
+template <int PER_LANE>
+__device__ __forceinline__ void RouteTokenN(const float *logits, const float *bias, int numExperts, int topK, int scoreFunc,
+                                            int renormalize, float routedScale, int lane, int32_t *idsOut, float *weightsOut)
 {
-    constexpr int PER_LANE = EP_MAX_EXPERTS / 32;
     float score[PER_LANE];
     float sel[PER_LANE];
     float mx = -INFINITY;
@@ -189,6 +190,21 @@ __device__ __forceinline__ void RouteToken(const float *logits, const float *bia
     }
 }
 
+// The per-lane score table is sized for the expert count, so that 256 experts keep 8 scores per lane in
+// registers instead of the 32 that the largest supported count needs.
+__device__ __forceinline__ void RouteToken(const float *logits, const float *bias, int numExperts, int topK, int scoreFunc,
+                                           int renormalize, float routedScale, int lane, int32_t *idsOut, float *weightsOut)
+{
+    if (numExperts <= 256) {
+        RouteTokenN<8>(logits, bias, numExperts, topK, scoreFunc, renormalize, routedScale, lane, idsOut, weightsOut);
+    } else if (numExperts <= 512) {
+        RouteTokenN<16>(logits, bias, numExperts, topK, scoreFunc, renormalize, routedScale, lane, idsOut, weightsOut);
+    } else {
+        RouteTokenN<EP_MAX_EXPERTS / 32>(logits, bias, numExperts, topK, scoreFunc, renormalize, routedScale, lane, idsOut,
+                                         weightsOut);
+    }
+}
+
 __global__ void __launch_bounds__(256) RoutingTopKKernel(const RoutingArgs a)
 {
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) / 32;
@@ -224,6 +240,46 @@ __device__ __forceinline__ DispatchSmem CarveSmem(uint8_t *base, int numExperts,
     return s;
 }
 
+// out[e] = sum over blocks b in [0, nb) of counts[b * E + e], by all threads of the block.  With E a multiple
+// of four a thread adds 16-byte vectors of several rows, so the chain of dependent loads is nb / (threads /
+// (E / 4)) long instead of nb.
+__device__ void SumBlockCounts(const int32_t *counts, int E, int nb, int32_t *out, int tid, int nThreads)
+{
+    for (int e = tid; e < E; e += nThreads) out[e] = 0;
+    __syncthreads();
+    if ((E & 3) == 0) {
+        const int vecPerRow = E / 4;
+        const int rowsPar = max(1, nThreads / vecPerRow);
+        for (int idx = tid; idx < vecPerRow * rowsPar; idx += nThreads) {
+            const int col = idx % vecPerRow;
+            int4 acc = make_int4(0, 0, 0, 0);
+#pragma unroll 4
+            for (int b = idx / vecPerRow; b < nb; b += rowsPar) {
+                const int4 v = *reinterpret_cast<const int4 *>(counts + static_cast<int64_t>(b) * E + col * 4);
+                acc.x += v.x;
+                acc.y += v.y;
+                acc.z += v.z;
+                acc.w += v.w;
+            }
+            atomicAdd(&out[col * 4 + 0], acc.x);
+            atomicAdd(&out[col * 4 + 1], acc.y);
+            atomicAdd(&out[col * 4 + 2], acc.z);
+            atomicAdd(&out[col * 4 + 3], acc.w);
+        }
+    } else {
+        for (int e = tid; e < E; e += nThreads) {
+            int c = 0;
+            for (int b = 0; b < nb; ++b) c += counts[static_cast<int64_t>(b) * E + e];
+            out[e] = c;
+        }
+    }
+    __syncthreads();
+}
+
+// Stage names of the profiler as the EP kernels use them: chunk_total = routing and counting (dispatch) or
+// nothing (combine); chunk_barrier = grid barrier; post_sync = count exchange and row placement;
+// local_input_to_ipc = rows pushed to their destinations; flag_poll_wait = waiting for arrivals;
+// peer_ipc_to_output = window to output (dispatch) or the weighted reduction (combine).
 __device__ void EpDispatchBody(const EpDispatchArgs &a)
 {
     extern __shared__ __align__(16) uint8_t smemRaw[];
@@ -242,6 +298,9 @@ __device__ void EpDispatchBody(const EpDispatchArgs &a)
     const int routesPerBlock = static_cast<int>(a.tokensPerBlock) * K;
     DispatchSmem sm = CarveSmem(smemRaw, E, routesPerBlock);
     uint8_t *myHalf = DataHalf(comm, rank, epoch);
+    PerfScope perf = PerfInit(tid == 0 ? a.perfTrace : nullptr, static_cast<uint32_t>(rank), blockIdx.x);
+    PerfStageBegin(perf, TILEXR_PERF_KERNEL_TOTAL);
+    PerfStageBegin(perf, TILEXR_PERF_CHUNK_TOTAL);
     int32_t *blockCounts = reinterpret_cast<int32_t *>(myHalf + a.win.blockCountOff);
     const int32_t *countMatrix = reinterpret_cast<const int32_t *>(myHalf + a.win.countOff);
 
@@ -282,17 +341,24 @@ __device__ void EpDispatchBody(const EpDispatchArgs &a)
     }
     __syncthreads();
     for (int e = tid; e < E; e += blockDim.x) blockCounts[static_cast<int64_t>(blockIdx.x) * E + e] = sm.hist[e];
+    PerfStageEnd(perf, TILEXR_PERF_CHUNK_TOTAL);
+    PerfStageBegin(perf, TILEXR_PERF_CHUNK_BARRIER);
     ok = GridBarrier(w, 0) && ok;
+    PerfStageEnd(perf, TILEXR_PERF_CHUNK_BARRIER);
+    PerfStageBegin(perf, TILEXR_PERF_POST_SYNC);
 
     // ---- 2. publish this rank's counts, learn everybody's ----------------------------------------------
     if (ok && blockIdx.x == 0) {
+        SumBlockCounts(blockCounts, E, G, sm.total, tid, blockDim.x);
         for (int e = tid; e < E; e += blockDim.x) {
-            int c = 0;
-            for (int b = 0; b < G; ++b) c += blockCounts[static_cast<int64_t>(b) * E + e];
+            const int c = sm.total[e];
             for (int i = 0; i < R; ++i) {
                 const int peer = (rank + i) % R;
                 reinterpret_cast<int32_t *>(DataHalf(comm, peer, epoch) + a.win.countOff)[static_cast<int64_t>(rank) * E + e] = c;
             }
+        }
+        if (tid < R) {
+            reinterpret_cast<int32_t *>(DataHalf(comm, tid, epoch) + a.win.countOff)[static_cast<int64_t>(R) * E + rank] = G;
         }
         __syncthreads();
         if (tid < R) {
@@ -300,11 +366,7 @@ __device__ void EpDispatchBody(const EpDispatchArgs &a)
                     epoch, 1);
         }
     }
-    for (int e = tid; e < E; e += blockDim.x) {
-        int c = 0;
-        for (int b = 0; b < static_cast<int>(blockIdx.x); ++b) c += blockCounts[static_cast<int64_t>(b) * E + e];
-        sm.blockBase[e] = c;
-    }
+    SumBlockCounts(blockCounts, E, ok ? static_cast<int>(blockIdx.x) : 0, sm.blockBase, tid, blockDim.x);
     {
         bool got = true;
         if (ok && tid < R) {
@@ -338,83 +400,106 @@ __device__ void EpDispatchBody(const EpDispatchArgs &a)
         ok = BlockBroadcastOk(fits);
     }
 
+    PerfStageEnd(perf, TILEXR_PERF_POST_SYNC);
+
     // ---- 3. send ----------------------------------------------------------------------------------------
+    PerfStageBegin(perf, TILEXR_PERF_LOCAL_INPUT_TO_IPC);
     if (ok) {
         const bool bf16 = a.isBf16 != 0;
         const bool quant = a.quantMode == TileXREp::TILEXR_EP_QUANT_FP8_1X128;
         const int chunks = a.h / 16;             // 16 elements per lane and iteration (fp8 path)
         const int iters = (chunks + 31) / 32;
         float *stage = sm.scaleStage + warp * 64;
+        const int scaleVecs = a.win.scaleRowBytes / 16;
         for (int i = warp; i < nTok; i += EP_WARPS) {
             const int t = t0 + i;
             const uint8_t *row = a.x + static_cast<int64_t>(t) * a.h * a.elemSize;
-            bool any = false;
-            for (int k = 0; k < K; ++k) any = any || sm.routeExpert[i * K + k] >= 0;
-            if (!any) continue;
-            constexpr int MAX_ITERS = EP_FP8_MAX_H / 512;
-            uint4 q[MAX_ITERS];
+            // lane k owns route k of this token: where its row, scales and tuple go
+            unsigned long long myPayload = 0, myHalf = 0;
+            uint32_t myRow = 0;
+            int myExpert = -1;
+            if (lane < K) {
+                const int e = sm.routeExpert[i * K + lane];
+                if (e >= 0) {
+                    const int dst = e / a.expertsPerRank;
+                    myRow = static_cast<uint32_t>(sm.dstRow[e] + sm.blockBase[e] + sm.routeRank[i * K + lane]);
+                    uint8_t *half = DataHalf(comm, dst, epoch);
+                    uint8_t *payload = a.zeroCopy
+                                           ? comm->registryPtr->regions[a.outHandle].peerBase[dst] + a.outOffset +
+                                                 static_cast<uint64_t>(myRow) * a.win.rowBytes
+                                           : half + a.win.payloadOff + static_cast<uint64_t>(myRow) * a.win.rowBytes;
+                    myPayload = reinterpret_cast<unsigned long long>(payload);
+                    myHalf = reinterpret_cast<unsigned long long>(half);
+                    myExpert = e;
+                }
+            }
+            if (lane < K && a.routeRowsOut != nullptr) {
+                a.routeRowsOut[static_cast<int64_t>(t) * K + lane] = myExpert >= 0 ? static_cast<int32_t>(myRow) : -1;
+            }
+            const uint32_t routes = __ballot_sync(0xffffffffu, myExpert >= 0);
+            if (routes == 0) continue;
             if (quant) {
+                // each 512-element chunk is quantised once and stored to every destination right away:
+                // nothing row-sized lives in registers, so two blocks fit on an SM
+#pragma unroll 2
+                for (int it = 0; it < iters; ++it) {
+                    const int c = it * 32 + lane;
+                    float f[16];
+                    if (c < chunks) {
+                        Unpack8(ld_vec16(row + static_cast<int64_t>(c) * 32), bf16, f);
+                        Unpack8(ld_vec16(row + static_cast<int64_t>(c) * 32 + 16), bf16, f + 8);
+                    } else {
 #pragma unroll
-                for (int it = 0; it < MAX_ITERS; ++it) {
-                    if (it < iters) {
-                        const int c = it * 32 + lane;
-                        float f[16];
-                        if (c < chunks) {
-                            Unpack8(ld_vec16(row + static_cast<int64_t>(c) * 32), bf16, f);
-                            Unpack8(ld_vec16(row + static_cast<int64_t>(c) * 32 + 16), bf16, f + 8);
-                        } else {
+                        for (int j = 0; j < 16; ++j) f[j] = 0.f;
+                    }
+                    float amax = 0.f;
 #pragma unroll
-                            for (int j = 0; j < 16; ++j) f[j] = 0.f;
-                        }
-                        float amax = 0.f;
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(f[j]));
-                        // 128 elements = 8 consecutive lanes
-                        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-                        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-                        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
-                        amax = fmaxf(amax, FP8_AMAX_FLOOR);
-                        const float inv = FP8_E4M3_MAX / amax;
-                        if ((lane & 7) == 0 && c < chunks) stage[it * 4 + (lane >> 3)] = amax / FP8_E4M3_MAX;
-                        q[it].x = Fp8x4(f[0] * inv, f[1] * inv, f[2] * inv, f[3] * inv);
-                        q[it].y = Fp8x4(f[4] * inv, f[5] * inv, f[6] * inv, f[7] * inv);
-                        q[it].z = Fp8x4(f[8] * inv, f[9] * inv, f[10] * inv, f[11] * inv);
-                        q[it].w = Fp8x4(f[12] * inv, f[13] * inv, f[14] * inv, f[15] * inv);
+                    for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(f[j]));
+                    // 128 elements = 8 consecutive lanes
+                    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+                    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+                    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+                    amax = fmaxf(amax, FP8_AMAX_FLOOR);
+                    const float inv = FP8_E4M3_MAX / amax;
+                    if ((lane & 7) == 0 && c < chunks) stage[it * 4 + (lane >> 3)] = amax / FP8_E4M3_MAX;
+                    Vec16 q;
+                    q.x = Fp8x4(f[0] * inv, f[1] * inv, f[2] * inv, f[3] * inv);
+                    q.y = Fp8x4(f[4] * inv, f[5] * inv, f[6] * inv, f[7] * inv);
+                    q.z = Fp8x4(f[8] * inv, f[9] * inv, f[10] * inv, f[11] * inv);
+                    q.w = Fp8x4(f[12] * inv, f[13] * inv, f[14] * inv, f[15] * inv);
+                    uint32_t m = routes;
+                    while (m != 0) {
+                        const int k = __ffs(m) - 1;
+                        m &= m - 1;
+                        uint8_t *p = reinterpret_cast<uint8_t *>(__shfl_sync(0xffffffffu, myPayload, k));
+                        if (c < chunks) st_vec16(p + static_cast<int64_t>(c) * 16, q);
                     }
                 }
                 __syncwarp();
-            }
-            for (int k = 0; k < K; ++k) {
-                const int e = sm.routeExpert[i * K + k];
-                if (e < 0) continue;
-                const int dst = e / a.expertsPerRank;
-                const uint32_t r = static_cast<uint32_t>(sm.dstRow[e] + sm.blockBase[e] + sm.routeRank[i * K + k]);
-                uint8_t *half = DataHalf(comm, dst, epoch);
-                uint8_t *payload = a.zeroCopy
-                                       ? comm->registryPtr->regions[a.outHandle].peerBase[dst] + a.outOffset +
-                                             static_cast<uint64_t>(r) * a.win.rowBytes
-                                       : half + a.win.payloadOff + static_cast<uint64_t>(r) * a.win.rowBytes;
-                if (quant) {
-#pragma unroll
-                    for (int it = 0; it < MAX_ITERS; ++it) {
-                        if (it < iters) {
-                            const int c = it * 32 + lane;
-                            if (c < chunks) st_vec16(payload + static_cast<int64_t>(c) * 16, Vec16{q[it].x, q[it].y, q[it].z, q[it].w});
-                        }
-                    }
-                    uint8_t *scales = half + a.win.scalesOff + static_cast<uint64_t>(r) * a.win.scaleRowBytes;
-                    const int scaleVecs = a.win.scaleRowBytes / 16;
+                uint32_t m = routes;
+                while (m != 0) {
+                    const int k = __ffs(m) - 1;
+                    m &= m - 1;
+                    uint8_t *half = reinterpret_cast<uint8_t *>(__shfl_sync(0xffffffffu, myHalf, k));
+                    const uint32_t r = __shfl_sync(0xffffffffu, myRow, k);
                     if (lane < scaleVecs) {
-                        st_vec16(scales + lane * 16, *reinterpret_cast<const Vec16 *>(stage + lane * 4));
+                        st_vec16(half + a.win.scalesOff + static_cast<uint64_t>(r) * a.win.scaleRowBytes + lane * 16,
+                                 *reinterpret_cast<const Vec16 *>(stage + lane * 4));
                     }
-                } else {
-                    CopyLanes(payload, row, a.win.rowBytes, lane, 32);
                 }
-                if (lane == 0) {
-                    st_vec16(half + a.win.assistOff + static_cast<uint64_t>(r) * 16,
-                             Vec16{static_cast<uint32_t>(rank), static_cast<uint32_t>(t), static_cast<uint32_t>(k),
-                                   static_cast<uint32_t>(e)});
+            } else {
+                uint32_t m = routes;
+                while (m != 0) {
+                    const int k = __ffs(m) - 1;
+                    m &= m - 1;
+                    uint8_t *p = reinterpret_cast<uint8_t *>(__shfl_sync(0xffffffffu, myPayload, k));
+                    CopyLanes(p, row, a.win.rowBytes, lane, 32);
                 }
+            }
+            if (myExpert >= 0) {
+                st_vec16(reinterpret_cast<uint8_t *>(myHalf) + a.win.assistOff + static_cast<uint64_t>(myRow) * 16,
+                         Vec16{static_cast<uint32_t>(rank), static_cast<uint32_t>(t), static_cast<uint32_t>(lane),
+                               static_cast<uint32_t>(myExpert)});
             }
             __syncwarp();
         }
@@ -423,18 +508,26 @@ __device__ void EpDispatchBody(const EpDispatchArgs &a)
     if (ok && tid < R) {
         SetFlag(FlagSlot(comm, tid, TILEXR_FLAG_OP_BASE + static_cast<int64_t>(rank) * TILEXR_FLAGS_PER_PAIR + blockIdx.x), epoch, 1);
     }
+    PerfStageEnd(perf, TILEXR_PERF_LOCAL_INPUT_TO_IPC, static_cast<uint64_t>(nRoutes) * a.win.rowBytes);
 
     // ---- 4. receive ---------------------------------------------------------------------------------------
+    PerfStageBegin(perf, TILEXR_PERF_FLAG_POLL_WAIT);
     {
+        // every thread polls its share of the (source, block) flags; a source's block count came with its counts
         bool got = true;
-        if (ok && tid < R) {
-            for (int b = 0; b < G && got; ++b) {
-                const int64_t slot = TILEXR_FLAG_OP_BASE + static_cast<int64_t>(tid) * TILEXR_FLAGS_PER_PAIR + b;
-                got = WaitFlagGE(w, FlagSlot(comm, rank, slot), 1, tid, slot);
+        if (ok) {
+            for (int s = 0; s < R && got; ++s) {
+                const int64_t base = TILEXR_FLAG_OP_BASE + static_cast<int64_t>(s) * TILEXR_FLAGS_PER_PAIR;
+                const int blocksOfS = min(countMatrix[static_cast<int64_t>(R) * E + s], static_cast<int>(EP_COUNT_FLAG_SLOT));
+                for (int b = tid; b < blocksOfS && got; b += blockDim.x) {
+                    got = WaitFlagGE(w, FlagSlot(comm, rank, base + b), 1, s, base + b);
+                }
             }
         }
         ok = BlockBroadcastOk(got) && ok;
     }
+    PerfStageEnd(perf, TILEXR_PERF_FLAG_POLL_WAIT);
+    PerfStageBegin(perf, TILEXR_PERF_PEER_IPC_TO_OUTPUT);
     if (ok) {
         const int firstLocal = rank * a.expertsPerRank;
         int64_t rows = 0;
@@ -455,21 +548,37 @@ __device__ void EpDispatchBody(const EpDispatchArgs &a)
                       blockDim.x);
         }
         if (blockIdx.x == 0) {
-            if (tid == 0) {
-                int64_t running = 0;
-                for (int le = 0; le < a.expertsPerRank; ++le) {
-                    const int e = firstLocal + le;
-                    for (int s = 0; s < R; ++s) {
-                        running += countMatrix[static_cast<int64_t>(s) * E + e];
-                        a.sendCountsOut[le * R + s] = static_cast<int32_t>(running);
+            // cumulative counts in (local expert, source) order: an inclusive scan of E_local * R numbers
+            const int n = a.expertsPerRank * R;
+            __syncthreads();
+            for (int i = tid; i < n; i += blockDim.x) sm.hist[i] = countMatrix[static_cast<int64_t>(i % R) * E + firstLocal + i / R];
+            __syncthreads();
+            if (warp == 0) {
+                int carry = 0;
+                for (int base = 0; base < n; base += 32) {
+                    int v = base + lane < n ? sm.hist[base + lane] : 0;
+#pragma unroll
+                    for (int o = 1; o < 32; o <<= 1) {
+                        const int u = __shfl_up_sync(0xffffffffu, v, o);
+                        if (lane >= o) v += u;
                     }
-                    a.expertTokenNumsOut[le] =
-                        a.tokenNumsType == TileXREp::TILEXR_EP_TOKEN_NUMS_COUNT ? static_cast<int64_t>(sm.total[e]) : running;
+                    v += carry;
+                    if (base + lane < n) sm.hist[base + lane] = v;
+                    carry = __shfl_sync(0xffffffffu, v, 31);
                 }
-                if (a.recvTotalOut != nullptr) *a.recvTotalOut = static_cast<int32_t>(running);
             }
+            __syncthreads();
+            for (int i = tid; i < n; i += blockDim.x) a.sendCountsOut[i] = sm.hist[i];
+            for (int le = tid; le < a.expertsPerRank; le += blockDim.x) {
+                a.expertTokenNumsOut[le] = a.tokenNumsType == TileXREp::TILEXR_EP_TOKEN_NUMS_COUNT
+                                               ? static_cast<int64_t>(sm.total[firstLocal + le])
+                                               : static_cast<int64_t>(sm.hist[le * R + R - 1]);
+            }
+            if (tid == 0 && a.recvTotalOut != nullptr) *a.recvTotalOut = n > 0 ? sm.hist[n - 1] : 0;
         }
     }
+    PerfStageEnd(perf, TILEXR_PERF_PEER_IPC_TO_OUTPUT);
+    PerfStageEnd(perf, TILEXR_PERF_KERNEL_TOTAL);
     KernelEpilogue(w, ok);
 }
 
@@ -488,26 +597,45 @@ __device__ void EpCombineBody(const EpCombineArgs &a)
     const int64_t nWarps = static_cast<int64_t>(gridDim.x) * warpsPerBlock;
     const uint32_t epoch = w.epoch;
     const bool bf16 = a.isBf16 != 0;
+    PerfScope perf = PerfInit(threadIdx.x == 0 ? a.perfTrace : nullptr, static_cast<uint32_t>(rank), blockIdx.x);
+    PerfStageBegin(perf, TILEXR_PERF_KERNEL_TOTAL);
 
     if (ok) {
+        PerfStageBegin(perf, TILEXR_PERF_LOCAL_INPUT_TO_IPC);
         // ---- send every processed row back to slot (token, k) of its source ------------------------------
         const int64_t rows = a.sendCounts[a.sendCountEntries - 1];
-        for (int64_t r = gwarp; r < rows; r += nWarps) {
-            const Vec16 tuple = ld_vec16(a.assist + r * 4);
-            const int src = static_cast<int>(tuple.x);
-            const int64_t slot = static_cast<int64_t>(tuple.y) * K + tuple.z;
-            if (src < 0 || src >= comm->rankSize || slot < 0 || slot >= static_cast<int64_t>(a.bs) * K) continue;
-            uint8_t *dst = DataHalf(comm, src, epoch) + slot * a.rowBytes;
-            CopyLanes(dst, a.expertOut + r * a.rowBytes, a.rowBytes, lane, 32);
+        // A warp copies a group of rows, then lanes 0..group-1 release one flag each with a single
+        // system-scope fence instruction for the whole group.
+        // Rows of this rank's own tokens stay where they are when the reducer knows their row (direct).
+        const bool direct = a.routeRows != nullptr && a.expertIds != nullptr;
+        constexpr int kRowGroup = 4;
+        for (int64_t r0 = gwarp * kRowGroup; r0 < rows; r0 += nWarps * kRowGroup) {
+            uint64_t *myFlag = nullptr;
+#pragma unroll 1
+            for (int g = 0; g < kRowGroup; ++g) {
+                const int64_t r = r0 + g;
+                if (r >= rows) break;
+                const Vec16 tuple = ld_vec16(a.assist + r * 4);
+                const int src = static_cast<int>(tuple.x);
+                const int64_t slot = static_cast<int64_t>(tuple.y) * K + tuple.z;
+                if (src < 0 || src >= comm->rankSize || slot < 0 || slot >= static_cast<int64_t>(a.bs) * K) continue;
+                if (direct && src == rank) continue;
+                uint8_t *dst = DataHalf(comm, src, epoch) + slot * a.rowBytes;
+                CopyLanes(dst, a.expertOut + r * a.rowBytes, a.rowBytes, lane, 32);
+                if (lane == g) myFlag = FlagSlot(comm, src, TILEXR_FLAG_OP_BASE + slot);
+            }
             __syncwarp();
-            if (lane == 0) SetFlag(FlagSlot(comm, src, TILEXR_FLAG_OP_BASE + slot), epoch, 1);
+            if (myFlag != nullptr) SetFlag(myFlag, epoch, 1);
         }
+        PerfStageEnd(perf, TILEXR_PERF_LOCAL_INPUT_TO_IPC);
+        PerfStageBegin(perf, TILEXR_PERF_PEER_IPC_TO_OUTPUT);
         // ---- reduce this rank's tokens ------------------------------------------------------------------------
         const uint8_t *half = DataHalf(comm, rank, epoch);
         const int vecs = a.rowBytes / 16;
         for (int64_t t = gwarp; t < a.bs && w.ok(); t += nWarps) {
             int e = -1;
             float wk = 0.f;
+            unsigned long long myRowPtr = 0;
             if (lane < K) {
                 e = a.expertIds != nullptr ? a.expertIds[t * K + lane] : 0;
                 if (e >= a.numExperts) e = -1;
@@ -516,7 +644,13 @@ __device__ void EpCombineBody(const EpCombineArgs &a)
                 wk = a.expertScales != nullptr ? a.expertScales[t * K + lane] : 1.0f;
                 if (e >= 0) {
                     const int64_t slot = t * K + lane;
-                    WaitFlagGE(w, FlagSlot(comm, rank, TILEXR_FLAG_OP_BASE + slot), 1, e / a.expertsPerRank, slot);
+                    const int64_t localRow = direct && e / a.expertsPerRank == rank ? a.routeRows[slot] : -1;
+                    if (localRow >= 0 && localRow < rows) {
+                        myRowPtr = reinterpret_cast<unsigned long long>(a.expertOut + localRow * a.rowBytes);
+                    } else {
+                        myRowPtr = reinterpret_cast<unsigned long long>(half + slot * a.rowBytes);
+                        WaitFlagGE(w, FlagSlot(comm, rank, TILEXR_FLAG_OP_BASE + slot), 1, e / a.expertsPerRank, slot);
+                    }
                 }
             }
             const bool good = __all_sync(0xffffffffu, w.ok());
@@ -526,36 +660,55 @@ __device__ void EpCombineBody(const EpCombineArgs &a)
             }
             const uint32_t active = __ballot_sync(0xffffffffu, e >= 0);
             uint8_t *y = a.yOut + t * a.rowBytes;
-            for (int v = lane; v < vecs; v += 32) {
+            for (int v0 = 0; v0 < vecs; v0 += 32) {  // warp-uniform trip count: the loop body shuffles
+                const int v = v0 + lane;
+                const bool mine = v < vecs;
                 float acc[8];
 #pragma unroll
                 for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-                for (int k = 0; k < K; ++k) {
-                    const float wgt = __shfl_sync(0xffffffffu, wk, k);
-                    if ((active >> k) & 1u) {
-                        float f[8];
-                        Unpack8(ld_vec16_stream(half + (t * K + k) * a.rowBytes + v * 16), bf16, f);
+                // the rows of up to eight routes are fetched together, then accumulated in k order
+                for (int k0 = 0; k0 < K; k0 += 8) {
+                    Vec16 q[8];
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) acc[j] = fmaf(wgt, f[j], acc[j]);
+                    for (int j = 0; j < 8; ++j) {
+                        const int k = k0 + j;
+                        q[j] = Vec16{0u, 0u, 0u, 0u};
+                        if (k < K && ((active >> k) & 1u)) {
+                            const uint8_t *src = reinterpret_cast<const uint8_t *>(__shfl_sync(0xffffffffu, myRowPtr, k));
+                            if (mine) q[j] = ld_vec16_stream(src + v * 16);
+                        }
+                    }
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const int k = k0 + j;
+                        if (k < K && ((active >> k) & 1u)) {
+                            const float wgt = __shfl_sync(0xffffffffu, wk, k);
+                            float f[8];
+                            Unpack8(q[j], bf16, f);
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) acc[i] = fmaf(wgt, f[i], acc[i]);
+                        }
                     }
                 }
-                if (a.sharedExpertX != nullptr) {
+                if (mine && a.sharedExpertX != nullptr) {
                     float f[8];
                     Unpack8(ld_vec16(a.sharedExpertX + t * a.rowBytes + v * 16), bf16, f);
 #pragma unroll
                     for (int j = 0; j < 8; ++j) acc[j] += f[j];
                 }
-                st_vec16(y + v * 16, Pack8(acc, bf16));
+                if (mine) st_vec16(y + v * 16, Pack8(acc, bf16));
             }
         }
         ok = w.ok();
+        PerfStageEnd(perf, TILEXR_PERF_PEER_IPC_TO_OUTPUT);
     }
     ok = BlockBroadcastOk(ok);
+    PerfStageEnd(perf, TILEXR_PERF_KERNEL_TOTAL);
     KernelEpilogue(w, ok);
 }
 
-TILEXR_DEFINE_KERNEL(TileXREpDispatchKernel, EpDispatchArgs, EpDispatchBody, EP_BLOCK_THREADS)
-TILEXR_DEFINE_KERNEL(TileXREpCombineKernel, EpCombineArgs, EpCombineBody, EP_BLOCK_THREADS)
+TILEXR_DEFINE_KERNEL_OCC(TileXREpDispatchKernel, EpDispatchArgs, EpDispatchBody, EP_BLOCK_THREADS, 2)
+TILEXR_DEFINE_KERNEL_OCC(TileXREpCombineKernel, EpCombineArgs, EpCombineBody, EP_BLOCK_THREADS, 2)
 
 // ---- stand-alone quantisation and norm kernels ---------------------------------------------------------------
 

@@ -23,7 +23,8 @@ struct EpDispatchWindow {
     uint64_t payloadOff;      // [maxRecvRows][rowBytes]           (unused when zeroCopy)
     uint64_t scalesOff;       // [maxRecvRows][scaleRowBytes]
     uint64_t assistOff;       // [maxRecvRows][16]
-    uint64_t countOff;        // [rankSize][numExperts] int32: routes of source s for expert e
+    uint64_t countOff;        // [rankSize][numExperts] int32: routes of source s for expert e; then [rankSize] int32:
+                              // blocks of source s that will each raise one "rows sent" flag
     uint64_t blockCountOff;   // [grid][numExperts] int32, local scratch of the sender
     uint64_t totalBytes;
     uint32_t rowBytes;
@@ -57,6 +58,8 @@ struct EpDispatchArgs {
     uint32_t zeroCopy;
     uint32_t outHandle;
     uint64_t outOffset;
+    void *perfTrace;                 // stage profiler buffer of this launch, or null
+    int32_t *routeRowsOut;           // [bs, topK] destination row per route, or null
 };
 
 struct EpCombineArgs {
@@ -75,6 +78,8 @@ struct EpCombineArgs {
     uint32_t rowBytes;
     uint32_t isBf16;
     uint32_t sendCountEntries;
+    void *perfTrace;
+    const int32_t *routeRows;        // [bs, topK] from dispatch: local routes bypass the window; or null
 };
 
 struct RoutingArgs {

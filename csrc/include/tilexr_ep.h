@@ -71,6 +71,7 @@ typedef struct TileXREpDispatchParams {
     int32_t *sendCountsOut;        // [moeExpertNum / R * R]
     int32_t *recvTotalOut;         // [1] rows received; may be null
     TXR_DT dtype;                  // dtype of x
+    int32_t *routeRowsOut;         // [bs, topK] row of each route at its destination rank (-1 = inactive); may be null
 } TileXREpDispatchParams;
 
 typedef struct TileXREpCombineParams {
@@ -85,9 +86,16 @@ typedef struct TileXREpCombineParams {
     int64_t bs, h, topK, moeExpertNum;
     void *yOut;                    // [bs, h]
     TXR_DT dtype;
+    // [bs, topK] from dispatch, or null.  With it (and expertIds) the routes whose expert lives on this rank
+    // are read straight from expertOut: they take no staging copy and no flag.
+    const int32_t *routeRows;
 } TileXREpCombineParams;
 
 int TileXRMoeEpDispatchFused(const TileXREpDispatchParams *params, TileXRCommPtr comm, TileXRStream stream);
+// Sizes of the two parameter structs as the library was compiled, (dispatch << 32) | combine.  A caller built
+// against other headers compares it with TILEXR_EP_ABI_STAMP before its first call.
+uint64_t TileXREpAbiStamp(void);
+#define TILEXR_EP_ABI_STAMP (((uint64_t)sizeof(TileXREpDispatchParams) << 32) | (uint64_t)sizeof(TileXREpCombineParams))
 int TileXRMoeEpCombineFused(const TileXREpCombineParams *params, TileXRCommPtr comm, TileXRStream stream);
 
 // Bytes of window each half must offer for a dispatch / combine of this shape (0 on bad shape).

@@ -52,9 +52,11 @@ int MaxCooperativeGrid(TileXRCommPtr comm, const KernelEntry &kernel, unsigned b
 #if defined(__CUDACC__)
 // Defines NAME_single / NAME_emulated around a device body `BODY(const ARGS &)` and a
 // KernelEntry named NAME##Entry.
-#define TILEXR_DEFINE_KERNEL(NAME, ARGS, BODY, MAX_THREADS)                                            \
-    __global__ void __launch_bounds__(MAX_THREADS) NAME##_single(const ARGS a) { BODY(a); }            \
-    __global__ void __launch_bounds__(MAX_THREADS) NAME##_emulated(const ARGS *perRank)                \
+#define TILEXR_DEFINE_KERNEL(NAME, ARGS, BODY, MAX_THREADS) TILEXR_DEFINE_KERNEL_OCC(NAME, ARGS, BODY, MAX_THREADS, 1)
+// Same, asking the compiler to keep MIN_BLOCKS blocks of MAX_THREADS threads resident per SM.
+#define TILEXR_DEFINE_KERNEL_OCC(NAME, ARGS, BODY, MAX_THREADS, MIN_BLOCKS)                            \
+    __global__ void __launch_bounds__(MAX_THREADS, MIN_BLOCKS) NAME##_single(const ARGS a) { BODY(a); } \
+    __global__ void __launch_bounds__(MAX_THREADS, MIN_BLOCKS) NAME##_emulated(const ARGS *perRank)    \
     {                                                                                                  \
         const ARGS a = perRank[blockIdx.y];                                                            \
         BODY(a);                                                                                       \

@@ -351,7 +351,8 @@ py::dict CollectivePlan(int opType, int64_t count, at::ScalarType dtype, int ran
 
 const void *PtrOrNull(const c10::optional<at::Tensor> &t) { return t.has_value() && t->defined() ? t->data_ptr() : nullptr; }
 
-// Returns (expand_x, dynamic_scales|None, assist, expert_token_nums, send_counts, recv_total, topk_ids, topk_weights).
+// Returns (expand_x, dynamic_scales|None, assist, expert_token_nums, send_counts, recv_total, topk_ids, topk_weights,
+// route_rows).
 py::tuple EpDispatch(const CommPtr &c, const at::Tensor &x, const c10::optional<at::Tensor> &expertIds,
                      const c10::optional<at::Tensor> &gateLogits, const c10::optional<at::Tensor> &selectionBias,
                      const c10::optional<at::Tensor> &activeMask, int64_t topK, int64_t numExperts, int64_t quantMode,
@@ -381,6 +382,7 @@ py::tuple EpDispatch(const CommPtr &c, const at::Tensor &x, const c10::optional<
     at::Tensor recvTotal = at::empty({1}, i32);
     at::Tensor topkIds = at::empty({bs, topK}, i32);
     at::Tensor topkWeights = at::empty({bs, topK}, x.options().dtype(at::kFloat));
+    at::Tensor routeRows = at::empty({bs, topK}, i32);
     TileXREpDispatchParams p;
     std::memset(&p, 0, sizeof(p));
     p.x = x.data_ptr();
@@ -416,19 +418,22 @@ py::tuple EpDispatch(const CommPtr &c, const at::Tensor &x, const c10::optional<
     p.expertTokenNumsOut = tokenNums.data_ptr<int64_t>();
     p.sendCountsOut = sendCounts.data_ptr<int32_t>();
     p.recvTotalOut = recvTotal.data_ptr<int32_t>();
+    p.routeRowsOut = routeRows.data_ptr<int32_t>();
     p.dtype = ToDtype(x.scalar_type());
-    for (const at::Tensor &t : {expandX, scales, assist, tokenNums, sendCounts, recvTotal, topkIds, topkWeights}) Keep(t);
+    for (const at::Tensor &t : {expandX, scales, assist, tokenNums, sendCounts, recvTotal, topkIds, topkWeights, routeRows}) Keep(t);
     Check(TileXRMoeEpDispatchFused(&p, c->ptr(), StreamOf(x)), "TileXRMoeEpDispatchFused");
     return py::make_tuple(expandX, quant ? py::cast(scales) : py::none(), assist, tokenNums, sendCounts, recvTotal, topkIds,
-                          topkWeights);
+                          topkWeights, routeRows);
 }
 
 at::Tensor EpCombine(const CommPtr &c, const at::Tensor &expertOut, const at::Tensor &assist, const at::Tensor &sendCounts,
                      const c10::optional<at::Tensor> &expertIds, const c10::optional<at::Tensor> &expertScales,
                      const c10::optional<at::Tensor> &activeMask, const c10::optional<at::Tensor> &sharedExpertX, int64_t bs,
-                     int64_t topK, int64_t numExperts, const c10::optional<at::Tensor> &yOut)
+                     int64_t topK, int64_t numExperts, const c10::optional<at::Tensor> &yOut,
+                     const c10::optional<at::Tensor> &routeRows)
 {
     RequireContiguous(expertOut, "expert_out");
+    Keep(routeRows);
     TORCH_CHECK(expertOut.dim() == 2 && expertOut.is_cuda(), "expert_out must be a 2-D CUDA tensor");
     Keep(expertOut);
     Keep(assist);
@@ -451,6 +456,11 @@ at::Tensor EpCombine(const CommPtr &c, const at::Tensor &expertOut, const at::Te
         p.activeMaskType = activeMask->dim() == 1 ? TileXREp::TILEXR_EP_ACTIVE_MASK_TOKEN : TileXREp::TILEXR_EP_ACTIVE_MASK_EXPERT;
     }
     p.sharedExpertX = PtrOrNull(sharedExpertX);
+    if (routeRows.has_value() && routeRows->defined()) {
+        TORCH_CHECK(routeRows->scalar_type() == at::kInt && routeRows->is_contiguous() && routeRows->numel() == bs * topK,
+                    "route_rows must be contiguous int32 [bs, top_k]");
+        p.routeRows = routeRows->data_ptr<int32_t>();
+    }
     p.bs = bs;
     p.h = h;
     p.topK = topK;
@@ -555,6 +565,8 @@ std::shared_ptr<PerfSession> PerfCreate(const std::string &dir, unsigned sampleE
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m)
 {
     m.doc() = "TileXR-B200 native binding";
+    TORCH_CHECK(TileXREpAbiStamp() == TILEXR_EP_ABI_STAMP,
+                "tilexr_b200._C was built against other headers than libtilexr.so; run python -m tilexr_b200._build");
     py::class_<Comm, CommPtr>(m, "Comm")
         .def_property_readonly("rank", &Comm::rank)
         .def_property_readonly("world_size", &Comm::rankSize)
@@ -609,7 +621,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m)
     m.def("ep_combine", &EpCombine, py::arg("comm"), py::arg("expert_out"), py::arg("assist"), py::arg("send_counts"),
           py::arg("expert_ids") = py::none(), py::arg("expert_scales") = py::none(), py::arg("active_mask") = py::none(),
           py::arg("shared_expert_x") = py::none(), py::arg("bs") = 0, py::arg("top_k") = 1, py::arg("num_experts") = 1,
-          py::arg("y_out") = py::none());
+          py::arg("y_out") = py::none(), py::arg("route_rows") = py::none());
     m.def("routing_topk", &RoutingTopK, py::arg("gate_logits"), py::arg("selection_bias") = py::none(), py::arg("top_k") = 1,
           py::arg("score_func") = 0, py::arg("renormalize") = true, py::arg("routed_scale") = 1.0);
     m.def("fp8_quant_1x128", &Fp8Quant);

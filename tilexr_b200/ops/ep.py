@@ -28,6 +28,7 @@ class DispatchResult:
     recv_total: torch.Tensor          # [1] int32
     topk_ids: torch.Tensor            # [bs, k] int32 (negative = inactive)
     topk_weights: torch.Tensor        # [bs, k] fp32 (only meaningful with fused routing)
+    route_rows: torch.Tensor          # [bs, k] int32 row of each route at its destination rank (-1 = inactive)
     bs: int
     top_k: int
     num_experts: int
@@ -50,4 +51,4 @@ def combine(comm, expert_out: torch.Tensor, d: DispatchResult, *, expert_scales:
             active_mask: Optional[torch.Tensor] = None, shared_expert_x: Optional[torch.Tensor] = None,
             y_out: Optional[torch.Tensor] = None) -> torch.Tensor:
     return _C.ep_combine(comm, expert_out, d.assist, d.send_counts, d.topk_ids, expert_scales, active_mask, shared_expert_x,
-                         d.bs, d.top_k, d.num_experts, y_out)
+                         d.bs, d.top_k, d.num_experts, y_out, d.route_rows)
