@@ -96,8 +96,10 @@ int Plan(int kind, uint64_t sliceBytes, int rankSize, uint64_t dataHalfBytes, un
     const uint32_t tiles = static_cast<uint32_t>((launchPair + tile - 1) / tile);
 
     // block roles
-    const bool big = launchPair >= (4u << 20);
-    uint32_t cap = static_cast<uint32_t>(EnvLong("TILEXR_COLL_BLOCKS", big ? 32 : 16));
+    // blocks per role: measured on NVLink 5, 16 blocks carry messages up to a few hundred KB at the lowest
+    // latency, and 64 are needed from about 1 MB per pair to keep the links busy
+    const uint32_t autoCap = launchPair >= (512u << 10) ? 64 : launchPair >= (128u << 10) ? 32 : 16;
+    uint32_t cap = static_cast<uint32_t>(EnvLong("TILEXR_COLL_BLOCKS", autoCap));
     if (EnvLong("LCCL_PARALLEL", 0) == 1) cap = static_cast<uint32_t>(rankSize);
     const uint64_t fanItems = (kind == COLL_ALL_TO_ALL) ? static_cast<uint64_t>(tiles) * rankSize
                               : (kind == COLL_REDUCE_SCATTER || twoShot) ? static_cast<uint64_t>(tiles) * (rankSize - 1)

@@ -211,10 +211,11 @@ int TileXRAllGatherMatmul(const void *aShard, void *aStaging, const void *b, voi
     FillTiling(&g, m, n, k);
     g.shardRows = static_cast<int32_t>(shardRows);
     g.blocksPerShard = static_cast<int32_t>(shardRows / GEMM_BM);
-    g.kChunks = std::max(1, std::min<int>(GEMM_MAX_K_CHUNKS, std::min<int>(g.kBlocks, (TILEXR_FLAGS_PER_PAIR - 1) / g.blocksPerShard)));
+    g.flagStride = TILEXR_MAX_RANK_SIZE * TILEXR_FLAGS_PER_PAIR / R;
+    g.kChunks = std::max(1, std::min<int>(GEMM_MAX_K_CHUNKS, std::min<int>(g.kBlocks, (g.flagStride - 1) / g.blocksPerShard)));
     g.kBlocksPerChunk = (g.kBlocks + g.kChunks - 1) / g.kChunks;
     g.kChunks = (g.kBlocks + g.kBlocksPerChunk - 1) / g.kBlocksPerChunk;
-    if (g.blocksPerShard * g.kChunks >= TILEXR_FLAGS_PER_PAIR) {
+    if (g.blocksPerShard * g.kChunks >= g.flagStride) {
         TILEXR_LOG(ERROR) << "all-gather matmul: " << shardRows << " rows per rank exceed the per-pair flag space";
         return TILEXR_ERROR_NOT_SUPPORT;
     }
@@ -268,7 +269,8 @@ int TileXRMatmulReduceScatter(const void *a, const void *b, void *partialStaging
     FillTiling(&g, m, n, k);
     g.shardRows = static_cast<int32_t>(shardRows);
     g.blocksPerShard = static_cast<int32_t>(shardRows / GEMM_BM);
-    if (static_cast<int64_t>(g.blocksPerShard) * g.nBlocks >= TILEXR_FLAGS_PER_PAIR) {
+    g.flagStride = TILEXR_MAX_RANK_SIZE * TILEXR_FLAGS_PER_PAIR / R;
+    if (static_cast<int64_t>(g.blocksPerShard) * g.nBlocks >= g.flagStride) {
         TILEXR_LOG(ERROR) << "matmul reduce-scatter: " << g.blocksPerShard * g.nBlocks << " tiles per owner exceed the per-pair flag space";
         return TILEXR_ERROR_NOT_SUPPORT;
     }

@@ -43,6 +43,7 @@ struct GemmArgs {
     int32_t shardRows;        // rows per rank in the fused modes
     int32_t blocksPerShard;   // shardRows / GEMM_BM
     int32_t kChunks;          // all-gather: flags per row block
+    int32_t flagStride;       // flags of one (source, destination) pair: the flag plane divided by the rank count
     int32_t kBlocksPerChunk;
     uint32_t commBlocks;      // all-gather: leading CTAs that only push
     uint32_t stageHandle;     // registry handle of the staging buffer (A staging or partial-C staging)

@@ -251,7 +251,7 @@ __device__ void GemmBody(const GemmArgs &a)
                 }
                 __syncthreads();
                 if (threadIdx.x == 0) {
-                    SetFlag(FlagSlot(a.comm, peer, FLAG_PLANE_A + static_cast<int64_t>(rank) * TILEXR_FLAGS_PER_PAIR + piece), epoch, 1);
+                    SetFlag(FlagSlot(a.comm, peer, FLAG_PLANE_A + static_cast<int64_t>(rank) * a.flagStride + piece), epoch, 1);
                 }
             }
         }
@@ -303,7 +303,7 @@ __device__ void GemmBody(const GemmArgs &a)
                     if (!WaitBar(&st->empty[stage], phase ^ 1u, st, budgetNs)) break;
                     if (remoteA && kb % a.kBlocksPerChunk == 0) {
                         const int piece = tc.mLocal * a.kChunks + kb / a.kBlocksPerChunk;
-                        const int64_t slot = FLAG_PLANE_A + static_cast<int64_t>(tc.shard) * TILEXR_FLAGS_PER_PAIR + piece;
+                        const int64_t slot = FLAG_PLANE_A + static_cast<int64_t>(tc.shard) * a.flagStride + piece;
                         if (!WaitFlagGE(w, FlagSlot(a.comm, rank, slot), 1, tc.shard, slot)) {
                             st->abortFlag = 1;
                             break;
@@ -420,7 +420,7 @@ __device__ void GemmBody(const GemmArgs &a)
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 if (warp == 2 && lane == 0) {
                     const int tileLocal = tc.mLocal * a.nBlocks + tc.nBlock;
-                    SetFlag(FlagSlot(a.comm, tc.shard, FLAG_PLANE_B + static_cast<int64_t>(rank) * TILEXR_FLAGS_PER_PAIR + tileLocal), epoch, 1);
+                    SetFlag(FlagSlot(a.comm, tc.shard, FLAG_PLANE_B + static_cast<int64_t>(rank) * a.flagStride + tileLocal), epoch, 1);
                 }
             }
         }
@@ -433,7 +433,7 @@ __device__ void GemmBody(const GemmArgs &a)
             for (int tl = cta; tl < owned; tl += nCta) {
                 bool got = true;
                 if (et < ranks) {
-                    const int64_t slot = FLAG_PLANE_B + static_cast<int64_t>(et) * TILEXR_FLAGS_PER_PAIR + tl;
+                    const int64_t slot = FLAG_PLANE_B + static_cast<int64_t>(et) * a.flagStride + tl;
                     got = WaitFlagGE(w, FlagSlot(a.comm, rank, slot), 1, et, slot);
                 }
                 // join the 128 epilogue threads and share the verdict

