@@ -40,6 +40,8 @@ bool DispatchLayout(int64_t h, int64_t numExperts, int64_t rankSize, int64_t max
     off = Align(off + static_cast<uint64_t>(maxRecvRows) * win->scaleRowBytes, 256);
     win->assistOff = off;
     off = Align(off + static_cast<uint64_t>(maxRecvRows) * 16, 256);
+    win->extOff = off;
+    off = Align(off + static_cast<uint64_t>(maxRecvRows) * 8, 256);
     win->countOff = off;
     off = Align(off + (static_cast<uint64_t>(rankSize) * numExperts + rankSize) * 4, 256);
     win->blockCountOff = off;
@@ -152,6 +154,10 @@ int TileXRMoeEpDispatchFused(const TileXREpDispatchParams *p, TileXRCommPtr comm
     if (p->activeMaskType != TILEXR_EP_ACTIVE_MASK_NONE && p->xActiveMask == nullptr) return TILEXR_ERROR_PARA_CHECK_FAIL;
     if (p->activeMaskType < 0 || p->activeMaskType > TILEXR_EP_ACTIVE_MASK_EXPERT) return TILEXR_ERROR_PARA_CHECK_FAIL;
     if (p->maxRecvRows <= 0) return TILEXR_ERROR_PARA_CHECK_FAIL;
+    if (p->dedup != 0 && (p->assistExtOut == nullptr || (p->gateLogits == nullptr && p->expertScales == nullptr))) {
+        TILEXR_LOG(ERROR) << "EP dispatch: dedup needs assistExtOut and gate weights (fused routing or expertScales)";
+        return TILEXR_ERROR_PARA_CHECK_FAIL;
+    }
 
     // grid: one block per ~8 tokens per warp-set, capped by what can be co-resident
     const int ranksPerDevice = (c.hostArgs->extraFlag & TILEXR_FLAG_EMULATED) ? c.rankSize : 1;
@@ -227,6 +233,10 @@ int TileXRMoeEpDispatchFused(const TileXREpDispatchParams *p, TileXRCommPtr comm
     a.outHandle = handle;
     a.outOffset = regionOffset;
     a.routeRowsOut = p->routeRowsOut;
+    a.expertScales = p->expertScales;
+    a.expandScalesOut = p->expandScalesOut;
+    a.assistExtOut = p->assistExtOut;
+    a.dedup = (p->dedup != 0 && c.rankSize > 1) ? 1u : 0u;
     int64_t magic = 0;
     ret = TileXRCommNextMagic(comm, &magic);
     if (ret != TILEXR_SUCCESS) return ret;
@@ -281,6 +291,12 @@ int TileXRMoeEpCombineFused(const TileXREpCombineParams *p, TileXRCommPtr comm, 
     a.isBf16 = p->dtype == TILEXR_DATA_TYPE_BFP16 ? 1u : 0u;
     a.sendCountEntries = static_cast<uint32_t>(p->moeExpertNum / c.rankSize * c.rankSize);
     a.routeRows = p->expertIds != nullptr ? p->routeRows : nullptr;
+    a.dedup = (p->dedup != 0 && c.rankSize > 1) ? 1u : 0u;
+    a.assistExt = p->assistExt;
+    if (a.dedup != 0 && (p->assistExt == nullptr || p->expertIds == nullptr)) {
+        TILEXR_LOG(ERROR) << "EP combine: dedup needs assistExt from dispatch and expertIds";
+        return TILEXR_ERROR_PARA_CHECK_FAIL;
+    }
     int64_t magic = 0;
     ret = TileXRCommNextMagic(comm, &magic);
     if (ret != TILEXR_SUCCESS) return ret;

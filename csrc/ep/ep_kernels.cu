@@ -438,6 +438,23 @@ __device__ void EpDispatchBody(const EpDispatchArgs &a)
             }
             const uint32_t routes = __ballot_sync(0xffffffffu, myExpert >= 0);
             if (routes == 0) continue;
+            // Routes of this token to one remote rank form a group: the lowest k (the head) carries the
+            // payload, the others only their tuple, and every member links to the next one.
+            const int myDst = myExpert >= 0 ? myExpert / a.expertsPerRank : -1;
+            uint32_t myLink = 0;
+            if (a.dedup != 0) {
+                bool follower = false;
+                for (int j = 0; j < K; ++j) {
+                    const int dj = __shfl_sync(0xffffffffu, myDst, j);
+                    const uint32_t rj = __shfl_sync(0xffffffffu, myRow, j);
+                    if (dj >= 0 && dj == myDst && myDst != rank) {
+                        if (j < lane) follower = true;
+                        else if (j > lane && myLink == 0) myLink = rj + 1;
+                    }
+                }
+                if (follower) myLink |= EP_LINK_FOLLOWER;
+            }
+            const uint32_t payloadRoutes = __ballot_sync(0xffffffffu, myExpert >= 0 && (myLink & EP_LINK_FOLLOWER) == 0);
             if (quant) {
                 // each 512-element chunk is quantised once and stored to every destination right away:
                 // nothing row-sized lives in registers, so two blocks fit on an SM
@@ -467,7 +484,7 @@ __device__ void EpDispatchBody(const EpDispatchArgs &a)
                     q.y = Fp8x4(f[4] * inv, f[5] * inv, f[6] * inv, f[7] * inv);
                     q.z = Fp8x4(f[8] * inv, f[9] * inv, f[10] * inv, f[11] * inv);
                     q.w = Fp8x4(f[12] * inv, f[13] * inv, f[14] * inv, f[15] * inv);
-                    uint32_t m = routes;
+                    uint32_t m = payloadRoutes;
                     while (m != 0) {
                         const int k = __ffs(m) - 1;
                         m &= m - 1;
@@ -476,7 +493,7 @@ __device__ void EpDispatchBody(const EpDispatchArgs &a)
                     }
                 }
                 __syncwarp();
-                uint32_t m = routes;
+                uint32_t m = payloadRoutes;
                 while (m != 0) {
                     const int k = __ffs(m) - 1;
                     m &= m - 1;
@@ -488,7 +505,7 @@ __device__ void EpDispatchBody(const EpDispatchArgs &a)
                     }
                 }
             } else {
-                uint32_t m = routes;
+                uint32_t m = payloadRoutes;
                 while (m != 0) {
                     const int k = __ffs(m) - 1;
                     m &= m - 1;
@@ -500,6 +517,11 @@ __device__ void EpDispatchBody(const EpDispatchArgs &a)
                 st_vec16(reinterpret_cast<uint8_t *>(myHalf) + a.win.assistOff + static_cast<uint64_t>(myRow) * 16,
                          Vec16{static_cast<uint32_t>(rank), static_cast<uint32_t>(t), static_cast<uint32_t>(lane),
                                static_cast<uint32_t>(myExpert)});
+                const int64_t route = static_cast<int64_t>(t) * K + lane;
+                const float wgt = a.gateLogits != nullptr ? a.topkWeightsOut[route]
+                                                           : (a.expertScales != nullptr ? a.expertScales[route] : 1.0f);
+                *reinterpret_cast<uint2 *>(reinterpret_cast<uint8_t *>(myHalf) + a.win.extOff + static_cast<uint64_t>(myRow) * 8) =
+                    make_uint2(myLink, __float_as_uint(wgt));
             }
             __syncwarp();
         }
@@ -535,17 +557,36 @@ __device__ void EpDispatchBody(const EpDispatchArgs &a)
         const int64_t perBlock = (rows + G - 1) / G;
         const int64_t r0 = min(rows, perBlock * blockIdx.x);
         const int64_t n = min(rows - r0, perBlock);
-        if (n > 0) {
-            if (!a.zeroCopy) {
-                CopyLanes(a.expandXOut + r0 * a.win.rowBytes, myHalf + a.win.payloadOff + r0 * a.win.rowBytes,
-                          n * a.win.rowBytes, tid, blockDim.x);
+        // One warp per row: tuple and link go to the outputs; a head row also fills the rows of its followers.
+        const bool quantOut = a.quantMode == TileXREp::TILEXR_EP_QUANT_FP8_1X128 && a.dynamicScalesOut != nullptr;
+        const uint8_t *winPayload = myHalf + a.win.payloadOff;
+        const uint8_t *winScales = myHalf + a.win.scalesOff;
+        const uint8_t *winExt = myHalf + a.win.extOff;
+        for (int64_t r = r0 + warp; r < r0 + n; r += EP_WARPS) {
+            const uint2 ext = *reinterpret_cast<const uint2 *>(winExt + r * 8);
+            if (lane == 0) {
+                st_vec16(reinterpret_cast<uint8_t *>(a.assistOut) + r * 16, ld_vec16(myHalf + a.win.assistOff + r * 16));
+                if (a.assistExtOut != nullptr) *reinterpret_cast<uint2 *>(a.assistExtOut + r * 2) = ext;
+                if (a.expandScalesOut != nullptr) a.expandScalesOut[r] = __uint_as_float(ext.y);
             }
-            if (a.quantMode == TileXREp::TILEXR_EP_QUANT_FP8_1X128 && a.dynamicScalesOut != nullptr) {
-                CopyLanes(reinterpret_cast<uint8_t *>(a.dynamicScalesOut) + r0 * a.win.scaleRowBytes,
-                          myHalf + a.win.scalesOff + r0 * a.win.scaleRowBytes, n * a.win.scaleRowBytes, tid, blockDim.x);
+            if ((ext.x & EP_LINK_FOLLOWER) != 0) continue;
+            if (!a.zeroCopy) CopyLanes(a.expandXOut + r * a.win.rowBytes, winPayload + r * a.win.rowBytes, a.win.rowBytes, lane, 32);
+            if (quantOut) {
+                CopyLanes(reinterpret_cast<uint8_t *>(a.dynamicScalesOut) + r * a.win.scaleRowBytes, winScales + r * a.win.scaleRowBytes,
+                          a.win.scaleRowBytes, lane, 32);
             }
-            CopyLanes(reinterpret_cast<uint8_t *>(a.assistOut) + r0 * 16, myHalf + a.win.assistOff + r0 * 16, n * 16, tid,
-                      blockDim.x);
+            uint32_t next = a.dedup != 0 ? (ext.x & EP_LINK_NEXT_MASK) : 0;
+            for (int hop = 0; next != 0 && hop < K; ++hop) {
+                const int64_t f = static_cast<int64_t>(next) - 1;
+                if (f >= static_cast<int64_t>(a.maxRecvRows)) break;
+                const uint8_t *src = a.zeroCopy ? a.expandXOut + r * a.win.rowBytes : winPayload + r * a.win.rowBytes;
+                CopyLanes(a.expandXOut + f * a.win.rowBytes, src, a.win.rowBytes, lane, 32);
+                if (quantOut) {
+                    CopyLanes(reinterpret_cast<uint8_t *>(a.dynamicScalesOut) + f * a.win.scaleRowBytes,
+                              winScales + r * a.win.scaleRowBytes, a.win.scaleRowBytes, lane, 32);
+                }
+                next = reinterpret_cast<const uint2 *>(winExt + f * 8)->x & EP_LINK_NEXT_MASK;
+            }
         }
         if (blockIdx.x == 0) {
             // cumulative counts in (local expert, source) order: an inclusive scan of E_local * R numbers
@@ -620,8 +661,51 @@ __device__ void EpCombineBody(const EpCombineArgs &a)
                 const int64_t slot = static_cast<int64_t>(tuple.y) * K + tuple.z;
                 if (src < 0 || src >= comm->rankSize || slot < 0 || slot >= static_cast<int64_t>(a.bs) * K) continue;
                 if (direct && src == rank) continue;
+                uint2 ext = make_uint2(0u, 0u);
+                if (a.dedup != 0) ext = *reinterpret_cast<const uint2 *>(a.assistExt + r * 2);
+                if ((ext.x & EP_LINK_FOLLOWER) != 0) continue;      // summed into its group's head row
                 uint8_t *dst = DataHalf(comm, src, epoch) + slot * a.rowBytes;
-                CopyLanes(dst, a.expertOut + r * a.rowBytes, a.rowBytes, lane, 32);
+                if ((ext.x & EP_LINK_NEXT_MASK) == 0) {
+                    CopyLanes(dst, a.expertOut + r * a.rowBytes, a.rowBytes, lane, 32);
+                } else {
+                    // The rows of this token on this rank, in k order, times their gate weights: lane j keeps
+                    // member j of the chain, then every 16-byte column is summed in fp32 and rounded once.
+                    int64_t memberRow = -1;
+                    float memberW = 0.f;
+                    int members = 0;
+                    int64_t cur = r;
+                    uint2 e2 = ext;
+                    while (members < K) {
+                        if (lane == members) {
+                            memberRow = cur;
+                            memberW = __uint_as_float(e2.y);
+                        }
+                        ++members;
+                        const uint32_t next = e2.x & EP_LINK_NEXT_MASK;
+                        if (next == 0 || static_cast<int64_t>(next) - 1 >= rows) break;
+                        cur = static_cast<int64_t>(next) - 1;
+                        e2 = *reinterpret_cast<const uint2 *>(a.assistExt + cur * 2);
+                    }
+                    const int rowVecs = a.rowBytes / 16;
+                    for (int v0 = 0; v0 < rowVecs; v0 += 32) {
+                        const int v = v0 + lane;
+                        float acc[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+#pragma unroll 4
+                        for (int j = 0; j < members; ++j) {
+                            const int64_t mr = __shfl_sync(0xffffffffu, memberRow, j);
+                            const float mw = __shfl_sync(0xffffffffu, memberW, j);
+                            if (v < rowVecs) {
+                                float f[8];
+                                Unpack8(ld_vec16_stream(a.expertOut + mr * a.rowBytes + v * 16), bf16, f);
+#pragma unroll
+                                for (int i = 0; i < 8; ++i) acc[i] = fmaf(mw, f[i], acc[i]);
+                            }
+                        }
+                        if (v < rowVecs) st_vec16(dst + v * 16, Pack8(acc, bf16));
+                    }
+                }
                 if (lane == g) myFlag = FlagSlot(comm, src, TILEXR_FLAG_OP_BASE + slot);
             }
             __syncwarp();
@@ -642,6 +726,22 @@ __device__ void EpCombineBody(const EpCombineArgs &a)
                 if (a.maskType == TileXREp::TILEXR_EP_ACTIVE_MASK_TOKEN && a.activeMask[t] == 0) e = -1;
                 if (a.maskType == TileXREp::TILEXR_EP_ACTIVE_MASK_EXPERT && a.activeMask[t * K + lane] == 0) e = -1;
                 wk = a.expertScales != nullptr ? a.expertScales[t * K + lane] : 1.0f;
+            }
+            if (a.dedup != 0) {
+                // routes to one remote rank come back as one weighted sum in the slot of the lowest k
+                const int myDst = e >= 0 ? e / a.expertsPerRank : -1;
+                bool lower = false, higher = false;
+                for (int j = 0; j < K; ++j) {
+                    const int dj = __shfl_sync(0xffffffffu, myDst, j);
+                    if (dj >= 0 && dj == myDst && myDst != rank) {
+                        if (j < lane) lower = true;
+                        else if (j > lane) higher = true;
+                    }
+                }
+                if (lower) e = -1;
+                else if (higher) wk = 1.0f;
+            }
+            if (lane < K) {
                 if (e >= 0) {
                     const int64_t slot = t * K + lane;
                     const int64_t localRow = direct && e / a.expertsPerRank == rank ? a.routeRows[slot] : -1;

@@ -23,6 +23,7 @@ struct EpDispatchWindow {
     uint64_t payloadOff;      // [maxRecvRows][rowBytes]           (unused when zeroCopy)
     uint64_t scalesOff;       // [maxRecvRows][scaleRowBytes]
     uint64_t assistOff;       // [maxRecvRows][16]
+    uint64_t extOff;          // [maxRecvRows] 8 bytes: {link, gate weight} of each row
     uint64_t countOff;        // [rankSize][numExperts] int32: routes of source s for expert e; then [rankSize] int32:
                               // blocks of source s that will each raise one "rows sent" flag
     uint64_t blockCountOff;   // [grid][numExperts] int32, local scratch of the sender
@@ -60,6 +61,10 @@ struct EpDispatchArgs {
     uint64_t outOffset;
     void *perfTrace;                 // stage profiler buffer of this launch, or null
     int32_t *routeRowsOut;           // [bs, topK] destination row per route, or null
+    const float *expertScales;       // [bs, topK] gate weights when routing is not fused, or null
+    float *expandScalesOut;          // [maxRecvRows] or null
+    int32_t *assistExtOut;           // [maxRecvRows, 2] or null
+    uint32_t dedup;
 };
 
 struct EpCombineArgs {
@@ -80,7 +85,14 @@ struct EpCombineArgs {
     uint32_t sendCountEntries;
     void *perfTrace;
     const int32_t *routeRows;        // [bs, topK] from dispatch: local routes bypass the window; or null
+    const int32_t *assistExt;        // [rows, 2] {link, weight bits}
+    uint32_t dedup;
 };
+
+// link word of a row: bit 31 = the row is a follower (its payload is a copy of its group's head row);
+// low bits = 1 + the next row of the same (source, token) group on this rank, 0 at the end of the chain.
+constexpr uint32_t EP_LINK_FOLLOWER = 0x80000000u;
+constexpr uint32_t EP_LINK_NEXT_MASK = 0x7fffffffu;
 
 struct RoutingArgs {
     const float *gateLogits;

@@ -72,6 +72,16 @@ typedef struct TileXREpDispatchParams {
     int32_t *recvTotalOut;         // [1] rows received; may be null
     TXR_DT dtype;                  // dtype of x
     int32_t *routeRowsOut;         // [bs, topK] row of each route at its destination rank (-1 = inactive); may be null
+    // Gate weights travel with the rows (the reference's expertScales / expandScalesOut pair,
+    // src/include/tilexr_ep.h:47-52).  With fused routing the kernel's own weights are used and
+    // expertScales is ignored.
+    const float *expertScales;     // [bs, topK] fp32, or null
+    float *expandScalesOut;        // [maxRecvRows] weight of each received row, or null
+    // dedup != 0: a token with several experts on one REMOTE rank crosses NVLink once; the receiving rank
+    // copies the row to the other experts' positions.  Needs weights (fused routing or expertScales) and
+    // assistExtOut; the matching combine must get the same flag.
+    int64_t dedup;
+    int32_t *assistExtOut;         // [maxRecvRows, 2] {link, weight bits} for combine; needed when dedup != 0
 } TileXREpDispatchParams;
 
 typedef struct TileXREpCombineParams {
@@ -89,6 +99,10 @@ typedef struct TileXREpCombineParams {
     // [bs, topK] from dispatch, or null.  With it (and expertIds) the routes whose expert lives on this rank
     // are read straight from expertOut: they take no staging copy and no flag.
     const int32_t *routeRows;
+    // dedup != 0 (dispatch ran with dedup): the rows of one token on this rank are summed with their gate
+    // weights here and cross NVLink once; needs assistExt from dispatch and expertIds.
+    int64_t dedup;
+    const int32_t *assistExt;      // [rows, 2] from dispatch
 } TileXREpCombineParams;
 
 int TileXRMoeEpDispatchFused(const TileXREpDispatchParams *params, TileXRCommPtr comm, TileXRStream stream);

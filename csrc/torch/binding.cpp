@@ -352,14 +352,15 @@ py::dict CollectivePlan(int opType, int64_t count, at::ScalarType dtype, int ran
 const void *PtrOrNull(const c10::optional<at::Tensor> &t) { return t.has_value() && t->defined() ? t->data_ptr() : nullptr; }
 
 // Returns (expand_x, dynamic_scales|None, assist, expert_token_nums, send_counts, recv_total, topk_ids, topk_weights,
-// route_rows).
+// route_rows, assist_ext, expand_scales).
 py::tuple EpDispatch(const CommPtr &c, const at::Tensor &x, const c10::optional<at::Tensor> &expertIds,
                      const c10::optional<at::Tensor> &gateLogits, const c10::optional<at::Tensor> &selectionBias,
                      const c10::optional<at::Tensor> &activeMask, int64_t topK, int64_t numExperts, int64_t quantMode,
                      int64_t scoreFunc, bool renormalize, double routedScale, int64_t tokenNumsType, int64_t maxRecvRows,
-                     const c10::optional<at::Tensor> &expandXOut)
+                     const c10::optional<at::Tensor> &expandXOut, const c10::optional<at::Tensor> &expertScales, bool dedup)
 {
     RequireContiguous(x, "x");
+    Keep(expertScales);
     TORCH_CHECK(x.dim() == 2 && x.is_cuda(), "x must be a 2-D CUDA tensor");
     Keep(x);
     Keep(expertIds);
@@ -383,6 +384,8 @@ py::tuple EpDispatch(const CommPtr &c, const at::Tensor &x, const c10::optional<
     at::Tensor topkIds = at::empty({bs, topK}, i32);
     at::Tensor topkWeights = at::empty({bs, topK}, x.options().dtype(at::kFloat));
     at::Tensor routeRows = at::empty({bs, topK}, i32);
+    at::Tensor assistExt = at::empty({maxRecvRows, 2}, i32);
+    at::Tensor expandScales = at::empty({maxRecvRows}, x.options().dtype(at::kFloat));
     TileXREpDispatchParams p;
     std::memset(&p, 0, sizeof(p));
     p.x = x.data_ptr();
@@ -419,19 +422,31 @@ py::tuple EpDispatch(const CommPtr &c, const at::Tensor &x, const c10::optional<
     p.sendCountsOut = sendCounts.data_ptr<int32_t>();
     p.recvTotalOut = recvTotal.data_ptr<int32_t>();
     p.routeRowsOut = routeRows.data_ptr<int32_t>();
+    p.assistExtOut = assistExt.data_ptr<int32_t>();
+    p.expandScalesOut = expandScales.data_ptr<float>();
+    if (expertScales.has_value() && expertScales->defined()) {
+        TORCH_CHECK(expertScales->scalar_type() == at::kFloat && expertScales->is_contiguous() && expertScales->numel() == bs * topK,
+                    "expert_scales must be contiguous fp32 [bs, top_k]");
+        p.expertScales = expertScales->data_ptr<float>();
+    }
+    p.dedup = dedup ? 1 : 0;
     p.dtype = ToDtype(x.scalar_type());
-    for (const at::Tensor &t : {expandX, scales, assist, tokenNums, sendCounts, recvTotal, topkIds, topkWeights, routeRows}) Keep(t);
+    for (const at::Tensor &t : {expandX, scales, assist, tokenNums, sendCounts, recvTotal, topkIds, topkWeights, routeRows,
+                                assistExt, expandScales}) {
+        Keep(t);
+    }
     Check(TileXRMoeEpDispatchFused(&p, c->ptr(), StreamOf(x)), "TileXRMoeEpDispatchFused");
     return py::make_tuple(expandX, quant ? py::cast(scales) : py::none(), assist, tokenNums, sendCounts, recvTotal, topkIds,
-                          topkWeights, routeRows);
+                          topkWeights, routeRows, assistExt, expandScales);
 }
 
 at::Tensor EpCombine(const CommPtr &c, const at::Tensor &expertOut, const at::Tensor &assist, const at::Tensor &sendCounts,
                      const c10::optional<at::Tensor> &expertIds, const c10::optional<at::Tensor> &expertScales,
                      const c10::optional<at::Tensor> &activeMask, const c10::optional<at::Tensor> &sharedExpertX, int64_t bs,
                      int64_t topK, int64_t numExperts, const c10::optional<at::Tensor> &yOut,
-                     const c10::optional<at::Tensor> &routeRows)
+                     const c10::optional<at::Tensor> &routeRows, const c10::optional<at::Tensor> &assistExt, bool dedup)
 {
+    Keep(assistExt);
     RequireContiguous(expertOut, "expert_out");
     Keep(routeRows);
     TORCH_CHECK(expertOut.dim() == 2 && expertOut.is_cuda(), "expert_out must be a 2-D CUDA tensor");
@@ -461,6 +476,11 @@ at::Tensor EpCombine(const CommPtr &c, const at::Tensor &expertOut, const at::Te
                     "route_rows must be contiguous int32 [bs, top_k]");
         p.routeRows = routeRows->data_ptr<int32_t>();
     }
+    if (assistExt.has_value() && assistExt->defined()) {
+        TORCH_CHECK(assistExt->scalar_type() == at::kInt && assistExt->is_contiguous(), "assist_ext must be contiguous int32");
+        p.assistExt = assistExt->data_ptr<int32_t>();
+    }
+    p.dedup = dedup ? 1 : 0;
     p.bs = bs;
     p.h = h;
     p.topK = topK;
@@ -617,11 +637,13 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m)
           py::arg("gate_logits") = py::none(), py::arg("selection_bias") = py::none(), py::arg("active_mask") = py::none(),
           py::arg("top_k") = 1, py::arg("num_experts") = 1, py::arg("quant_mode") = 0, py::arg("score_func") = 0,
           py::arg("renormalize") = true, py::arg("routed_scale") = 1.0, py::arg("token_nums_type") = 1,
-          py::arg("max_recv_rows") = 0, py::arg("expand_x_out") = py::none());
+          py::arg("max_recv_rows") = 0, py::arg("expand_x_out") = py::none(), py::arg("expert_scales") = py::none(),
+          py::arg("dedup") = false);
     m.def("ep_combine", &EpCombine, py::arg("comm"), py::arg("expert_out"), py::arg("assist"), py::arg("send_counts"),
           py::arg("expert_ids") = py::none(), py::arg("expert_scales") = py::none(), py::arg("active_mask") = py::none(),
           py::arg("shared_expert_x") = py::none(), py::arg("bs") = 0, py::arg("top_k") = 1, py::arg("num_experts") = 1,
-          py::arg("y_out") = py::none(), py::arg("route_rows") = py::none());
+          py::arg("y_out") = py::none(), py::arg("route_rows") = py::none(), py::arg("assist_ext") = py::none(),
+          py::arg("dedup") = false);
     m.def("routing_topk", &RoutingTopK, py::arg("gate_logits"), py::arg("selection_bias") = py::none(), py::arg("top_k") = 1,
           py::arg("score_func") = 0, py::arg("renormalize") = true, py::arg("routed_scale") = 1.0);
     m.def("fp8_quant_1x128", &Fp8Quant);

@@ -76,7 +76,8 @@ def test_rmsnorm(txr, with_residual):
         assert torch.equal(res_dev.cpu(), rres)
 
 
-def _ep_case(txr, ranks, bs, h, experts, top_k, quant, fused_routing, masks=False, zero_copy=False, dtype=torch.bfloat16):
+def _ep_case(txr, ranks, bs, h, experts, top_k, quant, fused_routing, masks=False, zero_copy=False, dtype=torch.bfloat16,
+             dedup=None, scales_at_dispatch=False):
     from tilexr_b200.ops import ep
     from tilexr_b200.utils import oracle
 
@@ -96,7 +97,9 @@ def _ep_case(txr, ranks, bs, h, experts, top_k, quant, fused_routing, masks=Fals
         def call(c, r):
             kw = dict(num_experts=experts, top_k=top_k, quant_mode=ep.QUANT_FP8_1X128 if quant else ep.QUANT_NONE,
                       score_func=1, renormalize=True, max_recv_rows=max_rows, expand_x_out=outs[r],
-                      active_mask=None if mask is None else mask[r].cuda())
+                      active_mask=None if mask is None else mask[r].cuda(), dedup=dedup)
+            if scales_at_dispatch:
+                kw["expert_scales"] = ws[r].cuda()
             if fused_routing:
                 return ep.dispatch(c, xs[r].cuda(), gate_logits=logits[r].cuda(), **kw)
             return ep.dispatch(c, xs[r].cuda(), expert_ids=ids[r].cuda(), **kw)
@@ -111,6 +114,11 @@ def _ep_case(txr, ranks, bs, h, experts, top_k, quant, fused_routing, masks=Fals
         assert torch.equal(d.assist[:n].cpu(), ref[r]["assist"])
         assert torch.equal(d.expert_token_nums.cpu(), ref[r]["token_nums"])
         assert torch.equal(d.send_counts.cpu(), ref[r]["send_counts"])
+        if fused_routing or scales_at_dispatch:
+            # the gate weight of every received row travelled with it
+            a = ref[r]["assist"].long()
+            want_w = torch.stack([ws[int(s)][int(t), int(k)] for s, t, k, _ in a.tolist()]) if n else torch.empty(0)
+            assert torch.allclose(d.expand_scales[:n].cpu(), want_w, rtol=1e-5, atol=1e-7)
         if fused_routing:
             assert torch.equal(d.topk_ids.cpu(), ids[r])
             assert torch.allclose(d.topk_weights.cpu(), ws[r], rtol=1e-5, atol=1e-7)
@@ -161,6 +169,20 @@ def test_ep_zero_copy_output(txr):
 
 def test_ep_eight_ranks_fp16(txr):
     _ep_case(txr, ranks=8, bs=24, h=512, experts=64, top_k=8, quant=False, fused_routing=True, dtype=torch.float16)
+
+
+def test_ep_dedup_explicit_ids_with_scales(txr):
+    # top-8 over 2 ranks: nearly every token has several experts on the remote rank
+    _ep_case(txr, ranks=2, bs=40, h=512, experts=16, top_k=8, quant=True, fused_routing=False, scales_at_dispatch=True,
+             zero_copy=True)
+
+
+def test_ep_dedup_staged_output_and_masks(txr):
+    _ep_case(txr, ranks=4, bs=37, h=256, experts=32, top_k=6, quant=False, fused_routing=True, masks=True)
+
+
+def test_ep_dedup_off_matches(txr):
+    _ep_case(txr, ranks=4, bs=40, h=1024, experts=32, top_k=4, quant=True, fused_routing=True, dedup=False)
 
 
 def test_ep_overflow_is_reported_not_written(txr):

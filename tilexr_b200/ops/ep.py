@@ -29,26 +29,37 @@ class DispatchResult:
     topk_ids: torch.Tensor            # [bs, k] int32 (negative = inactive)
     topk_weights: torch.Tensor        # [bs, k] fp32 (only meaningful with fused routing)
     route_rows: torch.Tensor          # [bs, k] int32 row of each route at its destination rank (-1 = inactive)
+    assist_ext: torch.Tensor          # [max_recv_rows, 2] int32 {group link, gate weight bits} for combine
+    expand_scales: torch.Tensor       # [max_recv_rows] fp32 gate weight of each received row
     bs: int
     top_k: int
     num_experts: int
+    dedup: bool = False
 
 
 def dispatch(comm, x: torch.Tensor, *, num_experts: int, top_k: int, expert_ids: Optional[torch.Tensor] = None,
              gate_logits: Optional[torch.Tensor] = None, selection_bias: Optional[torch.Tensor] = None,
              active_mask: Optional[torch.Tensor] = None, quant_mode: int = QUANT_NONE, score_func: int = 0,
              renormalize: bool = True, routed_scale: float = 1.0, token_nums_type: int = TOKEN_NUMS_COUNT,
-             max_recv_rows: Optional[int] = None, expand_x_out: Optional[torch.Tensor] = None) -> DispatchResult:
+             max_recv_rows: Optional[int] = None, expand_x_out: Optional[torch.Tensor] = None,
+             expert_scales: Optional[torch.Tensor] = None, dedup: Optional[bool] = None) -> DispatchResult:
+    """``dedup`` (default: on when gate weights are known at dispatch time): a token with several experts on one
+    remote rank crosses NVLink once in each direction; the expert rank replicates it after arrival and sums
+    its outputs, gate-weighted in fp32, before sending them back.  The weights used for those sums are the ones
+    given here (fused routing or ``expert_scales``), so pass the same ones to ``combine``."""
     bs = x.shape[0]
+    if dedup is None:
+        dedup = gate_logits is not None or expert_scales is not None
     if max_recv_rows is None:
         max_recv_rows = bs * comm.world_size * min(top_k, num_experts // comm.world_size)
     out = _C.ep_dispatch(comm, x, expert_ids, gate_logits, selection_bias, active_mask, top_k, num_experts, quant_mode,
-                         score_func, renormalize, routed_scale, token_nums_type, max_recv_rows, expand_x_out)
-    return DispatchResult(*out, bs=bs, top_k=top_k, num_experts=num_experts)
+                         score_func, renormalize, routed_scale, token_nums_type, max_recv_rows, expand_x_out, expert_scales,
+                         bool(dedup))
+    return DispatchResult(*out, bs=bs, top_k=top_k, num_experts=num_experts, dedup=bool(dedup))
 
 
 def combine(comm, expert_out: torch.Tensor, d: DispatchResult, *, expert_scales: Optional[torch.Tensor] = None,
             active_mask: Optional[torch.Tensor] = None, shared_expert_x: Optional[torch.Tensor] = None,
             y_out: Optional[torch.Tensor] = None) -> torch.Tensor:
     return _C.ep_combine(comm, expert_out, d.assist, d.send_counts, d.topk_ids, expert_scales, active_mask, shared_expert_x,
-                         d.bs, d.top_k, d.num_experts, y_out, d.route_rows)
+                         d.bs, d.top_k, d.num_experts, y_out, d.route_rows, d.assist_ext, d.dedup)
