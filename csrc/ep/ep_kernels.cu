@@ -554,15 +554,14 @@ __device__ void EpDispatchBody(const EpDispatchArgs &a)
         const int firstLocal = rank * a.expertsPerRank;
         int64_t rows = 0;
         for (int e = firstLocal; e < firstLocal + a.expertsPerRank; ++e) rows += sm.total[e];
-        const int64_t perBlock = (rows + G - 1) / G;
-        const int64_t r0 = min(rows, perBlock * blockIdx.x);
-        const int64_t n = min(rows - r0, perBlock);
-        // One warp per row: tuple and link go to the outputs; a head row also fills the rows of its followers.
+        // One warp per row, rows dealt out round-robin over all warps of the grid (local, head and follower rows
+        // cost different amounts and come in runs): tuple and link go to the outputs; a head row also fills the
+        // rows of its followers.
         const bool quantOut = a.quantMode == TileXREp::TILEXR_EP_QUANT_FP8_1X128 && a.dynamicScalesOut != nullptr;
         const uint8_t *winPayload = myHalf + a.win.payloadOff;
         const uint8_t *winScales = myHalf + a.win.scalesOff;
         const uint8_t *winExt = myHalf + a.win.extOff;
-        for (int64_t r = r0 + warp; r < r0 + n; r += EP_WARPS) {
+        for (int64_t r = static_cast<int64_t>(blockIdx.x) * EP_WARPS + warp; r < rows; r += static_cast<int64_t>(G) * EP_WARPS) {
             const uint2 ext = *reinterpret_cast<const uint2 *>(winExt + r * 8);
             if (lane == 0) {
                 st_vec16(reinterpret_cast<uint8_t *>(a.assistOut) + r * 16, ld_vec16(myHalf + a.win.assistOff + r * 16));
@@ -645,25 +644,42 @@ __device__ void EpCombineBody(const EpCombineArgs &a)
         PerfStageBegin(perf, TILEXR_PERF_LOCAL_INPUT_TO_IPC);
         // ---- send every processed row back to slot (token, k) of its source ------------------------------
         const int64_t rows = a.sendCounts[a.sendCountEntries - 1];
-        // A warp copies a group of rows, then lanes 0..group-1 release one flag each with a single
-        // system-scope fence instruction for the whole group.
-        // Rows of this rank's own tokens stay where they are when the reducer knows their row (direct).
+        // Rows of this rank's own tokens stay where they are when the reducer knows their row (direct), and the
+        // followers of a group are summed into their head's row.  What is left differs a lot from row to row, so
+        // a block first compacts the rows of its stripes that need sending into a list, and its warps then take
+        // list entries in turn: every warp has work, whatever the mix of local, follower and head rows.
         const bool direct = a.routeRows != nullptr && a.expertIds != nullptr;
-        constexpr int kRowGroup = 4;
-        for (int64_t r0 = gwarp * kRowGroup; r0 < rows; r0 += nWarps * kRowGroup) {
-            uint64_t *myFlag = nullptr;
-#pragma unroll 1
-            for (int g = 0; g < kRowGroup; ++g) {
-                const int64_t r = r0 + g;
-                if (r >= rows) break;
+        __shared__ int32_t sUnit[EP_BLOCK_THREADS];
+        __shared__ int sUnitCount;
+        const int tid = threadIdx.x;
+        const int warp = tid >> 5;
+        const int64_t stripe = static_cast<int64_t>(gridDim.x) * 4;
+        for (int64_t base = 0;; base += EP_BLOCK_THREADS) {
+            if ((base >> 2) * stripe + static_cast<int64_t>(blockIdx.x) * 4 >= rows) break;      // block-uniform
+            if (tid == 0) sUnitCount = 0;
+            __syncthreads();
+            {
+                const int64_t li = base + tid;
+                const int64_t r = (li >> 2) * stripe + static_cast<int64_t>(blockIdx.x) * 4 + (li & 3);
+                if (r < rows) {
+                    const Vec16 tuple = ld_vec16(a.assist + r * 4);
+                    const int src = static_cast<int>(tuple.x);
+                    const int64_t slot = static_cast<int64_t>(tuple.y) * K + tuple.z;
+                    bool send = src >= 0 && src < comm->rankSize && slot >= 0 && slot < static_cast<int64_t>(a.bs) * K;
+                    if (direct && src == rank) send = false;
+                    if (send && a.dedup != 0 && (static_cast<uint32_t>(a.assistExt[r * 2]) & EP_LINK_FOLLOWER) != 0) send = false;
+                    if (send) sUnit[atomicAdd(&sUnitCount, 1)] = static_cast<int32_t>(r);
+                }
+            }
+            __syncthreads();
+            const int units = sUnitCount;
+            for (int u = warp; u < units; u += warpsPerBlock) {
+                const int64_t r = sUnit[u];
                 const Vec16 tuple = ld_vec16(a.assist + r * 4);
                 const int src = static_cast<int>(tuple.x);
                 const int64_t slot = static_cast<int64_t>(tuple.y) * K + tuple.z;
-                if (src < 0 || src >= comm->rankSize || slot < 0 || slot >= static_cast<int64_t>(a.bs) * K) continue;
-                if (direct && src == rank) continue;
                 uint2 ext = make_uint2(0u, 0u);
                 if (a.dedup != 0) ext = *reinterpret_cast<const uint2 *>(a.assistExt + r * 2);
-                if ((ext.x & EP_LINK_FOLLOWER) != 0) continue;      // summed into its group's head row
                 uint8_t *dst = DataHalf(comm, src, epoch) + slot * a.rowBytes;
                 if ((ext.x & EP_LINK_NEXT_MASK) == 0) {
                     CopyLanes(dst, a.expertOut + r * a.rowBytes, a.rowBytes, lane, 32);
@@ -687,29 +703,35 @@ __device__ void EpCombineBody(const EpCombineArgs &a)
                         e2 = *reinterpret_cast<const uint2 *>(a.assistExt + cur * 2);
                     }
                     const int rowVecs = a.rowBytes / 16;
-                    for (int v0 = 0; v0 < rowVecs; v0 += 32) {
-                        const int v = v0 + lane;
-                        float acc[8];
+                    for (int v0 = 0; v0 < rowVecs; v0 += 64) {        // two columns per lane: eight loads in flight
+                        const int va = v0 + lane, vb = v0 + 32 + lane;
+                        float accA[8], accB[8];
 #pragma unroll
-                        for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+                        for (int i = 0; i < 8; ++i) accA[i] = accB[i] = 0.f;
 #pragma unroll 4
                         for (int j = 0; j < members; ++j) {
                             const int64_t mr = __shfl_sync(0xffffffffu, memberRow, j);
                             const float mw = __shfl_sync(0xffffffffu, memberW, j);
-                            if (v < rowVecs) {
-                                float f[8];
-                                Unpack8(ld_vec16_stream(a.expertOut + mr * a.rowBytes + v * 16), bf16, f);
+                            const uint8_t *rowPtr = a.expertOut + mr * a.rowBytes;
+                            Vec16 qa = Vec16{0u, 0u, 0u, 0u}, qb = Vec16{0u, 0u, 0u, 0u};
+                            if (va < rowVecs) qa = ld_vec16_stream(rowPtr + va * 16);
+                            if (vb < rowVecs) qb = ld_vec16_stream(rowPtr + vb * 16);
+                            float f[8];
+                            Unpack8(qa, bf16, f);
 #pragma unroll
-                                for (int i = 0; i < 8; ++i) acc[i] = fmaf(mw, f[i], acc[i]);
-                            }
+                            for (int i = 0; i < 8; ++i) accA[i] = fmaf(mw, f[i], accA[i]);
+                            Unpack8(qb, bf16, f);
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) accB[i] = fmaf(mw, f[i], accB[i]);
                         }
-                        if (v < rowVecs) st_vec16(dst + v * 16, Pack8(acc, bf16));
+                        if (va < rowVecs) st_vec16(dst + va * 16, Pack8(accA, bf16));
+                        if (vb < rowVecs) st_vec16(dst + vb * 16, Pack8(accB, bf16));
                     }
                 }
-                if (lane == g) myFlag = FlagSlot(comm, src, TILEXR_FLAG_OP_BASE + slot);
+                __syncwarp();
+                if (lane == 0) SetFlag(FlagSlot(comm, src, TILEXR_FLAG_OP_BASE + slot), epoch, 1);
             }
-            __syncwarp();
-            if (myFlag != nullptr) SetFlag(myFlag, epoch, 1);
+            __syncthreads();
         }
         PerfStageEnd(perf, TILEXR_PERF_LOCAL_INPUT_TO_IPC);
         PerfStageBegin(perf, TILEXR_PERF_PEER_IPC_TO_OUTPUT);

@@ -213,7 +213,7 @@ __device__ void GemmBody(const GemmArgs &a)
         rank = a.comm->rank;
         ranks = a.comm->rankSize;
         if (blockIdx.x == 0 && threadIdx.x == 0) {
-            a.comm->dfx[TILEXR_DFX_MAGIC] = a.magic;
+            a.comm->dfx[TILEXR_DFX_MAGIC] = w.epoch;
             a.comm->dfx[TILEXR_DFX_OP] = a.mode == GEMM_ALL_GATHER ? TILEXR_OP_ALL_GATHER_MATMUL : TILEXR_OP_MATMUL_REDUCE_SCATTER;
             a.comm->dfx[TILEXR_DFX_RUN_STATUS] = TILEXR_RUN_STARTED;
         }

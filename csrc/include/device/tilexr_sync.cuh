@@ -49,11 +49,20 @@ struct Waiter {
     TXR_D bool ok() const { return status == TileXR::TILEXR_DEV_OK; }
 };
 
+// The epoch of a launch tags its flags.  On a GPU communicator it is kept on the device: every launch reads
+// the epoch of the rank's last finished launch from its own control block and uses the next one, and the
+// last block to leave stores it back (KernelEpilogue).  A launch therefore carries no per-call host state,
+// so a captured CUDA graph can replay it; all ranks stay in step because they issue the same launches.
+// Host-memory communicators (CPU plumbing) take the epoch from the host's magic counter.
 TXR_D Waiter MakeWaiter(CommArgs *args, int64_t magic, int block)
 {
     Waiter w;
     w.args = args;
-    w.epoch = static_cast<uint32_t>(magic);
+    if (args->extraFlag & TileXR::TILEXR_FLAG_HOST_MEMORY) {
+        w.epoch = static_cast<uint32_t>(magic);
+    } else {
+        w.epoch = static_cast<uint32_t>(ld_relaxed_sys_u64(CtrlWord(args, args->rank, TILEXR_CTRL_EPOCH_WORD))) + 1u;
+    }
     w.block = block;
     w.status = TileXR::TILEXR_DEV_OK;
     w.deadline = 0;
@@ -222,7 +231,7 @@ __device__ __forceinline__ bool KernelPrologue(Waiter &w, CommArgs *args, int64_
 {
     w = MakeWaiter(args, magic, blockIdx.x);
     if (blockIdx.x == 0 && threadIdx.x == 0) {
-        args->dfx[TileXR::TILEXR_DFX_MAGIC] = magic;
+        args->dfx[TileXR::TILEXR_DFX_MAGIC] = w.epoch;
         args->dfx[TileXR::TILEXR_DFX_OP] = op;
         args->dfx[TileXR::TILEXR_DFX_COUNT_ARG] = count;
         args->dfx[TileXR::TILEXR_DFX_RUN_STATUS] = TILEXR_RUN_STARTED;
@@ -248,6 +257,7 @@ __device__ __forceinline__ void KernelEpilogue(Waiter &w, bool ok)
         if (atom_add_acq_rel_gpu_u32(exitCounter, 1) == gridDim.x - 1) {
             st_release_gpu_u32(exitCounter, 0);
             PublishDone(w);
+            *CtrlWord(a, a->rank, TILEXR_CTRL_EPOCH_WORD) = w.epoch;
             if (a->dfx[TileXR::TILEXR_DFX_FAIL_CODE] == 0 && ok) {
                 a->dfx[TileXR::TILEXR_DFX_RUN_STATUS] = TILEXR_RUN_FINISHED;
             }

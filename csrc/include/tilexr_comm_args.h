@@ -37,6 +37,7 @@
 #define TILEXR_CTRL_ABORT_WORD        0          // epoch of a launch that gave up; peers write it
 #define TILEXR_CTRL_GRIDBAR_WORD      8          // 16 x {uint32 count, uint32 generation}
 #define TILEXR_CTRL_GRIDBAR_COUNT     16
+#define TILEXR_CTRL_EPOCH_WORD        32         // epoch of the rank's last finished launch (GPU communicators)
 #define TILEXR_CTRL_DONE_WORD         64         // doneEpoch[src], written by src at kernel end
 #define TILEXR_CTRL_SCRATCH_WORD      1024       // operator scratch (counts, cursors), 56 KiB
 #define TILEXR_CTRL_SCRATCH_WORDS     7168

@@ -62,6 +62,35 @@ def _worker(rank, world, port, q):
         # identity expert: y ~= sum_k w_k * dequant(quant(x)) ~= x
         err = (y.cpu().float() - tok[rank].float()).abs().max().item()
         assert err < 0.35, err
+        # The same step captured in a CUDA graph and replayed on fresh inputs: launches carry no per-call host
+        # state (epochs live on the device), so every replay is a new launch for the flag protocol.
+        x_static = tok[rank].cuda()
+        lg_static = logits[rank].cuda()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            def graph_step():
+                dd = ep.dispatch(comm, x_static, gate_logits=lg_static, num_experts=E, top_k=K,
+                                 quant_mode=ep.QUANT_FP8_1X128, score_func=1)
+                rr = txr.quant.fp8_dequant_1x128(dd.expand_x, dd.dynamic_scales, torch.bfloat16)
+                return ep.combine(comm, rr, dd, expert_scales=dd.topk_weights), txr.all_reduce(comm, x_static)
+            graph_step()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            y_static, ar_static = graph_step()
+        for it in range(3):
+            fresh = [torch.randn(bs, h, generator=gg).to(torch.bfloat16) for gg in gens]
+            x_static.copy_(fresh[rank])
+            g.replay()
+            torch.cuda.synchronize()
+            assert comm.device_status() == 0
+            assert (y_static.cpu().float() - fresh[rank].float()).abs().max().item() < 0.35
+            assert torch.equal(ar_static.cpu(), oracle.all_reduce_ref(fresh))
+        eager = txr.all_reduce(comm, x_static)          # eager launches keep working after replays
+        torch.cuda.synchronize()
+        assert torch.equal(eager.cpu(), ar_static.cpu())
         comm.destroy()
         q.put((rank, "ok"))
     except Exception:
