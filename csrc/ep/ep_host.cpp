@@ -91,8 +91,8 @@ int ValidateShape(int64_t bs, int64_t h, int64_t topK, int64_t moeExpertNum, int
         TILEXR_LOG(ERROR) << "EP: hidden size must be a multiple of 8 elements";
         return TILEXR_ERROR_PARA_CHECK_FAIL;
     }
-    if (bs * topK > TILEXR_FLAG_OP_SLOTS) {
-        TILEXR_LOG(ERROR) << "EP: bs*topK exceeds the " << TILEXR_FLAG_OP_SLOTS << " slot flags of a window";
+    if (bs * topK > TILEXR_FLAG_SLOT_SLOTS) {
+        TILEXR_LOG(ERROR) << "EP: bs*topK exceeds the " << TILEXR_FLAG_SLOT_SLOTS << " slot flags of a window";
         return TILEXR_ERROR_PARA_CHECK_FAIL;
     }
     return TILEXR_SUCCESS;
@@ -161,8 +161,13 @@ int TileXRMoeEpDispatchFused(const TileXREpDispatchParams *p, TileXRCommPtr comm
 
     // grid: one block per ~8 tokens per warp-set, capped by what can be co-resident
     const int ranksPerDevice = (c.hostArgs->extraFlag & TILEXR_FLAG_EMULATED) ? c.rankSize : 1;
-    const int64_t wantBlocks = std::max<int64_t>(1, std::min<int64_t>((p->bs + 15) / 16, EnvLong("TILEXR_EP_BLOCKS", 296)));
+    // At least minBlocks blocks even for a handful of tokens: the receive side of the kernel (rows from all
+    // ranks) and the column split of the send side both want the parallelism; blocks may own no token.
+    const int64_t capBlocks = std::min<int64_t>(EP_COUNT_FLAG_SLOT - 1, std::max<int64_t>(1, EnvLong("TILEXR_EP_BLOCKS", 296)));
+    const int64_t minBlocks = std::min<int64_t>(capBlocks, std::max<int64_t>(1, EnvLong("TILEXR_EP_MIN_BLOCKS", 32)));
+    const int64_t wantBlocks = std::max<int64_t>(minBlocks, std::min<int64_t>((p->bs + 15) / 16, capBlocks));
     unsigned grid = static_cast<unsigned>(wantBlocks);
+    unsigned gridCap = 0;
     uint32_t tokensPerBlock = 0;
     size_t smem = 0;
     for (;;) {
@@ -177,10 +182,11 @@ int TileXRMoeEpDispatchFused(const TileXREpDispatchParams *p, TileXRCommPtr comm
         ret = MaxCooperativeGrid(comm, EpDispatchKernelEntry(), EP_BLOCK_THREADS, smem, ranksPerDevice, &maxGrid);
         if (ret != TILEXR_SUCCESS) return ret;
         if (maxGrid == 0) return TILEXR_ERROR_NOT_SUPPORT;
+        gridCap = maxGrid;
         if (grid <= maxGrid) break;
         grid = maxGrid;
     }
-    grid = static_cast<unsigned>((p->bs + tokensPerBlock - 1) / tokensPerBlock);
+    grid = static_cast<unsigned>(std::max<int64_t>((p->bs + tokensPerBlock - 1) / tokensPerBlock, std::min<int64_t>(minBlocks, gridCap)));
 
     const size_t elemSize = TileXRDataTypeSize(p->dtype);
     const bool quant = p->quantMode == TILEXR_EP_QUANT_FP8_1X128;

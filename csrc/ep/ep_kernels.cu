@@ -409,9 +409,11 @@ __device__ void EpDispatchBody(const EpDispatchArgs &a)
         const bool quant = a.quantMode == TileXREp::TILEXR_EP_QUANT_FP8_1X128;
         const int chunks = a.h / 16;             // 16 elements per lane and iteration (fp8 path)
         const int iters = (chunks + 31) / 32;
-        float *stage = sm.scaleStage + warp * 64;
-        const int scaleVecs = a.win.scaleRowBytes / 16;
-        for (int i = warp; i < nTok; i += EP_WARPS) {
+        // A block with few tokens (small batches) cuts every token into column ranges for several warps.
+        const int parts = nTok > 0 ? max(1, min(min(8, iters), static_cast<int>(EP_WARPS) / nTok)) : 1;
+        for (int item = warp; item < nTok * parts; item += EP_WARPS) {
+            const int i = item / parts;
+            const int part = item % parts;
             const int t = t0 + i;
             const uint8_t *row = a.x + static_cast<int64_t>(t) * a.h * a.elemSize;
             // lane k owns route k of this token: where its row, scales and tuple go
@@ -433,7 +435,7 @@ __device__ void EpDispatchBody(const EpDispatchArgs &a)
                     myExpert = e;
                 }
             }
-            if (lane < K && a.routeRowsOut != nullptr) {
+            if (lane < K && a.routeRowsOut != nullptr && part == 0) {
                 a.routeRowsOut[static_cast<int64_t>(t) * K + lane] = myExpert >= 0 ? static_cast<int32_t>(myRow) : -1;
             }
             const uint32_t routes = __ballot_sync(0xffffffffu, myExpert >= 0);
@@ -459,7 +461,7 @@ __device__ void EpDispatchBody(const EpDispatchArgs &a)
                 // each 512-element chunk is quantised once and stored to every destination right away:
                 // nothing row-sized lives in registers, so two blocks fit on an SM
 #pragma unroll 2
-                for (int it = 0; it < iters; ++it) {
+                for (int it = part; it < iters; it += parts) {
                     const int c = it * 32 + lane;
                     float f[16];
                     if (c < chunks) {
@@ -478,7 +480,18 @@ __device__ void EpDispatchBody(const EpDispatchArgs &a)
                     amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
                     amax = fmaxf(amax, FP8_AMAX_FLOOR);
                     const float inv = FP8_E4M3_MAX / amax;
-                    if ((lane & 7) == 0 && c < chunks) stage[it * 4 + (lane >> 3)] = amax / FP8_E4M3_MAX;
+                    // the four scales of this iteration are 16 bytes of the scale row: lane k stores them for route k
+                    const float scale = amax / FP8_E4M3_MAX;
+                    Vec16 sv;
+                    sv.x = __float_as_uint(__shfl_sync(0xffffffffu, scale, 0));
+                    sv.y = __float_as_uint(__shfl_sync(0xffffffffu, scale, 8));
+                    sv.z = __float_as_uint(__shfl_sync(0xffffffffu, scale, 16));
+                    sv.w = __float_as_uint(__shfl_sync(0xffffffffu, scale, 24));
+                    if ((payloadRoutes >> lane) & 1u) {
+                        st_vec16(reinterpret_cast<uint8_t *>(myHalf) + a.win.scalesOff +
+                                     static_cast<uint64_t>(myRow) * a.win.scaleRowBytes + it * 16,
+                                 sv);
+                    }
                     Vec16 q;
                     q.x = Fp8x4(f[0] * inv, f[1] * inv, f[2] * inv, f[3] * inv);
                     q.y = Fp8x4(f[4] * inv, f[5] * inv, f[6] * inv, f[7] * inv);
@@ -492,28 +505,19 @@ __device__ void EpDispatchBody(const EpDispatchArgs &a)
                         if (c < chunks) st_vec16(p + static_cast<int64_t>(c) * 16, q);
                     }
                 }
-                __syncwarp();
-                uint32_t m = payloadRoutes;
-                while (m != 0) {
-                    const int k = __ffs(m) - 1;
-                    m &= m - 1;
-                    uint8_t *half = reinterpret_cast<uint8_t *>(__shfl_sync(0xffffffffu, myHalf, k));
-                    const uint32_t r = __shfl_sync(0xffffffffu, myRow, k);
-                    if (lane < scaleVecs) {
-                        st_vec16(half + a.win.scalesOff + static_cast<uint64_t>(r) * a.win.scaleRowBytes + lane * 16,
-                                 *reinterpret_cast<const Vec16 *>(stage + lane * 4));
-                    }
-                }
             } else {
+                const uint64_t perPart = ((a.win.rowBytes + parts - 1) / parts + 511) & ~511ull;
+                const uint64_t b0 = min(static_cast<uint64_t>(a.win.rowBytes), perPart * part);
+                const uint64_t nBytes = min(static_cast<uint64_t>(a.win.rowBytes) - b0, perPart);
                 uint32_t m = payloadRoutes;
                 while (m != 0) {
                     const int k = __ffs(m) - 1;
                     m &= m - 1;
                     uint8_t *p = reinterpret_cast<uint8_t *>(__shfl_sync(0xffffffffu, myPayload, k));
-                    CopyLanes(p, row, a.win.rowBytes, lane, 32);
+                    if (nBytes > 0) CopyLanes(p + b0, row + b0, nBytes, lane, 32);
                 }
             }
-            if (myExpert >= 0) {
+            if (myExpert >= 0 && part == 0) {
                 st_vec16(reinterpret_cast<uint8_t *>(myHalf) + a.win.assistOff + static_cast<uint64_t>(myRow) * 16,
                          Vec16{static_cast<uint32_t>(rank), static_cast<uint32_t>(t), static_cast<uint32_t>(lane),
                                static_cast<uint32_t>(myExpert)});
@@ -554,38 +558,67 @@ __device__ void EpDispatchBody(const EpDispatchArgs &a)
         const int firstLocal = rank * a.expertsPerRank;
         int64_t rows = 0;
         for (int e = firstLocal; e < firstLocal + a.expertsPerRank; ++e) rows += sm.total[e];
-        // One warp per row, rows dealt out round-robin over all warps of the grid (local, head and follower rows
-        // cost different amounts and come in runs): tuple and link go to the outputs; a head row also fills the
-        // rows of its followers.
+        // Rows are dealt out to blocks in chunks of one row per thread.  Per chunk: (a) a thread per row copies
+        // the tuple, link and weight and notes the head rows that have followers; (b) a thread per 16 bytes
+        // copies the scales of the rows that arrived with a payload; (c) without zero-copy a warp per row moves
+        // the payload out of the window; (d) warps take the noted head rows in turn and fill their followers.
         const bool quantOut = a.quantMode == TileXREp::TILEXR_EP_QUANT_FP8_1X128 && a.dynamicScalesOut != nullptr;
         const uint8_t *winPayload = myHalf + a.win.payloadOff;
         const uint8_t *winScales = myHalf + a.win.scalesOff;
         const uint8_t *winExt = myHalf + a.win.extOff;
-        for (int64_t r = static_cast<int64_t>(blockIdx.x) * EP_WARPS + warp; r < rows; r += static_cast<int64_t>(G) * EP_WARPS) {
-            const uint2 ext = *reinterpret_cast<const uint2 *>(winExt + r * 8);
-            if (lane == 0) {
+        __shared__ int32_t sHead[EP_BLOCK_THREADS];
+        __shared__ int sHeadCount;
+        const int scaleVecsPerRow = static_cast<int>(a.win.scaleRowBytes / 16);
+        // a chunk is as small as it takes to give every block rows (32 at least), and one row per thread at most
+        const int64_t chunk = min(static_cast<int64_t>(EP_BLOCK_THREADS), max(static_cast<int64_t>(32), static_cast<int64_t>(((rows + G - 1) / G + 31) & ~static_cast<int64_t>(31))));
+        for (int64_t base = static_cast<int64_t>(blockIdx.x) * chunk; base < rows; base += static_cast<int64_t>(G) * chunk) {
+            const int chunkRows = static_cast<int>(min(chunk, rows - base));
+            if (tid == 0) sHeadCount = 0;
+            __syncthreads();
+            if (tid < chunkRows) {
+                const int64_t r = base + tid;
+                const uint2 ext = *reinterpret_cast<const uint2 *>(winExt + r * 8);
                 st_vec16(reinterpret_cast<uint8_t *>(a.assistOut) + r * 16, ld_vec16(myHalf + a.win.assistOff + r * 16));
                 if (a.assistExtOut != nullptr) *reinterpret_cast<uint2 *>(a.assistExtOut + r * 2) = ext;
                 if (a.expandScalesOut != nullptr) a.expandScalesOut[r] = __uint_as_float(ext.y);
-            }
-            if ((ext.x & EP_LINK_FOLLOWER) != 0) continue;
-            if (!a.zeroCopy) CopyLanes(a.expandXOut + r * a.win.rowBytes, winPayload + r * a.win.rowBytes, a.win.rowBytes, lane, 32);
-            if (quantOut) {
-                CopyLanes(reinterpret_cast<uint8_t *>(a.dynamicScalesOut) + r * a.win.scaleRowBytes, winScales + r * a.win.scaleRowBytes,
-                          a.win.scaleRowBytes, lane, 32);
-            }
-            uint32_t next = a.dedup != 0 ? (ext.x & EP_LINK_NEXT_MASK) : 0;
-            for (int hop = 0; next != 0 && hop < K; ++hop) {
-                const int64_t f = static_cast<int64_t>(next) - 1;
-                if (f >= static_cast<int64_t>(a.maxRecvRows)) break;
-                const uint8_t *src = a.zeroCopy ? a.expandXOut + r * a.win.rowBytes : winPayload + r * a.win.rowBytes;
-                CopyLanes(a.expandXOut + f * a.win.rowBytes, src, a.win.rowBytes, lane, 32);
-                if (quantOut) {
-                    CopyLanes(reinterpret_cast<uint8_t *>(a.dynamicScalesOut) + f * a.win.scaleRowBytes,
-                              winScales + r * a.win.scaleRowBytes, a.win.scaleRowBytes, lane, 32);
+                if (a.dedup != 0 && (ext.x & EP_LINK_FOLLOWER) == 0 && (ext.x & EP_LINK_NEXT_MASK) != 0) {
+                    sHead[atomicAdd(&sHeadCount, 1)] = tid;
                 }
-                next = reinterpret_cast<const uint2 *>(winExt + f * 8)->x & EP_LINK_NEXT_MASK;
             }
+            if (quantOut) {
+                for (int idx = tid; idx < chunkRows * scaleVecsPerRow; idx += EP_BLOCK_THREADS) {
+                    const int64_t r = base + idx / scaleVecsPerRow;
+                    const int v = idx % scaleVecsPerRow;
+                    if ((reinterpret_cast<const uint2 *>(winExt + r * 8)->x & EP_LINK_FOLLOWER) != 0) continue;
+                    st_vec16(reinterpret_cast<uint8_t *>(a.dynamicScalesOut) + r * a.win.scaleRowBytes + v * 16,
+                             ld_vec16(winScales + r * a.win.scaleRowBytes + v * 16));
+                }
+            }
+            if (!a.zeroCopy) {
+                for (int i = warp; i < chunkRows; i += EP_WARPS) {
+                    const int64_t r = base + i;
+                    if ((reinterpret_cast<const uint2 *>(winExt + r * 8)->x & EP_LINK_FOLLOWER) != 0) continue;
+                    CopyLanes(a.expandXOut + r * a.win.rowBytes, winPayload + r * a.win.rowBytes, a.win.rowBytes, lane, 32);
+                }
+            }
+            __syncthreads();
+            const int heads = sHeadCount;
+            for (int u = warp; u < heads; u += EP_WARPS) {
+                const int64_t r = base + sHead[u];
+                const uint8_t *src = a.zeroCopy ? a.expandXOut + r * a.win.rowBytes : winPayload + r * a.win.rowBytes;
+                uint32_t next = reinterpret_cast<const uint2 *>(winExt + r * 8)->x & EP_LINK_NEXT_MASK;
+                for (int hop = 0; next != 0 && hop < K; ++hop) {
+                    const int64_t f = static_cast<int64_t>(next) - 1;
+                    if (f >= static_cast<int64_t>(a.maxRecvRows)) break;
+                    CopyLanes(a.expandXOut + f * a.win.rowBytes, src, a.win.rowBytes, lane, 32);
+                    if (quantOut) {
+                        CopyLanes(reinterpret_cast<uint8_t *>(a.dynamicScalesOut) + f * a.win.scaleRowBytes,
+                                  winScales + r * a.win.scaleRowBytes, a.win.scaleRowBytes, lane, 32);
+                    }
+                    next = reinterpret_cast<const uint2 *>(winExt + f * 8)->x & EP_LINK_NEXT_MASK;
+                }
+            }
+            __syncthreads();
         }
         if (blockIdx.x == 0) {
             // cumulative counts in (local expert, source) order: an inclusive scan of E_local * R numbers
@@ -673,8 +706,15 @@ __device__ void EpCombineBody(const EpCombineArgs &a)
             }
             __syncthreads();
             const int units = sUnitCount;
-            for (int u = warp; u < units; u += warpsPerBlock) {
-                const int64_t r = sUnit[u];
+            // With few rows to send (small batches) a row is cut into column ranges for several warps.
+            const int rowVecs = a.rowBytes / 16;
+            const int parts = units > 0 ? max(1, min(8, warpsPerBlock / units)) : 1;
+            const int perPart = (((rowVecs + parts - 1) / parts) + 31) & ~31;
+            for (int item = warp; item < units * parts; item += warpsPerBlock) {
+                const int64_t r = sUnit[item / parts];
+                const int vBegin = (item % parts) * perPart;
+                const int vEnd = min(rowVecs, vBegin + perPart);
+                if (vBegin >= vEnd) continue;
                 const Vec16 tuple = ld_vec16(a.assist + r * 4);
                 const int src = static_cast<int>(tuple.x);
                 const int64_t slot = static_cast<int64_t>(tuple.y) * K + tuple.z;
@@ -682,7 +722,8 @@ __device__ void EpCombineBody(const EpCombineArgs &a)
                 if (a.dedup != 0) ext = *reinterpret_cast<const uint2 *>(a.assistExt + r * 2);
                 uint8_t *dst = DataHalf(comm, src, epoch) + slot * a.rowBytes;
                 if ((ext.x & EP_LINK_NEXT_MASK) == 0) {
-                    CopyLanes(dst, a.expertOut + r * a.rowBytes, a.rowBytes, lane, 32);
+                    CopyLanes(dst + static_cast<int64_t>(vBegin) * 16, a.expertOut + r * a.rowBytes + static_cast<int64_t>(vBegin) * 16,
+                              static_cast<uint64_t>(vEnd - vBegin) * 16, lane, 32);
                 } else {
                     // The rows of this token on this rank, in k order, times their gate weights: lane j keeps
                     // member j of the chain, then every 16-byte column is summed in fp32 and rounded once.
@@ -702,8 +743,7 @@ __device__ void EpCombineBody(const EpCombineArgs &a)
                         cur = static_cast<int64_t>(next) - 1;
                         e2 = *reinterpret_cast<const uint2 *>(a.assistExt + cur * 2);
                     }
-                    const int rowVecs = a.rowBytes / 16;
-                    for (int v0 = 0; v0 < rowVecs; v0 += 64) {        // two columns per lane: eight loads in flight
+                    for (int v0 = vBegin; v0 < vEnd; v0 += 64) {        // two columns per lane: eight loads in flight
                         const int va = v0 + lane, vb = v0 + 32 + lane;
                         float accA[8], accB[8];
 #pragma unroll
@@ -714,8 +754,8 @@ __device__ void EpCombineBody(const EpCombineArgs &a)
                             const float mw = __shfl_sync(0xffffffffu, memberW, j);
                             const uint8_t *rowPtr = a.expertOut + mr * a.rowBytes;
                             Vec16 qa = Vec16{0u, 0u, 0u, 0u}, qb = Vec16{0u, 0u, 0u, 0u};
-                            if (va < rowVecs) qa = ld_vec16_stream(rowPtr + va * 16);
-                            if (vb < rowVecs) qb = ld_vec16_stream(rowPtr + vb * 16);
+                            if (va < vEnd) qa = ld_vec16_stream(rowPtr + va * 16);
+                            if (vb < vEnd) qb = ld_vec16_stream(rowPtr + vb * 16);
                             float f[8];
                             Unpack8(qa, bf16, f);
 #pragma unroll
@@ -724,14 +764,18 @@ __device__ void EpCombineBody(const EpCombineArgs &a)
 #pragma unroll
                             for (int i = 0; i < 8; ++i) accB[i] = fmaf(mw, f[i], accB[i]);
                         }
-                        if (va < rowVecs) st_vec16(dst + va * 16, Pack8(accA, bf16));
-                        if (vb < rowVecs) st_vec16(dst + vb * 16, Pack8(accB, bf16));
+                        if (va < vEnd) st_vec16(dst + va * 16, Pack8(accA, bf16));
+                        if (vb < vEnd) st_vec16(dst + vb * 16, Pack8(accB, bf16));
                     }
                 }
-                __syncwarp();
-                if (lane == 0) SetFlag(FlagSlot(comm, src, TILEXR_FLAG_OP_BASE + slot), epoch, 1);
             }
             __syncthreads();
+            // every part of a row is stored: one thread per row releases its flag
+            for (int u = tid; u < units; u += blockDim.x) {
+                const Vec16 tuple = ld_vec16(a.assist + static_cast<int64_t>(sUnit[u]) * 4);
+                const int64_t slot = static_cast<int64_t>(tuple.y) * K + tuple.z;
+                SetFlag(FlagSlot(comm, static_cast<int>(tuple.x), TILEXR_FLAG_SLOT_BASE + slot), epoch, 1);
+            }
         }
         PerfStageEnd(perf, TILEXR_PERF_LOCAL_INPUT_TO_IPC);
         PerfStageBegin(perf, TILEXR_PERF_PEER_IPC_TO_OUTPUT);
@@ -771,7 +815,7 @@ __device__ void EpCombineBody(const EpCombineArgs &a)
                         myRowPtr = reinterpret_cast<unsigned long long>(a.expertOut + localRow * a.rowBytes);
                     } else {
                         myRowPtr = reinterpret_cast<unsigned long long>(half + slot * a.rowBytes);
-                        WaitFlagGE(w, FlagSlot(comm, rank, TILEXR_FLAG_OP_BASE + slot), 1, e / a.expertsPerRank, slot);
+                        WaitFlagGE(w, FlagSlot(comm, rank, TILEXR_FLAG_SLOT_BASE + slot), 1, e / a.expertsPerRank, slot);
                     }
                 }
             }

@@ -268,7 +268,7 @@ int TileXRHostEpCombine(const float *expertOut, const int32_t *assist, int32_t r
     int ret = Begin(comm, TILEXR_OP_EP_COMBINE, bs, &c);
     if (ret != TILEXR_SUCCESS) return ret;
     const uint64_t rowBytes = static_cast<uint64_t>(h) * sizeof(float);
-    if (static_cast<uint64_t>(bs) * topK * rowBytes > c.args->dataHalfBytes || bs * topK > TILEXR_FLAG_OP_SLOTS) {
+    if (static_cast<uint64_t>(bs) * topK * rowBytes > c.args->dataHalfBytes || bs * topK > TILEXR_FLAG_SLOT_SLOTS) {
         return TILEXR_ERROR_PARA_CHECK_FAIL;
     }
     for (int32_t r = 0; r < rows; ++r) {
@@ -276,7 +276,7 @@ int TileXRHostEpCombine(const float *expertOut, const int32_t *assist, int32_t r
         const int64_t slot = static_cast<int64_t>(assist[r * 4 + 1]) * topK + assist[r * 4 + 2];
         if (src < 0 || src >= c.R || slot < 0 || slot >= bs * topK) continue;
         std::memcpy(DataHalf(c.args, src, c.epoch) + slot * rowBytes, expertOut + static_cast<int64_t>(r) * h, rowBytes);
-        if (!g_skipFlags) SetFlag(FlagSlot(c.args, src, TILEXR_FLAG_OP_BASE + slot), c.epoch, 1);
+        if (!g_skipFlags) SetFlag(FlagSlot(c.args, src, TILEXR_FLAG_SLOT_BASE + slot), c.epoch, 1);
     }
     const uint8_t *half = DataHalf(c.args, c.rank, c.epoch);
     for (int64_t t = 0; t < bs && c.w.ok(); ++t) {
@@ -286,7 +286,7 @@ int TileXRHostEpCombine(const float *expertOut, const int32_t *assist, int32_t r
             const int e = expertIds != nullptr ? expertIds[t * topK + k] : 0;
             if (e < 0 || e >= moeExpertNum) continue;
             const int64_t slot = t * topK + k;
-            if (!WaitFlagGE(c.w, FlagSlot(c.args, c.rank, TILEXR_FLAG_OP_BASE + slot), 1, -1, slot)) break;
+            if (!WaitFlagGE(c.w, FlagSlot(c.args, c.rank, TILEXR_FLAG_SLOT_BASE + slot), 1, -1, slot)) break;
             const float wgt = expertScales != nullptr ? expertScales[slot] : 1.0f;
             const float *row = reinterpret_cast<const float *>(half + slot * rowBytes);
             for (int64_t j = 0; j < h; ++j) y[j] = wgt * row[j] + y[j];

@@ -11,9 +11,9 @@
 //
 //   [0, 1 MiB)            control block: abort word, grid barriers, done-epoch table,
 //                         signal words (the "credit plane"), operator scratch
-//   [1 MiB, 4 MiB)        flag area: 64-bit flags `(epoch << 32) | value`, never reset
-//   [4 MiB, 4 MiB + D)    data half 0   \  launch with epoch m uses half (m & 1); the
-//   [.., 4 MiB + 2D)      data half 1   /  done-epoch table guards reuse at m + 2
+//   [1 MiB, 5 MiB)        flag area: 64-bit flags `(epoch << 32) | value`, never reset
+//   [5 MiB, 5 MiB + D)    data half 0   \  launch with epoch m uses half (m & 1); the
+//   [.., 5 MiB + 2D)      data half 1   /  done-epoch table guards reuse at m + 2
 #ifndef TILEXR_COMM_ARGS_H
 #define TILEXR_COMM_ARGS_H
 
@@ -29,8 +29,8 @@
 #define TILEXR_WIN_CTRL_OFFSET   0LL
 #define TILEXR_WIN_CTRL_BYTES    (1LL << 20)
 #define TILEXR_WIN_FLAG_OFFSET   (1LL << 20)
-#define TILEXR_WIN_FLAG_BYTES    (3LL << 20)
-#define TILEXR_WIN_DATA_OFFSET   (4LL << 20)
+#define TILEXR_WIN_FLAG_BYTES    (4LL << 20)
+#define TILEXR_WIN_DATA_OFFSET   (5LL << 20)
 #define TILEXR_TILE_BYTES        (256LL << 10)   // pipelining granule of the tiled collectives
 
 // Control block, in units of 64-bit words from the window base.
@@ -51,6 +51,12 @@
 #define TILEXR_FLAG_ACK_BASE          (TILEXR_MAX_RANK_SIZE * TILEXR_FLAGS_PER_PAIR)      // "tile consumed"
 #define TILEXR_FLAG_OP_BASE           (2 * TILEXR_MAX_RANK_SIZE * TILEXR_FLAGS_PER_PAIR)  // operator specific
 #define TILEXR_FLAG_OP_SLOTS          (TILEXR_MAX_RANK_SIZE * TILEXR_FLAGS_PER_PAIR)
+// Slots indexed by the RECEIVER's own numbering (token*topK + k of a combine), written by whichever rank
+// holds the row.  They get a plane of their own: in the planes above a slot belongs to one source, so a rank
+// that has moved on to its next launch can only overwrite flags it wrote itself; a receiver-indexed slot in
+// one of those planes could be hit by another rank's next launch before its real writer arrived.
+#define TILEXR_FLAG_SLOT_BASE         (3 * TILEXR_MAX_RANK_SIZE * TILEXR_FLAGS_PER_PAIR)
+#define TILEXR_FLAG_SLOT_SLOTS        (TILEXR_MAX_RANK_SIZE * TILEXR_FLAGS_PER_PAIR)
 
 #ifdef __cplusplus
 namespace TileXR {

@@ -365,7 +365,7 @@ static int LaunchCombine(TileXRCommPtr comm, const int32_t *dstLocal, const int3
     if (ret != TILEXR_MOONEP_SUCCESS) return ret;
     const size_t es = ElemSize(dtype);
     if (dstLocal == nullptr || hiddenNvsh == nullptr || hiddenSh == nullptr || es == 0 || dtype == TILEXR_MOONEP_DTYPE_INT32 || s <= 0 ||
-        k <= 0 || k > TILEXR_MOONEP_MAX_TOPK || nvS <= 0 || h <= 0 || (h * es) % 16 != 0 || s * k > TILEXR_FLAG_OP_SLOTS ||
+        k <= 0 || k > TILEXR_MOONEP_MAX_TOPK || nvS <= 0 || h <= 0 || (h * es) % 16 != 0 || s * k > TILEXR_FLAG_SLOT_SLOTS ||
         (weightsNvs == nullptr) != (weightsSk == nullptr)) {
         return TILEXR_MOONEP_ERROR_INVALID_ARGUMENT;
     }

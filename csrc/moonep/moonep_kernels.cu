@@ -296,14 +296,14 @@ __device__ void MoonCombineBody(const MoonCombineArgs &a)
             CopyLanes(peerHalf + route * a.rowBytes, a.hiddenNvs + s * a.rowBytes, a.rowBytes, lane, 32);
             if (lane == 0 && a.weightsNvs != nullptr) reinterpret_cast<float *>(peerHalf + a.weightWinOff)[route] = a.weightsNvs[s];
             __syncwarp();
-            if (lane == 0) SetFlag(FlagSlot(comm, src, TILEXR_FLAG_OP_BASE + route), epoch, 1);
+            if (lane == 0) SetFlag(FlagSlot(comm, src, TILEXR_FLAG_SLOT_BASE + route), epoch, 1);
         }
         const uint8_t *half = DataHalf(comm, rank, epoch);
         const int vecs = a.rowBytes / 16;
         for (int64_t t = gwarp; t < a.S && w.ok(); t += nWarps) {
             if (lane < K) {
                 const int64_t route = t * K + lane;
-                WaitFlagGE(w, FlagSlot(comm, rank, TILEXR_FLAG_OP_BASE + route), 1, -1, route);
+                WaitFlagGE(w, FlagSlot(comm, rank, TILEXR_FLAG_SLOT_BASE + route), 1, -1, route);
             }
             if (!__all_sync(0xffffffffu, w.ok())) {
                 if (w.ok()) w.status = TILEXR_DEV_ABORTED;
