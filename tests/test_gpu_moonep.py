@@ -146,3 +146,21 @@ def test_buffer_facade_single_rank(txr, port):
     assert torch.equal(again[0], rows)
     buf.destroy()
     comm.destroy()
+
+
+def test_harness_correctness_runner_single_rank(txr, port):
+    """The harness compares the library with the torch reference, artifact by artifact."""
+    from tilexr_b200.tools.moonep.contracts import MoonEPCase
+    from tilexr_b200.tools.moonep.correctness import CorrectnessRunner
+    from tilexr_b200.tools.moonep.tilexr_backend import TileXRBackend
+    from tilexr_b200.tools.moonep.torch_reference_backend import TorchReferenceBackend
+
+    comm = txr.init_process(0, 1, comm_id=f"127.0.0.1:{port}", buffer_mb=64, device=0)
+    backend = TileXRBackend(comm)
+    runner = CorrectnessRunner(TorchReferenceBackend(), backend)
+    for case in (MoonEPCase("r1_k2", 1, 32, 256, 2, 4, 2, token_padding=4, ffn=8, seed=3),
+                 MoonEPCase("r1_k4_fp16", 1, 24, 512, 4, 8, 8, token_padding=1, dtype="float16", seed=4)):
+        result = runner.run_case(case)
+        assert result["ok_all_ranks"], result
+    backend.close()
+    comm.destroy()

@@ -1,0 +1,170 @@
+"""MoonEP harness on the CPU: the torch reference backend over gloo, the correctness runner's verdicts, plan
+invariants, the HMAC completion barrier and the route capture format."""
+import dataclasses
+import threading
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from conftest import free_port
+
+
+def _gloo_worker(rank, world, port, q):
+    try:
+        dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+        from tilexr_b200.tools.moonep.case_factory import load_cases
+        from tilexr_b200.tools.moonep.correctness import CorrectnessRunner
+        from tilexr_b200.tools.moonep.torch_reference_backend import TorchReferenceBackend
+
+        case = [c for c in load_cases("smoke") if c.ranks == world][0]
+        ref = TorchReferenceBackend()
+
+        class Faulty(TorchReferenceBackend):
+            name = "faulty"
+
+            def run(self, case, inputs, expert_rows=None):
+                art = super().run(case, inputs)
+                if dist.get_rank() == 1:
+                    art.combined_hidden[3, 5] += 1.0          # one wrong element on one rank
+                return art
+
+        class Scribbler(TorchReferenceBackend):
+            name = "scribbler"
+
+            def run(self, case, inputs, expert_rows=None):
+                art = super().run(case, inputs)
+                inputs.hidden_sh[0, 0] += 1.0                 # a backend must not touch its inputs
+                return art
+
+        good = CorrectnessRunner(ref, TorchReferenceBackend()).run_case(case)
+        bad = CorrectnessRunner(ref, Faulty()).run_case(case)
+        scribble = CorrectnessRunner(ref, Scribbler()).run_case(case)
+        q.put((rank, good, bad, scribble))
+        dist.destroy_process_group()
+    except Exception:
+        import traceback
+
+        q.put((rank, traceback.format_exc(), None, None))
+
+
+def test_reference_backend_and_runner_verdicts_over_gloo():
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = free_port()
+    procs = [ctx.Process(target=_gloo_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = sorted((q.get(timeout=180) for _ in procs), key=lambda r: r[0])
+    for p in procs:
+        p.join(timeout=30)
+    for rank, good, bad, scribble in results:
+        assert isinstance(good, dict), good
+        assert good["ok"] and good["ok_all_ranks"]
+        assert not bad["ok_all_ranks"]                          # every rank learns that the case failed
+        failing = [s["stage"] for s in bad["stages"] if not s["ok"]]
+        assert failing == (["combined_hidden"] if rank == 1 else [])
+        assert [s["stage"] for s in scribble["stages"] if not s["ok"]] == ["inputs_immutable"]
+
+
+def test_plan_invariants_hold_for_reference_plans_and_catch_a_collision():
+    from tilexr_b200.tools.moonep.case_factory import load_cases, routing
+    from tilexr_b200.tools.moonep.planner_reference import check_plan_invariants, dst_local_from_plans, reference_plan
+
+    for case in load_cases("correctness"):
+        topk = [routing(case, r) for r in range(case.ranks)]
+        plans = [reference_plan(case, topk, r) for r in range(case.ranks)]
+        assert check_plan_invariants(case, plans) == [], case.name
+        for r in range(case.ranks):
+            dl = dst_local_from_plans(case, [p["dst"] for p in plans], r)
+            assert int((dl >= 0).sum()) <= case.nvs
+        total = sum(int((dst_local_from_plans(case, [p["dst"] for p in plans], r) >= 0).sum()) for r in range(case.ranks))
+        assert total == case.ranks * case.routes               # every route lands exactly once
+    case = load_cases("smoke")[0]
+    topk = [routing(case, r) for r in range(case.ranks)]
+    plans = [reference_plan(case, topk, r) for r in range(case.ranks)]
+    plans[1]["dst"] = plans[1]["dst"].clone()
+    plans[1]["dst"][1] = plans[1]["dst"][0]                     # two routes into one slot
+    assert any("used twice" in v for v in check_plan_invariants(case, plans))
+
+
+def test_ulp_distance_and_compare_policies():
+    from tilexr_b200.tools.moonep.correctness import compare, ulp_distance
+
+    a = torch.tensor([1.0, -2.0, 0.5], dtype=torch.bfloat16)
+    b = a.clone()
+    assert ulp_distance(a, b) == 0
+    b[0] = torch.nextafter(a[0].float(), torch.tensor(2.0)).to(torch.bfloat16) if False else torch.tensor(1.0078125, dtype=torch.bfloat16)
+    assert ulp_distance(a, b) == 1
+    assert compare("combined_hidden", a, b).ok                  # one ulp is within the policy
+    assert not compare("dispatched_hidden", a, b).ok            # copies must be bit-exact
+    b[0] = torch.tensor(1.015625, dtype=torch.bfloat16)
+    assert not compare("combined_hidden", a, b).ok
+    assert compare("prefetched_gate", None, None).ok and not compare("prefetched_gate", a, None).ok
+
+
+def test_completion_barrier_ignores_unauthenticated_frames():
+    import socket
+
+    from tilexr_b200.tools.moonep.rendezvous import completion_barrier
+
+    port = free_port()
+    world = 3
+    out = [None] * world
+
+    def run(rank):
+        out[rank] = completion_barrier(rank, world, "127.0.0.1", port, b"secret", "t1", timeout_s=20)
+
+    threads = [threading.Thread(target=run, args=(r,)) for r in range(world)]
+    threads[0].start()
+    # a stranger with the wrong key talks to the server first
+    for _ in range(100):
+        try:
+            with socket.create_connection(("127.0.0.1", port), timeout=0.2) as s:
+                s.sendall(b"\\x00\\x00\\x00\\x02{}" + b"0" * 32)
+            break
+        except OSError:
+            import time
+
+            time.sleep(0.05)
+    for t in threads[1:]:
+        t.start()
+    for t in threads:
+        t.join(timeout=30)
+    assert out == [True, True, True]
+    assert completion_barrier(1, 2, "127.0.0.1", free_port(), b"k", "nobody-listens", timeout_s=0.5) is False
+
+
+def test_route_capture_round_trip_and_compare(tmp_path):
+    from tilexr_b200.tools.moonep.model_replay import RouteRecorder, compare_replays, layer_case, load_meta
+
+    for rank in range(2):
+        rec = RouteRecorder(str(tmp_path), rank, ranks=2, experts=8, prefetch_slots=2, token_padding=4)
+        for layer in range(3):
+            rec.record(f"layers.{layer}.moe", torch.randint(0, 8, (16, 2)), hidden=128)
+        rec.save()
+    meta = load_meta(str(tmp_path))
+    assert [l["name"] for l in meta["layers"]] == ["layers.0.moe", "layers.1.moe", "layers.2.moe"]
+    case = layer_case(meta, meta["layers"][1])
+    assert (case.ranks, case.tokens, case.top_k, case.hidden, case.experts) == (2, 16, 2, 128, 8)
+    case.validate()
+    assert (tmp_path / "layer0002_rank1.pt").exists()
+    rows = compare_replays({"total_us": {"dispatch_fwd": 200.0}}, {"total_us": {"dispatch_fwd": 100.0}})
+    assert rows[0]["speedup_b_over_a"] == 2.0
+
+
+def test_expert_forward_matches_a_per_expert_loop():
+    from tilexr_b200.tools.moonep.expert_forward import expert_forward
+
+    g = torch.Generator().manual_seed(0)
+    rows = torch.randn(20, 32, generator=g)
+    gate, up, down = (torch.randn(3, 16, 32, generator=g) * 0.1 for _ in range(3))
+    cu = torch.tensor([5, 5, 14])                  # expert 1 got nothing; rows 14.. are padding
+    out = expert_forward(rows, cu, gate, up, down)
+    assert torch.all(out[14:] == 0)
+    for j, (s, e) in enumerate([(0, 5), (5, 5), (5, 14)]):
+        if e > s:
+            want = (torch.nn.functional.silu(rows[s:e] @ gate[j].t()) * (rows[s:e] @ up[j].t())) @ down[j]
+            assert torch.allclose(out[s:e], want, atol=1e-5)
