@@ -129,6 +129,27 @@ int TileXRMatmul(const void *a, const void *b, void *c, int64_t m, int64_t n, in
     int sms = 0;
     ret = SmCount(&sms);
     if (ret != TILEXR_SUCCESS) return ret;
+    if (m > GEMM_BM && EnvLong("TILEXR_GEMM_PAIR", 1) != 0) {
+        // CTA pairs on 256x256 tiles: each CTA loads half of the B tile (its own tensor map box of 128 rows)
+        ret = MakeMap(&g.tmapB, b, n, k, GEMM_BN / 2, bf16);
+        if (ret != TILEXR_SUCCESS) return ret;
+        const int pairTiles = static_cast<int>((m + 2 * GEMM_BM - 1) / (2 * GEMM_BM)) * g.nBlocks;
+        const int pairs = std::max(1, std::min<int>(pairTiles, static_cast<int>(EnvLong("TILEXR_GEMM_CTAS", sms)) / 2));
+        static std::once_flag pairOnce;
+        std::call_once(pairOnce, [] {
+            cudaFuncSetAttribute(GemmPairKernel(), cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(GEMM_PAIR_SMEM_BYTES));
+        });
+        void *pairParams[] = {&g};
+        const cudaError_t pe = cudaLaunchKernel(GemmPairKernel(), dim3(2 * pairs), dim3(GEMM_THREADS), pairParams,
+                                                GEMM_PAIR_SMEM_BYTES, static_cast<cudaStream_t>(stream));
+        if (pe != cudaSuccess) {
+            TILEXR_LOG(ERROR) << "matmul (CTA pairs) launch failed: " << cudaGetErrorString(pe);
+            cudaGetLastError();
+            return TILEXR_ERROR_RUNTIME;
+        }
+        NoteLaunch();
+        return TILEXR_SUCCESS;
+    }
     const int tiles = g.mBlocks * g.nBlocks;
     const unsigned grid = static_cast<unsigned>(std::max(1, std::min<int>(tiles, static_cast<int>(EnvLong("TILEXR_GEMM_CTAS", sms)))));
     static std::once_flag once;

@@ -1,0 +1,369 @@
+// bf16/fp16 GEMM on CTA pairs: tcgen05.mma with cta_group::2.
+//
+//   C[M,N] = A[M,K] x B[N,K]^T      (both operands K-major, fp32 accumulation, 16-bit output)
+//
+// Two CTAs of a cluster (one per SM of a pair) work on one 256x256 tile of C.  Each CTA stages its own
+// 128 rows of A and HALF of the B tile (128 of its 256 rows) per 64-wide K step, so a K step costs each SM
+// 32 KB of shared-memory fill instead of the 48 KB of the one-CTA kernel: the operand stream from L2, which
+// bounds that kernel, shrinks by a third, and the ring holds six stages instead of four.  The leader CTA
+// (cluster rank 0) issues every tcgen05.mma for the pair; the accumulator of each CTA's 128 rows lives in that
+// CTA's own tensor memory, 2 x 256 columns, so epilogue and main loop overlap.
+//
+// Roles per CTA (192 threads): warp 0 lane 0 issues TMA loads (cp.async.bulk.tensor with cta_group::2 and no
+// multicast: both CTAs signal the LEADER's "full" barrier); warp 1 owns tensor memory and, in the leader, issues
+// the MMAs and commits them to both CTAs' barriers; warps 2-5 read the accumulator with tcgen05.ld and store C.
+// Every mbarrier wait is bounded and checks the pair's abort flags; on a give-up all roles fall through to the
+// tear-down, both CTAs meet at the cluster barrier, tensor memory is released and `status` tells the host.
+//
+// The reference has no GEMM of its own (operators ALL_GATHER_MATMUL / MATMUL_REDUCE_SCATTER are named in
+// src/include/tilexr_types.h:108-125 without a kernel).
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "device/tilexr_rma.cuh"
+#include "gemm_kernels.cuh"
+#include "tilexr_types.h"
+
+namespace TileXR {
+
+using namespace tilexr;
+
+namespace {
+
+constexpr uint32_t TMEM_COLS = 512;
+constexpr uint32_t PEER_BIT_MASK = 0xFEFFFFFFu;   // clears the CTA-rank bit of a shared::cluster address: the leader's copy
+
+struct PairState {
+    uint64_t full[GEMM_PAIR_STAGES];       // used in the leader: both CTAs' loads of a stage have landed
+    uint64_t empty[GEMM_PAIR_STAGES];      // in each CTA: the MMAs that read this stage have finished
+    uint64_t tmemFull[2];                  // in each CTA: accumulator buffer complete
+    uint64_t tmemEmpty[2];                 // used in the leader: all eight epilogue warps of the pair drained it
+    uint32_t tmemBase;
+    volatile int abortFlag;
+};
+
+__device__ __forceinline__ uint32_t ClusterCtaRank()
+{
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+
+__device__ __forceinline__ void ClusterSync()
+{
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// Address of the same shared-memory object in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t MapToCta(uint32_t smemAddr, uint32_t rank)
+{
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smemAddr), "r"(rank));
+    return r;
+}
+
+__device__ __forceinline__ int LoadRemoteInt(uint32_t clusterAddr)
+{
+    int v;
+    asm volatile("ld.volatile.shared::cluster.s32 %0, [%1];" : "=r"(v) : "r"(clusterAddr) : "memory");
+    return v;
+}
+
+__device__ __forceinline__ void ArriveCluster(uint32_t clusterBarAddr)
+{
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(clusterBarAddr) : "memory");
+}
+
+// TMA load whose completion bytes are counted on the LEADER's barrier (no multicast: each CTA fetches its own box).
+__device__ __forceinline__ void TmaLoadPair2D(void *smemDst, const CUtensorMap *map, int x, int y, uint64_t *bar)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(SmemAddr(smemDst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(SmemAddr(bar) & PEER_BIT_MASK)
+        : "memory");
+}
+
+__device__ __forceinline__ void TcFenceBefore() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void TcFenceAfter() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// K-major tile written by TMA with 128-byte swizzle (see the one-CTA kernel for the field layout).
+__device__ __forceinline__ uint64_t MakeSmemDesc(uint32_t smemAddr)
+{
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((smemAddr & 0x3ffffu) >> 4);
+    d |= static_cast<uint64_t>(1) << 16;
+    d |= static_cast<uint64_t>(1024 >> 4) << 32;
+    d |= static_cast<uint64_t>(1) << 46;
+    d |= static_cast<uint64_t>(2) << 61;
+    return d;
+}
+
+// kind::f16, D fp32, A/B K-major; M = 256 rows over the pair, N = 256.
+__device__ __forceinline__ uint32_t MakeInstrDesc(bool bf16)
+{
+    const uint32_t fmt = bf16 ? 1u : 0u;
+    return (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(GEMM_BN >> 3) << 17) |
+           (static_cast<uint32_t>((2 * GEMM_BM) >> 4) << 24);
+}
+
+__device__ __forceinline__ void UmmaPairF16(uint32_t tmemD, uint64_t descA, uint64_t descB, uint32_t idesc, uint32_t accumulate)
+{
+    const uint32_t zero = 0;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n"
+        "}\n"
+        ::"r"(tmemD), "l"(descA), "l"(descB), "r"(idesc), "r"(accumulate), "r"(zero)
+        : "memory");
+}
+
+// Arrives on `bar` in BOTH CTAs of the pair once every MMA issued so far has finished.
+__device__ __forceinline__ void UmmaCommitPair(uint64_t *bar)
+{
+    const uint16_t mask = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(SmemAddr(bar)), "h"(mask) : "memory");
+}
+
+__device__ __forceinline__ void TmemLoad32(uint32_t taddr, uint32_t *r)
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void TmemLoadWait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Bounded mbarrier wait; gives up when the budget runs out or either CTA of the pair raised its abort flag.
+__device__ __forceinline__ bool WaitBar(uint64_t *bar, uint32_t parity, PairState *st, uint32_t peerAbortAddr, uint64_t budgetNs)
+{
+    if (MbarTryWait(bar, parity)) return true;
+    uint64_t deadline = 0;
+    uint32_t polls = 0;
+    for (;;) {
+        if (MbarTryWait(bar, parity)) return true;
+        if ((++polls & 127u) == 0) {
+            if (st->abortFlag != 0 || LoadRemoteInt(peerAbortAddr) != 0) {
+                st->abortFlag = 1;
+                return false;
+            }
+            const uint64_t t = now_ns();
+            if (deadline == 0) {
+                deadline = t + budgetNs;
+            } else if (t > deadline) {
+                st->abortFlag = 1;
+                return false;
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ uint32_t PackPair(float lo, float hi, bool bf16)
+{
+    if (bf16) {
+        const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+        return *reinterpret_cast<const uint32_t *>(&v);
+    }
+    const __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t *>(&v);
+}
+
+// Tile t of the pair's walk: 256-row blocks advance fastest inside a group of four, so pairs that run side by
+// side share a B tile and the group's A rows stay in L2.
+__device__ __forceinline__ void PairTileAt(int t, int mTiles, int nBlocks, int *mTile, int *nBlock)
+{
+    constexpr int GROUP = 4;
+    const int perGroup = GROUP * nBlocks;
+    const int group = t / perGroup;
+    const int first = group * GROUP;
+    const int size = min(GROUP, mTiles - first);
+    const int u = t - group * perGroup;
+    *mTile = first + u % size;
+    *nBlock = u / size;
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+TileXRGemmTcgen05Pair(const __grid_constant__ GemmArgs a)
+{
+    extern __shared__ uint8_t smemRaw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smemRaw) + 1023) & ~static_cast<uintptr_t>(1023));
+    uint8_t *stageBase = smem;
+    PairState *st = reinterpret_cast<PairState *>(smem + GEMM_PAIR_STAGES * GEMM_PAIR_STAGE_BYTES);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t ctaRank = ClusterCtaRank();
+    const bool leader = ctaRank == 0;
+    const uint64_t budgetNs = 4000000000ull;
+    const uint32_t peerAbortAddr = MapToCta(SmemAddr(const_cast<int *>(&st->abortFlag)), ctaRank ^ 1u);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < GEMM_PAIR_STAGES; ++s) {
+            MbarInit(&st->full[s], 1);        // the leader's TMA lane arms it with the bytes of both CTAs
+            MbarInit(&st->empty[s], 1);       // one commit from the leader's MMA lane
+        }
+        for (int i = 0; i < 2; ++i) {
+            MbarInit(&st->tmemFull[i], 1);    // one commit
+            MbarInit(&st->tmemEmpty[i], 8);   // four epilogue warps in each of the two CTAs
+        }
+        st->abortFlag = 0;
+        MbarInitFence();
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&a.tmapA)) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&a.tmapB)) : "memory");
+    }
+    __syncthreads();
+    if (warp == 1) {
+        // the same warp of both CTAs allocates for the pair; the address is the same in both
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(SmemAddr(&st->tmemBase)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    TcFenceBefore();
+    __syncthreads();
+    ClusterSync();          // both CTAs' barriers exist before anything arrives on them from the other CTA
+    TcFenceAfter();
+    const uint32_t tmemBase = st->tmemBase;
+
+    const int pair = static_cast<int>(blockIdx.x) >> 1;
+    const int nPairs = static_cast<int>(gridDim.x) >> 1;
+    const int mTiles = (a.M + 2 * GEMM_BM - 1) / (2 * GEMM_BM);
+    const int totalTiles = mTiles * a.nBlocks;
+    const bool bf16 = a.isBf16 != 0;
+
+    if (warp == 0) {
+        // ---- TMA producer: this CTA's 128 rows of A and its half of the B tile ---------------------------------
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            for (int t = pair; t < totalTiles && st->abortFlag == 0; t += nPairs) {
+                int mTile, nBlock;
+                PairTileAt(t, mTiles, a.nBlocks, &mTile, &nBlock);
+                const int rowA = mTile * 2 * GEMM_BM + static_cast<int>(ctaRank) * GEMM_BM;
+                const int rowB = nBlock * GEMM_BN + static_cast<int>(ctaRank) * (GEMM_BN / 2);
+                bool broke = false;
+                for (int kb = 0; kb < a.kBlocks; ++kb) {
+                    if (!WaitBar(&st->empty[stage], phase ^ 1u, st, peerAbortAddr, budgetNs)) {
+                        broke = true;
+                        break;
+                    }
+                    uint8_t *sa = stageBase + stage * GEMM_PAIR_STAGE_BYTES;
+                    uint8_t *sb = sa + GEMM_STAGE_A_BYTES;
+                    if (leader) MbarExpectTx(&st->full[stage], 2 * GEMM_PAIR_STAGE_BYTES);
+                    TmaLoadPair2D(sa, &a.tmapA, kb * GEMM_BK, rowA, &st->full[stage]);
+                    TmaLoadPair2D(sb, &a.tmapB, kb * GEMM_BK, rowB, &st->full[stage]);
+                    if (++stage == GEMM_PAIR_STAGES) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (broke) break;
+            }
+        }
+    } else if (warp == 1) {
+        // ---- MMA issuer: the leader's lane 0 drives the tensor cores of both SMs ---------------------------------
+        if (leader && lane == 0) {
+            const uint32_t idesc = MakeInstrDesc(bf16);
+            uint32_t stage = 0, phase = 0;
+            int iter = 0;
+            for (int t = pair; t < totalTiles && st->abortFlag == 0; t += nPairs, ++iter) {
+                const int acc = iter & 1;
+                const uint32_t accPhase = (iter >> 1) & 1;
+                if (!WaitBar(&st->tmemEmpty[acc], accPhase ^ 1u, st, peerAbortAddr, budgetNs)) break;
+                TcFenceAfter();
+                const uint32_t tmemD = tmemBase + static_cast<uint32_t>(acc) * GEMM_BN;
+                bool broke = false;
+                for (int kb = 0; kb < a.kBlocks; ++kb) {
+                    if (!WaitBar(&st->full[stage], phase, st, peerAbortAddr, budgetNs)) {
+                        broke = true;
+                        break;
+                    }
+                    TcFenceAfter();
+                    const uint32_t sa = SmemAddr(stageBase + stage * GEMM_PAIR_STAGE_BYTES);
+                    const uint64_t descA = MakeSmemDesc(sa);
+                    const uint64_t descB = MakeSmemDesc(sa + GEMM_STAGE_A_BYTES);
+#pragma unroll
+                    for (int k = 0; k < GEMM_BK / GEMM_UMMA_K; ++k) {
+                        UmmaPairF16(tmemD, descA + static_cast<uint64_t>(k * 2), descB + static_cast<uint64_t>(k * 2), idesc,
+                                    (kb | k) != 0 ? 1u : 0u);
+                    }
+                    UmmaCommitPair(&st->empty[stage]);    // both CTAs may refill the stage once these MMAs have read it
+                    if (++stage == GEMM_PAIR_STAGES) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (broke) break;
+                UmmaCommitPair(&st->tmemFull[acc]);
+            }
+        }
+    } else {
+        // ---- epilogue: warps 2..5 of each CTA own TMEM lanes 32*(warp%4) .. +31 = 32 of the CTA's 128 rows --------
+        const int quad = warp & 3;
+        const int rowInTile = static_cast<int>(ctaRank) * GEMM_BM + quad * 32 + lane;
+        int iter = 0;
+        for (int t = pair; t < totalTiles; t += nPairs, ++iter) {
+            int mTile, nBlock;
+            PairTileAt(t, mTiles, a.nBlocks, &mTile, &nBlock);
+            const int acc = iter & 1;
+            const uint32_t accPhase = (iter >> 1) & 1;
+            bool got = true;
+            if (lane == 0) got = WaitBar(&st->tmemFull[acc], accPhase, st, peerAbortAddr, budgetNs);
+            got = __shfl_sync(0xffffffffu, got ? 1 : 0, 0) != 0;
+            if (!got) break;
+            TcFenceAfter();
+            const int64_t row = static_cast<int64_t>(mTile) * 2 * GEMM_BM + rowInTile;
+            const bool rowValid = row < a.M;
+            uint8_t *dstRow = a.c + static_cast<uint64_t>(row) * a.N * 2;
+            const int col0 = nBlock * GEMM_BN;
+#pragma unroll 1
+            for (int c = 0; c < GEMM_BN / 32; ++c) {
+                uint32_t r[32];
+                const uint32_t taddr = tmemBase + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(acc * GEMM_BN + c * 32);
+                TmemLoad32(taddr, r);
+                TmemLoadWait();
+                const int col = col0 + c * 32;
+                if (rowValid && col < a.N) {
+                    uint32_t packed[16];
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) packed[j] = PackPair(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]), bf16);
+                    uint8_t *p = dstRow + static_cast<uint64_t>(col) * 2;
+                    if (col + 32 <= a.N) {
+#pragma unroll
+                        for (int v = 0; v < 4; ++v) st_vec16(p + v * 16, Vec16{packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]});
+                    } else {
+                        for (int j = 0; j < 32 && col + j < a.N; ++j) {
+                            reinterpret_cast<uint16_t *>(p)[j] = static_cast<uint16_t>(j & 1 ? packed[j >> 1] >> 16 : packed[j >> 1] & 0xffffu);
+                        }
+                    }
+                }
+            }
+            // this warp is done with the buffer: tell the leader's MMA lane
+            TcFenceBefore();
+            __syncwarp();
+            if (lane == 0) ArriveCluster(SmemAddr(&st->tmemEmpty[acc]) & PEER_BIT_MASK);
+        }
+    }
+
+    // ---- tear-down: nobody frees tensor memory while the other CTA's MMAs or loads may still target it -------------
+    TcFenceBefore();
+    __syncthreads();
+    ClusterSync();
+    TcFenceAfter();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmemBase), "r"(TMEM_COLS) : "memory");
+    }
+    if (st->abortFlag != 0 && threadIdx.x == 0 && a.status != nullptr) atomicExch(a.status, TILEXR_DEV_MBARRIER_TIMEOUT);
+}
+
+} // namespace
+
+const void *GemmPairKernel() { return reinterpret_cast<const void *>(&TileXRGemmTcgen05Pair); }
+
+} // namespace TileXR
