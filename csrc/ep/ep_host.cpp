@@ -30,9 +30,11 @@ bool DispatchLayout(int64_t h, int64_t numExperts, int64_t rankSize, int64_t max
                     int64_t elemSize, int64_t grid, bool zeroCopy, EpDispatchWindow *win)
 {
     if (h <= 0 || numExperts <= 0 || rankSize <= 0 || maxRecvRows <= 0 || grid <= 0) return false;
-    const bool quant = quantMode == TILEXR_EP_QUANT_FP8_1X128;
+    const bool mx = quantMode == TILEXR_EP_QUANT_MXFP8_E4M3 || quantMode == TILEXR_EP_QUANT_MXFP8_E5M2;
+    const bool quant = mx || quantMode == TILEXR_EP_QUANT_FP8_1X128;
     win->rowBytes = static_cast<uint32_t>(quant ? h : h * elemSize);
-    win->scaleRowBytes = quant ? static_cast<uint32_t>(h / 128 * 4) : 0;
+    // fp32 scale per 128 elements, or one E8M0 exponent byte per 32 elements
+    win->scaleRowBytes = mx ? static_cast<uint32_t>(h / 32) : quant ? static_cast<uint32_t>(h / 128 * 4) : 0;
     uint64_t off = 0;
     win->payloadOff = off;
     if (!zeroCopy) off = Align(off + static_cast<uint64_t>(maxRecvRows) * win->rowBytes, 256);
@@ -140,12 +142,14 @@ int TileXRMoeEpDispatchFused(const TileXREpDispatchParams *p, TileXRCommPtr comm
     }
     ret = ValidateShape(p->bs, p->h, p->topK, p->moeExpertNum, c.rankSize, p->dtype);
     if (ret != TILEXR_SUCCESS) return ret;
-    if (p->quantMode != TILEXR_EP_QUANT_NONE && p->quantMode != TILEXR_EP_QUANT_FP8_1X128) {
-        TILEXR_LOG(ERROR) << "EP dispatch: quantMode " << p->quantMode << " is not fused into dispatch (use NONE or FP8_1X128; "
-                          << "MXFP8 is available as TileXRMxfp8Quant)";
+    const bool fp8Mode = p->quantMode == TILEXR_EP_QUANT_FP8_1X128 || p->quantMode == TILEXR_EP_QUANT_MXFP8_E4M3 ||
+                         p->quantMode == TILEXR_EP_QUANT_MXFP8_E5M2;
+    if (p->quantMode != TILEXR_EP_QUANT_NONE && !fp8Mode) {
+        TILEXR_LOG(ERROR) << "EP dispatch: quantMode " << p->quantMode << " is not fused into dispatch (NONE, MXFP8 e4m3/e5m2 "
+                          << "and FP8_1X128 are)";
         return TILEXR_ERROR_NOT_SUPPORT;
     }
-    if (p->quantMode == TILEXR_EP_QUANT_FP8_1X128) {
+    if (fp8Mode) {
         if (p->dynamicScalesOut == nullptr || p->h % 512 != 0 || p->h > EP_FP8_MAX_H) {
             TILEXR_LOG(ERROR) << "EP dispatch: fp8 mode needs dynamicScalesOut and h a multiple of 512 up to " << EP_FP8_MAX_H;
             return TILEXR_ERROR_PARA_CHECK_FAIL;
@@ -189,7 +193,7 @@ int TileXRMoeEpDispatchFused(const TileXREpDispatchParams *p, TileXRCommPtr comm
     grid = static_cast<unsigned>(std::max<int64_t>((p->bs + tokensPerBlock - 1) / tokensPerBlock, std::min<int64_t>(minBlocks, gridCap)));
 
     const size_t elemSize = TileXRDataTypeSize(p->dtype);
-    const bool quant = p->quantMode == TILEXR_EP_QUANT_FP8_1X128;
+    const bool quant = fp8Mode;
     const uint64_t outBytes = static_cast<uint64_t>(p->maxRecvRows) * (quant ? p->h : p->h * elemSize);
     TileXRUDMAMemHandle handle = 0;
     uint64_t regionOffset = 0;
@@ -361,7 +365,13 @@ int TileXRMoeEpDispatchMemoryV2(void *x, int32_t *expertIds, void *scales, bool 
         TILEXR_LOG(ERROR) << "EP dispatch: globalBs must be bs * epWorldSize";
         return TILEXR_ERROR_PARA_CHECK_FAIL;
     }
-    if (quantMode != TILEXR_EP_QUANT_NONE && expandXOutDtype != TILEXR_DATA_TYPE_FP8E4M3) return TILEXR_ERROR_PARA_CHECK_FAIL;
+    if (quantMode != TILEXR_EP_QUANT_NONE) {
+        const TileXRDataType want = quantMode == TILEXR_EP_QUANT_MXFP8_E5M2 ? TILEXR_DATA_TYPE_FP8E5M2 : TILEXR_DATA_TYPE_FP8E4M3;
+        if (expandXOutDtype != want) {
+            TILEXR_LOG(ERROR) << "EP dispatch: quantMode " << quantMode << " writes " << (want == TILEXR_DATA_TYPE_FP8E5M2 ? "e5m2" : "e4m3");
+            return TILEXR_ERROR_PARA_CHECK_FAIL;
+        }
+    }
     TileXREpDispatchParams p;
     std::memset(&p, 0, sizeof(p));
     p.x = x;

@@ -100,6 +100,13 @@ __device__ __forceinline__ uint32_t Fp8x4(float a, float b, float c, float d)
     return lo | (hi << 16);
 }
 
+__device__ __forceinline__ uint32_t Fp8x4E5m2(float a, float b, float c, float d)
+{
+    const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E5M2);
+    const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E5M2);
+    return lo | (hi << 16);
+}
+
 // ---- routing: one warp scores one token and picks its top-k -------------------------------------------
 // Lane l owns experts l, l+32, ...  Selection is by score (+ optional bias), ties go to the
 // lower expert id; the gate weight is the unbiased score, optionally renormalised over the
@@ -406,8 +413,10 @@ __device__ void EpDispatchBody(const EpDispatchArgs &a)
     PerfStageBegin(perf, TILEXR_PERF_LOCAL_INPUT_TO_IPC);
     if (ok) {
         const bool bf16 = a.isBf16 != 0;
-        const bool quant = a.quantMode == TileXREp::TILEXR_EP_QUANT_FP8_1X128;
-        const int chunks = a.h / 16;             // 16 elements per lane and iteration (fp8 path)
+        const bool mx = a.quantMode == TileXREp::TILEXR_EP_QUANT_MXFP8_E4M3 || a.quantMode == TileXREp::TILEXR_EP_QUANT_MXFP8_E5M2;
+        const bool mxE5m2 = a.quantMode == TileXREp::TILEXR_EP_QUANT_MXFP8_E5M2;
+        const bool quant = mx || a.quantMode == TileXREp::TILEXR_EP_QUANT_FP8_1X128;
+        const int chunks = a.h / 16;             // 16 elements per lane and iteration (fp8 paths)
         const int iters = (chunks + 31) / 32;
         // A block with few tokens (small batches) cuts every token into column ranges for several warps.
         const int parts = nTok > 0 ? max(1, min(min(8, iters), static_cast<int>(EP_WARPS) / nTok)) : 1;
@@ -474,6 +483,52 @@ __device__ void EpDispatchBody(const EpDispatchArgs &a)
                     float amax = 0.f;
 #pragma unroll
                     for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(f[j]));
+                    if (mx) {
+                        // MXFP8: 32 elements = 2 lanes share the exponent 2^(floor(log2 amax) - emax); this
+                        // iteration's 16 exponent bytes are 16 bytes of the scale row
+                        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+                        const int emax = mxE5m2 ? 15 : 8;
+                        int ex = -127;
+                        if (amax > 0.f) {
+                            const uint32_t biased = (__float_as_uint(amax) >> 23) & 0xffu;
+                            ex = (biased == 0 ? -126 : static_cast<int>(biased) - 127) - emax;
+                        }
+                        ex = max(-127, min(127, ex));
+                        const float inv = exp2f(static_cast<float>(-ex));
+                        uint32_t word = (lane & 1) == 0 ? static_cast<uint32_t>(ex + 127) << (8 * ((lane >> 1) & 3)) : 0u;
+                        word |= __shfl_xor_sync(0xffffffffu, word, 2);
+                        word |= __shfl_xor_sync(0xffffffffu, word, 4);
+                        Vec16 sv;
+                        sv.x = __shfl_sync(0xffffffffu, word, 0);
+                        sv.y = __shfl_sync(0xffffffffu, word, 8);
+                        sv.z = __shfl_sync(0xffffffffu, word, 16);
+                        sv.w = __shfl_sync(0xffffffffu, word, 24);
+                        if ((payloadRoutes >> lane) & 1u) {
+                            st_vec16(reinterpret_cast<uint8_t *>(myHalf) + a.win.scalesOff +
+                                         static_cast<uint64_t>(myRow) * a.win.scaleRowBytes + it * 16,
+                                     sv);
+                        }
+                        Vec16 q;
+                        if (mxE5m2) {
+                            q.x = Fp8x4E5m2(f[0] * inv, f[1] * inv, f[2] * inv, f[3] * inv);
+                            q.y = Fp8x4E5m2(f[4] * inv, f[5] * inv, f[6] * inv, f[7] * inv);
+                            q.z = Fp8x4E5m2(f[8] * inv, f[9] * inv, f[10] * inv, f[11] * inv);
+                            q.w = Fp8x4E5m2(f[12] * inv, f[13] * inv, f[14] * inv, f[15] * inv);
+                        } else {
+                            q.x = Fp8x4(f[0] * inv, f[1] * inv, f[2] * inv, f[3] * inv);
+                            q.y = Fp8x4(f[4] * inv, f[5] * inv, f[6] * inv, f[7] * inv);
+                            q.z = Fp8x4(f[8] * inv, f[9] * inv, f[10] * inv, f[11] * inv);
+                            q.w = Fp8x4(f[12] * inv, f[13] * inv, f[14] * inv, f[15] * inv);
+                        }
+                        uint32_t m = payloadRoutes;
+                        while (m != 0) {
+                            const int k = __ffs(m) - 1;
+                            m &= m - 1;
+                            uint8_t *p = reinterpret_cast<uint8_t *>(__shfl_sync(0xffffffffu, myPayload, k));
+                            if (c < chunks) st_vec16(p + static_cast<int64_t>(c) * 16, q);
+                        }
+                        continue;
+                    }
                     // 128 elements = 8 consecutive lanes
                     amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
                     amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
@@ -562,7 +617,7 @@ __device__ void EpDispatchBody(const EpDispatchArgs &a)
         // the tuple, link and weight and notes the head rows that have followers; (b) a thread per 16 bytes
         // copies the scales of the rows that arrived with a payload; (c) without zero-copy a warp per row moves
         // the payload out of the window; (d) warps take the noted head rows in turn and fill their followers.
-        const bool quantOut = a.quantMode == TileXREp::TILEXR_EP_QUANT_FP8_1X128 && a.dynamicScalesOut != nullptr;
+        const bool quantOut = a.win.scaleRowBytes != 0 && a.dynamicScalesOut != nullptr;
         const uint8_t *winPayload = myHalf + a.win.payloadOff;
         const uint8_t *winScales = myHalf + a.win.scalesOff;
         const uint8_t *winExt = myHalf + a.win.extOff;

@@ -32,8 +32,8 @@ enum TileXREpQuantMode {
     TILEXR_EP_QUANT_NONE = 0,
     TILEXR_EP_QUANT_STATIC_INT8 = 1,     // reference MVP route only; not supported here
     TILEXR_EP_QUANT_DYNAMIC_INT8 = 2,    // reference MVP route only; not supported here
-    TILEXR_EP_QUANT_MXFP8_E5M2 = 3,      // 1x32 E8M0 scales (see TileXRMxfp8Quant)
-    TILEXR_EP_QUANT_MXFP8_E4M3 = 4,
+    TILEXR_EP_QUANT_MXFP8_E5M2 = 3,      // fused: 1x32 blocks with E8M0 exponent bytes (dynamicScalesOut is [rows, h/32] uint8)
+    TILEXR_EP_QUANT_MXFP8_E4M3 = 4,      // fused, the reference's production quantisation (quantMode 4)
     TILEXR_EP_QUANT_FP8_1X128 = 5,       // e4m3 with one fp32 scale per 128 elements
 };
 enum TileXREpScoreFunc { TILEXR_EP_SCORE_SOFTMAX = 0, TILEXR_EP_SCORE_SIGMOID = 1 };
@@ -65,7 +65,7 @@ typedef struct TileXREpDispatchParams {
     int32_t *topkIdsOut;           // [bs, topK]  (fused routing; may be null otherwise)
     float *topkWeightsOut;         // [bs, topK]  (fused routing)
     void *expandXOut;              // [maxRecvRows, h]
-    float *dynamicScalesOut;       // [maxRecvRows, h/128]
+    float *dynamicScalesOut;       // FP8_1X128: [maxRecvRows, h/128] fp32; MXFP8: [maxRecvRows, h/32] bytes behind this pointer
     int32_t *assistInfoForCombineOut;   // [maxRecvRows, 4]
     int64_t *expertTokenNumsOut;   // [moeExpertNum / R]
     int32_t *sendCountsOut;        // [moeExpertNum / R * R]

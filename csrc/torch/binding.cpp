@@ -371,12 +371,16 @@ py::tuple EpDispatch(const CommPtr &c, const at::Tensor &x, const c10::optional<
     const int R = c->rankSize();
     const int64_t localExperts = numExperts / R;
     auto i32 = x.options().dtype(at::kInt);
-    const bool quant = quantMode == TileXREp::TILEXR_EP_QUANT_FP8_1X128;
+    const bool mx = quantMode == TileXREp::TILEXR_EP_QUANT_MXFP8_E4M3 || quantMode == TileXREp::TILEXR_EP_QUANT_MXFP8_E5M2;
+    const bool quant = mx || quantMode == TileXREp::TILEXR_EP_QUANT_FP8_1X128;
+    const at::ScalarType qType = quantMode == TileXREp::TILEXR_EP_QUANT_MXFP8_E5M2 ? at::kFloat8_e5m2 : at::kFloat8_e4m3fn;
     at::Tensor expandX = expandXOut.has_value() && expandXOut->defined()
                              ? *expandXOut
-                             : at::empty({maxRecvRows, h}, x.options().dtype(quant ? at::kFloat8_e4m3fn : x.scalar_type()));
+                             : at::empty({maxRecvRows, h}, x.options().dtype(quant ? qType : x.scalar_type()));
     TORCH_CHECK(expandX.is_contiguous() && expandX.size(0) >= maxRecvRows && expandX.size(1) == h, "bad expand_x_out");
-    at::Tensor scales = quant ? at::empty({maxRecvRows, h / 128}, x.options().dtype(at::kFloat)) : at::Tensor();
+    at::Tensor scales = mx      ? at::empty({maxRecvRows, h / 32}, x.options().dtype(at::kByte))
+                        : quant ? at::empty({maxRecvRows, h / 128}, x.options().dtype(at::kFloat))
+                                : at::Tensor();
     at::Tensor assist = at::empty({maxRecvRows, 4}, i32);
     at::Tensor tokenNums = at::empty({localExperts}, x.options().dtype(at::kLong));
     at::Tensor sendCounts = at::empty({localExperts * R}, i32);
@@ -416,7 +420,7 @@ py::tuple EpDispatch(const CommPtr &c, const at::Tensor &x, const c10::optional<
     p.topkIdsOut = topkIds.data_ptr<int32_t>();
     p.topkWeightsOut = topkWeights.data_ptr<float>();
     p.expandXOut = expandX.data_ptr();
-    p.dynamicScalesOut = quant ? scales.data_ptr<float>() : nullptr;
+    p.dynamicScalesOut = quant ? static_cast<float *>(scales.data_ptr()) : nullptr;
     p.assistInfoForCombineOut = assist.data_ptr<int32_t>();
     p.expertTokenNumsOut = tokenNums.data_ptr<int64_t>();
     p.sendCountsOut = sendCounts.data_ptr<int32_t>();

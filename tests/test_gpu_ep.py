@@ -185,6 +185,36 @@ def test_ep_dedup_off_matches(txr):
     _ep_case(txr, ranks=4, bs=40, h=1024, experts=32, top_k=4, quant=True, fused_routing=True, dedup=False)
 
 
+@pytest.mark.parametrize("e5m2", [False, True])
+def test_ep_dispatch_fused_mxfp8(txr, e5m2):
+    """quantMode 3 / 4: rows arrive as MXFP8 with one E8M0 exponent byte per 32 elements, bit-exact vs the reference."""
+    from tilexr_b200.ops import ep
+    from tilexr_b200.utils import oracle
+
+    ranks, bs, h, experts, top_k = 4, 36, 1024, 16, 4
+    world = txr.init_emulated_world(ranks, device=0, buffer_mb=64)
+    g = torch.Generator().manual_seed(21)
+    xs = [(torch.randn(bs, h, generator=g) * (1 + 3 * torch.rand(bs, 1, generator=g))).to(torch.bfloat16) for _ in range(ranks)]
+    xs[0][0, :40] = 0                                  # an all-zero block
+    logits = [torch.randn(bs, experts, generator=g) for _ in range(ranks)]
+    ids = [oracle.routing_topk_ref(l, top_k, 1, True, 1.0)[0] for l in logits]
+    mode = ep.QUANT_MXFP8_E5M2 if e5m2 else ep.QUANT_MXFP8_E4M3
+    res = world.run(lambda c, r: ep.dispatch(c, xs[r].cuda(), gate_logits=logits[r].cuda(), num_experts=experts, top_k=top_k,
+                                             quant_mode=mode, score_func=1))
+    world.check()
+    ref = oracle.ep_dispatch_ref(xs, ids, experts, None)
+    for r in range(ranks):
+        d = res[r]
+        n = int(d.recv_total.item())
+        assert n == len(ref[r]["rows"]) and n > 0
+        assert d.expand_x.dtype == (torch.float8_e5m2 if e5m2 else torch.float8_e4m3fn)
+        assert d.dynamic_scales.dtype == torch.uint8 and tuple(d.dynamic_scales.shape[1:]) == (h // 32,)
+        rq, rs = oracle.mxfp8_quant_ref(ref[r]["expand_x"], e5m2)
+        assert torch.equal(d.expand_x[:n].cpu().view(torch.uint8), rq.view(torch.uint8))
+        assert torch.equal(d.dynamic_scales[:n].cpu(), rs)
+    world.destroy()
+
+
 def test_ep_overflow_is_reported_not_written(txr):
     from tilexr_b200.ops import ep
 

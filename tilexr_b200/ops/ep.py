@@ -13,6 +13,8 @@ import torch
 from .. import _C
 
 QUANT_NONE = 0
+QUANT_MXFP8_E5M2 = 3     # 1x32 blocks, E8M0 exponent bytes; dynamic_scales is uint8 [rows, h/32]
+QUANT_MXFP8_E4M3 = 4
 QUANT_FP8_1X128 = 5
 TOKEN_NUMS_PREFIX = 0
 TOKEN_NUMS_COUNT = 1
