@@ -180,17 +180,29 @@ static int FusedCommon(TileXRCommPtr comm, TileXRCommArgs **hostArgs, GM_ADDR *d
     return TILEXR_SUCCESS;
 }
 
-static int FusedGrid(TileXRCommPtr comm, const TileXRCommArgs *hostArgs, unsigned *grid)
+static const KernelEntry &GemmPairEntry()
+{
+    static const KernelEntry e = {GemmPairKernel(), GemmPairKernelEmulated(), sizeof(GemmArgs), "TileXRGemmTcgen05Pair"};
+    return e;
+}
+
+// The CTA-pair kernel serves a fused call when a pair's 256-row tile lies within one shard.
+static bool UsePairs(int64_t shardRows) { return shardRows % (2 * GEMM_BM) == 0 && EnvLong("TILEXR_GEMM_PAIR", 1) != 0; }
+
+static int FusedGrid(TileXRCommPtr comm, const TileXRCommArgs *hostArgs, unsigned *grid, bool pairs = false)
 {
     const int ranksPerDevice = (hostArgs->extraFlag & TILEXR_FLAG_EMULATED) ? hostArgs->rankSize : 1;
     unsigned maxGrid = 0;
-    int ret = MaxCooperativeGrid(comm, GemmEntry(), GEMM_THREADS, GEMM_SMEM_BYTES, ranksPerDevice, &maxGrid);
+    int ret = pairs ? MaxCooperativeGrid(comm, GemmPairEntry(), GEMM_THREADS, GEMM_PAIR_SMEM_BYTES, ranksPerDevice, &maxGrid)
+                    : MaxCooperativeGrid(comm, GemmEntry(), GEMM_THREADS, GEMM_SMEM_BYTES, ranksPerDevice, &maxGrid);
     if (ret != TILEXR_SUCCESS) return ret;
+    if (pairs) maxGrid &= ~1u;
     if (maxGrid < 2) {
         TILEXR_LOG(ERROR) << "fused GEMM needs at least two co-resident CTAs per rank";
         return TILEXR_ERROR_NOT_SUPPORT;
     }
     *grid = static_cast<unsigned>(std::min<long>(maxGrid, EnvLong("TILEXR_GEMM_CTAS", maxGrid)));
+    if (pairs) *grid &= ~1u;
     return TILEXR_SUCCESS;
 }
 
@@ -222,7 +234,8 @@ int TileXRAllGatherMatmul(const void *aShard, void *aStaging, const void *b, voi
     if (ret != TILEXR_SUCCESS) return ret;
     ret = MakeMap(&g.tmapALocal, aShard, shardRows, k, GEMM_BM, bf16);
     if (ret != TILEXR_SUCCESS) return ret;
-    ret = MakeMap(&g.tmapB, b, n, k, GEMM_BN, bf16);
+    const bool pairs = UsePairs(shardRows);
+    ret = MakeMap(&g.tmapB, b, n, k, pairs ? GEMM_BN / 2 : GEMM_BN, bf16);
     if (ret != TILEXR_SUCCESS) return ret;
     g.c = static_cast<uint8_t *>(c);
     g.aLocal = static_cast<const uint8_t *>(aShard);
@@ -243,13 +256,19 @@ int TileXRAllGatherMatmul(const void *aShard, void *aStaging, const void *b, voi
     g.stageHandle = handle;
     g.stageOffset = offset;
     unsigned grid = 0;
-    ret = FusedGrid(comm, hostArgs, &grid);
+    ret = FusedGrid(comm, hostArgs, &grid, pairs);
     if (ret != TILEXR_SUCCESS) return ret;
     g.commBlocks = R > 1 ? static_cast<uint32_t>(std::max<long>(1, std::min<long>(grid / 2, EnvLong("TILEXR_AG_GEMM_COMM_CTAS", std::max(2u, grid / 10))))) : 0;
     int64_t magic = 0;
     ret = TileXRCommNextMagic(comm, &magic);
     if (ret != TILEXR_SUCCESS) return ret;
     g.magic = magic;
+    if (pairs) {
+        g.commBlocks = (g.commBlocks + 1) & ~1u;          // whole pairs push, whole pairs compute
+        if (g.commBlocks + 2 > grid) g.commBlocks = grid > 2 ? (grid - 2) & ~1u : 0;
+        LaunchConfig pairCfg{grid, GEMM_THREADS, GEMM_PAIR_SMEM_BYTES, true};
+        return LaunchKernel(comm, GemmPairEntry(), &g, pairCfg, stream);
+    }
     LaunchConfig cfg{grid, GEMM_THREADS, GEMM_SMEM_BYTES, true};
     return LaunchKernel(comm, GemmEntry(), &g, cfg, stream);
 }
@@ -281,7 +300,8 @@ int TileXRMatmulReduceScatter(const void *a, const void *b, void *partialStaging
     ret = MakeMap(&g.tmapA, a, m, k, GEMM_BM, bf16);
     if (ret != TILEXR_SUCCESS) return ret;
     g.tmapALocal = g.tmapA;
-    ret = MakeMap(&g.tmapB, b, n, k, GEMM_BN, bf16);
+    const bool pairs = UsePairs(shardRows);
+    ret = MakeMap(&g.tmapB, b, n, k, pairs ? GEMM_BN / 2 : GEMM_BN, bf16);
     if (ret != TILEXR_SUCCESS) return ret;
     g.c = static_cast<uint8_t *>(out);
     g.comm = reinterpret_cast<CommArgs *>(devArgs);
@@ -298,12 +318,16 @@ int TileXRMatmulReduceScatter(const void *a, const void *b, void *partialStaging
     g.stageHandle = handle;
     g.stageOffset = offset;
     unsigned grid = 0;
-    ret = FusedGrid(comm, hostArgs, &grid);
+    ret = FusedGrid(comm, hostArgs, &grid, pairs);
     if (ret != TILEXR_SUCCESS) return ret;
     int64_t magic = 0;
     ret = TileXRCommNextMagic(comm, &magic);
     if (ret != TILEXR_SUCCESS) return ret;
     g.magic = magic;
+    if (pairs) {
+        LaunchConfig pairCfg{grid, GEMM_THREADS, GEMM_PAIR_SMEM_BYTES, true};
+        return LaunchKernel(comm, GemmPairEntry(), &g, pairCfg, stream);
+    }
     LaunchConfig cfg{grid, GEMM_THREADS, GEMM_SMEM_BYTES, true};
     return LaunchKernel(comm, GemmEntry(), &g, cfg, stream);
 }

@@ -58,6 +58,7 @@ struct GemmArgs {
 const void *GemmKernelSingle();
 const void *GemmKernelEmulated();
 const void *GemmPairKernel();
+const void *GemmPairKernelEmulated();
 
 } // namespace TileXR
 

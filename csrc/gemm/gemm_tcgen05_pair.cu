@@ -15,12 +15,19 @@
 // Every mbarrier wait is bounded and checks the pair's abort flags; on a give-up all roles fall through to the
 // tear-down, both CTAs meet at the cluster barrier, tensor memory is released and `status` tells the host.
 //
+// Fused modes work as in the one-CTA kernel (all-gather -> GEMM: leading CTA pairs only push this rank's A shard
+// to the peers' staging buffers, and each TMA lane acquires the flag of a remote 128-row piece before loading it
+// from LOCAL staging memory; GEMM -> reduce-scatter: every CTA's epilogue stores its 128x256 partial tile into
+// the row owner's staging slot and raises the tile's flag, then the epilogue warps sum the tiles this rank owns
+// in rank order).  They need shards of a multiple of 256 rows, so that a pair's tile lies within one shard.
+//
 // The reference has no GEMM of its own (operators ALL_GATHER_MATMUL / MATMUL_REDUCE_SCATTER are named in
 // src/include/tilexr_types.h:108-125 without a kernel).
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
 #include "device/tilexr_rma.cuh"
+#include "device/tilexr_sync.cuh"
 #include "gemm_kernels.cuh"
 #include "tilexr_types.h"
 
@@ -30,6 +37,8 @@ using namespace tilexr;
 
 namespace {
 
+constexpr int FLAG_PLANE_A = TILEXR_FLAG_DATA_BASE;
+constexpr int FLAG_PLANE_B = TILEXR_FLAG_ACK_BASE;
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t PEER_BIT_MASK = 0xFEFFFFFFu;   // clears the CTA-rank bit of a shared::cluster address: the leader's copy
 
@@ -191,8 +200,34 @@ __device__ __forceinline__ void PairTileAt(int t, int mTiles, int nBlocks, int *
     *nBlock = u / size;
 }
 
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
-TileXRGemmTcgen05Pair(const __grid_constant__ GemmArgs a)
+struct PairTile {
+    int mTile;      // 256-row block of the whole product
+    int nBlock;
+    int shard;      // owner / source rank of the rows (fused modes)
+    int mLocalPair; // 256-row block inside the shard
+};
+
+__device__ __forceinline__ PairTile TileOf(const GemmArgs &a, int t, int mTiles, int rank, int ranks)
+{
+    PairTile c;
+    if (a.mode == GEMM_PLAIN) {
+        PairTileAt(t, mTiles, a.nBlocks, &c.mTile, &c.nBlock);
+        c.shard = 0;
+        c.mLocalPair = c.mTile;
+    } else {
+        const int pairsPerShard = a.blocksPerShard / 2;
+        const int perShard = pairsPerShard * a.nBlocks;
+        const int i = t / perShard;
+        const int u = t - i * perShard;
+        c.shard = a.mode == GEMM_ALL_GATHER ? (rank + i) % ranks : (rank + 1 + i) % ranks;
+        c.mLocalPair = u % pairsPerShard;
+        c.nBlock = u / pairsPerShard;
+        c.mTile = c.shard * pairsPerShard + c.mLocalPair;
+    }
+    return c;
+}
+
+__device__ void PairBody(const GemmArgs &a)
 {
     extern __shared__ uint8_t smemRaw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smemRaw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -203,7 +238,62 @@ TileXRGemmTcgen05Pair(const __grid_constant__ GemmArgs a)
     const int lane = threadIdx.x & 31;
     const uint32_t ctaRank = ClusterCtaRank();
     const bool leader = ctaRank == 0;
-    const uint64_t budgetNs = 4000000000ull;
+    const bool fused = a.mode != GEMM_PLAIN;
+    Waiter w;
+    bool ok = true;
+    int rank = 0, ranks = 1;
+    if (fused) {
+        // The staging buffers are not double buffered: nobody may write into a peer's staging buffer before that
+        // peer finished the previous launch on this communicator.
+        w = MakeWaiter(a.comm, a.magic, blockIdx.x);
+        rank = a.comm->rank;
+        ranks = a.comm->rankSize;
+        if (blockIdx.x == 0 && threadIdx.x == 0) {
+            a.comm->dfx[TILEXR_DFX_MAGIC] = w.epoch;
+            a.comm->dfx[TILEXR_DFX_OP] = a.mode == GEMM_ALL_GATHER ? TILEXR_OP_ALL_GATHER_MATMUL : TILEXR_OP_MATMUL_REDUCE_SCATTER;
+            a.comm->dfx[TILEXR_DFX_RUN_STATUS] = TILEXR_RUN_STARTED;
+        }
+        bool g = true;
+        if (w.epoch >= 2 && static_cast<int>(threadIdx.x) < ranks && static_cast<int>(threadIdx.x) != rank) {
+            g = WaitPeerFinished(w, threadIdx.x, w.epoch - 1);
+        }
+        ok = BlockBroadcastOk(g);
+    }
+    const uint64_t budgetNs = fused ? a.comm->waitTimeoutNs : 4000000000ull;
+    const uint32_t epoch = fused ? w.epoch : 0;
+
+    // ---- all-gather: leading CTAs (whole pairs) only move data ------------------------------------------------
+    if (fused && a.mode == GEMM_ALL_GATHER && blockIdx.x < a.commBlocks) {
+        if (ok) {
+            const TileXRRegistry *reg = a.comm->registryPtr;
+            const int pieces = a.blocksPerShard * a.kChunks;
+            const int64_t items = static_cast<int64_t>(ranks - 1) * pieces;
+            const uint64_t rowBytes = static_cast<uint64_t>(a.K) * 2;
+            const uint64_t chunkBytes = static_cast<uint64_t>(a.kBlocksPerChunk) * GEMM_BK * 2;
+            for (int64_t it = blockIdx.x; it < items; it += a.commBlocks) {
+                const int peer = (rank - 1 - static_cast<int>(it / pieces) + 2 * ranks) % ranks;   // rank-1 needs it first
+                const int piece = static_cast<int>(it % pieces);
+                const int mLocal = piece / a.kChunks;
+                const int kc = piece % a.kChunks;
+                const uint64_t colOff = kc * chunkBytes;
+                const uint64_t n = min(chunkBytes, rowBytes > colOff ? rowBytes - colOff : 0);
+                uint8_t *dstBase = reg->regions[a.stageHandle].peerBase[peer] + a.stageOffset +
+                                   (static_cast<uint64_t>(rank) * a.shardRows + static_cast<uint64_t>(mLocal) * GEMM_BM) * rowBytes + colOff;
+                const uint8_t *srcBase = a.aLocal + static_cast<uint64_t>(mLocal) * GEMM_BM * rowBytes + colOff;
+                const int rows = min(GEMM_BM, a.shardRows - mLocal * GEMM_BM);
+                for (int r = warp; r < rows; r += GEMM_THREADS / 32) {
+                    CopyLanes(dstBase + r * rowBytes, srcBase + r * rowBytes, n, lane, 32);
+                }
+                __syncthreads();
+                if (threadIdx.x == 0) {
+                    SetFlag(FlagSlot(a.comm, peer, FLAG_PLANE_A + static_cast<int64_t>(rank) * a.flagStride + piece), epoch, 1);
+                }
+            }
+        }
+        KernelEpilogue(w, ok);
+        return;
+    }
+
     const uint32_t peerAbortAddr = MapToCta(SmemAddr(const_cast<int *>(&st->abortFlag)), ctaRank ^ 1u);
 
     if (threadIdx.x == 0) {
@@ -215,10 +305,11 @@ TileXRGemmTcgen05Pair(const __grid_constant__ GemmArgs a)
             MbarInit(&st->tmemFull[i], 1);    // one commit
             MbarInit(&st->tmemEmpty[i], 8);   // four epilogue warps in each of the two CTAs
         }
-        st->abortFlag = 0;
+        st->abortFlag = ok ? 0 : 1;
         MbarInitFence();
         asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&a.tmapA)) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&a.tmapB)) : "memory");
+        if (a.mode == GEMM_ALL_GATHER) asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&a.tmapALocal)) : "memory");
     }
     __syncthreads();
     if (warp == 1) {
@@ -232,8 +323,9 @@ TileXRGemmTcgen05Pair(const __grid_constant__ GemmArgs a)
     TcFenceAfter();
     const uint32_t tmemBase = st->tmemBase;
 
-    const int pair = static_cast<int>(blockIdx.x) >> 1;
-    const int nPairs = static_cast<int>(gridDim.x) >> 1;
+    const int firstCta = (fused && a.mode == GEMM_ALL_GATHER) ? static_cast<int>(a.commBlocks) : 0;
+    const int pair = (static_cast<int>(blockIdx.x) - firstCta) >> 1;
+    const int nPairs = (static_cast<int>(gridDim.x) - firstCta) >> 1;
     const int mTiles = (a.M + 2 * GEMM_BM - 1) / (2 * GEMM_BM);
     const int totalTiles = mTiles * a.nBlocks;
     const bool bf16 = a.isBf16 != 0;
@@ -243,20 +335,33 @@ TileXRGemmTcgen05Pair(const __grid_constant__ GemmArgs a)
         if (lane == 0) {
             uint32_t stage = 0, phase = 0;
             for (int t = pair; t < totalTiles && st->abortFlag == 0; t += nPairs) {
-                int mTile, nBlock;
-                PairTileAt(t, mTiles, a.nBlocks, &mTile, &nBlock);
-                const int rowA = mTile * 2 * GEMM_BM + static_cast<int>(ctaRank) * GEMM_BM;
-                const int rowB = nBlock * GEMM_BN + static_cast<int>(ctaRank) * (GEMM_BN / 2);
+                const PairTile tc = TileOf(a, t, mTiles, rank, ranks);
+                const int mLocal = tc.mLocalPair * 2 + static_cast<int>(ctaRank);        // this CTA's 128-row block in the shard
+                const bool remoteA = a.mode == GEMM_ALL_GATHER && tc.shard != rank;
+                const CUtensorMap *mapA = (a.mode == GEMM_ALL_GATHER && !remoteA) ? &a.tmapALocal : &a.tmapA;
+                const int rowA = (a.mode == GEMM_ALL_GATHER && !remoteA) ? mLocal * GEMM_BM
+                                                                         : tc.mTile * 2 * GEMM_BM + static_cast<int>(ctaRank) * GEMM_BM;
+                const int rowB = tc.nBlock * GEMM_BN + static_cast<int>(ctaRank) * (GEMM_BN / 2);
                 bool broke = false;
                 for (int kb = 0; kb < a.kBlocks; ++kb) {
                     if (!WaitBar(&st->empty[stage], phase ^ 1u, st, peerAbortAddr, budgetNs)) {
                         broke = true;
                         break;
                     }
+                    if (remoteA && kb % a.kBlocksPerChunk == 0) {
+                        const int piece = mLocal * a.kChunks + kb / a.kBlocksPerChunk;
+                        const int64_t slot = FLAG_PLANE_A + static_cast<int64_t>(tc.shard) * a.flagStride + piece;
+                        if (!WaitFlagGE(w, FlagSlot(a.comm, rank, slot), 1, tc.shard, slot)) {
+                            st->abortFlag = 1;
+                            broke = true;
+                            break;
+                        }
+                        fence_proxy_async();   // the rows were written by a peer's stores, TMA reads them next
+                    }
                     uint8_t *sa = stageBase + stage * GEMM_PAIR_STAGE_BYTES;
                     uint8_t *sb = sa + GEMM_STAGE_A_BYTES;
                     if (leader) MbarExpectTx(&st->full[stage], 2 * GEMM_PAIR_STAGE_BYTES);
-                    TmaLoadPair2D(sa, &a.tmapA, kb * GEMM_BK, rowA, &st->full[stage]);
+                    TmaLoadPair2D(sa, mapA, kb * GEMM_BK, rowA, &st->full[stage]);
                     TmaLoadPair2D(sb, &a.tmapB, kb * GEMM_BK, rowB, &st->full[stage]);
                     if (++stage == GEMM_PAIR_STAGES) {
                         stage = 0;
@@ -307,10 +412,11 @@ TileXRGemmTcgen05Pair(const __grid_constant__ GemmArgs a)
         // ---- epilogue: warps 2..5 of each CTA own TMEM lanes 32*(warp%4) .. +31 = 32 of the CTA's 128 rows --------
         const int quad = warp & 3;
         const int rowInTile = static_cast<int>(ctaRank) * GEMM_BM + quad * 32 + lane;
+        const TileXRRegistry *reg = fused ? a.comm->registryPtr : nullptr;
         int iter = 0;
         for (int t = pair; t < totalTiles; t += nPairs, ++iter) {
-            int mTile, nBlock;
-            PairTileAt(t, mTiles, a.nBlocks, &mTile, &nBlock);
+            const PairTile tc = TileOf(a, t, mTiles, rank, ranks);
+            const int mTile = tc.mTile, nBlock = tc.nBlock;
             const int acc = iter & 1;
             const uint32_t accPhase = (iter >> 1) & 1;
             bool got = true;
@@ -319,8 +425,14 @@ TileXRGemmTcgen05Pair(const __grid_constant__ GemmArgs a)
             if (!got) break;
             TcFenceAfter();
             const int64_t row = static_cast<int64_t>(mTile) * 2 * GEMM_BM + rowInTile;
-            const bool rowValid = row < a.M;
+            bool rowValid = row < a.M;
             uint8_t *dstRow = a.c + static_cast<uint64_t>(row) * a.N * 2;
+            if (a.mode == GEMM_REDUCE_SCATTER) {
+                const int64_t localRow = static_cast<int64_t>(tc.mLocalPair) * 2 * GEMM_BM + rowInTile;
+                rowValid = localRow < a.shardRows;
+                dstRow = reg->regions[a.stageHandle].peerBase[tc.shard] + a.stageOffset +
+                         (static_cast<uint64_t>(rank) * a.shardRows + static_cast<uint64_t>(localRow)) * a.N * 2;
+            }
             const int col0 = nBlock * GEMM_BN;
 #pragma unroll 1
             for (int c = 0; c < GEMM_BN / 32; ++c) {
@@ -348,6 +460,71 @@ TileXRGemmTcgen05Pair(const __grid_constant__ GemmArgs a)
             TcFenceBefore();
             __syncwarp();
             if (lane == 0) ArriveCluster(SmemAddr(&st->tmemEmpty[acc]) & PEER_BIT_MASK);
+            if (a.mode == GEMM_REDUCE_SCATTER) {
+                // this CTA's four epilogue warps have stored their rows of its 128x256 tile: announce it to the owner
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (warp == 2 && lane == 0) {
+                    const int tileLocal = (tc.mLocalPair * 2 + static_cast<int>(ctaRank)) * a.nBlocks + tc.nBlock;
+                    SetFlag(FlagSlot(a.comm, tc.shard, FLAG_PLANE_B + static_cast<int64_t>(rank) * a.flagStride + tileLocal), epoch, 1);
+                }
+            }
+        }
+        // ---- reduce-scatter: sum the 128x256 tiles this rank owns, in rank order -----------------------------------
+        if (a.mode == GEMM_REDUCE_SCATTER && st->abortFlag == 0) {
+            const int et = static_cast<int>(threadIdx.x) - 64;     // 0..127 among the epilogue threads
+            const int owned = a.blocksPerShard * a.nBlocks;
+            const uint8_t *stage = reg->regions[a.stageHandle].peerBase[rank] + a.stageOffset;
+            const uint64_t rowBytes = static_cast<uint64_t>(a.N) * 2;
+            __shared__ int sGot;
+            for (int tl = static_cast<int>(blockIdx.x); tl < owned; tl += static_cast<int>(gridDim.x)) {
+                bool got = true;
+                if (et < ranks) {
+                    const int64_t slot = FLAG_PLANE_B + static_cast<int64_t>(et) * a.flagStride + tl;
+                    got = WaitFlagGE(w, FlagSlot(a.comm, rank, slot), 1, et, slot);
+                }
+                if (et == 0) sGot = 1;
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (!got) sGot = 0;
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (sGot == 0) {
+                    st->abortFlag = 1;
+                    break;
+                }
+                const int mLocal = tl / a.nBlocks;
+                const int nBlock = tl % a.nBlocks;
+                const int rows = min(GEMM_BM, a.shardRows - mLocal * GEMM_BM);
+                const int cols = min(GEMM_BN, a.N - nBlock * GEMM_BN);
+                const int vecsPerRow = cols / 8;
+                for (int i = et; i < rows * vecsPerRow; i += 128) {
+                    const int r = i / vecsPerRow;
+                    const int v = i % vecsPerRow;
+                    const uint64_t off = (static_cast<uint64_t>(mLocal) * GEMM_BM + r) * rowBytes + (static_cast<uint64_t>(nBlock) * GEMM_BN + v * 8) * 2;
+                    float accv[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) accv[j] = 0.f;
+                    for (int s = 0; s < ranks; ++s) {
+                        const Vec16 x = ld_vec16_stream(stage + static_cast<uint64_t>(s) * a.shardRows * rowBytes + off);
+                        const uint32_t wds[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            float lo, hi;
+                            if (bf16) {
+                                lo = __uint_as_float(wds[j] << 16);
+                                hi = __uint_as_float(wds[j] & 0xffff0000u);
+                            } else {
+                                const float2 f2 = __half22float2(*reinterpret_cast<const __half2 *>(&wds[j]));
+                                lo = f2.x;
+                                hi = f2.y;
+                            }
+                            accv[2 * j] = s == 0 ? lo : accv[2 * j] + lo;
+                            accv[2 * j + 1] = s == 0 ? hi : accv[2 * j + 1] + hi;
+                        }
+                    }
+                    st_vec16(a.c + off, Vec16{PackPair(accv[0], accv[1], bf16), PackPair(accv[2], accv[3], bf16),
+                                              PackPair(accv[4], accv[5], bf16), PackPair(accv[6], accv[7], bf16)});
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");     // sGot is rewritten in the next round
+            }
         }
     }
 
@@ -359,11 +536,23 @@ TileXRGemmTcgen05Pair(const __grid_constant__ GemmArgs a)
     if (warp == 1) {
         asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmemBase), "r"(TMEM_COLS) : "memory");
     }
-    if (st->abortFlag != 0 && threadIdx.x == 0 && a.status != nullptr) atomicExch(a.status, TILEXR_DEV_MBARRIER_TIMEOUT);
+    const bool failed = st->abortFlag != 0;
+    if (failed && threadIdx.x == 0 && a.status != nullptr) atomicExch(a.status, TILEXR_DEV_MBARRIER_TIMEOUT);
+    if (fused) {
+        if (failed && threadIdx.x == 0 && w.ok()) RaiseFailure(w, TILEXR_DEV_MBARRIER_TIMEOUT, rank, blockIdx.x, 0, 0);
+        KernelEpilogue(w, !failed);
+    }
 }
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+TileXRGemmTcgen05Pair_single(const __grid_constant__ GemmArgs a) { PairBody(a); }
+// Emulated worlds: one argument block per rank in global memory, rank = blockIdx.y.
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+TileXRGemmTcgen05Pair_emulated(const GemmArgs *perRank) { PairBody(perRank[blockIdx.y]); }
 
 } // namespace
 
-const void *GemmPairKernel() { return reinterpret_cast<const void *>(&TileXRGemmTcgen05Pair); }
+const void *GemmPairKernel() { return reinterpret_cast<const void *>(&TileXRGemmTcgen05Pair_single); }
+const void *GemmPairKernelEmulated() { return reinterpret_cast<const void *>(&TileXRGemmTcgen05Pair_emulated); }
 
 } // namespace TileXR

@@ -39,7 +39,7 @@ def test_matmul(txr, m, n, k, dtype):
     _close(c, a.float() @ b.float().t(), k)
 
 
-@pytest.mark.parametrize("ranks,shard_rows,n,k", [(2, 128, 256, 256), (2, 256, 512, 1024), (4, 128, 768, 512)])
+@pytest.mark.parametrize("ranks,shard_rows,n,k", [(2, 128, 256, 256), (2, 256, 512, 1024), (4, 128, 768, 512), (4, 512, 1024, 512)])
 def test_all_gather_matmul(txr, ranks, shard_rows, n, k):
     world = txr.init_emulated_world(ranks, device=0, buffer_mb=16)
     g = torch.Generator().manual_seed(7)
@@ -55,7 +55,7 @@ def test_all_gather_matmul(txr, ranks, shard_rows, n, k):
     world.destroy()
 
 
-@pytest.mark.parametrize("ranks,shard_rows,n,k", [(2, 128, 256, 128), (2, 256, 512, 512), (4, 128, 512, 256)])
+@pytest.mark.parametrize("ranks,shard_rows,n,k", [(2, 128, 256, 128), (2, 256, 512, 512), (4, 128, 512, 256), (4, 512, 1024, 768)])
 def test_matmul_reduce_scatter(txr, ranks, shard_rows, n, k):
     world = txr.init_emulated_world(ranks, device=0, buffer_mb=16)
     g = torch.Generator().manual_seed(9)
