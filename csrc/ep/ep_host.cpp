@@ -31,10 +31,13 @@ bool DispatchLayout(int64_t h, int64_t numExperts, int64_t rankSize, int64_t max
 {
     if (h <= 0 || numExperts <= 0 || rankSize <= 0 || maxRecvRows <= 0 || grid <= 0) return false;
     const bool mx = quantMode == TILEXR_EP_QUANT_MXFP8_E4M3 || quantMode == TILEXR_EP_QUANT_MXFP8_E5M2;
-    const bool quant = mx || quantMode == TILEXR_EP_QUANT_FP8_1X128;
+    const bool int8 = quantMode == TILEXR_EP_QUANT_STATIC_INT8 || quantMode == TILEXR_EP_QUANT_DYNAMIC_INT8;
+    const bool quant = mx || int8 || quantMode == TILEXR_EP_QUANT_FP8_1X128;
     win->rowBytes = static_cast<uint32_t>(quant ? h : h * elemSize);
-    // fp32 scale per 128 elements, or one E8M0 exponent byte per 32 elements
-    win->scaleRowBytes = mx ? static_cast<uint32_t>(h / 32) : quant ? static_cast<uint32_t>(h / 128 * 4) : 0;
+    // fp32 scale per 128 elements, one E8M0 exponent byte per 32 elements, or one fp32 per row (in a 16-byte cell)
+    win->scaleRowBytes = mx ? static_cast<uint32_t>(h / 32)
+                         : quantMode == TILEXR_EP_QUANT_DYNAMIC_INT8 ? 16u
+                         : quantMode == TILEXR_EP_QUANT_FP8_1X128 ? static_cast<uint32_t>(h / 128 * 4) : 0u;
     uint64_t off = 0;
     win->payloadOff = off;
     if (!zeroCopy) off = Align(off + static_cast<uint64_t>(maxRecvRows) * win->rowBytes, 256);
@@ -144,10 +147,17 @@ int TileXRMoeEpDispatchFused(const TileXREpDispatchParams *p, TileXRCommPtr comm
     if (ret != TILEXR_SUCCESS) return ret;
     const bool fp8Mode = p->quantMode == TILEXR_EP_QUANT_FP8_1X128 || p->quantMode == TILEXR_EP_QUANT_MXFP8_E4M3 ||
                          p->quantMode == TILEXR_EP_QUANT_MXFP8_E5M2;
-    if (p->quantMode != TILEXR_EP_QUANT_NONE && !fp8Mode) {
-        TILEXR_LOG(ERROR) << "EP dispatch: quantMode " << p->quantMode << " is not fused into dispatch (NONE, MXFP8 e4m3/e5m2 "
-                          << "and FP8_1X128 are)";
+    const bool int8Mode = p->quantMode == TILEXR_EP_QUANT_STATIC_INT8 || p->quantMode == TILEXR_EP_QUANT_DYNAMIC_INT8;
+    if (p->quantMode != TILEXR_EP_QUANT_NONE && !fp8Mode && !int8Mode) {
+        TILEXR_LOG(ERROR) << "EP dispatch: unknown quantMode " << p->quantMode;
         return TILEXR_ERROR_NOT_SUPPORT;
+    }
+    if (int8Mode) {
+        if (p->h % 16 != 0 || (p->quantMode == TILEXR_EP_QUANT_STATIC_INT8 && p->scales == nullptr) ||
+            (p->quantMode == TILEXR_EP_QUANT_DYNAMIC_INT8 && p->dynamicScalesOut == nullptr)) {
+            TILEXR_LOG(ERROR) << "EP dispatch: int8 modes need h % 16 == 0; static needs scales, dynamic needs dynamicScalesOut";
+            return TILEXR_ERROR_PARA_CHECK_FAIL;
+        }
     }
     if (fp8Mode) {
         if (p->dynamicScalesOut == nullptr || p->h % 512 != 0 || p->h > EP_FP8_MAX_H) {
@@ -193,7 +203,7 @@ int TileXRMoeEpDispatchFused(const TileXREpDispatchParams *p, TileXRCommPtr comm
     grid = static_cast<unsigned>(std::max<int64_t>((p->bs + tokensPerBlock - 1) / tokensPerBlock, std::min<int64_t>(minBlocks, gridCap)));
 
     const size_t elemSize = TileXRDataTypeSize(p->dtype);
-    const bool quant = fp8Mode;
+    const bool quant = fp8Mode || int8Mode;
     const uint64_t outBytes = static_cast<uint64_t>(p->maxRecvRows) * (quant ? p->h : p->h * elemSize);
     TileXRUDMAMemHandle handle = 0;
     uint64_t regionOffset = 0;
@@ -246,7 +256,9 @@ int TileXRMoeEpDispatchFused(const TileXREpDispatchParams *p, TileXRCommPtr comm
     a.expertScales = p->expertScales;
     a.expandScalesOut = p->expandScalesOut;
     a.assistExtOut = p->assistExtOut;
-    a.dedup = (p->dedup != 0 && c.rankSize > 1) ? 1u : 0u;
+    a.quantScales = int8Mode ? p->scales : nullptr;
+    // per-expert smoothing makes the rows of one token differ from expert to expert: nothing to share
+    a.dedup = (p->dedup != 0 && c.rankSize > 1 && a.quantScales == nullptr) ? 1u : 0u;
     int64_t magic = 0;
     ret = TileXRCommNextMagic(comm, &magic);
     if (ret != TILEXR_SUCCESS) return ret;

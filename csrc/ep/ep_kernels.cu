@@ -416,6 +416,8 @@ __device__ void EpDispatchBody(const EpDispatchArgs &a)
         const bool mx = a.quantMode == TileXREp::TILEXR_EP_QUANT_MXFP8_E4M3 || a.quantMode == TileXREp::TILEXR_EP_QUANT_MXFP8_E5M2;
         const bool mxE5m2 = a.quantMode == TileXREp::TILEXR_EP_QUANT_MXFP8_E5M2;
         const bool quant = mx || a.quantMode == TileXREp::TILEXR_EP_QUANT_FP8_1X128;
+        const bool int8Dynamic = a.quantMode == TileXREp::TILEXR_EP_QUANT_DYNAMIC_INT8;
+        const bool int8Mode = int8Dynamic || a.quantMode == TileXREp::TILEXR_EP_QUANT_STATIC_INT8;
         const int chunks = a.h / 16;             // 16 elements per lane and iteration (fp8 paths)
         const int iters = (chunks + 31) / 32;
         // A block with few tokens (small batches) cuts every token into column ranges for several warps.
@@ -466,7 +468,56 @@ __device__ void EpDispatchBody(const EpDispatchArgs &a)
                 if (follower) myLink |= EP_LINK_FOLLOWER;
             }
             const uint32_t payloadRoutes = __ballot_sync(0xffffffffu, myExpert >= 0 && (myLink & EP_LINK_FOLLOWER) == 0);
-            if (quant) {
+            if (int8Mode) {
+                // int8 with optional per-expert smoothing scales: every route is quantised for its own expert.
+                // dynamic: one pass for the row's amax (scale = amax / 127, stored beside the row), one to convert;
+                // static: the caller's scales already map into int8 range.
+                uint32_t m = payloadRoutes;
+                while (m != 0) {
+                    const int k = __ffs(m) - 1;
+                    m &= m - 1;
+                    uint8_t *p = reinterpret_cast<uint8_t *>(__shfl_sync(0xffffffffu, myPayload, k));
+                    uint8_t *half = reinterpret_cast<uint8_t *>(__shfl_sync(0xffffffffu, myHalf, k));
+                    const uint32_t rr = __shfl_sync(0xffffffffu, myRow, k);
+                    const int e = __shfl_sync(0xffffffffu, myExpert, k);
+                    const float *sc = a.quantScales != nullptr ? a.quantScales + static_cast<int64_t>(e) * a.h : nullptr;
+                    float inv = 1.0f;
+                    if (int8Dynamic) {
+                        float amax = 0.f;
+                        for (int it = 0; it < iters; ++it) {
+                            const int c = it * 32 + lane;
+                            if (c < chunks) {
+                                float f[16];
+                                Unpack8(ld_vec16(row + static_cast<int64_t>(c) * 32), bf16, f);
+                                Unpack8(ld_vec16(row + static_cast<int64_t>(c) * 32 + 16), bf16, f + 8);
+#pragma unroll
+                                for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(sc != nullptr ? f[j] * sc[c * 16 + j] : f[j]));
+                            }
+                        }
+                        amax = WarpMax(amax);
+                        if (amax > 0.f) inv = 127.0f / amax;
+                        if (part == 0 && lane == 0) {
+                            st_vec16(half + a.win.scalesOff + static_cast<uint64_t>(rr) * a.win.scaleRowBytes,
+                                     Vec16{__float_as_uint(amax > 0.f ? amax / 127.0f : 1.0f), 0u, 0u, 0u});
+                        }
+                    }
+                    for (int it = part; it < iters; it += parts) {
+                        const int c = it * 32 + lane;
+                        if (c >= chunks) continue;
+                        float f[16];
+                        Unpack8(ld_vec16(row + static_cast<int64_t>(c) * 32), bf16, f);
+                        Unpack8(ld_vec16(row + static_cast<int64_t>(c) * 32 + 16), bf16, f + 8);
+                        uint32_t wds[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const float v = (sc != nullptr ? f[j] * sc[c * 16 + j] : f[j]) * inv;
+                            const int q = max(-128, min(127, __float2int_rn(v)));
+                            wds[j >> 2] |= static_cast<uint32_t>(q & 0xff) << (8 * (j & 3));
+                        }
+                        st_vec16(p + static_cast<int64_t>(c) * 16, Vec16{wds[0], wds[1], wds[2], wds[3]});
+                    }
+                }
+            } else if (quant) {
                 // each 512-element chunk is quantised once and stored to every destination right away:
                 // nothing row-sized lives in registers, so two blocks fit on an SM
 #pragma unroll 2
@@ -618,6 +669,7 @@ __device__ void EpDispatchBody(const EpDispatchArgs &a)
         // copies the scales of the rows that arrived with a payload; (c) without zero-copy a warp per row moves
         // the payload out of the window; (d) warps take the noted head rows in turn and fill their followers.
         const bool quantOut = a.win.scaleRowBytes != 0 && a.dynamicScalesOut != nullptr;
+        const bool scalarScale = a.quantMode == TileXREp::TILEXR_EP_QUANT_DYNAMIC_INT8;     // one fp32 per row in the output
         const uint8_t *winPayload = myHalf + a.win.payloadOff;
         const uint8_t *winScales = myHalf + a.win.scalesOff;
         const uint8_t *winExt = myHalf + a.win.extOff;
@@ -645,6 +697,10 @@ __device__ void EpDispatchBody(const EpDispatchArgs &a)
                     const int64_t r = base + idx / scaleVecsPerRow;
                     const int v = idx % scaleVecsPerRow;
                     if ((reinterpret_cast<const uint2 *>(winExt + r * 8)->x & EP_LINK_FOLLOWER) != 0) continue;
+                    if (scalarScale) {
+                        a.dynamicScalesOut[r] = *reinterpret_cast<const float *>(winScales + r * a.win.scaleRowBytes);
+                        continue;
+                    }
                     st_vec16(reinterpret_cast<uint8_t *>(a.dynamicScalesOut) + r * a.win.scaleRowBytes + v * 16,
                              ld_vec16(winScales + r * a.win.scaleRowBytes + v * 16));
                 }
@@ -666,7 +722,9 @@ __device__ void EpDispatchBody(const EpDispatchArgs &a)
                     const int64_t f = static_cast<int64_t>(next) - 1;
                     if (f >= static_cast<int64_t>(a.maxRecvRows)) break;
                     CopyLanes(a.expandXOut + f * a.win.rowBytes, src, a.win.rowBytes, lane, 32);
-                    if (quantOut) {
+                    if (quantOut && scalarScale) {
+                        if (lane == 0) a.dynamicScalesOut[f] = *reinterpret_cast<const float *>(winScales + r * a.win.scaleRowBytes);
+                    } else if (quantOut) {
                         CopyLanes(reinterpret_cast<uint8_t *>(a.dynamicScalesOut) + f * a.win.scaleRowBytes,
                                   winScales + r * a.win.scaleRowBytes, a.win.scaleRowBytes, lane, 32);
                     }

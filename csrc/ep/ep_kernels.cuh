@@ -61,6 +61,7 @@ struct EpDispatchArgs {
     uint64_t outOffset;
     void *perfTrace;                 // stage profiler buffer of this launch, or null
     int32_t *routeRowsOut;           // [bs, topK] destination row per route, or null
+    const float *quantScales;        // int8 modes: [numExperts, h] smoothing scales, or null
     const float *expertScales;       // [bs, topK] gate weights when routing is not fused, or null
     float *expandScalesOut;          // [maxRecvRows] or null
     int32_t *assistExtOut;           // [maxRecvRows, 2] or null

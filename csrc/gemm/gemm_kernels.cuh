@@ -49,7 +49,8 @@ struct GemmArgs {
     int32_t kChunks;          // all-gather: flags per row block
     int32_t flagStride;       // flags of one (source, destination) pair: the flag plane divided by the rank count
     int32_t kBlocksPerChunk;
-    uint32_t commBlocks;      // all-gather: leading CTAs that only push
+    uint32_t commBlocks;      // all-gather: leading CTAs that push the local shard to the peers first
+    uint32_t commTilesPerPair; // CTA-pair kernel: tiles (taken from the END of the walk) that each pushing pair computes afterwards
     uint32_t stageHandle;     // registry handle of the staging buffer (A staging or partial-C staging)
     uint64_t stageOffset;
     uint32_t isBf16;

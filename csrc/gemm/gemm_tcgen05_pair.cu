@@ -262,8 +262,9 @@ __device__ void PairBody(const GemmArgs &a)
     const uint64_t budgetNs = fused ? a.comm->waitTimeoutNs : 4000000000ull;
     const uint32_t epoch = fused ? w.epoch : 0;
 
-    // ---- all-gather: leading CTAs (whole pairs) only move data ------------------------------------------------
-    if (fused && a.mode == GEMM_ALL_GATHER && blockIdx.x < a.commBlocks) {
+    // ---- all-gather: leading CTAs (whole pairs) first push this rank's shard, then compute the last tiles --------
+    const bool commCta = fused && a.mode == GEMM_ALL_GATHER && blockIdx.x < a.commBlocks;
+    if (commCta) {
         if (ok) {
             const TileXRRegistry *reg = a.comm->registryPtr;
             const int pieces = a.blocksPerShard * a.kChunks;
@@ -290,8 +291,7 @@ __device__ void PairBody(const GemmArgs &a)
                 }
             }
         }
-        KernelEpilogue(w, ok);
-        return;
+        __syncthreads();
     }
 
     const uint32_t peerAbortAddr = MapToCta(SmemAddr(const_cast<int *>(&st->abortFlag)), ctaRank ^ 1u);
@@ -323,11 +323,27 @@ __device__ void PairBody(const GemmArgs &a)
     TcFenceAfter();
     const uint32_t tmemBase = st->tmemBase;
 
+    // Tile walk: computing pairs stride over the front of the walk; the pairs that pushed take
+    // `commTilesPerPair` tiles each from its end (the shards that arrive last), so their SMs are not lost.
     const int firstCta = (fused && a.mode == GEMM_ALL_GATHER) ? static_cast<int>(a.commBlocks) : 0;
-    const int pair = (static_cast<int>(blockIdx.x) - firstCta) >> 1;
-    const int nPairs = (static_cast<int>(gridDim.x) - firstCta) >> 1;
+    const int commPairs = firstCta >> 1;
     const int mTiles = (a.M + 2 * GEMM_BM - 1) / (2 * GEMM_BM);
-    const int totalTiles = mTiles * a.nBlocks;
+    const int allTiles = mTiles * a.nBlocks;
+    const int commTiles = min(allTiles, commPairs * static_cast<int>(a.commTilesPerPair));
+    int pair, nPairs, totalTiles, tileBase, tileSign;
+    if (commCta) {
+        pair = static_cast<int>(blockIdx.x) >> 1;
+        nPairs = commPairs;
+        totalTiles = commTiles;             // walk index u -> tile allTiles - 1 - u
+        tileBase = allTiles - 1;
+        tileSign = -1;
+    } else {
+        pair = (static_cast<int>(blockIdx.x) - firstCta) >> 1;
+        nPairs = (static_cast<int>(gridDim.x) - firstCta) >> 1;
+        totalTiles = allTiles - commTiles;
+        tileBase = 0;
+        tileSign = 1;
+    }
     const bool bf16 = a.isBf16 != 0;
 
     if (warp == 0) {
@@ -335,7 +351,7 @@ __device__ void PairBody(const GemmArgs &a)
         if (lane == 0) {
             uint32_t stage = 0, phase = 0;
             for (int t = pair; t < totalTiles && st->abortFlag == 0; t += nPairs) {
-                const PairTile tc = TileOf(a, t, mTiles, rank, ranks);
+                const PairTile tc = TileOf(a, tileBase + tileSign * t, mTiles, rank, ranks);
                 const int mLocal = tc.mLocalPair * 2 + static_cast<int>(ctaRank);        // this CTA's 128-row block in the shard
                 const bool remoteA = a.mode == GEMM_ALL_GATHER && tc.shard != rank;
                 const CUtensorMap *mapA = (a.mode == GEMM_ALL_GATHER && !remoteA) ? &a.tmapALocal : &a.tmapA;
@@ -415,7 +431,7 @@ __device__ void PairBody(const GemmArgs &a)
         const TileXRRegistry *reg = fused ? a.comm->registryPtr : nullptr;
         int iter = 0;
         for (int t = pair; t < totalTiles; t += nPairs, ++iter) {
-            const PairTile tc = TileOf(a, t, mTiles, rank, ranks);
+            const PairTile tc = TileOf(a, tileBase + tileSign * t, mTiles, rank, ranks);
             const int mTile = tc.mTile, nBlock = tc.nBlock;
             const int acc = iter & 1;
             const uint32_t accPhase = (iter >> 1) & 1;

@@ -30,8 +30,8 @@ enum TileXREpActiveMaskType {
 };
 enum TileXREpQuantMode {
     TILEXR_EP_QUANT_NONE = 0,
-    TILEXR_EP_QUANT_STATIC_INT8 = 1,     // reference MVP route only; not supported here
-    TILEXR_EP_QUANT_DYNAMIC_INT8 = 2,    // reference MVP route only; not supported here
+    TILEXR_EP_QUANT_STATIC_INT8 = 1,     // q = rint(x * scales[expert]) saturated to int8; `scales` [moeExpertNum, h] required
+    TILEXR_EP_QUANT_DYNAMIC_INT8 = 2,    // per row: scale = amax(x * scales[expert]) / 127 -> dynamicScalesOut[row] (fp32), q = rint(x / scale)
     TILEXR_EP_QUANT_MXFP8_E5M2 = 3,      // fused: 1x32 blocks with E8M0 exponent bytes (dynamicScalesOut is [rows, h/32] uint8)
     TILEXR_EP_QUANT_MXFP8_E4M3 = 4,      // fused, the reference's production quantisation (quantMode 4)
     TILEXR_EP_QUANT_FP8_1X128 = 5,       // e4m3 with one fp32 scale per 128 elements
@@ -82,6 +82,7 @@ typedef struct TileXREpDispatchParams {
     // assistExtOut; the matching combine must get the same flag.
     int64_t dedup;
     int32_t *assistExtOut;         // [maxRecvRows, 2] {link, weight bits} for combine; needed when dedup != 0
+    const float *scales;           // int8 modes: [moeExpertNum, h] fp32 smoothing scales (required for static, optional for dynamic)
 } TileXREpDispatchParams;
 
 typedef struct TileXREpCombineParams {

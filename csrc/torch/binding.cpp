@@ -357,10 +357,12 @@ py::tuple EpDispatch(const CommPtr &c, const at::Tensor &x, const c10::optional<
                      const c10::optional<at::Tensor> &gateLogits, const c10::optional<at::Tensor> &selectionBias,
                      const c10::optional<at::Tensor> &activeMask, int64_t topK, int64_t numExperts, int64_t quantMode,
                      int64_t scoreFunc, bool renormalize, double routedScale, int64_t tokenNumsType, int64_t maxRecvRows,
-                     const c10::optional<at::Tensor> &expandXOut, const c10::optional<at::Tensor> &expertScales, bool dedup)
+                     const c10::optional<at::Tensor> &expandXOut, const c10::optional<at::Tensor> &expertScales, bool dedup,
+                     const c10::optional<at::Tensor> &quantScales)
 {
     RequireContiguous(x, "x");
     Keep(expertScales);
+    Keep(quantScales);
     TORCH_CHECK(x.dim() == 2 && x.is_cuda(), "x must be a 2-D CUDA tensor");
     Keep(x);
     Keep(expertIds);
@@ -372,15 +374,19 @@ py::tuple EpDispatch(const CommPtr &c, const at::Tensor &x, const c10::optional<
     const int64_t localExperts = numExperts / R;
     auto i32 = x.options().dtype(at::kInt);
     const bool mx = quantMode == TileXREp::TILEXR_EP_QUANT_MXFP8_E4M3 || quantMode == TileXREp::TILEXR_EP_QUANT_MXFP8_E5M2;
-    const bool quant = mx || quantMode == TileXREp::TILEXR_EP_QUANT_FP8_1X128;
-    const at::ScalarType qType = quantMode == TileXREp::TILEXR_EP_QUANT_MXFP8_E5M2 ? at::kFloat8_e5m2 : at::kFloat8_e4m3fn;
+    const bool int8 = quantMode == TileXREp::TILEXR_EP_QUANT_STATIC_INT8 || quantMode == TileXREp::TILEXR_EP_QUANT_DYNAMIC_INT8;
+    const bool quant = mx || int8 || quantMode == TileXREp::TILEXR_EP_QUANT_FP8_1X128;
+    const at::ScalarType qType = int8 ? at::kChar
+                                 : quantMode == TileXREp::TILEXR_EP_QUANT_MXFP8_E5M2 ? at::kFloat8_e5m2 : at::kFloat8_e4m3fn;
     at::Tensor expandX = expandXOut.has_value() && expandXOut->defined()
                              ? *expandXOut
                              : at::empty({maxRecvRows, h}, x.options().dtype(quant ? qType : x.scalar_type()));
     TORCH_CHECK(expandX.is_contiguous() && expandX.size(0) >= maxRecvRows && expandX.size(1) == h, "bad expand_x_out");
-    at::Tensor scales = mx      ? at::empty({maxRecvRows, h / 32}, x.options().dtype(at::kByte))
-                        : quant ? at::empty({maxRecvRows, h / 128}, x.options().dtype(at::kFloat))
-                                : at::Tensor();
+    const bool hasScales = quant && quantMode != TileXREp::TILEXR_EP_QUANT_STATIC_INT8;
+    at::Tensor scales = mx                                                      ? at::empty({maxRecvRows, h / 32}, x.options().dtype(at::kByte))
+                        : quantMode == TileXREp::TILEXR_EP_QUANT_DYNAMIC_INT8 ? at::empty({maxRecvRows}, x.options().dtype(at::kFloat))
+                        : hasScales                                            ? at::empty({maxRecvRows, h / 128}, x.options().dtype(at::kFloat))
+                                                                               : at::Tensor();
     at::Tensor assist = at::empty({maxRecvRows, 4}, i32);
     at::Tensor tokenNums = at::empty({localExperts}, x.options().dtype(at::kLong));
     at::Tensor sendCounts = at::empty({localExperts * R}, i32);
@@ -420,7 +426,12 @@ py::tuple EpDispatch(const CommPtr &c, const at::Tensor &x, const c10::optional<
     p.topkIdsOut = topkIds.data_ptr<int32_t>();
     p.topkWeightsOut = topkWeights.data_ptr<float>();
     p.expandXOut = expandX.data_ptr();
-    p.dynamicScalesOut = quant ? static_cast<float *>(scales.data_ptr()) : nullptr;
+    p.dynamicScalesOut = hasScales ? static_cast<float *>(scales.data_ptr()) : nullptr;
+    if (quantScales.has_value() && quantScales->defined()) {
+        TORCH_CHECK(quantScales->scalar_type() == at::kFloat && quantScales->is_contiguous() && quantScales->numel() == numExperts * h,
+                    "scales must be contiguous fp32 [num_experts, h]");
+        p.scales = quantScales->data_ptr<float>();
+    }
     p.assistInfoForCombineOut = assist.data_ptr<int32_t>();
     p.expertTokenNumsOut = tokenNums.data_ptr<int64_t>();
     p.sendCountsOut = sendCounts.data_ptr<int32_t>();
@@ -440,7 +451,7 @@ py::tuple EpDispatch(const CommPtr &c, const at::Tensor &x, const c10::optional<
         Keep(t);
     }
     Check(TileXRMoeEpDispatchFused(&p, c->ptr(), StreamOf(x)), "TileXRMoeEpDispatchFused");
-    return py::make_tuple(expandX, quant ? py::cast(scales) : py::none(), assist, tokenNums, sendCounts, recvTotal, topkIds,
+    return py::make_tuple(expandX, hasScales ? py::cast(scales) : py::none(), assist, tokenNums, sendCounts, recvTotal, topkIds,
                           topkWeights, routeRows, assistExt, expandScales);
 }
 
@@ -642,7 +653,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m)
           py::arg("top_k") = 1, py::arg("num_experts") = 1, py::arg("quant_mode") = 0, py::arg("score_func") = 0,
           py::arg("renormalize") = true, py::arg("routed_scale") = 1.0, py::arg("token_nums_type") = 1,
           py::arg("max_recv_rows") = 0, py::arg("expand_x_out") = py::none(), py::arg("expert_scales") = py::none(),
-          py::arg("dedup") = false);
+          py::arg("dedup") = false, py::arg("scales") = py::none());
     m.def("ep_combine", &EpCombine, py::arg("comm"), py::arg("expert_out"), py::arg("assist"), py::arg("send_counts"),
           py::arg("expert_ids") = py::none(), py::arg("expert_scales") = py::none(), py::arg("active_mask") = py::none(),
           py::arg("shared_expert_x") = py::none(), py::arg("bs") = 0, py::arg("top_k") = 1, py::arg("num_experts") = 1,

@@ -215,6 +215,45 @@ def test_ep_dispatch_fused_mxfp8(txr, e5m2):
     world.destroy()
 
 
+@pytest.mark.parametrize("dynamic,smooth", [(True, False), (True, True), (False, True)])
+def test_ep_dispatch_int8_modes(txr, dynamic, smooth):
+    """quantMode 1 (static) and 2 (per-row dynamic) int8, with per-expert smoothing scales."""
+    from tilexr_b200.ops import ep
+    from tilexr_b200.utils import oracle
+
+    ranks, bs, h, experts, top_k = 2, 20, 512, 8, 3
+    world = txr.init_emulated_world(ranks, device=0, buffer_mb=64)
+    g = torch.Generator().manual_seed(31)
+    xs = [torch.randn(bs, h, generator=g).to(torch.bfloat16) for _ in range(ranks)]
+    ids = [torch.stack([torch.randperm(experts, generator=g)[:top_k] for _ in range(bs)]).to(torch.int32) for _ in range(ranks)]
+    ws = [torch.rand(bs, top_k, generator=g) for _ in range(ranks)]
+    smooth_scales = (0.5 + torch.rand(experts, h, generator=g)) * (1.0 if dynamic else 20.0) if smooth else None
+    mode = ep.QUANT_DYNAMIC_INT8 if dynamic else ep.QUANT_STATIC_INT8
+    res = world.run(lambda c, r: ep.dispatch(c, xs[r].cuda(), expert_ids=ids[r].cuda(), expert_scales=ws[r].cuda(),
+                                             num_experts=experts, top_k=top_k, quant_mode=mode,
+                                             scales=None if smooth_scales is None else smooth_scales.cuda()))
+    world.check()
+    ref = oracle.ep_dispatch_ref(xs, ids, experts, None)
+    for r in range(ranks):
+        d = res[r]
+        n = int(d.recv_total.item())
+        assert n == len(ref[r]["rows"]) and d.expand_x.dtype == torch.int8
+        v = ref[r]["expand_x"].float()
+        if smooth_scales is not None:
+            v = v * smooth_scales[ref[r]["assist"][:, 3].long()]
+        if dynamic:
+            amax = v.abs().amax(dim=1)
+            inv = torch.where(amax > 0, 127.0 / amax, torch.ones_like(amax))
+            want = torch.round(v * inv.unsqueeze(1)).clamp(-128, 127).to(torch.int8)
+            assert torch.equal(d.dynamic_scales[:n].cpu(), torch.where(amax > 0, amax / 127.0, torch.ones_like(amax)))
+        else:
+            want = torch.round(v).clamp(-128, 127).to(torch.int8)
+            assert d.dynamic_scales is None
+        assert torch.equal(d.expand_x[:n].cpu(), want)
+        assert d.dedup == (smooth_scales is None)
+    world.destroy()
+
+
 def test_ep_overflow_is_reported_not_written(txr):
     from tilexr_b200.ops import ep
 

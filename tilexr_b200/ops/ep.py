@@ -13,6 +13,8 @@ import torch
 from .. import _C
 
 QUANT_NONE = 0
+QUANT_STATIC_INT8 = 1    # q = rint(x * scales[expert]); `scales` [num_experts, h] required
+QUANT_DYNAMIC_INT8 = 2   # per row: scale = amax(x * scales[expert]) / 127 in dynamic_scales [rows], q = rint(x / scale)
 QUANT_MXFP8_E5M2 = 3     # 1x32 blocks, E8M0 exponent bytes; dynamic_scales is uint8 [rows, h/32]
 QUANT_MXFP8_E4M3 = 4
 QUANT_FP8_1X128 = 5
@@ -44,7 +46,8 @@ def dispatch(comm, x: torch.Tensor, *, num_experts: int, top_k: int, expert_ids:
              active_mask: Optional[torch.Tensor] = None, quant_mode: int = QUANT_NONE, score_func: int = 0,
              renormalize: bool = True, routed_scale: float = 1.0, token_nums_type: int = TOKEN_NUMS_COUNT,
              max_recv_rows: Optional[int] = None, expand_x_out: Optional[torch.Tensor] = None,
-             expert_scales: Optional[torch.Tensor] = None, dedup: Optional[bool] = None) -> DispatchResult:
+             expert_scales: Optional[torch.Tensor] = None, dedup: Optional[bool] = None,
+             scales: Optional[torch.Tensor] = None) -> DispatchResult:
     """``dedup`` (default: on when gate weights are known at dispatch time): a token with several experts on one
     remote rank crosses NVLink once in each direction; the expert rank replicates it after arrival and sums
     its outputs, gate-weighted in fp32, before sending them back.  The weights used for those sums are the ones
@@ -52,11 +55,13 @@ def dispatch(comm, x: torch.Tensor, *, num_experts: int, top_k: int, expert_ids:
     bs = x.shape[0]
     if dedup is None:
         dedup = gate_logits is not None or expert_scales is not None
+    if scales is not None:
+        dedup = False        # per-expert smoothing scales make every route's row different
     if max_recv_rows is None:
         max_recv_rows = bs * comm.world_size * min(top_k, num_experts // comm.world_size)
     out = _C.ep_dispatch(comm, x, expert_ids, gate_logits, selection_bias, active_mask, top_k, num_experts, quant_mode,
                          score_func, renormalize, routed_scale, token_nums_type, max_recv_rows, expand_x_out, expert_scales,
-                         bool(dedup))
+                         bool(dedup), scales)
     return DispatchResult(*out, bs=bs, top_k=top_k, num_experts=num_experts, dedup=bool(dedup))
 
 
