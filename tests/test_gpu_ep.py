@@ -243,7 +243,7 @@ def test_ep_dispatch_int8_modes(txr, dynamic, smooth):
             v = v * smooth_scales[ref[r]["assist"][:, 3].long()]
         if dynamic:
             amax = v.abs().amax(dim=1)
-            inv = torch.where(amax > 0, 127.0 / amax, torch.ones_like(amax))
+            inv = torch.where(amax > 0, torch.full_like(amax, 127.0) / amax, torch.ones_like(amax))   # tensor / tensor: IEEE division
             want = torch.round(v * inv.unsqueeze(1)).clamp(-128, 127).to(torch.int8)
             assert torch.equal(d.dynamic_scales[:n].cpu(), torch.where(amax > 0, amax / 127.0, torch.ones_like(amax)))
         else:
