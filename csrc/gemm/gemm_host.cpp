@@ -133,6 +133,7 @@ int TileXRMatmul(const void *a, const void *b, void *c, int64_t m, int64_t n, in
         // CTA pairs on 256x256 tiles: each CTA loads half of the B tile (its own tensor map box of 128 rows)
         ret = MakeMap(&g.tmapB, b, n, k, GEMM_BN / 2, bf16);
         if (ret != TILEXR_SUCCESS) return ret;
+        g.rasterGroup = static_cast<int32_t>(std::max<long>(1, EnvLong("TILEXR_GEMM_GROUP", 8)));
         const int pairTiles = static_cast<int>((m + 2 * GEMM_BM - 1) / (2 * GEMM_BM)) * g.nBlocks;
         const int pairs = std::max(1, std::min<int>(pairTiles, static_cast<int>(EnvLong("TILEXR_GEMM_CTAS", sms)) / 2));
         static std::once_flag pairOnce;

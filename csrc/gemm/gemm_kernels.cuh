@@ -54,6 +54,7 @@ struct GemmArgs {
     uint32_t stageHandle;     // registry handle of the staging buffer (A staging or partial-C staging)
     uint64_t stageOffset;
     uint32_t isBf16;
+    int32_t rasterGroup;      // CTA-pair kernel, plain mode: 256-row blocks per group of the tile walk
 };
 
 const void *GemmKernelSingle();

@@ -186,11 +186,10 @@ __device__ __forceinline__ uint32_t PackPair(float lo, float hi, bool bf16)
     return *reinterpret_cast<const uint32_t *>(&v);
 }
 
-// Tile t of the pair's walk: 256-row blocks advance fastest inside a group of four, so pairs that run side by
+// Tile t of the pair's walk: 256-row blocks advance fastest inside a group (eight by default), so pairs that run side by
 // side share a B tile and the group's A rows stay in L2.
-__device__ __forceinline__ void PairTileAt(int t, int mTiles, int nBlocks, int *mTile, int *nBlock)
+__device__ __forceinline__ void PairTileAt(int t, int mTiles, int nBlocks, int GROUP, int *mTile, int *nBlock)
 {
-    constexpr int GROUP = 4;
     const int perGroup = GROUP * nBlocks;
     const int group = t / perGroup;
     const int first = group * GROUP;
@@ -211,7 +210,7 @@ __device__ __forceinline__ PairTile TileOf(const GemmArgs &a, int t, int mTiles,
 {
     PairTile c;
     if (a.mode == GEMM_PLAIN) {
-        PairTileAt(t, mTiles, a.nBlocks, &c.mTile, &c.nBlock);
+        PairTileAt(t, mTiles, a.nBlocks, a.rasterGroup, &c.mTile, &c.nBlock);
         c.shard = 0;
         c.mLocalPair = c.mTile;
     } else {
