@@ -1,0 +1,60 @@
+"""tcgen05 GEMM against cuBLAS (torch.matmul) on one GPU: CUDA-event medians with an L2 flush between
+iterations, bit comparison of the results.
+
+    python -m tilexr_b200.tools.gemm_perf [--shapes 4096x4096x4096,8192x8192x8192] [--iters 8]
+
+`TILEXR_GEMM_PAIR=0` selects the one-CTA kernel, `TILEXR_GEMM_GROUP=n` the raster group of the CTA-pair kernel.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+
+import torch
+
+import tilexr_b200 as txr
+
+DEFAULT = "4096x4096x4096,8192x8192x8192,8192x28672x8192,8192x8192x14336,16384x7168x2048"
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--shapes", default=DEFAULT, help="comma separated MxNxK")
+    ap.add_argument("--iters", type=int, default=8)
+    ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float16"])
+    args = ap.parse_args()
+    dtype = getattr(torch, args.dtype)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")       # larger than the 126 MB L2
+
+    def median_ms(fn):
+        for _ in range(3):
+            fn()
+        times = []
+        for _ in range(args.iters):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            times.append(e0.elapsed_time(e1))
+        times.sort()
+        return times[len(times) // 2]
+
+    for shape in args.shapes.split(","):
+        m, n, k = (int(v) for v in shape.split("x"))
+        a = (torch.randn(m, k, device="cuda") * 0.5).to(dtype)
+        b = (torch.randn(n, k, device="cuda") * 0.5).to(dtype)
+        ours = median_ms(lambda: txr.gemm.matmul(a, b))
+        cublas = median_ms(lambda: torch.matmul(a, b.t()))
+        c, ref = txr.gemm.matmul(a, b), torch.matmul(a, b.t())
+        torch.cuda.synchronize()
+        flops = 2.0 * m * n * k
+        print(json.dumps({"shape": [m, n, k], "ours_us": ours * 1e3, "cublas_us": cublas * 1e3, "ours_tflops": flops / ours / 1e9,
+                          "cublas_tflops": flops / cublas / 1e9, "ratio": cublas / ours, "identical_bits": bool(torch.equal(c, ref))}),
+              flush=True)
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())
