@@ -268,3 +268,38 @@ def test_ep_overflow_is_reported_not_written(txr):
     for c in world.comms:
         c.reset_status()
     world.destroy()
+
+
+@pytest.mark.parametrize("fp8", [False, True])
+def test_moe_layer_matches_a_dense_reference(txr, fp8):
+    """The MoE block (routing, dispatch, expert FFN on the tcgen05 GEMM, combine) against plain PyTorch in fp32."""
+    from conftest import free_port
+    from tilexr_b200.models import ExpertParallelMoE, MoEConfig
+    from tilexr_b200.utils import oracle
+
+    comm = txr.init_process(0, 1, comm_id=f"127.0.0.1:{free_port()}", buffer_mb=64, device=0)
+    cfg = MoEConfig(hidden=512, ffn=256, num_experts=8, top_k=2, fp8_dispatch=fp8)
+    layer = ExpertParallelMoE(comm, cfg, seed=3)
+    g = torch.Generator().manual_seed(9)
+    x = torch.randn(96, cfg.hidden, generator=g).to(torch.bfloat16)
+    y = layer(x.cuda())
+    torch.cuda.synchronize()
+    assert comm.device_status() == 0
+    logits = x.float() @ layer.gate.detach().cpu().t()
+    ids, ws = oracle.routing_topk_ref(logits, cfg.top_k, cfg.score_func, cfg.renormalize, cfg.routed_scale)
+    xin = x.float()
+    if fp8:
+        q, s = oracle.fp8_quant_1x128_ref(x)
+        xin = oracle.fp8_dequant_1x128_ref(q, s).to(torch.bfloat16).float()
+    w13, w2 = layer.w13.detach().cpu().float(), layer.w2.detach().cpu().float()
+    want = torch.zeros(96, cfg.hidden)
+    for t in range(96):
+        for k in range(cfg.top_k):
+            e = int(ids[t, k])
+            gu = (xin[t] @ w13[e].t()).to(torch.bfloat16).float()
+            g_, u_ = gu.chunk(2)
+            hmid = (torch.nn.functional.silu(g_) * u_).to(torch.bfloat16).float()
+            want[t] += float(ws[t, k]) * (hmid @ w2[e].t()).to(torch.bfloat16).float()
+    got = y.cpu().float()
+    assert torch.allclose(got, want, rtol=3e-2, atol=3e-3), (got - want).abs().max()
+    comm.destroy()

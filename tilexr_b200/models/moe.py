@@ -4,8 +4,9 @@ The reference ships no model code; its harness drives dispatch -> expert FFN (gr
 SwiGLU, grouped GEMM) -> combine with synthetic experts (tools/moonep/expert_forward.py).  This
 module is the same workload as a reusable layer, shaped like a DeepSeek-V3 MoE block: sigmoid
 router with top-k renormalisation, fp8 (e4m3, 1x128 scales) token transport, bf16 combine.
-The expert FFN itself uses library GEMMs; the communication, routing, quantisation and the
-gate-weighted reduction are this repository's kernels.
+The expert GEMMs run on this repository's tcgen05 kernel (one launch per local expert segment; cuBLAS only
+for shapes the kernel does not take); the communication, routing, quantisation and the gate-weighted
+reduction are this repository's kernels too.
 """
 from __future__ import annotations
 
@@ -14,7 +15,15 @@ from typing import Optional
 
 import torch
 
-from ..ops import ep, quant
+from ..ops import ep, gemm, quant
+
+
+def _linear(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """x [m, k] times w [n, k] transposed."""
+    if x.is_cuda and x.dtype in (torch.bfloat16, torch.float16) and w.dtype == x.dtype and x.shape[1] % 8 == 0 and w.shape[0] % 8 == 0 \
+            and x.is_contiguous() and w.is_contiguous() and x.data_ptr() % 16 == 0:
+        return gemm.matmul(x, w)
+    return x @ w.t()
 
 
 @dataclasses.dataclass
@@ -65,9 +74,9 @@ class ExpertParallelMoE(torch.nn.Module):
             if n == 0:
                 continue
             seg = rows[start:start + n]
-            gu = seg @ self.w13[e].t()
+            gu = _linear(seg, self.w13[e])
             g_, u_ = gu.chunk(2, dim=-1)
-            out[start:start + n] = (torch.nn.functional.silu(g_) * u_) @ self.w2[e].t()
+            out[start:start + n] = _linear((torch.nn.functional.silu(g_) * u_).contiguous(), self.w2[e])
             start += n
         return out
 
