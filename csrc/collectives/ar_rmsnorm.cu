@@ -203,8 +203,7 @@ __device__ void ArNormBody(const ArNormArgs &a)
         const int foreign = a.rows - myRows;
         for (int it = blockIdx.x; it < foreign; it += gridDim.x) {
             // enumerate foreign rows starting after my own range so that ranks start on different owners
-            int row = myFirst + myRows + it;
-            if (row >= a.rows) row -= a.rows;
+            const int row = (min(myFirst, a.rows) + myRows + it) % a.rows;   // with fewer rows than ranks myFirst lies past the end
             const int owner = row / per;
             const int local = row - owner * per;
             CopyLanes(PlaneA(a, owner, rank, local, epoch), a.x + row * rb, rb, tid, blockDim.x);
@@ -241,8 +240,7 @@ __device__ void ArNormBody(const ArNormArgs &a)
         }
         // 3. rows of other owners come back normalised
         for (int it = blockIdx.x; it < foreign && ok; it += gridDim.x) {
-            int row = myFirst + myRows + it;
-            if (row >= a.rows) row -= a.rows;
+            const int row = (min(myFirst, a.rows) + myRows + it) % a.rows;   // with fewer rows than ranks myFirst lies past the end
             const int owner = row / per;
             const int local = row - owner * per;
             bool got = true;

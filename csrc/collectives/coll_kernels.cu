@@ -249,19 +249,22 @@ __device__ void PushBody(const CollArgs &a)
     const bool isProducer = blockIdx.x < a.producers;
 
     if (ok && isProducer) {
-        if (a.kind == COLL_ALL_TO_ALL) {
-            // item (tile, k): slice for peer (rank+1+k) % R; k == R-1 is the local slice
-            const uint64_t items = static_cast<uint64_t>(a.tiles) * R;
+        if (a.kind == COLL_ALL_TO_ALL || a.kind == COLL_SCATTER) {
+            // item (tile, k): slice for peer (rank+1+k) % R; k == R-1 is the local slice.  A scatter is the root's
+            // row of the all-to-all: only the root sends, and the slice lands at its own index in the output.
+            const bool scatter = a.kind == COLL_SCATTER;
+            const uint64_t items = (scatter && rank != a.root) ? 0 : static_cast<uint64_t>(a.tiles) * R;
             for (uint64_t it = blockIdx.x; it < items; it += a.producers) {
                 const uint32_t t = static_cast<uint32_t>(it / R);
                 const int peer = (rank + 1 + static_cast<int>(it % R)) % R;
+                if (scatter && peer == rank) continue;
                 const uint32_t n = TileLen(S, t, a.tileBytes);
                 const uint8_t *src = a.in + static_cast<uint64_t>(peer) * a.sliceStride + static_cast<uint64_t>(t) * a.tileBytes;
                 uint8_t *dst;
                 if (peer == rank) {
                     dst = a.out + static_cast<uint64_t>(rank) * a.sliceStride + static_cast<uint64_t>(t) * a.tileBytes;
                 } else if (a.zeroCopy) {
-                    dst = PeerOut(a, peer, static_cast<uint64_t>(rank) * a.sliceStride + static_cast<uint64_t>(t) * a.tileBytes);
+                    dst = PeerOut(a, peer, static_cast<uint64_t>(scatter ? peer : rank) * a.sliceStride + static_cast<uint64_t>(t) * a.tileBytes);
                 } else {
                     dst = RingSlot(a, peer, rank, t, epoch, 0);
                 }
@@ -317,7 +320,8 @@ __device__ void PushBody(const CollArgs &a)
         // consumers: tiles that other ranks push into this rank's window
         const uint32_t consumers = gridDim.x - a.producers;
         const uint32_t me = blockIdx.x - a.producers;
-        const bool bcast = a.kind == COLL_BROADCAST;
+        const bool scatterKind = a.kind == COLL_SCATTER;
+        const bool bcast = a.kind == COLL_BROADCAST || scatterKind;      // one source: the root
         const int nSrc = bcast ? (rank == a.root ? 0 : 1) : R - 1;
         const uint64_t items = static_cast<uint64_t>(a.tiles) * nSrc;
         for (uint64_t it = me; it < items && ok; it += consumers) {
@@ -333,7 +337,10 @@ __device__ void PushBody(const CollArgs &a)
             ok = BlockBroadcastOk(got);
             if (ok && !a.zeroCopy) {
                 if (threadIdx.x == 0) PerfStageBegin(c.perf, TILEXR_PERF_PEER_IPC_TO_OUTPUT);
-                uint8_t *dst = a.out + (bcast ? 0 : static_cast<uint64_t>(src) * a.sliceStride) + static_cast<uint64_t>(t) * a.tileBytes;
+                uint8_t *dst = a.out + (scatterKind ? static_cast<uint64_t>(rank) * a.sliceStride
+                                        : bcast     ? 0
+                                                    : static_cast<uint64_t>(src) * a.sliceStride) +
+                               static_cast<uint64_t>(t) * a.tileBytes;
                 CopyLanes(dst, RingSlot(a, rank, src, t, epoch, 0), n, threadIdx.x, blockDim.x);
                 if (threadIdx.x == 0) PerfStageEnd(c.perf, TILEXR_PERF_PEER_IPC_TO_OUTPUT, n);
             }

@@ -27,6 +27,7 @@ enum CollKind : int32_t {
     COLL_ALL_REDUCE_ONE_SHOT = 4,   // everybody reduces everything
     COLL_ALL_REDUCE_TWO_SHOT = 5,   // reduce-scatter then all-gather of reduced slices
     COLL_PROFILE_PROBE = 6,  // local copy that exercises every profiler stage
+    COLL_SCATTER = 7,        // root's slice p goes to rank p (in == out, the root's own slice stays); first half of a large broadcast
 };
 
 struct CollArgs {

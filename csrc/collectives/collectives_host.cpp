@@ -101,7 +101,7 @@ int Plan(int kind, uint64_t sliceBytes, int rankSize, uint64_t dataHalfBytes, un
     const uint32_t autoCap = launchPair >= (512u << 10) ? 64 : launchPair >= (128u << 10) ? 32 : 16;
     uint32_t cap = static_cast<uint32_t>(EnvLong("TILEXR_COLL_BLOCKS", autoCap));
     if (EnvLong("LCCL_PARALLEL", 0) == 1) cap = static_cast<uint32_t>(rankSize);
-    const uint64_t fanItems = (kind == COLL_ALL_TO_ALL) ? static_cast<uint64_t>(tiles) * rankSize
+    const uint64_t fanItems = (kind == COLL_ALL_TO_ALL || kind == COLL_SCATTER) ? static_cast<uint64_t>(tiles) * rankSize
                               : (kind == COLL_REDUCE_SCATTER || twoShot) ? static_cast<uint64_t>(tiles) * (rankSize - 1)
                                                                         : tiles;
     uint32_t producers = static_cast<uint32_t>(std::min<uint64_t>(fanItems, cap));
@@ -205,7 +205,8 @@ int Run(TileXRCommPtr comm, const CallContext &ctx, int kind, int opType, const 
     TileXRUDMAMemHandle handle = 0;
     uint64_t regionOffset = 0;
     bool zeroCopy = false;
-    if (kind == COLL_ALL_GATHER || kind == COLL_ALL_TO_ALL || kind == COLL_BROADCAST || kind == COLL_ALL_REDUCE_TWO_SHOT) {
+    if (kind == COLL_ALL_GATHER || kind == COLL_ALL_TO_ALL || kind == COLL_BROADCAST || kind == COLL_SCATTER ||
+        kind == COLL_ALL_REDUCE_TWO_SHOT) {
         zeroCopy = EnvLong("TILEXR_COLL_ZERO_COPY", 1) != 0 &&
                    TileXRFindRegistration(comm, out, outBytes, &handle, &regionOffset) == TILEXR_SUCCESS;
     }
@@ -241,7 +242,7 @@ int Run(TileXRCommPtr comm, const CallContext &ctx, int kind, int opType, const 
         a.producers = g.producers;
         a.reducers = g.reducers;
         uint32_t grid = g.producers + g.reducers + g.consumers;
-        if (kind == COLL_BROADCAST) {
+        if (kind == COLL_BROADCAST || kind == COLL_SCATTER) {
             // the root only pushes, the others only consume; keep the grid equal on all ranks
             a.producers = (ctx.rank == root) ? grid : 0;
         }
@@ -396,6 +397,17 @@ int TileXRBroadcast(void *buf, int64_t count, TileXRDataType dataType, int root,
     uint64_t bytes = 0;
     if (MulOverflows(static_cast<uint64_t>(count), TileXRDataTypeSize(dataType), &bytes)) return TILEXR_ERROR_PARA_CHECK_FAIL;
     if (ctx.rankSize == 1) return TILEXR_SUCCESS;
+    // Large messages on more than two ranks: the root scatters 1/R of the buffer to every rank and an in-place
+    // all-gather completes it, so the root sends the buffer about twice instead of R-1 times.
+    const uint64_t R = static_cast<uint64_t>(ctx.rankSize);
+    if (ctx.rankSize > 2 && bytes >= static_cast<uint64_t>(EnvLong("TILEXR_BCAST_SCATTER_MIN_BYTES", 2 << 20)) && bytes % (R * 16) == 0) {
+        const uint64_t slice = bytes / R;
+        uint8_t *base = static_cast<uint8_t *>(buf);
+        ret = Run(comm, ctx, COLL_SCATTER, TILEXR_OP_BROADCAST, base, base, slice, slice, bytes, dataType, 0, root, stream);
+        if (ret != TILEXR_SUCCESS) return ret;
+        return Run(comm, ctx, COLL_ALL_GATHER, TILEXR_OP_BROADCAST, base + static_cast<uint64_t>(ctx.rank) * slice, base, slice, slice,
+                   bytes, dataType, 0, 0, stream);
+    }
     return Run(comm, ctx, COLL_BROADCAST, TILEXR_OP_BROADCAST, static_cast<const uint8_t *>(buf), static_cast<uint8_t *>(buf),
                bytes, bytes, bytes, dataType, 0, root, stream);
 }

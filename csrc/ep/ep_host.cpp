@@ -74,6 +74,32 @@ int Prepare(TileXRCommPtr comm, Ctx *c)
     return TILEXR_SUCCESS;
 }
 
+// Fills `topo` and checks the expert placement: shared experts on the leading ranks, routed experts on the others.
+int MakeTopology(int64_t moeExpertNum, int64_t topK, int rankSize, int64_t sharedExpertNum, int64_t sharedExpertRankNum, EpTopology *topo)
+{
+    if (sharedExpertNum < 0 || sharedExpertRankNum < 0 || (sharedExpertNum == 0) != (sharedExpertRankNum == 0)) {
+        TILEXR_LOG(ERROR) << "EP: sharedExpertNum and sharedExpertRankNum must both be zero or both be positive";
+        return TILEXR_ERROR_PARA_CHECK_FAIL;
+    }
+    if (sharedExpertNum > 0 && (sharedExpertRankNum % sharedExpertNum != 0 || sharedExpertRankNum >= rankSize)) {
+        TILEXR_LOG(ERROR) << "EP: sharedExpertRankNum must be a multiple of sharedExpertNum and leave ranks for the routed experts";
+        return TILEXR_ERROR_PARA_CHECK_FAIL;
+    }
+    const int64_t moeRanks = rankSize - sharedExpertRankNum;
+    if (moeExpertNum % moeRanks != 0) {
+        TILEXR_LOG(ERROR) << "EP: " << moeExpertNum << " experts do not divide over " << moeRanks << " ranks";
+        return TILEXR_ERROR_PARA_CHECK_FAIL;
+    }
+    if (topK + sharedExpertNum > 32 || sharedExpertRankNum + moeExpertNum > EP_MAX_EXPERTS) {
+        TILEXR_LOG(ERROR) << "EP: topK + sharedExpertNum <= 32 and sharedExpertRankNum + experts <= " << EP_MAX_EXPERTS << " required";
+        return TILEXR_ERROR_PARA_CHECK_FAIL;
+    }
+    topo->sharedRanks = static_cast<int32_t>(sharedExpertRankNum);
+    topo->sharedExperts = static_cast<int32_t>(sharedExpertNum);
+    topo->moePerRank = static_cast<int32_t>(moeExpertNum / moeRanks);
+    return TILEXR_SUCCESS;
+}
+
 int ValidateShape(int64_t bs, int64_t h, int64_t topK, int64_t moeExpertNum, int rankSize, int dtype)
 {
     if (dtype != TILEXR_DATA_TYPE_FP16 && dtype != TILEXR_DATA_TYPE_BFP16) {
@@ -88,15 +114,12 @@ int ValidateShape(int64_t bs, int64_t h, int64_t topK, int64_t moeExpertNum, int
         TILEXR_LOG(ERROR) << "EP: topK <= " << EP_MAX_TOPK << ", topK <= experts <= " << EP_MAX_EXPERTS << " required";
         return TILEXR_ERROR_PARA_CHECK_FAIL;
     }
-    if (moeExpertNum % rankSize != 0) {
-        TILEXR_LOG(ERROR) << "EP: " << moeExpertNum << " experts do not divide over " << rankSize << " ranks";
-        return TILEXR_ERROR_PARA_CHECK_FAIL;
-    }
+    (void)rankSize;
     if ((h * 2) % 16 != 0) {
         TILEXR_LOG(ERROR) << "EP: hidden size must be a multiple of 8 elements";
         return TILEXR_ERROR_PARA_CHECK_FAIL;
     }
-    if (bs * topK > TILEXR_FLAG_SLOT_SLOTS) {
+    if (bs * 32 > TILEXR_FLAG_SLOT_SLOTS && bs * topK > TILEXR_FLAG_SLOT_SLOTS) {
         TILEXR_LOG(ERROR) << "EP: bs*topK exceeds the " << TILEXR_FLAG_SLOT_SLOTS << " slot flags of a window";
         return TILEXR_ERROR_PARA_CHECK_FAIL;
     }
@@ -145,6 +168,16 @@ int TileXRMoeEpDispatchFused(const TileXREpDispatchParams *p, TileXRCommPtr comm
     }
     ret = ValidateShape(p->bs, p->h, p->topK, p->moeExpertNum, c.rankSize, p->dtype);
     if (ret != TILEXR_SUCCESS) return ret;
+    EpTopology topo;
+    ret = MakeTopology(p->moeExpertNum, p->topK, c.rankSize, p->sharedExpertNum, p->sharedExpertRankNum, &topo);
+    if (ret != TILEXR_SUCCESS) return ret;
+    const int64_t numCols = topo.sharedRanks + p->moeExpertNum;
+    const int64_t routesPerToken = p->topK + topo.sharedExperts;
+    const int64_t smemCols = std::max<int64_t>(numCols, static_cast<int64_t>(topo.moePerRank) * c.rankSize);
+    if (p->bs * routesPerToken > TILEXR_FLAG_SLOT_SLOTS) {
+        TILEXR_LOG(ERROR) << "EP: bs * (topK + sharedExpertNum) exceeds the " << TILEXR_FLAG_SLOT_SLOTS << " slot flags of a window";
+        return TILEXR_ERROR_PARA_CHECK_FAIL;
+    }
     const bool fp8Mode = p->quantMode == TILEXR_EP_QUANT_FP8_1X128 || p->quantMode == TILEXR_EP_QUANT_MXFP8_E4M3 ||
                          p->quantMode == TILEXR_EP_QUANT_MXFP8_E5M2;
     const bool int8Mode = p->quantMode == TILEXR_EP_QUANT_STATIC_INT8 || p->quantMode == TILEXR_EP_QUANT_DYNAMIC_INT8;
@@ -186,12 +219,12 @@ int TileXRMoeEpDispatchFused(const TileXREpDispatchParams *p, TileXRCommPtr comm
     size_t smem = 0;
     for (;;) {
         tokensPerBlock = static_cast<uint32_t>((p->bs + grid - 1) / grid);
-        if (static_cast<int64_t>(tokensPerBlock) * p->topK > EP_MAX_ROUTES_PER_BLOCK) {
+        if (static_cast<int64_t>(tokensPerBlock) * routesPerToken > EP_MAX_ROUTES_PER_BLOCK) {
             TILEXR_LOG(ERROR) << "EP dispatch: " << tokensPerBlock << " tokens per block exceed the per-block route table; "
                               << "raise TILEXR_EP_BLOCKS";
             return TILEXR_ERROR_NOT_SUPPORT;
         }
-        smem = EpDispatchSmemBytes(static_cast<int>(p->moeExpertNum), static_cast<int>(tokensPerBlock * p->topK));
+        smem = EpDispatchSmemBytes(static_cast<int>(smemCols), static_cast<int>(tokensPerBlock * routesPerToken));
         unsigned maxGrid = 0;
         ret = MaxCooperativeGrid(comm, EpDispatchKernelEntry(), EP_BLOCK_THREADS, smem, ranksPerDevice, &maxGrid);
         if (ret != TILEXR_SUCCESS) return ret;
@@ -212,7 +245,7 @@ int TileXRMoeEpDispatchFused(const TileXREpDispatchParams *p, TileXRCommPtr comm
 
     EpDispatchArgs a;
     std::memset(&a, 0, sizeof(a));
-    if (!DispatchLayout(p->h, p->moeExpertNum, c.rankSize, p->maxRecvRows, p->quantMode, elemSize, grid, zeroCopy, &a.win)) {
+    if (!DispatchLayout(p->h, numCols, c.rankSize, p->maxRecvRows, p->quantMode, elemSize, grid, zeroCopy, &a.win)) {
         return TILEXR_ERROR_PARA_CHECK_FAIL;
     }
     if (a.win.totalBytes > c.hostArgs->dataHalfBytes) {
@@ -238,7 +271,8 @@ int TileXRMoeEpDispatchFused(const TileXREpDispatchParams *p, TileXRCommPtr comm
     a.h = static_cast<int32_t>(p->h);
     a.topK = static_cast<int32_t>(p->topK);
     a.numExperts = static_cast<int32_t>(p->moeExpertNum);
-    a.expertsPerRank = static_cast<int32_t>(p->moeExpertNum / c.rankSize);
+    a.numCols = static_cast<int32_t>(numCols);
+    a.topo = topo;
     a.maskType = static_cast<int32_t>(p->activeMaskType);
     a.quantMode = static_cast<int32_t>(p->quantMode);
     a.scoreFunc = static_cast<int32_t>(p->scoreFunc);
@@ -286,7 +320,12 @@ int TileXRMoeEpCombineFused(const TileXREpCombineParams *p, TileXRCommPtr comm, 
     ret = ValidateShape(p->bs, p->h, p->topK, p->moeExpertNum, c.rankSize, p->dtype);
     if (ret != TILEXR_SUCCESS) return ret;
     if (p->activeMaskType != TILEXR_EP_ACTIVE_MASK_NONE && p->xActiveMask == nullptr) return TILEXR_ERROR_PARA_CHECK_FAIL;
-    const uint64_t need = TileXREpCombineWindowBytes(p->bs, p->h, p->topK, 2);
+    EpTopology topo;
+    ret = MakeTopology(p->moeExpertNum, p->topK, c.rankSize, p->sharedExpertNum, p->sharedExpertRankNum, &topo);
+    if (ret != TILEXR_SUCCESS) return ret;
+    const int64_t slotsPerToken = p->topK + topo.sharedExperts;
+    if (p->bs * slotsPerToken > TILEXR_FLAG_SLOT_SLOTS) return TILEXR_ERROR_PARA_CHECK_FAIL;
+    const uint64_t need = TileXREpCombineWindowBytes(p->bs, p->h, slotsPerToken, 2);
     if (need > c.hostArgs->dataHalfBytes) {
         TILEXR_LOG(ERROR) << "EP combine needs " << need << " bytes of window per half, the communicator has "
                           << c.hostArgs->dataHalfBytes;
@@ -307,11 +346,12 @@ int TileXRMoeEpCombineFused(const TileXREpCombineParams *p, TileXRCommPtr comm, 
     a.h = static_cast<int32_t>(p->h);
     a.topK = static_cast<int32_t>(p->topK);
     a.numExperts = static_cast<int32_t>(p->moeExpertNum);
-    a.expertsPerRank = static_cast<int32_t>(p->moeExpertNum / c.rankSize);
+    a.numCols = static_cast<int32_t>(topo.sharedRanks + p->moeExpertNum);
+    a.topo = topo;
     a.maskType = static_cast<int32_t>(p->activeMaskType);
     a.rowBytes = static_cast<uint32_t>(p->h * 2);
     a.isBf16 = p->dtype == TILEXR_DATA_TYPE_BFP16 ? 1u : 0u;
-    a.sendCountEntries = static_cast<uint32_t>(p->moeExpertNum / c.rankSize * c.rankSize);
+    a.sendCountEntries = static_cast<uint32_t>(EpRankCols(topo, c.rank) * c.rankSize);
     a.routeRows = p->expertIds != nullptr ? p->routeRows : nullptr;
     a.dedup = (p->dedup != 0 && c.rankSize > 1) ? 1u : 0u;
     a.assistExt = p->assistExt;
@@ -327,7 +367,7 @@ int TileXRMoeEpCombineFused(const TileXREpCombineParams *p, TileXRCommPtr comm, 
     unsigned maxGrid = 0;
     ret = MaxCooperativeGrid(comm, EpCombineKernelEntry(), EP_BLOCK_THREADS, 0, ranksPerDevice, &maxGrid);
     if (ret != TILEXR_SUCCESS) return ret;
-    const int64_t want = std::min<int64_t>(EnvLong("TILEXR_EP_BLOCKS", 296), std::max<int64_t>(1, (p->bs * p->topK + 15) / 16));
+    const int64_t want = std::min<int64_t>(EnvLong("TILEXR_EP_BLOCKS", 296), std::max<int64_t>(1, (p->bs * slotsPerToken + 15) / 16));
     const unsigned grid = static_cast<unsigned>(std::max<int64_t>(1, std::min<int64_t>(want, maxGrid)));
     {
         PerfLaunchInfo info{static_cast<uint32_t>(TILEXR_OP_EP_COMBINE), static_cast<uint32_t>(p->dtype),
@@ -367,11 +407,6 @@ int TileXRMoeEpDispatchMemoryV2(void *x, int32_t *expertIds, void *scales, bool 
         TILEXR_LOG(ERROR) << "EP dispatch: tpWorldSize must be 1";
         return TILEXR_ERROR_NOT_SUPPORT;
     }
-    if (sharedExpertNum != 0 || sharedExpertRankNum != 0) {
-        TILEXR_LOG(ERROR) << "EP dispatch: dedicated shared-expert ranks are not supported; add the shared expert's "
-                          << "output through sharedExpertX in combine";
-        return TILEXR_ERROR_NOT_SUPPORT;
-    }
     if (epWorldSize != c.rankSize || epRankId != c.rank) return TILEXR_ERROR_PARA_CHECK_FAIL;
     if (globalBs != 0 && globalBs != bs * c.rankSize) {
         TILEXR_LOG(ERROR) << "EP dispatch: globalBs must be bs * epWorldSize";
@@ -396,7 +431,10 @@ int TileXRMoeEpDispatchMemoryV2(void *x, int32_t *expertIds, void *scales, bool 
     p.moeExpertNum = moeExpertNum;
     p.quantMode = quantMode;
     p.expertTokenNumsType = expertTokenNumsType;
-    p.maxRecvRows = bs * c.rankSize * std::min<int64_t>(topK, moeExpertNum / c.rankSize);   // worst case, as the reference sizes it
+    p.sharedExpertNum = sharedExpertNum;
+    p.sharedExpertRankNum = sharedExpertRankNum;
+    // worst case, as the reference sizes it: every token of every rank with all its routes on this rank
+    p.maxRecvRows = bs * c.rankSize * std::min<int64_t>(topK, moeExpertNum / std::max<int64_t>(1, c.rankSize - sharedExpertRankNum));
     p.expandXOut = expandXOut;
     p.dynamicScalesOut = static_cast<float *>(dynamicScalesOut);
     p.assistInfoForCombineOut = assistInfoForCombineOut;
@@ -461,7 +499,7 @@ int TileXRMoeEpCombineMemoryV2(void *expertOut, int32_t *assistInfoForCombine, i
     Ctx c;
     int ret = Prepare(comm, &c);
     if (ret != TILEXR_SUCCESS) return ret;
-    if (tpWorldSize > 1 || sharedExpertNum != 0 || sharedExpertRankNum != 0) return TILEXR_ERROR_NOT_SUPPORT;
+    if (tpWorldSize > 1) return TILEXR_ERROR_NOT_SUPPORT;
     if (quantMode != TILEXR_EP_QUANT_NONE) {
         TILEXR_LOG(ERROR) << "EP combine: rows travel in their own dtype; communication quantisation is not supported";
         return TILEXR_ERROR_NOT_SUPPORT;
@@ -476,6 +514,8 @@ int TileXRMoeEpCombineMemoryV2(void *expertOut, int32_t *assistInfoForCombine, i
     p.xActiveMask = xActiveMask;
     p.activeMaskType = activeMaskType;
     p.sharedExpertX = sharedExpertX;
+    p.sharedExpertNum = sharedExpertNum;
+    p.sharedExpertRankNum = sharedExpertRankNum;
     p.bs = bs;
     p.h = h;
     p.topK = topK;

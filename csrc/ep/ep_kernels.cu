@@ -295,15 +295,18 @@ __device__ void EpDispatchBody(const EpDispatchArgs &a)
     CommArgs *comm = a.comm;
     const int rank = comm->rank;
     const int R = comm->rankSize;
-    const int E = a.numExperts;
+    const int E = a.numExperts;          // routed experts (what the router chooses from)
+    const int C = a.numCols;             // columns of the count tables: shared ranks first, then the routed experts
     const int K = a.topK;
+    const int KR = K + a.topo.sharedExperts;   // routes per token: top-k and one per shared expert
     const int G = gridDim.x;
     const int tid = threadIdx.x;
     const int lane = tid & 31;
     const int warp = tid >> 5;
     const uint32_t epoch = w.epoch;
-    const int routesPerBlock = static_cast<int>(a.tokensPerBlock) * K;
-    DispatchSmem sm = CarveSmem(smemRaw, E, routesPerBlock);
+    const int routesPerBlock = static_cast<int>(a.tokensPerBlock) * KR;
+    // the tables also serve as scratch for the final scan over (local expert, source): moePerRank * R numbers
+    DispatchSmem sm = CarveSmem(smemRaw, max(C, a.topo.moePerRank * R), routesPerBlock);
     uint8_t *myHalf = DataHalf(comm, rank, epoch);
     PerfScope perf = PerfInit(tid == 0 ? a.perfTrace : nullptr, static_cast<uint32_t>(rank), blockIdx.x);
     PerfStageBegin(perf, TILEXR_PERF_KERNEL_TOTAL);
@@ -314,10 +317,10 @@ __device__ void EpDispatchBody(const EpDispatchArgs &a)
     const int t0 = min(a.bs, static_cast<int>(blockIdx.x * a.tokensPerBlock));
     const int t1 = min(a.bs, t0 + static_cast<int>(a.tokensPerBlock));
     const int nTok = t1 - t0;
-    const int nRoutes = nTok * K;
+    const int nRoutes = nTok * KR;
 
-    // ---- 1. route, rank, count --------------------------------------------------------------------
-    for (int e = tid; e < E; e += blockDim.x) sm.hist[e] = 0;
+    // ---- 1. route, rank, count (routeExpert holds the COLUMN of a route, -1 when inactive) ---------------
+    for (int e = tid; e < C; e += blockDim.x) sm.hist[e] = 0;
     for (int i = warp; i < nTok; i += EP_WARPS) {
         const int t = t0 + i;
         if (a.gateLogits != nullptr) {
@@ -332,8 +335,12 @@ __device__ void EpDispatchBody(const EpDispatchArgs &a)
             if (e < 0 || e >= E) e = -1;
             if (a.maskType == TileXREp::TILEXR_EP_ACTIVE_MASK_TOKEN && a.activeMask[t] == 0) e = -1;
             if (a.maskType == TileXREp::TILEXR_EP_ACTIVE_MASK_EXPERT && a.activeMask[static_cast<int64_t>(t) * K + lane] == 0) e = -1;
-            sm.routeExpert[i * K + lane] = e;
+            sm.routeExpert[i * KR + lane] = e >= 0 ? a.topo.sharedRanks + e : -1;
             if (a.gateLogits == nullptr && a.topkIdsOut != nullptr) a.topkIdsOut[static_cast<int64_t>(t) * K + lane] = e;
+        } else if (lane < KR) {
+            // every active token also goes to its copy of each shared expert
+            const bool active = !(a.maskType == TileXREp::TILEXR_EP_ACTIVE_MASK_TOKEN && a.activeMask[t] == 0);
+            sm.routeExpert[i * KR + lane] = active ? EpSharedCol(a.topo, rank, lane - K) : -1;
         }
     }
     __syncthreads();
@@ -347,7 +354,7 @@ __device__ void EpDispatchBody(const EpDispatchArgs &a)
         sm.routeRank[i] = r;
     }
     __syncthreads();
-    for (int e = tid; e < E; e += blockDim.x) blockCounts[static_cast<int64_t>(blockIdx.x) * E + e] = sm.hist[e];
+    for (int e = tid; e < C; e += blockDim.x) blockCounts[static_cast<int64_t>(blockIdx.x) * C + e] = sm.hist[e];
     PerfStageEnd(perf, TILEXR_PERF_CHUNK_TOTAL);
     PerfStageBegin(perf, TILEXR_PERF_CHUNK_BARRIER);
     ok = GridBarrier(w, 0) && ok;
@@ -356,16 +363,16 @@ __device__ void EpDispatchBody(const EpDispatchArgs &a)
 
     // ---- 2. publish this rank's counts, learn everybody's ----------------------------------------------
     if (ok && blockIdx.x == 0) {
-        SumBlockCounts(blockCounts, E, G, sm.total, tid, blockDim.x);
-        for (int e = tid; e < E; e += blockDim.x) {
+        SumBlockCounts(blockCounts, C, G, sm.total, tid, blockDim.x);
+        for (int e = tid; e < C; e += blockDim.x) {
             const int c = sm.total[e];
             for (int i = 0; i < R; ++i) {
                 const int peer = (rank + i) % R;
-                reinterpret_cast<int32_t *>(DataHalf(comm, peer, epoch) + a.win.countOff)[static_cast<int64_t>(rank) * E + e] = c;
+                reinterpret_cast<int32_t *>(DataHalf(comm, peer, epoch) + a.win.countOff)[static_cast<int64_t>(rank) * C + e] = c;
             }
         }
         if (tid < R) {
-            reinterpret_cast<int32_t *>(DataHalf(comm, tid, epoch) + a.win.countOff)[static_cast<int64_t>(R) * E + rank] = G;
+            reinterpret_cast<int32_t *>(DataHalf(comm, tid, epoch) + a.win.countOff)[static_cast<int64_t>(R) * C + rank] = G;
         }
         __syncthreads();
         if (tid < R) {
@@ -373,7 +380,7 @@ __device__ void EpDispatchBody(const EpDispatchArgs &a)
                     epoch, 1);
         }
     }
-    SumBlockCounts(blockCounts, E, ok ? static_cast<int>(blockIdx.x) : 0, sm.blockBase, tid, blockDim.x);
+    SumBlockCounts(blockCounts, C, ok ? static_cast<int>(blockIdx.x) : 0, sm.blockBase, tid, blockDim.x);
     {
         bool got = true;
         if (ok && tid < R) {
@@ -383,24 +390,25 @@ __device__ void EpDispatchBody(const EpDispatchArgs &a)
         ok = BlockBroadcastOk(got) && ok;
     }
     if (ok) {
-        for (int e = tid; e < E; e += blockDim.x) {
+        for (int e = tid; e < C; e += blockDim.x) {
             int c = 0;
-            for (int s = 0; s < R; ++s) c += countMatrix[static_cast<int64_t>(s) * E + e];
+            for (int s = 0; s < R; ++s) c += countMatrix[static_cast<int64_t>(s) * C + e];
             sm.total[e] = c;
         }
         __syncthreads();
-        for (int e = tid; e < E; e += blockDim.x) {
-            const int first = (e / a.expertsPerRank) * a.expertsPerRank;
+        for (int e = tid; e < C; e += blockDim.x) {
+            const int first = EpRankFirstCol(a.topo, EpColRank(a.topo, e));
             int row = 0;
             for (int p = first; p < e; ++p) row += sm.total[p];
-            for (int s = 0; s < rank; ++s) row += countMatrix[static_cast<int64_t>(s) * E + e];
+            for (int s = 0; s < rank; ++s) row += countMatrix[static_cast<int64_t>(s) * C + e];
             sm.dstRow[e] = row;
         }
         // Every rank sees the same counts, so every rank reaches the same verdict on overflow.
         bool fits = true;
         if (tid < R) {
             int64_t rows = 0;
-            for (int e = tid * a.expertsPerRank; e < (tid + 1) * a.expertsPerRank; ++e) rows += sm.total[e];
+            const int firstCol = EpRankFirstCol(a.topo, tid);
+            for (int e = firstCol; e < firstCol + EpRankCols(a.topo, tid); ++e) rows += sm.total[e];
             fits = rows <= static_cast<int64_t>(a.maxRecvRows);
             if (!fits) RaiseFailure(w, TILEXR_DEV_BAD_ARGUMENT, tid, 0, a.maxRecvRows, static_cast<uint64_t>(rows));
         }
@@ -431,11 +439,11 @@ __device__ void EpDispatchBody(const EpDispatchArgs &a)
             unsigned long long myPayload = 0, myHalf = 0;
             uint32_t myRow = 0;
             int myExpert = -1;
-            if (lane < K) {
-                const int e = sm.routeExpert[i * K + lane];
+            if (lane < KR) {
+                const int e = sm.routeExpert[i * KR + lane];
                 if (e >= 0) {
-                    const int dst = e / a.expertsPerRank;
-                    myRow = static_cast<uint32_t>(sm.dstRow[e] + sm.blockBase[e] + sm.routeRank[i * K + lane]);
+                    const int dst = EpColRank(a.topo, e);
+                    myRow = static_cast<uint32_t>(sm.dstRow[e] + sm.blockBase[e] + sm.routeRank[i * KR + lane]);
                     uint8_t *half = DataHalf(comm, dst, epoch);
                     uint8_t *payload = a.zeroCopy
                                            ? comm->registryPtr->regions[a.outHandle].peerBase[dst] + a.outOffset +
@@ -446,18 +454,18 @@ __device__ void EpDispatchBody(const EpDispatchArgs &a)
                     myExpert = e;
                 }
             }
-            if (lane < K && a.routeRowsOut != nullptr && part == 0) {
-                a.routeRowsOut[static_cast<int64_t>(t) * K + lane] = myExpert >= 0 ? static_cast<int32_t>(myRow) : -1;
+            if (lane < KR && a.routeRowsOut != nullptr && part == 0) {
+                a.routeRowsOut[static_cast<int64_t>(t) * KR + lane] = myExpert >= 0 ? static_cast<int32_t>(myRow) : -1;
             }
             const uint32_t routes = __ballot_sync(0xffffffffu, myExpert >= 0);
             if (routes == 0) continue;
             // Routes of this token to one remote rank form a group: the lowest k (the head) carries the
             // payload, the others only their tuple, and every member links to the next one.
-            const int myDst = myExpert >= 0 ? myExpert / a.expertsPerRank : -1;
+            const int myDst = myExpert >= 0 ? EpColRank(a.topo, myExpert) : -1;
             uint32_t myLink = 0;
             if (a.dedup != 0) {
                 bool follower = false;
-                for (int j = 0; j < K; ++j) {
+                for (int j = 0; j < KR; ++j) {
                     const int dj = __shfl_sync(0xffffffffu, myDst, j);
                     const uint32_t rj = __shfl_sync(0xffffffffu, myRow, j);
                     if (dj >= 0 && dj == myDst && myDst != rank) {
@@ -480,7 +488,8 @@ __device__ void EpDispatchBody(const EpDispatchArgs &a)
                     uint8_t *half = reinterpret_cast<uint8_t *>(__shfl_sync(0xffffffffu, myHalf, k));
                     const uint32_t rr = __shfl_sync(0xffffffffu, myRow, k);
                     const int e = __shfl_sync(0xffffffffu, myExpert, k);
-                    const float *sc = a.quantScales != nullptr ? a.quantScales + static_cast<int64_t>(e) * a.h : nullptr;
+                    const float *sc = (a.quantScales != nullptr && e >= a.topo.sharedRanks)
+                                          ? a.quantScales + static_cast<int64_t>(e - a.topo.sharedRanks) * a.h : nullptr;
                     float inv = 1.0f;
                     if (int8Dynamic) {
                         float amax = 0.f;
@@ -626,10 +635,11 @@ __device__ void EpDispatchBody(const EpDispatchArgs &a)
             if (myExpert >= 0 && part == 0) {
                 st_vec16(reinterpret_cast<uint8_t *>(myHalf) + a.win.assistOff + static_cast<uint64_t>(myRow) * 16,
                          Vec16{static_cast<uint32_t>(rank), static_cast<uint32_t>(t), static_cast<uint32_t>(lane),
-                               static_cast<uint32_t>(myExpert)});
+                               static_cast<uint32_t>(lane < K ? myExpert - a.topo.sharedRanks : lane - K)});   // routed expert id, or shared expert id
                 const int64_t route = static_cast<int64_t>(t) * K + lane;
-                const float wgt = a.gateLogits != nullptr ? a.topkWeightsOut[route]
-                                                           : (a.expertScales != nullptr ? a.expertScales[route] : 1.0f);
+                const float wgt = lane >= K ? 1.0f
+                                  : a.gateLogits != nullptr ? a.topkWeightsOut[route]
+                                                            : (a.expertScales != nullptr ? a.expertScales[route] : 1.0f);
                 *reinterpret_cast<uint2 *>(reinterpret_cast<uint8_t *>(myHalf) + a.win.extOff + static_cast<uint64_t>(myRow) * 8) =
                     make_uint2(myLink, __float_as_uint(wgt));
             }
@@ -650,7 +660,7 @@ __device__ void EpDispatchBody(const EpDispatchArgs &a)
         if (ok) {
             for (int s = 0; s < R && got; ++s) {
                 const int64_t base = TILEXR_FLAG_OP_BASE + static_cast<int64_t>(s) * TILEXR_FLAGS_PER_PAIR;
-                const int blocksOfS = min(countMatrix[static_cast<int64_t>(R) * E + s], static_cast<int>(EP_COUNT_FLAG_SLOT));
+                const int blocksOfS = min(countMatrix[static_cast<int64_t>(R) * C + s], static_cast<int>(EP_COUNT_FLAG_SLOT));
                 for (int b = tid; b < blocksOfS && got; b += blockDim.x) {
                     got = WaitFlagGE(w, FlagSlot(comm, rank, base + b), 1, s, base + b);
                 }
@@ -661,9 +671,10 @@ __device__ void EpDispatchBody(const EpDispatchArgs &a)
     PerfStageEnd(perf, TILEXR_PERF_FLAG_POLL_WAIT);
     PerfStageBegin(perf, TILEXR_PERF_PEER_IPC_TO_OUTPUT);
     if (ok) {
-        const int firstLocal = rank * a.expertsPerRank;
+        const int firstLocal = EpRankFirstCol(a.topo, rank);
+        const int localCols = EpRankCols(a.topo, rank);
         int64_t rows = 0;
-        for (int e = firstLocal; e < firstLocal + a.expertsPerRank; ++e) rows += sm.total[e];
+        for (int e = firstLocal; e < firstLocal + localCols; ++e) rows += sm.total[e];
         // Rows are dealt out to blocks in chunks of one row per thread.  Per chunk: (a) a thread per row copies
         // the tuple, link and weight and notes the head rows that have followers; (b) a thread per 16 bytes
         // copies the scales of the rows that arrived with a payload; (c) without zero-copy a warp per row moves
@@ -718,7 +729,7 @@ __device__ void EpDispatchBody(const EpDispatchArgs &a)
                 const int64_t r = base + sHead[u];
                 const uint8_t *src = a.zeroCopy ? a.expandXOut + r * a.win.rowBytes : winPayload + r * a.win.rowBytes;
                 uint32_t next = reinterpret_cast<const uint2 *>(winExt + r * 8)->x & EP_LINK_NEXT_MASK;
-                for (int hop = 0; next != 0 && hop < K; ++hop) {
+                for (int hop = 0; next != 0 && hop < KR; ++hop) {
                     const int64_t f = static_cast<int64_t>(next) - 1;
                     if (f >= static_cast<int64_t>(a.maxRecvRows)) break;
                     CopyLanes(a.expandXOut + f * a.win.rowBytes, src, a.win.rowBytes, lane, 32);
@@ -735,9 +746,9 @@ __device__ void EpDispatchBody(const EpDispatchArgs &a)
         }
         if (blockIdx.x == 0) {
             // cumulative counts in (local expert, source) order: an inclusive scan of E_local * R numbers
-            const int n = a.expertsPerRank * R;
+            const int n = localCols * R;
             __syncthreads();
-            for (int i = tid; i < n; i += blockDim.x) sm.hist[i] = countMatrix[static_cast<int64_t>(i % R) * E + firstLocal + i / R];
+            for (int i = tid; i < n; i += blockDim.x) sm.hist[i] = countMatrix[static_cast<int64_t>(i % R) * C + firstLocal + i / R];
             __syncthreads();
             if (warp == 0) {
                 int carry = 0;
@@ -755,7 +766,7 @@ __device__ void EpDispatchBody(const EpDispatchArgs &a)
             }
             __syncthreads();
             for (int i = tid; i < n; i += blockDim.x) a.sendCountsOut[i] = sm.hist[i];
-            for (int le = tid; le < a.expertsPerRank; le += blockDim.x) {
+            for (int le = tid; le < localCols; le += blockDim.x) {
                 a.expertTokenNumsOut[le] = a.tokenNumsType == TileXREp::TILEXR_EP_TOKEN_NUMS_COUNT
                                                ? static_cast<int64_t>(sm.total[firstLocal + le])
                                                : static_cast<int64_t>(sm.hist[le * R + R - 1]);
@@ -777,6 +788,7 @@ __device__ void EpCombineBody(const EpCombineArgs &a)
     CommArgs *comm = a.comm;
     const int rank = comm->rank;
     const int K = a.topK;
+    const int KR = K + a.topo.sharedExperts;     // slots per token: top-k routes and one per shared expert
     const int lane = threadIdx.x & 31;
     const int warpsPerBlock = blockDim.x >> 5;
     const int64_t gwarp = static_cast<int64_t>(blockIdx.x) * warpsPerBlock + (threadIdx.x >> 5);
@@ -810,8 +822,8 @@ __device__ void EpCombineBody(const EpCombineArgs &a)
                 if (r < rows) {
                     const Vec16 tuple = ld_vec16(a.assist + r * 4);
                     const int src = static_cast<int>(tuple.x);
-                    const int64_t slot = static_cast<int64_t>(tuple.y) * K + tuple.z;
-                    bool send = src >= 0 && src < comm->rankSize && slot >= 0 && slot < static_cast<int64_t>(a.bs) * K;
+                    const int64_t slot = static_cast<int64_t>(tuple.y) * KR + tuple.z;
+                    bool send = src >= 0 && src < comm->rankSize && slot >= 0 && slot < static_cast<int64_t>(a.bs) * KR;
                     if (direct && src == rank) send = false;
                     if (send && a.dedup != 0 && (static_cast<uint32_t>(a.assistExt[r * 2]) & EP_LINK_FOLLOWER) != 0) send = false;
                     if (send) sUnit[atomicAdd(&sUnitCount, 1)] = static_cast<int32_t>(r);
@@ -830,7 +842,7 @@ __device__ void EpCombineBody(const EpCombineArgs &a)
                 if (vBegin >= vEnd) continue;
                 const Vec16 tuple = ld_vec16(a.assist + r * 4);
                 const int src = static_cast<int>(tuple.x);
-                const int64_t slot = static_cast<int64_t>(tuple.y) * K + tuple.z;
+                const int64_t slot = static_cast<int64_t>(tuple.y) * KR + tuple.z;
                 uint2 ext = make_uint2(0u, 0u);
                 if (a.dedup != 0) ext = *reinterpret_cast<const uint2 *>(a.assistExt + r * 2);
                 uint8_t *dst = DataHalf(comm, src, epoch) + slot * a.rowBytes;
@@ -845,7 +857,7 @@ __device__ void EpCombineBody(const EpCombineArgs &a)
                     int members = 0;
                     int64_t cur = r;
                     uint2 e2 = ext;
-                    while (members < K) {
+                    while (members < KR) {
                         if (lane == members) {
                             memberRow = cur;
                             memberW = __uint_as_float(e2.y);
@@ -886,7 +898,7 @@ __device__ void EpCombineBody(const EpCombineArgs &a)
             // every part of a row is stored: one thread per row releases its flag
             for (int u = tid; u < units; u += blockDim.x) {
                 const Vec16 tuple = ld_vec16(a.assist + static_cast<int64_t>(sUnit[u]) * 4);
-                const int64_t slot = static_cast<int64_t>(tuple.y) * K + tuple.z;
+                const int64_t slot = static_cast<int64_t>(tuple.y) * KR + tuple.z;
                 SetFlag(FlagSlot(comm, static_cast<int>(tuple.x), TILEXR_FLAG_SLOT_BASE + slot), epoch, 1);
             }
         }
@@ -899,18 +911,25 @@ __device__ void EpCombineBody(const EpCombineArgs &a)
             int e = -1;
             float wk = 0.f;
             unsigned long long myRowPtr = 0;
+            // `e` is the COLUMN of the route (shared ranks first, then routed experts), -1 when inactive
             if (lane < K) {
                 e = a.expertIds != nullptr ? a.expertIds[t * K + lane] : 0;
                 if (e >= a.numExperts) e = -1;
                 if (a.maskType == TileXREp::TILEXR_EP_ACTIVE_MASK_TOKEN && a.activeMask[t] == 0) e = -1;
                 if (a.maskType == TileXREp::TILEXR_EP_ACTIVE_MASK_EXPERT && a.activeMask[t * K + lane] == 0) e = -1;
+                if (e >= 0) e += a.topo.sharedRanks;
                 wk = a.expertScales != nullptr ? a.expertScales[t * K + lane] : 1.0f;
+            } else if (lane < KR) {
+                // the shared experts' outputs are added with weight one
+                const bool activeTok = !(a.maskType == TileXREp::TILEXR_EP_ACTIVE_MASK_TOKEN && a.activeMask[t] == 0);
+                e = activeTok ? EpSharedCol(a.topo, rank, lane - K) : -1;
+                wk = 1.0f;
             }
+            const int myDst = e >= 0 ? EpColRank(a.topo, e) : -1;
             if (a.dedup != 0) {
                 // routes to one remote rank come back as one weighted sum in the slot of the lowest k
-                const int myDst = e >= 0 ? e / a.expertsPerRank : -1;
                 bool lower = false, higher = false;
-                for (int j = 0; j < K; ++j) {
+                for (int j = 0; j < KR; ++j) {
                     const int dj = __shfl_sync(0xffffffffu, myDst, j);
                     if (dj >= 0 && dj == myDst && myDst != rank) {
                         if (j < lane) lower = true;
@@ -920,15 +939,15 @@ __device__ void EpCombineBody(const EpCombineArgs &a)
                 if (lower) e = -1;
                 else if (higher) wk = 1.0f;
             }
-            if (lane < K) {
+            if (lane < KR) {
                 if (e >= 0) {
-                    const int64_t slot = t * K + lane;
-                    const int64_t localRow = direct && e / a.expertsPerRank == rank ? a.routeRows[slot] : -1;
+                    const int64_t slot = t * KR + lane;
+                    const int64_t localRow = direct && myDst == rank ? a.routeRows[slot] : -1;
                     if (localRow >= 0 && localRow < rows) {
                         myRowPtr = reinterpret_cast<unsigned long long>(a.expertOut + localRow * a.rowBytes);
                     } else {
                         myRowPtr = reinterpret_cast<unsigned long long>(half + slot * a.rowBytes);
-                        WaitFlagGE(w, FlagSlot(comm, rank, TILEXR_FLAG_SLOT_BASE + slot), 1, e / a.expertsPerRank, slot);
+                        WaitFlagGE(w, FlagSlot(comm, rank, TILEXR_FLAG_SLOT_BASE + slot), 1, myDst, slot);
                     }
                 }
             }
@@ -946,13 +965,13 @@ __device__ void EpCombineBody(const EpCombineArgs &a)
 #pragma unroll
                 for (int j = 0; j < 8; ++j) acc[j] = 0.f;
                 // the rows of up to eight routes are fetched together, then accumulated in k order
-                for (int k0 = 0; k0 < K; k0 += 8) {
+                for (int k0 = 0; k0 < KR; k0 += 8) {
                     Vec16 q[8];
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
                         const int k = k0 + j;
                         q[j] = Vec16{0u, 0u, 0u, 0u};
-                        if (k < K && ((active >> k) & 1u)) {
+                        if (k < KR && ((active >> k) & 1u)) {
                             const uint8_t *src = reinterpret_cast<const uint8_t *>(__shfl_sync(0xffffffffu, myRowPtr, k));
                             if (mine) q[j] = ld_vec16_stream(src + v * 16);
                         }
@@ -960,7 +979,7 @@ __device__ void EpCombineBody(const EpCombineArgs &a)
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
                         const int k = k0 + j;
-                        if (k < K && ((active >> k) & 1u)) {
+                        if (k < KR && ((active >> k) & 1u)) {
                             const float wgt = __shfl_sync(0xffffffffu, wk, k);
                             float f[8];
                             Unpack8(q[j], bf16, f);

@@ -32,6 +32,36 @@ struct EpDispatchWindow {
     uint32_t scaleRowBytes;
 };
 
+// Which rank holds which expert.  The first `sharedRanks` ranks hold the shared experts (one each; shared expert
+// g is replicated on ranksPerShared = sharedRanks / sharedExperts ranks and a token of source rank s goes to
+// rank s % ranksPerShared + g * ranksPerShared), the others `moePerRank` routed experts each (reference:
+// tests/ep/demo/tilexr_ep_dispatch_demo.cpp:647-661).  Counts and row placement work on COLUMNS: column c <
+// sharedRanks is the shared expert held by rank c, column sharedRanks + e is routed expert e.
+#if defined(__CUDACC__)
+#define TXR_EP_HD __host__ __device__
+#else
+#define TXR_EP_HD
+#endif
+struct EpTopology {
+    int32_t sharedRanks;
+    int32_t sharedExperts;
+    int32_t moePerRank;
+};
+TXR_EP_HD inline int EpColRank(const EpTopology &t, int col)
+{
+    return col < t.sharedRanks ? col : t.sharedRanks + (col - t.sharedRanks) / t.moePerRank;
+}
+TXR_EP_HD inline int EpRankFirstCol(const EpTopology &t, int rank)
+{
+    return rank < t.sharedRanks ? rank : t.sharedRanks + (rank - t.sharedRanks) * t.moePerRank;
+}
+TXR_EP_HD inline int EpRankCols(const EpTopology &t, int rank) { return rank < t.sharedRanks ? 1 : t.moePerRank; }
+TXR_EP_HD inline int EpSharedCol(const EpTopology &t, int srcRank, int g)
+{
+    const int per = t.sharedRanks / t.sharedExperts;
+    return srcRank % per + g * per;
+}
+
 struct EpDispatchArgs {
     const uint8_t *x;
     const int32_t *expertIds;
@@ -49,7 +79,8 @@ struct EpDispatchArgs {
     CommArgs *comm;
     int64_t magic;
     EpDispatchWindow win;
-    int32_t bs, h, topK, numExperts, expertsPerRank;
+    int32_t bs, h, topK, numExperts, numCols;   // numCols = sharedRanks + numExperts
+    EpTopology topo;
     int32_t maskType, quantMode, scoreFunc, renormalize, tokenNumsType;
     float routedScale;
     uint32_t maxRecvRows;
@@ -79,7 +110,8 @@ struct EpCombineArgs {
     uint8_t *yOut;
     CommArgs *comm;
     int64_t magic;
-    int32_t bs, h, topK, numExperts, expertsPerRank;
+    int32_t bs, h, topK, numExperts, numCols;
+    EpTopology topo;
     int32_t maskType;
     uint32_t rowBytes;
     uint32_t isBf16;

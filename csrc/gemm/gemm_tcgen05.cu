@@ -451,33 +451,49 @@ __device__ void GemmBody(const GemmArgs &a)
                 const int rows = min(GEMM_BM, a.shardRows - mLocal * GEMM_BM);
                 const int cols = min(GEMM_BN, a.N - nBlock * GEMM_BN);
                 const int vecsPerRow = cols / 8;
-                for (int i = et; i < rows * vecsPerRow; i += 128) {
-                    const int r = i / vecsPerRow;
-                    const int v = i % vecsPerRow;
-                    const uint64_t off = (static_cast<uint64_t>(mLocal) * GEMM_BM + r) * rowBytes + (static_cast<uint64_t>(nBlock) * GEMM_BN + v * 8) * 2;
-                    float accv[8];
+                // four 16-byte columns per thread and step, all ranks' copies of them fetched before they are summed
+                // in rank order: enough loads in flight to run the tail of the kernel at memory speed
+                const int total = rows * vecsPerRow;
+                for (int i0 = et; i0 < total; i0 += 128 * 4) {
+                    float accv[4][8];
+                    uint64_t off[4];
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) accv[j] = 0.f;
+                    for (int q = 0; q < 4; ++q) {
+                        const int i = min(i0 + q * 128, total - 1);
+                        const int r = i / vecsPerRow;
+                        const int v = i % vecsPerRow;
+                        off[q] = (static_cast<uint64_t>(mLocal) * GEMM_BM + r) * rowBytes + (static_cast<uint64_t>(nBlock) * GEMM_BN + v * 8) * 2;
+                    }
                     for (int s = 0; s < ranks; ++s) {
-                        const Vec16 x = ld_vec16_stream(stage + static_cast<uint64_t>(s) * a.shardRows * rowBytes + off);
-                        const uint32_t wds[4] = {x.x, x.y, x.z, x.w};
+                        Vec16 x[4];
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            float lo, hi;
-                            if (bf16) {
-                                lo = __uint_as_float(wds[j] << 16);
-                                hi = __uint_as_float(wds[j] & 0xffff0000u);
-                            } else {
-                                const float2 f2 = __half22float2(*reinterpret_cast<const __half2 *>(&wds[j]));
-                                lo = f2.x;
-                                hi = f2.y;
+                        for (int q = 0; q < 4; ++q) x[q] = ld_vec16_stream(stage + static_cast<uint64_t>(s) * a.shardRows * rowBytes + off[q]);
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            const uint32_t wds[4] = {x[q].x, x[q].y, x[q].z, x[q].w};
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                float lo, hi;
+                                if (bf16) {
+                                    lo = __uint_as_float(wds[j] << 16);
+                                    hi = __uint_as_float(wds[j] & 0xffff0000u);
+                                } else {
+                                    const float2 f2 = __half22float2(*reinterpret_cast<const __half2 *>(&wds[j]));
+                                    lo = f2.x;
+                                    hi = f2.y;
+                                }
+                                accv[q][2 * j] = s == 0 ? lo : accv[q][2 * j] + lo;
+                                accv[q][2 * j + 1] = s == 0 ? hi : accv[q][2 * j + 1] + hi;
                             }
-                            accv[2 * j] = s == 0 ? lo : accv[2 * j] + lo;
-                            accv[2 * j + 1] = s == 0 ? hi : accv[2 * j + 1] + hi;
                         }
                     }
-                    st_vec16(a.c + off, Vec16{PackPair(accv[0], accv[1], bf16), PackPair(accv[2], accv[3], bf16),
-                                              PackPair(accv[4], accv[5], bf16), PackPair(accv[6], accv[7], bf16)});
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        if (i0 + q * 128 < total) {
+                            st_vec16(a.c + off[q], Vec16{PackPair(accv[q][0], accv[q][1], bf16), PackPair(accv[q][2], accv[q][3], bf16),
+                                                         PackPair(accv[q][4], accv[q][5], bf16), PackPair(accv[q][6], accv[q][7], bf16)});
+                        }
+                    }
                 }
             }
         }

@@ -60,7 +60,7 @@ typedef struct TileXREpDispatchParams {
     int64_t renormalize;           // divide the top-k scores by their sum
     float routedScalingFactor;     // multiplies the gate weights (0 is read as 1)
     int64_t expertTokenNumsType;
-    int64_t maxRecvRows;           // rows expandXOut can hold
+    int64_t maxRecvRows;           // rows expandXOut can hold; the SAME value on every rank (peers place rows by it)
     // outputs
     int32_t *topkIdsOut;           // [bs, topK]  (fused routing; may be null otherwise)
     float *topkWeightsOut;         // [bs, topK]  (fused routing)
@@ -83,6 +83,12 @@ typedef struct TileXREpDispatchParams {
     int64_t dedup;
     int32_t *assistExtOut;         // [maxRecvRows, 2] {link, weight bits} for combine; needed when dedup != 0
     const float *scales;           // int8 modes: [moeExpertNum, h] fp32 smoothing scales (required for static, optional for dynamic)
+    // Shared experts on dedicated ranks: the first sharedExpertRankNum ranks hold them (shared expert g on
+    // sharedExpertRankNum / sharedExpertNum of them), the other ranks hold moeExpertNum / (R - sharedExpertRankNum)
+    // routed experts each.  Every active token then has topK + sharedExpertNum routes; shared routes use slot
+    // topK + g and weight 1.  Per-rank outputs have one entry per expert the rank holds.
+    int64_t sharedExpertNum;
+    int64_t sharedExpertRankNum;
 } TileXREpDispatchParams;
 
 typedef struct TileXREpCombineParams {
@@ -104,6 +110,8 @@ typedef struct TileXREpCombineParams {
     // weights here and cross NVLink once; needs assistExt from dispatch and expertIds.
     int64_t dedup;
     const int32_t *assistExt;      // [rows, 2] from dispatch
+    int64_t sharedExpertNum;       // as given to dispatch
+    int64_t sharedExpertRankNum;
 } TileXREpCombineParams;
 
 int TileXRMoeEpDispatchFused(const TileXREpDispatchParams *params, TileXRCommPtr comm, TileXRStream stream);

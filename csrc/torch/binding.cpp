@@ -358,7 +358,7 @@ py::tuple EpDispatch(const CommPtr &c, const at::Tensor &x, const c10::optional<
                      const c10::optional<at::Tensor> &activeMask, int64_t topK, int64_t numExperts, int64_t quantMode,
                      int64_t scoreFunc, bool renormalize, double routedScale, int64_t tokenNumsType, int64_t maxRecvRows,
                      const c10::optional<at::Tensor> &expandXOut, const c10::optional<at::Tensor> &expertScales, bool dedup,
-                     const c10::optional<at::Tensor> &quantScales)
+                     const c10::optional<at::Tensor> &quantScales, int64_t sharedExpertNum, int64_t sharedExpertRankNum)
 {
     RequireContiguous(x, "x");
     Keep(expertScales);
@@ -371,7 +371,8 @@ py::tuple EpDispatch(const CommPtr &c, const at::Tensor &x, const c10::optional<
     Keep(activeMask);
     const int64_t bs = x.size(0), h = x.size(1);
     const int R = c->rankSize();
-    const int64_t localExperts = numExperts / R;
+    TORCH_CHECK(sharedExpertRankNum >= 0 && sharedExpertRankNum < R, "shared_expert_rank_num must leave ranks for the routed experts");
+    const int64_t localExperts = c->rank() < sharedExpertRankNum ? 1 : numExperts / (R - sharedExpertRankNum);
     auto i32 = x.options().dtype(at::kInt);
     const bool mx = quantMode == TileXREp::TILEXR_EP_QUANT_MXFP8_E4M3 || quantMode == TileXREp::TILEXR_EP_QUANT_MXFP8_E5M2;
     const bool int8 = quantMode == TileXREp::TILEXR_EP_QUANT_STATIC_INT8 || quantMode == TileXREp::TILEXR_EP_QUANT_DYNAMIC_INT8;
@@ -393,7 +394,7 @@ py::tuple EpDispatch(const CommPtr &c, const at::Tensor &x, const c10::optional<
     at::Tensor recvTotal = at::empty({1}, i32);
     at::Tensor topkIds = at::empty({bs, topK}, i32);
     at::Tensor topkWeights = at::empty({bs, topK}, x.options().dtype(at::kFloat));
-    at::Tensor routeRows = at::empty({bs, topK}, i32);
+    at::Tensor routeRows = at::empty({bs, topK + sharedExpertNum}, i32);
     at::Tensor assistExt = at::empty({maxRecvRows, 2}, i32);
     at::Tensor expandScales = at::empty({maxRecvRows}, x.options().dtype(at::kFloat));
     TileXREpDispatchParams p;
@@ -445,6 +446,8 @@ py::tuple EpDispatch(const CommPtr &c, const at::Tensor &x, const c10::optional<
         p.expertScales = expertScales->data_ptr<float>();
     }
     p.dedup = dedup ? 1 : 0;
+    p.sharedExpertNum = sharedExpertNum;
+    p.sharedExpertRankNum = sharedExpertRankNum;
     p.dtype = ToDtype(x.scalar_type());
     for (const at::Tensor &t : {expandX, scales, assist, tokenNums, sendCounts, recvTotal, topkIds, topkWeights, routeRows,
                                 assistExt, expandScales}) {
@@ -459,7 +462,8 @@ at::Tensor EpCombine(const CommPtr &c, const at::Tensor &expertOut, const at::Te
                      const c10::optional<at::Tensor> &expertIds, const c10::optional<at::Tensor> &expertScales,
                      const c10::optional<at::Tensor> &activeMask, const c10::optional<at::Tensor> &sharedExpertX, int64_t bs,
                      int64_t topK, int64_t numExperts, const c10::optional<at::Tensor> &yOut,
-                     const c10::optional<at::Tensor> &routeRows, const c10::optional<at::Tensor> &assistExt, bool dedup)
+                     const c10::optional<at::Tensor> &routeRows, const c10::optional<at::Tensor> &assistExt, bool dedup,
+                     int64_t sharedExpertNum, int64_t sharedExpertRankNum)
 {
     Keep(assistExt);
     RequireContiguous(expertOut, "expert_out");
@@ -487,8 +491,9 @@ at::Tensor EpCombine(const CommPtr &c, const at::Tensor &expertOut, const at::Te
     }
     p.sharedExpertX = PtrOrNull(sharedExpertX);
     if (routeRows.has_value() && routeRows->defined()) {
-        TORCH_CHECK(routeRows->scalar_type() == at::kInt && routeRows->is_contiguous() && routeRows->numel() == bs * topK,
-                    "route_rows must be contiguous int32 [bs, top_k]");
+        TORCH_CHECK(routeRows->scalar_type() == at::kInt && routeRows->is_contiguous() &&
+                        routeRows->numel() == bs * (topK + sharedExpertNum),
+                    "route_rows must be contiguous int32 [bs, top_k + shared_expert_num]");
         p.routeRows = routeRows->data_ptr<int32_t>();
     }
     if (assistExt.has_value() && assistExt->defined()) {
@@ -496,6 +501,8 @@ at::Tensor EpCombine(const CommPtr &c, const at::Tensor &expertOut, const at::Te
         p.assistExt = assistExt->data_ptr<int32_t>();
     }
     p.dedup = dedup ? 1 : 0;
+    p.sharedExpertNum = sharedExpertNum;
+    p.sharedExpertRankNum = sharedExpertRankNum;
     p.bs = bs;
     p.h = h;
     p.topK = topK;
@@ -653,12 +660,13 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m)
           py::arg("top_k") = 1, py::arg("num_experts") = 1, py::arg("quant_mode") = 0, py::arg("score_func") = 0,
           py::arg("renormalize") = true, py::arg("routed_scale") = 1.0, py::arg("token_nums_type") = 1,
           py::arg("max_recv_rows") = 0, py::arg("expand_x_out") = py::none(), py::arg("expert_scales") = py::none(),
-          py::arg("dedup") = false, py::arg("scales") = py::none());
+          py::arg("dedup") = false, py::arg("scales") = py::none(), py::arg("shared_expert_num") = 0,
+          py::arg("shared_expert_rank_num") = 0);
     m.def("ep_combine", &EpCombine, py::arg("comm"), py::arg("expert_out"), py::arg("assist"), py::arg("send_counts"),
           py::arg("expert_ids") = py::none(), py::arg("expert_scales") = py::none(), py::arg("active_mask") = py::none(),
           py::arg("shared_expert_x") = py::none(), py::arg("bs") = 0, py::arg("top_k") = 1, py::arg("num_experts") = 1,
           py::arg("y_out") = py::none(), py::arg("route_rows") = py::none(), py::arg("assist_ext") = py::none(),
-          py::arg("dedup") = false);
+          py::arg("dedup") = false, py::arg("shared_expert_num") = 0, py::arg("shared_expert_rank_num") = 0);
     m.def("routing_topk", &RoutingTopK, py::arg("gate_logits"), py::arg("selection_bias") = py::none(), py::arg("top_k") = 1,
           py::arg("score_func") = 0, py::arg("renormalize") = true, py::arg("routed_scale") = 1.0);
     m.def("fp8_quant_1x128", &Fp8Quant);

@@ -116,7 +116,7 @@ def test_reduce_scatter(txr, ranks, per_rank, dtype):
     world.destroy()
 
 
-@pytest.mark.parametrize("ranks,numel,root", [(2, 100, 1), (4, 500000, 0), (8, 4097, 5)])
+@pytest.mark.parametrize("ranks,numel,root", [(2, 100, 1), (4, 500000, 0), (8, 4097, 5), (4, 1 << 20, 2), (8, 3 << 19, 7)])   # the last two: scatter + all-gather
 def test_broadcast(txr, ranks, numel, root):
     world = _world(txr, ranks)
     xs = _inputs(ranks, numel, torch.float32, seed=7)

@@ -254,6 +254,54 @@ def test_ep_dispatch_int8_modes(txr, dynamic, smooth):
     world.destroy()
 
 
+def test_ep_shared_expert_ranks(txr):
+    """Two leading ranks hold the shared expert (one copy each), two hold the routed experts: every token also
+    goes to its copy of the shared expert (slot top_k, weight 1), cf. the reference's destination rule."""
+    from tilexr_b200.ops import ep
+    from tilexr_b200.utils import oracle
+
+    ranks, shared_ranks, shared_experts, bs, h, experts, top_k = 4, 2, 1, 24, 256, 8, 2
+    world = txr.init_emulated_world(ranks, device=0, buffer_mb=64)
+    g = torch.Generator().manual_seed(41)
+    xs = [torch.randn(bs, h, generator=g).to(torch.bfloat16) for _ in range(ranks)]
+    logits = [torch.randn(bs, experts, generator=g) for _ in range(ranks)]
+    routed = [oracle.routing_topk_ref(l, top_k, 1, True, 1.0) for l in logits]
+    ids, ws = [r[0] for r in routed], [r[1] for r in routed]
+    res = world.run(lambda c, r: ep.dispatch(c, xs[r].cuda(), gate_logits=logits[r].cuda(), num_experts=experts, top_k=top_k,
+                                             score_func=1, shared_expert_num=shared_experts, shared_expert_rank_num=shared_ranks))
+    world.check()
+    per_shared = shared_ranks // shared_experts
+    moe_per_rank = experts // (ranks - shared_ranks)
+    # expected rows per destination: local expert major, then source rank, then token order
+    for dst in range(ranks):
+        want = []      # (src, token, slot, expert id)
+        local = [None] if dst < shared_ranks else list(range((dst - shared_ranks) * moe_per_rank, (dst - shared_ranks + 1) * moe_per_rank))
+        for e in local:
+            for src in range(ranks):
+                for t in range(bs):
+                    if e is None:
+                        if src % per_shared + 0 * per_shared == dst:
+                            want.append((src, t, top_k, 0))
+                    else:
+                        for k in range(top_k):
+                            if int(ids[src][t, k]) == e:
+                                want.append((src, t, k, e))
+        d = res[dst]
+        n = int(d.recv_total.item())
+        assert n == len(want), (dst, n, len(want))
+        assert d.assist[:n].cpu().tolist() == [list(w) for w in want]
+        rows = torch.stack([xs[s][t] for s, t, _, _ in want]) if want else torch.empty(0, h, dtype=torch.bfloat16)
+        assert torch.equal(d.expand_x[:n].cpu(), rows)
+        assert d.expert_token_nums.numel() == (1 if dst < shared_ranks else moe_per_rank)
+    # identity experts: y = sum_k w_k x + x (the shared expert's copy)
+    ys = world.run(lambda c, r: ep.combine(c, res[r].expand_x, res[r], expert_scales=ws[r].cuda()))
+    world.check()
+    for r in range(ranks):
+        want = (xs[r].float() * (ws[r].sum(dim=1, keepdim=True) + 1.0))
+        assert torch.allclose(ys[r].cpu().float(), want, rtol=2e-2, atol=2e-2)
+    world.destroy()
+
+
 def test_ep_overflow_is_reported_not_written(txr):
     from tilexr_b200.ops import ep
 

@@ -35,6 +35,8 @@ def _reference(xs, residual, gamma, eps):
     (8, 203, 2048, 2, True, False),       # rows do not divide by the rank count
     (4, 128, 8192, 2, True, True),        # peers write y and the residual directly
     (8, 37, 1024, 0, True, False),
+    (8, 1, 2048, 2, True, False),         # two-shot with fewer rows than ranks: most ranks own nothing
+    (8, 3, 1024, 2, True, True),
 ])
 def test_all_reduce_rmsnorm(txr, ranks, rows, h, algo, with_res, symmetric):
     world = txr.init_emulated_world(ranks, device=0, buffer_mb=64)

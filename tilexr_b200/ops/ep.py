@@ -39,6 +39,8 @@ class DispatchResult:
     top_k: int
     num_experts: int
     dedup: bool = False
+    shared_expert_num: int = 0
+    shared_expert_rank_num: int = 0
 
 
 def dispatch(comm, x: torch.Tensor, *, num_experts: int, top_k: int, expert_ids: Optional[torch.Tensor] = None,
@@ -47,7 +49,8 @@ def dispatch(comm, x: torch.Tensor, *, num_experts: int, top_k: int, expert_ids:
              renormalize: bool = True, routed_scale: float = 1.0, token_nums_type: int = TOKEN_NUMS_COUNT,
              max_recv_rows: Optional[int] = None, expand_x_out: Optional[torch.Tensor] = None,
              expert_scales: Optional[torch.Tensor] = None, dedup: Optional[bool] = None,
-             scales: Optional[torch.Tensor] = None) -> DispatchResult:
+             scales: Optional[torch.Tensor] = None, shared_expert_num: int = 0,
+             shared_expert_rank_num: int = 0) -> DispatchResult:
     """``dedup`` (default: on when gate weights are known at dispatch time): a token with several experts on one
     remote rank crosses NVLink once in each direction; the expert rank replicates it after arrival and sums
     its outputs, gate-weighted in fp32, before sending them back.  The weights used for those sums are the ones
@@ -58,15 +61,18 @@ def dispatch(comm, x: torch.Tensor, *, num_experts: int, top_k: int, expert_ids:
     if scales is not None:
         dedup = False        # per-expert smoothing scales make every route's row different
     if max_recv_rows is None:
-        max_recv_rows = bs * comm.world_size * min(top_k, num_experts // comm.world_size)
+        # the same on every rank (the window layout depends on it): all tokens of all ranks with every route here
+        max_recv_rows = bs * comm.world_size * min(top_k, num_experts // (comm.world_size - shared_expert_rank_num))
     out = _C.ep_dispatch(comm, x, expert_ids, gate_logits, selection_bias, active_mask, top_k, num_experts, quant_mode,
                          score_func, renormalize, routed_scale, token_nums_type, max_recv_rows, expand_x_out, expert_scales,
-                         bool(dedup), scales)
-    return DispatchResult(*out, bs=bs, top_k=top_k, num_experts=num_experts, dedup=bool(dedup))
+                         bool(dedup), scales, shared_expert_num, shared_expert_rank_num)
+    return DispatchResult(*out, bs=bs, top_k=top_k, num_experts=num_experts, dedup=bool(dedup),
+                          shared_expert_num=shared_expert_num, shared_expert_rank_num=shared_expert_rank_num)
 
 
 def combine(comm, expert_out: torch.Tensor, d: DispatchResult, *, expert_scales: Optional[torch.Tensor] = None,
             active_mask: Optional[torch.Tensor] = None, shared_expert_x: Optional[torch.Tensor] = None,
             y_out: Optional[torch.Tensor] = None) -> torch.Tensor:
     return _C.ep_combine(comm, expert_out, d.assist, d.send_counts, d.topk_ids, expert_scales, active_mask, shared_expert_x,
-                         d.bs, d.top_k, d.num_experts, y_out, d.route_rows, d.assist_ext, d.dedup)
+                         d.bs, d.top_k, d.num_experts, y_out, d.route_rows, d.assist_ext, d.dedup, d.shared_expert_num,
+                         d.shared_expert_rank_num)

@@ -141,12 +141,17 @@ def main():
                 ref = torch.empty_like(out)
                 if op == "broadcast":
                     ref.copy_(x)
-                run_nccl(op, x, ref)
                 run_ours(txr, comm, op, x, out)
-                torch.cuda.synchronize()
                 if dtype.is_floating_point and op in ("all_reduce", "reduce_scatter"):
-                    errors = int((~torch.isclose(out.float(), ref.float(), rtol=2e-2, atol=2e-2)).sum().item())
+                    # reference summed in fp32 and rounded once (NCCL may accumulate 16-bit types in their own
+                    # precision hop by hop, which alone exceeds a 2 % tolerance now and then at 8 ranks)
+                    ref32 = torch.empty(out.shape, dtype=torch.float32, device=out.device)
+                    run_nccl(op, x.float(), ref32)
+                    torch.cuda.synchronize()
+                    errors = int((~torch.isclose(out.float(), ref32.to(dtype).float(), rtol=2e-2, atol=2e-2)).sum().item())
                 else:
+                    run_nccl(op, x, ref)
+                    torch.cuda.synchronize()
                     errors = int((out != ref).sum().item())
                 if comm.device_status() != 0:
                     errors += 1
