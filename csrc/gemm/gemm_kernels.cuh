@@ -24,7 +24,8 @@ constexpr int GEMM_MAX_K_CHUNKS = 4;     // all-gather flags per 128-row block
 // CTA-pair kernel (cta_group::2): per CTA and stage 128 rows of A and half of the 256-row B tile.
 constexpr uint32_t GEMM_PAIR_STAGE_BYTES = GEMM_STAGE_A_BYTES + GEMM_STAGE_B_BYTES / 2;
 constexpr int GEMM_PAIR_STAGES = 6;
-constexpr size_t GEMM_PAIR_SMEM_BYTES = 1024 + GEMM_PAIR_STAGES * GEMM_PAIR_STAGE_BYTES + 256;
+constexpr size_t GEMM_PAIR_SMEM_BYTES = 1024 /* alignment slack */ + GEMM_PAIR_STAGES * GEMM_PAIR_STAGE_BYTES + 1024 /* barriers */ +
+                                        GEMM_BM * 256 /* epilogue staging tile */;
 
 enum GemmMode : int32_t {
     GEMM_PLAIN = 0,

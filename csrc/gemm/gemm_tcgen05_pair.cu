@@ -232,6 +232,7 @@ __device__ void PairBody(const GemmArgs &a)
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smemRaw) + 1023) & ~static_cast<uintptr_t>(1023));
     uint8_t *stageBase = smem;
     PairState *st = reinterpret_cast<PairState *>(smem + GEMM_PAIR_STAGES * GEMM_PAIR_STAGE_BYTES);
+    uint8_t *stageC = smem + GEMM_PAIR_STAGES * GEMM_PAIR_STAGE_BYTES + 1024;      // 128 rows x 256 bytes for the epilogue
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -425,56 +426,82 @@ __device__ void PairBody(const GemmArgs &a)
         }
     } else {
         // ---- epilogue: warps 2..5 of each CTA own TMEM lanes 32*(warp%4) .. +31 = 32 of the CTA's 128 rows --------
+        // Per tile: TMEM -> registers -> a swizzled 128x128 staging tile in shared memory -> global memory with every
+        // warp store covering two whole 256-byte row pieces.  (Storing straight from the TMEM layout, one thread per
+        // row, sends 16-byte pieces to 32 different rows per instruction: fine for local memory behind L2, slow
+        // when the destination is a peer's staging buffer behind NVLink.)
         const int quad = warp & 3;
-        const int rowInTile = static_cast<int>(ctaRank) * GEMM_BM + quad * 32 + lane;
+        const int et = static_cast<int>(threadIdx.x) - 64;          // 0..127 among the epilogue threads
+        const int myRow = quad * 32 + lane;                          // row of this CTA's 128-row sub-tile held by this thread
         const TileXRRegistry *reg = fused ? a.comm->registryPtr : nullptr;
+        __shared__ int sEpiGot[4];
         int iter = 0;
         for (int t = pair; t < totalTiles; t += nPairs, ++iter) {
             const PairTile tc = TileOf(a, tileBase + tileSign * t, mTiles, rank, ranks);
-            const int mTile = tc.mTile, nBlock = tc.nBlock;
+            const int nBlock = tc.nBlock;
             const int acc = iter & 1;
             const uint32_t accPhase = (iter >> 1) & 1;
             bool got = true;
-            if (lane == 0) got = WaitBar(&st->tmemFull[acc], accPhase, st, peerAbortAddr, budgetNs);
-            got = __shfl_sync(0xffffffffu, got ? 1 : 0, 0) != 0;
-            if (!got) break;
+            if (lane == 0) {
+                got = WaitBar(&st->tmemFull[acc], accPhase, st, peerAbortAddr, budgetNs);
+                sEpiGot[quad] = got ? 1 : 0;
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");           // the four warps leave the loop together or not at all
+            if ((sEpiGot[0] & sEpiGot[1] & sEpiGot[2] & sEpiGot[3]) == 0) break;
             TcFenceAfter();
-            const int64_t row = static_cast<int64_t>(mTile) * 2 * GEMM_BM + rowInTile;
-            bool rowValid = row < a.M;
-            uint8_t *dstRow = a.c + static_cast<uint64_t>(row) * a.N * 2;
+            // first row of this CTA's sub-tile at its destination, and how many of its 128 rows exist
+            uint8_t *rowBase;
+            int rowsValid;
             if (a.mode == GEMM_REDUCE_SCATTER) {
-                const int64_t localRow = static_cast<int64_t>(tc.mLocalPair) * 2 * GEMM_BM + rowInTile;
-                rowValid = localRow < a.shardRows;
-                dstRow = reg->regions[a.stageHandle].peerBase[tc.shard] + a.stageOffset +
-                         (static_cast<uint64_t>(rank) * a.shardRows + static_cast<uint64_t>(localRow)) * a.N * 2;
+                const int64_t localRow0 = static_cast<int64_t>(tc.mLocalPair) * 2 * GEMM_BM + static_cast<int64_t>(ctaRank) * GEMM_BM;
+                rowsValid = static_cast<int>(max(static_cast<int64_t>(0), min(static_cast<int64_t>(GEMM_BM), a.shardRows - localRow0)));
+                rowBase = reg->regions[a.stageHandle].peerBase[tc.shard] + a.stageOffset +
+                          (static_cast<uint64_t>(rank) * a.shardRows + static_cast<uint64_t>(localRow0)) * a.N * 2;
+            } else {
+                const int64_t row0 = static_cast<int64_t>(tc.mTile) * 2 * GEMM_BM + static_cast<int64_t>(ctaRank) * GEMM_BM;
+                rowsValid = static_cast<int>(max(static_cast<int64_t>(0), min(static_cast<int64_t>(GEMM_BM), a.M - row0)));
+                rowBase = a.c + static_cast<uint64_t>(row0) * a.N * 2;
             }
             const int col0 = nBlock * GEMM_BN;
 #pragma unroll 1
-            for (int c = 0; c < GEMM_BN / 32; ++c) {
-                uint32_t r[32];
-                const uint32_t taddr = tmemBase + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(acc * GEMM_BN + c * 32);
-                TmemLoad32(taddr, r);
-                TmemLoadWait();
-                const int col = col0 + c * 32;
-                if (rowValid && col < a.N) {
+            for (int pass = 0; pass < 2; ++pass) {                   // 128 columns at a time
+#pragma unroll 1
+                for (int cc = 0; cc < 4; ++cc) {
+                    uint32_t r[32];
+                    const uint32_t taddr = tmemBase + (static_cast<uint32_t>(quad * 32) << 16) +
+                                           static_cast<uint32_t>(acc * GEMM_BN + pass * 128 + cc * 32);
+                    TmemLoad32(taddr, r);
+                    TmemLoadWait();
                     uint32_t packed[16];
 #pragma unroll
                     for (int j = 0; j < 16; ++j) packed[j] = PackPair(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]), bf16);
-                    uint8_t *p = dstRow + static_cast<uint64_t>(col) * 2;
-                    if (col + 32 <= a.N) {
 #pragma unroll
-                        for (int v = 0; v < 4; ++v) st_vec16(p + v * 16, Vec16{packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]});
-                    } else {
-                        for (int j = 0; j < 32 && col + j < a.N; ++j) {
-                            reinterpret_cast<uint16_t *>(p)[j] = static_cast<uint16_t>(j & 1 ? packed[j >> 1] >> 16 : packed[j >> 1] & 0xffffu);
-                        }
+                    for (int v = 0; v < 4; ++v) {
+                        const int chunk = (cc * 4 + v) ^ (myRow & 15);    // 16-byte chunks of a 256-byte row, XOR-swizzled
+                        *reinterpret_cast<uint4 *>(stageC + myRow * 256 + chunk * 16) =
+                            make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
                     }
                 }
+                if (pass == 1) {
+                    // the accumulator buffer is read out: the MMA lane may overwrite it with the tile after next
+                    TcFenceBefore();
+                    __syncwarp();
+                    if (lane == 0) ArriveCluster(SmemAddr(&st->tmemEmpty[acc]) & PEER_BIT_MASK);
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+#pragma unroll 4
+                for (int k = 0; k < 16; ++k) {
+                    const int idx = et + k * 128;
+                    const int rr = idx >> 4;
+                    const int ch = idx & 15;
+                    const int col = col0 + pass * 128 + ch * 8;
+                    if (rr < rowsValid && col < a.N) {
+                        const uint4 v = *reinterpret_cast<const uint4 *>(stageC + rr * 256 + ((ch ^ (rr & 15)) * 16));
+                        st_vec16(rowBase + static_cast<uint64_t>(rr) * a.N * 2 + static_cast<uint64_t>(col) * 2, Vec16{v.x, v.y, v.z, v.w});
+                    }
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");       // the staging tile may be rewritten
             }
-            // this warp is done with the buffer: tell the leader's MMA lane
-            TcFenceBefore();
-            __syncwarp();
-            if (lane == 0) ArriveCluster(SmemAddr(&st->tmemEmpty[acc]) & PEER_BIT_MASK);
             if (a.mode == GEMM_REDUCE_SCATTER) {
                 // this CTA's four epilogue warps have stored their rows of its 128x256 tile: announce it to the owner
                 asm volatile("bar.sync 1, 128;" ::: "memory");
