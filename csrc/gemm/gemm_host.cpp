@@ -39,6 +39,29 @@ long EnvLong(const char *name, long fallback)
     return *end == '\0' ? x : fallback;
 }
 
+// Row-major [rows, cols] 8-bit matrix, box = boxRows x 128 columns (one 128-byte swizzle row).
+int MakeMap8(CUtensorMap *map, const void *base, int64_t rows, int64_t cols, int boxRows)
+{
+    EncodeTiledFn fn = EncodeTiled();
+    if (fn == nullptr) {
+        TILEXR_LOG(ERROR) << "cuTensorMapEncodeTiled is not available from this driver";
+        return TILEXR_ERROR_RUNTIME;
+    }
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols)};
+    const cuuint32_t box[2] = {2 * GEMM_BK, static_cast<cuuint32_t>(boxRows)};
+    const cuuint32_t elemStrides[2] = {1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box, elemStrides,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        TILEXR_LOG(ERROR) << "cuTensorMapEncodeTiled failed with " << static_cast<int>(r) << " for an 8-bit " << rows << "x" << cols
+                          << " matrix at " << base;
+        return TILEXR_ERROR_RUNTIME;
+    }
+    return TILEXR_SUCCESS;
+}
+
 // Row-major [rows, cols] 16-bit matrix, box = boxRows x 64 columns, 128-byte swizzle.
 int MakeMap(CUtensorMap *map, const void *base, int64_t rows, int64_t cols, int boxRows, bool bf16)
 {
@@ -163,6 +186,57 @@ int TileXRMatmul(const void *a, const void *b, void *c, int64_t m, int64_t n, in
                                            static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) {
         TILEXR_LOG(ERROR) << "matmul launch failed: " << cudaGetErrorString(e);
+        cudaGetLastError();
+        return TILEXR_ERROR_RUNTIME;
+    }
+    NoteLaunch();
+    return TILEXR_SUCCESS;
+}
+
+int TileXRMatmulFp8(const void *a, const void *b, void *c, int64_t m, int64_t n, int64_t k, TileXRDataType inDtype,
+                    TileXRDataType outDtype, float alpha, int32_t *status, TileXRStream stream)
+{
+    if (a == nullptr || b == nullptr || c == nullptr || m <= 0 || n <= 0 || k <= 0) return TILEXR_ERROR_PARA_CHECK_FAIL;
+    if ((inDtype != TILEXR_DATA_TYPE_FP8E4M3 && inDtype != TILEXR_DATA_TYPE_FP8E5M2) ||
+        (outDtype != TILEXR_DATA_TYPE_FP16 && outDtype != TILEXR_DATA_TYPE_BFP16)) {
+        TILEXR_LOG(ERROR) << "fp8 matmul: operands e4m3 or e5m2, output fp16 or bf16";
+        return TILEXR_ERROR_PARA_CHECK_FAIL;
+    }
+    if (k % 16 != 0 || n % 8 != 0 ||
+        ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(c)) & 15u) != 0) {
+        TILEXR_LOG(ERROR) << "fp8 matmul: K a multiple of 16, N a multiple of 8, operands 16-byte aligned";
+        return TILEXR_ERROR_PARA_CHECK_FAIL;
+    }
+    GemmArgs g;
+    std::memset(&g, 0, sizeof(g));
+    int ret = MakeMap8(&g.tmapA, a, m, k, GEMM_BM);
+    if (ret != TILEXR_SUCCESS) return ret;
+    ret = MakeMap8(&g.tmapB, b, n, k, GEMM_BN / 2);
+    if (ret != TILEXR_SUCCESS) return ret;
+    g.tmapALocal = g.tmapA;
+    g.c = static_cast<uint8_t *>(c);
+    g.status = status;
+    g.mode = GEMM_PLAIN;
+    g.isBf16 = outDtype == TILEXR_DATA_TYPE_BFP16 ? 1u : 0u;
+    g.fp8Format = inDtype == TILEXR_DATA_TYPE_FP8E5M2 ? 2 : 1;
+    g.alpha = alpha;
+    FillTiling(&g, m, n, k);
+    g.kBlocks = static_cast<int32_t>((k + 2 * GEMM_BK - 1) / (2 * GEMM_BK));
+    g.rasterGroup = static_cast<int32_t>(std::max<long>(1, EnvLong("TILEXR_GEMM_GROUP", 8)));
+    int sms = 0;
+    ret = SmCount(&sms);
+    if (ret != TILEXR_SUCCESS) return ret;
+    const int pairTiles = static_cast<int>((m + 2 * GEMM_BM - 1) / (2 * GEMM_BM)) * g.nBlocks;
+    const int pairs = std::max(1, std::min<int>(pairTiles, static_cast<int>(EnvLong("TILEXR_GEMM_CTAS", sms)) / 2));
+    static std::once_flag once;
+    std::call_once(once, [] {
+        cudaFuncSetAttribute(GemmPairKernel(), cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(GEMM_PAIR_SMEM_BYTES));
+    });
+    void *params[] = {&g};
+    const cudaError_t e = cudaLaunchKernel(GemmPairKernel(), dim3(2 * pairs), dim3(GEMM_THREADS), params, GEMM_PAIR_SMEM_BYTES,
+                                           static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) {
+        TILEXR_LOG(ERROR) << "fp8 matmul launch failed: " << cudaGetErrorString(e);
         cudaGetLastError();
         return TILEXR_ERROR_RUNTIME;
     }

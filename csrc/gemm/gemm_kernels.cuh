@@ -56,6 +56,11 @@ struct GemmArgs {
     uint64_t stageOffset;
     uint32_t isBf16;
     int32_t rasterGroup;      // CTA-pair kernel, plain mode: 256-row blocks per group of the tile walk
+    // 8-bit operands (CTA-pair kernel, plain mode): 0 = 16-bit operands per isBf16, 1 = fp8 e4m3, 2 = fp8 e5m2.
+    // A stage still holds one 128-byte swizzle row per operand row, i.e. 128 elements of K, and one tcgen05.mma
+    // (kind::f8f6f4) covers 32 of them; C = alpha * A x B^T is written in the 16-bit type named by isBf16.
+    int32_t fp8Format;
+    float alpha;
 };
 
 const void *GemmKernelSingle();

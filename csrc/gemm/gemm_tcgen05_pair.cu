@@ -129,6 +129,27 @@ __device__ __forceinline__ void UmmaPairF16(uint32_t tmemD, uint64_t descA, uint
         : "memory");
 }
 
+// 8-bit floating point operands: kind::f8f6f4, D fp32, format codes 0 = e4m3, 1 = e5m2, K = 32 per instruction.
+__device__ __forceinline__ uint32_t MakeInstrDescFp8(int fp8Format)
+{
+    const uint32_t fmt = fp8Format == 2 ? 1u : 0u;
+    return (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(GEMM_BN >> 3) << 17) |
+           (static_cast<uint32_t>((2 * GEMM_BM) >> 4) << 24);
+}
+
+__device__ __forceinline__ void UmmaPairF8(uint32_t tmemD, uint64_t descA, uint64_t descB, uint32_t idesc, uint32_t accumulate)
+{
+    const uint32_t zero = 0;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n"
+        "}\n"
+        ::"r"(tmemD), "l"(descA), "l"(descB), "r"(idesc), "r"(accumulate), "r"(zero)
+        : "memory");
+}
+
 // Arrives on `bar` in BOTH CTAs of the pair once every MMA issued so far has finished.
 __device__ __forceinline__ void UmmaCommitPair(uint64_t *bar)
 {
@@ -345,6 +366,8 @@ __device__ void PairBody(const GemmArgs &a)
         tileSign = 1;
     }
     const bool bf16 = a.isBf16 != 0;
+    const bool fp8 = a.fp8Format != 0;
+    const int kPerStage = fp8 ? 2 * GEMM_BK : GEMM_BK;      // elements of K in one 128-byte swizzle row
 
     if (warp == 0) {
         // ---- TMA producer: this CTA's 128 rows of A and its half of the B tile ---------------------------------
@@ -377,8 +400,8 @@ __device__ void PairBody(const GemmArgs &a)
                     uint8_t *sa = stageBase + stage * GEMM_PAIR_STAGE_BYTES;
                     uint8_t *sb = sa + GEMM_STAGE_A_BYTES;
                     if (leader) MbarExpectTx(&st->full[stage], 2 * GEMM_PAIR_STAGE_BYTES);
-                    TmaLoadPair2D(sa, mapA, kb * GEMM_BK, rowA, &st->full[stage]);
-                    TmaLoadPair2D(sb, &a.tmapB, kb * GEMM_BK, rowB, &st->full[stage]);
+                    TmaLoadPair2D(sa, mapA, kb * kPerStage, rowA, &st->full[stage]);
+                    TmaLoadPair2D(sb, &a.tmapB, kb * kPerStage, rowB, &st->full[stage]);
                     if (++stage == GEMM_PAIR_STAGES) {
                         stage = 0;
                         phase ^= 1u;
@@ -390,7 +413,7 @@ __device__ void PairBody(const GemmArgs &a)
     } else if (warp == 1) {
         // ---- MMA issuer: the leader's lane 0 drives the tensor cores of both SMs ---------------------------------
         if (leader && lane == 0) {
-            const uint32_t idesc = MakeInstrDesc(bf16);
+            const uint32_t idesc = fp8 ? MakeInstrDescFp8(a.fp8Format) : MakeInstrDesc(bf16);
             uint32_t stage = 0, phase = 0;
             int iter = 0;
             for (int t = pair; t < totalTiles && st->abortFlag == 0; t += nPairs, ++iter) {
@@ -411,8 +434,14 @@ __device__ void PairBody(const GemmArgs &a)
                     const uint64_t descB = MakeSmemDesc(sa + GEMM_STAGE_A_BYTES);
 #pragma unroll
                     for (int k = 0; k < GEMM_BK / GEMM_UMMA_K; ++k) {
-                        UmmaPairF16(tmemD, descA + static_cast<uint64_t>(k * 2), descB + static_cast<uint64_t>(k * 2), idesc,
-                                    (kb | k) != 0 ? 1u : 0u);
+                        // each instruction consumes 32 bytes of K (16 16-bit or 32 8-bit elements): +2 in descriptor units
+                        if (fp8) {
+                            UmmaPairF8(tmemD, descA + static_cast<uint64_t>(k * 2), descB + static_cast<uint64_t>(k * 2), idesc,
+                                       (kb | k) != 0 ? 1u : 0u);
+                        } else {
+                            UmmaPairF16(tmemD, descA + static_cast<uint64_t>(k * 2), descB + static_cast<uint64_t>(k * 2), idesc,
+                                        (kb | k) != 0 ? 1u : 0u);
+                        }
                     }
                     UmmaCommitPair(&st->empty[stage]);    // both CTAs may refill the stage once these MMAs have read it
                     if (++stage == GEMM_PAIR_STAGES) {
@@ -435,6 +464,7 @@ __device__ void PairBody(const GemmArgs &a)
         const int myRow = quad * 32 + lane;                          // row of this CTA's 128-row sub-tile held by this thread
         const TileXRRegistry *reg = fused ? a.comm->registryPtr : nullptr;
         __shared__ int sEpiGot[4];
+        const float outScale = fp8 ? a.alpha : 1.0f;
         int iter = 0;
         for (int t = pair; t < totalTiles; t += nPairs, ++iter) {
             const PairTile tc = TileOf(a, tileBase + tileSign * t, mTiles, rank, ranks);
@@ -474,7 +504,9 @@ __device__ void PairBody(const GemmArgs &a)
                     TmemLoadWait();
                     uint32_t packed[16];
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) packed[j] = PackPair(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]), bf16);
+                    for (int j = 0; j < 16; ++j) {
+                        packed[j] = PackPair(__uint_as_float(r[2 * j]) * outScale, __uint_as_float(r[2 * j + 1]) * outScale, bf16);
+                    }
 #pragma unroll
                     for (int v = 0; v < 4; ++v) {
                         const int chunk = (cc * 4 + v) ^ (myRow & 15);    // 16-byte chunks of a 256-byte row, XOR-swizzled

@@ -40,6 +40,12 @@ int TileXRAllReduceRmsNorm(const void *x, void *residualInOut, const void *gamma
 int TileXRMatmul(const void *a, const void *b, void *c, int64_t m, int64_t n, int64_t k, TXR_DT dtype, int32_t *status,
                  TileXRStream stream);
 
+// C = alpha * A x B^T with fp8 operands (e4m3 or e5m2, both the same type; K a multiple of 16) and fp32 accumulation on
+// the 8-bit tensor-core path (tcgen05.mma kind::f8f6f4, twice the rate of 16-bit operands); C is fp16 or bf16.  `alpha`
+// is the product of the operands' per-tensor dequantisation scales.
+int TileXRMatmulFp8(const void *a, const void *b, void *c, int64_t m, int64_t n, int64_t k, TXR_DT inDtype, TXR_DT outDtype,
+                    float alpha, int32_t *status, TileXRStream stream);
+
 // C[R*shardRows, N] = all_gather(aShard)[R*shardRows, K] x B[N,K]^T.  `aStaging` is a registered
 // buffer of R*shardRows*K elements at the same offset on every rank (TileXRSymmAlloc): the
 // kernel pushes aShard into every peer's staging buffer and multiplies as rows arrive.  Row

@@ -39,6 +39,28 @@ def test_matmul(txr, m, n, k, dtype):
     _close(c, a.float() @ b.float().t(), k)
 
 
+@pytest.mark.parametrize("m,n,k,fmt", [
+    (256, 256, 128, torch.float8_e4m3fn),
+    (1000, 520, 400, torch.float8_e4m3fn),      # ragged in every dimension
+    (2048, 4096, 2048, torch.float8_e5m2),
+    (4096, 2048, 7168, torch.float8_e4m3fn),    # more tiles than CTA pairs, long K
+])
+def test_matmul_fp8(txr, m, n, k, fmt):
+    """fp8 operands on the kind::f8f6f4 tensor-core path against an fp32 product of the same fp8 values."""
+    g = torch.Generator().manual_seed(m + n + k)
+    a = torch.randn(m, k, generator=g).to(fmt).cuda()
+    b = torch.randn(n, k, generator=g).to(fmt).cuda()
+    alpha = 0.37
+    for _ in range(2):
+        c = txr.gemm.matmul_fp8(a, b, alpha)
+    torch.cuda.synchronize()
+    want = alpha * (a.float() @ b.float().t())
+    got = c.float()
+    # fp32 accumulation of exact fp8 products: only the final bf16 rounding differs
+    assert torch.allclose(got, want, rtol=1e-2, atol=1e-2 * (k ** 0.5)), (got - want).abs().max()
+    assert (got - want).abs().mean() < 4e-3 * want.abs().mean() + 1e-4
+
+
 @pytest.mark.parametrize("ranks,shard_rows,n,k", [(2, 128, 256, 256), (2, 256, 512, 1024), (4, 128, 768, 512), (4, 512, 1024, 512)])
 def test_all_gather_matmul(txr, ranks, shard_rows, n, k):
     world = txr.init_emulated_world(ranks, device=0, buffer_mb=16)

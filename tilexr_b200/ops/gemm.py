@@ -15,6 +15,12 @@ def matmul(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
     return _C.matmul(a.contiguous(), b.contiguous())
 
 
+def matmul_fp8(a: torch.Tensor, b: torch.Tensor, alpha: float = 1.0, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """``alpha * a @ b.T`` for fp8 operands (both float8_e4m3fn or both float8_e5m2; a [M, K], b [N, K], K % 16 == 0) with fp32
+    accumulation on the 8-bit tensor-core path; ``alpha`` is the product of the two per-tensor dequantisation scales."""
+    return _C.matmul_fp8(a.contiguous(), b.contiguous(), float(alpha), out_dtype)
+
+
 def all_gather_matmul(comm, a_shard: torch.Tensor, b: torch.Tensor, staging: torch.Tensor) -> torch.Tensor:
     """``all_gather(a_shard) @ b.T`` with the gather overlapped tile by tile.
 

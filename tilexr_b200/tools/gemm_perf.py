@@ -21,7 +21,8 @@ def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--shapes", default=DEFAULT, help="comma separated MxNxK")
     ap.add_argument("--iters", type=int, default=8)
-    ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float16"])
+    ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float16", "float8_e4m3fn", "float8_e5m2"],
+                    help="operand type; the fp8 types run the kind::f8f6f4 path against torch._scaled_mm (cuBLASLt)")
     args = ap.parse_args()
     dtype = getattr(torch, args.dtype)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")       # larger than the 126 MB L2
@@ -45,9 +46,16 @@ def main() -> int:
         m, n, k = (int(v) for v in shape.split("x"))
         a = (torch.randn(m, k, device="cuda") * 0.5).to(dtype)
         b = (torch.randn(n, k, device="cuda") * 0.5).to(dtype)
-        ours = median_ms(lambda: txr.gemm.matmul(a, b))
-        cublas = median_ms(lambda: torch.matmul(a, b.t()))
-        c, ref = txr.gemm.matmul(a, b), torch.matmul(a, b.t())
+        if dtype in (torch.float8_e4m3fn, torch.float8_e5m2):
+            one = torch.tensor(1.0, device="cuda")
+            run_ours = lambda: txr.gemm.matmul_fp8(a, b, 1.0)
+            run_lib = lambda: torch._scaled_mm(a, b.t(), scale_a=one, scale_b=one, out_dtype=torch.bfloat16)
+        else:
+            run_ours = lambda: txr.gemm.matmul(a, b)
+            run_lib = lambda: torch.matmul(a, b.t())
+        ours = median_ms(run_ours)
+        cublas = median_ms(run_lib)
+        c, ref = run_ours(), run_lib()
         torch.cuda.synchronize()
         flops = 2.0 * m * n * k
         print(json.dumps({"shape": [m, n, k], "ours_us": ours * 1e3, "cublas_us": cublas * 1e3, "ours_tflops": flops / ours / 1e9,
