@@ -240,8 +240,9 @@ __device__ __forceinline__ PairTile TileOf(const GemmArgs &a, int t, int mTiles,
         const int i = t / perShard;
         const int u = t - i * perShard;
         c.shard = a.mode == GEMM_ALL_GATHER ? (rank + i) % ranks : (rank + 1 + i) % ranks;
-        c.mLocalPair = u % pairsPerShard;
-        c.nBlock = u / pairsPerShard;
+        // inside a shard the same grouped walk as the plain mode: with many row blocks per shard (few ranks) a wave
+        // of pairs would otherwise span all of the shard's A rows and little of B, and A would stream from DRAM
+        PairTileAt(u, pairsPerShard, a.nBlocks, max(1, a.rasterGroup), &c.mLocalPair, &c.nBlock);
         c.mTile = c.shard * pairsPerShard + c.mLocalPair;
     }
     return c;
