@@ -348,7 +348,7 @@ int TileXRAllGatherMatmul(const void *aShard, void *aStaging, const void *b, voi
             // shifts a few tiles between the two groups).
             const double tileUs = 2.0 * 256 * 256 * static_cast<double>(k) / (static_cast<double>(EnvLong("TILEXR_GEMM_PAIR_TFLOPS", 17)) * 1e6);
             const double pushBytes = static_cast<double>(R - 1) * static_cast<double>(shardRows) * static_cast<double>(k) * 2.0;
-            const double pushUs = pushBytes / (g.commBlocks * static_cast<double>(EnvLong("TILEXR_AG_PUSH_GBPS_PER_CTA", 6)) * 1e3);
+            const double pushUs = pushBytes / (g.commBlocks * static_cast<double>(EnvLong("TILEXR_AG_PUSH_GBPS_PER_CTA", 10)) * 1e3);
             const double tiles = static_cast<double>((m + 2 * GEMM_BM - 1) / (2 * GEMM_BM)) * g.nBlocks;
             const double totalUs = tiles * tileUs / (grid / 2);
             g.commTilesPerPair = totalUs > pushUs ? static_cast<uint32_t>((totalUs - pushUs) / tileUs) : 0u;

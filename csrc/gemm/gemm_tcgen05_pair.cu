@@ -304,8 +304,23 @@ __device__ void PairBody(const GemmArgs &a)
                                    (static_cast<uint64_t>(rank) * a.shardRows + static_cast<uint64_t>(mLocal) * GEMM_BM) * rowBytes + colOff;
                 const uint8_t *srcBase = a.aLocal + static_cast<uint64_t>(mLocal) * GEMM_BM * rowBytes + colOff;
                 const int rows = min(GEMM_BM, a.shardRows - mLocal * GEMM_BM);
-                for (int r = warp; r < rows; r += GEMM_THREADS / 32) {
-                    CopyLanes(dstBase + r * rowBytes, srcBase + r * rowBytes, n, lane, 32);
+                // 128 rows x n bytes: every thread keeps eight 16-byte loads in flight before it stores them, so a
+                // pushing CTA has 24 KB on the way instead of the few KB of a row-by-row copy
+                const int vecsPerRow = static_cast<int>(n / 16);
+                const int total = rows * vecsPerRow;
+                for (int i0 = static_cast<int>(threadIdx.x); i0 < total; i0 += static_cast<int>(GEMM_THREADS) * 8) {
+                    Vec16 v[8];
+                    uint64_t off[8];
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) {
+                        const int i = min(i0 + q * static_cast<int>(GEMM_THREADS), total - 1);
+                        off[q] = static_cast<uint64_t>(i / vecsPerRow) * rowBytes + static_cast<uint64_t>(i % vecsPerRow) * 16;
+                        v[q] = ld_vec16_stream(srcBase + off[q]);
+                    }
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) {
+                        if (i0 + q * static_cast<int>(GEMM_THREADS) < total) st_vec16(dstBase + off[q], v[q]);
+                    }
                 }
                 __syncthreads();
                 if (threadIdx.x == 0) {
