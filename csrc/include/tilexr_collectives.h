@@ -48,6 +48,19 @@ typedef struct TileXRCollPlanInfo {
 int TileXRCollectivePlan(int opType, int64_t count, int dataType, int rankSize, uint64_t dataHalfBytes,
                          unsigned maxGrid, TileXRCollPlanInfo *info);
 
+// Collectives through the NVSwitch multicast object (NVLS).  `mcAddr` is the MULTICAST address of the message inside
+// a symmetric buffer that every rank bound to one multicast object (the same offset on every rank); addresses
+// and byte counts are multiples of 16.  Reductions run inside the switch with fp32 accumulation (bf16, fp16,
+// fp32) and every rank receives bit-identical results.  Not available on emulated or host-memory communicators.
+//   AllReduce       in place in the buffer: `bytes` of every rank's copy become the sum.
+//   ReduceScatter   `out` (local, bytes / rankSize rounded up to 16) receives slice `rank` of the sum.
+//   AllGather       `shard` (local) lands at mcAddr + rank * shardBytes in every copy.
+//   Broadcast       the root's `in` (local; may be null elsewhere) lands at mcAddr in every copy.
+int TileXRNvlsAllReduce(void *mcAddr, uint64_t bytes, TXR_DT dataType, TileXRCommPtr comm, TileXRStream stream);
+int TileXRNvlsReduceScatter(void *mcAddr, void *out, uint64_t bytes, TXR_DT dataType, TileXRCommPtr comm, TileXRStream stream);
+int TileXRNvlsAllGather(const void *shard, void *mcAddr, uint64_t shardBytes, TileXRCommPtr comm, TileXRStream stream);
+int TileXRNvlsBroadcast(const void *in, void *mcAddr, uint64_t bytes, int root, TileXRCommPtr comm, TileXRStream stream);
+
 #ifdef __cplusplus
 }
 #endif

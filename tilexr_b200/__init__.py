@@ -44,7 +44,7 @@ from .parallel.comm import (  # noqa: E402
     init_host_memory,
     init_process,
 )
-from .ops import collectives, ep, gemm, quant  # noqa: E402
+from .ops import collectives, ep, gemm, nvls, quant  # noqa: E402
 from .ops.collectives import (  # noqa: E402
     ReduceOp,
     all_gather,

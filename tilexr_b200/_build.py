@@ -67,7 +67,7 @@ def _sources():
 
 def _newest_header_mtime() -> float:
     newest = 0.0
-    for pattern in ("*.h", "*.cuh", "*.hpp"):
+    for pattern in ("*.h", "*.cuh", "*.hpp", "*.inc"):
         for p in CSRC.rglob(pattern):
             newest = max(newest, p.stat().st_mtime)
     return newest
