@@ -1,0 +1,169 @@
+// Planner kernel of the second-generation MoonEP plan (contract: tilexr_ep_plan.h, algorithm: plan_v2_algorithm.h).
+//
+// One block per rank.  The ranks do not exchange plan data: each runs the same deterministic algorithm on the same
+// histogram table.  What crosses NVLink is a "mailbox" per (receiver, sender) in the receiver's window:
+//   1. header hash (dimensions, configuration, global rank ids) and the sender's own histogram row, checked by the
+//      receiver against its caller's table: ranks that were called with different arguments or tables find out here
+//      instead of computing plans that do not fit together;
+//   2. the sender's final status; every rank returns the largest code, so all ranks agree on whether the plan holds.
+// The balancing part is sequential and runs on thread 0; ordinals, destinations and duplicate marks use the block.
+// All waits are bounded (communicator's wait budget); a give-up is reported through the device status.
+//
+// Reference: src/moonep/planner_v2/kernels/tilexr_moonep_planner_kernel.cpp:232-366 (mailbox phases), 542-695.
+#include "device/tilexr_rma.cuh"
+#include "device/tilexr_sync.cuh"
+#include "plan_v2_kernel.h"
+#include "tilexr_types.h"
+
+namespace TileXR {
+
+using namespace tilexr;
+
+namespace {
+
+struct Mail {
+    uint64_t hash;
+    int32_t status;
+    int32_t pad;
+};
+
+__device__ __forceinline__ uint8_t *MailBox(const PlanV2Args &a, int owner, int src, uint32_t epoch)
+{
+    return DataHalf(a.comm, owner, epoch) + static_cast<uint64_t>(src) * a.mailStride;
+}
+
+__device__ __forceinline__ uint64_t *MailFlag(const PlanV2Args &a, int owner, int src)
+{
+    return FlagSlot(a.comm, owner, TILEXR_FLAG_DATA_BASE + static_cast<int64_t>(src) * TILEXR_FLAGS_PER_PAIR);
+}
+
+// Thread t raises the flag of this rank in rank t's window and waits for rank t's flag here.
+__device__ __forceinline__ bool MeetRanks(Waiter &w, const PlanV2Args &a, uint32_t value)
+{
+    const int R = a.dims.R, rank = a.dims.rank;
+    __syncthreads();
+    bool ok = true;
+    const int t = threadIdx.x;
+    if (t < R && t != rank) {
+        fence_acq_rel_sys();
+        SetFlag(MailFlag(a, t, rank), w.epoch, value);
+        ok = WaitFlagGE(w, MailFlag(a, rank, t), value, t, value);
+    }
+    return BlockBroadcastOk(ok);
+}
+
+__device__ void PlanV2Body(const PlanV2Args &a)
+{
+    __shared__ plan2::Progress g;
+    __shared__ int sValidate;
+    __shared__ int sBadRoute;
+    __shared__ int sFinal;
+    __shared__ uint64_t sHash;
+
+    Waiter w;
+    bool ok = KernelPrologue(w, a.comm, a.magic, TILEXR_OP_MOONEP_PLANNING, a.dims.cap, true);
+    const plan2::Dims d = a.dims;
+    const int tid = threadIdx.x, nt = blockDim.x;
+    const plan2::Inputs in{a.topk, a.tpe, a.globalIds};
+    plan2::Tables t;
+    plan2::Carve(d, a.tables, &t);
+    if (tid == 0) {
+        sValidate = PLAN_OK;
+        sBadRoute = 0;
+        sFinal = PLAN_OK;
+        // the global rank ids are device data: they join the host's hash of dimensions and configuration here
+        uint64_t h = a.headerHash;
+        for (int r = 0; r < d.R; ++r) {
+            h ^= static_cast<uint64_t>(static_cast<uint32_t>(a.globalIds[r])) + 0x9e3779b97f4a7c15ull + (h << 6) + (h >> 2);
+            h *= 0xff51afd7ed558ccdull;
+        }
+        sHash = h;
+    }
+    __syncthreads();
+
+    // 1. mail: header and own histogram row to everybody (own window included: one code path for the check)
+    if (ok) {
+        for (int p = 0; p < d.R; ++p) {
+            uint8_t *box = MailBox(a, p, d.rank, w.epoch);
+            if (tid == 0) {
+                Mail *m = reinterpret_cast<Mail *>(box);
+                m->hash = sHash;
+                m->status = -1;
+            }
+            int32_t *row = reinterpret_cast<int32_t *>(box + sizeof(Mail));
+            for (int e = tid; e < d.E; e += nt) row[e] = a.tpe[plan2::At(d, d.rank, e)];
+        }
+        ok = MeetRanks(w, a, 1);
+    }
+    // 2. check what arrived against the caller's table
+    int mismatch = 0;
+    if (ok) {
+        for (int i = tid; i < d.R * d.E; i += nt) {
+            const int src = i / d.E, e = i - src * d.E;
+            const int32_t *row = reinterpret_cast<const int32_t *>(MailBox(a, d.rank, src, w.epoch) + sizeof(Mail));
+            if (row[e] != a.tpe[i]) mismatch |= 1;
+        }
+        if (tid < d.R && reinterpret_cast<const Mail *>(MailBox(a, d.rank, tid, w.epoch))->hash != sHash) mismatch |= 2;
+    }
+    mismatch = __syncthreads_or(mismatch);
+
+    // 3. the plan
+    if (tid == 0) {
+        int32_t v = (mismatch & 2) ? PLAN_ERROR_CONFIG_MISMATCH : (mismatch & 1) ? PLAN_ERROR_TPE_MISMATCH : PLAN_OK;
+        if (ok && v == PLAN_OK) v = plan2::PlanValidate(d, in, t);
+        sValidate = v;
+        g = plan2::Progress{};
+        if (ok && v == PLAN_OK) plan2::PlanBalance(d, in, a.out, t, g);
+    }
+    __syncthreads();
+    const bool planned = ok && sValidate == PLAN_OK;
+    if (planned && plan2::PlanHasDestinations(g)) {
+        for (int e = tid; e < d.E; e += nt) plan2::PlanOrdinalsOfExpert(d, in, t, e);
+        __syncthreads();
+        for (int r = tid; r < d.cap; r += nt) {
+            const int32_t raw = plan2::PlanRouteDst(d, in, t, g, r);
+            if (raw < 0) sBadRoute = 1;
+            a.out.dst[r] = raw < 0 ? 0 : raw;
+        }
+        __syncthreads();
+        if (sBadRoute == 0) {
+            for (int tok = tid; tok < d.S; tok += nt) plan2::PlanMarkDuplicates(d, a.out.dst, tok);
+        }
+    } else {
+        for (int r = tid; r < d.cap; r += nt) a.out.dst[r] = 0;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        for (int i = 0; i < TILEXR_MOONEP_PLAN_STATUS_WORDS; ++i) a.out.status[i] = 0;
+        if (planned) {
+            sFinal = plan2::PlanFinish(d, t, g, sBadRoute == 0, a.out.status);
+        } else {
+            sFinal = ok ? sValidate : PLAN_ERROR_INTERNAL_INVARIANT;
+            a.out.status[0] = sFinal;
+        }
+    }
+    __syncthreads();
+
+    // 4. consensus: every rank ends with the largest status code
+    if (ok) {
+        if (tid < d.R) reinterpret_cast<Mail *>(MailBox(a, tid, d.rank, w.epoch))->status = sFinal;
+        ok = MeetRanks(w, a, 2);
+        if (ok && tid == 0) {
+            int32_t worst = sFinal;
+            for (int src = 0; src < d.R; ++src) {
+                const int32_t s = reinterpret_cast<const volatile Mail *>(MailBox(a, d.rank, src, w.epoch))->status;
+                if (s > worst) worst = s;
+            }
+            a.out.status[0] = worst;
+        }
+    }
+    KernelEpilogue(w, ok);
+}
+
+TILEXR_DEFINE_KERNEL(TileXRMoonEpPlanV2Kernel, PlanV2Args, PlanV2Body, PLAN_V2_THREADS)
+
+} // namespace
+
+const KernelEntry &PlanV2KernelEntry() { return TileXRMoonEpPlanV2KernelEntry; }
+
+} // namespace TileXR

@@ -18,6 +18,7 @@
 #include "tilexr_collectives.h"
 #include "tilexr_collectives_perf.h"
 #include "tilexr_ep.h"
+#include "tilexr_ep_plan.h"
 #include "tilexr_launch.h"
 #include "tilexr_extras.h"
 
