@@ -276,3 +276,55 @@ class Buffer:
     def __exit__(self, *exc):
         self.destroy()
         return False
+
+
+# ---- planner, second generation ---------------------------------------------------------------------------------
+
+PLAN_STATUS_NAMES = ("PLAN_OK", "PLAN_PARTIAL_NO_FEASIBLE_PAIR", "PLAN_PARTIAL_PREFETCH_SLOT_EXHAUSTED", "PLAN_PARTIAL_TOKEN_SUPPLY",
+                     "PLAN_ERROR_CONFIG_MISMATCH", "PLAN_ERROR_TPE_MISMATCH", "PLAN_ERROR_LAYOUT_EXCEEDS_NVS",
+                     "PLAN_ERROR_MOVE_RECORD_OVERFLOW", "PLAN_ERROR_INTERNAL_INVARIANT")
+
+
+@dataclasses.dataclass
+class MoonEPPlanV2:
+    """Tables of the topology-aware planner (C API ``TileXRMoeEpPlanV2WithMetadata``, csrc/include/tilexr_ep_plan.h;
+    reference: src/include/tilexr_ep_plan.h:27-58).  ``dst`` holds ``dst_rank * nvs + row`` per route, ``~raw`` for a
+    route whose token already has an earlier route to the same rank."""
+    dst: torch.Tensor
+    cu_seqlens: torch.Tensor
+    experts_to_copy: torch.Tensor
+    remote_stats: torch.Tensor
+    remote_experts: torch.Tensor
+    expert_targets: torch.Tensor
+    status: torch.Tensor
+    nvs: int
+    workspace: Optional[torch.Tensor] = None
+
+    def status_name(self) -> str:
+        """Reads the status word (synchronises with the stream that planned)."""
+        return PLAN_STATUS_NAMES[int(self.status[0].item())]
+
+    def decode(self, world_size: int):
+        """(dst_rank, row, sends_hidden) per route, as tensors on the plan's device."""
+        raw = torch.where(self.dst >= 0, self.dst, ~self.dst)
+        return raw // self.nvs, raw % self.nvs, self.dst >= 0
+
+
+def planning_v2(comm, topk_experts_sk: torch.Tensor, tokens_per_expert_re: torch.Tensor, global_rank_ids: Optional[torch.Tensor] = None,
+                prefetch_slots: int = 8, nvs: Optional[int] = None, token_padding: int = 1, route_limit_per_pair: int = 0) -> MoonEPPlanV2:
+    """Plans one step on this rank of ``comm`` (every rank calls it with the same ``tokens_per_expert_re`` [R, E]).
+
+    ``global_rank_ids`` places the ranks in servers of 8 consecutive ids; the default is the communicator's own
+    numbering, i.e. one server per 8 ranks.  Nothing synchronises with the host: read ``plan.status`` when needed.
+    """
+    S, K = topk_experts_sk.shape
+    R, E = tokens_per_expert_re.shape
+    if global_rank_ids is None:
+        global_rank_ids = torch.arange(R, dtype=torch.int32, device=topk_experts_sk.device)
+    if nvs is None:
+        nvs = S * K + (E + prefetch_slots) * token_padding
+    d = _C.moonep_plan_v2(comm, topk_experts_sk.to(torch.int32).contiguous(), tokens_per_expert_re.to(torch.int32).contiguous(),
+                          global_rank_ids.to(torch.int32).contiguous(), prefetch_slots, nvs, token_padding, route_limit_per_pair)
+    return MoonEPPlanV2(dst=d["dst"], cu_seqlens=d["cu_seqlens"], experts_to_copy=d["experts_to_copy"], remote_stats=d["remote_stats"],
+                        remote_experts=d["remote_experts"], expert_targets=d["expert_targets"], status=d["status"], nvs=nvs,
+                        workspace=d["workspace"])
