@@ -23,6 +23,9 @@
 #include <cstdlib>
 #include <cstring>
 
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
 #include "device/tilexr_rma.cuh"
 #include "device/tilexr_sync.cuh"
 #include "tilexr_collectives.h"
@@ -153,6 +156,132 @@ __device__ void NvlsBody(const NvlsArgs &a)
 
 TILEXR_DEFINE_KERNEL(TileXRNvlsKernel, NvlsArgs, NvlsBody, NVLS_THREADS)
 
+// ---- all-reduce + residual add + RMSNorm through the switch -----------------------------------------------------------
+// y = RMSNorm(sum over ranks of x + residual) * gamma, residual <- sum + residual, for [rows, h] of 16-bit elements.
+// Rows are dealt to the ranks in contiguous ranges.  The owner of a row reads it with multimem.ld_reduce (one pass
+// through the switch sums all ranks' copies), adds its local residual row, normalises, and writes y and the new
+// residual with multimem.st into every rank's copy: per rank rows/R x rowBytes in and 2 x that out, where the
+// peer-to-peer two-shot kernel moves (R-1)/R x rows x rowBytes in and twice that out.  x, y and the residual are
+// views of the symmetric buffer at the same offsets on every rank; y may be x (only a row's owner reads it).
+// The sum of x leaves the switch rounded to the storage type, as NCCL's all-reduce result would be.
+struct NvlsNormArgs {
+    uint8_t *mcX;
+    uint8_t *mcY;
+    uint8_t *mcRes;            // null: no residual
+    const uint8_t *resLocal;   // this rank's copy of the residual
+    const uint8_t *gamma;
+    CommArgs *comm;
+    int64_t magic;
+    float eps;
+    int32_t rows;
+    int32_t h;
+    uint32_t rowBytes;
+    uint32_t isBf16;
+};
+
+constexpr int NVLS_NORM_MAX_VECS = 4;   // 512 threads x 4 x 8 elements = 16384 columns
+
+__device__ __forceinline__ void Unpack8(const Vec16 &v, bool bf16, float *f)
+{
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        if (bf16) {
+            f[2 * i] = __uint_as_float(w[i] << 16);
+            f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        } else {
+            const float2 f2 = __half22float2(*reinterpret_cast<const __half2 *>(&w[i]));
+            f[2 * i] = f2.x;
+            f[2 * i + 1] = f2.y;
+        }
+    }
+}
+
+__device__ __forceinline__ Vec16 Pack8(const float *f, bool bf16)
+{
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        if (bf16) {
+            const __nv_bfloat162 b = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+            w[i] = *reinterpret_cast<const uint32_t *>(&b);
+        } else {
+            const __half2 h2 = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+            w[i] = *reinterpret_cast<const uint32_t *>(&h2);
+        }
+    }
+    return Vec16{w[0], w[1], w[2], w[3]};
+}
+
+__device__ void NvlsNormBody(const NvlsNormArgs &a)
+{
+    __shared__ float sPartial[NVLS_THREADS / 32];
+    Waiter w;
+    bool ok = KernelPrologue(w, a.comm, a.magic, TILEXR_OP_ALL_REDUCE_RMSNORM, a.rows, false);
+    const int R = a.comm->rankSize;
+    const int rank = a.comm->rank;
+    NvlsArgs meet;
+    meet.comm = a.comm;
+    if (ok) ok = MeetPeers(w, meet, 1);
+    if (ok) {
+        const bool bf16 = a.isBf16 != 0;
+        const int per = (a.rows + R - 1) / R;
+        const int first = min(a.rows, per * rank);
+        const int last = min(a.rows, first + per);
+        const int vecs = a.rowBytes / 16;
+        const int kind = bf16 ? 0 : 1;
+        for (int row = first + blockIdx.x; row < last; row += gridDim.x) {
+            const uint64_t off = static_cast<uint64_t>(row) * a.rowBytes;
+            float vals[NVLS_NORM_MAX_VECS][8];
+            float ss = 0.f;
+#pragma unroll
+            for (int i = 0; i < NVLS_NORM_MAX_VECS; ++i) {
+                const int v = i * NVLS_THREADS + threadIdx.x;
+                if (v < vecs) {
+                    float acc[8];
+                    Unpack8(MultimemLdReduce(a.mcX + off + v * 16, kind), bf16, acc);
+                    if (a.mcRes != nullptr) {
+                        float r[8];
+                        Unpack8(ld_vec16(a.resLocal + off + v * 16), bf16, r);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) acc[j] += r[j];
+                    }
+                    // the sum rounded to the storage type is the new residual and the input of the norm
+                    const Vec16 packed = Pack8(acc, bf16);
+                    if (a.mcRes != nullptr) MultimemSt(a.mcRes + off + v * 16, packed);
+                    Unpack8(packed, bf16, vals[i]);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) ss += vals[i][j] * vals[i][j];
+                }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            __syncthreads();   // sPartial of the previous row is no longer read
+            if ((threadIdx.x & 31) == 0) sPartial[threadIdx.x >> 5] = ss;
+            __syncthreads();
+            float tot = 0.f;
+#pragma unroll
+            for (int i = 0; i < static_cast<int>(NVLS_THREADS / 32); ++i) tot += sPartial[i];
+            const float rstd = rsqrtf(tot / static_cast<float>(a.h) + a.eps);
+#pragma unroll
+            for (int i = 0; i < NVLS_NORM_MAX_VECS; ++i) {
+                const int v = i * NVLS_THREADS + threadIdx.x;
+                if (v < vecs) {
+                    float g[8], o[8];
+                    Unpack8(ld_vec16(a.gamma + v * 16), bf16, g);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) o[j] = vals[i][j] * rstd * g[j];
+                    MultimemSt(a.mcY + off + v * 16, Pack8(o, bf16));
+                }
+            }
+        }
+        ok = MeetPeers(w, meet, 2);
+    }
+    KernelEpilogue(w, ok);
+}
+
+TILEXR_DEFINE_KERNEL(TileXRNvlsNormKernel, NvlsNormArgs, NvlsNormBody, NVLS_THREADS)
+
 long EnvLongNvls(const char *name, long fallback)
 {
     const char *v = std::getenv(name);
@@ -242,6 +371,52 @@ int TileXRNvlsAllGather(const void *shard, void *mcAddr, uint64_t shardBytes, Ti
 int TileXRNvlsBroadcast(const void *in, void *mcAddr, uint64_t bytes, int root, TileXRCommPtr comm, TileXRStream stream)
 {
     return Launch(NVLS_BROADCAST, mcAddr, in, nullptr, bytes, TILEXR_DATA_TYPE_FP32, root, comm, stream);
+}
+
+int TileXRNvlsAllReduceRmsNorm(void *mcX, void *mcResidual, const void *residualLocal, const void *gamma, float eps, int64_t rows,
+                               int64_t h, TileXRDataType dtype, void *mcY, TileXRCommPtr comm, TileXRStream stream)
+{
+    if (comm == nullptr) return TILEXR_ERROR_NOT_INITIALIZED;
+    TileXRCommArgs *hostArgs = nullptr;
+    GM_ADDR devArgs = nullptr;
+    int ret = TileXRGetCommArgsHost(comm, &hostArgs);
+    if (ret != TILEXR_SUCCESS) return ret;
+    ret = TileXRGetCommArgsDev(comm, &devArgs);
+    if (ret != TILEXR_SUCCESS) return ret;
+    if (hostArgs->extraFlag & (TILEXR_FLAG_HOST_MEMORY | TILEXR_FLAG_EMULATED)) return TILEXR_ERROR_NOT_SUPPORT;
+    const auto misaligned = [](const void *p) { return reinterpret_cast<uintptr_t>(p) % 16 != 0; };
+    if (mcX == nullptr || mcY == nullptr || gamma == nullptr || rows <= 0 || rows > 0x7fffffff || h <= 0 || h % 8 != 0 ||
+        h > static_cast<int64_t>(NVLS_THREADS) * NVLS_NORM_MAX_VECS * 8 || (dtype != TILEXR_DATA_TYPE_FP16 && dtype != TILEXR_DATA_TYPE_BFP16) ||
+        ((mcResidual == nullptr) != (residualLocal == nullptr)) || misaligned(mcX) || misaligned(mcY) || misaligned(mcResidual) ||
+        misaligned(residualLocal) || misaligned(gamma)) {
+        TILEXR_LOG(ERROR) << "nvls all-reduce+rmsnorm: bad arguments (rows " << rows << ", h " << h << ", dtype " << dtype << ")";
+        return TILEXR_ERROR_PARA_CHECK_FAIL;
+    }
+    NvlsNormArgs a;
+    std::memset(&a, 0, sizeof(a));
+    a.mcX = static_cast<uint8_t *>(mcX);
+    a.mcY = static_cast<uint8_t *>(mcY);
+    a.mcRes = static_cast<uint8_t *>(mcResidual);
+    a.resLocal = static_cast<const uint8_t *>(residualLocal);
+    a.gamma = static_cast<const uint8_t *>(gamma);
+    a.comm = reinterpret_cast<CommArgs *>(devArgs);
+    a.eps = eps;
+    a.rows = static_cast<int32_t>(rows);
+    a.h = static_cast<int32_t>(h);
+    a.rowBytes = static_cast<uint32_t>(h * 2);
+    a.isBf16 = dtype == TILEXR_DATA_TYPE_BFP16 ? 1u : 0u;
+    int64_t magic = 0;
+    ret = TileXRCommNextMagic(comm, &magic);
+    if (ret != TILEXR_SUCCESS) return ret;
+    a.magic = magic;
+    unsigned maxGrid = 0;
+    ret = MaxCooperativeGrid(comm, TileXRNvlsNormKernelEntry, NVLS_THREADS, 0, 1, &maxGrid);
+    if (ret != TILEXR_SUCCESS) return ret;
+    const int64_t mine = (rows + hostArgs->rankSize - 1) / hostArgs->rankSize;
+    const long want = EnvLongNvls("TILEXR_NVLS_NORM_BLOCKS", 128);
+    const unsigned grid = std::max(1u, std::min<unsigned>(static_cast<unsigned>(std::min<int64_t>(std::min<long>(want, TILEXR_FLAGS_PER_PAIR), mine)), maxGrid));
+    LaunchConfig cfg{grid, NVLS_THREADS, 0, true};
+    return LaunchKernel(comm, TileXRNvlsNormKernelEntry, &a, cfg, stream);
 }
 
 } // extern "C"

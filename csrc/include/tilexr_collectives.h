@@ -60,6 +60,12 @@ int TileXRNvlsAllReduce(void *mcAddr, uint64_t bytes, TXR_DT dataType, TileXRCom
 int TileXRNvlsReduceScatter(void *mcAddr, void *out, uint64_t bytes, TXR_DT dataType, TileXRCommPtr comm, TileXRStream stream);
 int TileXRNvlsAllGather(const void *shard, void *mcAddr, uint64_t shardBytes, TileXRCommPtr comm, TileXRStream stream);
 int TileXRNvlsBroadcast(const void *in, void *mcAddr, uint64_t bytes, int root, TileXRCommPtr comm, TileXRStream stream);
+// y = RMSNorm(sum over ranks of x + residual) * gamma and residual <- sum + residual, [rows, h] fp16 / bf16, in one
+// kernel: a row's owner reduces it inside the switch, normalises it and multicasts y and the new residual.  mcX, mcY
+// (may be equal) and mcResidual are multicast addresses of views at the same offset on every rank; residualLocal is
+// this rank's own copy of the residual view (both null: no residual); gamma [h] is local.
+int TileXRNvlsAllReduceRmsNorm(void *mcX, void *mcResidual, const void *residualLocal, const void *gamma, float eps, int64_t rows,
+                               int64_t h, TXR_DT dataType, void *mcY, TileXRCommPtr comm, TileXRStream stream);
 
 #ifdef __cplusplus
 }

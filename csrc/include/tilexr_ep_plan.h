@@ -144,6 +144,23 @@ int TileXRMoeEpPlanV2WithMetadata(const int32_t *topkExperts, const int32_t *tok
                                   uint64_t localWorkspaceBytes, void *registeredMetaWorkspace, uint64_t registeredMetaBytes,
                                   TileXRStream stream);
 
+// The same call, which also fills the tables that this library's dispatch / combine stage kernels take
+// (TileXRMoonEpPlanV1 in tilexr_moonep.h): destinations with duplicates decoded (every route carries its hidden state
+// to its own row), the rows dispatch has to clear, for every row the route that fills it, and a one-word status
+// (0 = usable; a partially balanced plan whose layout fits is usable).  All four are device pointers.
+typedef struct TileXRMoonEPStageTables {
+    int32_t *dst;             // [s * k]
+    int32_t *zeroFillRanges;  // [(e + b) * 2]: {first row, number of rows} per group
+    int32_t *dstLocal;        // [nvS]
+    int32_t *status;          // [1]
+} TileXRMoonEPStageTables;
+
+int TileXRMoeEpPlanV2WithStageTables(const int32_t *topkExperts, const int32_t *tokensPerExpert, const int32_t *globalRankIds,
+                                     TileXRCommPtr comm, int64_t s, int64_t topK, int64_t expertNum,
+                                     const TileXRMoonEPPlanConfig *config, TileXRMoonEPPlanMetadataV2 *metadata,
+                                     const TileXRMoonEPStageTables *stage, void *localWorkspace, uint64_t localWorkspaceBytes,
+                                     TileXRStream stream);
+
 // CPU oracle: the same algorithm source on host memory, for rank `rank` of `rankSize`.  remoteExperts and
 // expertTargets may both be null.  Returns the plan status (also in status[0]).
 int TileXRMoeEpPlanV2Reference(int32_t rank, int64_t rankSize, const int32_t *topkExperts, const int32_t *tokensPerExpert,

@@ -649,6 +649,29 @@ TXR_PLAN2_FN void PlanMarkDuplicates(const Dims &d, int32_t *dst, int32_t token)
     }
 }
 
+// Rows of this rank that no route fills: the padding behind every group, and everything behind the last group.
+// zeroFill[g] = {first row, number of rows}: the form the dispatch stage takes, which clears them.
+TXR_PLAN2_FN void PlanZeroFill(const Dims &d, const Tables &t, const int32_t *cuSeqlens, int32_t *zeroFill)
+{
+    const int32_t *row = t.slots + static_cast<int64_t>(d.rank) * d.B;
+    const int32_t groups = d.E + d.B;
+    for (int32_t g = 0; g < groups; ++g) {
+        int32_t expert = -1;
+        if (g < d.E) {
+            bool inSlot = false;
+            for (int32_t i = 0; i < d.B; ++i) inSlot = inSlot || row[i] == g;
+            if (!inSlot) expert = g;
+        } else {
+            expert = row[g - d.E];
+        }
+        const int32_t begin = g == 0 ? 0 : cuSeqlens[g - 1];
+        const int32_t count = expert >= 0 ? t.alloc[At(d, d.rank, expert)] : 0;
+        const int32_t end = g == groups - 1 ? d.nvS : cuSeqlens[g];
+        zeroFill[2 * g] = begin + count;
+        zeroFill[2 * g + 1] = end - (begin + count);
+    }
+}
+
 // ---- status ---------------------------------------------------------------------------------------------------------------
 // `routesOk` is false when some route found no segment.
 TXR_PLAN2_FN int32_t PlanFinish(const Dims &d, const Tables &t, const Progress &g, bool routesOk, int32_t *status)

@@ -43,7 +43,7 @@ int RankOf(TileXRCommPtr comm, int *rank, int *rankSize)
 
 int LaunchPlan(const int32_t *topk, const int32_t *tpe, const int32_t *globalIds, TileXRCommPtr comm, int64_t s, int64_t k, int64_t e,
                const TileXRMoonEPPlanConfig *config, const plan2::Outputs &out, void *workspace, uint64_t workspaceBytes,
-               TileXRStream stream)
+               TileXRStream stream, const TileXRMoonEPStageTables *stage = nullptr)
 {
     if (comm == nullptr) return TILEXR_ERROR_NOT_INITIALIZED;
     TileXRCommArgs *hostArgs = nullptr;
@@ -73,9 +73,20 @@ int LaunchPlan(const int32_t *topk, const int32_t *tpe, const int32_t *globalIds
         return TILEXR_ERROR_PARA_CHECK_FAIL;
     }
     a.mailStride = static_cast<uint32_t>((16 + static_cast<uint64_t>(e) * 4 + 15) / 16 * 16);
-    if (static_cast<uint64_t>(a.mailStride) * R > hostArgs->dataHalfBytes) {
-        TILEXR_LOG(ERROR) << "MoonEP plan v2: the histogram exchange needs " << static_cast<uint64_t>(a.mailStride) * R << " window bytes";
+    a.dstLocalOff = (static_cast<uint64_t>(a.mailStride) * R + 255) / 256 * 256;
+    const uint64_t windowBytes = a.dstLocalOff + (stage != nullptr ? static_cast<uint64_t>(a.dims.nvS) * 8 : 0);
+    if (windowBytes > hostArgs->dataHalfBytes) {
+        TILEXR_LOG(ERROR) << "MoonEP plan v2: the exchange needs " << windowBytes << " window bytes";
         return TILEXR_ERROR_PARA_CHECK_FAIL;
+    }
+    if (stage != nullptr) {
+        if (stage->dst == nullptr || stage->zeroFillRanges == nullptr || stage->dstLocal == nullptr || stage->status == nullptr) {
+            return TILEXR_ERROR_PARA_CHECK_FAIL;
+        }
+        a.stageDst = stage->dst;
+        a.stageZeroFill = stage->zeroFillRanges;
+        a.stageDstLocal = stage->dstLocal;
+        a.stageStatus = stage->status;
     }
     a.topk = topk;
     a.tpe = tpe;
@@ -345,6 +356,16 @@ int TileXRMoeEpPlanV2WithMetadata(const int32_t *topkExperts, const int32_t *tok
 {
     (void)registeredMetaWorkspace;
     (void)registeredMetaBytes;
+    return TileXRMoeEpPlanV2WithStageTables(topkExperts, tokensPerExpert, globalRankIds, comm, s, topK, expertNum, config, m, nullptr,
+                                            localWorkspace, localWorkspaceBytes, stream);
+}
+
+int TileXRMoeEpPlanV2WithStageTables(const int32_t *topkExperts, const int32_t *tokensPerExpert, const int32_t *globalRankIds,
+                                     TileXRCommPtr comm, int64_t s, int64_t topK, int64_t expertNum,
+                                     const TileXRMoonEPPlanConfig *config, TileXRMoonEPPlanMetadataV2 *m,
+                                     const TileXRMoonEPStageTables *stage, void *localWorkspace, uint64_t localWorkspaceBytes,
+                                     TileXRStream stream)
+{
     if (m == nullptr || config == nullptr || m->structSize < sizeof(TileXRMoonEPPlanMetadataV2) ||
         m->abiVersion != TILEXR_MOONEP_PLAN_METADATA_V2_ABI_VERSION) {
         return TILEXR_ERROR_PARA_CHECK_FAIL;
@@ -364,7 +385,7 @@ int TileXRMoeEpPlanV2WithMetadata(const int32_t *topkExperts, const int32_t *tok
     const plan2::Outputs out{m->dst, m->cuSeqlens, m->remoteExperts + static_cast<uint64_t>(rank) * B, m->remoteStats, m->remoteExperts,
                              m->expertTargets, m->status};
     const int ret = LaunchPlan(topkExperts, tokensPerExpert, globalRankIds, comm, s, topK, expertNum, config, out, localWorkspace,
-                               localWorkspaceBytes, stream);
+                               localWorkspaceBytes, stream, stage);
     if (ret != TILEXR_SUCCESS) return ret;
     m->s = s;
     m->k = topK;

@@ -133,6 +133,21 @@ __device__ void PlanV2Body(const PlanV2Args &a)
         for (int r = tid; r < d.cap; r += nt) a.out.dst[r] = 0;
     }
     __syncthreads();
+    const bool routed = planned && plan2::PlanHasDestinations(g) && sBadRoute == 0;
+    if (a.stageDst != nullptr) {
+        // every route tells its destination which row it fills (the combine stage walks the rows)
+        for (int r = tid; r < d.cap; r += nt) {
+            const int32_t enc = a.out.dst[r];
+            const int32_t raw = enc >= 0 ? enc : ~enc;
+            a.stageDst[r] = routed ? raw : 0;
+            if (routed) {
+                const int dstRank = raw / d.nvS;
+                uint64_t *cell = reinterpret_cast<uint64_t *>(DataHalf(a.comm, dstRank, w.epoch) + a.dstLocalOff) + (raw - dstRank * d.nvS);
+                st_relaxed_sys_u64(cell, MakeFlag(w.epoch, static_cast<uint32_t>(d.rank * d.cap + r)));
+            }
+        }
+        if (tid == 0 && routed) plan2::PlanZeroFill(d, t, a.out.cuSeqlens, a.stageZeroFill);
+    }
     if (tid == 0) {
         for (int i = 0; i < TILEXR_MOONEP_PLAN_STATUS_WORDS; ++i) a.out.status[i] = 0;
         if (planned) {
@@ -155,7 +170,20 @@ __device__ void PlanV2Body(const PlanV2Args &a)
                 if (s > worst) worst = s;
             }
             a.out.status[0] = worst;
+            sFinal = worst;
         }
+    }
+    __syncthreads();
+    if (a.stageDst != nullptr) {
+        const bool usable = ok && routed && sFinal <= PLAN_PARTIAL_TOKEN_SUPPLY;
+        if (usable) {
+            const uint64_t *cells = reinterpret_cast<const uint64_t *>(DataHalf(a.comm, d.rank, w.epoch) + a.dstLocalOff);
+            for (int s = tid; s < d.nvS; s += nt) {
+                const uint64_t v = ld_relaxed_sys_u64(cells + s);
+                a.stageDstLocal[s] = FlagEpoch(v) == w.epoch ? static_cast<int32_t>(FlagValue(v)) : -1;
+            }
+        }
+        if (tid == 0) *a.stageStatus = usable ? 0 : (sFinal != PLAN_OK ? sFinal : PLAN_ERROR_INTERNAL_INVARIANT);
     }
     KernelEpilogue(w, ok);
 }

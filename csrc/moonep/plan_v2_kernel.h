@@ -24,6 +24,12 @@ struct PlanV2Args {
     uint64_t headerHash;        // dimensions, configuration and global ids as seen by the host of this rank
     uint32_t mailStride;        // bytes per sender in a window: header + E int32, rounded up to 16
     uint32_t pad;
+    // Optional tables in the form the dispatch / combine stage kernels take (all null or all set):
+    int32_t *stageDst;          // [cap] raw destinations, duplicates decoded (every route carries its hidden state)
+    int32_t *stageZeroFill;     // [(E + B) * 2]
+    int32_t *stageDstLocal;     // [nvS] source rank * cap + route of the route that fills each row, -1 = none
+    int32_t *stageStatus;       // [1] 0 = usable
+    uint64_t dstLocalOff;       // window offset of the [nvS] cells the sources write
 };
 
 const KernelEntry &PlanV2KernelEntry();

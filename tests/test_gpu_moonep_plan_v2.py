@@ -56,3 +56,61 @@ def test_wrong_table_on_one_rank_is_seen_by_all():
         assert [int(g["status"][0]) for g in ok] == [PLAN_OK] * R
     finally:
         world.destroy()
+
+
+def test_v2_plan_drives_dispatch_and_combine():
+    """The stage tables of a V2 plan (skewed routing, foreign experts in slots) through dispatch and combine."""
+    R, S, K, E, B, pad, h = 8, 48, 4, 64, 8, 8, 256
+    world = txr.init_emulated_world(R, device=0, buffer_mb=64)
+    try:
+        topk, tpe = make_routing(R, S, K, E, seed=31, skew=0.4)
+        nvs = 2 * S * K + (E + B) * pad
+        n = S * K
+        got = run_kernel(world, topk, tpe, list(range(R)), B, nvs, padding=pad)
+        assert int(got[0]["status"][0]) == PLAN_OK and int(got[0]["status"][6]) > 0      # experts moved
+        plans = [g["stage_plan"] for g in got]
+        assert all(int(p["status"].item()) == 0 for p in plans)
+        # dst_local is the inverse of the decoded destinations; rows outside it lie in the zero-fill ranges
+        for rank in range(R):
+            dl = plans[rank]["dst_local"].cpu()
+            filled = 0
+            for src in range(R):
+                for i, raw in enumerate(plans[src]["dst"].cpu().tolist()):
+                    if raw // nvs == rank:
+                        assert int(dl[raw % nvs]) == src * n + i
+                        filled += 1
+            assert int((dl >= 0).sum()) == filled == n
+            zero = torch.zeros(nvs, dtype=torch.bool)
+            for lo, count in plans[rank]["zero_fill_ranges"].cpu().tolist():
+                assert 0 <= lo and count >= 0 and lo + count <= nvs
+                zero[lo:lo + count] = True
+            assert torch.equal(zero, dl < 0)
+        g = torch.Generator().manual_seed(5)
+        hidden = [torch.randn(S, h, generator=g).to(torch.bfloat16).cuda() for _ in range(R)]
+        weights = [torch.rand(S, K, generator=g).cuda() for _ in range(R)]
+        rows = world.symm_empty((nvs, h), torch.bfloat16)
+        wrow = world.symm_empty((nvs,), torch.float32)
+        for x in rows:
+            x.fill_(7.0)
+        world.run(lambda c, rank: _C.moonep_dispatch(c, plans[rank], hidden[rank], weights[rank], rows[rank], wrow[rank]))
+        world.check()
+        for rank in range(R):
+            dl = plans[rank]["dst_local"].cpu()
+            rows_cpu = rows[rank].cpu()
+            for slot in range(nvs):
+                v = int(dl[slot])
+                if v < 0:
+                    assert torch.all(rows_cpu[slot] == 0)
+                else:
+                    src, route = divmod(v, n)
+                    assert torch.equal(rows_cpu[slot], hidden[src].cpu()[route // K])
+        outs = [torch.empty(S, h, dtype=torch.bfloat16, device="cuda") for _ in range(R)]
+        wout = [torch.empty(S, K, dtype=torch.float32, device="cuda") for _ in range(R)]
+        world.run(lambda c, rank: _C.moonep_combine(c, plans[rank], rows[rank], wrow[rank], outs[rank], wout[rank]))
+        world.check()
+        for rank in range(R):
+            want = (hidden[rank].float() * K).to(torch.bfloat16)
+            assert torch.allclose(outs[rank].float(), want.float(), rtol=1e-2, atol=1e-2)
+            assert torch.equal(wout[rank], weights[rank])
+    finally:
+        world.destroy()

@@ -299,6 +299,12 @@ class MoonEPPlanV2:
     status: torch.Tensor
     nvs: int
     workspace: Optional[torch.Tensor] = None
+    stage_plan: Optional[dict] = None      # the tables the dispatch / combine / prefetch / reduce-grad stages take
+
+    def comm_plan(self) -> MoonEPCommPlan:
+        """The plan in the form ``TileXRMoonEPBuffer`` passes to the stage kernels: destinations with duplicates
+        decoded (every route carries its hidden state), zero-fill ranges, the row -> route table and a one-word status."""
+        return MoonEPCommPlan.from_dict(self.stage_plan)
 
     def status_name(self) -> str:
         """Reads the status word (synchronises with the stream that planned)."""
@@ -327,4 +333,4 @@ def planning_v2(comm, topk_experts_sk: torch.Tensor, tokens_per_expert_re: torch
                           global_rank_ids.to(torch.int32).contiguous(), prefetch_slots, nvs, token_padding, route_limit_per_pair)
     return MoonEPPlanV2(dst=d["dst"], cu_seqlens=d["cu_seqlens"], experts_to_copy=d["experts_to_copy"], remote_stats=d["remote_stats"],
                         remote_experts=d["remote_experts"], expert_targets=d["expert_targets"], status=d["status"], nvs=nvs,
-                        workspace=d["workspace"])
+                        workspace=d["workspace"], stage_plan=d["stage_plan"])

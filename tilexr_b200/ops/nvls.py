@@ -103,6 +103,20 @@ class Workspace:
         _C.nvls_broadcast(self.comm, src.contiguous() if src is not None else None, self._mc_addr(t), t, root)
         return t
 
+    def all_reduce_rmsnorm_(self, x: torch.Tensor, gamma: torch.Tensor, residual: Optional[torch.Tensor] = None,
+                            eps: float = 1e-6, y: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """``y = RMSNorm(sum over ranks of x + residual) * gamma`` and ``residual <- sum + residual`` in one kernel.
+
+        ``x`` [rows, h] (fp16 / bf16), ``y`` (default: ``x`` itself) and ``residual`` are views of the workspace at the
+        same offsets on every rank; every rank holds the same residual and receives the same ``y`` and residual.
+        A row's owner reduces it inside the switch, normalises it and multicasts the results.
+        """
+        if y is None:
+            y = x
+        _C.nvls_all_reduce_rmsnorm(self.comm, self._mc_addr(x), x, self._mc_addr(residual) if residual is not None else 0, residual,
+                                   gamma.contiguous(), float(eps), self._mc_addr(y))
+        return y
+
     # ---- convenience: operands outside the workspace ---------------------------------------------
     def all_reduce(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         buf = self.view(x.dtype, x.numel())
