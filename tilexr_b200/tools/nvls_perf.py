@@ -88,8 +88,59 @@ def check(ws, comm, rank, world, dtype, n):
     torch.cuda.synchronize()
     if y.shape != (4, n // 4) or (y.cpu().float().reshape(-1) - ref).abs().max().item() > tol * scale:
         bad.append(f"all_reduce (copying form) {dtype}")
+    if dtype != torch.float32:
+        bad += check_norm(ws, rank, world, dtype)
     if comm.device_status() != 0:
         bad.append(f"device status {comm.device_status()}")
+    return bad
+
+
+def norm_reference(xs, res, gamma, eps, dtype):
+    """fp32 oracle of the fused op; the sum of x is rounded to the storage type first, as it leaves the switch."""
+    total = torch.zeros_like(xs[0], dtype=torch.float32)
+    for x in xs:
+        total += x.float()
+    new_res = (total.to(dtype).float() + res.float()).to(dtype)
+    v = new_res.float()
+    y = v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps) * gamma.float()
+    return y.to(dtype), new_res
+
+
+def check_norm(ws, rank, world, dtype, rows=37, h=1024):
+    bad = []
+    gens = [torch.Generator().manual_seed(900 + r) for r in range(world)]
+    xs = [torch.randn(rows, h, generator=g).to(dtype) for g in gens]
+    g0 = torch.Generator().manual_seed(77)
+    res = torch.randn(rows, h, generator=g0).to(dtype)
+    gamma = (1 + 0.1 * torch.randn(h, generator=g0)).to(dtype)
+    n = rows * h
+    size = n * 2
+    x = ws.view(dtype, n, 0).view(rows, h)
+    r = ws.view(dtype, n, (size + 255) // 256 * 256).view(rows, h)
+    y = ws.view(dtype, n, 2 * ((size + 255) // 256 * 256)).view(rows, h)
+    want_y, want_res = norm_reference(xs, res, gamma, 1e-6, dtype)
+    tol = 3e-2 if dtype == torch.bfloat16 else 4e-3
+    for out in (y, x):                       # separate output, then in place
+        x.copy_(xs[rank])
+        r.copy_(res)
+        torch.cuda.synchronize()
+        dist.barrier()                       # nobody multicasts into a buffer that a peer is still filling
+        ws.all_reduce_rmsnorm_(x, gamma.cuda(), residual=r, eps=1e-6, y=out)
+        torch.cuda.synchronize()
+        ey = (out.cpu().float() - want_y.float()).abs().max().item()
+        er = (r.cpu().float() - want_res.float()).abs().max().item()
+        if ey > tol * (want_y.float().abs().max().item() + 1) or er > tol * (want_res.float().abs().max().item() + 1):
+            bad.append(f"all_reduce_rmsnorm {dtype}: y err {ey:.4g}, residual err {er:.4g}")
+        dist.barrier()
+    x.copy_(xs[rank])
+    torch.cuda.synchronize()
+    dist.barrier()
+    ws.all_reduce_rmsnorm_(x, gamma.cuda(), eps=1e-6, y=y)     # without a residual
+    torch.cuda.synchronize()
+    want_y2, _ = norm_reference(xs, torch.zeros_like(res), gamma, 1e-6, dtype)
+    if (y.cpu().float() - want_y2.float()).abs().max().item() > tol * (want_y2.float().abs().max().item() + 1):
+        bad.append(f"all_reduce_rmsnorm without residual {dtype}")
+    dist.barrier()
     return bad
 
 
@@ -99,6 +150,8 @@ def main():
     p.add_argument("--iters", type=int, default=20)
     p.add_argument("--json", default="")
     p.add_argument("--check-only", action="store_true")
+    p.add_argument("--norm-batches", default="", help="also time all-reduce + residual + RMSNorm for these batch sizes (hidden 8192)")
+    p.add_argument("--hidden", type=int, default=8192)
     args = p.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -112,8 +165,10 @@ def main():
 
     sizes = [int(v) << 10 for v in args.sizes_kb.split(",")]
     comm = txr.init_from_torch_distributed(buffer_mb=1024)
+    norm_batches = [int(v) for v in args.norm_batches.split(",") if v]
+    norm_bytes = max([3 * (b * args.hidden * 2 + 256) for b in norm_batches] + [0])
     try:
-        ws = nvls.Workspace(comm, max(sizes + [1 << 20]))
+        ws = nvls.Workspace(comm, max(sizes + [1 << 20, norm_bytes]))
     except (nvls.NvlsUnavailable, RuntimeError) as e:  # the allocator raises RuntimeError without multicast support
         if rank == 0:
             print(json.dumps({"nvls": "unavailable", "why": str(e).splitlines()[0][:200], "world": world}))
@@ -159,13 +214,43 @@ def main():
             out["rows"].append(row)
             if rank == 0:
                 print(json.dumps(row), flush=True)
+        out["norm_rows"] = []
+        H = args.hidden
+        gamma = torch.ones(H, device="cuda", dtype=torch.bfloat16)
+        for b in norm_batches:
+            n = b * H
+            stride = (n * 2 + 255) // 256 * 256
+            x = ws.view(torch.bfloat16, n, 0).view(b, H)
+            r = ws.view(torch.bfloat16, n, stride).view(b, H)
+            y = ws.view(torch.bfloat16, n, 2 * stride).view(b, H)
+            x.normal_()
+            r.zero_()
+            lx = torch.randn(b, H, device="cuda").to(torch.bfloat16)
+            lr = torch.zeros_like(lx)
+            ly = torch.empty_like(lx)
+            torch.cuda.synchronize()
+            dist.barrier()
+
+            def nccl_path():
+                dist.all_reduce(lx)
+                lr.add_(lx)
+                v = lr.float()
+                ly.copy_(v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + 1e-6) * gamma.float())
+
+            row = {"batch": b, "bytes": n * 2}
+            row["nvls_fused_us"] = timed(lambda: ws.all_reduce_rmsnorm_(x, gamma, residual=r, eps=1e-6, y=y), args.iters, 5)
+            row["p2p_fused_us"] = timed(lambda: txr.collectives.all_reduce_rmsnorm(comm, lx, gamma, 1e-6, residual=lr, out=ly), args.iters, 5)
+            row["nccl_torch_us"] = timed(nccl_path, args.iters, 5)
+            out["norm_rows"].append(row)
+            if rank == 0:
+                print(json.dumps(row), flush=True)
         torch.cuda.synchronize()
         if comm.device_status() != 0:
             print(f"rank {rank}: device status {comm.device_status()}", file=sys.stderr)
             dist.destroy_process_group()
             return 1
     if rank == 0:
-        print(json.dumps(out if args.check_only else {k: v for k, v in out.items() if k != "rows"}))
+        print(json.dumps(out if args.check_only else {k: v for k, v in out.items() if k not in ("rows", "norm_rows")}))
         if args.json:
             with open(args.json, "w") as f:
                 json.dump(out, f, indent=1)
