@@ -48,6 +48,12 @@ typedef struct TileXRCollPlanInfo {
 int TileXRCollectivePlan(int opType, int64_t count, int dataType, int rankSize, uint64_t dataHalfBytes,
                          unsigned maxGrid, TileXRCollPlanInfo *info);
 
+// All-reduce of int8 payloads with dequantisation: recvBuf[i] = sum over ranks of (sendBuf_r[i] + offset) *
+// scale[i % scaleCount], fp16 or bf16 (`outType`; `scale` has that type, scaleCount 1 = one scale for all elements).
+// `count` is a multiple of 16.  The first hop carries int8, the sum is formed in fp32 in rank order.
+int TileXRAllReduceQuant(const void *sendBuf, void *recvBuf, int64_t count, TXR_DT outType, const void *scale,
+                         int64_t scaleCount, float offset, TileXRCommPtr comm, TileXRStream stream);
+
 // Collectives through the NVSwitch multicast object (NVLS).  `mcAddr` is the MULTICAST address of the message inside
 // a symmetric buffer that every rank bound to one multicast object (the same offset on every rank); addresses
 // and byte counts are multiples of 16.  Reductions run inside the switch with fp32 accumulation (bf16, fp16,

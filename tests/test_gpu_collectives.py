@@ -176,3 +176,27 @@ def test_perf_session_writes_reports(txr, tmp_path):
     assert (tmp_path / "rank1" / "launch1" / "summary.csv").exists()
     assert (tmp_path / "rank0" / "launch0" / "ai_prompt.md").exists()
     world.destroy()
+
+
+@pytest.mark.parametrize("ranks,numel,scale_count,dtype", [
+    (2, 4096, 1, torch.float16), (4, 16 * 1031, 1, torch.bfloat16), (8, 64 * 1024, 256, torch.bfloat16), (3, 48 * 7, 48, torch.float16),
+])
+def test_all_reduce_quant(txr, ranks, numel, scale_count, dtype):
+    """int8 payloads, dequantised and summed in fp32: out = sum_r (x_r + offset) * scale[i % scale_count]."""
+    world = _world(txr, ranks)
+    g = torch.Generator().manual_seed(11)
+    xs = [torch.randint(-128, 128, (numel,), generator=g, dtype=torch.int16).to(torch.int8).cuda() for _ in range(ranks)]
+    scale = (0.01 + 0.02 * torch.rand(scale_count, generator=g)).to(dtype).cuda()
+    offset = 3.0
+    for _ in range(3):
+        outs = world.run(lambda c, r: txr.collectives.all_reduce_quant(c, xs[r], scale, offset))
+        world.check()
+    ref = torch.zeros(numel, dtype=torch.float32)
+    sc = scale.float().cpu().repeat(numel // scale_count)
+    for x in xs:
+        ref += (x.cpu().float() + offset) * sc
+    ref = ref.to(dtype)
+    for o in outs:
+        assert o.dtype == dtype
+        assert torch.equal(o.cpu(), ref), (o.cpu().float() - ref.float()).abs().max()
+    world.destroy()

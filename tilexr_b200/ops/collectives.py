@@ -78,3 +78,9 @@ def all_reduce_rmsnorm(comm, x: torch.Tensor, gamma: torch.Tensor, eps: float = 
     """``y = RMSNorm(all_reduce(x) + residual) * gamma`` in one kernel; ``residual`` is updated in
     place with the pre-norm sum.  ``algo`` forces one-shot or two-shot (default: by size)."""
     return _C.all_reduce_rmsnorm(comm, x.contiguous(), residual, gamma, eps, algo, out)
+
+
+def all_reduce_quant(comm, x: torch.Tensor, scale: torch.Tensor, offset: float = 0.0) -> torch.Tensor:
+    """Sum over ranks of ``(x + offset) * scale`` for int8 ``x``; ``scale`` (fp16 / bf16, one element or one per
+    channel of the last dimension) gives the output dtype.  int8 crosses NVLink in the first hop, sums are fp32."""
+    return _C.all_reduce_quant(comm, x.contiguous(), scale.contiguous(), float(offset))
