@@ -122,7 +122,8 @@ __device__ void ArQuantBody(const ArQuantArgs &a)
                     const int8_t b = static_cast<int8_t>((words[j >> 2] >> ((j & 3) * 8)) & 0xffu);
                     const uint64_t e = vec * 16 + j;
                     const float sc = ToFloat16Bit(reinterpret_cast<const uint16_t *>(a.scale)[a.scaleCount == 1 ? 0 : e % a.scaleCount], bf16);
-                    acc[j] += (static_cast<float>(b) + a.offset) * sc;
+                    // separate roundings (no fused multiply-add): the result equals a plain fp32 evaluation in rank order
+                    acc[j] = __fadd_rn(acc[j], __fmul_rn(static_cast<float>(b) + a.offset, sc));
                 }
             }
             uint32_t o[8];

@@ -237,6 +237,19 @@ __device__ __forceinline__ void Epilogue(BlockCtx &c, const CollArgs &a, bool ok
 
 // ---- all-gather / all-to-all / broadcast -----------------------------------------------------------
 
+// Bytes [first, first + n) of the slice for `peer` of a transposed all-to-all: the slice is the column block `peer` of
+// the [rows, R * burst] input, read row by row.  first, n and burst are multiples of 16.
+__device__ __forceinline__ void GatherColumnBlock(uint8_t *dst, const CollArgs &a, int peer, uint64_t first, uint32_t n)
+{
+    const uint64_t burst = a.burstBytes;
+    const uint8_t *base = a.in + static_cast<uint64_t>(peer) * burst;
+    for (uint32_t v = threadIdx.x; v < n / 16; v += blockDim.x) {
+        const uint64_t o = first + static_cast<uint64_t>(v) * 16;
+        const uint64_t row = o / burst;
+        st_vec16(dst + static_cast<uint64_t>(v) * 16, ld_vec16_stream(base + row * a.pitchBytes + (o - row * burst)));
+    }
+}
+
 __device__ void PushBody(const CollArgs &a)
 {
     __shared__ uint8_t *sDst[TILEXR_MAX_RANK_SIZE + 1];
@@ -269,7 +282,11 @@ __device__ void PushBody(const CollArgs &a)
                     dst = RingSlot(a, peer, rank, t, epoch, 0);
                 }
                 if (threadIdx.x == 0) PerfStageBegin(c.perf, TILEXR_PERF_LOCAL_INPUT_TO_IPC);
-                if (dst != src) CopyLanes(dst, src, n, threadIdx.x, blockDim.x);
+                if (a.burstBytes != 0) {
+                    GatherColumnBlock(dst, a, peer, a.sliceBase + static_cast<uint64_t>(t) * a.tileBytes, n);
+                } else if (dst != src) {
+                    CopyLanes(dst, src, n, threadIdx.x, blockDim.x);
+                }
                 __syncthreads();
                 if (threadIdx.x == 0) {
                     if (peer != rank) RaiseTileFlag(a, peer, FLAG_PLANE_A, rank, t, epoch);

@@ -54,6 +54,11 @@ struct CollArgs {
     uint64_t outOffset;       // offset of `out` inside its region
     uint32_t elemSize;
     uint32_t opType;          // TileXROpType for DFX
+    // All-to-all with transpose: `in` is a [rows, R * burstBytes] matrix with row pitch pitchBytes; the slice for peer p
+    // is its column block p, rows x burstBytes, sent as a contiguous block.  burstBytes == 0: plain contiguous slices.
+    uint32_t burstBytes;      // multiple of 16
+    uint32_t pitchBytes;
+    uint64_t sliceBase;       // first byte of the slice that this launch covers
 };
 
 const KernelEntry &PushKernelEntry();          // all-gather, all-to-all, broadcast

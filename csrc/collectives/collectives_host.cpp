@@ -190,7 +190,8 @@ const KernelEntry &KernelFor(int kind)
 // Issues the launches of one collective call.  `sliceBytes`: bytes per pair (all-reduce
 // kinds: bytes of the whole vector); `sliceStride`: distance of slices in the user buffers.
 int Run(TileXRCommPtr comm, const CallContext &ctx, int kind, int opType, const uint8_t *in, uint8_t *out,
-        uint64_t sliceBytes, uint64_t sliceStride, uint64_t outBytes, int dtype, int op, int root, TileXRStream stream)
+        uint64_t sliceBytes, uint64_t sliceStride, uint64_t outBytes, int dtype, int op, int root, TileXRStream stream,
+        uint32_t burstBytes = 0, uint32_t pitchBytes = 0)
 {
     const KernelEntry &kernel = KernelFor(kind);
     const int ranksPerDevice = (ctx.hostArgs->extraFlag & TILEXR_FLAG_EMULATED) ? ctx.rankSize : 1;
@@ -218,8 +219,11 @@ int Run(TileXRCommPtr comm, const CallContext &ctx, int kind, int opType, const 
         const uint64_t n = std::min<uint64_t>(g.bytesPerLaunch, total - done);
         CollArgs a;
         std::memset(&a, 0, sizeof(a));
-        a.in = in + done;
+        a.in = burstBytes != 0 ? in : in + done;   // a transposed all-to-all addresses its input by (row, column block)
         a.out = out + done;
+        a.burstBytes = burstBytes;
+        a.pitchBytes = pitchBytes;
+        a.sliceBase = done;
         a.comm = reinterpret_cast<CommArgs *>(ctx.devArgs);
         a.kind = kind;
         a.opType = static_cast<uint32_t>(opType);
@@ -350,6 +354,33 @@ int TileXRAllToAll(void *sendBuf, void *recvBuf, int64_t sendCount, TileXRDataTy
     if (ctx.rankSize == 1) return Loopback(recvBuf, sendBuf, bytes, stream);
     return Run(comm, ctx, COLL_ALL_TO_ALL, TILEXR_OP_ALL2ALL, static_cast<const uint8_t *>(sendBuf),
                static_cast<uint8_t *>(recvBuf), bytes, bytes, outBytes, dataType, 0, 0, stream);
+}
+
+// recvBuf[s][row][0:burst] = sendBuf of rank s [row][rank * burst : (rank + 1) * burst], burst = width / rankSize.
+int TileXRAllToAllTranspose(void *sendBuf, void *recvBuf, int64_t count, int64_t width, TileXRDataType dataType, TileXRCommPtr comm,
+                            TileXRStream stream)
+{
+    CallContext ctx;
+    int ret = Prepare(comm, &ctx);
+    if (ret != TILEXR_SUCCESS) return ret;
+    ret = ValidateCommon(sendBuf, recvBuf, count, dataType, false, 0);
+    if (ret != TILEXR_SUCCESS) return ret;
+    const uint64_t es = TileXRDataTypeSize(dataType);
+    uint64_t bytes = 0;
+    if (sendBuf == recvBuf || width <= 0 || count % width != 0 || width % ctx.rankSize != 0 ||
+        MulOverflows(static_cast<uint64_t>(count), es, &bytes) || static_cast<uint64_t>(width) * es > 0xffffffffull) {
+        TILEXR_LOG(ERROR) << "all-to-all transpose: count " << count << " must be rows x width, width " << width << " a multiple of the rank count";
+        return TILEXR_ERROR_PARA_CHECK_FAIL;
+    }
+    const uint64_t burst = static_cast<uint64_t>(width) / ctx.rankSize * es;
+    if (burst % 16 != 0 || reinterpret_cast<uintptr_t>(sendBuf) % 16 != 0) {
+        TILEXR_LOG(ERROR) << "all-to-all transpose: a column block of " << burst << " bytes per row must be a multiple of 16";
+        return TILEXR_ERROR_PARA_CHECK_FAIL;
+    }
+    if (ctx.rankSize == 1) return Loopback(recvBuf, sendBuf, bytes, stream);
+    const uint64_t slice = bytes / ctx.rankSize;
+    return Run(comm, ctx, COLL_ALL_TO_ALL, TILEXR_OP_ALL2ALL, static_cast<const uint8_t *>(sendBuf), static_cast<uint8_t *>(recvBuf), slice,
+               slice, bytes, dataType, 0, 0, stream, static_cast<uint32_t>(burst), static_cast<uint32_t>(static_cast<uint64_t>(width) * es));
 }
 
 int TileXRAllReduce(void *sendBuf, void *recvBuf, int64_t count, TileXRDataType dataType, TileXRReduceOp op,

@@ -48,6 +48,14 @@ typedef struct TileXRCollPlanInfo {
 int TileXRCollectivePlan(int opType, int64_t count, int dataType, int rankSize, uint64_t dataHalfBytes,
                          unsigned maxGrid, TileXRCollPlanInfo *info);
 
+// All-to-all with transpose (the sequence-parallel <-> head-parallel exchange): sendBuf is a [rows, width] matrix
+// (count = rows * width elements); rank p receives column block p of every rank's matrix, and recvBuf holds them as
+// [rankSize][rows][width / rankSize].  A column block of one row is a multiple of 16 bytes.
+// (Reference: TileXRAll2AllTranspose, selected when the all-to-all is called with op and root set, root = width:
+// src/collectives/kernels/lccl_op.h:236-237.)
+int TileXRAllToAllTranspose(void *sendBuf, void *recvBuf, int64_t count, int64_t width, TXR_DT dataType, TileXRCommPtr comm,
+                            TileXRStream stream);
+
 // All-reduce of int8 payloads with dequantisation: recvBuf[i] = sum over ranks of (sendBuf_r[i] + offset) *
 // scale[i % scaleCount], fp16 or bf16 (`outType`; `scale` has that type, scaleCount 1 = one scale for all elements).
 // `count` is a multiple of 16.  The first hop carries int8, the sum is formed in fp32 in rank order.

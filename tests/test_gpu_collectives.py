@@ -200,3 +200,22 @@ def test_all_reduce_quant(txr, ranks, numel, scale_count, dtype):
         assert o.dtype == dtype
         assert torch.equal(o.cpu(), ref), (o.cpu().float() - ref.float()).abs().max()
     world.destroy()
+
+
+@pytest.mark.parametrize("ranks,rows,width,dtype", [
+    (2, 7, 64, torch.bfloat16), (4, 129, 4 * 24, torch.float32), (8, 1024, 8 * 128, torch.bfloat16), (4, 3000, 4 * 1024, torch.float16),
+])
+def test_all_to_all_transpose(txr, ranks, rows, width, dtype):
+    """Rank p receives column block p of every rank's [rows, width] matrix."""
+    world = _world(txr, ranks)
+    g = torch.Generator().manual_seed(23)
+    xs = [torch.randn(rows, width, generator=g).to(dtype).cuda() for _ in range(ranks)]
+    for _ in range(3):
+        outs = world.run(lambda c, r: txr.collectives.all_to_all_transpose(c, xs[r]))
+        world.check()
+    burst = width // ranks
+    for r, o in enumerate(outs):
+        assert o.shape == (ranks, rows, burst)
+        for s in range(ranks):
+            assert torch.equal(o[s], xs[s][:, r * burst:(r + 1) * burst]), (r, s)
+    world.destroy()

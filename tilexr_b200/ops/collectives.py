@@ -84,3 +84,9 @@ def all_reduce_quant(comm, x: torch.Tensor, scale: torch.Tensor, offset: float =
     """Sum over ranks of ``(x + offset) * scale`` for int8 ``x``; ``scale`` (fp16 / bf16, one element or one per
     channel of the last dimension) gives the output dtype.  int8 crosses NVLink in the first hop, sums are fp32."""
     return _C.all_reduce_quant(comm, x.contiguous(), scale.contiguous(), float(offset))
+
+
+def all_to_all_transpose(comm, x: torch.Tensor) -> torch.Tensor:
+    """``x`` is [rows, width]; returns [world, rows, width // world] where entry ``s`` is column block ``rank`` of rank
+    ``s``'s matrix: the sequence-parallel <-> head-parallel exchange, with the transpose done by the sending kernel."""
+    return _C.all_to_all_transpose(comm, x.contiguous())
