@@ -210,9 +210,12 @@ TXR_D bool WaitPeerFinished(Waiter &w, int peer, uint32_t finishedEpoch)
 TXR_D void PublishDone(const Waiter &w)
 {
     CommArgs *a = w.args;
+    // One fence orders everything this rank did before all of the stores below; a release store per peer would
+    // wait for the previous peer's store to be acknowledged over NVLink, rankSize - 1 round trips in a row.
+    fence_acq_rel_sys();
     for (int i = 0; i < a->rankSize; ++i) {
         const int r = (a->rank + i) % a->rankSize;
-        st_release_sys_u64(CtrlWord(a, r, TILEXR_CTRL_DONE_WORD + a->rank), MakeFlag(w.epoch, 0));
+        st_relaxed_sys_u64(CtrlWord(a, r, TILEXR_CTRL_DONE_WORD + a->rank), MakeFlag(w.epoch, 0));
     }
 }
 
