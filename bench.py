@@ -136,15 +136,36 @@ def free_port() -> int:
 
 
 def reference_unavailable():
-    print(json.dumps({
+    emit(json.dumps({
         "impl": "reference",
         "unavailable": "the reference builds only for Huawei Ascend (CANN toolchain, AICore kernels); it has no "
                        "setup.py/pyproject.toml and no CUDA path, so it cannot be installed or run on a B200",
     }))
 
 
+_RESULT_STREAM = None
+
+
+def claim_stdout():
+    """Keeps the process's stdout for the one JSON line: file descriptor 1 is pointed at stderr, so that what
+    libraries print on it (NCCL's version banner, for one) cannot land beside the result."""
+    global _RESULT_STREAM
+    if _RESULT_STREAM is None:
+        sys.stdout.flush()
+        _RESULT_STREAM = os.fdopen(os.dup(1), "w")
+        os.dup2(2, 1)
+        sys.stdout = sys.stderr
+
+
+def emit(line: str) -> None:
+    stream = _RESULT_STREAM if _RESULT_STREAM is not None else sys.stdout
+    stream.write(line + "\n")
+    stream.flush()
+
+
 def main():
     args = parse_args()
+    claim_stdout()
     if args.impl == "reference":
         reference_unavailable()
         return 0
@@ -422,7 +443,7 @@ def main():
     if e2e is not None:
         out["e2e"] = e2e
     if rank == 0:
-        print(json.dumps(out))
+        emit(json.dumps(out))
     if comm is not None:
         comm.destroy()
     if world > 1:
