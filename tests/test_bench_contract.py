@@ -1,0 +1,29 @@
+"""bench.py prints exactly one JSON line on stdout, whatever libraries write there; the reference arm reports why it
+cannot run."""
+import json
+import subprocess
+import sys
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def test_reference_arm_prints_one_json_line():
+    proc = subprocess.run([sys.executable, str(ROOT / "bench.py"), "--impl", "reference", "--gpus", "1", "--steps", "2", "--warmup", "3"],
+                          capture_output=True, text=True, timeout=120, cwd=ROOT)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    lines = [ln for ln in proc.stdout.splitlines() if ln.strip()]
+    assert len(lines) == 1
+    out = json.loads(lines[0])
+    assert out["impl"] == "reference" and "unavailable" in out and "\n" not in out["unavailable"]
+
+
+def test_stdout_is_reserved_for_the_result():
+    code = (
+        "import os, sys; sys.argv = ['bench.py']; sys.path.insert(0, %r); import bench; bench.claim_stdout();"
+        "os.write(1, b'banner from a library\\n'); print('a stray print'); bench.emit('{\"ok\": 1}')" % str(ROOT)
+    )
+    proc = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=120, cwd=ROOT)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert proc.stdout == '{"ok": 1}\n'
+    assert "banner from a library" in proc.stderr and "a stray print" in proc.stderr

@@ -22,11 +22,13 @@ import torch
 import torch.distributed as dist
 
 OPS = ("all_gather", "all_to_all", "all_reduce", "reduce_scatter", "broadcast")
+EXTRA_OPS = ("all_to_all_transpose",)      # not part of --op all
+TRANSPOSE_BURST = 512                      # elements of one row that go to one peer
 
 
 def parse():
     p = argparse.ArgumentParser()
-    p.add_argument("--op", default="all_gather", choices=OPS + ("all",))
+    p.add_argument("--op", default="all_gather", choices=OPS + EXTRA_OPS + ("all",))
     p.add_argument("--min-bytes", type=int, default=4096)
     p.add_argument("--max-bytes", type=int, default=64 << 20)
     p.add_argument("--step-factor", type=int, default=4)
@@ -51,17 +53,26 @@ def message_elems(op: str, nbytes: int, world: int, esize: int):
     if op == "all_to_all":
         n = max(n // world, 1) * world
         return n, n
+    if op == "all_to_all_transpose":
+        width = world * TRANSPOSE_BURST
+        n = max(n // width, 1) * width
+        return n, n
     if op == "reduce_scatter":
         n = max(n // world, 1)
         return n * world, n
     return n, n
 
 
-def run_ours(txr, comm, op, x, out):
+def run_ours(txr, comm, op, x, out, keep=False):
     if op == "all_gather":
         txr.all_gather(comm, x, out=out)
     elif op == "all_to_all":
         txr.all_to_all(comm, x, out=out)
+    elif op == "all_to_all_transpose":
+        # the sending kernel gathers the column blocks; the result is a fresh tensor, as for the NCCL arm's transpose
+        res = txr.collectives.all_to_all_transpose(comm, x.view(-1, comm.world_size * TRANSPOSE_BURST))
+        if keep:
+            out.copy_(res.reshape(-1))
     elif op == "all_reduce":
         txr.all_reduce(comm, x, out=out)
     elif op == "reduce_scatter":
@@ -75,6 +86,9 @@ def run_nccl(op, x, out):
         dist.all_gather_into_tensor(out, x)
     elif op == "all_to_all":
         dist.all_to_all_single(out, x)
+    elif op == "all_to_all_transpose":
+        world = dist.get_world_size()
+        dist.all_to_all_single(out, x.view(-1, world, TRANSPOSE_BURST).transpose(0, 1).contiguous())
     elif op == "all_reduce":
         out.copy_(x)
         dist.all_reduce(out)
@@ -141,7 +155,7 @@ def main():
                 ref = torch.empty_like(out)
                 if op == "broadcast":
                     ref.copy_(x)
-                run_ours(txr, comm, op, x, out)
+                run_ours(txr, comm, op, x, out, keep=True)
                 if dtype.is_floating_point and op in ("all_reduce", "reduce_scatter"):
                     # reference summed in fp32 and rounded once (NCCL may accumulate 16-bit types in their own
                     # precision hop by hop, which alone exceeds a 2 % tolerance now and then at 8 ranks)
