@@ -172,33 +172,38 @@ TXR_PLAN2_FN Dims MakeDims(int32_t rank, int64_t R, int64_t S, int64_t K, int64_
     return d;
 }
 
-// Global ids distinct and non-negative; expert ids in range; the rank's own row equals the histogram of its routes;
-// every row sums to cap.
+// Global ids distinct and non-negative, expert ids in range, counts non-negative (else CONFIG_MISMATCH); the rank's own
+// row equals the histogram of its routes and every row sums to cap (else TPE_MISMATCH).  Everything is looked at and a
+// configuration problem wins, so that a parallel check reaches the same verdict.
 TXR_PLAN2_FN int32_t PlanValidate(const Dims &d, const Inputs &in, Tables &t)
 {
+    bool config = false, histogram = false;
     for (int32_t a = 0; a < d.R; ++a) {
-        if (in.globalIds[a] < 0) return PLAN_ERROR_CONFIG_MISMATCH;
+        if (in.globalIds[a] < 0) config = true;
         for (int32_t b = 0; b < a; ++b) {
-            if (in.globalIds[a] == in.globalIds[b]) return PLAN_ERROR_CONFIG_MISMATCH;
+            if (in.globalIds[a] == in.globalIds[b]) config = true;
         }
     }
     for (int32_t e = 0; e < d.E; ++e) t.expertList[e] = 0;
     for (int32_t i = 0; i < d.cap; ++i) {
         const int32_t e = in.topk[i];
-        if (e < 0 || e >= d.E) return PLAN_ERROR_CONFIG_MISMATCH;
-        ++t.expertList[e];
+        if (e < 0 || e >= d.E) {
+            config = true;
+        } else {
+            ++t.expertList[e];
+        }
     }
     for (int32_t src = 0; src < d.R; ++src) {
         int64_t sum = 0;
         for (int32_t e = 0; e < d.E; ++e) {
             const int32_t v = in.tpe[At(d, src, e)];
-            if (v < 0) return PLAN_ERROR_CONFIG_MISMATCH;
-            if (src == d.rank && v != t.expertList[e]) return PLAN_ERROR_TPE_MISMATCH;
+            if (v < 0) config = true;
+            if (src == d.rank && v != t.expertList[e]) histogram = true;
             sum += v;
         }
-        if (sum != d.cap) return PLAN_ERROR_TPE_MISMATCH;
+        if (sum != d.cap) histogram = true;
     }
-    return PLAN_OK;
+    return config ? PLAN_ERROR_CONFIG_MISMATCH : histogram ? PLAN_ERROR_TPE_MISMATCH : PLAN_OK;
 }
 
 // ---- orders -------------------------------------------------------------------------------------------------------
@@ -501,7 +506,6 @@ TXR_PLAN2_FN int32_t BuildLayouts(const Dims &d, const Outputs &out, Tables &t, 
     out.remoteStats[1] = 0;
     g.maxRemote = 0;
     g.localEnd = 0;
-    for (int64_t i = 0; i < static_cast<int64_t>(d.R) * d.E; ++i) t.base[i] = 0;
 
     for (int32_t dst = 0; dst < d.R; ++dst) {
         int32_t *row = t.slots + static_cast<int64_t>(dst) * d.B;
@@ -534,15 +538,18 @@ TXR_PLAN2_FN int32_t BuildLayouts(const Dims &d, const Outputs &out, Tables &t, 
         }
     }
 
+    int32_t *inSlot = t.expertList;   // scratch: 1 for the experts that sit in a slot of the current destination
     for (int32_t dst = 0; dst < d.R; ++dst) {
         const int32_t *row = t.slots + static_cast<int64_t>(dst) * d.B;
+        for (int32_t e = 0; e < d.E; ++e) inSlot[e] = 0;
+        for (int32_t i = 0; i < d.B; ++i) {
+            if (row[i] >= 0) inSlot[row[i]] = 1;
+        }
         int64_t end = 0;
         for (int32_t group = 0; group < groups; ++group) {
             int32_t expert = -1;
             if (group < d.E) {
-                bool inSlot = false;
-                for (int32_t i = 0; i < d.B; ++i) inSlot = inSlot || row[i] == group;
-                if (!inSlot) expert = group;
+                if (!inSlot[group]) expert = group;
             } else {
                 expert = row[group - d.E];
             }
@@ -561,30 +568,54 @@ TXR_PLAN2_FN int32_t BuildLayouts(const Dims &d, const Outputs &out, Tables &t, 
     return PLAN_OK;
 }
 
-// ---- the sequential part ----------------------------------------------------------------------------------------------
-// Runs on one thread.  Afterwards g.fatal / g.balanced / g.layoutStatus say whether destinations can be computed.
-TXR_PLAN2_FN void PlanBalance(const Dims &d, const Inputs &in, const Outputs &out, Tables &t, Progress &g)
+// Table initialisation, cut so that the kernel can spread it over its threads: every function handles the items
+// first, first + stride, ... ; the caller runs A, then (after a barrier when parallel) B, then PlanBalance on one thread.
+TXR_PLAN2_FN void PlanInitA(const Dims &d, const Inputs &in, Tables &t, int32_t first, int32_t stride)
 {
-    g = Progress{};
-    for (int32_t r = 0; r < d.R; ++r) {
-        t.load[r] = 0;
-        t.slotsUsed[r] = 0;
-    }
-    for (int64_t i = 0; i < static_cast<int64_t>(d.R) * d.E; ++i) {
+    for (int64_t i = first; i < static_cast<int64_t>(d.R) * d.E; i += stride) {
         t.remaining[i] = in.tpe[i];
         t.alloc[i] = 0;
         t.srcCursor[i] = 0;
         t.dstCursor[i] = 0;
         t.base[i] = 0;
     }
-    for (int64_t i = 0; i < static_cast<int64_t>(d.R) * d.B; ++i) t.slots[i] = -1;
-    for (int64_t i = 0; i < static_cast<int64_t>(d.R) * d.R; ++i) t.pairTokens[i] = 0;
-    for (int32_t e = 0; e < d.E; ++e) {
+    for (int64_t i = first; i < static_cast<int64_t>(d.R) * d.B; i += stride) t.slots[i] = -1;
+    for (int64_t i = first; i < static_cast<int64_t>(d.R) * d.R; i += stride) t.pairTokens[i] = 0;
+    for (int32_t r = first; r < d.R; r += stride) t.slotsUsed[r] = 0;
+}
+
+// Every expert starts at home with all of its routes; a rank's load is the sum over its home experts.
+TXR_PLAN2_FN void PlanInitB(const Dims &d, const Inputs &in, Tables &t, int32_t first, int32_t stride)
+{
+    for (int32_t e = first; e < d.E; e += stride) {
         int32_t n = 0;
         for (int32_t src = 0; src < d.R; ++src) n += in.tpe[At(d, src, e)];
         t.alloc[At(d, e / d.L, e)] = n;
-        t.load[e / d.L] += n;
     }
+}
+
+TXR_PLAN2_FN void PlanInitC(const Dims &d, Tables &t, int32_t first, int32_t stride)
+{
+    for (int32_t r = first; r < d.R; r += stride) {
+        int32_t n = 0;
+        for (int32_t e = r * d.L; e < (r + 1) * d.L; ++e) n += t.alloc[At(d, r, e)];
+        t.load[r] = n;
+    }
+}
+
+TXR_PLAN2_FN void PlanInitSerial(const Dims &d, const Inputs &in, Tables &t)
+{
+    PlanInitA(d, in, t, 0, 1);
+    PlanInitB(d, in, t, 0, 1);
+    PlanInitC(d, t, 0, 1);
+}
+
+// ---- the sequential part ----------------------------------------------------------------------------------------------
+// Runs on one thread, after the initialisation above.  Afterwards g.fatal / g.balanced / g.layoutStatus say whether
+// destinations can be computed.
+TXR_PLAN2_FN void PlanBalance(const Dims &d, const Inputs &in, const Outputs &out, Tables &t, Progress &g)
+{
+    g = Progress{};
     BuildAffinity(d, in, t);
     BalanceWithinServers(d, in, t, g);
     if (g.fatal == PLAN_OK) BalanceAcrossServers(d, in, t, g);
@@ -655,12 +686,15 @@ TXR_PLAN2_FN void PlanZeroFill(const Dims &d, const Tables &t, const int32_t *cu
 {
     const int32_t *row = t.slots + static_cast<int64_t>(d.rank) * d.B;
     const int32_t groups = d.E + d.B;
+    int32_t *inSlot = t.expertList;   // scratch, free once the plan is balanced
+    for (int32_t e = 0; e < d.E; ++e) inSlot[e] = 0;
+    for (int32_t i = 0; i < d.B; ++i) {
+        if (row[i] >= 0) inSlot[row[i]] = 1;
+    }
     for (int32_t g = 0; g < groups; ++g) {
         int32_t expert = -1;
         if (g < d.E) {
-            bool inSlot = false;
-            for (int32_t i = 0; i < d.B; ++i) inSlot = inSlot || row[i] == g;
-            if (!inSlot) expert = g;
+            if (!inSlot[g]) expert = g;
         } else {
             expert = row[g - d.E];
         }

@@ -305,6 +305,7 @@ int TileXRMoeEpPlanV2Reference(int32_t rank, int64_t rankSize, const int32_t *to
         return v;
     }
     plan2::Progress g;
+    plan2::PlanInitSerial(d, in, t);
     plan2::PlanBalance(d, in, out, t, g);
     bool routesOk = true;
     for (int32_t i = 0; i < d.cap; ++i) dst[i] = 0;

@@ -107,10 +107,49 @@ __device__ void PlanV2Body(const PlanV2Args &a)
     }
     mismatch = __syncthreads_or(mismatch);
 
-    // 3. the plan
+    // 3. the caller's own inputs (the rules of plan2::PlanValidate, checked by the whole block), then the plan
+    int bad = 0;   // bit 0: histogram problem, bit 1: configuration problem
+    if (ok) {
+        for (int e = tid; e < d.E; e += nt) t.expertList[e] = 0;
+        for (int r = tid; r < d.R; r += nt) t.listA[r] = 0;
+        if (tid < d.R) {
+            if (a.globalIds[tid] < 0) bad |= 2;
+            for (int b = 0; b < tid; ++b) {
+                if (a.globalIds[b] == a.globalIds[tid]) bad |= 2;
+            }
+        }
+        __syncthreads();
+        for (int i = tid; i < d.cap; i += nt) {
+            const int32_t e = a.topk[i];
+            if (e < 0 || e >= d.E) {
+                bad |= 2;
+            } else {
+                atomicAdd(&t.expertList[e], 1);
+            }
+        }
+        __syncthreads();
+        for (int i = tid; i < d.R * d.E; i += nt) {
+            const int src = i / d.E, e = i - src * d.E;
+            const int32_t v = a.tpe[i];
+            if (v < 0) bad |= 2;
+            if (src == d.rank && v != t.expertList[e]) bad |= 1;
+            atomicAdd(&t.listA[src], v);      // a negative count is a configuration problem already
+        }
+        __syncthreads();
+        if (tid < d.R && t.listA[tid] != d.cap) bad |= 1;
+    }
+    bad = __syncthreads_or(bad);
+    if (ok && mismatch == 0 && bad == 0) {      // block-uniform
+        plan2::PlanInitA(d, in, t, tid, nt);
+        __syncthreads();
+        plan2::PlanInitB(d, in, t, tid, nt);
+        __syncthreads();
+        plan2::PlanInitC(d, t, tid, nt);
+        __syncthreads();
+    }
     if (tid == 0) {
         int32_t v = (mismatch & 2) ? PLAN_ERROR_CONFIG_MISMATCH : (mismatch & 1) ? PLAN_ERROR_TPE_MISMATCH : PLAN_OK;
-        if (ok && v == PLAN_OK) v = plan2::PlanValidate(d, in, t);
+        if (ok && v == PLAN_OK) v = (bad & 2) ? PLAN_ERROR_CONFIG_MISMATCH : (bad & 1) ? PLAN_ERROR_TPE_MISMATCH : PLAN_OK;
         sValidate = v;
         g = plan2::Progress{};
         if (ok && v == PLAN_OK) plan2::PlanBalance(d, in, a.out, t, g);
