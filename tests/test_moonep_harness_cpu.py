@@ -90,6 +90,30 @@ def test_plan_invariants_hold_for_reference_plans_and_catch_a_collision():
     assert any("used twice" in v for v in check_plan_invariants(case, plans))
 
 
+def test_plan_invariants_hold_for_v2_plans():
+    """The topology-aware planner's oracle through the harness: the same invariants, with duplicate routes encoded."""
+    from tilexr_b200.tools.moonep.case_factory import load_cases, routing
+    from tilexr_b200.tools.moonep.planner_reference import check_plan_invariants, reference_plan_v2
+
+    checked = 0
+    for case in load_cases("correctness"):
+        topk = [routing(case, r) for r in range(case.ranks)]
+        plans = [reference_plan_v2(case, topk, r, nvs=case.ranks * case.routes) for r in range(case.ranks)]
+        assert all(int(p["code"]) <= 3 for p in plans), (case.name, [p["status"].tolist() for p in plans])
+        assert check_plan_invariants(case, plans) == [], case.name
+        codes = {int(p["code"]) for p in plans}
+        assert len(codes) == 1                                   # every rank reaches the same verdict
+        if codes == {0}:
+            per_rank = [0] * case.ranks
+            for p in plans:
+                raw = torch.where(p["dst"] >= 0, p["dst"], ~p["dst"]).to(torch.int64)
+                for r in range(case.ranks):
+                    per_rank[r] += int((raw // p["NvS"] == r).sum())
+            assert per_rank == [case.routes] * case.ranks, (case.name, per_rank)     # balanced to the capacity
+        checked += 1
+    assert checked > 0
+
+
 def test_ulp_distance_and_compare_policies():
     from tilexr_b200.tools.moonep.correctness import compare, ulp_distance
 
