@@ -11,6 +11,9 @@
 
 #include <stddef.h>
 #include <stdint.h>
+#ifndef __cplusplus
+#include <stdbool.h>
+#endif
 
 #include "tilexr_comm_args.h"
 #include "tilexr_types.h"
