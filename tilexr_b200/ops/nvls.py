@@ -50,8 +50,11 @@ class Workspace:
         nbytes = (int(nbytes) + 255) // 256 * 256
         self.comm = comm
         self.nbytes = nbytes
-        self.buffer = symm.empty(nbytes, dtype=torch.uint8, device=device)
-        self.handle = symm.rendezvous(self.buffer, group)
+        try:
+            self.buffer = symm.empty(nbytes, dtype=torch.uint8, device=device)
+            self.handle = symm.rendezvous(self.buffer, group)
+        except RuntimeError as e:      # no symmetric-memory support on this system (driver, fabric, or permissions)
+            raise NvlsUnavailable(str(e).splitlines()[0] if str(e) else "symmetric memory allocation failed") from e
         self.mc_base = int(getattr(self.handle, "multicast_ptr", 0) or 0)
         if self.mc_base == 0:
             raise NvlsUnavailable("the symmetric allocation has no multicast address on this system")
