@@ -67,7 +67,9 @@ def test_unsupported_case():
 
 
 def test_cli_writes_reports(tmp_path):
-    exe = Path(checker.__file__).resolve().parents[1] / "bin" / "tilexr_checker"
+    from tilexr_b200 import _build
+
+    exe = _build.build_checker_cli(verbose=False)  # rebuilt when checker sources are newer
     assert exe.exists()
     r = subprocess.run([str(exe), "--op", "allreduce", "--ranks", "4", "--count", "1024", "--launches", "3", "--out", str(tmp_path)],
                        capture_output=True, text=True)

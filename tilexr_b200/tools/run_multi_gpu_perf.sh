@@ -1,11 +1,12 @@
 #!/bin/bash
 # Runs every multi-GPU measurement of this repository on N GPUs of one node and leaves the
-# results under $OUT (default gpurun_out/perf_nN): bench (this library and the NCCL baseline),
-# the collective sweep, the tensor-parallel MLP fusions and the fused all-reduce.
-#   usage: run_multi_gpu_perf.sh N [OUT]
+# results under OUT: bench (this library and the NCCL baseline), the collective sweep, the
+# tensor-parallel MLP fusions and the fused all-reduce.
+#   usage: run_multi_gpu_perf.sh N OUT
 set -u
-N=${1:-2}
-OUT=${2:-gpurun_out/perf_n$N}
+if [ $# -lt 2 ]; then echo "usage: $0 N OUT" >&2; exit 2; fi
+N=$1
+OUT=$2
 mkdir -p "$OUT"
 RUN="python -m torch.distributed.run --nnodes=1 --nproc-per-node $N --master-addr 127.0.0.1"
 export NCCL_DEBUG=${NCCL_DEBUG:-WARN}
