@@ -261,6 +261,27 @@ __device__ void PushBody(const CollArgs &a)
     const uint64_t S = a.sliceBytes;
     const bool isProducer = blockIdx.x < a.producers;
 
+    // Zero-copy stores land in the peer's own output tensor, which the peer's stream may still be reading (the
+    // consumer of its previous collective) or may not have produced yet.  Nothing in the window protocol orders
+    // that: the done-epoch guard only covers window halves.  So every rank announces "I have entered this
+    // launch" to all peers, and a producer block stores to a peer only after that peer's announcement: by then
+    // all earlier work of the peer's stream has finished.  The staged path needs none of this (halves alternate).
+    if (a.zeroCopy && R > 1) {
+        constexpr int64_t READY_SLOT = TILEXR_FLAGS_PER_PAIR - 2;
+        if (ok && blockIdx.x == 0 && static_cast<int>(threadIdx.x) < R && static_cast<int>(threadIdx.x) != rank) {
+            SetFlag(FlagSlot(a.comm, threadIdx.x, TILEXR_FLAG_OP_BASE + static_cast<int64_t>(rank) * TILEXR_FLAGS_PER_PAIR + READY_SLOT),
+                    epoch, 1);
+        }
+        if (isProducer) {
+            bool got = true;
+            if (ok && static_cast<int>(threadIdx.x) < R && static_cast<int>(threadIdx.x) != rank) {
+                const int64_t slot = TILEXR_FLAG_OP_BASE + static_cast<int64_t>(threadIdx.x) * TILEXR_FLAGS_PER_PAIR + READY_SLOT;
+                got = WaitFlagGE(c.w, FlagSlot(a.comm, rank, slot), 1, threadIdx.x, slot);
+            }
+            ok = BlockBroadcastOk(got) && ok;
+        }
+    }
+
     if (ok && isProducer) {
         if (a.kind == COLL_ALL_TO_ALL || a.kind == COLL_SCATTER) {
             // item (tile, k): slice for peer (rank+1+k) % R; k == R-1 is the local slice.  A scatter is the root's

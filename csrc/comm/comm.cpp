@@ -578,14 +578,24 @@ int TileXRComm::DeviceStatus(int *status)
 int TileXRComm::ResetStatus()
 {
     if (!initialized_) return TILEXR_ERROR_NOT_INITIALIZED;
+    // Cleared: the failure record, the abort word, the grid-barrier pairs with the exit counter, and the
+    // operator scratch words (work cursors that a launch returns to zero only when it ends normally).
+    // NOT cleared: the launch epoch word.  Flags and the done-epoch table are never reset, they stay valid
+    // only as long as the epoch keeps growing; a rank that restarted at epoch 1 would find every flag of
+    // its earlier launches already "raised".
+    const size_t headBytes = TILEXR_CTRL_EPOCH_WORD * 8;
+    const size_t scratchOff = TILEXR_CTRL_SCRATCH_WORD * 8;
+    const size_t scratchBytes = TILEXR_CTRL_SCRATCH_WORDS * 8;
     if (isHostMemory()) {
         std::memset(hostArgs_->dfx, 0, sizeof(hostArgs_->dfx));
-        std::memset(window_, 0, TILEXR_CTRL_DONE_WORD * 8);
+        std::memset(window_, 0, headBytes);
+        std::memset(window_ + scratchOff, 0, scratchBytes);
     } else {
         TXR_CUDA(cudaSetDevice(device_));
         TXR_CUDA(cudaDeviceSynchronize());
         TXR_CUDA(cudaMemset(devArgs_->dfx, 0, sizeof(hostArgs_->dfx)));
-        TXR_CUDA(cudaMemset(window_, 0, TILEXR_CTRL_DONE_WORD * 8));
+        TXR_CUDA(cudaMemset(window_, 0, headBytes));
+        TXR_CUDA(cudaMemset(window_ + scratchOff, 0, scratchBytes));
         TXR_CUDA(cudaDeviceSynchronize());
     }
     return isEmulated() ? TILEXR_SUCCESS : HostBarrier();

@@ -367,8 +367,31 @@ int TileXRMoeEpCombineFused(const TileXREpCombineParams *p, TileXRCommPtr comm, 
     unsigned maxGrid = 0;
     ret = MaxCooperativeGrid(comm, EpCombineKernelEntry(), EP_BLOCK_THREADS, 0, ranksPerDevice, &maxGrid);
     if (ret != TILEXR_SUCCESS) return ret;
-    const int64_t want = std::min<int64_t>(EnvLong("TILEXR_EP_BLOCKS", 296), std::max<int64_t>(1, (p->bs * slotsPerToken + 15) / 16));
+    const int64_t minBlocks = std::max<int64_t>(1, EnvLong("TILEXR_EP_MIN_BLOCKS", 32));
+    const int64_t want = std::min<int64_t>(EnvLong("TILEXR_EP_BLOCKS", 296),
+                                           std::max<int64_t>(minBlocks, (p->bs * slotsPerToken + 15) / 16));
     const unsigned grid = static_cast<unsigned>(std::max<int64_t>(1, std::min<int64_t>(want, maxGrid)));
+    // Work decomposition.  It depends on bs, topK, h and the grid cap only, so every rank derives the same one
+    // (bs is the same on all ranks: the slot numbering of the windows relies on it already).
+    {
+        const int64_t warps = static_cast<int64_t>(want) * EP_WARPS;      // `want`, not `grid`: ranks may get different caps
+        const int64_t routes = p->bs * slotsPerToken;
+        const int64_t rowVecs = a.rowBytes / 16;
+        int64_t parts = std::min<int64_t>(8, std::max<int64_t>(1, (4 * warps + routes - 1) / routes));
+        parts = std::min<int64_t>(parts, std::max<int64_t>(1, rowVecs / 32));
+        parts = std::min<int64_t>(parts, std::max<int64_t>(1, TILEXR_FLAG_SLOT_SLOTS / routes));
+        const int64_t partVecs = ((rowVecs + parts - 1) / parts + 31) / 32 * 32;
+        parts = (rowVecs + partVecs - 1) / partVecs;                       // no empty part
+        a.parts = static_cast<uint32_t>(parts);
+        a.partVecs = static_cast<uint32_t>(partVecs);
+        const bool overlap = c.rankSize > 1 && routes >= 8192 && grid >= 16;
+        a.reducerBlocks = overlap ? static_cast<uint32_t>(std::min<int64_t>(grid / 2, std::max<int64_t>(1, EnvLong("TILEXR_EP_REDUCER_BLOCKS", grid / 8)))) : 0u;
+        a.buckets = overlap ? static_cast<uint32_t>(std::min<int64_t>(16, std::max<int64_t>(1, p->bs / 512))) : 1u;
+        a.bucketTokens = static_cast<uint32_t>((p->bs + a.buckets - 1) / a.buckets);
+        int64_t chunkRows = 32;
+        while (chunkRows > 1 && (routes / chunkRows) * a.buckets * parts < 4 * warps) chunkRows /= 2;
+        a.chunkRows = static_cast<uint32_t>(chunkRows);
+    }
     {
         PerfLaunchInfo info{static_cast<uint32_t>(TILEXR_OP_EP_COMBINE), static_cast<uint32_t>(p->dtype),
                             static_cast<uint32_t>(c.rank), static_cast<uint32_t>(c.rankSize), grid,

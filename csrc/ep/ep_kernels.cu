@@ -780,6 +780,26 @@ __device__ void EpDispatchBody(const EpDispatchArgs &a)
 }
 
 // ---- combine -----------------------------------------------------------------------------------------------
+//
+// Work is handed out by two cursors in the rank's control block, so that no warp idles while another still has
+// a queue (rows differ a lot: local rows are skipped, followers are folded into their head, heads sum a chain).
+//
+//   send items    (bucket, chunk of rows, column part): the warp reads the tuples of the chunk's rows, keeps the
+//                 rows that must travel and whose token lies in `bucket`, and sends that column part of each.
+//                 Buckets are ranges of the SOURCE's token index, walked in increasing order by every rank, so a
+//                 token's slots arrive from all ranks at about the same time and in token order;
+//   reduce items  (token, column part) in increasing token order: wait for the part's slot flags, sum.
+//
+// The last `reducerBlocks` blocks take reduce items from the start, the others first send and then join: the
+// reduction of the early buckets overlaps the transfer of the later ones, and after the last row has landed
+// only the last bucket is left to sum.  Every (row, part) has a flag of its own, raised by the sending warp.
+
+__device__ __forceinline__ uint32_t TakeItem(uint32_t *cursor, int lane)
+{
+    uint32_t it = 0;
+    if (lane == 0) it = atomicAdd(cursor, 1u);
+    return __shfl_sync(0xffffffffu, it, 0);
+}
 
 __device__ void EpCombineBody(const EpCombineArgs &a)
 {
@@ -790,124 +810,128 @@ __device__ void EpCombineBody(const EpCombineArgs &a)
     const int K = a.topK;
     const int KR = K + a.topo.sharedExperts;     // slots per token: top-k routes and one per shared expert
     const int lane = threadIdx.x & 31;
-    const int warpsPerBlock = blockDim.x >> 5;
-    const int64_t gwarp = static_cast<int64_t>(blockIdx.x) * warpsPerBlock + (threadIdx.x >> 5);
-    const int64_t nWarps = static_cast<int64_t>(gridDim.x) * warpsPerBlock;
     const uint32_t epoch = w.epoch;
     const bool bf16 = a.isBf16 != 0;
+    const uint32_t P = a.parts;
+    const int rowVecs = a.rowBytes / 16;
+    const int partVecs = a.partVecs;
+    uint32_t *cursors = reinterpret_cast<uint32_t *>(CtrlWord(comm, rank, TILEXR_CTRL_SCRATCH_WORD));
     PerfScope perf = PerfInit(threadIdx.x == 0 ? a.perfTrace : nullptr, static_cast<uint32_t>(rank), blockIdx.x);
     PerfStageBegin(perf, TILEXR_PERF_KERNEL_TOTAL);
 
     if (ok) {
-        PerfStageBegin(perf, TILEXR_PERF_LOCAL_INPUT_TO_IPC);
-        // ---- send every processed row back to slot (token, k) of its source ------------------------------
         const int64_t rows = a.sendCounts[a.sendCountEntries - 1];
         // Rows of this rank's own tokens stay where they are when the reducer knows their row (direct), and the
-        // followers of a group are summed into their head's row.  What is left differs a lot from row to row, so
-        // a block first compacts the rows of its stripes that need sending into a list, and its warps then take
-        // list entries in turn: every warp has work, whatever the mix of local, follower and head rows.
+        // followers of a group are summed into their head's row.
         const bool direct = a.routeRows != nullptr && a.expertIds != nullptr;
-        __shared__ int32_t sUnit[EP_BLOCK_THREADS];
-        __shared__ int sUnitCount;
-        const int tid = threadIdx.x;
-        const int warp = tid >> 5;
-        const int64_t stripe = static_cast<int64_t>(gridDim.x) * 4;
-        for (int64_t base = 0;; base += EP_BLOCK_THREADS) {
-            if ((base >> 2) * stripe + static_cast<int64_t>(blockIdx.x) * 4 >= rows) break;      // block-uniform
-            if (tid == 0) sUnitCount = 0;
-            __syncthreads();
-            {
-                const int64_t li = base + tid;
-                const int64_t r = (li >> 2) * stripe + static_cast<int64_t>(blockIdx.x) * 4 + (li & 3);
-                if (r < rows) {
-                    const Vec16 tuple = ld_vec16(a.assist + r * 4);
-                    const int src = static_cast<int>(tuple.x);
-                    const int64_t slot = static_cast<int64_t>(tuple.y) * KR + tuple.z;
-                    bool send = src >= 0 && src < comm->rankSize && slot >= 0 && slot < static_cast<int64_t>(a.bs) * KR;
-                    if (direct && src == rank) send = false;
-                    if (send && a.dedup != 0 && (static_cast<uint32_t>(a.assistExt[r * 2]) & EP_LINK_FOLLOWER) != 0) send = false;
-                    if (send) sUnit[atomicAdd(&sUnitCount, 1)] = static_cast<int32_t>(r);
-                }
-            }
-            __syncthreads();
-            const int units = sUnitCount;
-            // With few rows to send (small batches) a row is cut into column ranges for several warps.
-            const int rowVecs = a.rowBytes / 16;
-            const int parts = units > 0 ? max(1, min(8, warpsPerBlock / units)) : 1;
-            const int perPart = (((rowVecs + parts - 1) / parts) + 31) & ~31;
-            for (int item = warp; item < units * parts; item += warpsPerBlock) {
-                const int64_t r = sUnit[item / parts];
-                const int vBegin = (item % parts) * perPart;
-                const int vEnd = min(rowVecs, vBegin + perPart);
-                if (vBegin >= vEnd) continue;
-                const Vec16 tuple = ld_vec16(a.assist + r * 4);
-                const int src = static_cast<int>(tuple.x);
-                const int64_t slot = static_cast<int64_t>(tuple.y) * KR + tuple.z;
+        const bool sender = blockIdx.x + a.reducerBlocks < gridDim.x;
+        if (sender) {
+            PerfStageBegin(perf, TILEXR_PERF_LOCAL_INPUT_TO_IPC);
+            const uint32_t c = a.chunkRows;
+            const uint32_t nChunks = static_cast<uint32_t>((rows + c - 1) / c);
+            const uint32_t perBucket = nChunks * P;
+            const uint32_t nItems = perBucket * a.buckets;
+            for (;;) {
+                const uint32_t it = TakeItem(&cursors[0], lane);
+                if (it >= nItems) break;
+                const uint32_t bucket = it / perBucket;
+                const uint32_t inBucket = it - bucket * perBucket;
+                const uint32_t chunk = inBucket / P;
+                const uint32_t part = inBucket - chunk * P;
+                const int64_t r = static_cast<int64_t>(chunk) * c + lane;
+                int src = -1;
+                int64_t slot = 0;
                 uint2 ext = make_uint2(0u, 0u);
-                if (a.dedup != 0) ext = *reinterpret_cast<const uint2 *>(a.assistExt + r * 2);
-                uint8_t *dst = DataHalf(comm, src, epoch) + slot * a.rowBytes;
-                if ((ext.x & EP_LINK_NEXT_MASK) == 0) {
-                    CopyLanes(dst + static_cast<int64_t>(vBegin) * 16, a.expertOut + r * a.rowBytes + static_cast<int64_t>(vBegin) * 16,
-                              static_cast<uint64_t>(vEnd - vBegin) * 16, lane, 32);
-                } else {
-                    // The rows of this token on this rank, in k order, times their gate weights: lane j keeps
-                    // member j of the chain, then every 16-byte column is summed in fp32 and rounded once.
-                    int64_t memberRow = -1;
-                    float memberW = 0.f;
-                    int members = 0;
-                    int64_t cur = r;
-                    uint2 e2 = ext;
-                    while (members < KR) {
-                        if (lane == members) {
-                            memberRow = cur;
-                            memberW = __uint_as_float(e2.y);
-                        }
-                        ++members;
-                        const uint32_t next = e2.x & EP_LINK_NEXT_MASK;
-                        if (next == 0 || static_cast<int64_t>(next) - 1 >= rows) break;
-                        cur = static_cast<int64_t>(next) - 1;
-                        e2 = *reinterpret_cast<const uint2 *>(a.assistExt + cur * 2);
-                    }
-                    for (int v0 = vBegin; v0 < vEnd; v0 += 64) {        // two columns per lane: eight loads in flight
-                        const int va = v0 + lane, vb = v0 + 32 + lane;
-                        float accA[8], accB[8];
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) accA[i] = accB[i] = 0.f;
-#pragma unroll 4
-                        for (int j = 0; j < members; ++j) {
-                            const int64_t mr = __shfl_sync(0xffffffffu, memberRow, j);
-                            const float mw = __shfl_sync(0xffffffffu, memberW, j);
-                            const uint8_t *rowPtr = a.expertOut + mr * a.rowBytes;
-                            Vec16 qa = Vec16{0u, 0u, 0u, 0u}, qb = Vec16{0u, 0u, 0u, 0u};
-                            if (va < vEnd) qa = ld_vec16_stream(rowPtr + va * 16);
-                            if (vb < vEnd) qb = ld_vec16_stream(rowPtr + vb * 16);
-                            float f[8];
-                            Unpack8(qa, bf16, f);
-#pragma unroll
-                            for (int i = 0; i < 8; ++i) accA[i] = fmaf(mw, f[i], accA[i]);
-                            Unpack8(qb, bf16, f);
-#pragma unroll
-                            for (int i = 0; i < 8; ++i) accB[i] = fmaf(mw, f[i], accB[i]);
-                        }
-                        if (va < vEnd) st_vec16(dst + va * 16, Pack8(accA, bf16));
-                        if (vb < vEnd) st_vec16(dst + vb * 16, Pack8(accB, bf16));
+                bool send = false;
+                if (lane < static_cast<int>(c) && r < rows) {
+                    const Vec16 tuple = ld_vec16(a.assist + r * 4);
+                    src = static_cast<int>(tuple.x);
+                    slot = static_cast<int64_t>(tuple.y) * KR + tuple.z;
+                    send = src >= 0 && src < comm->rankSize && tuple.y < static_cast<uint32_t>(a.bs) && tuple.z < static_cast<uint32_t>(KR);
+                    if (direct && src == rank) send = false;
+                    if (send && min(tuple.y / a.bucketTokens, a.buckets - 1u) != bucket) send = false;
+                    if (send && a.dedup != 0) {
+                        ext = *reinterpret_cast<const uint2 *>(a.assistExt + r * 2);
+                        if ((ext.x & EP_LINK_FOLLOWER) != 0) send = false;
                     }
                 }
+                uint32_t m = __ballot_sync(0xffffffffu, send);
+                const int vBegin = static_cast<int>(part) * partVecs;
+                const int vEnd = min(rowVecs, vBegin + partVecs);
+                while (m != 0) {
+                    const int j = __ffs(m) - 1;
+                    m &= m - 1;
+                    const int64_t rj = static_cast<int64_t>(chunk) * c + j;
+                    const int srcJ = __shfl_sync(0xffffffffu, src, j);
+                    const int64_t slotJ = __shfl_sync(0xffffffffu, slot, j);
+                    const uint32_t linkJ = __shfl_sync(0xffffffffu, ext.x, j);
+                    const uint32_t wbitsJ = __shfl_sync(0xffffffffu, ext.y, j);
+                    uint8_t *dst = DataHalf(comm, srcJ, epoch) + slotJ * a.rowBytes;
+                    if ((linkJ & EP_LINK_NEXT_MASK) == 0) {
+                        CopyLanes(dst + static_cast<int64_t>(vBegin) * 16, a.expertOut + rj * a.rowBytes + static_cast<int64_t>(vBegin) * 16,
+                                  static_cast<uint64_t>(vEnd - vBegin) * 16, lane, 32);
+                    } else {
+                        // The rows of this token on this rank, in k order, times their gate weights: lane i keeps
+                        // member i of the chain, then every 16-byte column is summed in fp32 and rounded once.
+                        int64_t memberRow = -1;
+                        float memberW = 0.f;
+                        int members = 0;
+                        int64_t cur = rj;
+                        uint2 e2 = make_uint2(linkJ, wbitsJ);
+                        while (members < KR) {
+                            if (lane == members) {
+                                memberRow = cur;
+                                memberW = __uint_as_float(e2.y);
+                            }
+                            ++members;
+                            const uint32_t next = e2.x & EP_LINK_NEXT_MASK;
+                            if (next == 0 || static_cast<int64_t>(next) - 1 >= rows) break;
+                            cur = static_cast<int64_t>(next) - 1;
+                            e2 = *reinterpret_cast<const uint2 *>(a.assistExt + cur * 2);
+                        }
+                        for (int v0 = vBegin; v0 < vEnd; v0 += 64) {        // two columns per lane: eight loads in flight
+                            const int va = v0 + lane, vb = v0 + 32 + lane;
+                            float accA[8], accB[8];
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) accA[i] = accB[i] = 0.f;
+#pragma unroll 4
+                            for (int i = 0; i < members; ++i) {
+                                const int64_t mr = __shfl_sync(0xffffffffu, memberRow, i);
+                                const float mw = __shfl_sync(0xffffffffu, memberW, i);
+                                const uint8_t *rowPtr = a.expertOut + mr * a.rowBytes;
+                                Vec16 qa = Vec16{0u, 0u, 0u, 0u}, qb = Vec16{0u, 0u, 0u, 0u};
+                                if (va < vEnd) qa = ld_vec16_stream(rowPtr + va * 16);
+                                if (vb < vEnd) qb = ld_vec16_stream(rowPtr + vb * 16);
+                                float f[8];
+                                Unpack8(qa, bf16, f);
+#pragma unroll
+                                for (int q = 0; q < 8; ++q) accA[q] = fmaf(mw, f[q], accA[q]);
+                                Unpack8(qb, bf16, f);
+#pragma unroll
+                                for (int q = 0; q < 8; ++q) accB[q] = fmaf(mw, f[q], accB[q]);
+                            }
+                            if (va < vEnd) st_vec16(dst + va * 16, Pack8(accA, bf16));
+                            if (vb < vEnd) st_vec16(dst + vb * 16, Pack8(accB, bf16));
+                        }
+                    }
+                    // every lane's stores of this part are ordered before the flag by the warp barrier and the release
+                    __syncwarp();
+                    if (lane == 0) SetFlag(FlagSlot(comm, srcJ, TILEXR_FLAG_SLOT_BASE + slotJ * P + part), epoch, 1);
+                }
             }
-            __syncthreads();
-            // every part of a row is stored: one thread per row releases its flag
-            for (int u = tid; u < units; u += blockDim.x) {
-                const Vec16 tuple = ld_vec16(a.assist + static_cast<int64_t>(sUnit[u]) * 4);
-                const int64_t slot = static_cast<int64_t>(tuple.y) * KR + tuple.z;
-                SetFlag(FlagSlot(comm, static_cast<int>(tuple.x), TILEXR_FLAG_SLOT_BASE + slot), epoch, 1);
-            }
+            PerfStageEnd(perf, TILEXR_PERF_LOCAL_INPUT_TO_IPC);
         }
-        PerfStageEnd(perf, TILEXR_PERF_LOCAL_INPUT_TO_IPC);
         PerfStageBegin(perf, TILEXR_PERF_PEER_IPC_TO_OUTPUT);
         // ---- reduce this rank's tokens ------------------------------------------------------------------------
         const uint8_t *half = DataHalf(comm, rank, epoch);
-        const int vecs = a.rowBytes / 16;
-        for (int64_t t = gwarp; t < a.bs && w.ok(); t += nWarps) {
+        const uint32_t nReduce = static_cast<uint32_t>(a.bs) * P;
+        while (w.ok()) {
+            const uint32_t it = TakeItem(&cursors[1], lane);
+            if (it >= nReduce) break;
+            const int64_t t = it / P;
+            const uint32_t part = it - static_cast<uint32_t>(t) * P;
+            const int vBegin = static_cast<int>(part) * partVecs;
+            const int vEnd = min(rowVecs, vBegin + partVecs);
             int e = -1;
             float wk = 0.f;
             unsigned long long myRowPtr = 0;
@@ -939,16 +963,14 @@ __device__ void EpCombineBody(const EpCombineArgs &a)
                 if (lower) e = -1;
                 else if (higher) wk = 1.0f;
             }
-            if (lane < KR) {
-                if (e >= 0) {
-                    const int64_t slot = t * KR + lane;
-                    const int64_t localRow = direct && myDst == rank ? a.routeRows[slot] : -1;
-                    if (localRow >= 0 && localRow < rows) {
-                        myRowPtr = reinterpret_cast<unsigned long long>(a.expertOut + localRow * a.rowBytes);
-                    } else {
-                        myRowPtr = reinterpret_cast<unsigned long long>(half + slot * a.rowBytes);
-                        WaitFlagGE(w, FlagSlot(comm, rank, TILEXR_FLAG_SLOT_BASE + slot), 1, myDst, slot);
-                    }
+            if (lane < KR && e >= 0) {
+                const int64_t slot = t * KR + lane;
+                const int64_t localRow = direct && myDst == rank ? a.routeRows[slot] : -1;
+                if (localRow >= 0 && localRow < rows) {
+                    myRowPtr = reinterpret_cast<unsigned long long>(a.expertOut + localRow * a.rowBytes);
+                } else {
+                    myRowPtr = reinterpret_cast<unsigned long long>(half + slot * a.rowBytes);
+                    WaitFlagGE(w, FlagSlot(comm, rank, TILEXR_FLAG_SLOT_BASE + slot * P + part), 1, myDst, slot);
                 }
             }
             const bool good = __all_sync(0xffffffffu, w.ok());
@@ -958,9 +980,9 @@ __device__ void EpCombineBody(const EpCombineArgs &a)
             }
             const uint32_t active = __ballot_sync(0xffffffffu, e >= 0);
             uint8_t *y = a.yOut + t * a.rowBytes;
-            for (int v0 = 0; v0 < vecs; v0 += 32) {  // warp-uniform trip count: the loop body shuffles
+            for (int v0 = vBegin; v0 < vEnd; v0 += 32) {  // warp-uniform trip count: the loop body shuffles
                 const int v = v0 + lane;
-                const bool mine = v < vecs;
+                const bool mine = v < vEnd;
                 float acc[8];
 #pragma unroll
                 for (int j = 0; j < 8; ++j) acc[j] = 0.f;
@@ -1002,7 +1024,7 @@ __device__ void EpCombineBody(const EpCombineArgs &a)
     }
     ok = BlockBroadcastOk(ok);
     PerfStageEnd(perf, TILEXR_PERF_KERNEL_TOTAL);
-    KernelEpilogue(w, ok);
+    KernelEpilogue(w, ok, 1);      // both cursors live in scratch word 0
 }
 
 TILEXR_DEFINE_KERNEL_OCC(TileXREpDispatchKernel, EpDispatchArgs, EpDispatchBody, EP_BLOCK_THREADS, 2)

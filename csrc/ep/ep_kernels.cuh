@@ -120,6 +120,13 @@ struct EpCombineArgs {
     const int32_t *routeRows;        // [bs, topK] from dispatch: local routes bypass the window; or null
     const int32_t *assistExt;        // [rows, 2] {link, weight bits}
     uint32_t dedup;
+    // Work decomposition, the same on every rank (the flag of (slot, part) is slot * parts + part):
+    uint32_t parts;                  // column ranges a row is cut into (1 unless the batch is small)
+    uint32_t partVecs;               // 16-byte vectors per part, a multiple of 32
+    uint32_t chunkRows;              // rows whose tuples one send item examines, a power of two <= 32
+    uint32_t buckets;                // ranges of the source token index that the senders walk in order
+    uint32_t bucketTokens;           // tokens per bucket
+    uint32_t reducerBlocks;          // trailing blocks that only reduce
 };
 
 // link word of a row: bit 31 = the row is a follower (its payload is a copy of its group's head row);

@@ -249,7 +249,9 @@ __device__ __forceinline__ bool KernelPrologue(Waiter &w, CommArgs *args, int64_
 
 // Everything a kernel body does last.  `exitCounter` is a 32-bit word in the rank's control
 // block that counts finished blocks; the last block publishes the done epoch and the status.
-__device__ __forceinline__ void KernelEpilogue(Waiter &w, bool ok)
+// `scratchWords` operator scratch words of the rank's control block (work cursors and the like) are returned
+// to zero by the last block, so that the next launch that uses them finds them clear.
+__device__ __forceinline__ void KernelEpilogue(Waiter &w, bool ok, int scratchWords = 0)
 {
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -258,6 +260,7 @@ __device__ __forceinline__ void KernelEpilogue(Waiter &w, bool ok)
         uint32_t *exitCounter =
             reinterpret_cast<uint32_t *>(CtrlWord(a, a->rank, TILEXR_CTRL_GRIDBAR_WORD + TILEXR_CTRL_GRIDBAR_COUNT));
         if (atom_add_acq_rel_gpu_u32(exitCounter, 1) == gridDim.x - 1) {
+            for (int i = 0; i < scratchWords; ++i) *CtrlWord(a, a->rank, TILEXR_CTRL_SCRATCH_WORD + i) = 0;
             st_release_gpu_u32(exitCounter, 0);
             PublishDone(w);
             *CtrlWord(a, a->rank, TILEXR_CTRL_EPOCH_WORD) = w.epoch;

@@ -181,6 +181,11 @@ def test_ep_dedup_staged_output_and_masks(txr):
     _ep_case(txr, ranks=4, bs=37, h=256, experts=32, top_k=6, quant=False, fused_routing=True, masks=True)
 
 
+def test_ep_large_batch_overlapped_combine(txr):
+    # enough routes for combine's bucketed send order with dedicated reducer blocks
+    _ep_case(txr, ranks=2, bs=1536, h=512, experts=16, top_k=8, quant=True, fused_routing=True, zero_copy=True)
+
+
 def test_ep_dedup_off_matches(txr):
     _ep_case(txr, ranks=4, bs=40, h=1024, experts=32, top_k=4, quant=True, fused_routing=True, dedup=False)
 
@@ -315,6 +320,56 @@ def test_ep_overflow_is_reported_not_written(txr):
     assert all(c.device_status() == 4 for c in world.comms)      # TILEXR_DEV_BAD_ARGUMENT on every rank
     for c in world.comms:
         c.reset_status()
+    world.destroy()
+
+
+def test_reset_status_keeps_flags_meaningful(txr):
+    """After a failed launch and reset_status the next launches must still WAIT for their flags: the reset keeps
+    the launch epoch, so flags left by earlier launches stay older than anything a new launch waits for."""
+    from tilexr_b200.ops import ep
+    from tilexr_b200.utils import oracle
+
+    ranks = 4
+    world = txr.init_emulated_world(ranks, device=0, buffer_mb=64)
+    g = torch.Generator().manual_seed(5)
+    # a few launches first, so that flags and done epochs of earlier launches exist
+    for i in range(5):
+        xs = [torch.randn(3000, generator=g).cuda() for _ in range(ranks)]
+        outs = world.run(lambda c, r: txr.all_reduce(c, xs[r]))
+        world.check()
+        assert torch.allclose(outs[0], sum(xs), rtol=1e-5, atol=1e-5)
+    epoch_before = [c.dfx()[0] for c in world.comms]
+    x = [torch.randn(16, 256, generator=g).to(torch.bfloat16).cuda() for _ in range(ranks)]
+    ids = [torch.zeros(16, 2, dtype=torch.int32).cuda() for _ in range(ranks)]
+    for r in range(ranks):
+        ids[r][:, 1] = 1
+    world.run(lambda c, r: ep.dispatch(c, x[r], expert_ids=ids[r], num_experts=8, top_k=2, max_recv_rows=8))
+    torch.cuda.synchronize()
+    assert all(c.device_status() == 4 for c in world.comms)
+    for c in world.comms:
+        c.reset_status()
+    assert all(c.device_status() == 0 for c in world.comms)
+    for i in range(3):
+        xs = [torch.randn(5000, generator=g).cuda() for _ in range(ranks)]
+        outs = world.run(lambda c, r: txr.all_reduce(c, xs[r]))
+        gathered = world.run(lambda c, r: txr.all_gather(c, xs[r]))
+        world.check()
+        for r in range(ranks):
+            assert torch.allclose(outs[r], sum(xs), rtol=1e-5, atol=1e-5)
+            assert torch.equal(gathered[r], torch.stack(xs))
+    assert all(c.dfx()[0] > e for c, e in zip(world.comms, epoch_before))      # the epoch went on, it did not restart
+    xs = [torch.randn(24, 256, generator=g).to(torch.bfloat16) for _ in range(ranks)]
+    ids = [torch.randint(0, 8, (24, 2), generator=g, dtype=torch.int32) for _ in range(ranks)]
+    for t in ids:
+        t[:, 1] = (t[:, 0] + 1 + t[:, 1] % 7) % 8                                # two different experts per token
+    res = world.run(lambda c, r: ep.dispatch(c, xs[r].cuda(), expert_ids=ids[r].cuda(), num_experts=8, top_k=2))
+    world.check()
+    ref = oracle.ep_dispatch_ref(xs, ids, 8, None)
+    for r in range(ranks):
+        n = int(res[r].recv_total.item())
+        assert n == len(ref[r]["rows"])
+        assert torch.equal(res[r].assist[:n].cpu(), ref[r]["assist"])
+        assert torch.equal(res[r].expand_x[:n].cpu(), ref[r]["expand_x"])
     world.destroy()
 
 
