@@ -143,6 +143,77 @@ def reference_unavailable():
     }))
 
 
+def verify_against_oracle(txr, ep, quant, comm, rank, world, dev, H, E, K, dist, tokens=256):
+    """One dispatch -> dequantise -> combine step on `tokens` tokens per rank, compared with the CPU oracle: the
+    assist tuples exactly, the received fp8 rows and scales exactly, y within 2e-2 of the fp32 gate-weighted
+    sum of the dequantised rows.  Every rank regenerates all ranks' inputs from fixed seeds.  Raises on a
+    mismatch; returns True."""
+    import torch
+    from tilexr_b200.utils import oracle
+
+    gens = [torch.Generator(device="cpu").manual_seed(777 + r) for r in range(world)]
+    xs = [torch.randn(tokens, H, generator=g).to(torch.bfloat16) for g in gens]
+    logits = [torch.randn(tokens, E, generator=g) for g in gens]
+    routed = [oracle.routing_topk_ref(l, K, quant.SCORE_SIGMOID, True) for l in logits]
+    cap = tokens * K * world
+    recv = comm.symm_empty([cap, H], torch.float8_e4m3fn)
+    d = ep.dispatch(comm, xs[rank].to(dev), gate_logits=logits[rank].to(dev), num_experts=E, top_k=K,
+                    quant_mode=ep.QUANT_FP8_1X128, score_func=quant.SCORE_SIGMOID, renormalize=True, max_recv_rows=cap,
+                    expand_x_out=recv)
+    rows = quant.fp8_dequant_1x128(d.expand_x, d.dynamic_scales, torch.bfloat16)
+    y = ep.combine(comm, rows, d, expert_scales=d.topk_weights)
+    torch.cuda.synchronize()
+    if comm.device_status() != 0:
+        raise SystemExit(f"rank {rank}: verification step failed on the device: status {comm.device_status()}")
+    want_assist = oracle.ep_dispatch_assist_ref([r[0] for r in routed], E)[rank]
+    n = int(d.recv_total.item())
+    problems = []
+    if n != want_assist.shape[0] or not torch.equal(d.assist[:n].cpu(), want_assist):
+        problems.append("assist tuples differ from the oracle")
+    else:
+        src_rows = torch.stack([xs[int(s)][int(t)] for s, t, _, _ in want_assist.tolist()]) if n else xs[0][:0]
+        rq, rs = oracle.fp8_quant_1x128_ref(src_rows) if n else (None, None)
+        if n and not torch.equal(d.expand_x[:n].cpu().view(torch.uint8), rq.view(torch.uint8)):
+            problems.append("received fp8 rows differ from the oracle")
+        if n and not torch.equal(d.dynamic_scales[:n].cpu(), rs):
+            problems.append("received scales differ from the oracle")
+    if not torch.equal(d.topk_ids.cpu(), routed[rank][0]):
+        problems.append("top-k ids differ from the oracle")
+    q, sc = oracle.fp8_quant_1x128_ref(xs[rank])
+    deq = oracle.fp8_dequant_1x128_ref(q, sc).to(torch.bfloat16).float()
+    want_y = deq * routed[rank][1].sum(dim=1, keepdim=True)          # identity expert: y = sum_k w_k * row
+    got_y = y.cpu().float()
+    if not torch.allclose(got_y, want_y, rtol=2e-2, atol=2e-2):
+        problems.append(f"y differs from the oracle by up to {(got_y - want_y).abs().max().item():.4f}")
+    if problems:
+        raise SystemExit(f"rank {rank}: verification against the CPU oracle failed: " + "; ".join(problems))
+    return True
+
+
+def nccl_comm_only(torch, dist, dev, world, T, H, K, max_over_ranks, iters=10):
+    """Device time of `all_to_all_single` moving exactly the bytes that cross NVLink in dispatch (fp8 rows, scales
+    and tuples) and in combine (bf16 rows), equal splits, nothing else: no routing, no permutation, no host sync."""
+    remote_rows = (world - 1) * (1.0 - (1.0 - 1.0 / world) ** K)
+    out = {}
+    for name, row_bytes in (("dispatch", H + H // 128 * 4 + 16), ("combine", H * 2)):
+        per_peer = int(T * remote_rows / (world - 1) * row_bytes) // 16 * 16
+        send = torch.empty(world * per_peer, dtype=torch.uint8, device=dev)
+        recv = torch.empty_like(send)
+        for _ in range(3):
+            dist.all_to_all_single(recv, send)
+        torch.cuda.synchronize()
+        dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            dist.all_to_all_single(recv, send)
+        e1.record()
+        torch.cuda.synchronize()
+        out[name] = max_over_ranks(e0.elapsed_time(e1) * 1000 / iters)
+        out[name + "_bytes_per_gpu"] = per_peer * (world - 1)
+    return out
+
+
 _RESULT_STREAM = None
 
 
@@ -255,6 +326,13 @@ def main():
             comm.print_dfx()
             raise SystemExit(f"rank {rank}: a device-side wait gave up: status {comm.device_status()}, dfx {list(comm.dfx())[:24]}")
 
+    # ---- correctness first: one step on a reduced token count against the CPU oracle ------------------
+    verified = None
+    if args.impl == "tilexr":
+        verified = verify_against_oracle(txr, ep, quant, comm, rank, world, dev, H, E, K, dist if world > 1 else None)
+        barrier()
+        check()
+
     # NVML is brought up before the warm-up steps so that its first, slow queries are long over
     sampler = ClockSampler(physical_device_index(local_rank), args.clock_interval_ms / 1000.0)
     sampler.start()
@@ -312,14 +390,25 @@ def main():
     check()
 
     # per-phase medians (separate pass, not the headline)
+    # A tiny all-reduce in front of each measured step lines the ranks up on the device, so that a phase's
+    # time is the kernel's and not the distance between two ranks' Python threads.
     parts = []
+    align = torch.zeros(1, device=dev)
     for i in range(min(steps, 10)):
         ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+        if world > 1:
+            dist.all_reduce(align)
         step_parts(i, ev)
         torch.cuda.synchronize()
         parts.append([ev[j].elapsed_time(ev[j + 1]) * 1000 for j in range(3)])
     phase_us = [max_over_ranks(statistics.median(p[j] for p in parts)) for j in range(3)]
     barrier()
+
+    # ---- communication-only NCCL arm: all_to_all_single of exactly the bytes the kernels move ---------
+    nccl_comm_us = None
+    if world > 1 and args.impl == "tilexr":
+        nccl_comm_us = nccl_comm_only(torch, dist, dev, world, T, H, K, max_over_ranks)
+        barrier()
 
     if args.stage_profile and args.impl == "tilexr":
         from tilexr_b200.utils.stage_profile import format_summaries, stage_profile
@@ -440,6 +529,22 @@ def main():
         "gpu_launches": int(launches),
         "host_issue_ms_per_step": round(host_issue_ms, 4),
     }
+    if args.impl == "tilexr":
+        out["verified"] = bool(verified)
+        comm_us = phase_us[0] + phase_us[2]
+        out["value_comm_only"] = T * world / (comm_us * 1e-6)      # dispatch + combine without the stand-in kernel
+        if world > 1:
+            disp_bytes = T * remote_rows * route_bytes
+            comb_bytes = T * remote_rows * H * 2
+            out["roofline_fraction"] = {
+                "of_900_GBps_nominal": {"dispatch": disp_bytes / 900e9 / (phase_us[0] * 1e-6),
+                                        "combine": comb_bytes / 900e9 / (phase_us[2] * 1e-6)},
+                "of_770_GBps_measured_peer_copy": {"dispatch": disp_bytes / 770e9 / (phase_us[0] * 1e-6),
+                                                   "combine": comb_bytes / 770e9 / (phase_us[2] * 1e-6)},
+            }
+        if nccl_comm_us is not None:
+            out["nccl_comm_only_us"] = nccl_comm_us
+            out["vs_nccl_comm_only"] = (nccl_comm_us["dispatch"] + nccl_comm_us["combine"]) / comm_us
     if e2e is not None:
         out["e2e"] = e2e
     if rank == 0:

@@ -2,6 +2,7 @@
 // Validation rules follow the reference's memory route (src/ep/host/ep_dispatch_memory_host.cpp:44-107,
 // ep_memory_layout.cpp:67-306) where they still apply on this hardware.
 #include <algorithm>
+#include <cmath>
 #include <cstdlib>
 #include <cstring>
 
@@ -47,8 +48,6 @@ bool DispatchLayout(int64_t h, int64_t numExperts, int64_t rankSize, int64_t max
     off = Align(off + static_cast<uint64_t>(maxRecvRows) * 16, 256);
     win->extOff = off;
     off = Align(off + static_cast<uint64_t>(maxRecvRows) * 8, 256);
-    win->countOff = off;
-    off = Align(off + (static_cast<uint64_t>(rankSize) * numExperts + rankSize) * 4, 256);
     win->blockCountOff = off;
     off = Align(off + static_cast<uint64_t>(grid) * numExperts * 4, 256);
     win->totalBytes = off;
@@ -174,6 +173,10 @@ int TileXRMoeEpDispatchFused(const TileXREpDispatchParams *p, TileXRCommPtr comm
     const int64_t numCols = topo.sharedRanks + p->moeExpertNum;
     const int64_t routesPerToken = p->topK + topo.sharedExperts;
     const int64_t smemCols = std::max<int64_t>(numCols, static_cast<int64_t>(topo.moePerRank) * c.rankSize);
+    if (static_cast<int64_t>(c.rankSize) * ((numCols + 3) / 3) * 16 > TILEXR_WIN_LL_HALF_BYTES) {
+        TILEXR_LOG(ERROR) << "EP: the count vectors of " << c.rankSize << " ranks x " << numCols << " columns exceed the low-latency plane";
+        return TILEXR_ERROR_PARA_CHECK_FAIL;
+    }
     if (p->bs * routesPerToken > TILEXR_FLAG_SLOT_SLOTS) {
         TILEXR_LOG(ERROR) << "EP: bs * (topK + sharedExpertNum) exceeds the " << TILEXR_FLAG_SLOT_SLOTS << " slot flags of a window";
         return TILEXR_ERROR_PARA_CHECK_FAIL;
@@ -377,7 +380,24 @@ int TileXRMoeEpCombineFused(const TileXREpCombineParams *p, TileXRCommPtr comm, 
         const int64_t warps = static_cast<int64_t>(want) * EP_WARPS;      // `want`, not `grid`: ranks may get different caps
         const int64_t routes = p->bs * slotsPerToken;
         const int64_t rowVecs = a.rowBytes / 16;
-        int64_t parts = std::min<int64_t>(8, std::max<int64_t>(1, (4 * warps + routes - 1) / routes));
+        // The rows that travel, estimated for uniform routing (one row per token and remote rank with dedup).
+        double travel = static_cast<double>(routes) * (c.rankSize - 1) / c.rankSize;
+        if (a.dedup != 0) {
+            double miss = 1.0;
+            for (int64_t k = 0; k < slotsPerToken; ++k) miss *= 1.0 - 1.0 / c.rankSize;
+            travel = static_cast<double>(p->bs) * (c.rankSize - 1) * (1.0 - miss);
+        }
+        // one rank that knows the row of each of its own routes: nothing travels
+        a.noSend = (c.rankSize == 1 && a.routeRows != nullptr && a.expertIds != nullptr) ? 1u : 0u;
+        // Column parts: a warp should get through about eight send items in a row, so that rows leave in the
+        // order of the queue (the reducers follow that order) instead of all at once; small batches are cut up
+        // so that every warp has something to do.
+        int64_t parts;
+        if (a.noSend != 0) {
+            parts = std::min<int64_t>(8, std::max<int64_t>(1, (4 * warps + routes - 1) / routes));
+        } else {
+            parts = static_cast<int64_t>(std::min(8.0, std::max(1.0, std::ceil(8.0 * warps / std::max(1.0, travel)))));
+        }
         parts = std::min<int64_t>(parts, std::max<int64_t>(1, rowVecs / 32));
         parts = std::min<int64_t>(parts, std::max<int64_t>(1, TILEXR_FLAG_SLOT_SLOTS / routes));
         const int64_t partVecs = ((rowVecs + parts - 1) / parts + 31) / 32 * 32;
@@ -385,11 +405,27 @@ int TileXRMoeEpCombineFused(const TileXREpCombineParams *p, TileXRCommPtr comm, 
         a.parts = static_cast<uint32_t>(parts);
         a.partVecs = static_cast<uint32_t>(partVecs);
         const bool overlap = c.rankSize > 1 && routes >= 8192 && grid >= 16;
-        a.reducerBlocks = overlap ? static_cast<uint32_t>(std::min<int64_t>(grid / 2, std::max<int64_t>(1, EnvLong("TILEXR_EP_REDUCER_BLOCKS", grid / 8)))) : 0u;
-        a.buckets = overlap ? static_cast<uint32_t>(std::min<int64_t>(16, std::max<int64_t>(1, p->bs / 512))) : 1u;
+        // Blocks that only reduce, in proportion to the rows each side reads and writes: the senders read every
+        // remote-bound row and write the travelling ones, the reducers read what arrives plus the local rows and
+        // write the tokens.
+        const double sendWork = static_cast<double>(routes) * (c.rankSize - 1) / c.rankSize + travel;
+        const double reduceWork = travel + static_cast<double>(routes) / c.rankSize + static_cast<double>(p->bs);
+        const int64_t reducersAuto = static_cast<int64_t>(grid * reduceWork / (sendWork + reduceWork));
+        a.reducerBlocks = overlap ? static_cast<uint32_t>(std::min<int64_t>(grid / 2, std::max<int64_t>(grid / 8, EnvLong("TILEXR_EP_REDUCER_BLOCKS", reducersAuto)))) : 0u;
+        a.buckets = overlap ? static_cast<uint32_t>(std::min<int64_t>(EP_MAX_BUCKETS, std::max<int64_t>(1, p->bs / 512))) : 1u;
+        // bucket lists live behind the slots in the same data half, when there is room for every row of the worst case
+        a.listOff = (need + 255) & ~static_cast<uint64_t>(255);
+        const uint64_t listRoom = c.hostArgs->dataHalfBytes > a.listOff ? (c.hostArgs->dataHalfBytes - a.listOff) / (4ull * a.buckets) : 0;
+        a.listCap = static_cast<uint32_t>(std::min<uint64_t>(listRoom, static_cast<uint64_t>(routes) * c.rankSize));
+        if (a.listCap < static_cast<uint64_t>(routes)) a.buckets = 1;
         a.bucketTokens = static_cast<uint32_t>((p->bs + a.buckets - 1) / a.buckets);
+        // Unsorted walk: a send item looks at the tuples of chunkRows rows; about one travelling row per item
+        // keeps the queue fine-grained without paying a cursor update for nothing.
         int64_t chunkRows = 32;
-        while (chunkRows > 1 && (routes / chunkRows) * a.buckets * parts < 4 * warps) chunkRows /= 2;
+        while (chunkRows > 1 && (static_cast<double>(routes) / std::max(1.0, travel) < chunkRows ||
+                                 (routes / chunkRows) * parts < 2 * warps)) {
+            chunkRows /= 2;
+        }
         a.chunkRows = static_cast<uint32_t>(chunkRows);
     }
     {

@@ -5,11 +5,12 @@
 //   1. every block takes a contiguous range of tokens, routes them (top-k over the gate logits,
 //      or reads the given expert ids and masks), and ranks its routes per expert in (token, k)
 //      order; per-block expert counts go to a scratch table;
-//   2. after one barrier among the rank's blocks, block 0 sums the table and pushes the rank's
-//      count vector to every peer (an all-gather of R x E integers).  With everybody's counts
-//      each rank computes, for itself as a sender, the exact row at which each of its routes
-//      lands in the destination's expert-major / source-major layout: rows are placed at their
-//      FINAL position by the sender, the receiver never sorts or compacts;
+//   2. blocks also add their counts to the rank's totals; the block that finishes last pushes the totals
+//      to every peer as epoch-tagged 16-byte units (an all-gather of R x E integers without fence or
+//      flag), and a block goes on as soon as the blocks before it have written their counts (no grid
+//      barrier).  With everybody's counts each rank computes, for itself as a sender, the exact row at
+//      which each of its routes lands in the destination's expert-major / source-major layout: rows are
+//      placed at their FINAL position by the sender, the receiver never sorts or compacts;
 //   3. a warp per token quantises the row once (fp8 e4m3, one fp32 scale per 128 elements, kept
 //      in registers) and stores it to each destination together with its scales and the assist
 //      tuple; when the block is done it raises one flag per destination;
@@ -31,6 +32,7 @@
 #include <cstdio>
 #include <cuda_runtime_api.h>
 
+#include "device/tilexr_data_as_flag.cuh"
 #include "device/tilexr_perf_trace.cuh"
 #include "device/tilexr_rma.cuh"
 #include "device/tilexr_sync.cuh"
@@ -284,7 +286,7 @@ __device__ void SumBlockCounts(const int32_t *counts, int E, int nb, int32_t *ou
 }
 
 // Stage names of the profiler as the EP kernels use them: chunk_total = routing and counting (dispatch) or
-// nothing (combine); chunk_barrier = grid barrier; post_sync = count exchange and row placement;
+// nothing (combine); chunk_barrier = wait for the earlier blocks' counts; post_sync = count exchange and row placement;
 // local_input_to_ipc = rows pushed to their destinations; flag_poll_wait = waiting for arrivals;
 // peer_ipc_to_output = window to output (dispatch) or the weighted reduction (combine).
 __device__ void EpDispatchBody(const EpDispatchArgs &a)
@@ -312,7 +314,16 @@ __device__ void EpDispatchBody(const EpDispatchArgs &a)
     PerfStageBegin(perf, TILEXR_PERF_KERNEL_TOTAL);
     PerfStageBegin(perf, TILEXR_PERF_CHUNK_TOTAL);
     int32_t *blockCounts = reinterpret_cast<int32_t *>(myHalf + a.win.blockCountOff);
-    const int32_t *countMatrix = reinterpret_cast<const int32_t *>(myHalf + a.win.countOff);
+    // operator scratch of the rank's control block (tilexr_comm_args.h): a count of the blocks that have finished
+    // counting and the rank's totals per column, both back to zero when the launch ends; and one word per
+    // block that holds the epoch of the launch whose histogram the block has written (never cleared)
+    uint32_t *doneBlocks = reinterpret_cast<uint32_t *>(CtrlWord(comm, rank, TILEXR_CTRL_SCRATCH_WORD + EP_SCRATCH_DONE_WORD));
+    uint32_t *totals = reinterpret_cast<uint32_t *>(CtrlWord(comm, rank, TILEXR_CTRL_SCRATCH_WORD + EP_SCRATCH_TOTALS_WORD));
+    uint32_t *histReady = reinterpret_cast<uint32_t *>(CtrlWord(comm, rank, TILEXR_CTRL_SCRATCH_WORD + EP_SCRATCH_READY_WORD));
+    int32_t *srcBlocks = reinterpret_cast<int32_t *>(sm.scaleStage);       // [R] blocks of each source that raise a flag
+    const int units = (C + 1 + 2) / 3;           // 16-byte units of one source's counts: C counts and its block count
+    const uint8_t *llMine = LlHalf(comm, rank, epoch);
+    __shared__ int sIsLast;
 
     const int t0 = min(a.bs, static_cast<int>(blockIdx.x * a.tokensPerBlock));
     const int t1 = min(a.bs, t0 + static_cast<int>(a.tokensPerBlock));
@@ -344,63 +355,113 @@ __device__ void EpDispatchBody(const EpDispatchArgs &a)
         }
     }
     __syncthreads();
-    for (int i = tid; i < nRoutes; i += blockDim.x) {
-        const int e = sm.routeExpert[i];
-        int r = 0;
-        if (e >= 0) {
-            for (int j = 0; j < i; ++j) r += (sm.routeExpert[j] == e) ? 1 : 0;
-            atomicAdd(&sm.hist[e], 1);
+    // Rank of each route among the block's routes to the same column, in (token, k) order: one warp walks the
+    // routes 32 at a time; lanes with the same column find one another with a match and the last of them
+    // moves the column's running count on.
+    if (warp == 0) {
+        for (int base = 0; base < nRoutes; base += 32) {
+            const int i = base + lane;
+            const int e = i < nRoutes ? sm.routeExpert[i] : -1;
+            const uint32_t same = __match_any_sync(0xffffffffu, e);
+            int r = 0;
+            if (e >= 0) r = sm.hist[e] + __popc(same & ((1u << lane) - 1u));
+            __syncwarp();
+            if (e >= 0 && (same & ~((2u << lane) - 1u)) == 0) sm.hist[e] += __popc(same);
+            __syncwarp();
+            if (i < nRoutes) sm.routeRank[i] = r;
         }
-        sm.routeRank[i] = r;
     }
     __syncthreads();
-    for (int e = tid; e < C; e += blockDim.x) blockCounts[static_cast<int64_t>(blockIdx.x) * C + e] = sm.hist[e];
+    for (int e = tid; e < C; e += blockDim.x) {
+        const int hcount = sm.hist[e];
+        blockCounts[static_cast<int64_t>(blockIdx.x) * C + e] = hcount;
+        if (hcount != 0) atomicAdd(&totals[e], static_cast<uint32_t>(hcount));
+    }
+    __syncthreads();
+    if (tid == 0) {
+        __threadfence();
+        st_release_gpu_u32(&histReady[blockIdx.x], epoch);
+        sIsLast = atom_add_acq_rel_gpu_u32(doneBlocks, 1u) == static_cast<uint32_t>(G) - 1u ? 1 : 0;
+    }
+    __syncthreads();
     PerfStageEnd(perf, TILEXR_PERF_CHUNK_TOTAL);
-    PerfStageBegin(perf, TILEXR_PERF_CHUNK_BARRIER);
-    ok = GridBarrier(w, 0) && ok;
-    PerfStageEnd(perf, TILEXR_PERF_CHUNK_BARRIER);
     PerfStageBegin(perf, TILEXR_PERF_POST_SYNC);
 
     // ---- 2. publish this rank's counts, learn everybody's ----------------------------------------------
-    if (ok && blockIdx.x == 0) {
-        SumBlockCounts(blockCounts, C, G, sm.total, tid, blockDim.x);
-        for (int e = tid; e < C; e += blockDim.x) {
-            const int c = sm.total[e];
+    // The block that finishes counting last has the rank's totals in front of it and sends them to every
+    // peer as self-validating 16-byte units (three counts and the epoch): no fence, no flag, one NVLink
+    // crossing.  Nobody waits at a barrier: a block only needs the histograms of the blocks before it.
+    if (ok && sIsLast != 0) {
+        for (int u = tid; u < units; u += blockDim.x) {
+            uint32_t v[3];
+#pragma unroll
+            for (int q = 0; q < 3; ++q) {
+                const int idx = u * 3 + q;
+                v[q] = idx < C ? __ldcg(&totals[idx]) : (idx == C ? static_cast<uint32_t>(G) : 0u);
+            }
             for (int i = 0; i < R; ++i) {
                 const int peer = (rank + i) % R;
-                reinterpret_cast<int32_t *>(DataHalf(comm, peer, epoch) + a.win.countOff)[static_cast<int64_t>(rank) * C + e] = c;
+                Ll16SendUnit(LlHalf(comm, peer, epoch) + (static_cast<uint64_t>(rank) * units + u) * LL16_UNIT_BYTES, v[0], v[1], v[2], epoch);
             }
         }
-        if (tid < R) {
-            reinterpret_cast<int32_t *>(DataHalf(comm, tid, epoch) + a.win.countOff)[static_cast<int64_t>(R) * C + rank] = G;
-        }
-        __syncthreads();
-        if (tid < R) {
-            SetFlag(FlagSlot(comm, tid, TILEXR_FLAG_OP_BASE + static_cast<int64_t>(rank) * TILEXR_FLAGS_PER_PAIR + EP_COUNT_FLAG_SLOT),
-                    epoch, 1);
-        }
     }
-    SumBlockCounts(blockCounts, C, ok ? static_cast<int>(blockIdx.x) : 0, sm.blockBase, tid, blockDim.x);
+    PerfStageBegin(perf, TILEXR_PERF_CHUNK_BARRIER);
     {
         bool got = true;
-        if (ok && tid < R) {
-            const int64_t slot = TILEXR_FLAG_OP_BASE + static_cast<int64_t>(tid) * TILEXR_FLAGS_PER_PAIR + EP_COUNT_FLAG_SLOT;
-            got = WaitFlagGE(w, FlagSlot(comm, rank, slot), 1, tid, slot);
+        for (int b = tid; ok && got && b < static_cast<int>(blockIdx.x); b += blockDim.x) {
+            uint32_t polls = 0;
+            while (ld_acquire_gpu_u32(&histReady[b]) != epoch) {
+                if ((++polls & 63u) == 0) {
+                    const uint64_t t = now_ns();
+                    if (w.deadline == 0) {
+                        w.deadline = t + w.args->waitTimeoutNs;
+                    } else if (t > w.deadline || AbortRaised(w)) {
+                        RaiseFailure(w, TILEXR_DEV_GRID_BARRIER_TIMEOUT, rank, b, epoch, histReady[b]);
+                        got = false;
+                        break;
+                    }
+                }
+                spin_pause();
+            }
+        }
+        ok = BlockBroadcastOk(got) && ok;
+    }
+    PerfStageEnd(perf, TILEXR_PERF_CHUNK_BARRIER);
+    SumBlockCounts(blockCounts, C, ok ? static_cast<int>(blockIdx.x) : 0, sm.blockBase, tid, blockDim.x);
+    for (int e = tid; e < C; e += blockDim.x) {
+        sm.total[e] = 0;
+        sm.hist[e] = 0;       // from here on: routes of lower ranks to column e
+    }
+    __syncthreads();
+    {
+        bool got = true;
+        for (int u = tid; ok && got && u < R * units; u += blockDim.x) {
+            const int s = u / units;
+            const int j = u - s * units;
+            Vec16 v;
+            got = Ll16WaitUnit(w, llMine + static_cast<uint64_t>(u) * LL16_UNIT_BYTES, s, u, &v);
+            if (!got) break;
+            const uint32_t vals[3] = {v.x, v.y, v.z};
+#pragma unroll
+            for (int q = 0; q < 3; ++q) {
+                const int idx = j * 3 + q;
+                if (idx < C) {
+                    if (vals[q] != 0) {
+                        atomicAdd(&sm.total[idx], static_cast<int32_t>(vals[q]));
+                        if (s < rank) atomicAdd(&sm.hist[idx], static_cast<int32_t>(vals[q]));
+                    }
+                } else if (idx == C) {
+                    srcBlocks[s] = static_cast<int32_t>(vals[q]);
+                }
+            }
         }
         ok = BlockBroadcastOk(got) && ok;
     }
     if (ok) {
         for (int e = tid; e < C; e += blockDim.x) {
-            int c = 0;
-            for (int s = 0; s < R; ++s) c += countMatrix[static_cast<int64_t>(s) * C + e];
-            sm.total[e] = c;
-        }
-        __syncthreads();
-        for (int e = tid; e < C; e += blockDim.x) {
             const int first = EpRankFirstCol(a.topo, EpColRank(a.topo, e));
-            int row = 0;
+            int row = sm.hist[e];
             for (int p = first; p < e; ++p) row += sm.total[p];
-            for (int s = 0; s < rank; ++s) row += countMatrix[static_cast<int64_t>(s) * C + e];
             sm.dstRow[e] = row;
         }
         // Every rank sees the same counts, so every rank reaches the same verdict on overflow.
@@ -660,7 +721,7 @@ __device__ void EpDispatchBody(const EpDispatchArgs &a)
         if (ok) {
             for (int s = 0; s < R && got; ++s) {
                 const int64_t base = TILEXR_FLAG_OP_BASE + static_cast<int64_t>(s) * TILEXR_FLAGS_PER_PAIR;
-                const int blocksOfS = min(countMatrix[static_cast<int64_t>(R) * C + s], static_cast<int>(EP_COUNT_FLAG_SLOT));
+                const int blocksOfS = min(srcBlocks[s], static_cast<int>(EP_COUNT_FLAG_SLOT));
                 for (int b = tid; b < blocksOfS && got; b += blockDim.x) {
                     got = WaitFlagGE(w, FlagSlot(comm, rank, base + b), 1, s, base + b);
                 }
@@ -728,18 +789,48 @@ __device__ void EpDispatchBody(const EpDispatchArgs &a)
             for (int u = warp; u < heads; u += EP_WARPS) {
                 const int64_t r = base + sHead[u];
                 const uint8_t *src = a.zeroCopy ? a.expandXOut + r * a.win.rowBytes : winPayload + r * a.win.rowBytes;
+                // lane j keeps follower j of the chain; the head row is then read once and stored to all of them
+                int64_t myFollower = -1;
+                int followers = 0;
                 uint32_t next = reinterpret_cast<const uint2 *>(winExt + r * 8)->x & EP_LINK_NEXT_MASK;
                 for (int hop = 0; next != 0 && hop < KR; ++hop) {
                     const int64_t f = static_cast<int64_t>(next) - 1;
                     if (f >= static_cast<int64_t>(a.maxRecvRows)) break;
-                    CopyLanes(a.expandXOut + f * a.win.rowBytes, src, a.win.rowBytes, lane, 32);
+                    if (lane == followers) myFollower = f;
+                    ++followers;
+                    next = reinterpret_cast<const uint2 *>(winExt + f * 8)->x & EP_LINK_NEXT_MASK;
+                }
+                const int rowVecs16 = static_cast<int>(a.win.rowBytes / 16);
+                for (int v0 = 0; v0 < rowVecs16; v0 += 128) {
+                    Vec16 q[4];
+#pragma unroll
+                    for (int k4 = 0; k4 < 4; ++k4) {
+                        const int v = v0 + k4 * 32 + lane;
+                        if (v < rowVecs16) q[k4] = ld_vec16_stream(src + static_cast<int64_t>(v) * 16);
+                    }
+                    for (int j = 0; j < followers; ++j) {
+                        uint8_t *dst = a.expandXOut + __shfl_sync(0xffffffffu, myFollower, j) * a.win.rowBytes;
+#pragma unroll
+                        for (int k4 = 0; k4 < 4; ++k4) {
+                            const int v = v0 + k4 * 32 + lane;
+                            if (v < rowVecs16) st_vec16(dst + static_cast<int64_t>(v) * 16, q[k4]);
+                        }
+                    }
+                }
+                // a row whose length is not a multiple of 16 bytes keeps its tail
+                for (uint32_t bidx = static_cast<uint32_t>(rowVecs16) * 16 + lane; bidx < a.win.rowBytes; bidx += 32) {
+                    for (int j = 0; j < followers; ++j) {
+                        (a.expandXOut + __shfl_sync(0xffffffffu, myFollower, j) * a.win.rowBytes)[bidx] = src[bidx];
+                    }
+                }
+                for (int j = 0; j < followers; ++j) {
+                    const int64_t f = __shfl_sync(0xffffffffu, myFollower, j);
                     if (quantOut && scalarScale) {
                         if (lane == 0) a.dynamicScalesOut[f] = *reinterpret_cast<const float *>(winScales + r * a.win.scaleRowBytes);
                     } else if (quantOut) {
                         CopyLanes(reinterpret_cast<uint8_t *>(a.dynamicScalesOut) + f * a.win.scaleRowBytes,
                                   winScales + r * a.win.scaleRowBytes, a.win.scaleRowBytes, lane, 32);
                     }
-                    next = reinterpret_cast<const uint2 *>(winExt + f * 8)->x & EP_LINK_NEXT_MASK;
                 }
             }
             __syncthreads();
@@ -748,7 +839,12 @@ __device__ void EpDispatchBody(const EpDispatchArgs &a)
             // cumulative counts in (local expert, source) order: an inclusive scan of E_local * R numbers
             const int n = localCols * R;
             __syncthreads();
-            for (int i = tid; i < n; i += blockDim.x) sm.hist[i] = countMatrix[static_cast<int64_t>(i % R) * C + firstLocal + i / R];
+            for (int i = tid; i < n; i += blockDim.x) {
+                // count of source i % R for local column i / R, out of that source's units (all seen to be complete above)
+                const int idx = firstLocal + i / R;
+                sm.hist[i] = static_cast<int32_t>(reinterpret_cast<const uint32_t *>(
+                    llMine + (static_cast<uint64_t>(i % R) * units + idx / 3) * LL16_UNIT_BYTES)[idx % 3]);
+            }
             __syncthreads();
             if (warp == 0) {
                 int carry = 0;
@@ -776,7 +872,7 @@ __device__ void EpDispatchBody(const EpDispatchArgs &a)
     }
     PerfStageEnd(perf, TILEXR_PERF_PEER_IPC_TO_OUTPUT);
     PerfStageEnd(perf, TILEXR_PERF_KERNEL_TOTAL);
-    KernelEpilogue(w, ok);
+    KernelEpilogue(w, ok, EP_SCRATCH_TOTALS_WORD + (C + 1) / 2);
 }
 
 // ---- combine -----------------------------------------------------------------------------------------------
@@ -799,6 +895,73 @@ __device__ __forceinline__ uint32_t TakeItem(uint32_t *cursor, int lane)
     uint32_t it = 0;
     if (lane == 0) it = atomicAdd(cursor, 1u);
     return __shfl_sync(0xffffffffu, it, 0);
+}
+
+// Sends column part `part` of row `r` to slot `slot` of rank `src` and raises the part's flag there.  A head row
+// of a group is replaced by the gate-weighted fp32 sum of the group's rows (one rounding).  Called by a whole warp.
+__device__ __forceinline__ void CombineSendPart(const EpCombineArgs &a, CommArgs *comm, uint32_t epoch, int64_t r, int64_t rows,
+                                                int src, int64_t slot, uint32_t link, uint32_t weightBits, uint32_t part, int lane)
+{
+    const bool bf16 = a.isBf16 != 0;
+    const int KR = a.topK + a.topo.sharedExperts;
+    const int rowVecs = a.rowBytes / 16;
+    const int vBegin = static_cast<int>(part) * static_cast<int>(a.partVecs);
+    const int vEnd = min(rowVecs, vBegin + static_cast<int>(a.partVecs));
+    uint8_t *dst = DataHalf(comm, src, epoch) + slot * a.rowBytes;
+    if ((link & EP_LINK_NEXT_MASK) == 0) {
+        CopyLanes(dst + static_cast<int64_t>(vBegin) * 16, a.expertOut + r * a.rowBytes + static_cast<int64_t>(vBegin) * 16,
+                  static_cast<uint64_t>(vEnd - vBegin) * 16, lane, 32);
+    } else {
+        // The rows of this token on this rank, in k order, times their gate weights: lane i keeps member i of
+        // the chain, then every 16-byte column is summed in fp32 and rounded once.
+        int64_t memberRow = -1;
+        float memberW = 0.f;
+        int members = 0;
+        int64_t cur = r;
+        uint2 e2 = make_uint2(link, weightBits);
+        while (members < KR) {
+            if (lane == members) {
+                memberRow = cur;
+                memberW = __uint_as_float(e2.y);
+            }
+            ++members;
+            const uint32_t next = e2.x & EP_LINK_NEXT_MASK;
+            if (next == 0 || static_cast<int64_t>(next) - 1 >= rows) break;
+            cur = static_cast<int64_t>(next) - 1;
+            e2 = *reinterpret_cast<const uint2 *>(a.assistExt + cur * 2);
+        }
+        for (int v0 = vBegin; v0 < vEnd; v0 += 32) {
+            const int v = v0 + lane;
+            float acc[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+            // the columns of four members are fetched together, then added in k order
+            for (int i0 = 0; i0 < members; i0 += 4) {
+                Vec16 q[4];
+                float mw[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int64_t mr = __shfl_sync(0xffffffffu, memberRow, (i0 + i) & 31);
+                    mw[i] = __shfl_sync(0xffffffffu, memberW, (i0 + i) & 31);
+                    q[i] = Vec16{0u, 0u, 0u, 0u};
+                    if (i0 + i < members && v < vEnd) q[i] = ld_vec16_stream(a.expertOut + mr * a.rowBytes + v * 16);
+                }
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    if (i0 + i < members) {
+                        float f[8];
+                        Unpack8(q[i], bf16, f);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) acc[j] = fmaf(mw[i], f[j], acc[j]);
+                    }
+                }
+            }
+            if (v < vEnd) st_vec16(dst + v * 16, Pack8(acc, bf16));
+        }
+    }
+    // every lane's stores of this part are ordered before the flag by the warp barrier and the release
+    __syncwarp();
+    if (lane == 0) SetFlag(FlagSlot(comm, src, TILEXR_FLAG_SLOT_BASE + slot * a.parts + part), epoch, 1);
 }
 
 __device__ void EpCombineBody(const EpCombineArgs &a)
@@ -824,99 +987,107 @@ __device__ void EpCombineBody(const EpCombineArgs &a)
         // Rows of this rank's own tokens stay where they are when the reducer knows their row (direct), and the
         // followers of a group are summed into their head's row.
         const bool direct = a.routeRows != nullptr && a.expertIds != nullptr;
-        const bool sender = blockIdx.x + a.reducerBlocks < gridDim.x;
-        if (sender) {
+        const bool sender = a.noSend == 0 && blockIdx.x + a.reducerBlocks < gridDim.x;
+        // What a lane learns about row r: does it travel, where to, which bucket of the source's tokens.
+        auto classify = [&](int64_t r, int &src, int64_t &slot, uint2 &ext, uint32_t &bucket) -> bool {
+            const Vec16 tuple = ld_vec16(a.assist + r * 4);
+            src = static_cast<int>(tuple.x);
+            slot = static_cast<int64_t>(tuple.y) * KR + tuple.z;
+            bucket = min(tuple.y / a.bucketTokens, a.buckets - 1u);
+            bool send = src >= 0 && src < comm->rankSize && tuple.y < static_cast<uint32_t>(a.bs) && tuple.z < static_cast<uint32_t>(KR);
+            if (direct && src == rank) send = false;
+            if (send && a.dedup != 0) {
+                ext = *reinterpret_cast<const uint2 *>(a.assistExt + r * 2);
+                if ((ext.x & EP_LINK_FOLLOWER) != 0) send = false;
+            }
+            return send;
+        };
+        const uint32_t senders = gridDim.x - a.reducerBlocks;
+        const bool sorted = a.buckets > 1 && rows <= static_cast<int64_t>(a.listCap);
+        if (sender && sorted) {
             PerfStageBegin(perf, TILEXR_PERF_LOCAL_INPUT_TO_IPC);
+            // Rows in a (local expert, source) segment are in token order, so consecutive rows share a bucket:
+            // the rows that travel are first sorted by bucket into lists (positions by atomics, order within a
+            // bucket does not matter), then one cursor walks the lists bucket after bucket, a row part per item.
+            uint32_t *bucketCount = cursors + 2 * EP_SCRATCH_BUCKET_WORD;
+            int32_t *lists = reinterpret_cast<int32_t *>(DataHalf(comm, rank, epoch) + a.listOff);
+            const int64_t gw = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+            const int64_t nw = static_cast<int64_t>(senders) * (blockDim.x >> 5);
+            for (int64_t base = gw * 32; base < rows; base += nw * 32) {
+                const int64_t r = base + lane;
+                int src = -1;
+                int64_t slot = 0;
+                uint2 ext = make_uint2(0u, 0u);
+                uint32_t bucket = 0;
+                const bool send = r < rows && classify(r, src, slot, ext, bucket);
+                uint32_t left = __ballot_sync(0xffffffffu, send);
+                while (left != 0) {
+                    const uint32_t bb = __shfl_sync(0xffffffffu, bucket, __ffs(left) - 1);
+                    const uint32_t m = __ballot_sync(0xffffffffu, send && bucket == bb);
+                    uint32_t pos = 0;
+                    if (lane == 0) pos = atomicAdd(&bucketCount[bb], static_cast<uint32_t>(__popc(m)));
+                    pos = __shfl_sync(0xffffffffu, pos, 0);
+                    if (send && bucket == bb) lists[static_cast<uint64_t>(bb) * a.listCap + pos + __popc(m & ((1u << lane) - 1u))] = static_cast<int32_t>(r);
+                    left &= ~m;
+                }
+            }
+            __syncthreads();
+            {
+                bool got = true;
+                if (threadIdx.x == 0) {
+                    __threadfence();
+                    got = GridBarrierThread0(w, 1, senders);
+                }
+                ok = BlockBroadcastOk(got);
+            }
+            if (ok) {
+                uint32_t incl = lane < static_cast<int>(a.buckets) ? __ldcg(&bucketCount[lane]) : 0u;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const uint32_t u = __shfl_up_sync(0xffffffffu, incl, o);
+                    if (lane >= o) incl += u;
+                }
+                const uint32_t nItems = __shfl_sync(0xffffffffu, incl, 31) * P;
+                for (;;) {
+                    const uint32_t it = TakeItem(&cursors[0], lane);
+                    if (it >= nItems) break;
+                    const uint32_t i = it / P;
+                    const uint32_t part = it - i * P;
+                    const int b = __popc(__ballot_sync(0xffffffffu, lane < static_cast<int>(a.buckets) && incl <= i));
+                    const uint32_t before = b > 0 ? __shfl_sync(0xffffffffu, incl, b - 1) : 0u;
+                    const int64_t r = __ldcg(&lists[static_cast<uint64_t>(b) * a.listCap + (i - before)]);
+                    const Vec16 tuple = ld_vec16(a.assist + r * 4);
+                    uint2 ext = make_uint2(0u, 0u);
+                    if (a.dedup != 0) ext = *reinterpret_cast<const uint2 *>(a.assistExt + r * 2);
+                    CombineSendPart(a, comm, epoch, r, rows, static_cast<int>(tuple.x), static_cast<int64_t>(tuple.y) * KR + tuple.z, ext.x,
+                                    ext.y, part, lane);
+                }
+            }
+            PerfStageEnd(perf, TILEXR_PERF_LOCAL_INPUT_TO_IPC);
+        } else if (sender) {
+            PerfStageBegin(perf, TILEXR_PERF_LOCAL_INPUT_TO_IPC);
+            // Unsorted: items are (chunk of rows, column part) in row order.
             const uint32_t c = a.chunkRows;
             const uint32_t nChunks = static_cast<uint32_t>((rows + c - 1) / c);
-            const uint32_t perBucket = nChunks * P;
-            const uint32_t nItems = perBucket * a.buckets;
+            const uint32_t nItems = nChunks * P;
             for (;;) {
                 const uint32_t it = TakeItem(&cursors[0], lane);
                 if (it >= nItems) break;
-                const uint32_t bucket = it / perBucket;
-                const uint32_t inBucket = it - bucket * perBucket;
-                const uint32_t chunk = inBucket / P;
-                const uint32_t part = inBucket - chunk * P;
+                const uint32_t chunk = it / P;
+                const uint32_t part = it - chunk * P;
                 const int64_t r = static_cast<int64_t>(chunk) * c + lane;
                 int src = -1;
                 int64_t slot = 0;
                 uint2 ext = make_uint2(0u, 0u);
-                bool send = false;
-                if (lane < static_cast<int>(c) && r < rows) {
-                    const Vec16 tuple = ld_vec16(a.assist + r * 4);
-                    src = static_cast<int>(tuple.x);
-                    slot = static_cast<int64_t>(tuple.y) * KR + tuple.z;
-                    send = src >= 0 && src < comm->rankSize && tuple.y < static_cast<uint32_t>(a.bs) && tuple.z < static_cast<uint32_t>(KR);
-                    if (direct && src == rank) send = false;
-                    if (send && min(tuple.y / a.bucketTokens, a.buckets - 1u) != bucket) send = false;
-                    if (send && a.dedup != 0) {
-                        ext = *reinterpret_cast<const uint2 *>(a.assistExt + r * 2);
-                        if ((ext.x & EP_LINK_FOLLOWER) != 0) send = false;
-                    }
-                }
+                uint32_t bucket = 0;
+                const bool send = lane < static_cast<int>(c) && r < rows && classify(r, src, slot, ext, bucket);
                 uint32_t m = __ballot_sync(0xffffffffu, send);
-                const int vBegin = static_cast<int>(part) * partVecs;
-                const int vEnd = min(rowVecs, vBegin + partVecs);
                 while (m != 0) {
                     const int j = __ffs(m) - 1;
                     m &= m - 1;
                     const int64_t rj = static_cast<int64_t>(chunk) * c + j;
-                    const int srcJ = __shfl_sync(0xffffffffu, src, j);
-                    const int64_t slotJ = __shfl_sync(0xffffffffu, slot, j);
-                    const uint32_t linkJ = __shfl_sync(0xffffffffu, ext.x, j);
-                    const uint32_t wbitsJ = __shfl_sync(0xffffffffu, ext.y, j);
-                    uint8_t *dst = DataHalf(comm, srcJ, epoch) + slotJ * a.rowBytes;
-                    if ((linkJ & EP_LINK_NEXT_MASK) == 0) {
-                        CopyLanes(dst + static_cast<int64_t>(vBegin) * 16, a.expertOut + rj * a.rowBytes + static_cast<int64_t>(vBegin) * 16,
-                                  static_cast<uint64_t>(vEnd - vBegin) * 16, lane, 32);
-                    } else {
-                        // The rows of this token on this rank, in k order, times their gate weights: lane i keeps
-                        // member i of the chain, then every 16-byte column is summed in fp32 and rounded once.
-                        int64_t memberRow = -1;
-                        float memberW = 0.f;
-                        int members = 0;
-                        int64_t cur = rj;
-                        uint2 e2 = make_uint2(linkJ, wbitsJ);
-                        while (members < KR) {
-                            if (lane == members) {
-                                memberRow = cur;
-                                memberW = __uint_as_float(e2.y);
-                            }
-                            ++members;
-                            const uint32_t next = e2.x & EP_LINK_NEXT_MASK;
-                            if (next == 0 || static_cast<int64_t>(next) - 1 >= rows) break;
-                            cur = static_cast<int64_t>(next) - 1;
-                            e2 = *reinterpret_cast<const uint2 *>(a.assistExt + cur * 2);
-                        }
-                        for (int v0 = vBegin; v0 < vEnd; v0 += 64) {        // two columns per lane: eight loads in flight
-                            const int va = v0 + lane, vb = v0 + 32 + lane;
-                            float accA[8], accB[8];
-#pragma unroll
-                            for (int i = 0; i < 8; ++i) accA[i] = accB[i] = 0.f;
-#pragma unroll 4
-                            for (int i = 0; i < members; ++i) {
-                                const int64_t mr = __shfl_sync(0xffffffffu, memberRow, i);
-                                const float mw = __shfl_sync(0xffffffffu, memberW, i);
-                                const uint8_t *rowPtr = a.expertOut + mr * a.rowBytes;
-                                Vec16 qa = Vec16{0u, 0u, 0u, 0u}, qb = Vec16{0u, 0u, 0u, 0u};
-                                if (va < vEnd) qa = ld_vec16_stream(rowPtr + va * 16);
-                                if (vb < vEnd) qb = ld_vec16_stream(rowPtr + vb * 16);
-                                float f[8];
-                                Unpack8(qa, bf16, f);
-#pragma unroll
-                                for (int q = 0; q < 8; ++q) accA[q] = fmaf(mw, f[q], accA[q]);
-                                Unpack8(qb, bf16, f);
-#pragma unroll
-                                for (int q = 0; q < 8; ++q) accB[q] = fmaf(mw, f[q], accB[q]);
-                            }
-                            if (va < vEnd) st_vec16(dst + va * 16, Pack8(accA, bf16));
-                            if (vb < vEnd) st_vec16(dst + vb * 16, Pack8(accB, bf16));
-                        }
-                    }
-                    // every lane's stores of this part are ordered before the flag by the warp barrier and the release
-                    __syncwarp();
-                    if (lane == 0) SetFlag(FlagSlot(comm, srcJ, TILEXR_FLAG_SLOT_BASE + slotJ * P + part), epoch, 1);
+                    CombineSendPart(a, comm, epoch, rj, rows, __shfl_sync(0xffffffffu, src, j), __shfl_sync(0xffffffffu, slot, j),
+                                    __shfl_sync(0xffffffffu, ext.x, j), __shfl_sync(0xffffffffu, ext.y, j), part, lane);
                 }
             }
             PerfStageEnd(perf, TILEXR_PERF_LOCAL_INPUT_TO_IPC);
@@ -980,43 +1151,48 @@ __device__ void EpCombineBody(const EpCombineArgs &a)
             }
             const uint32_t active = __ballot_sync(0xffffffffu, e >= 0);
             uint8_t *y = a.yOut + t * a.rowBytes;
-            for (int v0 = vBegin; v0 < vEnd; v0 += 32) {  // warp-uniform trip count: the loop body shuffles
-                const int v = v0 + lane;
-                const bool mine = v < vEnd;
-                float acc[8];
+            // RU 16-byte columns per lane and row: a warp reads RU * 512 contiguous bytes of a row in one go (DRAM
+            // pages are used well although up to KR rows are walked together), and accumulates route by route
+            // in k order.
+            constexpr int RU = 2;
+            for (int v0 = vBegin; v0 < vEnd; v0 += 32 * RU) {  // warp-uniform trip count: the loop body shuffles
+                float acc[RU][8];
 #pragma unroll
-                for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-                // the rows of up to eight routes are fetched together, then accumulated in k order
-                for (int k0 = 0; k0 < KR; k0 += 8) {
-                    Vec16 q[8];
+                for (int u = 0; u < RU; ++u) {
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        const int k = k0 + j;
-                        q[j] = Vec16{0u, 0u, 0u, 0u};
-                        if (k < KR && ((active >> k) & 1u)) {
-                            const uint8_t *src = reinterpret_cast<const uint8_t *>(__shfl_sync(0xffffffffu, myRowPtr, k));
-                            if (mine) q[j] = ld_vec16_stream(src + v * 16);
-                        }
+                    for (int j = 0; j < 8; ++j) acc[u][j] = 0.f;
+                }
+                for (int k = 0; k < KR; ++k) {
+                    if (((active >> k) & 1u) == 0) continue;
+                    const uint8_t *src = reinterpret_cast<const uint8_t *>(__shfl_sync(0xffffffffu, myRowPtr, k));
+                    const float wgt = __shfl_sync(0xffffffffu, wk, k);
+                    Vec16 q[RU];
+#pragma unroll
+                    for (int u = 0; u < RU; ++u) {
+                        const int v = v0 + u * 32 + lane;
+                        q[u] = Vec16{0u, 0u, 0u, 0u};
+                        if (v < vEnd) q[u] = ld_vec16_stream(src + v * 16);
                     }
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        const int k = k0 + j;
-                        if (k < KR && ((active >> k) & 1u)) {
-                            const float wgt = __shfl_sync(0xffffffffu, wk, k);
-                            float f[8];
-                            Unpack8(q[j], bf16, f);
+                    for (int u = 0; u < RU; ++u) {
+                        float f[8];
+                        Unpack8(q[u], bf16, f);
 #pragma unroll
-                            for (int i = 0; i < 8; ++i) acc[i] = fmaf(wgt, f[i], acc[i]);
-                        }
+                        for (int i = 0; i < 8; ++i) acc[u][i] = fmaf(wgt, f[i], acc[u][i]);
                     }
                 }
-                if (mine && a.sharedExpertX != nullptr) {
-                    float f[8];
-                    Unpack8(ld_vec16(a.sharedExpertX + t * a.rowBytes + v * 16), bf16, f);
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) acc[j] += f[j];
+                for (int u = 0; u < RU; ++u) {
+                    const int v = v0 + u * 32 + lane;
+                    if (v >= vEnd) continue;
+                    if (a.sharedExpertX != nullptr) {
+                        float f[8];
+                        Unpack8(ld_vec16(a.sharedExpertX + t * a.rowBytes + v * 16), bf16, f);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) acc[u][j] += f[j];
+                    }
+                    st_vec16(y + v * 16, Pack8(acc[u], bf16));
                 }
-                if (mine) st_vec16(y + v * 16, Pack8(acc, bf16));
             }
         }
         ok = w.ok();
@@ -1024,7 +1200,7 @@ __device__ void EpCombineBody(const EpCombineArgs &a)
     }
     ok = BlockBroadcastOk(ok);
     PerfStageEnd(perf, TILEXR_PERF_KERNEL_TOTAL);
-    KernelEpilogue(w, ok, 1);      // both cursors live in scratch word 0
+    KernelEpilogue(w, ok, EP_SCRATCH_TOTALS_WORD);      // the cursors and the bucket counts
 }
 
 TILEXR_DEFINE_KERNEL_OCC(TileXREpDispatchKernel, EpDispatchArgs, EpDispatchBody, EP_BLOCK_THREADS, 2)

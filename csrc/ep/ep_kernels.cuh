@@ -15,7 +15,14 @@ constexpr int EP_MAX_EXPERTS = 1024;
 constexpr int EP_MAX_TOPK = 32;
 constexpr int EP_MAX_ROUTES_PER_BLOCK = 4096;
 constexpr int EP_FP8_MAX_H = 8192;      // register-resident quantised row: 16 x 512 elements
-constexpr uint32_t EP_COUNT_FLAG_SLOT = TILEXR_FLAGS_PER_PAIR - 1;   // "my expert counts are published"
+constexpr uint32_t EP_COUNT_FLAG_SLOT = TILEXR_FLAGS_PER_PAIR - 1;   // blocks of a dispatch stay below this flag slot
+// Operator scratch of the control block (64-bit words from TILEXR_CTRL_SCRATCH_WORD) as the EP kernels use it.
+constexpr int EP_SCRATCH_CURSOR_WORD = 0;     // combine: two 32-bit work cursors
+constexpr int EP_SCRATCH_DONE_WORD = 1;       // dispatch: 32-bit count of blocks that have finished counting
+constexpr int EP_SCRATCH_BUCKET_WORD = 2;     // combine: 32-bit rows per bucket, EP_MAX_BUCKETS of them
+constexpr int EP_MAX_BUCKETS = 8;
+constexpr int EP_SCRATCH_TOTALS_WORD = 8;     // dispatch: 32-bit routes per column of this rank, EP_MAX_EXPERTS at most
+constexpr int EP_SCRATCH_READY_WORD = 640;    // dispatch: per block, epoch of the launch whose histogram it has written
 
 // Where a dispatch puts things inside one data half of the DESTINATION's window.  Identical
 // on every rank; computed by EpDispatchLayout() on the host.
@@ -24,8 +31,6 @@ struct EpDispatchWindow {
     uint64_t scalesOff;       // [maxRecvRows][scaleRowBytes]
     uint64_t assistOff;       // [maxRecvRows][16]
     uint64_t extOff;          // [maxRecvRows] 8 bytes: {link, gate weight} of each row
-    uint64_t countOff;        // [rankSize][numExperts] int32: routes of source s for expert e; then [rankSize] int32:
-                              // blocks of source s that will each raise one "rows sent" flag
     uint64_t blockCountOff;   // [grid][numExperts] int32, local scratch of the sender
     uint64_t totalBytes;
     uint32_t rowBytes;
@@ -127,6 +132,9 @@ struct EpCombineArgs {
     uint32_t buckets;                // ranges of the source token index that the senders walk in order
     uint32_t bucketTokens;           // tokens per bucket
     uint32_t reducerBlocks;          // trailing blocks that only reduce
+    uint32_t noSend;                 // 1: no row leaves this rank, the send items are skipped
+    uint64_t listOff;                // bucket lists of travelling rows inside this rank's data half: [buckets][listCap] int32
+    uint32_t listCap;                // rows a list can hold; with more rows than that the senders walk the rows unsorted
 };
 
 // link word of a row: bit 31 = the row is a follower (its payload is a copy of its group's head row);

@@ -67,6 +67,40 @@ TXR_D void Ll16Send(void *dst, const void *src, uint64_t payloadBytes, uint32_t 
     }
 }
 
+// One unit, stored with a single 16-byte transaction.
+TXR_D void Ll16SendUnit(void *dst, uint32_t a, uint32_t b, uint32_t c, uint32_t epoch)
+{
+    st_vec16_flagged(dst, Vec16{a, b, c, epoch});
+}
+
+// Polls one unit until it carries the waiter's epoch.  Returns false if the budget ran out or another rank
+// raised the abort word; `index` only labels the failure record.
+TXR_D bool Ll16WaitUnit(Waiter &w, const void *unit, int peer, int64_t index, Vec16 *out)
+{
+    Vec16 v = ld_vec16_volatile(unit);
+    uint32_t polls = 0;
+    while (v.w != w.epoch) {
+        if (!w.ok()) return false;
+        if ((++polls & 63u) == 0) {
+            if (AbortRaised(w)) {
+                RaiseFailure(w, TileXR::TILEXR_DEV_ABORTED, peer, index, w.epoch, v.w);
+                return false;
+            }
+            const uint64_t t = now_ns();
+            if (w.deadline == 0) {
+                w.deadline = t + w.args->waitTimeoutNs;
+            } else if (t > w.deadline) {
+                RaiseFailure(w, TileXR::TILEXR_DEV_WAIT_TIMEOUT, peer, index, w.epoch, v.w);
+                return false;
+            }
+        }
+        spin_pause();
+        v = ld_vec16_volatile(unit);
+    }
+    *out = v;
+    return true;
+}
+
 // Polls each unit until it carries `epoch`, then stores its payload words to `dst`.
 // Returns false if the waiter's budget ran out.
 TXR_D bool Ll16Recv(Waiter &w, void *dst, const void *src, uint64_t payloadBytes, int peer, int lane, int lanes)
@@ -76,26 +110,8 @@ TXR_D bool Ll16Recv(Waiter &w, void *dst, const void *src, uint64_t payloadBytes
     const uint64_t words = payloadBytes / 4;
     for (uint64_t u = lane; u < units; u += lanes) {
         const uint8_t *p = reinterpret_cast<const uint8_t *>(src) + u * LL16_UNIT_BYTES;
-        Vec16 v = ld_vec16_volatile(p);
-        uint32_t polls = 0;
-        while (v.w != w.epoch) {
-            if (!w.ok()) return false;
-            if ((++polls & 63u) == 0) {
-                if (AbortRaised(w)) {
-                    RaiseFailure(w, TileXR::TILEXR_DEV_ABORTED, peer, static_cast<int64_t>(u), w.epoch, v.w);
-                    return false;
-                }
-                const uint64_t t = now_ns();
-                if (w.deadline == 0) {
-                    w.deadline = t + w.args->waitTimeoutNs;
-                } else if (t > w.deadline) {
-                    RaiseFailure(w, TileXR::TILEXR_DEV_WAIT_TIMEOUT, peer, static_cast<int64_t>(u), w.epoch, v.w);
-                    return false;
-                }
-            }
-            spin_pause();
-            v = ld_vec16_volatile(p);
-        }
+        Vec16 v;
+        if (!Ll16WaitUnit(w, p, peer, static_cast<int64_t>(u), &v)) return false;
         const uint64_t w0 = u * 3;
         if (w0 < words) d[w0] = v.x;
         if (w0 + 1 < words) d[w0 + 1] = v.y;

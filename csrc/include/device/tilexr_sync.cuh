@@ -36,6 +36,13 @@ TXR_D uint8_t *DataHalf(const CommArgs *args, int owner, uint32_t epoch)
     return args->peerMems[owner] + TILEXR_WIN_DATA_OFFSET + static_cast<uint64_t>(epoch & 1u) * args->dataHalfBytes;
 }
 
+// Half (epoch & 1) of the low-latency plane of `owner`: written only with epoch-tagged 16-byte units
+// (tilexr_data_as_flag.cuh).  The halves alternate like the data halves and fall under the same reuse guard.
+TXR_D uint8_t *LlHalf(const CommArgs *args, int owner, uint32_t epoch)
+{
+    return args->peerMems[owner] + TILEXR_WIN_LL_OFFSET + static_cast<uint64_t>(epoch & 1u) * TILEXR_WIN_LL_HALF_BYTES;
+}
+
 // Per-thread wait state.  `status` stays TILEXR_DEV_OK until the first failure; after that
 // every wait returns false at once so the caller walks to the kernel's end without touching
 // more flags (the reference's failed cores also keep walking its barrier skeleton).

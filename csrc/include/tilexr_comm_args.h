@@ -12,8 +12,10 @@
 //   [0, 1 MiB)            control block: abort word, grid barriers, done-epoch table,
 //                         signal words (the "credit plane"), operator scratch
 //   [1 MiB, 5 MiB)        flag area: 64-bit flags `(epoch << 32) | value`, never reset
-//   [5 MiB, 5 MiB + D)    data half 0   \  launch with epoch m uses half (m & 1); the
-//   [.., 5 MiB + 2D)      data half 1   /  done-epoch table guards reuse at m + 2
+//   [5 MiB, 7 MiB)        low-latency plane: two halves of 16-byte units {12 payload bytes, epoch}; nothing else is
+//                         ever stored there, so a unit that carries the current epoch is this launch's data
+//   [7 MiB, 7 MiB + D)    data half 0   \  launch with epoch m uses half (m & 1); the
+//   [.., 7 MiB + 2D)      data half 1   /  done-epoch table guards reuse at m + 2
 #ifndef TILEXR_COMM_ARGS_H
 #define TILEXR_COMM_ARGS_H
 
@@ -30,7 +32,9 @@
 #define TILEXR_WIN_CTRL_BYTES    (1LL << 20)
 #define TILEXR_WIN_FLAG_OFFSET   (1LL << 20)
 #define TILEXR_WIN_FLAG_BYTES    (4LL << 20)
-#define TILEXR_WIN_DATA_OFFSET   (5LL << 20)
+#define TILEXR_WIN_LL_OFFSET     (5LL << 20)
+#define TILEXR_WIN_LL_HALF_BYTES (1LL << 20)
+#define TILEXR_WIN_DATA_OFFSET   (7LL << 20)
 #define TILEXR_TILE_BYTES        (256LL << 10)   // pipelining granule of the tiled collectives
 
 // Control block, in units of 64-bit words from the window base.

@@ -145,6 +145,27 @@ def ep_dispatch_ref(xs: Sequence[torch.Tensor], ids: Sequence[torch.Tensor], num
     return out
 
 
+def ep_dispatch_assist_ref(ids: Sequence[torch.Tensor], num_experts: int) -> List[torch.Tensor]:
+    """The assist tuples of :func:`ep_dispatch_ref` (no masks, no shared experts) computed with tensor ops, for
+    batches where the loops above take too long: per destination rank, int32 ``[n, 4]`` rows
+    ``(src, token, k, expert)`` sorted by expert, then source, then token, then k."""
+    world = len(ids)
+    per = num_experts // world
+    rows = []
+    for s, idt in enumerate(ids):
+        idt = idt.cpu().long()
+        bs, k = idt.shape
+        t = torch.arange(bs).unsqueeze(1).expand(bs, k)
+        kk = torch.arange(k).unsqueeze(0).expand(bs, k)
+        keep = (idt >= 0) & (idt < num_experts)
+        rows.append(torch.stack([torch.full_like(idt, s)[keep], t[keep], kk[keep], idt[keep]], dim=1))
+    allrows = torch.cat(rows)
+    key = ((allrows[:, 3] * world + allrows[:, 0]) * (allrows[:, 1].max() + 1) + allrows[:, 1]) * (allrows[:, 2].max() + 1) + allrows[:, 2]
+    allrows = allrows[torch.argsort(key, stable=True)]
+    dest = allrows[:, 3] // per
+    return [allrows[dest == d].to(torch.int32) for d in range(world)]
+
+
 def ep_combine_ref(dispatch, expert_outs: Sequence[torch.Tensor], ids: Sequence[torch.Tensor],
                    weights: Sequence[Optional[torch.Tensor]], out_dtype, shared: Optional[Sequence[torch.Tensor]] = None):
     """``expert_outs[d]`` are the processed rows of rank d in dispatch order.  Each token sums its
