@@ -192,3 +192,52 @@ def test_expert_forward_matches_a_per_expert_loop():
         if e > s:
             want = (torch.nn.functional.silu(rows[s:e] @ gate[j].t()) * (rows[s:e] @ up[j].t())) @ down[j]
             assert torch.allclose(out[s:e], want, atol=1e-5)
+
+
+def test_report_statistics_and_rank_aggregation(tmp_path):
+    import math
+
+    from tilexr_b200.tools.moonep import report
+
+    assert report.percentile([1, 2, 3, 4], 0.5) == 2.5
+    assert report.percentile([5.0], 0.99) == 5.0
+    assert math.isnan(report.percentile([], 0.5))
+    s = report.metric_summary([10.0, 0.5, 30.0, 20.0, 1.0])          # 0.5 and 1.0 us did not bracket a kernel
+    assert s["samples"] == 5 and s["invalid"] == 2 and s["p50"] == 20.0 and s["min"] == 10.0 and s["max"] == 30.0
+    assert math.isnan(report.metric_summary([0.2, 0.9])["p50"])
+    agg = report.aggregate_rank_samples([[10, 20, 30], [12, 18, 33], [11, 25, 29, 99]])
+    assert agg["iterations"] == 3 and agg["ranks"] == 3
+    assert agg["cross_rank_max"]["p50"] == 25.0 and agg["cross_rank_max"]["max"] == 33.0     # slowest rank per iteration
+    assert agg["rank_p50"][:2] == [20.0, 18.0]
+    # per-rank files of a multi-node run fold into the same numbers
+    for r, vals in enumerate([[10, 20, 30], [12, 18, 33]]):
+        report.write_jsonl(tmp_path / f"rank{r}.jsonl",
+                           report.rank_sample_rows("c", r, {"dispatch": vals}, {"dispatch": 1e6 * (r + 1)}))
+    rows = report.aggregate_rank_artifacts(tmp_path)
+    assert len(rows) == 1 and rows[0]["stage"] == "dispatch" and rows[0]["cross_rank_max"]["p50"] == 20.0
+    assert rows[0]["bytes_per_rank"] == 2e6 and abs(rows[0]["gbps_at_p50"] - 2e6 / 20.0 / 1e3) < 1e-9
+    md = report.benchmark_markdown([{"case": "c", "stage_us": {"dispatch": 20.0}, "stage_stats": {"dispatch": rows[0]},
+                                     "stage_bytes": {"dispatch": 2e6}, "stage_gbps": {"dispatch": 100.0}}])
+    assert "| c | dispatch | 20.0 |" in md
+    report.write_stage_csv(tmp_path / "s.csv", [{"case": "c", "ranks": 2, "stage_stats": {"dispatch": rows[0]},
+                                                 "stage_bytes": {"dispatch": 2e6}, "stage_gbps": {"dispatch": 100.0}}])
+    assert (tmp_path / "s.csv").read_text().splitlines()[1].startswith("c,2,dispatch,20.0")
+
+
+def test_algorithm_bytes_follow_the_plan():
+    import types
+
+    import torch
+
+    from tilexr_b200.tools.moonep.benchmark import algorithm_bytes
+    from tilexr_b200.tools.moonep.prefetch_weight_benchmark import synthetic_borrow_table
+
+    plan = types.SimpleNamespace(dst=torch.tensor([0, 5, 10 + 3, -(10 + 4) - 1, 2 * 10 + 1, -1 - 7], dtype=torch.int32), NvS=10, R=3,
+                                 remote_stats=torch.tensor([2, 3]))
+    b = algorithm_bytes(plan, rank=0, hidden_row_bytes=100, weight_bytes=4, projection_row_bytes=1000, gradient_row_bytes=2000)
+    assert b["dispatch"] == b["combine"] == 3 * 204            # routes to ranks 1, 1 (duplicate) and 2
+    assert b["prefetch_weight"] == 2000 and b["reduce_grad"] == 6000
+    t = synthetic_borrow_table(4, 2, 3)
+    for r in range(4):
+        assert all(int(e) // 2 != r and 0 <= int(e) < 8 for e in t[r])          # always a remote owner
+    assert (synthetic_borrow_table(1, 2, 2) == -1).all()

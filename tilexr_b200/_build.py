@@ -10,6 +10,10 @@ Two shared objects are produced next to this file:
 
 Objects are cached under ``build/`` keyed by source mtime and flags, so a rebuild after a
 one-file change takes seconds.  ``python -m tilexr_b200._build`` runs it from the shell.
+
+Both shared objects are linked under a temporary name and renamed into place together at the
+end, so that a reader of the tree (a packaging step, another process importing the package)
+never finds a half-written library or a binding that is older than the library beside it.
 """
 from __future__ import annotations
 
@@ -73,6 +77,18 @@ def _newest_header_mtime() -> float:
     return newest
 
 
+def _staged(out: Path) -> Path:
+    """Where a shared object is linked before it is renamed into place."""
+    return out.with_name(out.name + ".staged")
+
+
+def _publish(*outs: Path) -> None:
+    for out in outs:
+        staged = _staged(out)
+        if staged.exists():
+            os.replace(staged, out)
+
+
 def _obj_path(src: Path, flags) -> Path:
     key = hashlib.sha1((str(src) + " ".join(flags)).encode()).hexdigest()[:10]
     return BUILD / "obj" / f"{src.stem}.{key}.o"
@@ -114,16 +130,17 @@ def build_library(verbose: bool = True) -> Path:
     out = PKG / "lib" / "libtilexr.so"
     if out.exists() and all(out.stat().st_mtime >= o.stat().st_mtime for o in objs):
         return out
+    staged = _staged(out)
     cmd = [
-        NVCC, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", str(out), *map(str, objs),
-        "-cudart", "static", "-lpthread", "-lrt", "-ldl",
+        NVCC, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", str(staged), *map(str, objs),
+        "-cudart", "static", "-lpthread", "-lrt", "-ldl", "-Xlinker", "-soname=libtilexr.so",
     ]
     if verbose:
         print("  ld", out.relative_to(ROOT), flush=True)
     proc = subprocess.run(cmd, capture_output=True, text=True)
     if proc.returncode != 0:
         raise RuntimeError(f"link failed: {' '.join(cmd)}\n{proc.stdout}\n{proc.stderr}")
-    return out
+    return staged
 
 
 def build_binding(verbose: bool = True) -> Path:
@@ -135,6 +152,8 @@ def build_binding(verbose: bool = True) -> Path:
     src = CSRC / "torch" / "binding.cpp"
     out = PKG / "_C.so"
     lib = PKG / "lib" / "libtilexr.so"
+    if _staged(lib).exists():
+        lib = _staged(lib)            # link against the library that is about to be published
     header_mtime = _newest_header_mtime()
     if out.exists() and out.stat().st_mtime >= max(src.stat().st_mtime, header_mtime, lib.stat().st_mtime):
         return out
@@ -145,8 +164,8 @@ def build_binding(verbose: bool = True) -> Path:
     cmd = [
         "g++", "-std=c++17", "-O2", "-fPIC", "-shared", "-Wall", "-Wno-unused-parameter",
         f"-D_GLIBCXX_USE_CXX11_ABI={abi}", "-DTORCH_EXTENSION_NAME=_C", "-DTORCH_API_INCLUDE_EXTENSION_H",
-        *inc, str(src), "-o", str(out),
-        f"-L{lib.parent}", "-ltilexr", f"-L{torch_lib}", "-lc10", "-ltorch", "-ltorch_cpu", "-ltorch_python",
+        *inc, str(src), "-o", str(_staged(out)),
+        str(lib), f"-L{torch_lib}", "-lc10", "-ltorch", "-ltorch_cpu", "-ltorch_python",
         "-Wl,-rpath,$ORIGIN/lib", f"-Wl,-rpath,{torch_lib}",
     ]
     if verbose:
@@ -154,7 +173,7 @@ def build_binding(verbose: bool = True) -> Path:
     proc = subprocess.run(cmd, capture_output=True, text=True)
     if proc.returncode != 0:
         raise RuntimeError(f"binding build failed: {' '.join(cmd)}\n{proc.stdout}\n{proc.stderr}")
-    return out
+    return _staged(out)
 
 
 def build_checker_cli(verbose: bool = True) -> Path:
@@ -175,8 +194,10 @@ def build_checker_cli(verbose: bool = True) -> Path:
 
 
 def build_all(verbose: bool = True):
-    lib = build_library(verbose)
-    ext = build_binding(verbose)
+    build_library(verbose)
+    build_binding(verbose)
+    lib, ext = PKG / "lib" / "libtilexr.so", PKG / "_C.so"
+    _publish(lib, ext)
     build_checker_cli(verbose)
     return lib, ext
 

@@ -1,28 +1,75 @@
-"""Full-protocol timing of the MoonEP stages (reference: tools/moonep/benchmark.py,
-prefetch_weight_benchmark.py, reduce_grad_benchmark.py): CUDA events around each stage on the launching
-stream, warm-up first, max over ranks."""
+"""Full-protocol timing of the MoonEP stages (reference: tools/moonep/benchmark.py): CUDA events around each
+stage on the launching stream, warm-up first; every iteration's sample of every rank is kept, a stage's time in
+an iteration is the slowest rank's, and the report gives P50 / P99 of that with the bytes of the reference's own
+formula (tools/moonep/benchmark.py:433-462):
+
+* dispatch, combine: remote routes x (2 x hidden row bytes + route weight bytes);
+* prefetch_weight: remote_stats[0] x (gate + up + down row bytes);
+* reduce_grad: remote_stats[1] x (gate + up + down gradient row bytes).
+"""
 from __future__ import annotations
 
-import statistics
-from typing import Dict
+from typing import Dict, List, Mapping, Optional, Sequence
 
 import torch
 import torch.distributed as dist
 
 from ...integrations.moonep import ProjectionBuffers, TileXRMoonEPBuffer
+from . import report
 from .case_factory import make_inputs
 from .contracts import MoonEPCase
 
 
-def _max_over_ranks(v: float, device) -> float:
+def gather_samples(samples: Mapping[str, Sequence[float]]) -> Dict[str, List[List[float]]]:
+    """{stage: [rank][iteration]} on every rank."""
     if not dist.is_initialized() or dist.get_world_size() == 1:
-        return v
-    t = torch.tensor([v], dtype=torch.float64, device=device)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    return float(t.item())
+        return {s: [list(v)] for s, v in samples.items()}
+    world = dist.get_world_size()
+    everybody: List[Optional[dict]] = [None] * world
+    dist.all_gather_object(everybody, {s: list(v) for s, v in samples.items()})
+    return {s: [everybody[r][s] for r in range(world)] for s in samples}
 
 
-def benchmark_case(comm, case: MoonEPCase, iters: int = 20, warmup: int = 5) -> Dict[str, object]:
+def algorithm_bytes(plan, rank: int, hidden_row_bytes: int, weight_bytes: int, projection_row_bytes: int,
+                    gradient_row_bytes: int) -> Dict[str, int]:
+    """Bytes per stage for one rank from its plan.  A negative destination is a route that sends nothing of its own
+    (-(v) - 1 decodes the raw value: the planner of the second generation marks duplicates that way)."""
+    dst = plan.dst.to(torch.int64).cpu()
+    raw = torch.where(dst < 0, -dst - 1, dst)
+    dest_rank = raw // int(plan.NvS)
+    remote = int(((dest_rank != rank) & (dest_rank >= 0) & (dest_rank < int(plan.R))).sum())
+    stats = plan.remote_stats.cpu().reshape(-1).tolist()
+    route_bytes = remote * (2 * hidden_row_bytes + weight_bytes)
+    return {"dispatch": route_bytes, "combine": route_bytes, "prefetch_weight": int(stats[0]) * projection_row_bytes,
+            "reduce_grad": int(stats[1]) * gradient_row_bytes}
+
+
+def _row_bytes(t: Optional[torch.Tensor]) -> int:
+    return 0 if t is None else t[0].numel() * t.element_size()
+
+
+def summarise(case: MoonEPCase, samples: Mapping[str, Sequence[float]], bytes_by_stage: Mapping[str, float], iters: int,
+              warmup: int, device) -> Dict[str, object]:
+    """Cross-rank statistics of one case; the byte count of a stage is the largest over ranks."""
+    gathered = gather_samples(samples)
+    stats = {s: report.aggregate_rank_samples(v) for s, v in gathered.items()}
+    nbytes = {}
+    for s in samples:
+        b = float(bytes_by_stage.get(s, 0.0))
+        if dist.is_initialized() and dist.get_world_size() > 1:
+            t = torch.tensor([b], dtype=torch.float64, device=device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            b = float(t.item())
+        nbytes[s] = b
+    stage_us = {s: stats[s]["cross_rank_max"]["p50"] for s in samples}
+    return {"case": case.name, "ranks": case.ranks, "stage_us": stage_us, "stage_stats": stats, "stage_bytes": nbytes,
+            "stage_gbps": {s: report.bandwidth_gbps(nbytes[s], stage_us[s]) for s in samples if nbytes[s] > 0},
+            "iters": iters, "warmup": warmup,
+            "shape": {"S": case.tokens, "K": case.top_k, "E": case.experts, "H": case.hidden, "Hf": case.ffn,
+                      "B": case.prefetch_slots, "dtype": case.dtype}}
+
+
+def benchmark_case(comm, case: MoonEPCase, iters: int = 20, warmup: int = 5, sample_dir: str = "") -> Dict[str, object]:
     rank = comm.rank
     buf = TileXRMoonEPBuffer(comm, case.tokens, case.hidden, case.top_k, case.experts, token_padding=case.token_padding,
                              B=case.prefetch_slots, dtype=case.torch_dtype())
@@ -40,6 +87,7 @@ def benchmark_case(comm, case: MoonEPCase, iters: int = 20, warmup: int = 5) -> 
         comm.barrier()
     stages = ["planning", "dispatch", "combine"] + (["prefetch_weight", "reduce_grad"] if proj is not None else [])
     samples = {s: [] for s in stages}
+    plan = None
     for it in range(warmup + iters):
         ev = {s: (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for s in stages}
         ev["planning"][0].record()
@@ -63,10 +111,12 @@ def benchmark_case(comm, case: MoonEPCase, iters: int = 20, warmup: int = 5) -> 
         if it >= warmup:
             for s in stages:
                 samples[s].append(ev[s][0].elapsed_time(ev[s][1]) * 1e3)
-    stage_us = {s: _max_over_ranks(statistics.median(v), dev) for s, v in samples.items()}
     esize = torch.tensor([], dtype=case.torch_dtype()).element_size()
-    moved = case.routes * case.hidden * esize
-    stage_gbps = {"dispatch": moved / stage_us["dispatch"] / 1e3, "combine": moved / stage_us["combine"] / 1e3}
+    proj_row = 0 if proj is None else _row_bytes(proj.gate) + _row_bytes(proj.up) + _row_bytes(proj.down)
+    grad_row = 0 if grads is None else _row_bytes(grads.gate) + _row_bytes(grads.up) + _row_bytes(grads.down)
+    nbytes = algorithm_bytes(plan, rank, case.hidden * esize, 4, proj_row, grad_row)
+    out = summarise(case, samples, nbytes, iters, warmup, dev)
+    if sample_dir:
+        report.write_jsonl(f"{sample_dir}/rank{rank}.jsonl", report.rank_sample_rows(case.name, rank, samples, nbytes))
     buf.close()
-    return {"case": case.name, "ranks": case.ranks, "stage_us": stage_us, "stage_gbps": stage_gbps,
-            "bytes_per_rank": moved, "iters": iters, "warmup": warmup}
+    return out

@@ -4,8 +4,11 @@ Run under torchrun, one process per GPU:
 
     python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 -m tilexr_b200.tools.moonep.launcher \\
         --mode correctness --cases smoke
-    ... --mode benchmark --cases correctness --json out.json
+    ... --mode benchmark --cases perf --json out.json --csv out.csv --samples DIR
+    ... --mode prefetch --cases perf          (PrefetchWeight on its own, synthetic borrow table)
+    ... --mode reduce-grad --cases perf       (ReduceGrad on its own)
     ... --mode replay --capture DIR
+    python -m tilexr_b200.tools.moonep.launcher --mode aggregate --samples DIR   (no GPU: folds rank*.jsonl of several nodes)
 
 Cases whose rank count differs from the world size are skipped.
 """
@@ -22,17 +25,33 @@ import torch.distributed as dist
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--mode", choices=["correctness", "benchmark", "replay"], default="correctness")
+    ap.add_argument("--mode", choices=["correctness", "benchmark", "prefetch", "reduce-grad", "replay", "aggregate"], default="correctness")
     ap.add_argument("--cases", default="smoke", help="name of a case file under cases/ or a path")
     ap.add_argument("--capture", default="", help="replay: directory written by RouteRecorder")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--json", default="")
+    ap.add_argument("--csv", default="", help="benchmark modes: one row per (case, stage) with P50 / P99")
+    ap.add_argument("--samples", default="", help="benchmark: directory for per-rank sample files; aggregate: where to read them")
+    ap.add_argument("--buffer-mb", type=int, default=0, help="communicator window size (default: sized for the largest case)")
     args = ap.parse_args(argv)
+
+    if args.mode == "aggregate":
+        from . import report as _report
+
+        rows = _report.aggregate_rank_artifacts(args.samples)
+        for r in rows:
+            s = r["cross_rank_max"]
+            print(f"{r['case']} {r['stage']}: P50 {s['p50']:.1f} us, P99 {s['p99']:.1f} us, {r['gbps_at_p50']:.1f} GB/s ({s['invalid']} invalid)")
+        if args.json:
+            _report.write_json(args.json, rows)
+        return 0
 
     import tilexr_b200 as txr
     from . import report
     from .benchmark import benchmark_case
+    from .prefetch_weight_benchmark import prefetch_weight_benchmark
+    from .reduce_grad_benchmark import reduce_grad_benchmark
     from .case_factory import load_cases
     from .correctness import CorrectnessRunner
     from .model_replay import replay
@@ -44,11 +63,20 @@ def main(argv=None) -> int:
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
+    buffer_mb = args.buffer_mb
+    if buffer_mb <= 0:
+        # two halves, each holding the K rows per token that a combine receives, of the largest case that will run
+        buffer_mb = 256
+        if args.mode != "replay":
+            for c in load_cases(args.cases):
+                if c.ranks == world:
+                    need = c.nvs * c.hidden * 2 + c.nvs * 4
+                    buffer_mb = max(buffer_mb, int(2 * need / (1 << 20)) + 64)
     if world > 1:
         dist.init_process_group("nccl")
-        comm = txr.init_from_torch_distributed(buffer_mb=256)
+        comm = txr.init_from_torch_distributed(buffer_mb=buffer_mb)
     else:
-        comm = txr.init_process(0, 1, comm_id=f"127.0.0.1:{29700 + os.getpid() % 200}", buffer_mb=256, device=local)
+        comm = txr.init_process(0, 1, comm_id=f"127.0.0.1:{29700 + os.getpid() % 200}", buffer_mb=buffer_mb, device=local)
     results = []
     failed = False
     if args.mode == "replay":
@@ -68,10 +96,19 @@ def main(argv=None) -> int:
             if rank == 0:
                 print(report.correctness_markdown(results))
         else:
+            run = {"benchmark": lambda c: benchmark_case(comm, c, iters=args.iters, warmup=args.warmup, sample_dir=args.samples),
+                   "prefetch": lambda c: prefetch_weight_benchmark(comm, c, iters=args.iters, warmup=args.warmup),
+                   "reduce-grad": lambda c: reduce_grad_benchmark(comm, c, iters=args.iters, warmup=args.warmup)}[args.mode]
             for c in cases:
-                results.append(benchmark_case(comm, c, iters=args.iters, warmup=args.warmup))
+                if args.mode != "benchmark" and c.ffn <= 0:
+                    continue
+                r = run(c)
+                results.append(r)
+                failed |= r.get("verified") is False
             if rank == 0:
                 print(report.benchmark_markdown(results))
+                if args.csv:
+                    report.write_stage_csv(args.csv, results)
     if args.json and rank == 0:
         report.write_json(args.json, results)
     if world > 1:
