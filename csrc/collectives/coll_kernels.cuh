@@ -14,6 +14,7 @@
 
 #include <stdint.h>
 
+#include "tilexr_api.h"
 #include "tilexr_comm_args.h"
 #include "tilexr_launch.h"
 
@@ -67,6 +68,12 @@ const KernelEntry &TwoShotKernelEntry();       // two-shot all-reduce
 const KernelEntry &ProbeKernelEntry();
 
 constexpr unsigned COLL_BLOCK_THREADS = 512;
+
+// The operations that can run through the window's NVLink multicast alias (nvls_kernels.cu).
+enum NvlsCollKind : int32_t { COLL_KIND_ALL_REDUCE = 0, COLL_KIND_REDUCE_SCATTER = 1, COLL_KIND_ALL_GATHER = 2, COLL_KIND_BROADCAST = 3 };
+// TILEXR_SUCCESS: launched.  TILEXR_ERROR_NOT_SUPPORT: not a case for the switch, take the peer-to-peer kernels.
+int NvlsWindowCollective(int kind, const void *in, void *out, int64_t count, TileXRDataType dtype, int reduceOp, int root,
+                         TileXRCommPtr comm, TileXRStream stream);
 
 } // namespace TileXR
 

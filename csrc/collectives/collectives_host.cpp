@@ -330,6 +330,12 @@ int TileXRAllGather(void *sendBuf, void *recvBuf, int64_t sendCount, TileXRDataT
         return TILEXR_ERROR_PARA_CHECK_FAIL;
     }
     if (ctx.rankSize == 1) return Loopback(recvBuf, sendBuf, bytes, stream);
+    // A registered output takes the peers' stores directly; otherwise large shards go through the switch once
+    // instead of R - 1 times.
+    if (TileXRFindRegistration(comm, recvBuf, outBytes, nullptr, nullptr) != TILEXR_SUCCESS) {
+        ret = NvlsWindowCollective(COLL_KIND_ALL_GATHER, sendBuf, recvBuf, sendCount, dataType, 0, 0, comm, stream);
+        if (ret != TILEXR_ERROR_NOT_SUPPORT) return ret;
+    }
     return Run(comm, ctx, COLL_ALL_GATHER, TILEXR_OP_ALL_GATHER, static_cast<const uint8_t *>(sendBuf),
                static_cast<uint8_t *>(recvBuf), bytes, bytes, outBytes, dataType, 0, 0, stream);
 }
@@ -394,6 +400,9 @@ int TileXRAllReduce(void *sendBuf, void *recvBuf, int64_t count, TileXRDataType 
     uint64_t bytes = 0;
     if (MulOverflows(static_cast<uint64_t>(count), TileXRDataTypeSize(dataType), &bytes)) return TILEXR_ERROR_PARA_CHECK_FAIL;
     if (ctx.rankSize == 1) return Loopback(recvBuf, sendBuf, bytes, stream);
+    // the switch reduces each element once, at its owner, and all ranks receive the owner's bits
+    ret = NvlsWindowCollective(COLL_KIND_ALL_REDUCE, sendBuf, recvBuf, count, dataType, op, 0, comm, stream);
+    if (ret != TILEXR_ERROR_NOT_SUPPORT) return ret;
     const int kind = bytes <= OneShotMaxBytes() ? COLL_ALL_REDUCE_ONE_SHOT : COLL_ALL_REDUCE_TWO_SHOT;
     return Run(comm, ctx, kind, TILEXR_OP_ALL_REDUCE, static_cast<const uint8_t *>(sendBuf), static_cast<uint8_t *>(recvBuf),
                bytes, bytes, bytes, dataType, op, 0, stream);
@@ -410,6 +419,8 @@ int TileXRReduceScatter(void *sendBuf, void *recvBuf, int64_t recvCount, TileXRD
     uint64_t bytes = 0;
     if (MulOverflows(static_cast<uint64_t>(recvCount), TileXRDataTypeSize(dataType), &bytes)) return TILEXR_ERROR_PARA_CHECK_FAIL;
     if (ctx.rankSize == 1) return Loopback(recvBuf, sendBuf, bytes, stream);
+    ret = NvlsWindowCollective(COLL_KIND_REDUCE_SCATTER, sendBuf, recvBuf, recvCount, dataType, op, 0, comm, stream);
+    if (ret != TILEXR_ERROR_NOT_SUPPORT) return ret;
     return Run(comm, ctx, COLL_REDUCE_SCATTER, TILEXR_OP_REDUCE_SCATTER, static_cast<const uint8_t *>(sendBuf),
                static_cast<uint8_t *>(recvBuf), bytes, bytes, bytes, dataType, op, 0, stream);
 }
@@ -428,6 +439,9 @@ int TileXRBroadcast(void *buf, int64_t count, TileXRDataType dataType, int root,
     uint64_t bytes = 0;
     if (MulOverflows(static_cast<uint64_t>(count), TileXRDataTypeSize(dataType), &bytes)) return TILEXR_ERROR_PARA_CHECK_FAIL;
     if (ctx.rankSize == 1) return TILEXR_SUCCESS;
+    // one multicast store stream of the root reaches every rank
+    ret = NvlsWindowCollective(COLL_KIND_BROADCAST, buf, buf, count, dataType, 0, root, comm, stream);
+    if (ret != TILEXR_ERROR_NOT_SUPPORT) return ret;
     // Large messages on more than two ranks: the root scatters 1/R of the buffer to every rank and an in-place
     // all-gather completes it, so the root sends the buffer about twice instead of R-1 times.
     const uint64_t R = static_cast<uint64_t>(ctx.rankSize);

@@ -28,6 +28,7 @@
 
 #include "device/tilexr_rma.cuh"
 #include "device/tilexr_sync.cuh"
+#include "coll_kernels.cuh"
 #include "tilexr_collectives.h"
 #include "tilexr_launch.h"
 #include "tilexr_log.h"
@@ -282,6 +283,171 @@ __device__ void NvlsNormBody(const NvlsNormArgs &a)
 
 TILEXR_DEFINE_KERNEL(TileXRNvlsNormKernel, NvlsNormArgs, NvlsNormBody, NVLS_THREADS)
 
+// ---- the same operations for ordinary buffers, staged through the window ---------------------------------------------
+// TileXRAllReduce / ReduceScatter / AllGather / Broadcast take any device pointers.  When the communicator's
+// window is bound to a multicast object they run here for large messages: the message is cut into one chunk per
+// block; block c of every rank copies its chunk into the window's data half of this launch, meets block c of the
+// other ranks, works on the chunk through the multicast alias of the window, and copies the result out.  Blocks
+// never wait for other blocks of their own rank, so copy-in, switch traffic and copy-out of different chunks
+// overlap.  The data halves alternate with the launch epoch and the prologue's guard keeps a rank from reusing a
+// half that a peer may still read, so the kernels need no meeting for reuse:
+//
+//   all-reduce, small   copy in, ONE meeting, every rank load-reduces the whole chunk into its output;
+//   all-reduce, large   copy in, meeting, rank r load-reduces part r of the chunk and multicasts the sum into the
+//                       half, meeting, copy out: 2/R of the bytes leave each GPU;
+//   reduce-scatter      copy in (all R slices), meeting, load-reduce the own slice's chunk into the output;
+//   all-gather          multicast the shard's chunk into slot `rank` of the half, meeting, copy all slots out;
+//   broadcast           the root multicasts its chunk, meeting, the others copy out.
+enum NvlsWindowMode : int32_t {
+    NVLS_WIN_ALL_REDUCE_ONE_SHOT = 0,
+    NVLS_WIN_ALL_REDUCE_TWO_SHOT = 1,
+    NVLS_WIN_REDUCE_SCATTER = 2,
+    NVLS_WIN_ALL_GATHER = 3,
+    NVLS_WIN_BROADCAST = 4,
+};
+
+struct NvlsWindowArgs {
+    const uint8_t *in;
+    uint8_t *out;
+    CommArgs *comm;
+    int64_t magic;
+    uint64_t vecs;          // 16-byte vectors per rank's contribution: the message (all-reduce, broadcast), one slice
+                            // (reduce-scatter: of R in the input), one shard (all-gather)
+    int32_t mode;
+    int32_t kind;           // 0 bf16, 1 fp16, 2 fp32 (reductions)
+    int32_t root;
+    int32_t opType;
+};
+
+__device__ __forceinline__ void CopyVecs(uint8_t *dst, const uint8_t *src, uint64_t vecs)
+{
+    uint64_t i = threadIdx.x;
+    for (; i + 3ull * NVLS_THREADS < vecs; i += 4ull * NVLS_THREADS) {
+        const Vec16 a = ld_vec16_stream(src + i * 16);
+        const Vec16 b = ld_vec16_stream(src + (i + NVLS_THREADS) * 16);
+        const Vec16 c = ld_vec16_stream(src + (i + 2ull * NVLS_THREADS) * 16);
+        const Vec16 d = ld_vec16_stream(src + (i + 3ull * NVLS_THREADS) * 16);
+        st_vec16(dst + i * 16, a);
+        st_vec16(dst + (i + NVLS_THREADS) * 16, b);
+        st_vec16(dst + (i + 2ull * NVLS_THREADS) * 16, c);
+        st_vec16(dst + (i + 3ull * NVLS_THREADS) * 16, d);
+    }
+    for (; i < vecs; i += NVLS_THREADS) st_vec16(dst + i * 16, ld_vec16_stream(src + i * 16));
+}
+
+// dst (local memory or null) and mcDst (multicast address or null) receive the in-switch sum of `vecs` vectors at mcSrc.
+__device__ __forceinline__ void ReduceVecs(uint8_t *dst, uint8_t *mcDst, const uint8_t *mcSrc, uint64_t vecs, int kind)
+{
+    for (uint64_t i0 = threadIdx.x; i0 < vecs; i0 += static_cast<uint64_t>(NVLS_THREADS) * NVLS_UNROLL) {
+        Vec16 v[NVLS_UNROLL];
+#pragma unroll
+        for (int q = 0; q < NVLS_UNROLL; ++q) {
+            const uint64_t i = i0 + static_cast<uint64_t>(q) * NVLS_THREADS;
+            if (i < vecs) v[q] = MultimemLdReduce(mcSrc + i * 16, kind);
+        }
+#pragma unroll
+        for (int q = 0; q < NVLS_UNROLL; ++q) {
+            const uint64_t i = i0 + static_cast<uint64_t>(q) * NVLS_THREADS;
+            if (i < vecs) {
+                if (mcDst != nullptr) MultimemSt(mcDst + i * 16, v[q]);
+                if (dst != nullptr) st_vec16(dst + i * 16, v[q]);
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void MulticastVecs(uint8_t *mcDst, const uint8_t *src, uint64_t vecs)
+{
+    for (uint64_t i0 = threadIdx.x; i0 < vecs; i0 += static_cast<uint64_t>(NVLS_THREADS) * NVLS_UNROLL) {
+        Vec16 v[NVLS_UNROLL];
+#pragma unroll
+        for (int q = 0; q < NVLS_UNROLL; ++q) {
+            const uint64_t i = i0 + static_cast<uint64_t>(q) * NVLS_THREADS;
+            if (i < vecs) v[q] = ld_vec16_stream(src + i * 16);
+        }
+#pragma unroll
+        for (int q = 0; q < NVLS_UNROLL; ++q) {
+            const uint64_t i = i0 + static_cast<uint64_t>(q) * NVLS_THREADS;
+            if (i < vecs) MultimemSt(mcDst + i * 16, v[q]);
+        }
+    }
+}
+
+__device__ void NvlsWindowBody(const NvlsWindowArgs &a)
+{
+    Waiter w;
+    bool ok = KernelPrologue(w, a.comm, a.magic, a.opType, static_cast<int64_t>(a.vecs), true);
+    CommArgs *comm = a.comm;
+    const int R = comm->rankSize;
+    const int rank = comm->rank;
+    const uint64_t halfOff = TILEXR_WIN_DATA_OFFSET + static_cast<uint64_t>(w.epoch & 1u) * comm->dataHalfBytes;
+    uint8_t *stage = comm->peerMems[rank] + halfOff;          // this rank's copy
+    uint8_t *mcStage = comm->multicastMem + halfOff;          // all ranks' copies at once
+    NvlsArgs meet;
+    meet.comm = comm;
+    // chunk of this block: vectors [c0, c0 + n) of every rank's contribution
+    const uint64_t per = (a.vecs + gridDim.x - 1) / gridDim.x;
+    const uint64_t c0 = min(a.vecs, per * blockIdx.x);
+    const uint64_t n = min(a.vecs - c0, per);
+    if (ok) {
+        switch (a.mode) {
+            case NVLS_WIN_ALL_REDUCE_ONE_SHOT: {
+                CopyVecs(stage + c0 * 16, a.in + c0 * 16, n);
+                ok = MeetPeers(w, meet, 1);
+                if (ok) ReduceVecs(a.out + c0 * 16, nullptr, mcStage + c0 * 16, n, a.kind);
+                break;
+            }
+            case NVLS_WIN_ALL_REDUCE_TWO_SHOT: {
+                CopyVecs(stage + c0 * 16, a.in + c0 * 16, n);
+                ok = MeetPeers(w, meet, 1);
+                if (ok) {
+                    const uint64_t part = (n + R - 1) / R;
+                    const uint64_t p0 = min(n, part * rank);
+                    const uint64_t pn = min(n - p0, part);
+                    // the rank's own output gets its part straight from the registers
+                    ReduceVecs(a.out + (c0 + p0) * 16, mcStage + (c0 + p0) * 16, mcStage + (c0 + p0) * 16, pn, a.kind);
+                    ok = MeetPeers(w, meet, 2);
+                    if (ok) {
+                        if (p0 > 0) CopyVecs(a.out + c0 * 16, stage + c0 * 16, p0);
+                        if (p0 + pn < n) CopyVecs(a.out + (c0 + p0 + pn) * 16, stage + (c0 + p0 + pn) * 16, n - p0 - pn);
+                    }
+                }
+                break;
+            }
+            case NVLS_WIN_REDUCE_SCATTER: {
+                for (int s = 0; s < R; ++s) CopyVecs(stage + (static_cast<uint64_t>(s) * a.vecs + c0) * 16, a.in + (static_cast<uint64_t>(s) * a.vecs + c0) * 16, n);
+                ok = MeetPeers(w, meet, 1);
+                if (ok) ReduceVecs(a.out + c0 * 16, nullptr, mcStage + (static_cast<uint64_t>(rank) * a.vecs + c0) * 16, n, a.kind);
+                break;
+            }
+            case NVLS_WIN_ALL_GATHER: {
+                MulticastVecs(mcStage + (static_cast<uint64_t>(rank) * a.vecs + c0) * 16, a.in + c0 * 16, n);
+                ok = MeetPeers(w, meet, 1);
+                if (ok) {
+                    for (int s = 0; s < R; ++s) {
+                        const uint64_t off = (static_cast<uint64_t>(s) * a.vecs + c0) * 16;
+                        if (s == rank) {
+                            if (a.out + off != a.in + c0 * 16) CopyVecs(a.out + off, a.in + c0 * 16, n);
+                        } else {
+                            CopyVecs(a.out + off, stage + off, n);
+                        }
+                    }
+                }
+                break;
+            }
+            default: {   // broadcast: in == out == the caller's buffer
+                if (rank == a.root) MulticastVecs(mcStage + c0 * 16, a.in + c0 * 16, n);
+                ok = MeetPeers(w, meet, 1);
+                if (ok && rank != a.root) CopyVecs(a.out + c0 * 16, stage + c0 * 16, n);
+                break;
+            }
+        }
+    }
+    KernelEpilogue(w, ok);
+}
+
+TILEXR_DEFINE_KERNEL(TileXRNvlsWindowKernel, NvlsWindowArgs, NvlsWindowBody, NVLS_THREADS)
+
 long EnvLongNvls(const char *name, long fallback)
 {
     const char *v = std::getenv(name);
@@ -347,6 +513,72 @@ int Launch(int mode, void *mc, const void *in, void *out, uint64_t bytes, TileXR
 }
 
 } // namespace
+
+// Runs `op` of the plain collective API through the window's multicast alias, or says NOT_SUPPORT so that the
+// caller takes the peer-to-peer kernels (no multicast object, message too small or too large for a data half,
+// dtype or reduce op the switch cannot do, misaligned buffers).  `count` as in the API: elements of the whole
+// vector (all-reduce, broadcast), of one output slice (reduce-scatter), of one shard (all-gather).
+int NvlsWindowCollective(int kind, const void *in, void *out, int64_t count, TileXRDataType dtype, int reduceOp, int root,
+                         TileXRCommPtr comm, TileXRStream stream)
+{
+    TileXRCommArgs *hostArgs = nullptr;
+    GM_ADDR devArgs = nullptr;
+    if (comm == nullptr || TileXRGetCommArgsHost(comm, &hostArgs) != TILEXR_SUCCESS || TileXRGetCommArgsDev(comm, &devArgs) != TILEXR_SUCCESS) {
+        return TILEXR_ERROR_NOT_SUPPORT;
+    }
+    if ((hostArgs->extraFlag & TILEXR_FLAG_NVLS) == 0 || hostArgs->multicastMem == nullptr || hostArgs->rankSize < 2) return TILEXR_ERROR_NOT_SUPPORT;
+    if (EnvLongNvls("TILEXR_NVLS_AUTO", 1) == 0) return TILEXR_ERROR_NOT_SUPPORT;
+    const int R = hostArgs->rankSize;
+    const uint64_t bytes = static_cast<uint64_t>(count) * TileXRDataTypeSize(dtype);
+    const bool reduces = kind == COLL_KIND_ALL_REDUCE || kind == COLL_KIND_REDUCE_SCATTER;
+    int ek = 2;
+    if (reduces) {
+        if (reduceOp != TILEXR_REDUCE_SUM) return TILEXR_ERROR_NOT_SUPPORT;
+        if (dtype == TILEXR_DATA_TYPE_BFP16) ek = 0;
+        else if (dtype == TILEXR_DATA_TYPE_FP16) ek = 1;
+        else if (dtype == TILEXR_DATA_TYPE_FP32) ek = 2;
+        else return TILEXR_ERROR_NOT_SUPPORT;
+    }
+    if (bytes == 0 || bytes % 16 != 0 || reinterpret_cast<uintptr_t>(in) % 16 != 0 || reinterpret_cast<uintptr_t>(out) % 16 != 0) return TILEXR_ERROR_NOT_SUPPORT;
+    const uint64_t staged = (kind == COLL_KIND_REDUCE_SCATTER || kind == COLL_KIND_ALL_GATHER) ? bytes * R : bytes;
+    if (staged > hostArgs->dataHalfBytes) return TILEXR_ERROR_NOT_SUPPORT;
+    // Below these sizes the peer-to-peer kernels (one launch, direct pushes) are as fast or faster.
+    const uint64_t floorBytes = static_cast<uint64_t>(EnvLongNvls("TILEXR_NVLS_MIN_BYTES", kind == COLL_KIND_ALL_REDUCE ? (32 << 10) : (1 << 20)));
+    if (staged < floorBytes) return TILEXR_ERROR_NOT_SUPPORT;
+    NvlsWindowArgs a;
+    std::memset(&a, 0, sizeof(a));
+    a.in = static_cast<const uint8_t *>(in);
+    a.out = static_cast<uint8_t *>(out);
+    a.comm = reinterpret_cast<CommArgs *>(devArgs);
+    a.vecs = bytes / 16;
+    a.kind = ek;
+    a.root = root;
+    switch (kind) {
+        case COLL_KIND_ALL_REDUCE:
+            a.mode = bytes <= static_cast<uint64_t>(EnvLongNvls("TILEXR_NVLS_ONE_SHOT_BYTES", 512 << 10)) ? NVLS_WIN_ALL_REDUCE_ONE_SHOT : NVLS_WIN_ALL_REDUCE_TWO_SHOT;
+            a.opType = TILEXR_OP_ALL_REDUCE;
+            break;
+        case COLL_KIND_REDUCE_SCATTER: a.mode = NVLS_WIN_REDUCE_SCATTER; a.opType = TILEXR_OP_REDUCE_SCATTER; break;
+        case COLL_KIND_ALL_GATHER: a.mode = NVLS_WIN_ALL_GATHER; a.opType = TILEXR_OP_ALL_GATHER; break;
+        case COLL_KIND_BROADCAST: a.mode = NVLS_WIN_BROADCAST; a.opType = TILEXR_OP_BROADCAST; break;
+        default: return TILEXR_ERROR_NOT_SUPPORT;
+    }
+    int64_t magic = 0;
+    int ret = TileXRCommNextMagic(comm, &magic);
+    if (ret != TILEXR_SUCCESS) return ret;
+    a.magic = magic;
+    unsigned maxGrid = 0;
+    ret = MaxCooperativeGrid(comm, TileXRNvlsWindowKernelEntry, NVLS_THREADS, 0, 1, &maxGrid);
+    if (ret != TILEXR_SUCCESS) return ret;
+    // one chunk per block: enough blocks to keep the switch busy, few enough that a chunk is worth a meeting
+    const uint64_t perBlockFloor = 64u << 10;
+    long want = static_cast<long>(std::max<uint64_t>(1, std::min<uint64_t>(128, bytes / perBlockFloor)));
+    want = EnvLongNvls("TILEXR_NVLS_BLOCKS", want);
+    const unsigned grid = std::max(1u, std::min<unsigned>(static_cast<unsigned>(std::min<long>(want, TILEXR_FLAGS_PER_PAIR)), maxGrid));
+    LaunchConfig cfg{grid, NVLS_THREADS, 0, true};
+    return LaunchKernel(comm, TileXRNvlsWindowKernelEntry, &a, cfg, stream);
+}
+
 } // namespace TileXR
 
 using namespace TileXR;

@@ -110,12 +110,21 @@ TileXRComm::TileXRComm(int rank, int rankSize, const InitOptions &opt) : rank_(r
     }
     if (EnvLong("TILEXR_ENABLE_SDMA", 1) != 0) knobFlags_ |= TILEXR_FLAG_LOCAL_COPY;
     if (EnvLong("TILEXR_ENABLE_UDMA", 1) != 0 && !opt.memoryOnly) knobFlags_ |= TILEXR_FLAG_RMA;
+    wantVmm_ = EnvLong("TILEXR_ENABLE_VMM", 1) != 0;
+    wantNvls_ = EnvLong("TILEXR_ENABLE_NVLS", 1) != 0;
 }
 
 TileXRComm::~TileXRComm()
 {
+    destroying_ = true;
     const bool gpu = !isHostMemory();
     if (gpu && device_ >= 0) cudaSetDevice(device_);
+    if (gpu && windowVmm_.live && initialized_) {
+        // Memory bound to a multicast object is let go only after every rank has finished its kernels: all
+        // ranks destroy the communicator together, and they meet here once before anybody unbinds anything.
+        cudaDeviceSynchronize();
+        if (exchange_ != nullptr) exchange_->Barrier();
+    }
     for (size_t h = 0; h < regions_.size(); ++h) {
         if (regions_[h].live) Unregister(static_cast<TileXRUDMAMemHandle>(h));
     }
@@ -124,6 +133,10 @@ TileXRComm::~TileXRComm()
         if (devArgs_ != nullptr) cudaFree(devArgs_);
         if (devRegistry_ != nullptr) cudaFree(devRegistry_);
         if (localCopyWorkspace_ != nullptr) cudaFree(localCopyWorkspace_);
+        if (windowVmm_.live) {
+            VmmFree(nullptr, &windowVmm_);          // the ranks have met above
+            window_ = nullptr;
+        }
         if (window_ != nullptr) cudaFree(window_);
         if (copyStream_ != nullptr) cudaStreamDestroy(copyStream_);
         if (copyEventIn_ != nullptr) cudaEventDestroy(copyEventIn_);
@@ -181,6 +194,36 @@ int TileXRComm::AllocateWindow()
     return TILEXR_SUCCESS;
 }
 
+// The window through the virtual-memory API: one collective call allocates, trades POSIX descriptors, maps every
+// peer and, where the node has NVSwitch multicast, binds all copies to one multicast object.  Only processes of
+// one host can pass descriptors; anything else (or a refusal anywhere) returns NOT_SUPPORT on every rank and the
+// caller takes the cudaMalloc + CUDA IPC route.
+int TileXRComm::TryVmmWindow()
+{
+    if (opt_.mode != CommMode::PROCESS || !wantVmm_) return TILEXR_ERROR_NOT_SUPPORT;
+    struct Probe {
+        uint64_t hostHash;
+        uint64_t job;
+    } mine{HashString(SockExchange::ReadBootId()),
+           (static_cast<uint64_t>(getpid()) << 32) ^ static_cast<uint64_t>(time(nullptr)) ^ reinterpret_cast<uintptr_t>(this)};
+    std::vector<Probe> all(rankSize_);
+    int ret = exchange_->AllGather(&mine, all.data(), sizeof(Probe));
+    if (ret != TILEXR_SUCCESS) return ret;
+    for (const Probe &p : all) {
+        if (p.hostHash != mine.hostHash) return TILEXR_ERROR_NOT_SUPPORT;
+    }
+    vmmTag_ = all[0].job ^ (static_cast<uint64_t>(opt_.commDomain) << 48);
+    const size_t dataBytes = static_cast<size_t>(opt_.bufferMB) << 20;
+    windowBytes_ = static_cast<size_t>(TILEXR_WIN_DATA_OFFSET) + dataBytes;
+    ret = VmmAllocate(*exchange_, rank_, rankSize_, device_, windowBytes_, wantNvls_, vmmTag_ + vmmSeq_++, &windowVmm_);
+    if (ret != TILEXR_SUCCESS) return ret;
+    window_ = windowVmm_.local;
+    peerWindows_ = windowVmm_.peers;
+    TXR_CUDA(cudaMemset(window_, 0, static_cast<size_t>(TILEXR_WIN_DATA_OFFSET)));
+    TXR_CUDA(cudaDeviceSynchronize());
+    return exchange_->Barrier();
+}
+
 int TileXRComm::AgreeOnKnobs()
 {
     struct Knobs {
@@ -189,7 +232,10 @@ int TileXRComm::AgreeOnKnobs()
         uint64_t timeoutNs;
         int32_t memoryOnly;
         int32_t domain;
-    } mine{knobFlags_, static_cast<uint32_t>(opt_.bufferMB), waitTimeoutNs_, opt_.memoryOnly ? 1 : 0, opt_.commDomain};
+        int32_t vmm;
+        int32_t nvls;
+    } mine{knobFlags_, static_cast<uint32_t>(opt_.bufferMB), waitTimeoutNs_, opt_.memoryOnly ? 1 : 0, opt_.commDomain,
+           wantVmm_ ? 1 : 0, wantNvls_ ? 1 : 0};
     std::vector<Knobs> all(rankSize_);
     int ret = exchange_->AllGather(&mine, all.data(), sizeof(Knobs));
     if (ret != TILEXR_SUCCESS) return ret;
@@ -306,6 +352,10 @@ void TileXRComm::FillCommArgs()
     }
     a.localCopyWorkspace = localCopyWorkspace_;
     a.registryPtr = devRegistry_;
+    if (windowVmm_.live && windowVmm_.multicast != nullptr) {
+        a.multicastMem = windowVmm_.multicast;
+        a.extraFlag |= TILEXR_FLAG_NVLS;
+    }
 }
 
 int TileXRComm::SyncCommArgs()
@@ -337,9 +387,13 @@ int TileXRComm::Init(std::unique_ptr<Exchange> exchange)
         return TILEXR_SUCCESS;
     }
     TXR_CUDA(cudaGetDevice(&device_));
-    ret = AllocateWindow();
-    if (ret != TILEXR_SUCCESS) return ret;
-    ret = ExchangeWindows();
+    TXR_CUDA(cudaFree(nullptr));             // the device's context exists before any driver call
+    ret = TryVmmWindow();
+    if (ret == TILEXR_ERROR_NOT_SUPPORT) {
+        ret = AllocateWindow();
+        if (ret != TILEXR_SUCCESS) return ret;
+        ret = ExchangeWindows();
+    }
     if (ret != TILEXR_SUCCESS) return ret;
     TXR_CUDA(cudaMalloc(reinterpret_cast<void **>(&devArgs_), sizeof(CommArgs)));
     TXR_CUDA(cudaMemset(devArgs_, 0, sizeof(CommArgs)));
@@ -354,7 +408,9 @@ int TileXRComm::Init(std::unique_ptr<Exchange> exchange)
     if (ret != TILEXR_SUCCESS) return ret;
     initialized_ = true;
     TILEXR_LOG(INFO) << "rank " << rank_ << "/" << rankSize_ << " ready on device " << device_ << ", window "
-                     << (windowBytes_ >> 20) << " MiB";
+                     << (windowBytes_ >> 20) << " MiB, "
+                     << (windowVmm_.live ? (windowVmm_.multicast != nullptr ? "virtual-memory API with NVLink multicast" : "virtual-memory API")
+                                         : "cudaMalloc + CUDA IPC");
     return exchange_->Barrier();
 }
 
@@ -409,6 +465,7 @@ int TileXRComm::UploadRegistry()
         registry_.regions[h].bytes = rec.live ? rec.bytes : 0;
         registry_.regions[h].localBase = rec.live ? rec.localBase : nullptr;
         registry_.regions[h].peerBase = rec.live ? rec.devPeerBase : nullptr;
+        registry_.regions[h].mcBase = (rec.live && rec.vmm.live) ? rec.vmm.multicast : nullptr;
         if (rec.live) count = h + 1;
     }
     registry_.regionCount = count;
@@ -532,6 +589,37 @@ int TileXRComm::Register(uint8_t *ptr, size_t bytes, bool owned, TileXRUDMAMemHa
     return exchange_->Barrier();
 }
 
+int TileXRComm::SymmAllocVmm(size_t bytes, void **localPtr, TileXRUDMAMemHandle *handle)
+{
+    if (!initialized_) return TILEXR_ERROR_NOT_INITIALIZED;
+    if (!windowVmm_.live || (hostArgs_->extraFlag & TILEXR_FLAG_RMA) == 0) return TILEXR_ERROR_NOT_SUPPORT;
+    uint32_t h = 0;
+    while (h < regions_.size() && regions_[h].live) ++h;
+    if (h == regions_.size()) {
+        TILEXR_LOG(ERROR) << "all " << regions_.size() << " registration slots are in use";
+        return TILEXR_ERROR_INTERNAL;
+    }
+    TXR_CUDA(cudaSetDevice(device_));
+    RegionRecord rec;
+    int ret = VmmAllocate(*exchange_, rank_, rankSize_, device_, bytes, wantNvls_, vmmTag_ + vmmSeq_++, &rec.vmm);
+    if (ret != TILEXR_SUCCESS) return ret;
+    rec.live = true;
+    rec.ownedAllocation = true;
+    rec.localBase = rec.vmm.local;
+    rec.bytes = bytes;
+    rec.peerBase = rec.vmm.peers;
+    TXR_CUDA(cudaMemset(rec.localBase, 0, bytes));
+    TXR_CUDA(cudaMalloc(reinterpret_cast<void **>(&rec.devPeerBase), sizeof(uint8_t *) * rankSize_));
+    TXR_CUDA(cudaMemcpy(rec.devPeerBase, rec.peerBase.data(), sizeof(uint8_t *) * rankSize_, cudaMemcpyHostToDevice));
+    TXR_CUDA(cudaDeviceSynchronize());
+    regions_[h] = rec;
+    *handle = h;
+    *localPtr = rec.localBase;
+    ret = UploadRegistry();
+    if (ret != TILEXR_SUCCESS) return ret;
+    return exchange_->Barrier();
+}
+
 int TileXRComm::Unregister(TileXRUDMAMemHandle handle)
 {
     if (handle >= regions_.size() || !regions_[handle].live) return TILEXR_ERROR_NOT_FOUND;
@@ -540,7 +628,12 @@ int TileXRComm::Unregister(TileXRUDMAMemHandle handle)
         cudaSetDevice(device_);
         for (void *p : rec.ipcOpened) cudaIpcCloseMemHandle(p);
         if (rec.devPeerBase != nullptr) cudaFree(rec.devPeerBase);
-        if (rec.ownedAllocation && rec.localBase != nullptr) cudaFree(rec.localBase);
+        if (rec.vmm.live) {
+            // a collective free while the communicator is up (TileXRSymmFree is collective, like the allocation)
+            VmmFree(initialized_ && !destroying_ ? exchange_.get() : nullptr, &rec.vmm);
+        } else if (rec.ownedAllocation && rec.localBase != nullptr) {
+            cudaFree(rec.localBase);
+        }
     }
     rec = RegionRecord();
     if (initialized_) UploadRegistry();

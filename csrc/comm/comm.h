@@ -20,6 +20,7 @@
 
 #include "sock_exchange.h"
 #include "tilexr_api.h"
+#include "vmm.h"
 
 namespace TileXR {
 
@@ -45,6 +46,7 @@ struct RegionRecord {
     std::vector<uint8_t *> peerBase;       // [rankSize], as mapped in this process
     std::vector<void *> ipcOpened;         // bases returned by cudaIpcOpenMemHandle, to close
     uint8_t **devPeerBase = nullptr;       // device copy of peerBase
+    VmmAllocation vmm;                     // TileXRSymmAlloc through the virtual-memory API (live when used)
 };
 
 struct ProfileRecord {
@@ -67,6 +69,12 @@ public:
     int SyncCommArgs();                                 // host copy -> device copy
 
     int Register(uint8_t *ptr, size_t bytes, bool owned, TileXRUDMAMemHandle *handle);
+    // Collective allocation of `bytes` per rank that every rank maps, with a multicast alias where the node
+    // offers one; registered like any region.  TILEXR_ERROR_NOT_SUPPORT when this communicator cannot (the
+    // caller then allocates with cudaMalloc and registers).
+    int SymmAllocVmm(size_t bytes, void **localPtr, TileXRUDMAMemHandle *handle);
+    bool usesVmm() const { return windowVmm_.live; }
+    uint8_t *windowMulticast() const { return windowVmm_.live ? windowVmm_.multicast : nullptr; }
     int Unregister(TileXRUDMAMemHandle handle);
     int FindRegistration(const void *ptr, size_t bytes, TileXRUDMAMemHandle *handle, uint64_t *offset) const;
     int UploadRegistry();
@@ -95,6 +103,7 @@ public:
 
 private:
     int AllocateWindow();
+    int TryVmmWindow();
     int ExchangeWindows();
     int MapHostMemoryWindows();
     void FillCommArgs();
@@ -113,6 +122,12 @@ private:
     std::vector<uint8_t *> peerWindows_;
     std::vector<void *> ipcOpened_;
     std::vector<std::string> shmNames_;
+    VmmAllocation windowVmm_;             // live when the window came from the virtual-memory API
+    uint64_t vmmTag_ = 0;                 // names the descriptor sockets of this communicator's allocations
+    uint32_t vmmSeq_ = 0;
+    bool wantVmm_ = true;
+    bool wantNvls_ = true;
+    bool destroying_ = false;             // regions released by the destructor do not meet the peers one by one
 
     CommArgs *hostArgs_ = nullptr;
     CommArgs *devArgs_ = nullptr;

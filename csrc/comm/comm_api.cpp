@@ -528,6 +528,11 @@ int TileXRSymmAlloc(TileXRCommPtr comm, size_t bytes, void **localPtr, TileXRUDM
     if (cudaSetDevice(c->device()) != cudaSuccess) return TILEXR_ERROR_RUNTIME;
     void *p = nullptr;
     const size_t rounded = (bytes + 511) & ~static_cast<size_t>(511);
+    if (c->usesVmm()) {
+        // every rank of the communicator took the same route at bring-up, so all of them are in here
+        const int ret = c->SymmAllocVmm(rounded, localPtr, handle);
+        if (ret != TILEXR_ERROR_NOT_SUPPORT) return ret;
+    }
     if (cudaMalloc(&p, rounded) != cudaSuccess) {
         cudaGetLastError();
         return TILEXR_ERROR_RUNTIME;
@@ -548,6 +553,33 @@ int TileXRSymmFree(TileXRCommPtr comm, TileXRUDMAMemHandle handle)
     TileXRComm *c = AsComm(comm);
     if (c == nullptr) return TILEXR_ERROR_NOT_INITIALIZED;
     return c->Unregister(handle);
+}
+
+int TileXRGetMulticastPointer(TileXRCommPtr comm, const void *ptr, size_t bytes, void **mcPtr)
+{
+    TileXRComm *c = AsComm(comm);
+    if (c == nullptr) return TILEXR_ERROR_NOT_INITIALIZED;
+    if (ptr == nullptr || mcPtr == nullptr) return TILEXR_ERROR_PARA_CHECK_FAIL;
+    *mcPtr = nullptr;
+    const uint8_t *p = static_cast<const uint8_t *>(ptr);
+    if (c->usesVmm() && p >= c->window() && p + bytes <= c->window() + c->hostArgs()->peerMemBytes) {
+        if (c->windowMulticast() != nullptr) *mcPtr = c->windowMulticast() + (p - c->window());
+        return TILEXR_SUCCESS;
+    }
+    for (const RegionRecord &rec : c->regions()) {
+        if (!rec.live || !rec.vmm.live) continue;
+        if (p >= rec.localBase && p + bytes <= rec.localBase + rec.bytes) {
+            if (rec.vmm.multicast != nullptr) *mcPtr = rec.vmm.multicast + (p - rec.localBase);
+            return TILEXR_SUCCESS;
+        }
+    }
+    return TILEXR_ERROR_NOT_FOUND;
+}
+
+int TileXRNvlsAvailable(TileXRCommPtr comm)
+{
+    TileXRComm *c = AsComm(comm);
+    return (c != nullptr && c->initialized() && (c->hostArgs()->extraFlag & TILEXR_FLAG_NVLS) != 0) ? 1 : 0;
 }
 
 int TileXRGetPeerPointers(TileXRCommPtr comm, TileXRUDMAMemHandle handle, void **peerPtrs)

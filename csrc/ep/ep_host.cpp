@@ -405,13 +405,17 @@ int TileXRMoeEpCombineFused(const TileXREpCombineParams *p, TileXRCommPtr comm, 
         a.parts = static_cast<uint32_t>(parts);
         a.partVecs = static_cast<uint32_t>(partVecs);
         const bool overlap = c.rankSize > 1 && routes >= 8192 && grid >= 16;
-        // Blocks that only reduce, in proportion to the rows each side reads and writes: the senders read every
-        // remote-bound row and write the travelling ones, the reducers read what arrives plus the local rows and
-        // write the tokens.
-        const double sendWork = static_cast<double>(routes) * (c.rankSize - 1) / c.rankSize + travel;
-        const double reduceWork = travel + static_cast<double>(routes) / c.rankSize + static_cast<double>(p->bs);
-        const int64_t reducersAuto = static_cast<int64_t>(grid * reduceWork / (sendWork + reduceWork));
-        a.reducerBlocks = overlap ? static_cast<uint32_t>(std::min<int64_t>(grid / 2, std::max<int64_t>(grid / 8, EnvLong("TILEXR_EP_REDUCER_BLOCKS", reducersAuto)))) : 0u;
+        // Blocks that only reduce.  The senders are bound by the link (about 550 GB/s per GPU in an all-to-all of
+        // eight) or by the rows they read and write; the reducers must keep up with what arrives.  With T the
+        // time of the slower of the two, a share reduceTime / T of the blocks, plus a margin, reduces.
+        const double sendRows = static_cast<double>(routes) * (c.rankSize - 1) / c.rankSize + travel;
+        const double reduceRows = travel + static_cast<double>(routes) / c.rankSize + static_cast<double>(p->bs);
+        const double tLink = travel * a.rowBytes / 550e9;
+        const double tSend = sendRows * a.rowBytes / 5e12;
+        const double tReduce = reduceRows * a.rowBytes / 5e12;
+        const double share = 1.25 * tReduce / std::max(tLink, tSend + tReduce);
+        const int64_t reducersAuto = static_cast<int64_t>(grid * std::min(0.5, std::max(0.125, share)));
+        a.reducerBlocks = overlap ? static_cast<uint32_t>(std::min<int64_t>(grid / 2, std::max<int64_t>(1, EnvLong("TILEXR_EP_REDUCER_BLOCKS", reducersAuto)))) : 0u;
         a.buckets = overlap ? static_cast<uint32_t>(std::min<int64_t>(EP_MAX_BUCKETS, std::max<int64_t>(1, p->bs / 512))) : 1u;
         // bucket lists live behind the slots in the same data half, when there is room for every row of the worst case
         a.listOff = (need + 255) & ~static_cast<uint64_t>(255);

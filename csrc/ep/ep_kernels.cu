@@ -909,8 +909,18 @@ __device__ __forceinline__ void CombineSendPart(const EpCombineArgs &a, CommArgs
     const int vEnd = min(rowVecs, vBegin + static_cast<int>(a.partVecs));
     uint8_t *dst = DataHalf(comm, src, epoch) + slot * a.rowBytes;
     if ((link & EP_LINK_NEXT_MASK) == 0) {
-        CopyLanes(dst + static_cast<int64_t>(vBegin) * 16, a.expertOut + r * a.rowBytes + static_cast<int64_t>(vBegin) * 16,
-                  static_cast<uint64_t>(vEnd - vBegin) * 16, lane, 32);
+        // eight 16-byte vectors in flight per lane: under an all-to-all of eight ranks a store takes several
+        // microseconds to be acknowledged, and the warps on an SM must cover that with bytes in flight
+        const uint8_t *src = a.expertOut + r * a.rowBytes;
+        int v = vBegin + lane;
+        for (; v + 7 * 32 < vEnd; v += 8 * 32) {
+            Vec16 q[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) q[u] = ld_vec16_stream(src + static_cast<int64_t>(v + u * 32) * 16);
+#pragma unroll
+            for (int u = 0; u < 8; ++u) st_vec16(dst + static_cast<int64_t>(v + u * 32) * 16, q[u]);
+        }
+        for (; v < vEnd; v += 32) st_vec16(dst + static_cast<int64_t>(v) * 16, ld_vec16_stream(src + static_cast<int64_t>(v) * 16));
     } else {
         // The rows of this token on this rank, in k order, times their gate weights: lane i keeps member i of
         // the chain, then every 16-byte column is summed in fp32 and rounded once.

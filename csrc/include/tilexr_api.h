@@ -119,6 +119,12 @@ int TileXRCommGetInfo(TileXRCommPtr comm, int *rank, int *rankSize, int *device,
 int TileXRSymmAlloc(TileXRCommPtr comm, size_t bytes, void **localPtr, TileXRUDMAMemHandle *handle);
 int TileXRSymmFree(TileXRCommPtr comm, TileXRUDMAMemHandle handle);
 int TileXRGetPeerPointers(TileXRCommPtr comm, TileXRUDMAMemHandle handle, void **peerPtrs /*[rankSize]*/);
+/* The address of [ptr, ptr + bytes) through the NVLink multicast object (a multimem store there reaches every
+ * rank's copy, a multimem load-reduce sums all copies in the switch).  ptr must lie in memory of TileXRSymmAlloc
+ * or in the communicator's window; *mcPtr is null when the node gave no multicast object. */
+int TileXRGetMulticastPointer(TileXRCommPtr comm, const void *ptr, size_t bytes, void **mcPtr);
+/* 1 when the communicator's window is bound to a multicast object (TILEXR_FLAG_NVLS is set in CommArgs). */
+int TileXRNvlsAvailable(TileXRCommPtr comm);
 // Finds the registered region that contains [ptr, ptr+bytes); TILEXR_ERROR_NOT_FOUND if none.
 int TileXRFindRegistration(TileXRCommPtr comm, const void *ptr, size_t bytes, TileXRUDMAMemHandle *handle,
                            uint64_t *offset);

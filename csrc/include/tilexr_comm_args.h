@@ -85,6 +85,7 @@ struct TileXRRegion {
     uint64_t bytes;
     uint8_t *localBase;
     uint8_t **peerBase;    // device array [rankSize]: the region of rank r mapped here
+    uint8_t *mcBase;       // the region through the NVLink multicast object (all ranks' copies at once), or null
 };
 
 #define TILEXR_REGISTRY_MAGIC 0x52525854u   // "TXRR"

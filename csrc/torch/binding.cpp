@@ -200,6 +200,15 @@ public:
         for (void *q : p) out.push_back(reinterpret_cast<uint64_t>(q));
         return out;
     }
+    uint64_t MulticastPtr(const at::Tensor &t)
+    {
+        void *mc = nullptr;
+        const int ret = TileXRGetMulticastPointer(ptr(), t.data_ptr(), t.nbytes(), &mc);
+        if (ret == TileXR::TILEXR_ERROR_NOT_FOUND) return 0;
+        Check(ret, "TileXRGetMulticastPointer");
+        return reinterpret_cast<uint64_t>(mc);
+    }
+    bool NvlsAvailable() { return TileXRNvlsAvailable(ptr()) != 0; }
     bool IsRegistered(const at::Tensor &t)
     {
         return TileXRFindRegistration(ptr(), t.data_ptr(), t.nbytes(), nullptr, nullptr) == TileXR::TILEXR_SUCCESS;
@@ -630,6 +639,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m)
         .def("unregister", &Comm::Unregister)
         .def("peer_pointers", &Comm::PeerPointers)
         .def("is_registered", &Comm::IsRegistered)
+        .def("multicast_ptr", &Comm::MulticastPtr)
+        .def("nvls_available", &Comm::NvlsAvailable)
         .def("destroy", &Comm::Destroy);
     m.def("init_process", &InitProcess, py::arg("rank"), py::arg("world_size"), py::arg("comm_id") = "", py::arg("domain") = 0,
           py::arg("buffer_mb") = 0, py::arg("device") = -1);

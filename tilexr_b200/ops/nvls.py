@@ -4,10 +4,11 @@
 ``multimem`` loads reduce inside the switch and ``multimem`` stores reach every rank's copy of a
 buffer, so an all-reduce moves 2/R of the message out of each GPU instead of (R-1) x (one-shot
 pushes) or 2 (R-1)/R x (two-shot).  The buffer has to be a symmetric allocation bound to a
-multicast object.  The allocation and the exchange of its handles between the processes are
-plumbing and come from ``torch.distributed._symmetric_memory``; the kernels that read and write
-through the multicast address are this package's own, and they synchronise the ranks through the
-communicator's flag windows with bounded waits.
+multicast object.  The communicator allocates it (CUDA virtual-memory API, POSIX descriptors traded
+over the library's own exchange, one multicast object per allocation: csrc/comm/vmm.cpp), and the same
+mechanism backs the communicator's window, so ``txr.all_reduce`` and friends take the in-switch path
+by themselves for large messages.  The kernels synchronise the ranks through the communicator's flag
+windows with bounded waits.
 
     ws = nvls.Workspace(comm, 64 << 20)              # collective: every rank of the group calls it
     buf = ws.view(torch.bfloat16, n)                  # a tensor inside this rank's copy
@@ -38,18 +39,36 @@ class Workspace:
     """
 
     def __init__(self, comm, nbytes: int, group=None, device: Optional[torch.device] = None):
+        nbytes = (int(nbytes) + 255) // 256 * 256
+        self.comm = comm
+        self.nbytes = nbytes
+        self.handle = None
+        if comm.nvls_available():
+            # The communicator's own allocator: virtual-memory API, POSIX descriptors over the library's
+            # exchange, every copy bound to one multicast object (csrc/comm/vmm.cpp).
+            self.buffer = comm.symm_empty([nbytes], torch.uint8)
+            self.mc_base = int(comm.multicast_ptr(self.buffer))
+            self.local_base = self.buffer.data_ptr()
+            if self.mc_base == 0:
+                raise NvlsUnavailable("the allocation has no multicast address on this system")
+            self.source = "runtime"
+            return
+        self._init_from_torch(nbytes, group, device)
+
+    def _init_from_torch(self, nbytes: int, group, device) -> None:
+        """Where the communicator has no multicast object of its own (created with TILEXR_ENABLE_VMM=0 or
+        TILEXR_ENABLE_NVLS=0, say), a buffer of ``torch.distributed._symmetric_memory`` serves."""
         import torch.distributed as dist
+
+        comm = self.comm
+        if not dist.is_initialized():
+            raise NvlsUnavailable("the communicator has no multicast object and torch.distributed is not initialised")
         import torch.distributed._symmetric_memory as symm
 
-        if not dist.is_initialized():
-            raise NvlsUnavailable("torch.distributed is not initialised: the multicast handles are exchanged through its store")
         group = group if group is not None else dist.group.WORLD
         if dist.get_world_size(group) != comm.world_size or dist.get_rank(group) != comm.rank:
             raise ValueError("the process group and the communicator must have the same ranks in the same order")
         device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
-        nbytes = (int(nbytes) + 255) // 256 * 256
-        self.comm = comm
-        self.nbytes = nbytes
         try:
             self.buffer = symm.empty(nbytes, dtype=torch.uint8, device=device)
             self.handle = symm.rendezvous(self.buffer, group)
@@ -62,6 +81,7 @@ class Workspace:
         self.local_base = int(self.handle.buffer_ptrs[comm.rank])
         if not (self.local_base <= self.buffer.data_ptr() < self.local_base + max(int(self.handle.buffer_size), 1)):
             raise NvlsUnavailable("the symmetric tensor does not lie in the mapped allocation")
+        self.source = "torch"
 
     # ---- views ------------------------------------------------------------------------------
     def view(self, dtype: torch.dtype, numel: int, offset_bytes: int = 0) -> torch.Tensor:
