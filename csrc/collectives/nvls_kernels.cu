@@ -534,6 +534,8 @@ int NvlsWindowCollective(int kind, const void *in, void *out, int64_t count, Til
     int ek = 2;
     if (reduces) {
         if (reduceOp != TILEXR_REDUCE_SUM) return TILEXR_ERROR_NOT_SUPPORT;
+        // the order in which the switch adds the ranks' values is not ours to fix
+        if (hostArgs->extraFlag & TILEXR_FLAG_DETERMINISTIC) return TILEXR_ERROR_NOT_SUPPORT;
         if (dtype == TILEXR_DATA_TYPE_BFP16) ek = 0;
         else if (dtype == TILEXR_DATA_TYPE_FP16) ek = 1;
         else if (dtype == TILEXR_DATA_TYPE_FP32) ek = 2;
@@ -545,6 +547,9 @@ int NvlsWindowCollective(int kind, const void *in, void *out, int64_t count, Til
     // Below these sizes the peer-to-peer kernels (one launch, direct pushes) are as fast or faster.
     const uint64_t floorBytes = static_cast<uint64_t>(EnvLongNvls("TILEXR_NVLS_MIN_BYTES", kind == COLL_KIND_ALL_REDUCE ? (32 << 10) : (1 << 20)));
     if (staged < floorBytes) return TILEXR_ERROR_NOT_SUPPORT;
+    // With two or three ranks the switch saves little traffic and the staging copies cost more than they save on
+    // large messages; the latency advantage of the single meeting remains below a few megabytes.
+    if (R < 4 && staged > static_cast<uint64_t>(EnvLongNvls("TILEXR_NVLS_SMALL_WORLD_MAX_BYTES", 8 << 20))) return TILEXR_ERROR_NOT_SUPPORT;
     NvlsWindowArgs a;
     std::memset(&a, 0, sizeof(a));
     a.in = static_cast<const uint8_t *>(in);
