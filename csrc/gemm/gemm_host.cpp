@@ -244,6 +244,62 @@ int TileXRMatmulFp8(const void *a, const void *b, void *c, int64_t m, int64_t n,
     return TILEXR_SUCCESS;
 }
 
+int TileXRMatmulFp8BlockScaled(const void *a, const float *scaleA, const void *b, const float *scaleB, void *c, int64_t m, int64_t n,
+                               int64_t k, TileXRDataType inDtype, TileXRDataType outDtype, int32_t *status, TileXRStream stream)
+{
+    if (a == nullptr || b == nullptr || c == nullptr || scaleA == nullptr || scaleB == nullptr || m <= 0 || n <= 0 || k <= 0) {
+        return TILEXR_ERROR_PARA_CHECK_FAIL;
+    }
+    if ((inDtype != TILEXR_DATA_TYPE_FP8E4M3 && inDtype != TILEXR_DATA_TYPE_FP8E5M2) ||
+        (outDtype != TILEXR_DATA_TYPE_FP16 && outDtype != TILEXR_DATA_TYPE_BFP16)) {
+        TILEXR_LOG(ERROR) << "block-scaled fp8 matmul: operands e4m3 or e5m2, output fp16 or bf16";
+        return TILEXR_ERROR_PARA_CHECK_FAIL;
+    }
+    if (k % 128 != 0 || n % 8 != 0 ||
+        ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(c)) & 15u) != 0) {
+        TILEXR_LOG(ERROR) << "block-scaled fp8 matmul: K a multiple of 128 (the scale block), N a multiple of 8, operands 16-byte aligned";
+        return TILEXR_ERROR_PARA_CHECK_FAIL;
+    }
+    GemmBlockArgs g;
+    std::memset(&g, 0, sizeof(g));
+    int ret = MakeMap8(&g.tmapA, a, m, k, GEMM_BM);
+    if (ret != TILEXR_SUCCESS) return ret;
+    ret = MakeMap8(&g.tmapB, b, n, k, GEMM_BN / 2);
+    if (ret != TILEXR_SUCCESS) return ret;
+    g.scaleA = scaleA;
+    g.scaleB = scaleB;
+    g.c = static_cast<uint8_t *>(c);
+    g.status = status;
+    g.M = static_cast<int32_t>(m);
+    g.N = static_cast<int32_t>(n);
+    g.K = static_cast<int32_t>(k);
+    g.nBlocks = static_cast<int32_t>((n + GEMM_BN - 1) / GEMM_BN);
+    g.kBlocks = static_cast<int32_t>(k / 128);
+    g.scaleBRows = static_cast<int32_t>((n + 127) / 128);
+    g.rasterGroup = static_cast<int32_t>(std::max<long>(1, EnvLong("TILEXR_GEMM_GROUP", 8)));
+    g.isBf16 = outDtype == TILEXR_DATA_TYPE_BFP16 ? 1u : 0u;
+    g.fp8Format = inDtype == TILEXR_DATA_TYPE_FP8E5M2 ? 2 : 1;
+    int sms = 0;
+    ret = SmCount(&sms);
+    if (ret != TILEXR_SUCCESS) return ret;
+    const int pairTiles = static_cast<int>((m + 2 * GEMM_BM - 1) / (2 * GEMM_BM)) * g.nBlocks;
+    const int pairs = std::max(1, std::min<int>(pairTiles, static_cast<int>(EnvLong("TILEXR_GEMM_CTAS", sms)) / 2));
+    static std::once_flag once;
+    std::call_once(once, [] {
+        cudaFuncSetAttribute(GemmFp8BlockKernel(), cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(GEMM_FP8_BLOCK_SMEM_BYTES));
+    });
+    void *params[] = {&g};
+    const cudaError_t e = cudaLaunchKernel(GemmFp8BlockKernel(), dim3(2 * pairs), dim3(GEMM_FP8_BLOCK_THREADS), params, GEMM_FP8_BLOCK_SMEM_BYTES,
+                                           static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) {
+        TILEXR_LOG(ERROR) << "block-scaled fp8 matmul launch failed: " << cudaGetErrorString(e);
+        cudaGetLastError();
+        return TILEXR_ERROR_RUNTIME;
+    }
+    NoteLaunch();
+    return TILEXR_SUCCESS;
+}
+
 static int FusedCommon(TileXRCommPtr comm, TileXRCommArgs **hostArgs, GM_ADDR *devArgs)
 {
     if (comm == nullptr) return TILEXR_ERROR_NOT_INITIALIZED;

@@ -63,6 +63,29 @@ struct GemmArgs {
     float alpha;
 };
 
+// Block-scaled fp8 GEMM (gemm_tcgen05_fp8_block.cu): warp 0 TMA, warp 1 MMA, warps 4-11 fold the scratch accumulators.
+constexpr unsigned GEMM_FP8_BLOCK_THREADS = 384;
+constexpr int GEMM_FP8_BLOCK_STAGES = 5;     // one stage less than the bf16 kernel: the weight scales of a tile live in shared memory too
+constexpr size_t GEMM_FP8_BLOCK_SMEM_BYTES = 1024 /* alignment slack */ + GEMM_FP8_BLOCK_STAGES * GEMM_PAIR_STAGE_BYTES + 1024 /* barriers */ +
+                                             GEMM_BM * 256 /* epilogue staging tile */;
+
+struct GemmBlockArgs {
+    CUtensorMap tmapA;        // A [M, K] 8-bit, box 128 rows x 128 bytes
+    CUtensorMap tmapB;        // B [N, K] 8-bit, box 128 rows x 128 bytes
+    const float *scaleA;      // [M, K / 128]
+    const float *scaleB;      // [scaleBRows, K / 128], one row per 128 rows of B
+    uint8_t *c;               // [M, N] bf16 or fp16
+    int32_t *status;
+    int32_t M, N, K;
+    int32_t nBlocks;          // 256-column tiles
+    int32_t kBlocks;          // K / 128
+    int32_t scaleBRows;       // ceil(N / 128)
+    int32_t rasterGroup;
+    uint32_t isBf16;
+    int32_t fp8Format;        // 1 = e4m3, 2 = e5m2
+};
+
+const void *GemmFp8BlockKernel();
 const void *GemmKernelSingle();
 const void *GemmKernelEmulated();
 const void *GemmPairKernel();

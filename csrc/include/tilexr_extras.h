@@ -5,6 +5,8 @@
 #include "tilexr_fused.h"
 #include "tilexr_hostsim.h"
 #include "tilexr_moonep.h"
+#include "tilexr_moonep_combine_v2.h"
+#include "tilexr_moonep_trace.h"
 #include "tilexr_probes.h"
 #include "../checker/checker.h"
 

@@ -46,6 +46,14 @@ int TileXRMatmul(const void *a, const void *b, void *c, int64_t m, int64_t n, in
 int TileXRMatmulFp8(const void *a, const void *b, void *c, int64_t m, int64_t n, int64_t k, TXR_DT inDtype, TXR_DT outDtype,
                     float alpha, int32_t *status, TileXRStream stream);
 
+// Block-scaled fp8: C[m, n] = sum over 128-wide blocks kb of K of scaleA[m, kb] * scaleB[n / 128, kb] * (A x B^T restricted to
+// kb).  A [M, K] and B [N, K] are e4m3 or e5m2, scaleA is [M, K/128] fp32 (one scale per row and block: the layout the
+// expert-parallel dispatch emits), scaleB is [ceil(N/128), K/128] fp32 (one scale per 128 x 128 block of the weight).
+// K a multiple of 128.  The tensor cores form each block's product exactly in fp32; CUDA cores fold the blocks
+// together with their scales while the next block is being multiplied.
+int TileXRMatmulFp8BlockScaled(const void *a, const float *scaleA, const void *b, const float *scaleB, void *c, int64_t m, int64_t n,
+                               int64_t k, TXR_DT inDtype, TXR_DT outDtype, int32_t *status, TileXRStream stream);
+
 // C[R*shardRows, N] = all_gather(aShard)[R*shardRows, K] x B[N,K]^T.  `aStaging` is a registered
 // buffer of R*shardRows*K elements at the same offset on every rank (TileXRSymmAlloc): the
 // kernel pushes aShard into every peer's staging buffer and multiplies as rows arrive.  Row

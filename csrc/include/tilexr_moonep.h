@@ -276,11 +276,6 @@ int TileXRMoonEpPlannerV3(const int32_t *topkExperts, const int32_t *tokensPerEx
                           int32_t *remoteStats, int32_t *dupCounts, int32_t *status, uint64_t waitIterations,
                           TileXRStream stream);
 
-// Combine over an explicit dstLocal, reference name (src/include/tilexr_moonep_combine_v2.h:12-41).
-int TileXRMoonEpCombineStageV2(const int32_t *dstLocal, TileXRCommPtr comm, int64_t bs, int64_t h, int64_t topK, int64_t nvS,
-                               const void *hiddenNvsh, void *hiddenSh, const float *routeWeightsNvs, float *routeWeightsSk,
-                               int dtype /* TileXRMoonEpDType */, TileXRStream stream);
-
 // ---- CPU reference of the whole protocol (single process, all ranks) --------------------------------------
 // allTopk int32 [r, s*k].  Outputs for rank `rank`; any output pointer may be null.
 int TileXRMoonEpReferencePlan(int rank, int64_t r, int64_t s, int64_t k, int64_t e, int64_t b, int64_t tokenPadding,

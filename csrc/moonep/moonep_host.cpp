@@ -9,6 +9,7 @@
 #include "moonep_kernels.cuh"
 #include "tilexr_log.h"
 #include "tilexr_moonep.h"
+#include "tilexr_moonep_trace.h"
 #include "tilexr_types.h"
 
 using namespace TileXR;
@@ -338,14 +339,29 @@ int TileXRMoonEpDispatchV1(const TileXRMoonEpDispatchArgsV1 *args, TileXRStream 
     a.weightHandle = h2;
     a.weightOffset = o2;
     a.weightWinOff = Align(static_cast<uint64_t>(p->nvS) * rowBytes, 256);
+    unsigned grid = 0;
+    ret = CoopGrid(args->comm, c, MoonDispatchKernelEntry(), 0, std::min<long>(EnvLong("TILEXR_MOONEP_DISPATCH_BLOCKS", 128), (p->n + 15) / 16), &grid);
+    if (ret != TILEXR_MOONEP_SUCCESS) return ret;
+    if (args->trace != nullptr && args->trace->buffer != nullptr) {
+        // the buffer must hold the layout of tilexr_moonep_trace.h for this grid; a short buffer is refused, not overrun
+        const TileXRMoonEpDispatchTraceV1 *t = args->trace;
+        uint64_t recOff = 0, evOff = 0, total = 0;
+        if (t->structSize < sizeof(TileXRMoonEpDispatchTraceV1) || t->iteration >= t->iterationCount ||
+            TileXRMoonEpTraceLayout(t->iterationCount, grid, t->eventCapacity, &recOff, &evOff, &total) != 0 || total > t->bufferBytes) {
+            TILEXR_LOG(ERROR) << "MoonEP dispatch: the trace buffer of " << t->bufferBytes << " bytes does not hold " << t->iterationCount
+                              << " iterations of " << grid << " blocks with " << t->eventCapacity << " events each";
+            return TILEXR_MOONEP_ERROR_INVALID_ARGUMENT;
+        }
+        a.traceBuffer = t->buffer;
+        a.traceIteration = t->iteration;
+        a.traceIterationCount = t->iterationCount;
+        a.traceEventCapacity = t->eventCapacity;
+    }
     if (!zeroCopy && a.weightWinOff + static_cast<uint64_t>(p->nvS) * 4 > c.hostArgs->dataHalfBytes) {
         TILEXR_LOG(ERROR) << "MoonEP dispatch: " << p->nvS << " rows of " << rowBytes << " bytes do not fit the window; allocate "
                           << "hiddenNvsh (and routeWeightsNvs) with TileXRSymmAlloc so that peers write them directly";
         return TILEXR_MOONEP_ERROR_INVALID_ARGUMENT;
     }
-    unsigned grid = 0;
-    ret = CoopGrid(args->comm, c, MoonDispatchKernelEntry(), 0, std::min<long>(EnvLong("TILEXR_MOONEP_DISPATCH_BLOCKS", 128), (p->n + 15) / 16), &grid);
-    if (ret != TILEXR_MOONEP_SUCCESS) return ret;
     int64_t magic = 0;
     if (TileXRCommNextMagic(args->comm, &magic) != TILEXR_SUCCESS) return TILEXR_MOONEP_ERROR_INTERNAL;
     a.magic = magic;
@@ -420,14 +436,6 @@ int TileXRMoonEpCombineV1(const TileXRMoonEpCombineArgsV1 *args, TileXRStream st
                          args->hiddenSh->shape[1], args->hiddenSh->dtype, args->hiddenNvsh->data, args->hiddenSh->data,
                          args->routeWeightsNvs != nullptr ? static_cast<const float *>(args->routeWeightsNvs->data) : nullptr,
                          args->routeWeightsSk != nullptr ? static_cast<float *>(args->routeWeightsSk->data) : nullptr, stream);
-}
-
-int TileXRMoonEpCombineStageV2(const int32_t *dstLocal, TileXRCommPtr comm, int64_t bs, int64_t h, int64_t topK, int64_t nvS,
-                               const void *hiddenNvsh, void *hiddenSh, const float *routeWeightsNvs, float *routeWeightsSk,
-                               int dtype, TileXRStream stream)
-{
-    return LaunchCombine(comm, dstLocal, nullptr, bs, topK, nvS, h, static_cast<uint32_t>(dtype), hiddenNvsh, hiddenSh,
-                         routeWeightsNvs, routeWeightsSk, stream);
 }
 
 int TileXRMoonEpPrefetchWeightV1(const TileXRMoonEpPrefetchWeightArgsV1 *args, TileXRStream stream)

@@ -11,6 +11,7 @@
 #include <cuda_fp16.h>
 
 #include "device/tilexr_convert.cuh"
+#include "device/tilexr_moonep_trace.cuh"
 #include "device/tilexr_rma.cuh"
 #include "device/tilexr_sync.cuh"
 #include "moonep_kernels.cuh"
@@ -200,6 +201,8 @@ __device__ void PlannerBody(const PlannerArgs &a)
 
 __device__ void MoonDispatchBody(const MoonDispatchArgs &a)
 {
+    __shared__ unsigned int sPeerRows[TILEXR_MAX_RANK_SIZE];     // rows this block sent to each rank (for the trace)
+    __shared__ int sBad;                                         // 1 + index of a route whose destination is impossible
     Waiter w;
     bool ok = KernelPrologue(w, a.comm, a.magic, TILEXR_OP_MOONEP_DISPATCH, a.N, true);
     ok = PlanUsable(w, a.status, ok);
@@ -211,9 +214,21 @@ __device__ void MoonDispatchBody(const MoonDispatchArgs &a)
     const int64_t gwarp = static_cast<int64_t>(blockIdx.x) * MOONEP_WARPS + (threadIdx.x >> 5);
     const int64_t nWarps = static_cast<int64_t>(gridDim.x) * MOONEP_WARPS;
     uint8_t *half = DataHalf(comm, rank, epoch);
+    MoonTrace trace{nullptr, nullptr, 0, 0, 0, 0};
+    if (threadIdx.x == 0) {
+        trace = MoonTraceOpen(a.traceBuffer, a.traceIteration, a.traceIterationCount, a.traceEventCapacity, static_cast<uint32_t>(rank),
+                              static_cast<uint32_t>(R), blockIdx.x, gridDim.x, epoch);
+        MoonTraceBegin(trace);
+        MoonTraceEnd(trace, TILEXR_MOONEP_TRACE_PLAN_CHECK, TILEXR_MOONEP_TRACE_NO_PEER, 0, 0);
+        sBad = 0;
+    }
+    for (int r = threadIdx.x; r < R; r += blockDim.x) sPeerRows[r] = 0;
+    __syncthreads();
 
     if (ok) {
         // padding rows are cleared by their owner; they never overlap a delivered row
+        MoonTraceBegin(trace);
+        uint64_t cleared = 0;
         for (int g = blockIdx.x; g < a.groups; g += gridDim.x) {
             const int64_t first = a.zeroFill[g * 2];
             const int64_t rows = a.zeroFill[g * 2 + 1];
@@ -223,13 +238,20 @@ __device__ void MoonDispatchBody(const MoonDispatchArgs &a)
             if (a.weightsOut != nullptr) {
                 for (int64_t i = threadIdx.x; i < rows; i += blockDim.x) a.weightsOut[first + i] = 0.f;
             }
+            cleared += static_cast<uint64_t>(rows);
         }
+        MoonTraceEnd(trace, TILEXR_MOONEP_TRACE_ZERO_FILL, rank, cleared * a.rowBytes, static_cast<uint32_t>(cleared));
+        MoonTraceBegin(trace);
         for (int64_t i = gwarp; i < a.N; i += nWarps) {
             int32_t raw = a.dst[i];
             if (raw < 0) raw = ~raw;     // a duplicate is delivered like a primary
             const int dstRank = raw / a.NvS;
             const int64_t slot = raw - dstRank * a.NvS;
-            if (dstRank >= R) continue;
+            if (dstRank >= R) {
+                // a plan that names a rank outside the communicator is not skipped over: every rank learns of it
+                if (lane == 0) atomicMax(&sBad, static_cast<int>(min(i, static_cast<int64_t>(0x7ffffffe))) + 1);
+                continue;
+            }
             const uint8_t *row = a.hidden + (i / a.K) * a.rowBytes;
             uint8_t *out;
             float *wout = nullptr;
@@ -243,13 +265,35 @@ __device__ void MoonDispatchBody(const MoonDispatchArgs &a)
                 out = peerHalf + slot * a.rowBytes;
                 if (a.weights != nullptr) wout = reinterpret_cast<float *>(peerHalf + a.weightWinOff) + slot;
             }
-            CopyLanes(out, row, a.rowBytes, lane, 32);
-            if (lane == 0 && wout != nullptr) *wout = a.weights[i];
+            CopyLanesDeep(out, row, a.rowBytes, lane, 32);
+            if (lane == 0) {
+                if (wout != nullptr) *wout = a.weights[i];
+                if (trace.capacity != 0 || a.traceBuffer != nullptr) atomicAdd(&sPeerRows[dstRank], 1u);
+            }
         }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            if (sBad != 0) RaiseFailure(w, TILEXR_DEV_BAD_ARGUMENT, rank, sBad - 1, static_cast<uint64_t>(R), static_cast<uint64_t>(a.dst[sBad - 1]));
+            if (trace.record != nullptr) {
+                // one event per destination: all of them span the block's whole send phase
+                const uint64_t opened = trace.openedNs;
+                for (int r = 0; r < R; ++r) {
+                    if (sPeerRows[r] == 0) continue;
+                    trace.openedNs = opened;
+                    MoonTraceEnd(trace, TILEXR_MOONEP_TRACE_ROUTE_SEND, r, static_cast<uint64_t>(sPeerRows[r]) * a.rowBytes, sPeerRows[r]);
+                }
+            }
+        }
+        ok = BlockBroadcastOk(sBad == 0);
+        MoonTraceBegin(trace);
         RaiseBlockFlags(comm, rank, R, epoch);
+        MoonTraceEnd(trace, TILEXR_MOONEP_TRACE_FLAG_RAISE, TILEXR_MOONEP_TRACE_NO_PEER, 0, 0);
     }
+    MoonTraceBegin(trace);
     ok = WaitAllBlockFlags(w, comm, rank, R, ok);
+    MoonTraceEnd(trace, TILEXR_MOONEP_TRACE_FLAG_WAIT, TILEXR_MOONEP_TRACE_NO_PEER, 0, 0);
     if (ok && !a.zeroCopy) {
+        MoonTraceBegin(trace);
         // copy the delivered rows out of the window; padding rows were cleared above
         const int64_t total = static_cast<int64_t>(a.NvS);
         const int64_t perBlock = (total + gridDim.x - 1) / gridDim.x;
@@ -266,7 +310,9 @@ __device__ void MoonDispatchBody(const MoonDispatchArgs &a)
             CopyLanes(a.hiddenOut + s * a.rowBytes, half + s * a.rowBytes, a.rowBytes, lane, 32);
             if (lane == 0 && a.weightsOut != nullptr) a.weightsOut[s] = reinterpret_cast<const float *>(half + a.weightWinOff)[s];
         }
+        MoonTraceEnd(trace, TILEXR_MOONEP_TRACE_OUTPUT_COPY, rank, static_cast<uint64_t>(n) * a.rowBytes, static_cast<uint32_t>(n));
     }
+    MoonTraceClose(trace, static_cast<uint32_t>(w.status));
     KernelEpilogue(w, ok);
 }
 

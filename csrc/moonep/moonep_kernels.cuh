@@ -60,6 +60,9 @@ struct MoonDispatchArgs {
     uint32_t outHandle, weightHandle;
     uint64_t outOffset, weightOffset;
     uint64_t weightWinOff;       // weights region inside the data half when staged
+    // event trace (tilexr_moonep_trace.h), off when traceBuffer is null
+    void *traceBuffer;
+    uint32_t traceIteration, traceIterationCount, traceEventCapacity;
 };
 
 struct MoonCombineArgs {

@@ -96,3 +96,26 @@ def test_matmul_reduce_scatter(txr, ranks, shard_rows, n, k):
     for r in range(ranks):
         _close(outs[r], want[r * shard_rows:(r + 1) * shard_rows], k * ranks)
     world.destroy()
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 128), (256, 256, 512), (300, 384, 1024), (1024, 2048, 7168), (96, 128, 256)])
+def test_matmul_fp8_block_scaled(txr, m, n, k):
+    """Block-scaled fp8 (1 x 128 activation scales, 128 x 128 weight scales, fp32) against the fp32 product of the
+    dequantised operands.  Rows are given very different magnitudes, and so are the weight blocks, so that a scale
+    applied to the wrong row, column group or block of K shows."""
+    from tilexr_b200.utils import oracle
+
+    g = torch.Generator().manual_seed(31)
+    a = torch.randn(m, k, generator=g) * (0.25 + 4.0 * torch.rand(m, 1, generator=g)) * (0.5 + torch.rand(1, k // 128, generator=g)).repeat_interleave(128, dim=1)
+    w = torch.randn(n, k, generator=g) * 0.5
+    nb = (n + 127) // 128
+    w = w * (0.2 + 3.0 * torch.rand(nb, k // 128, generator=g)).repeat_interleave(128, dim=0)[:n].repeat_interleave(128, dim=1)
+    qa, sa = txr.quant.fp8_quant_1x128(a.to(torch.bfloat16).cuda())
+    qw, sw = txr.gemm.quantize_weight_128x128(w.cuda())
+    got = txr.gemm.matmul_fp8_block(qa, sa, qw, sw).float().cpu()
+    torch.cuda.synchronize()
+    da = oracle.fp8_dequant_1x128_ref(qa.cpu(), sa.cpu())
+    dw = qw.cpu().float().view(-1, k) * sw.cpu().repeat_interleave(128, dim=0)[:n].repeat_interleave(128, dim=1)
+    want = da @ dw.t()
+    assert torch.allclose(got, want, rtol=1e-2, atol=1e-2 * want.abs().max().item()), (got - want).abs().max()
+    assert (got - want).abs().mean() < 4e-3 * want.abs().mean() + 1e-4

@@ -164,3 +164,129 @@ def test_harness_correctness_runner_single_rank(txr, port):
         assert result["ok_all_ranks"], result
     backend.close()
     comm.destroy()
+
+
+@pytest.mark.parametrize("r,s,k,e,b,dtype", [(2, 40, 8, 8, 2, torch.bfloat16), (4, 64, 8, 16, 4, torch.bfloat16), (4, 48, 4, 32, 4, torch.float32)])
+def test_combine_folds_duplicates_and_leaves_a_profile(txr, r, s, k, e, b, dtype):
+    """Second-generation combine: the rows a token has on one rank come back as one.  Against the first generation
+    (one rounding) the result may move by about a unit in the last place; the weights return bit-exact; every block
+    leaves a profile record whose counters add up to the rows of the plan."""
+    C = txr._C
+    from tilexr_b200.tools.moonep import combine_v2_trace
+
+    world = txr.init_emulated_world(r, device=0, buffer_mb=64)
+    topk = _topk(r, s, k, e, 13)
+    topk_dev = [t.cuda() for t in topk]
+    plans = world.run(lambda c, rank: C.moonep_planning(c, topk_dev[rank], e, b, 4))
+    world.check()
+    nvs, n, h = plans[0]["NvS"], s * k, 512
+    g = torch.Generator().manual_seed(21)
+    hidden = [torch.randn(s, h, generator=g).to(dtype).cuda() for _ in range(r)]
+    weights = [torch.rand(s, k, generator=g).cuda() for _ in range(r)]
+    rows = world.symm_empty((nvs, h), dtype)
+    wrow = world.symm_empty((nvs,), torch.float32)
+    world.run(lambda c, rank: C.moonep_dispatch(c, plans[rank], hidden[rank], weights[rank], rows[rank], wrow[rank]))
+    world.check()
+    # a stand-in expert that makes every row different: scale by 1 + slot / 64
+    processed = [(rows[rank].float() * (1 + torch.arange(nvs, device="cuda").unsqueeze(1) / 64)).to(dtype) for rank in range(r)]
+    out1 = [torch.empty(s, h, dtype=dtype, device="cuda") for _ in range(r)]
+    w1 = [torch.empty(s, k, dtype=torch.float32, device="cuda") for _ in range(r)]
+    world.run(lambda c, rank: C.moonep_combine(c, plans[rank], processed[rank], wrow[rank], out1[rank], w1[rank]))
+    world.check()
+    nbytes, prof_off, _, _, rec_bytes, rec_max = C.moonep_combine_v2_workspace(s, h, k, nvs, dtype)
+    assert rec_bytes == combine_v2_trace.RECORD_BYTES
+    ws = [torch.zeros(nbytes, dtype=torch.uint8, device="cuda") for _ in range(r)]
+    for launch in range(2):                                         # the index is rebuilt by every launch
+        out2 = [torch.full((s, h), float("nan"), dtype=dtype, device="cuda") for _ in range(r)]
+        w2 = [torch.empty(s, k, dtype=torch.float32, device="cuda") for _ in range(r)]
+        world.run(lambda c, rank: C.moonep_combine_v2(c, plans[rank]["dst_local"], processed[rank], wrow[rank], out2[rank], w2[rank], ws[rank], k))
+        world.check()
+        for rank in range(r):
+            assert torch.equal(w2[rank], weights[rank])
+            tol = 1e-5 if dtype == torch.float32 else 2e-2
+            assert torch.allclose(out2[rank].float(), out1[rank].float(), rtol=tol, atol=tol), (out2[rank].float() - out1[rank].float()).abs().max()
+    folded_total = 0
+    for rank in range(r):
+        raw = ws[rank][prof_off:prof_off + rec_bytes * rec_max].cpu().numpy().tobytes()
+        recs = combine_v2_trace.decode_profile_records(raw)
+        assert recs and all(x["rank"] == rank and "failure" not in x for x in recs)
+        assert {x["block"] for x in recs} == set(range(recs[0]["grid_dim"]))
+        tot = combine_v2_trace.totals(recs)
+        valid = int((plans[rank]["dst_local"] >= 0).sum())
+        assert tot["rows_indexed"] == valid and tot["groups_sent"] + tot["rows_folded"] == valid
+        assert tot["tokens_reduced"] == s and tot["bytes_sent"] == tot["groups_sent"] * h * hidden[0].element_size()
+        folded_total += tot["rows_folded"]
+        t = recs[0]["time_ns"]
+        assert t["begin"] <= t["index_cleared"] <= t["index_built"] <= t["send_end"] <= t["reduce_end"] <= t["end"]
+        assert [row["stage"] for row in combine_v2_trace.stage_table(recs)] == [st[0] for st in combine_v2_trace.STAGES]
+        assert combine_v2_trace.chrome_trace(recs)["traceEvents"]
+    # the expected number of folded rows from the plans themselves: routes of a token that share a destination rank
+    want_folded = 0
+    for src in range(r):
+        dst = plans[src]["dst"].cpu()
+        dest = (torch.where(dst >= 0, dst, ~dst) // nvs).view(s, k)
+        for t_ in range(s):
+            want_folded += k - len(set(dest[t_].tolist()))
+    assert folded_total == want_folded and (k <= r or folded_total > 0)
+    world.destroy()
+
+
+def test_dispatch_event_trace_decodes(txr):
+    """The dispatch kernel's event trace: header, one record per block, route-send events whose rows add up to the
+    routes of the plan; a short buffer is refused before anything is launched."""
+    C = txr._C
+    from tilexr_b200.tools.moonep import dispatch_trace
+
+    r, s, k, e, b, h = 4, 64, 4, 16, 4, 256
+    world = txr.init_emulated_world(r, device=0, buffer_mb=32)
+    topk_dev = [t.cuda() for t in _topk(r, s, k, e, 17)]
+    plans = world.run(lambda c, rank: C.moonep_planning(c, topk_dev[rank], e, b, 1))
+    world.check()
+    nvs = plans[0]["NvS"]
+    g = torch.Generator().manual_seed(2)
+    hidden = [torch.randn(s, h, generator=g).to(torch.bfloat16).cuda() for _ in range(r)]
+    rows = world.symm_empty((nvs, h), torch.bfloat16)
+    blocks, cap, iters = 128, 32, 2
+    assert dispatch_trace.trace_layout(iters, blocks, cap)["trace_bytes"] == C.moonep_trace_layout(iters, blocks, cap)[2]
+    bufs = [torch.zeros(C.moonep_trace_layout(iters, blocks, cap)[2], dtype=torch.uint8, device="cuda") for _ in range(r)]
+    for it in range(iters):
+        world.run(lambda c, rank: C.moonep_dispatch(c, plans[rank], hidden[rank], None, rows[rank], None, bufs[rank], it, iters, cap))
+        world.check()
+    for rank in range(r):
+        trace = dispatch_trace.decode_trace(bufs[rank].cpu().numpy().tobytes())
+        assert trace["header"]["rank"] == rank and trace["header"]["rank_size"] == r and trace["header"]["iterations"] == iters
+        grid = trace["header"]["blocks"]
+        assert len(trace["blocks"]) == iters * grid and all(blk["status"] == 0 and blk["dropped"] == 0 for blk in trace["blocks"])
+        for it in range(iters):
+            sent = sum(ev["rows"] for blk in trace["blocks"] if blk["iteration"] == it for ev in blk["events"] if ev["phase_name"] == "route-send")
+            assert sent == s * k
+        names = {row["phase"] for row in dispatch_trace.phase_summary(trace)}
+        assert {"plan-check", "zero-fill", "route-send", "flag-raise", "flag-wait"} <= names and "output-copy" not in names
+        assert all(ev["end_ns"] >= ev["begin_ns"] for blk in trace["blocks"] for ev in blk["events"])
+        assert dispatch_trace.chrome_trace(trace)["traceEvents"]
+    small = torch.zeros(1024, dtype=torch.uint8, device="cuda")
+    with pytest.raises(RuntimeError):
+        with txr.group():
+            for rank, c in enumerate(world.comms):
+                C.moonep_dispatch(c, plans[rank], hidden[rank], None, rows[rank], None, small, 0, 1, cap)
+    world.destroy()
+
+
+def test_dispatch_reports_a_destination_outside_the_communicator(txr):
+    C = txr._C
+    r, s, k, e, b, h = 2, 16, 2, 4, 2, 128
+    world = txr.init_emulated_world(r, device=0, buffer_mb=32)
+    topk_dev = [t.cuda() for t in _topk(r, s, k, e, 19)]
+    plans = world.run(lambda c, rank: C.moonep_planning(c, topk_dev[rank], e, b, 1))
+    world.check()
+    nvs = plans[0]["NvS"]
+    plans[1]["dst"][3] = 5 * nvs + 1                                    # rank 5 of 2
+    hidden = [torch.randn(s, h).to(torch.bfloat16).cuda() for _ in range(r)]
+    rows = world.symm_empty((nvs, h), torch.bfloat16)
+    world.run(lambda c, rank: C.moonep_dispatch(c, plans[rank], hidden[rank], None, rows[rank], None))
+    torch.cuda.synchronize()
+    assert world.comms[1].device_status() == 4                          # TILEXR_DEV_BAD_ARGUMENT, not a silent skip
+    assert world.comms[1].dfx()[6] == 3                                 # the failing route
+    for c in world.comms:
+        c.reset_status()
+    world.destroy()

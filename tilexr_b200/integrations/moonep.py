@@ -94,13 +94,25 @@ class TileXRMoonEPBuffer:
         return MoonEPCommPlan.from_dict(_C.moonep_planning(self.comm, topk, self.E, self.B, self.token_padding))
 
     def dispatch(self, hidden_sh: torch.Tensor, route_weights_sk: Optional[torch.Tensor], plan: MoonEPCommPlan,
-                 out: Optional[torch.Tensor] = None):
+                 out: Optional[torch.Tensor] = None, trace: Optional["DispatchTrace"] = None):
+        """``trace`` (a :class:`DispatchTrace`) makes the kernel record its phases, one traced launch per call until the
+        trace's iterations are used up."""
         self._check_alive()
         hidden_out = self.hidden_nvsh if out is None else out
         w_out = self.weights_nvs if route_weights_sk is not None else None
+        kw = {}
+        if trace is not None and trace.iteration < trace.iterations:
+            kw = dict(trace_buffer=trace.buffer, trace_iteration=trace.iteration, trace_iterations=trace.iterations,
+                      trace_event_capacity=trace.event_capacity)
+            trace.iteration += 1
         _C.moonep_dispatch(self.comm, plan.as_dict(), hidden_sh.contiguous(),
-                           None if route_weights_sk is None else route_weights_sk.float().contiguous(), hidden_out, w_out)
+                           None if route_weights_sk is None else route_weights_sk.float().contiguous(), hidden_out, w_out, **kw)
         return hidden_out, w_out
+
+    def dispatch_trace(self, iterations: int = 1, event_capacity: int = 64, blocks: int = 128) -> "DispatchTrace":
+        """A device buffer for the event trace of ``iterations`` dispatch launches (``blocks`` must be at least the grid of
+        the kernel: 128 unless TILEXR_MOONEP_DISPATCH_BLOCKS says otherwise)."""
+        return DispatchTrace(self.hidden_nvsh.device, iterations, event_capacity, blocks)
 
     def register_projection_buffers(self, rows_gate, rows_up, rows_down, dtype=torch.bfloat16) -> ProjectionBuffers:
         L = self.E // self.R
@@ -111,14 +123,41 @@ class TileXRMoonEPBuffer:
         self._check_alive()
         _C.moonep_prefetch_weight(self.comm, plan.as_dict(), projections.gate, projections.up, projections.down)
 
-    def combine(self, plan: MoonEPCommPlan, hidden_nvsh: torch.Tensor, route_weights_nvs: Optional[torch.Tensor] = None):
+    def combine(self, plan: MoonEPCommPlan, hidden_nvsh: torch.Tensor, route_weights_nvs: Optional[torch.Tensor] = None,
+                fold_duplicates: bool = False):
+        """``fold_duplicates`` runs the second-generation kernel: the rows that a token has on one expert rank are summed
+        there (fp32, route order, one rounding) and travel back as one row, so a token costs one row per distinct rank
+        instead of one per route; the result may differ from the single-rounding sum by about one unit in the last
+        place (csrc/moonep/moonep_combine_v2.cu).  Each block leaves a profile record: :meth:`combine_profile`."""
         self._check_alive()
         hidden_sh = torch.empty(self.S, hidden_nvsh.shape[1], dtype=hidden_nvsh.dtype, device=hidden_nvsh.device)
         w_sk = None
         if route_weights_nvs is not None:
             w_sk = torch.empty(self.S, self.K, dtype=torch.float32, device=hidden_nvsh.device)
-        _C.moonep_combine(self.comm, plan.as_dict(), hidden_nvsh.contiguous(), route_weights_nvs, hidden_sh, w_sk)
+        if fold_duplicates:
+            ws = self._combine_workspace(hidden_nvsh.shape[1], hidden_nvsh.dtype)
+            _C.moonep_combine_v2(self.comm, plan.dst_local, hidden_nvsh.contiguous(), route_weights_nvs, hidden_sh, w_sk, ws, self.K)
+        else:
+            _C.moonep_combine(self.comm, plan.as_dict(), hidden_nvsh.contiguous(), route_weights_nvs, hidden_sh, w_sk)
         return hidden_sh, w_sk
+
+    def _combine_workspace(self, h: int, dtype) -> torch.Tensor:
+        key = (h, dtype)
+        if getattr(self, "_combine_ws_key", None) != key:
+            nbytes, self._profile_off, _, _, self._profile_bytes, self._profile_max = _C.moonep_combine_v2_workspace(self.S, h, self.K, self.NvS, dtype)
+            self._combine_ws = torch.zeros(nbytes, dtype=torch.uint8, device=self.hidden_nvsh.device)
+            self._combine_ws_key = key
+        return self._combine_ws
+
+    def combine_profile(self):
+        """Decoded profile records of the last ``combine(..., fold_duplicates=True)`` (synchronises with the device)."""
+        from ..tools.moonep.combine_v2_trace import decode_profile_records
+
+        if getattr(self, "_combine_ws", None) is None:
+            return []
+        torch.cuda.synchronize()
+        raw = self._combine_ws[self._profile_off:self._profile_off + self._profile_bytes * self._profile_max].cpu().numpy().tobytes()
+        return decode_profile_records(raw)
 
     def prepare_reduce_grad(self, projections: ProjectionBuffers) -> ProjectionBuffers:
         """Gradient tensors must be fp32 and symmetric; returns zero-filled ones of the right shape."""
@@ -175,6 +214,25 @@ class TileXRMoonEPBuffer:
 
     def close(self) -> None:
         self._poisoned = True
+
+
+class DispatchTrace:
+    """Device buffer of the dispatch event trace (csrc/include/tilexr_moonep_trace.h) with its host-side decoding."""
+
+    def __init__(self, device, iterations: int = 1, event_capacity: int = 64, blocks: int = 128):
+        _, _, total = _C.moonep_trace_layout(iterations, blocks, event_capacity)
+        self.buffer = torch.zeros(total, dtype=torch.uint8, device=device)
+        self.iterations, self.event_capacity, self.blocks = iterations, event_capacity, blocks
+        self.iteration = 0
+
+    def raw(self) -> bytes:
+        torch.cuda.synchronize()
+        return self.buffer.cpu().numpy().tobytes()
+
+    def decode(self):
+        from ..tools.moonep.dispatch_trace import decode_trace
+
+        return decode_trace(self.raw())
 
 
 class Buffer:

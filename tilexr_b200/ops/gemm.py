@@ -21,6 +21,32 @@ def matmul_fp8(a: torch.Tensor, b: torch.Tensor, alpha: float = 1.0, out_dtype: 
     return _C.matmul_fp8(a.contiguous(), b.contiguous(), float(alpha), out_dtype)
 
 
+def matmul_fp8_block(a: torch.Tensor, scale_a: torch.Tensor, b: torch.Tensor, scale_b: torch.Tensor,
+                     out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """Block-scaled fp8 product ``(a * scale_a) @ (b * scale_b).T`` with fp32 scales: ``a`` [M, K] with one scale per row and
+    128 elements of K (``scale_a`` [M, K/128], what ``ep.dispatch(..., quant_mode=QUANT_FP8_1X128)`` and
+    ``quant.fp8_quant_1x128`` produce), ``b`` [N, K] with one scale per 128 x 128 block (``scale_b`` [ceil(N/128), K/128],
+    see :func:`quantize_weight_128x128`).  The tensor cores multiply one block of K at a time in fp32; the blocks are folded
+    together with their scales on the CUDA cores while the next block is being multiplied."""
+    return _C.matmul_fp8_block(a.contiguous(), scale_a.contiguous(), b.contiguous(), scale_b.contiguous(), out_dtype)
+
+
+def quantize_weight_128x128(w: torch.Tensor, dtype: torch.dtype = torch.float8_e4m3fn):
+    """``w`` [N, K] (K a multiple of 128) -> (fp8 [N, K], fp32 scales [ceil(N/128), K/128]): one scale per 128 x 128 block,
+    the block's largest magnitude mapped to the largest finite value of the fp8 type."""
+    n, k = w.shape
+    if k % 128 != 0:
+        raise ValueError("K must be a multiple of 128")
+    fmax = torch.finfo(dtype).max
+    nb = (n + 127) // 128
+    wp = torch.nn.functional.pad(w.float(), (0, 0, 0, nb * 128 - n))
+    blocks = wp.view(nb, 128, k // 128, 128)
+    amax = blocks.abs().amax(dim=(1, 3)).clamp_min(1e-4)
+    scale = amax / fmax
+    q = (blocks / scale[:, None, :, None]).clamp(-fmax, fmax).to(dtype).view(nb * 128, k)[:n].contiguous()
+    return q, scale.contiguous()
+
+
 def all_gather_matmul(comm, a_shard: torch.Tensor, b: torch.Tensor, staging: torch.Tensor) -> torch.Tensor:
     """``all_gather(a_shard) @ b.T`` with the gather overlapped tile by tile.
 

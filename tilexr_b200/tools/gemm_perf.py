@@ -21,10 +21,13 @@ def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--shapes", default=DEFAULT, help="comma separated MxNxK")
     ap.add_argument("--iters", type=int, default=8)
-    ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float16", "float8_e4m3fn", "float8_e5m2"],
-                    help="operand type; the fp8 types run the kind::f8f6f4 path against torch._scaled_mm (cuBLASLt)")
+    ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float16", "float8_e4m3fn", "float8_e5m2", "fp8_block"],
+                    help="operand type; the fp8 types run the kind::f8f6f4 path against torch._scaled_mm (cuBLASLt); fp8_block "
+                         "is e4m3 with fp32 block scales (1 x 128 activations, 128 x 128 weights) against torch._scaled_mm "
+                         "with the same scales where this torch / cuBLASLt accepts them, else against its per-tensor fp8 GEMM")
     args = ap.parse_args()
-    dtype = getattr(torch, args.dtype)
+    block = args.dtype == "fp8_block"
+    dtype = torch.float8_e4m3fn if block else getattr(torch, args.dtype)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")       # larger than the 126 MB L2
 
     def median_ms(fn):
@@ -46,7 +49,26 @@ def main() -> int:
         m, n, k = (int(v) for v in shape.split("x"))
         a = (torch.randn(m, k, device="cuda") * 0.5).to(dtype)
         b = (torch.randn(n, k, device="cuda") * 0.5).to(dtype)
-        if dtype in (torch.float8_e4m3fn, torch.float8_e5m2):
+        baseline = "torch.matmul (cuBLAS)"
+        if block:
+            qa, sa = txr.quant.fp8_quant_1x128((torch.randn(m, k, device="cuda") * 0.5).to(torch.bfloat16))
+            qb, sb = txr.gemm.quantize_weight_128x128(torch.randn(n, k, device="cuda") * 0.5)
+            run_ours = lambda: txr.gemm.matmul_fp8_block(qa, sa, qb, sb)
+            # cuBLASLt's block-wise modes want the activation scales K-major-outer ([M, K/128] stored column-major) and the
+            # weight scales as [K/128, N/128]; whether they exist depends on the torch / cuBLASLt build
+            sa_t = sa.t().contiguous().t()
+            sb_t = sb.t().contiguous()
+            run_lib = lambda: torch._scaled_mm(qa, qb.t(), scale_a=sa_t, scale_b=sb_t, out_dtype=torch.bfloat16)
+            baseline = "torch._scaled_mm block-wise (cuBLASLt)"
+            try:
+                run_lib()
+                torch.cuda.synchronize()
+            except Exception:
+                one = torch.tensor(1.0, device="cuda")
+                run_lib = lambda: torch._scaled_mm(qa, qb.t(), scale_a=one, scale_b=one, out_dtype=torch.bfloat16)
+                baseline = "torch._scaled_mm per-tensor (cuBLASLt; block-wise scales are not accepted by this build)"
+        elif dtype in (torch.float8_e4m3fn, torch.float8_e5m2):
+            baseline = "torch._scaled_mm per-tensor (cuBLASLt)"
             one = torch.tensor(1.0, device="cuda")
             run_ours = lambda: txr.gemm.matmul_fp8(a, b, 1.0)
             run_lib = lambda: torch._scaled_mm(a, b.t(), scale_a=one, scale_b=one, out_dtype=torch.bfloat16)
@@ -58,8 +80,12 @@ def main() -> int:
         c, ref = run_ours(), run_lib()
         torch.cuda.synchronize()
         flops = 2.0 * m * n * k
-        print(json.dumps({"shape": [m, n, k], "ours_us": ours * 1e3, "cublas_us": cublas * 1e3, "ours_tflops": flops / ours / 1e9,
-                          "cublas_tflops": flops / cublas / 1e9, "ratio": cublas / ours, "identical_bits": bool(torch.equal(c, ref))}),
+        identical = bool(torch.equal(c, ref)) if not block else None
+        close = None
+        if block:
+            close = bool(torch.allclose(c.float(), ref.float(), rtol=2e-2, atol=2e-2 * ref.float().abs().max().item())) if "block-wise" in baseline and "not accepted" not in baseline else None
+        print(json.dumps({"shape": [m, n, k], "baseline": baseline, "close_to_baseline": close, "ours_us": ours * 1e3, "cublas_us": cublas * 1e3, "ours_tflops": flops / ours / 1e9,
+                          "cublas_tflops": flops / cublas / 1e9, "ratio": cublas / ours, "identical_bits": identical}),
               flush=True)
     return 0
 
