@@ -709,6 +709,7 @@ std::vector<Event> ParseTraceJsonl(const std::string &text, std::vector<Finding>
     std::istringstream is(text);
     std::string line;
     int lineNo = 0;
+    bool allHaveIds = true;
     while (std::getline(is, line)) {
         ++lineNo;
         if (line.find_first_not_of(" \t\r") == std::string::npos) continue;
@@ -735,7 +736,10 @@ std::vector<Event> ParseTraceJsonl(const std::string &text, std::vector<Finding>
             }
             continue;
         }
-        e.id = out.size();
+        // Files of several ranks concatenate into one trace: when every line carries its global id, the events are put
+        // in that order below; otherwise the line order is the order.
+        if (FindInt(line, "id", &v)) e.id = static_cast<uint64_t>(v);
+        else allHaveIds = false;
         if (FindInt(line, "peer", &v)) e.peer = static_cast<int>(v);
         if (FindInt(line, "block", &v)) e.block = static_cast<int>(v);
         if (FindInt(line, "slot", &v)) e.slot = v;
@@ -752,6 +756,10 @@ std::vector<Event> ParseTraceJsonl(const std::string &text, std::vector<Finding>
         FindStr(line, "source", &e.source);
         out.push_back(e);
     }
+    if (allHaveIds) {
+        std::stable_sort(out.begin(), out.end(), [](const Event &a, const Event &b) { return a.id < b.id; });
+    }
+    for (size_t i = 0; i < out.size(); ++i) out[i].id = i;
     return out;
 }
 

@@ -15,6 +15,23 @@ namespace {
 
 bool g_skipFlags = false;
 
+// Every copy into a window and every load out of one passes here, so that a protocol recorder (host_trace.cpp) sees
+// them; the flag stores and waits report themselves from tilexr_sync.cuh.
+void WindowStore(void *dst, const void *src, uint64_t bytes)
+{
+    if (HostTraceHooks *h = HostTraceSlot()) h->onCopy(h->ctx, dst, src, bytes);
+    std::memcpy(dst, src, bytes);
+}
+void WindowLoad(void *dst, const void *src, uint64_t bytes)
+{
+    if (HostTraceHooks *h = HostTraceSlot()) h->onRead(h->ctx, src, bytes);
+    std::memcpy(dst, src, bytes);
+}
+void WindowRead(const void *src, uint64_t bytes)
+{
+    if (HostTraceHooks *h = HostTraceSlot()) h->onRead(h->ctx, src, bytes);
+}
+
 struct HostCtx {
     CommArgs *args = nullptr;
     Waiter w;
@@ -39,6 +56,7 @@ int Begin(TileXRCommPtr comm, int op, int64_t count, HostCtx *c)
     c->R = args->rankSize;
     c->w = MakeWaiter(args, magic, 0);
     c->epoch = c->w.epoch;
+    if (HostTraceHooks *h = HostTraceSlot()) h->epoch = c->epoch;
     args->dfx[TILEXR_DFX_MAGIC] = magic;
     args->dfx[TILEXR_DFX_OP] = op;
     args->dfx[TILEXR_DFX_COUNT_ARG] = count;
@@ -94,7 +112,7 @@ int TileXRHostAllGather(const void *send, void *recv, uint64_t bytes, uint32_t t
         const uint64_t n = std::min<uint64_t>(tileBytes, bytes - off);
         for (int i = 1; i < c.R; ++i) {
             const int peer = (c.rank + i) % c.R;
-            std::memcpy(DataHalf(c.args, peer, c.epoch) + c.rank * pairStride + off, in + off, n);
+            WindowStore(DataHalf(c.args, peer, c.epoch) + c.rank * pairStride + off, in + off, n);
             if (!g_skipFlags) {
                 SetFlag(FlagSlot(c.args, peer, TILEXR_FLAG_DATA_BASE + static_cast<int64_t>(c.rank) * TILEXR_FLAGS_PER_PAIR + t),
                         c.epoch, static_cast<uint32_t>(t + 1));
@@ -110,7 +128,7 @@ int TileXRHostAllGather(const void *send, void *recv, uint64_t bytes, uint32_t t
             const int src = (c.rank + i) % c.R;
             const int64_t slot = TILEXR_FLAG_DATA_BASE + static_cast<int64_t>(src) * TILEXR_FLAGS_PER_PAIR + t;
             if (!WaitFlagGE(c.w, FlagSlot(c.args, c.rank, slot), static_cast<uint32_t>(t + 1), src, slot)) break;
-            std::memcpy(out + src * bytes + off, DataHalf(c.args, c.rank, c.epoch) + src * pairStride + off, n);
+            WindowLoad(out + src * bytes + off, DataHalf(c.args, c.rank, c.epoch) + src * pairStride + off, n);
         }
     }
     return End(c);
@@ -127,7 +145,7 @@ int TileXRHostAllReduceSumF32(const float *send, float *recv, uint64_t count, Ti
     if (bytes > pairStride) return TILEXR_ERROR_PARA_CHECK_FAIL;
     for (int i = 1; i < c.R; ++i) {
         const int peer = (c.rank + i) % c.R;
-        std::memcpy(DataHalf(c.args, peer, c.epoch) + c.rank * pairStride, send, bytes);
+        WindowStore(DataHalf(c.args, peer, c.epoch) + c.rank * pairStride, send, bytes);
         if (!g_skipFlags) {
             SetFlag(FlagSlot(c.args, peer, TILEXR_FLAG_DATA_BASE + static_cast<int64_t>(c.rank) * TILEXR_FLAGS_PER_PAIR), c.epoch, 1);
         }
@@ -138,6 +156,9 @@ int TileXRHostAllReduceSumF32(const float *send, float *recv, uint64_t count, Ti
         WaitFlagGE(c.w, FlagSlot(c.args, c.rank, slot), 1, s, slot);
     }
     if (c.w.ok()) {
+        for (int s = 0; s < c.R; ++s) {
+            if (s != c.rank) WindowRead(DataHalf(c.args, c.rank, c.epoch) + s * pairStride, bytes);
+        }
         // rank order 0..R-1, like the CUDA kernels
         for (uint64_t i = 0; i < count; ++i) {
             float acc = 0.f;
@@ -186,7 +207,7 @@ int TileXRHostEpDispatch(const float *x, const int32_t *expertIds, int64_t bs, i
     // 2. publish counts
     for (int i = 0; i < c.R; ++i) {
         const int peer = (c.rank + i) % c.R;
-        std::memcpy(DataHalf(c.args, peer, c.epoch) + countOff + static_cast<uint64_t>(c.rank) * E * 4, count.data(), E * 4);
+        WindowStore(DataHalf(c.args, peer, c.epoch) + countOff + static_cast<uint64_t>(c.rank) * E * 4, count.data(), E * 4);
         if (!g_skipFlags) {
             SetFlag(FlagSlot(c.args, peer, TILEXR_FLAG_OP_BASE + static_cast<int64_t>(c.rank) * TILEXR_FLAGS_PER_PAIR + TILEXR_FLAGS_PER_PAIR - 1),
                     c.epoch, 1);
@@ -197,6 +218,7 @@ int TileXRHostEpDispatch(const float *x, const int32_t *expertIds, int64_t bs, i
         if (!WaitFlagGE(c.w, FlagSlot(c.args, c.rank, slot), 1, s, slot)) return End(c);
     }
     const int32_t *matrix = reinterpret_cast<const int32_t *>(DataHalf(c.args, c.rank, c.epoch) + countOff);
+    WindowRead(matrix, static_cast<uint64_t>(c.R) * E * 4);
     std::vector<int64_t> tot(E, 0), dstRow(E, 0);
     for (int e = 0; e < E; ++e) {
         for (int s = 0; s < c.R; ++s) tot[e] += matrix[s * E + e];
@@ -224,9 +246,9 @@ int TileXRHostEpDispatch(const float *x, const int32_t *expertIds, int64_t bs, i
             const int dst = e / perRank;
             const int64_t r = dstRow[e] + pos[t * topK + k];
             uint8_t *half = DataHalf(c.args, dst, c.epoch);
-            std::memcpy(half + payloadOff + r * rowBytes, x + t * h, rowBytes);
+            WindowStore(half + payloadOff + r * rowBytes, x + t * h, rowBytes);
             const int32_t tuple[4] = {c.rank, static_cast<int32_t>(t), static_cast<int32_t>(k), e};
-            std::memcpy(half + assistOff + r * 16, tuple, 16);
+            WindowStore(half + assistOff + r * 16, tuple, 16);
         }
     }
     if (!g_skipFlags) {
@@ -251,8 +273,8 @@ int TileXRHostEpDispatch(const float *x, const int32_t *expertIds, int64_t bs, i
         expertTokenNumsOut[le] = tot[e];
     }
     const uint8_t *half = DataHalf(c.args, c.rank, c.epoch);
-    std::memcpy(expandXOut, half + payloadOff, rows * rowBytes);
-    std::memcpy(assistOut, half + assistOff, rows * 16);
+    WindowLoad(expandXOut, half + payloadOff, rows * rowBytes);
+    WindowLoad(assistOut, half + assistOff, rows * 16);
     if (recvTotalOut != nullptr) *recvTotalOut = static_cast<int32_t>(rows);
     return End(c);
 }
@@ -275,7 +297,7 @@ int TileXRHostEpCombine(const float *expertOut, const int32_t *assist, int32_t r
         const int src = assist[r * 4];
         const int64_t slot = static_cast<int64_t>(assist[r * 4 + 1]) * topK + assist[r * 4 + 2];
         if (src < 0 || src >= c.R || slot < 0 || slot >= bs * topK) continue;
-        std::memcpy(DataHalf(c.args, src, c.epoch) + slot * rowBytes, expertOut + static_cast<int64_t>(r) * h, rowBytes);
+        WindowStore(DataHalf(c.args, src, c.epoch) + slot * rowBytes, expertOut + static_cast<int64_t>(r) * h, rowBytes);
         if (!g_skipFlags) SetFlag(FlagSlot(c.args, src, TILEXR_FLAG_SLOT_BASE + slot), c.epoch, 1);
     }
     const uint8_t *half = DataHalf(c.args, c.rank, c.epoch);
@@ -286,9 +308,12 @@ int TileXRHostEpCombine(const float *expertOut, const int32_t *assist, int32_t r
             const int e = expertIds != nullptr ? expertIds[t * topK + k] : 0;
             if (e < 0 || e >= moeExpertNum) continue;
             const int64_t slot = t * topK + k;
-            if (!WaitFlagGE(c.w, FlagSlot(c.args, c.rank, TILEXR_FLAG_SLOT_BASE + slot), 1, -1, slot)) break;
+            // the row comes from the rank that holds expert e
+            const int producer = static_cast<int>(e / std::max<int64_t>(1, moeExpertNum / c.R));
+            if (!WaitFlagGE(c.w, FlagSlot(c.args, c.rank, TILEXR_FLAG_SLOT_BASE + slot), 1, producer, slot)) break;
             const float wgt = expertScales != nullptr ? expertScales[slot] : 1.0f;
             const float *row = reinterpret_cast<const float *>(half + slot * rowBytes);
+            WindowRead(row, rowBytes);
             for (int64_t j = 0; j < h; ++j) y[j] = wgt * row[j] + y[j];
         }
     }

@@ -29,6 +29,28 @@
 
 namespace tilexr {
 
+// ---- host builds only: observation points for a protocol trace --------------------------------
+// When the flag and window primitives below run on a CPU (the host-memory communicator), a recorder can watch
+// them: every flag store, every wait that ends, every copy into a window and every read out of one.  The protocol
+// checker analyses what the PRODUCTION code did, not a model of it (the reference replays its kernel headers through
+// shims for the same purpose: tools/checker/shim/tilexr/checker/collective_trace_shim.h).  A null slot costs one
+// thread-local load per call; device code has none of this.
+#if !TXR_ON_DEVICE
+struct HostTraceHooks {
+    void (*onFlagStore)(void *ctx, const void *addr, uint64_t value);                  // BEFORE the store is performed
+    void (*onFlagWait)(void *ctx, const void *addr, uint64_t want, uint64_t seen, int peer, int satisfied);   // when the wait ends
+    void (*onCopy)(void *ctx, const void *dst, const void *src, uint64_t bytes);       // BEFORE a copy into a window
+    void (*onRead)(void *ctx, const void *src, uint64_t bytes);                        // a read out of a window
+    void *ctx;
+    uint64_t epoch;                                                                    // of the launch that is running (set by its prologue)
+};
+inline HostTraceHooks *&HostTraceSlot()
+{
+    static thread_local HostTraceHooks *hooks = nullptr;
+    return hooks;
+}
+#endif
+
 // ---- 64-bit flag words --------------------------------------------------------------------
 
 TXR_D void st_release_sys_u64(uint64_t *p, uint64_t v)
@@ -36,6 +58,7 @@ TXR_D void st_release_sys_u64(uint64_t *p, uint64_t v)
 #if TXR_ON_DEVICE
     asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 #else
+    if (HostTraceHooks *h = HostTraceSlot()) h->onFlagStore(h->ctx, p, v);
     __atomic_store_n(p, v, __ATOMIC_RELEASE);
 #endif
 }
@@ -45,6 +68,7 @@ TXR_D void st_relaxed_sys_u64(uint64_t *p, uint64_t v)
 #if TXR_ON_DEVICE
     asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 #else
+    if (HostTraceHooks *h = HostTraceSlot()) h->onFlagStore(h->ctx, p, v);
     __atomic_store_n(p, v, __ATOMIC_RELAXED);
 #endif
 }

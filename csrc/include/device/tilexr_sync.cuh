@@ -107,18 +107,35 @@ TXR_D bool AbortRaised(const Waiter &w)
 
 // Spin until `*flag >= MakeFlag(epoch, value)`.  Returns false (and records why) when the
 // budget CommArgs::waitTimeoutNs runs out or the abort word is raised.
+// Host builds tell a protocol recorder how a wait ended (tilexr_platform.cuh); device builds compile this away.
+TXR_D void TraceWaitEnd(const uint64_t *flag, uint64_t want, uint64_t seen, int peer, bool satisfied)
+{
+#if !TXR_ON_DEVICE
+    if (HostTraceHooks *h = HostTraceSlot()) h->onFlagWait(h->ctx, flag, want, seen, peer, satisfied ? 1 : 0);
+#else
+    (void)flag; (void)want; (void)seen; (void)peer; (void)satisfied;
+#endif
+}
+
 TXR_D bool WaitFlagGE(Waiter &w, const uint64_t *flag, uint32_t value, int peer, int64_t slot, int failCode)
 {
     if (!w.ok()) return false;
     const uint64_t want = MakeFlag(w.epoch, value);
     uint64_t seen = ld_acquire_sys_u64(flag);
-    if (seen >= want) return true;
+    if (seen >= want) {
+        TraceWaitEnd(flag, want, seen, peer, true);
+        return true;
+    }
     uint32_t polls = 0;
     for (;;) {
         seen = ld_acquire_sys_u64(flag);
-        if (seen >= want) return true;
+        if (seen >= want) {
+            TraceWaitEnd(flag, want, seen, peer, true);
+            return true;
+        }
         if ((++polls & 63u) == 0) {
             if (AbortRaised(w)) {
+                TraceWaitEnd(flag, want, seen, peer, false);
                 RaiseFailure(w, TileXR::TILEXR_DEV_ABORTED, peer, slot, want, seen);
                 return false;
             }
@@ -126,6 +143,7 @@ TXR_D bool WaitFlagGE(Waiter &w, const uint64_t *flag, uint32_t value, int peer,
             if (w.deadline == 0) {
                 w.deadline = t + w.args->waitTimeoutNs;
             } else if (t > w.deadline) {
+                TraceWaitEnd(flag, want, seen, peer, false);
                 RaiseFailure(w, failCode, peer, slot, want, seen);
                 return false;
             }
@@ -194,9 +212,13 @@ TXR_D bool WaitPeerFinished(Waiter &w, int peer, uint32_t finishedEpoch)
     uint32_t polls = 0;
     for (;;) {
         const uint64_t seen = ld_acquire_sys_u64(done);
-        if (seen >= want) return true;
+        if (seen >= want) {
+            TraceWaitEnd(done, want, seen, peer, true);
+            return true;
+        }
         if ((++polls & 63u) == 0) {
             if (AbortRaised(w)) {
+                TraceWaitEnd(done, want, seen, peer, false);
                 RaiseFailure(w, TileXR::TILEXR_DEV_ABORTED, peer, TILEXR_CTRL_DONE_WORD + peer, want, seen);
                 return false;
             }
@@ -204,6 +226,7 @@ TXR_D bool WaitPeerFinished(Waiter &w, int peer, uint32_t finishedEpoch)
             if (w.deadline == 0) {
                 w.deadline = t + w.args->waitTimeoutNs;
             } else if (t > w.deadline) {
+                TraceWaitEnd(done, want, seen, peer, false);
                 RaiseFailure(w, TileXR::TILEXR_DEV_REUSE_GUARD_TIMEOUT, peer, TILEXR_CTRL_DONE_WORD + peer, want, seen);
                 return false;
             }

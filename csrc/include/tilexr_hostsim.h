@@ -30,6 +30,13 @@ int TileXRHostEpCombine(const float *expertOut, const int32_t *assist, int32_t r
 // into their wait budget (failure-detection tests make the failure on the host).
 int TileXRHostInjectSkipFlags(int enable);
 
+// Protocol trace of what the host kernels above (and the flag primitives under them) do on this rank, in the event
+// format of the protocol checker, one JSON object per line.  Event ids are global over the ranks of the communicator
+// (one counter in rank 0's window), so the ranks' files concatenate into one trace for TileXRCheckerCheckTrace /
+// `tilexr_checker --trace`.  Start and stop on the thread that runs the kernels.
+int TileXRHostTraceStart(TileXRCommPtr comm, const char *path);
+int TileXRHostTraceStop(TileXRCommPtr comm, uint64_t *eventCount /* may be null */);
+
 #ifdef __cplusplus
 }
 #endif

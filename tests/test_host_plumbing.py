@@ -66,6 +66,35 @@ def _worker(rank, world, port, scenario, result_queue):
                     for k in range(K):
                         yref[t] += w[t, k] * (x[t] * 2.0 + 1.0)
                 assert torch.allclose(y, yref, rtol=1e-5, atol=1e-5), (y - yref).abs().max()
+        elif scenario in ("traced", "traced_lost_flag"):
+            # the production flag primitives and host kernels, recorded while they run between two processes, judged
+            # by the protocol checker
+            from tilexr_b200.tools import checker
+            trace_dir = os.environ["TILEXR_TEST_TRACE_DIR"]
+            path = os.path.join(trace_dir, f"rank{rank}.jsonl")
+            if scenario == "traced":
+                bs, h, E, K = 16, 64, 4, 2
+                x = torch.randn(bs, h, generator=g)
+                ids, w = oracle.routing_topk_ref(torch.randn(bs, E, generator=g), K, score_func=0, renormalize=True)
+                big = torch.randn(3 * 4096, generator=g)
+                out = torch.empty(world * big.numel())
+                with checker.record_host_trace(comm, path):
+                    for _ in range(3):                        # both data halves and the reuse guard
+                        txr._C.host_all_gather(comm, big, out, 16384)
+                    txr._C.host_all_reduce(comm, big[:1024].contiguous())
+                    expand, assist, nums, counts, total = txr._C.host_ep_dispatch(comm, x, ids, E, bs * world * K)
+                    txr._C.host_ep_combine(comm, expand[:total].contiguous(), assist, total, ids, w, E)
+            else:
+                comm.set_wait_timeout_ms(300)
+                x = torch.ones(4096)
+                out = torch.empty(world * 4096)
+                with checker.record_host_trace(comm, path):
+                    if rank == 1:
+                        txr._C.host_inject_skip_flags(True)
+                        txr._C.host_all_gather(comm, x, out, 4096)
+                    else:
+                        with pytest.raises(RuntimeError):
+                            txr._C.host_all_gather(comm, x, out, 4096)
         elif scenario == "lost_flag":
             # rank 1 never raises its flags: rank 0 must give up within the budget and say why
             x = torch.ones(4096)
@@ -87,6 +116,40 @@ def _worker(rank, world, port, scenario, result_queue):
         result_queue.put((rank, "ok"))
     except Exception:
         result_queue.put((rank, traceback.format_exc()))
+
+
+def _traced(scenario, tmp_path, world=2):
+    os.environ["TILEXR_TEST_TRACE_DIR"] = str(tmp_path)
+    try:
+        _run(scenario, world)
+    finally:
+        os.environ.pop("TILEXR_TEST_TRACE_DIR", None)
+    return [str(tmp_path / f"rank{r}.jsonl") for r in range(world)]
+
+
+def test_production_protocol_trace_passes_the_checker(tmp_path):
+    from tilexr_b200.tools import checker
+    paths = _traced("traced", tmp_path)
+    text = "".join(open(p).read() for p in paths)
+    kinds = [line.split('"kind": "')[1].split('"')[0] for line in text.splitlines()]
+    assert kinds.count("FlagStore") > 20 and kinds.count("FlagWait") > 20 and kinds.count("Copy") > 10 and kinds.count("Read") > 10
+    assert checker.check_trace_files(paths) == []
+    # the same run with rank 1's flag stores taken out of the record: the checker must miss them ...
+    lines = text.splitlines(keepends=True)
+    dropped = [l for l in lines if not ('"kind": "FlagStore"' in l and '"rank": 1,' in l)]
+    names = {f[0] for f in checker.check_trace("".join(dropped))}
+    assert "FLAG_NO_PRODUCER" in names
+    # ... and with rank 0's waits taken out, its reads of rank 1's data are no longer ordered after the copies
+    unwaited = [l for l in lines if not ('"kind": "FlagWait"' in l and '"rank": 0,' in l)]
+    names = {f[0] for f in checker.check_trace("".join(unwaited))}
+    assert "READ_BEFORE_COPY" in names
+
+
+def test_production_run_with_a_lost_flag_is_reported_by_the_checker(tmp_path):
+    from tilexr_b200.tools import checker
+    paths = _traced("traced_lost_flag", tmp_path)
+    findings = checker.check_trace_files(paths)
+    assert any(f[0] == "FLAG_NO_PRODUCER" and f[1] == 0 for f in findings), findings
 
 
 def _run(scenario, world=2):

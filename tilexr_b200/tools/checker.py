@@ -1,11 +1,14 @@
 """Python front end of the protocol checker (csrc/checker): run modelled protocols on the CPU,
-inject single-step faults, analyse event traces.
+inject single-step faults, analyse event traces -- the checker's own, or what the production flag
+primitives and host kernels did in a real multi-process run (`record_host_trace`).
 
     python -m tilexr_b200.tools.checker --op ep_dispatch --ranks 4 --experts 8 --out report/
+    python -m tilexr_b200.tools.checker --trace rank0.jsonl,rank1.jsonl
 """
 from __future__ import annotations
 
 import argparse
+import contextlib
 import sys
 
 from .. import _C
@@ -25,6 +28,23 @@ def check_trace(jsonl: str) -> list:
     return list(_C.checker_check_trace(jsonl))
 
 
+@contextlib.contextmanager
+def record_host_trace(comm, path: str):
+    """Record what this rank's host kernels (`_C.host_*` on a `host_memory=True` communicator) and the flag
+    primitives below them do while the block runs, as checker events in `path`.  Event ids are global over the
+    ranks, so `check_trace_files` of all ranks' files judges the run as a whole."""
+    _C.host_trace_start(comm, path)
+    try:
+        yield
+    finally:
+        _C.host_trace_stop(comm)
+
+
+def check_trace_files(paths) -> list:
+    """Ordering analysis of one run recorded by several ranks (one file each)."""
+    return check_trace("".join(open(p).read() for p in paths))
+
+
 def main(argv=None) -> int:
     p = argparse.ArgumentParser(description=__doc__)
     p.add_argument("--op", default="allgather")
@@ -39,12 +59,12 @@ def main(argv=None) -> int:
     p.add_argument("--launches", type=int, default=1)
     p.add_argument("--scheduler", default="round_robin")
     p.add_argument("--out", default="")
-    p.add_argument("--trace", default="")
+    p.add_argument("--trace", default="", help="event file(s) to analyse, comma separated (one per rank of a recorded run)")
     for name in INJECTIONS:
         p.add_argument("--inject-" + name.replace("_", "-"), action="store_true")
     a = p.parse_args(argv)
     if a.trace:
-        findings = check_trace(open(a.trace).read())
+        findings = check_trace_files(a.trace.split(","))
         for f in findings:
             print(*f)
         return 1 if findings else 0
