@@ -36,6 +36,7 @@
 #include "device/tilexr_perf_trace.cuh"
 #include "device/tilexr_rma.cuh"
 #include "device/tilexr_sync.cuh"
+#include "device/tilexr_convert.cuh"
 #include "ep_kernels.cuh"
 #include "tilexr_ep.h"
 
@@ -59,40 +60,6 @@ __device__ __forceinline__ float WarpSum(float v)
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
     return v;
-}
-
-// 8 halfs/bfloats packed in 16 bytes -> 8 floats
-__device__ __forceinline__ void Unpack8(const Vec16 &v, bool bf16, float *f)
-{
-    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        if (bf16) {
-            f[2 * i] = __uint_as_float(w[i] << 16);
-            f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
-        } else {
-            const __half2 h2 = *reinterpret_cast<const __half2 *>(&w[i]);
-            const float2 f2 = __half22float2(h2);
-            f[2 * i] = f2.x;
-            f[2 * i + 1] = f2.y;
-        }
-    }
-}
-
-__device__ __forceinline__ Vec16 Pack8(const float *f, bool bf16)
-{
-    uint32_t w[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        if (bf16) {
-            const __nv_bfloat162 b = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
-            w[i] = *reinterpret_cast<const uint32_t *>(&b);
-        } else {
-            const __half2 h2 = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
-            w[i] = *reinterpret_cast<const uint32_t *>(&h2);
-        }
-    }
-    return Vec16{w[0], w[1], w[2], w[3]};
 }
 
 __device__ __forceinline__ uint32_t Fp8x4(float a, float b, float c, float d)

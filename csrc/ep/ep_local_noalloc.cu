@@ -5,10 +5,13 @@
 //   2. after a barrier among the blocks, each block derives the first output row of every
 //      expert and its own offset inside it, then copies its rows and writes the assist tuples.
 #include <algorithm>
+#include <atomic>
 #include <cstdio>
+#include <mutex>
 #include <cuda_runtime_api.h>
 
 #include "device/tilexr_rma.cuh"
+#include "device/tilexr_route_rank.cuh"
 #include "tilexr_noalloc.h"
 #include "tilexr_types.h"
 
@@ -21,9 +24,11 @@ constexpr unsigned WARPS = THREADS / 32;
 constexpr int MAX_ROUTES_PER_BLOCK = 4096;
 constexpr int MAX_DEVICES = 64;
 
+// `barrier` holds (call number << 32) | blocks that arrived.  Its first arriver of a call finds another call's number
+// (or a count that is already complete or poisoned) and restarts the word, so nothing has to be put back at the end
+// of a call and a call whose barrier gave up leaves nothing that the next call could trip over.
 struct Scratch {
-    uint32_t barrierCount;
-    uint32_t barrierGen;
+    unsigned long long barrier;
     int32_t status;
     int32_t pad[61];
     int32_t blockCounts[TILEXR_NOALLOC_MAX_BLOCKS][TILEXR_NOALLOC_MAX_EXPERTS];
@@ -44,7 +49,10 @@ struct Args {
     int32_t bs, topK, experts;
     uint32_t rowBytes;
     uint32_t tokensPerBlock;
+    uint32_t call;            // number of this call on its device, from 1
 };
+
+constexpr uint32_t BARRIER_POISON = 0xffffffffu;
 
 __global__ void __launch_bounds__(THREADS) LocalDispatchKernel(const Args a)
 {
@@ -71,15 +79,8 @@ __global__ void __launch_bounds__(THREADS) LocalDispatchKernel(const Args a)
         sExpert[i] = e;
     }
     __syncthreads();
-    for (int i = tid; i < nRoutes; i += blockDim.x) {
-        const int e = sExpert[i];
-        int r = 0;
-        if (e >= 0) {
-            for (int j = 0; j < i; ++j) r += sExpert[j] == e ? 1 : 0;
-            atomicAdd(&sHist[e], 1);
-        }
-        sRank[i] = r;
-    }
+    // rank of each route among the block's routes to its expert, and the per-expert counts: one warp, linear time
+    if (warp == 0) RankRoutesByWarp(sExpert, sRank, sHist, nRoutes, lane);
     __syncthreads();
     for (int e = tid; e < E; e += blockDim.x) sc->blockCounts[blockIdx.x][e] = sHist[e];
 
@@ -88,22 +89,33 @@ __global__ void __launch_bounds__(THREADS) LocalDispatchKernel(const Args a)
     __shared__ int sOk;
     if (tid == 0) {
         sOk = 1;
+        __threadfence();              // this block's counts before its arrival
+        // arrive: continue this call's count, or restart a word that another call (or a poisoned one) left
+        unsigned long long seen = *reinterpret_cast<volatile unsigned long long *>(&sc->barrier);
+        for (;;) {
+            const bool mine = static_cast<uint32_t>(seen >> 32) == a.call && static_cast<uint32_t>(seen) < static_cast<uint32_t>(G);
+            const unsigned long long next = mine ? seen + 1ull : ((static_cast<unsigned long long>(a.call) << 32) | 1ull);
+            const unsigned long long old = atomicCAS(&sc->barrier, seen, next);
+            if (old == seen) break;
+            seen = old;
+        }
         __threadfence();
-        const uint32_t gen = ld_acquire_gpu_u32(&sc->barrierGen);
-        if (atom_add_acq_rel_gpu_u32(&sc->barrierCount, 1) == static_cast<uint32_t>(G) - 1) {
-            st_release_gpu_u32(&sc->barrierCount, 0);      // back to zero for the next call
-            st_release_gpu_u32(&sc->barrierGen, gen + 1);
-        } else {
-            const uint64_t deadline = now_ns() + 2000000000ull;
-            uint32_t polls = 0;
-            while (ld_acquire_gpu_u32(&sc->barrierGen) == gen) {
-                if ((++polls & 255u) == 0 && now_ns() > deadline) {
-                    sOk = 0;
-                    atomicExch(&sc->status, 5);
-                    break;
-                }
+        const unsigned long long full = (static_cast<unsigned long long>(a.call) << 32) | static_cast<uint32_t>(G);
+        const uint64_t deadline = now_ns() + 2000000000ull;
+        uint32_t polls = 0;
+        for (;;) {
+            const unsigned long long v = *reinterpret_cast<volatile unsigned long long *>(&sc->barrier);
+            if (v == full) break;
+            const bool poisoned = static_cast<uint32_t>(v >> 32) == a.call && static_cast<uint32_t>(v) == BARRIER_POISON;
+            if (poisoned || ((++polls & 255u) == 0 && now_ns() > deadline)) {
+                // give up, and make every other block of this call give up at once instead of after its own two seconds
+                atomicExch(&sc->barrier, (static_cast<unsigned long long>(a.call) << 32) | BARRIER_POISON);
+                sOk = 0;
+                atomicExch(&sc->status, 5);
+                break;
             }
         }
+        __threadfence();
     }
     __syncthreads();
     if (sOk == 0) return;
@@ -145,7 +157,22 @@ __global__ void __launch_bounds__(THREADS) LocalDispatchKernel(const Args a)
     }
 }
 
+// Per device: the scratch array's address (looked up once, under the flag) and the number of calls made.
 Scratch *g_devicePtr[MAX_DEVICES] = {};
+std::once_flag g_deviceOnce[MAX_DEVICES];
+std::atomic<uint32_t> g_deviceCalls[MAX_DEVICES];
+
+void LookUpScratch(int dev)
+{
+    void *p = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&p, g_scratchBytes);
+    if (e != cudaSuccess || p == nullptr) {
+        std::fprintf(stderr, "[TileXR] cudaGetSymbolAddress(scratch) failed: %s\n", cudaGetErrorString(e));
+        return;
+    }
+    if (cudaMemset(p, 0, 256) != cudaSuccess) return;     // barrier word and status
+    g_devicePtr[dev] = static_cast<Scratch *>(p);
+}
 
 } // namespace
 
@@ -172,17 +199,10 @@ int TileXRMoeLocalDispatchNoAlloc(const void *x, const int32_t *expertIds, int64
     }
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return TILEXR_ERROR_RUNTIME;
-    if (g_devicePtr[dev] == nullptr) {
-        // once per device, with that device current
-        void *p = nullptr;
-        const cudaError_t e = cudaGetSymbolAddress(&p, g_scratchBytes);
-        if (e != cudaSuccess || p == nullptr) {
-            std::fprintf(stderr, "[TileXR] cudaGetSymbolAddress(scratch) failed: %s\n", cudaGetErrorString(e));
-            return TILEXR_ERROR_RUNTIME;
-        }
-        if (cudaMemset(p, 0, 256) != cudaSuccess) return TILEXR_ERROR_RUNTIME;     // barrier words and status
-        g_devicePtr[dev] = static_cast<Scratch *>(p);
-    }
+    // once per device, with that device current; host threads that make their first calls together wait for the one
+    // that does the lookup
+    std::call_once(g_deviceOnce[dev], LookUpScratch, dev);
+    if (g_devicePtr[dev] == nullptr) return TILEXR_ERROR_RUNTIME;
     // grid: blocks must be co-resident (they meet at a barrier)
     unsigned grid = static_cast<unsigned>(std::min<int64_t>(TILEXR_NOALLOC_MAX_BLOCKS, (bs + 15) / 16));
     if (grid == 0) grid = 1;
@@ -224,6 +244,7 @@ int TileXRMoeLocalDispatchNoAlloc(const void *x, const int32_t *expertIds, int64
     a.experts = static_cast<int32_t>(moeExpertNum);
     a.rowBytes = static_cast<uint32_t>(h * 2);
     a.tokensPerBlock = tokensPerBlock;
+    a.call = g_deviceCalls[dev].fetch_add(1, std::memory_order_relaxed) + 1u;
     void *params[] = {&a};
     const cudaError_t e = cudaLaunchCooperativeKernel(reinterpret_cast<const void *>(&LocalDispatchKernel), dim3(grid), dim3(THREADS),
                                                       params, smem, static_cast<cudaStream_t>(stream));

@@ -193,6 +193,63 @@ int TileXRMatmul(const void *a, const void *b, void *c, int64_t m, int64_t n, in
     return TILEXR_SUCCESS;
 }
 
+int TileXRGroupedMatmul(const void *a, const void *b, const int64_t *groupRows, void *c, int64_t maxRows, int64_t n, int64_t k,
+                        int64_t groups, TileXRDataType dtype, int epilogue, int32_t *status, TileXRStream stream)
+{
+    int ret = CheckShape(a, b, c, maxRows, n, k, dtype);
+    if (ret != TILEXR_SUCCESS) return ret;
+    if ((epilogue != GEMM_EPI_STORE && epilogue != GEMM_EPI_SWIGLU) || (epilogue == GEMM_EPI_SWIGLU && n % 16 != 0)) {
+        TILEXR_LOG(ERROR) << "grouped matmul: epilogue 0 (store) or 1 (SwiGLU over interleaved gate / up rows, N a multiple of 16)";
+        return TILEXR_ERROR_PARA_CHECK_FAIL;
+    }
+    if (groupRows == nullptr || groups <= 0 || groups * n > INT32_MAX || maxRows > INT32_MAX - 512) {
+        TILEXR_LOG(ERROR) << "grouped matmul: a device array of row counts, at least one group, groups * N and rows within int32";
+        return TILEXR_ERROR_PARA_CHECK_FAIL;
+    }
+    const bool bf16 = dtype == TILEXR_DATA_TYPE_BFP16;
+    GemmArgs g;
+    std::memset(&g, 0, sizeof(g));
+    ret = MakeMap(&g.tmapA, a, maxRows, k, GEMM_BM, bf16);
+    if (ret != TILEXR_SUCCESS) return ret;
+    ret = MakeMap(&g.tmapB, b, groups * n, k, GEMM_BN / 2, bf16);
+    if (ret != TILEXR_SUCCESS) return ret;
+    g.tmapALocal = g.tmapA;
+    g.c = static_cast<uint8_t *>(c);
+    g.status = status;
+    g.mode = GEMM_GROUPED;
+    g.isBf16 = bf16 ? 1u : 0u;
+    g.groupRows = groupRows;
+    g.groupsTotal = static_cast<int32_t>(groups);
+    g.epilogue = epilogue;
+    FillTiling(&g, maxRows, n, k);
+    g.rasterGroup = static_cast<int32_t>(std::max<long>(1, EnvLong("TILEXR_GEMM_GROUP", 8)));
+    int sms = 0;
+    ret = SmCount(&sms);
+    if (ret != TILEXR_SUCCESS) return ret;
+    static std::once_flag pairOnce;
+    std::call_once(pairOnce, [] {
+        cudaFuncSetAttribute(GemmPairKernel(), cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(GEMM_PAIR_SMEM_BYTES));
+    });
+    // The row counts stay on the device, so the number of tiles is not known here: every launch gets as many CTA pairs
+    // as could be busy if all rows fell into its groups, and pairs without a tile leave at once.
+    for (int64_t base = 0; base < groups; base += GEMM_MAX_GROUPS) {
+        g.groupBase = static_cast<int32_t>(base);
+        g.groups = static_cast<int32_t>(std::min<int64_t>(GEMM_MAX_GROUPS, groups - base));
+        const int64_t tilesAtMost = ((maxRows + 2 * GEMM_BM - 1) / (2 * GEMM_BM) + g.groups) * g.nBlocks;
+        const int pairs = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(tilesAtMost, EnvLong("TILEXR_GEMM_CTAS", sms) / 2)));
+        void *params[] = {&g};
+        const cudaError_t e = cudaLaunchKernel(GemmPairKernel(), dim3(2 * pairs), dim3(GEMM_THREADS), params, GEMM_PAIR_SMEM_BYTES,
+                                               static_cast<cudaStream_t>(stream));
+        if (e != cudaSuccess) {
+            TILEXR_LOG(ERROR) << "grouped matmul launch failed: " << cudaGetErrorString(e);
+            cudaGetLastError();
+            return TILEXR_ERROR_RUNTIME;
+        }
+        NoteLaunch();
+    }
+    return TILEXR_SUCCESS;
+}
+
 int TileXRMatmulFp8(const void *a, const void *b, void *c, int64_t m, int64_t n, int64_t k, TileXRDataType inDtype,
                     TileXRDataType outDtype, float alpha, int32_t *status, TileXRStream stream)
 {

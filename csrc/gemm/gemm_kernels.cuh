@@ -31,7 +31,9 @@ enum GemmMode : int32_t {
     GEMM_PLAIN = 0,
     GEMM_ALL_GATHER = 1,      // A is gathered: local shard + staging filled by peers
     GEMM_REDUCE_SCATTER = 2,  // C is reduce-scattered: partial tiles pushed to the row owner
+    GEMM_GROUPED = 3,         // rows of A grouped by expert, one weight per group, row counts read on the device
 };
+constexpr int GEMM_MAX_GROUPS = 64;      // groups of one launch (their row and tile offsets live in shared memory)
 
 struct GemmArgs {
     CUtensorMap tmapA;        // A [M, K] row-major (all-gather: the staging buffer [R * shardRows, K])
@@ -61,7 +63,18 @@ struct GemmArgs {
     // (kind::f8f6f4) covers 32 of them; C = alpha * A x B^T is written in the 16-bit type named by isBf16.
     int32_t fp8Format;
     float alpha;
+    // Grouped mode (CTA-pair kernel): A [M, K] holds the rows of group 0, then group 1, ...; groupRows[g] of them (a
+    // device array, so that no host round trip separates the kernel that counted the rows from this one).  B is
+    // [groupsTotal * N, K], the weight of group g in rows [g * N, (g + 1) * N); C [M, N].  One launch covers groups
+    // [groupBase, groupBase + groups).
+    const int64_t *groupRows;
+    int32_t groups, groupBase, groupsTotal;
+    // Epilogue of the CTA-pair kernel (plain and grouped modes): 0 stores the product; 1 treats the columns as
+    // (gate, up) pairs -- weight row 2i the gate row i, row 2i+1 the up row i -- and stores silu(gate) * up, so C is
+    // [M, N / 2] and the [M, N] intermediate of a SwiGLU feed-forward never reaches memory.
+    int32_t epilogue;
 };
+enum GemmEpilogue : int32_t { GEMM_EPI_STORE = 0, GEMM_EPI_SWIGLU = 1 };
 
 // Block-scaled fp8 GEMM (gemm_tcgen05_fp8_block.cu): warp 0 TMA, warp 1 MMA, warps 4-11 fold the scratch accumulators.
 constexpr unsigned GEMM_FP8_BLOCK_THREADS = 384;

@@ -225,11 +225,36 @@ struct PairTile {
     int nBlock;
     int shard;      // owner / source rank of the rows (fused modes)
     int mLocalPair; // 256-row block inside the shard
+    int row0;       // grouped mode: first row of the pair's 256-row block in A and C
+    int rowEnd;     // grouped mode: end of the group's rows
+    int rowB0;      // grouped mode: first row of the group's weight in B
 };
 
-__device__ __forceinline__ PairTile TileOf(const GemmArgs &a, int t, int mTiles, int rank, int ranks)
+// Grouped mode: where the rows and the 256-row blocks of each group of this launch start (shared memory, behind the barriers).
+struct GroupTable {
+    int rowStart[GEMM_MAX_GROUPS + 1];
+    int blockStart[GEMM_MAX_GROUPS + 1];
+};
+
+__device__ __forceinline__ PairTile TileOf(const GemmArgs &a, int t, int mTiles, int rank, int ranks, const GroupTable *gt)
 {
     PairTile c;
+    if (a.mode == GEMM_GROUPED) {
+        PairTileAt(t, mTiles, a.nBlocks, a.rasterGroup, &c.mTile, &c.nBlock);
+        int lo = 0, hi = a.groups - 1;           // last group whose first block is at or before mTile (empty groups share a start)
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (gt->blockStart[mid] <= c.mTile) lo = mid;
+            else hi = mid - 1;
+        }
+        c.shard = lo;
+        c.mLocalPair = c.mTile - gt->blockStart[lo];
+        c.row0 = gt->rowStart[lo] + c.mLocalPair * 2 * GEMM_BM;
+        c.rowEnd = gt->rowStart[lo + 1];
+        c.rowB0 = (a.groupBase + lo) * a.N;
+        return c;
+    }
+    c.row0 = c.rowEnd = c.rowB0 = 0;
     if (a.mode == GEMM_PLAIN) {
         PairTileAt(t, mTiles, a.nBlocks, a.rasterGroup, &c.mTile, &c.nBlock);
         c.shard = 0;
@@ -254,13 +279,15 @@ __device__ void PairBody(const GemmArgs &a)
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smemRaw) + 1023) & ~static_cast<uintptr_t>(1023));
     uint8_t *stageBase = smem;
     PairState *st = reinterpret_cast<PairState *>(smem + GEMM_PAIR_STAGES * GEMM_PAIR_STAGE_BYTES);
+    GroupTable *gt = reinterpret_cast<GroupTable *>(smem + GEMM_PAIR_STAGES * GEMM_PAIR_STAGE_BYTES + 256);
+    static_assert(sizeof(PairState) <= 256 && 256 + sizeof(GroupTable) <= 1024, "barriers and group table share one KB");
     uint8_t *stageC = smem + GEMM_PAIR_STAGES * GEMM_PAIR_STAGE_BYTES + 1024;      // 128 rows x 256 bytes for the epilogue
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const uint32_t ctaRank = ClusterCtaRank();
     const bool leader = ctaRank == 0;
-    const bool fused = a.mode != GEMM_PLAIN;
+    const bool fused = a.mode == GEMM_ALL_GATHER || a.mode == GEMM_REDUCE_SCATTER;     // the modes with a communicator
     Waiter w;
     bool ok = true;
     int rank = 0, ranks = 1;
@@ -348,6 +375,27 @@ __device__ void PairBody(const GemmArgs &a)
         asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&a.tmapB)) : "memory");
         if (a.mode == GEMM_ALL_GATHER) asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&a.tmapALocal)) : "memory");
     }
+    if (a.mode == GEMM_GROUPED && warp == 2) {
+        // rows before this launch's first group, then the running row and block offsets of its groups
+        long long before = 0;
+        for (int g = lane; g < a.groupBase; g += 32) before += max(0ll, static_cast<long long>(a.groupRows[g]));
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) before += __shfl_xor_sync(0xffffffffu, before, o);
+        if (lane == 0) {
+            int row = static_cast<int>(min(before, static_cast<long long>(a.M)));
+            int block = 0;
+            for (int g = 0; g < a.groups; ++g) {
+                gt->rowStart[g] = row;
+                gt->blockStart[g] = block;
+                const long long want = max(0ll, static_cast<long long>(a.groupRows[a.groupBase + g]));
+                const int rows = static_cast<int>(min(want, static_cast<long long>(a.M - row)));      // never past the buffers
+                row += rows;
+                block += (rows + 2 * GEMM_BM - 1) / (2 * GEMM_BM);
+            }
+            gt->rowStart[a.groups] = row;
+            gt->blockStart[a.groups] = block;
+        }
+    }
     __syncthreads();
     if (warp == 1) {
         // the same warp of both CTAs allocates for the pair; the address is the same in both
@@ -364,7 +412,7 @@ __device__ void PairBody(const GemmArgs &a)
     // `commTilesPerPair` tiles each from its end (the shards that arrive last), so their SMs are not lost.
     const int firstCta = (fused && a.mode == GEMM_ALL_GATHER) ? static_cast<int>(a.commBlocks) : 0;
     const int commPairs = firstCta >> 1;
-    const int mTiles = (a.M + 2 * GEMM_BM - 1) / (2 * GEMM_BM);
+    const int mTiles = a.mode == GEMM_GROUPED ? gt->blockStart[a.groups] : (a.M + 2 * GEMM_BM - 1) / (2 * GEMM_BM);
     const int allTiles = mTiles * a.nBlocks;
     const int commTiles = min(allTiles, commPairs * static_cast<int>(a.commTilesPerPair));
     int pair, nPairs, totalTiles, tileBase, tileSign;
@@ -390,13 +438,16 @@ __device__ void PairBody(const GemmArgs &a)
         if (lane == 0) {
             uint32_t stage = 0, phase = 0;
             for (int t = pair; t < totalTiles && st->abortFlag == 0; t += nPairs) {
-                const PairTile tc = TileOf(a, tileBase + tileSign * t, mTiles, rank, ranks);
+                const PairTile tc = TileOf(a, tileBase + tileSign * t, mTiles, rank, ranks, gt);
                 const int mLocal = tc.mLocalPair * 2 + static_cast<int>(ctaRank);        // this CTA's 128-row block in the shard
                 const bool remoteA = a.mode == GEMM_ALL_GATHER && tc.shard != rank;
                 const CUtensorMap *mapA = (a.mode == GEMM_ALL_GATHER && !remoteA) ? &a.tmapALocal : &a.tmapA;
-                const int rowA = (a.mode == GEMM_ALL_GATHER && !remoteA) ? mLocal * GEMM_BM
-                                                                         : tc.mTile * 2 * GEMM_BM + static_cast<int>(ctaRank) * GEMM_BM;
-                const int rowB = tc.nBlock * GEMM_BN + static_cast<int>(ctaRank) * (GEMM_BN / 2);
+                // grouped: a block starts wherever its group's rows start; rows past the group's end belong to the
+                // next group (or are filled with zeros past the end of A) and are computed but never stored
+                const int rowA = a.mode == GEMM_GROUPED ? tc.row0 + static_cast<int>(ctaRank) * GEMM_BM
+                                 : (a.mode == GEMM_ALL_GATHER && !remoteA) ? mLocal * GEMM_BM
+                                                                           : tc.mTile * 2 * GEMM_BM + static_cast<int>(ctaRank) * GEMM_BM;
+                const int rowB = tc.rowB0 + tc.nBlock * GEMM_BN + static_cast<int>(ctaRank) * (GEMM_BN / 2);
                 bool broke = false;
                 for (int kb = 0; kb < a.kBlocks; ++kb) {
                     if (!WaitBar(&st->empty[stage], phase ^ 1u, st, peerAbortAddr, budgetNs)) {
@@ -483,7 +534,7 @@ __device__ void PairBody(const GemmArgs &a)
         const float outScale = fp8 ? a.alpha : 1.0f;
         int iter = 0;
         for (int t = pair; t < totalTiles; t += nPairs, ++iter) {
-            const PairTile tc = TileOf(a, tileBase + tileSign * t, mTiles, rank, ranks);
+            const PairTile tc = TileOf(a, tileBase + tileSign * t, mTiles, rank, ranks, gt);
             const int nBlock = tc.nBlock;
             const int acc = iter & 1;
             const uint32_t accPhase = (iter >> 1) & 1;
@@ -496,6 +547,9 @@ __device__ void PairBody(const GemmArgs &a)
             if ((sEpiGot[0] & sEpiGot[1] & sEpiGot[2] & sEpiGot[3]) == 0) break;
             TcFenceAfter();
             // first row of this CTA's sub-tile at its destination, and how many of its 128 rows exist
+            const bool swiglu = a.epilogue == GEMM_EPI_SWIGLU && a.mode != GEMM_REDUCE_SCATTER;
+            const int outN = swiglu ? a.N / 2 : a.N;                  // columns of C
+            const uint64_t outRowBytes = static_cast<uint64_t>(outN) * 2;
             uint8_t *rowBase;
             int rowsValid;
             if (a.mode == GEMM_REDUCE_SCATTER) {
@@ -503,14 +557,18 @@ __device__ void PairBody(const GemmArgs &a)
                 rowsValid = static_cast<int>(max(static_cast<int64_t>(0), min(static_cast<int64_t>(GEMM_BM), a.shardRows - localRow0)));
                 rowBase = reg->regions[a.stageHandle].peerBase[tc.shard] + a.stageOffset +
                           (static_cast<uint64_t>(rank) * a.shardRows + static_cast<uint64_t>(localRow0)) * a.N * 2;
+            } else if (a.mode == GEMM_GROUPED) {
+                const int row0 = tc.row0 + static_cast<int>(ctaRank) * GEMM_BM;
+                rowsValid = max(0, min(GEMM_BM, tc.rowEnd - row0));
+                rowBase = a.c + static_cast<uint64_t>(row0) * outRowBytes;
             } else {
                 const int64_t row0 = static_cast<int64_t>(tc.mTile) * 2 * GEMM_BM + static_cast<int64_t>(ctaRank) * GEMM_BM;
                 rowsValid = static_cast<int>(max(static_cast<int64_t>(0), min(static_cast<int64_t>(GEMM_BM), a.M - row0)));
-                rowBase = a.c + static_cast<uint64_t>(row0) * a.N * 2;
+                rowBase = a.c + static_cast<uint64_t>(row0) * outRowBytes;
             }
             const int col0 = nBlock * GEMM_BN;
 #pragma unroll 1
-            for (int pass = 0; pass < 2; ++pass) {                   // 128 columns at a time
+            for (int pass = 0; pass < 2; ++pass) {                   // 128 columns of the product at a time
 #pragma unroll 1
                 for (int cc = 0; cc < 4; ++cc) {
                     uint32_t r[32];
@@ -518,16 +576,38 @@ __device__ void PairBody(const GemmArgs &a)
                                            static_cast<uint32_t>(acc * GEMM_BN + pass * 128 + cc * 32);
                     TmemLoad32(taddr, r);
                     TmemLoadWait();
-                    uint32_t packed[16];
+                    if (swiglu) {
+                        // 32 columns = 16 (gate, up) pairs -> 16 outputs = two 16-byte chunks of a 128-byte row piece
+                        uint32_t packed[8];
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        packed[j] = PackPair(__uint_as_float(r[2 * j]) * outScale, __uint_as_float(r[2 * j + 1]) * outScale, bf16);
-                    }
+                        for (int j = 0; j < 8; ++j) {
+                            float o[2];
 #pragma unroll
-                    for (int v = 0; v < 4; ++v) {
-                        const int chunk = (cc * 4 + v) ^ (myRow & 15);    // 16-byte chunks of a 256-byte row, XOR-swizzled
-                        *reinterpret_cast<uint4 *>(stageC + myRow * 256 + chunk * 16) =
-                            make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
+                            for (int q = 0; q < 2; ++q) {
+                                const float gate = __uint_as_float(r[4 * j + 2 * q]) * outScale;
+                                const float up = __uint_as_float(r[4 * j + 2 * q + 1]) * outScale;
+                                o[q] = gate / (1.0f + __expf(-gate)) * up;
+                            }
+                            packed[j] = PackPair(o[0], o[1], bf16);
+                        }
+#pragma unroll
+                        for (int v = 0; v < 2; ++v) {
+                            const int chunk = (cc * 2 + v) ^ (myRow & 7);
+                            *reinterpret_cast<uint4 *>(stageC + myRow * 256 + chunk * 16) =
+                                make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
+                        }
+                    } else {
+                        uint32_t packed[16];
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            packed[j] = PackPair(__uint_as_float(r[2 * j]) * outScale, __uint_as_float(r[2 * j + 1]) * outScale, bf16);
+                        }
+#pragma unroll
+                        for (int v = 0; v < 4; ++v) {
+                            const int chunk = (cc * 4 + v) ^ (myRow & 15);    // 16-byte chunks of a 256-byte row, XOR-swizzled
+                            *reinterpret_cast<uint4 *>(stageC + myRow * 256 + chunk * 16) =
+                                make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
+                        }
                     }
                 }
                 if (pass == 1) {
@@ -537,15 +617,29 @@ __device__ void PairBody(const GemmArgs &a)
                     if (lane == 0) ArriveCluster(SmemAddr(&st->tmemEmpty[acc]) & PEER_BIT_MASK);
                 }
                 asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (swiglu) {
 #pragma unroll 4
-                for (int k = 0; k < 16; ++k) {
-                    const int idx = et + k * 128;
-                    const int rr = idx >> 4;
-                    const int ch = idx & 15;
-                    const int col = col0 + pass * 128 + ch * 8;
-                    if (rr < rowsValid && col < a.N) {
-                        const uint4 v = *reinterpret_cast<const uint4 *>(stageC + rr * 256 + ((ch ^ (rr & 15)) * 16));
-                        st_vec16(rowBase + static_cast<uint64_t>(rr) * a.N * 2 + static_cast<uint64_t>(col) * 2, Vec16{v.x, v.y, v.z, v.w});
+                    for (int k = 0; k < 8; ++k) {
+                        const int idx = et + k * 128;
+                        const int rr = idx >> 3;
+                        const int ch = idx & 7;
+                        const int col = (col0 + pass * 128) / 2 + ch * 8;
+                        if (rr < rowsValid && col < outN) {
+                            const uint4 v = *reinterpret_cast<const uint4 *>(stageC + rr * 256 + ((ch ^ (rr & 7)) * 16));
+                            st_vec16(rowBase + static_cast<uint64_t>(rr) * outRowBytes + static_cast<uint64_t>(col) * 2, Vec16{v.x, v.y, v.z, v.w});
+                        }
+                    }
+                } else {
+#pragma unroll 4
+                    for (int k = 0; k < 16; ++k) {
+                        const int idx = et + k * 128;
+                        const int rr = idx >> 4;
+                        const int ch = idx & 15;
+                        const int col = col0 + pass * 128 + ch * 8;
+                        if (rr < rowsValid && col < a.N) {
+                            const uint4 v = *reinterpret_cast<const uint4 *>(stageC + rr * 256 + ((ch ^ (rr & 15)) * 16));
+                            st_vec16(rowBase + static_cast<uint64_t>(rr) * a.N * 2 + static_cast<uint64_t>(col) * 2, Vec16{v.x, v.y, v.z, v.w});
+                        }
                     }
                 }
                 asm volatile("bar.sync 1, 128;" ::: "memory");       // the staging tile may be rewritten

@@ -40,6 +40,19 @@ int TileXRAllReduceRmsNorm(const void *x, void *residualInOut, const void *gamma
 int TileXRMatmul(const void *a, const void *b, void *c, int64_t m, int64_t n, int64_t k, TXR_DT dtype, int32_t *status,
                  TileXRStream stream);
 
+// Grouped GEMM (the expert FFN of a MoE layer): the rows of A [maxRows, K] are grouped -- groupRows[0] rows of
+// group 0, then groupRows[1] rows of group 1, ... -- and group g is multiplied with its own weight
+// B[g] ([groups, N, K] contiguous): C[row] = A[row] x B[g(row)]^T.  groupRows is a DEVICE array of int64 (e.g. the
+// expertTokenNums output of dispatch): nothing is read back to the host, and the tile list is built inside the
+// kernel.  Rows at and past the sum of the counts are not written.  Same type and alignment rules as TileXRMatmul.
+// epilogue 0 stores the product, C [maxRows, N].  epilogue 1 (TILEXR_GEMM_EPILOGUE_SWIGLU) takes weight row 2i as
+// gate row i and row 2i+1 as up row i and stores silu(gate) * up, C [maxRows, N / 2]: the first GEMM of a SwiGLU
+// feed-forward with its activation, without the [rows, N] intermediate.
+#define TILEXR_GEMM_EPILOGUE_STORE 0
+#define TILEXR_GEMM_EPILOGUE_SWIGLU 1
+int TileXRGroupedMatmul(const void *a, const void *b, const int64_t *groupRows, void *c, int64_t maxRows, int64_t n, int64_t k,
+                        int64_t groups, TXR_DT dtype, int epilogue, int32_t *status, TileXRStream stream);
+
 // C = alpha * A x B^T with fp8 operands (e4m3 or e5m2, both the same type; K a multiple of 16) and fp32 accumulation on
 // the 8-bit tensor-core path (tcgen05.mma kind::f8f6f4, twice the rate of 16-bit operands); C is fp16 or bf16.  `alpha`
 // is the product of the operands' per-tensor dequantisation scales.

@@ -41,11 +41,16 @@ extern "C" {
 // per block exceed the limits above: nothing is launched in that case.
 //
 // The first call on each device looks up the scratch array's device address and clears its
-// barrier words (a synchronous cudaMemset); make that first call outside any stream capture.
-// All calls on a device share the scratch array, which keeps what the previous call left in it:
-// the kernel overwrites every counter it later reads, and its barrier words return to zero at
-// the end of each call.  Two calls that overlap on the GPU (different streams) would race on
-// it, so issue calls for one device on one stream or order them with events.
+// barrier word (a synchronous cudaMemset); make that first call outside any stream capture.
+// Host threads may call concurrently: the lookup runs once per device and later callers wait
+// for it.  All calls on a device share the scratch array, which keeps what the previous call
+// left in it: the kernel overwrites every counter it later reads, and the barrier word carries
+// the number of the call it belongs to, so a call starts it afresh whatever the previous call
+// left there -- also after a call whose barrier gave up (status 5), which needs no clean-up.
+// Two calls that overlap on the GPU (different streams) would race on the array, so issue
+// calls for one device on one stream or order them with events.  The call number is a kernel
+// argument: a captured call replayed from a CUDA graph repeats it, which the barrier accepts
+// (a word that is complete or was given up counts as left over, whatever its number).
 int TileXRMoeLocalDispatchNoAlloc(const void *x, const int32_t *expertIds, int64_t bs, int64_t h, int64_t topK,
                                   int64_t moeExpertNum, void *expandXOut, int32_t *assistOut, int64_t *expertTokenNumsOut,
                                   int32_t *sendCountsOut, int dtype, TileXRStream stream);

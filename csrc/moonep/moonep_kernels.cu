@@ -11,6 +11,7 @@
 #include <cuda_fp16.h>
 
 #include "device/tilexr_convert.cuh"
+#include "device/tilexr_route_rank.cuh"
 #include "device/tilexr_moonep_trace.cuh"
 #include "device/tilexr_rma.cuh"
 #include "device/tilexr_sync.cuh"
@@ -100,15 +101,7 @@ __device__ void PlannerBody(const PlannerArgs &a)
     valid = BlockBroadcastOk(valid);
     if (!valid && tid == 0 && ok) RaiseFailure(w, TILEXR_DEV_BAD_ARGUMENT, rank, 0, 0, 0);
     ok = ok && valid;
-    if (ok) {
-        for (int i = tid; i < nRoutes; i += blockDim.x) {
-            const int e = sExpert[i];
-            int r = 0;
-            for (int j = 0; j < i; ++j) r += sExpert[j] == e ? 1 : 0;
-            sRank[i] = r;
-            atomicAdd(&sHist[e], 1);
-        }
-    }
+    if (ok && tid < 32) RankRoutesByWarp(sExpert, sRank, sHist, nRoutes, tid);
     __syncthreads();
     for (int e = tid; e < E; e += blockDim.x) blockCounts[static_cast<int64_t>(blockIdx.x) * E + e] = sHist[e];
     ok = GridBarrier(w, 0) && ok;

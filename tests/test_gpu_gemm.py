@@ -119,3 +119,26 @@ def test_matmul_fp8_block_scaled(txr, m, n, k):
     want = da @ dw.t()
     assert torch.allclose(got, want, rtol=1e-2, atol=1e-2 * want.abs().max().item()), (got - want).abs().max()
     assert (got - want).abs().mean() < 4e-3 * want.abs().mean() + 1e-4
+
+
+@pytest.mark.parametrize("counts,n,k,swiglu", [
+    ([300, 0, 17, 256, 1, 700], 512, 256, False),          # empty group, groups smaller and larger than a tile, ragged starts
+    ([300, 0, 17, 256, 1, 700], 512, 256, True),
+    ([5] * 70, 264, 128, False),                             # more groups than one launch holds, N not a multiple of the tile
+    ([2000, 3000, 100, 4000], 4096, 1024, True),             # more tiles than CTA pairs
+])
+def test_grouped_matmul(txr, counts, n, k, swiglu):
+    """One launch over all groups, row counts read on the device, against fp32 PyTorch; rows past the counts untouched."""
+    g = torch.Generator().manual_seed(sum(counts) + n)
+    total = sum(counts)
+    rows = (torch.randn(total + 40, k, generator=g) * 0.5).to(torch.bfloat16).cuda()
+    w = (torch.randn(len(counts), n, k, generator=g) * 0.2).to(torch.bfloat16).cuda()
+    group_rows = torch.tensor(counts, dtype=torch.int64).cuda()
+    epi = txr.gemm.EPILOGUE_SWIGLU if swiglu else txr.gemm.EPILOGUE_STORE
+    out = torch.full((total + 40, n // 2 if swiglu else n), 7.0, dtype=torch.bfloat16, device="cuda")
+    for _ in range(2):
+        got = txr.gemm.grouped_matmul(rows, w, group_rows, epilogue=epi, out=out)
+    torch.cuda.synchronize()
+    want = txr.gemm.grouped_matmul_ref(rows, w, group_rows, epi)
+    _close(got[:total], want[:total], k)
+    assert torch.all(got[total:] == 7.0)

@@ -17,13 +17,17 @@ from conftest import free_port, require_cuda
 pytestmark = pytest.mark.gpu
 
 
-def _call(lib, x, ids, experts):
+def _outputs(x, ids, experts):
     bs, h = x.shape
     k = ids.shape[1]
-    expand = torch.empty(bs * k, h, dtype=x.dtype, device=x.device)
-    assist = torch.empty(bs * k, 4, dtype=torch.int32, device=x.device)
-    nums = torch.empty(experts, dtype=torch.int64, device=x.device)
-    counts = torch.empty(experts, dtype=torch.int32, device=x.device)
+    return (torch.empty(bs * k, h, dtype=x.dtype, device=x.device), torch.empty(bs * k, 4, dtype=torch.int32, device=x.device),
+            torch.empty(experts, dtype=torch.int64, device=x.device), torch.empty(experts, dtype=torch.int32, device=x.device))
+
+
+def _call(lib, x, ids, experts, outputs=None):
+    bs, h = x.shape
+    k = ids.shape[1]
+    expand, assist, nums, counts = outputs if outputs is not None else _outputs(x, ids, experts)
     dtype_code = 11 if x.dtype == torch.bfloat16 else 3
     stream = torch.cuda.current_stream().cuda_stream
     rc = lib.TileXRMoeLocalDispatchNoAlloc(
@@ -61,6 +65,25 @@ def test_no_alloc_dispatch_matches_communicator_dispatch():
         assert torch.equal(assist[:n], ref.assist[:n])
         assert torch.equal(nums, ref.expert_token_nums)
         assert torch.equal(counts, ref.send_counts)
+    # the property the entry point exists for: with the outputs in place, a call takes no device memory, neither
+    # from the driver nor from torch's pool, and the results are those of the call before
+    outputs = _outputs(x, ids, experts)
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    stop.record()
+    torch.cuda.synchronize()
+    free_before, allocated_before = torch.cuda.mem_get_info()[0], torch.cuda.memory_allocated()
+    reserved_before = torch.cuda.memory_reserved()
+    start.record()
+    for _ in range(10):
+        rc, expand2, *_ = _call(lib, x, ids, experts, outputs)
+        assert rc == 0
+    stop.record()
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free_before
+    assert torch.cuda.memory_allocated() == allocated_before and torch.cuda.memory_reserved() == reserved_before
+    assert torch.equal(expand2[:n], expand[:n])
+    print(f"no-alloc dispatch {bs} x {h} top-{k}: {start.elapsed_time(stop) * 100:.1f} us per call")
     # sizes beyond the built-in scratch are refused, nothing is launched
     rc, *_ = _call(lib, x, ids, 4096)
     assert rc == -3

@@ -4,9 +4,10 @@ The reference ships no model code; its harness drives dispatch -> expert FFN (gr
 SwiGLU, grouped GEMM) -> combine with synthetic experts (tools/moonep/expert_forward.py).  This
 module is the same workload as a reusable layer, shaped like a DeepSeek-V3 MoE block: sigmoid
 router with top-k renormalisation, fp8 (e4m3, 1x128 scales) token transport, bf16 combine.
-The expert GEMMs run on this repository's tcgen05 kernel (one launch per local expert segment; cuBLAS only
-for shapes the kernel does not take); the communication, routing, quantisation and the gate-weighted
-reduction are this repository's kernels too.
+The expert feed-forward is two launches of this repository's grouped tcgen05 GEMM over all local experts at
+once -- the first with the SwiGLU activation in its epilogue -- driven by the per-expert row counts that dispatch
+left on the device, so nothing is read back to the host between dispatch and combine; the communication, routing,
+quantisation and the gate-weighted reduction are this repository's kernels too.
 """
 from __future__ import annotations
 
@@ -16,14 +17,6 @@ from typing import Optional
 import torch
 
 from ..ops import ep, gemm, quant
-
-
-def _linear(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
-    """x [m, k] times w [n, k] transposed."""
-    if x.is_cuda and x.dtype in (torch.bfloat16, torch.float16) and w.dtype == x.dtype and x.shape[1] % 8 == 0 and w.shape[0] % 8 == 0 \
-            and x.is_contiguous() and w.is_contiguous() and x.data_ptr() % 16 == 0:
-        return gemm.matmul(x, w)
-    return x @ w.t()
 
 
 @dataclasses.dataclass
@@ -64,21 +57,12 @@ class ExpertParallelMoE(torch.nn.Module):
         return torch.matmul(x.float(), self.gate.t()).contiguous()
 
     def experts(self, rows: torch.Tensor, token_nums: torch.Tensor) -> torch.Tensor:
-        """Grouped SwiGLU FFN over rows that arrive grouped by local expert."""
-        out = torch.empty_like(rows)
+        """SwiGLU feed-forward over rows that arrive grouped by local expert; ``token_nums`` (int64, on the device) holds
+        the rows per expert.  ``w13[e]`` is [2 * ffn, hidden] with gate row i at 2i and up row i at 2i + 1."""
         if self.w13 is None:
-            return out.copy_(rows)
-        counts = token_nums.tolist()
-        start = 0
-        for e, n in enumerate(counts):
-            if n == 0:
-                continue
-            seg = rows[start:start + n]
-            gu = _linear(seg, self.w13[e])
-            g_, u_ = gu.chunk(2, dim=-1)
-            out[start:start + n] = _linear((torch.nn.functional.silu(g_) * u_).contiguous(), self.w2[e])
-            start += n
-        return out
+            return rows.clone()
+        mid = gemm.grouped_matmul(rows, self.w13, token_nums, epilogue=gemm.EPILOGUE_SWIGLU)
+        return gemm.grouped_matmul(mid, self.w2, token_nums)
 
     @torch.no_grad()
     def forward(self, x: torch.Tensor, gate_logits: Optional[torch.Tensor] = None, max_recv_rows: Optional[int] = None,

@@ -15,6 +15,43 @@ def matmul(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
     return _C.matmul(a.contiguous(), b.contiguous())
 
 
+EPILOGUE_STORE = 0
+EPILOGUE_SWIGLU = 1
+
+
+def grouped_matmul(rows: torch.Tensor, weights: torch.Tensor, group_rows: torch.Tensor, epilogue: int = EPILOGUE_STORE,
+                   out: torch.Tensor | None = None) -> torch.Tensor:
+    """Grouped GEMM of an expert feed-forward in one launch: ``rows`` [R, K] hold ``group_rows[0]`` rows of group 0, then
+    ``group_rows[1]`` rows of group 1, ...; group g is multiplied with ``weights[g]`` ([groups, N, K]).  ``group_rows`` is
+    an int64 tensor ON THE DEVICE (``DispatchResult.expert_token_nums``): the tile list is built inside the kernel and
+    nothing is read back to the host.  Rows past the sum of the counts are left as they are.
+
+    ``epilogue=EPILOGUE_SWIGLU`` reads weight row 2i as gate row i and row 2i+1 as up row i (see
+    :func:`interleave_gate_up`) and returns ``silu(gate) * up`` [R, N/2] without the [R, N] intermediate."""
+    return _C.grouped_matmul(rows.contiguous(), weights.contiguous(), group_rows, int(epilogue), out)
+
+
+def interleave_gate_up(w_gate: torch.Tensor, w_up: torch.Tensor) -> torch.Tensor:
+    """[..., F, K] gate and up projections -> [..., 2F, K] with gate row i at 2i and up row i at 2i+1, the layout the
+    SwiGLU epilogue of :func:`grouped_matmul` expects."""
+    return torch.stack((w_gate, w_up), dim=-2).reshape(*w_gate.shape[:-2], 2 * w_gate.shape[-2], w_gate.shape[-1]).contiguous()
+
+
+def grouped_matmul_ref(rows: torch.Tensor, weights: torch.Tensor, group_rows, epilogue: int = EPILOGUE_STORE) -> torch.Tensor:
+    """Plain PyTorch statement of :func:`grouped_matmul` in fp32 (rows past the counts come back as zeros)."""
+    n = weights.shape[1] // 2 if epilogue == EPILOGUE_SWIGLU else weights.shape[1]
+    out = torch.zeros(rows.shape[0], n, dtype=torch.float32, device=rows.device)
+    start = 0
+    for g, count in enumerate(int(v) for v in group_rows.tolist()):
+        count = max(0, min(count, rows.shape[0] - start))
+        prod = rows[start:start + count].float() @ weights[g].float().t()
+        if epilogue == EPILOGUE_SWIGLU:
+            prod = torch.nn.functional.silu(prod[:, 0::2]) * prod[:, 1::2]
+        out[start:start + count] = prod
+        start += count
+    return out
+
+
 def matmul_fp8(a: torch.Tensor, b: torch.Tensor, alpha: float = 1.0, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
     """``alpha * a @ b.T`` for fp8 operands (both float8_e4m3fn or both float8_e5m2; a [M, K], b [N, K], K % 16 == 0) with fp32
     accumulation on the 8-bit tensor-core path; ``alpha`` is the product of the two per-tensor dequantisation scales."""

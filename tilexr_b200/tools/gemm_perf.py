@@ -25,6 +25,11 @@ def main() -> int:
                     help="operand type; the fp8 types run the kind::f8f6f4 path against torch._scaled_mm (cuBLASLt); fp8_block "
                          "is e4m3 with fp32 block scales (1 x 128 activations, 128 x 128 weights) against torch._scaled_mm "
                          "with the same scales where this torch / cuBLASLt accepts them, else against its per-tensor fp8 GEMM")
+    ap.add_argument("--groups", type=int, default=0,
+                    help="grouped GEMM: the M rows split evenly over this many groups with one [N, K] weight each (bf16), one launch "
+                         "with the row counts on the device, against torch.bmm (cuBLAS batched) on the same equal split; "
+                         "--swiglu adds the fused activation (N counts gate and up rows) against bmm + silu * mul")
+    ap.add_argument("--swiglu", action="store_true")
     args = ap.parse_args()
     block = args.dtype == "fp8_block"
     dtype = torch.float8_e4m3fn if block else getattr(torch, args.dtype)
@@ -50,6 +55,32 @@ def main() -> int:
         a = (torch.randn(m, k, device="cuda") * 0.5).to(dtype)
         b = (torch.randn(n, k, device="cuda") * 0.5).to(dtype)
         baseline = "torch.matmul (cuBLAS)"
+        if args.groups > 0:
+            G = args.groups
+            per = m // G
+            a = a[:per * G].contiguous()
+            wg = (torch.randn(G, n, k, device="cuda") * 0.2).to(dtype)
+            counts = torch.full((G,), per, dtype=torch.int64, device="cuda")
+            epi = txr.gemm.EPILOGUE_SWIGLU if args.swiglu else txr.gemm.EPILOGUE_STORE
+            out = torch.empty(per * G, n // 2 if args.swiglu else n, dtype=dtype, device="cuda")
+            run_ours = lambda: txr.gemm.grouped_matmul(a, wg, counts, epilogue=epi, out=out)
+            a3, wt = a.view(G, per, k), wg.transpose(1, 2)
+            if args.swiglu:
+                def run_lib():
+                    p = torch.bmm(a3, wt)
+                    return torch.nn.functional.silu(p[..., 0::2]) * p[..., 1::2]
+                baseline = "torch.bmm + silu * mul (cuBLAS batched, equal groups)"
+            else:
+                run_lib = lambda: torch.bmm(a3, wt)
+                baseline = "torch.bmm (cuBLAS batched, equal groups)"
+            ours, cublas = median_ms(run_ours), median_ms(run_lib)
+            c, ref = run_ours().float(), run_lib().reshape(per * G, -1).float()
+            torch.cuda.synchronize()
+            flops = 2.0 * per * G * n * k
+            print(json.dumps({"shape": [per * G, n, k], "groups": G, "swiglu": args.swiglu, "baseline": baseline, "ours_us": ours * 1e3,
+                              "cublas_us": cublas * 1e3, "ours_tflops": flops / ours / 1e9, "cublas_tflops": flops / cublas / 1e9,
+                              "ratio": cublas / ours, "max_abs_diff": (c - ref).abs().max().item()}), flush=True)
+            continue
         if block:
             qa, sa = txr.quant.fp8_quant_1x128((torch.randn(m, k, device="cuda") * 0.5).to(torch.bfloat16))
             qb, sb = txr.gemm.quantize_weight_128x128(torch.randn(n, k, device="cuda") * 0.5)

@@ -175,24 +175,26 @@ def ep_combine_ref(dispatch, expert_outs: Sequence[torch.Tensor], ids: Sequence[
     ys = []
     slot = {}
     for d in range(world):
+        rows_d = expert_outs[d].float().cpu()                  # once per rank: a per-row conversion would keep a copy per row
         for i, (s, t, k, _) in enumerate(dispatch[d]["rows"]):
-            slot[(s, t, k)] = expert_outs[d].float().cpu()[i]
+            slot[(s, t, k)] = rows_d[i]
+    shared_cpu = None if shared is None else [x.float().cpu() for x in shared]
     for s in range(world):
         bs, k = ids[s].shape
         y = torch.zeros(bs, h, dtype=torch.float32)
-        w = weights[s]
+        w = None if weights[s] is None else weights[s].float().cpu()
         for t in range(bs):
             acc = torch.zeros(h, dtype=torch.float64)
             acc32 = torch.zeros(h, dtype=torch.float32)
             for kk in range(k):
                 if (s, t, kk) not in slot:
                     continue
-                wt = 1.0 if w is None else float(w.cpu()[t, kk])
+                wt = 1.0 if w is None else float(w[t, kk])
                 # fma(w, row, acc) in fp32: emulate with one rounding from a float64 product-sum
                 acc = acc32.double() + torch.tensor(wt, dtype=torch.float32).double() * slot[(s, t, kk)].double()
                 acc32 = acc.float()
             if shared is not None:
-                acc32 = acc32 + shared[s].float().cpu()[t]
+                acc32 = acc32 + shared_cpu[s][t]
             y[t] = acc32
         ys.append(y.to(out_dtype))
     return ys
