@@ -133,6 +133,7 @@ TileXRComm::~TileXRComm()
         if (devArgs_ != nullptr) cudaFree(devArgs_);
         if (devRegistry_ != nullptr) cudaFree(devRegistry_);
         if (localCopyWorkspace_ != nullptr) cudaFree(localCopyWorkspace_);
+        if (operatorScratch_ != nullptr) cudaFree(operatorScratch_);
         if (windowVmm_.live) {
             VmmFree(nullptr, &windowVmm_);          // the ranks have met above
             window_ = nullptr;
@@ -272,6 +273,50 @@ int TileXRComm::MapHostMemoryWindows()
     return exchange_->Barrier();
 }
 
+// What this device is and how it reaches its peers.  Read-only queries; nothing is configured.  Device ordinals of
+// peers in other processes are theirs, which equals ours when the processes see the same devices (the usual
+// one-process-per-GPU launch); an ordinal this process does not have is skipped.
+void TileXRComm::DetectTopology(const std::vector<int> &peerDevices)
+{
+    TileXRPhysicalInfo &ph = physical_;
+    ph = TileXRPhysicalInfo{};
+    cudaDeviceProp prop{};
+    if (cudaGetDeviceProperties(&prop, device_) == cudaSuccess) {
+        ph.ccMajor = prop.major;
+        ph.ccMinor = prop.minor;
+        ph.smCount = static_cast<uint32_t>(prop.multiProcessorCount);
+        ph.l2Bytes = static_cast<uint32_t>(prop.l2CacheSize);
+        ph.memoryBytes = prop.totalGlobalMem;
+    }
+    int deviceCount = 0;
+    cudaGetDeviceCount(&deviceCount);
+    bool anyPeer = false, allAtomics = true, anyPcie = false;
+    int worstRank = 0;
+    for (int r = 0; r < static_cast<int>(peerDevices.size()); ++r) {
+        const int d = peerDevices[r];
+        if (r == rank_ || d == device_ || d < 0 || d >= deviceCount) continue;
+        int access = 0, atomics = 0, perf = 0;
+        if (cudaDeviceGetP2PAttribute(&access, cudaDevP2PAttrAccessSupported, device_, d) != cudaSuccess || access == 0) {
+            cudaGetLastError();
+            continue;
+        }
+        anyPeer = true;
+        cudaDeviceGetP2PAttribute(&atomics, cudaDevP2PAttrNativeAtomicSupported, device_, d);
+        cudaDeviceGetP2PAttribute(&perf, cudaDevP2PAttrPerformanceRank, device_, d);
+        cudaGetLastError();
+        if (atomics == 0) {
+            allAtomics = false;
+            anyPcie = true;
+        }
+        worstRank = std::max(worstRank, perf);
+    }
+    ph.link = !anyPeer ? TILEXR_LINK_SAME_DEVICE : anyPcie ? TILEXR_LINK_PCIE : TILEXR_LINK_NVLINK;
+    ph.p2pNativeAtomics = anyPeer && allAtomics ? 1 : 0;
+    ph.p2pPerformanceRank = worstRank;
+    bool vmm = false, multicast = false;
+    if (VmmDeviceSupport(device_, &vmm, &multicast) == TILEXR_SUCCESS) ph.multicastSupported = multicast ? 1 : 0;
+}
+
 int TileXRComm::ExchangeWindows()
 {
     PeerInfo mine{};
@@ -287,6 +332,11 @@ int TileXRComm::ExchangeWindows()
     int ret = exchange_->AllGather(&mine, all.data(), sizeof(PeerInfo));
     if (ret != TILEXR_SUCCESS) return ret;
     peerWindows_.assign(rankSize_, nullptr);
+    {
+        std::vector<int> peerDevices(rankSize_);
+        for (int r = 0; r < rankSize_; ++r) peerDevices[r] = all[r].device;
+        DetectTopology(peerDevices);
+    }
     for (int i = 0; i < rankSize_; ++i) {
         const int r = (rank_ + i) % rankSize_;
         const PeerInfo &p = all[r];
@@ -355,7 +405,14 @@ void TileXRComm::FillCommArgs()
     if (windowVmm_.live && windowVmm_.multicast != nullptr) {
         a.multicastMem = windowVmm_.multicast;
         a.extraFlag |= TILEXR_FLAG_NVLS;
+        physical_.nvlsBound = 1;
     }
+    if (!isHostMemory() && physical_.smCount == 0) DetectTopology(std::vector<int>());     // worlds that exchange no peer records
+    physical_.vmmWindow = windowVmm_.live ? 1 : 0;
+    if (opt_.mode == CommMode::HOST_MEMORY) physical_.link = TILEXR_LINK_HOST_MEMORY;
+    else if (opt_.mode == CommMode::EMULATED || rankSize_ == 1) physical_.link = TILEXR_LINK_SAME_DEVICE;
+    if (physical_.link == TILEXR_LINK_NVLINK) a.extraFlag |= TILEXR_FLAG_TOPO_NVLINK;
+    if (physical_.link == TILEXR_LINK_PCIE) a.extraFlag |= TILEXR_FLAG_TOPO_PCIE;
 }
 
 int TileXRComm::SyncCommArgs()
@@ -722,6 +779,29 @@ void TileXRComm::PrintDfx()
     std::lock_guard<std::mutex> lock(LogMutex());
     std::fprintf(stdout, "[TileXR] %s\n", os.str().c_str());
     std::fflush(stdout);
+}
+
+// Operators whose host side has to stage small per-call arrays on the device (the widened route arrays of EP x TP)
+// take them from here instead of allocating per call.  Growing the buffer frees the old one, which waits for the
+// device: it happens on the first call of a larger shape only.
+int TileXRComm::OperatorScratch(size_t bytes, void **ptr)
+{
+    if (ptr == nullptr) return TILEXR_ERROR_PARA_CHECK_FAIL;
+    if (isHostMemory()) return TILEXR_ERROR_NOT_SUPPORT;
+    if (bytes > operatorScratchBytes_) {
+        TXR_CUDA(cudaSetDevice(device_));
+        if (operatorScratch_ != nullptr) {
+            TXR_CUDA(cudaDeviceSynchronize());
+            TXR_CUDA(cudaFree(operatorScratch_));
+            operatorScratch_ = nullptr;
+            operatorScratchBytes_ = 0;
+        }
+        const size_t want = (bytes + (1u << 20) - 1) & ~static_cast<size_t>((1u << 20) - 1);
+        TXR_CUDA(cudaMalloc(&operatorScratch_, want));
+        operatorScratchBytes_ = want;
+    }
+    *ptr = operatorScratch_;
+    return TILEXR_SUCCESS;
 }
 
 int TileXRComm::LocalCopyAsync(void *dst, const void *src, size_t bytes, cudaStream_t stream)

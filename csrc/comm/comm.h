@@ -84,6 +84,8 @@ public:
     void PrintDfx();
     int HostBarrier();
     int LocalCopyAsync(void *dst, const void *src, size_t bytes, cudaStream_t stream);
+    int OperatorScratch(size_t bytes, void **ptr);
+    const TileXRPhysicalInfo &physicalInfo() const { return physical_; }      // device memory that lives as long as the communicator, grown on demand
 
     int rank() const { return rank_; }
     int rankSize() const { return rankSize_; }
@@ -136,6 +138,10 @@ private:
     std::vector<RegionRecord> regions_;
     std::vector<ProfileRecord> profiles_;
     void *localCopyWorkspace_ = nullptr;
+    void DetectTopology(const std::vector<int> &peerDevices);
+    TileXRPhysicalInfo physical_{};
+    void *operatorScratch_ = nullptr;
+    size_t operatorScratchBytes_ = 0;
     cudaStream_t copyStream_ = nullptr;
     cudaEvent_t copyEventIn_ = nullptr;
     cudaEvent_t copyEventOut_ = nullptr;

@@ -601,6 +601,22 @@ int TileXRFindRegistration(TileXRCommPtr comm, const void *ptr, size_t bytes, Ti
     return c->FindRegistration(ptr, bytes, handle, offset);
 }
 
+int TileXRGetPhysicalInfo(TileXRCommPtr comm, TileXRPhysicalInfoT *info)
+{
+    TileXRComm *c = AsComm(comm);
+    if (c == nullptr) return TILEXR_ERROR_NOT_INITIALIZED;
+    if (info == nullptr) return TILEXR_ERROR_PARA_CHECK_FAIL;
+    *info = c->physicalInfo();
+    return TILEXR_SUCCESS;
+}
+
+int TileXRGetOperatorScratch(TileXRCommPtr comm, size_t bytes, void **ptr)
+{
+    TileXRComm *c = AsComm(comm);
+    if (c == nullptr) return TILEXR_ERROR_NOT_INITIALIZED;
+    return c->OperatorScratch(bytes, ptr);
+}
+
 int TileXRLocalCopyAsync(TileXRCommPtr comm, void *dst, const void *src, size_t bytes, TileXRStream stream)
 {
     TileXRComm *c = AsComm(comm);

@@ -2,6 +2,7 @@
 
 #include <atomic>
 #include <cstring>
+#include <functional>
 #include <map>
 #include <vector>
 
@@ -20,6 +21,7 @@ struct PendingLaunch {
     std::vector<uint8_t> args;
     LaunchConfig cfg;
     cudaStream_t stream;
+    std::vector<std::function<int()>> after;     // host work to run once the launch has been issued (RunAfterLaunch)
 };
 
 struct GroupState {
@@ -130,6 +132,20 @@ int LaunchKernel(TileXRCommPtr commPtr, const KernelEntry &kernel, const void *a
     return TILEXR_SUCCESS;
 }
 
+int RunAfterLaunch(TileXRCommPtr commPtr, std::function<int()> fn)
+{
+    TileXRComm *comm = static_cast<TileXRComm *>(commPtr);
+    if (comm != nullptr && comm->isEmulated() && g_group.depth > 0) {
+        for (auto it = g_group.pending.rbegin(); it != g_group.pending.rend(); ++it) {
+            if (it->comm == comm) {
+                it->after.push_back(std::move(fn));
+                return TILEXR_SUCCESS;
+            }
+        }
+    }
+    return fn();
+}
+
 int MaxCooperativeGrid(TileXRCommPtr commPtr, const KernelEntry &kernel, unsigned block, size_t smemBytes,
                        int ranksPerDevice, unsigned *maxGrid)
 {
@@ -189,6 +205,12 @@ extern "C" int TileXRGroupEnd(void)
             for (int r = 0; r < w->rankSize; ++r) row[r] = kv.second[r][k];
             int ret = IssueWorldLaunch(w, row);
             if (ret != TILEXR_SUCCESS) result = ret;
+            for (PendingLaunch *p : row) {
+                for (auto &fn : p->after) {
+                    ret = fn();
+                    if (ret != TILEXR_SUCCESS) result = ret;
+                }
+            }
         }
     }
     return result;

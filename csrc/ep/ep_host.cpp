@@ -6,6 +6,8 @@
 #include <cstdlib>
 #include <cstring>
 
+#include <cuda_runtime_api.h>
+
 #include "ep_kernels.cuh"
 #include "../collectives/perf_trace_session.h"
 #include "tilexr_ep.h"
@@ -53,6 +55,15 @@ bool DispatchLayout(int64_t h, int64_t numExperts, int64_t rankSize, int64_t max
     win->totalBytes = off;
     return true;
 }
+
+// ep_tp.cu
+}
+namespace TileXR {
+int EpTpExpand(const int32_t *ids, const float *weights, const uint8_t *routeMask, int64_t routes, int T, int experts, int perGroup,
+               int32_t *idsOut, float *weightsOut, uint8_t *routeMaskOut, cudaStream_t stream);
+int EpTpLaneCounts(const int32_t *sendCounts, int entries, int R, int T, int32_t *tpRecvCounts, cudaStream_t stream);
+}
+namespace {
 
 struct Ctx {
     TileXRCommArgs *hostArgs = nullptr;
@@ -125,6 +136,115 @@ int ValidateShape(int64_t bs, int64_t h, int64_t topK, int64_t moeExpertNum, int
     return TILEXR_SUCCESS;
 }
 
+// ---- tensor parallelism inside expert parallelism: see ep_tp.cu ---------------------------------------------------
+
+struct TpStaging {
+    int32_t *ids = nullptr;
+    float *weights = nullptr;
+    uint8_t *mask = nullptr;
+};
+
+int ValidateTp(const Ctx &c, int64_t tpWorldSize, int64_t tpRankId, int64_t topK, int64_t moeExpertNum, int64_t sharedExpertRankNum,
+               const char *what)
+{
+    const int64_t T = tpWorldSize;
+    if (T > c.rankSize || c.rankSize % T != 0 || tpRankId != c.rank % T) {
+        TILEXR_LOG(ERROR) << what << ": tpWorldSize " << T << " must divide the " << c.rankSize << " ranks and tpRankId must be rank % tpWorldSize";
+        return TILEXR_ERROR_PARA_CHECK_FAIL;
+    }
+    const int64_t groups = c.rankSize / T;
+    if (sharedExpertRankNum != 0 || topK * T > EP_MAX_TOPK || moeExpertNum % groups != 0 || moeExpertNum * T > EP_MAX_EXPERTS) {
+        TILEXR_LOG(ERROR) << what << " with tensor parallelism: no shared-expert ranks, topK * tpWorldSize <= " << EP_MAX_TOPK
+                          << ", experts divisible by the " << groups << " groups, experts * tpWorldSize <= " << EP_MAX_EXPERTS;
+        return TILEXR_ERROR_NOT_SUPPORT;
+    }
+    return TILEXR_SUCCESS;
+}
+
+// Carves the widened per-route arrays out of the communicator's scratch buffer (dispatch uses its first half, combine
+// the second, so a combine queued behind a dispatch on another stream does not overwrite what that dispatch reads).
+int StageTp(TileXRCommPtr comm, bool forCombine, int64_t routes, int T, bool ids, bool weights, bool mask, TpStaging *out)
+{
+    const uint64_t wide = static_cast<uint64_t>(routes) * T;
+    const uint64_t half = Align(wide * 4, 256) * 2 + Align(wide, 256);
+    void *base = nullptr;
+    const int ret = TileXRGetOperatorScratch(comm, 2 * half, &base);
+    if (ret != TILEXR_SUCCESS) return ret;
+    uint8_t *p = static_cast<uint8_t *>(base) + (forCombine ? half : 0);
+    if (ids) out->ids = reinterpret_cast<int32_t *>(p);
+    if (weights) out->weights = reinterpret_cast<float *>(p + Align(wide * 4, 256));
+    if (mask) out->mask = p + 2 * Align(wide * 4, 256);
+    return TILEXR_SUCCESS;
+}
+
+int DispatchWithTp(const TileXREpDispatchParams *p, TileXRCommPtr comm, TileXRStream stream, const Ctx &c)
+{
+    const int T = static_cast<int>(p->tpWorldSize);
+    if (p->tpRecvCountsOut == nullptr || p->expertIds == nullptr || p->gateLogits != nullptr) {
+        TILEXR_LOG(ERROR) << "EP dispatch with tensor parallelism needs tpRecvCountsOut and explicit expertIds (no fused routing)";
+        return TILEXR_ERROR_PARA_CHECK_FAIL;
+    }
+    int ret = ValidateTp(c, p->tpWorldSize, p->tpRankId, p->topK, p->moeExpertNum, p->sharedExpertRankNum, "EP dispatch");
+    if (ret != TILEXR_SUCCESS) return ret;
+    const int groups = c.rankSize / T;
+    const int perGroup = static_cast<int>(p->moeExpertNum / groups);
+    const bool routeMask = p->xActiveMask != nullptr && p->activeMaskType == TILEXR_EP_ACTIVE_MASK_EXPERT;
+    TpStaging st;
+    ret = StageTp(comm, false, p->bs * p->topK, T, true, p->expertScales != nullptr, routeMask, &st);
+    if (ret != TILEXR_SUCCESS) return ret;
+    cudaStream_t cs = static_cast<cudaStream_t>(stream);
+    if (EpTpExpand(p->expertIds, p->expertScales, routeMask ? reinterpret_cast<const uint8_t *>(p->xActiveMask) : nullptr, p->bs * p->topK, T,
+                   static_cast<int>(p->moeExpertNum), perGroup, st.ids, st.weights, st.mask, cs) != 0) {
+        return TILEXR_ERROR_RUNTIME;
+    }
+    TileXREpDispatchParams q = *p;
+    q.tpWorldSize = 1;
+    q.tpRankId = 0;
+    q.tpRecvCountsOut = nullptr;
+    q.topK = p->topK * T;
+    q.moeExpertNum = p->moeExpertNum * T;
+    q.expertIds = st.ids;
+    if (st.weights != nullptr) q.expertScales = st.weights;
+    if (routeMask) q.xActiveMask = reinterpret_cast<const bool *>(st.mask);
+    q.topkIdsOut = nullptr;           // [bs, topK] buffers of the caller: the kernel would write topK * T columns
+    q.topkWeightsOut = nullptr;
+    ret = TileXRMoeEpDispatchFused(&q, comm, stream);
+    if (ret != TILEXR_SUCCESS) return ret;
+    const int32_t *sendCounts = p->sendCountsOut;
+    int32_t *laneCounts = p->tpRecvCountsOut;
+    const int entries = perGroup * c.rankSize, R = c.rankSize;
+    return RunAfterLaunch(comm, [=]() { return EpTpLaneCounts(sendCounts, entries, R, T, laneCounts, cs) == 0 ? TILEXR_SUCCESS : TILEXR_ERROR_RUNTIME; });
+}
+
+int CombineWithTp(const TileXREpCombineParams *p, TileXRCommPtr comm, TileXRStream stream, const Ctx &c)
+{
+    const int T = static_cast<int>(p->tpWorldSize);
+    int ret = ValidateTp(c, p->tpWorldSize, p->tpRankId, p->topK, p->moeExpertNum, p->sharedExpertRankNum, "EP combine");
+    if (ret != TILEXR_SUCCESS) return ret;
+    const int groups = c.rankSize / T;
+    const int perGroup = static_cast<int>(p->moeExpertNum / groups);
+    const bool routeMask = p->xActiveMask != nullptr && p->activeMaskType == TILEXR_EP_ACTIVE_MASK_EXPERT;
+    TpStaging st;
+    ret = StageTp(comm, true, p->bs * p->topK, T, p->expertIds != nullptr, p->expertScales != nullptr, routeMask, &st);
+    if (ret != TILEXR_SUCCESS) return ret;
+    if (st.ids != nullptr || st.weights != nullptr || st.mask != nullptr) {
+        if (EpTpExpand(p->expertIds, p->expertScales, routeMask ? reinterpret_cast<const uint8_t *>(p->xActiveMask) : nullptr,
+                       p->bs * p->topK, T, static_cast<int>(p->moeExpertNum), perGroup, st.ids, st.weights, st.mask,
+                       static_cast<cudaStream_t>(stream)) != 0) {
+            return TILEXR_ERROR_RUNTIME;
+        }
+    }
+    TileXREpCombineParams q = *p;
+    q.tpWorldSize = 1;
+    q.tpRankId = 0;
+    q.topK = p->topK * T;
+    q.moeExpertNum = p->moeExpertNum * T;
+    if (st.ids != nullptr) q.expertIds = st.ids;
+    if (st.weights != nullptr) q.expertScales = st.weights;
+    if (routeMask) q.xActiveMask = reinterpret_cast<const bool *>(st.mask);
+    return TileXRMoeEpCombineFused(&q, comm, stream);
+}
+
 } // namespace
 
 extern "C" {
@@ -157,6 +277,7 @@ int TileXRMoeEpDispatchFused(const TileXREpDispatchParams *p, TileXRCommPtr comm
         TILEXR_LOG(ERROR) << "EP dispatch: null tensor";
         return TILEXR_ERROR_PARA_CHECK_FAIL;
     }
+    if (p->tpWorldSize > 1) return DispatchWithTp(p, comm, stream, c);
     if ((p->expertIds == nullptr) == (p->gateLogits == nullptr)) {
         TILEXR_LOG(ERROR) << "EP dispatch: give either expertIds or gateLogits";
         return TILEXR_ERROR_PARA_CHECK_FAIL;
@@ -320,6 +441,7 @@ int TileXRMoeEpCombineFused(const TileXREpCombineParams *p, TileXRCommPtr comm, 
         TILEXR_LOG(ERROR) << "EP combine: null tensor";
         return TILEXR_ERROR_PARA_CHECK_FAIL;
     }
+    if (p->tpWorldSize > 1) return CombineWithTp(p, comm, stream, c);
     ret = ValidateShape(p->bs, p->h, p->topK, p->moeExpertNum, c.rankSize, p->dtype);
     if (ret != TILEXR_SUCCESS) return ret;
     if (p->activeMaskType != TILEXR_EP_ACTIVE_MASK_NONE && p->xActiveMask == nullptr) return TILEXR_ERROR_PARA_CHECK_FAIL;
@@ -454,11 +576,7 @@ int TileXRMoeEpDispatchMemoryV2(void *x, int32_t *expertIds, void *scales, bool 
                                 int32_t *tpRecvCountsOut, void *expandScalesOut, TileXRDataType dtype,
                                 TileXRDataType expandXOutDtype, TileXRStream stream)
 {
-    (void)expertScales;
-    (void)tpRankId;
     (void)expertShardType;
-    (void)tpRecvCountsOut;
-    (void)expandScalesOut;
     Ctx c;
     int ret = Prepare(comm, &c);
     if (ret != TILEXR_SUCCESS) return ret;
@@ -466,11 +584,12 @@ int TileXRMoeEpDispatchMemoryV2(void *x, int32_t *expertIds, void *scales, bool 
         TILEXR_LOG(ERROR) << "EP dispatch: static scales are not supported (the reference rejects them too)";
         return TILEXR_ERROR_NOT_SUPPORT;
     }
-    if (tpWorldSize > 1) {
-        TILEXR_LOG(ERROR) << "EP dispatch: tpWorldSize must be 1";
-        return TILEXR_ERROR_NOT_SUPPORT;
+    // epWorldSize counts the ranks that exchange rows: all of them (every route reaches all lanes of its group), or, as the
+    // reference counts it, the expert groups
+    const int64_t T = tpWorldSize > 1 ? tpWorldSize : 1;
+    if (!((epWorldSize == c.rankSize && epRankId == c.rank) || (T > 1 && epWorldSize == c.rankSize / T && epRankId == c.rank / T))) {
+        return TILEXR_ERROR_PARA_CHECK_FAIL;
     }
-    if (epWorldSize != c.rankSize || epRankId != c.rank) return TILEXR_ERROR_PARA_CHECK_FAIL;
     if (globalBs != 0 && globalBs != bs * c.rankSize) {
         TILEXR_LOG(ERROR) << "EP dispatch: globalBs must be bs * epWorldSize";
         return TILEXR_ERROR_PARA_CHECK_FAIL;
@@ -497,7 +616,12 @@ int TileXRMoeEpDispatchMemoryV2(void *x, int32_t *expertIds, void *scales, bool 
     p.sharedExpertNum = sharedExpertNum;
     p.sharedExpertRankNum = sharedExpertRankNum;
     // worst case, as the reference sizes it: every token of every rank with all its routes on this rank
-    p.maxRecvRows = bs * c.rankSize * std::min<int64_t>(topK, moeExpertNum / std::max<int64_t>(1, c.rankSize - sharedExpertRankNum));
+    p.maxRecvRows = bs * c.rankSize * std::min<int64_t>(topK, moeExpertNum / std::max<int64_t>(1, c.rankSize / T - sharedExpertRankNum));
+    p.tpWorldSize = T;
+    p.tpRankId = tpRankId;
+    p.tpRecvCountsOut = tpRecvCountsOut;
+    p.expertScales = static_cast<const float *>(expertScales);
+    p.expandScalesOut = static_cast<float *>(expandScalesOut);
     p.expandXOut = expandXOut;
     p.dynamicScalesOut = static_cast<float *>(dynamicScalesOut);
     p.assistInfoForCombineOut = assistInfoForCombineOut;
@@ -556,20 +680,23 @@ int TileXRMoeEpCombineMemoryV2(void *expertOut, int32_t *assistInfoForCombine, i
                                int64_t sharedExpertNum, int64_t sharedExpertRankNum, int64_t quantMode, int64_t globalBs,
                                void *yOut, TileXRDataType dtype, TileXRStream stream)
 {
-    (void)tpRankId;
     (void)expertShardType;
     (void)globalBs;
     Ctx c;
     int ret = Prepare(comm, &c);
     if (ret != TILEXR_SUCCESS) return ret;
-    if (tpWorldSize > 1) return TILEXR_ERROR_NOT_SUPPORT;
+    const int64_t T = tpWorldSize > 1 ? tpWorldSize : 1;
     if (quantMode != TILEXR_EP_QUANT_NONE) {
         TILEXR_LOG(ERROR) << "EP combine: rows travel in their own dtype; communication quantisation is not supported";
         return TILEXR_ERROR_NOT_SUPPORT;
     }
-    if (epWorldSize != c.rankSize || epRankId != c.rank) return TILEXR_ERROR_PARA_CHECK_FAIL;
+    if (!((epWorldSize == c.rankSize && epRankId == c.rank) || (T > 1 && epWorldSize == c.rankSize / T && epRankId == c.rank / T))) {
+        return TILEXR_ERROR_PARA_CHECK_FAIL;
+    }
     TileXREpCombineParams p;
     std::memset(&p, 0, sizeof(p));
+    p.tpWorldSize = T;
+    p.tpRankId = tpRankId;
     p.expertOut = expertOut;
     p.assistInfoForCombine = assistInfoForCombine;
     p.sendCounts = sendCounts;

@@ -21,10 +21,12 @@
 #ifdef __cplusplus
 typedef TileXR::CommArgs TileXRCommArgs;
 typedef TileXR::TileXRRegistry TileXRRegistryT;
+typedef TileXR::TileXRPhysicalInfo TileXRPhysicalInfoT;
 extern "C" {
 #else
 typedef struct CommArgs TileXRCommArgs;
 typedef struct TileXRRegistry TileXRRegistryT;
+typedef struct TileXRPhysicalInfo TileXRPhysicalInfoT;
 #endif
 
 typedef uint8_t *GM_ADDR;
@@ -128,6 +130,15 @@ int TileXRNvlsAvailable(TileXRCommPtr comm);
 // Finds the registered region that contains [ptr, ptr+bytes); TILEXR_ERROR_NOT_FOUND if none.
 int TileXRFindRegistration(TileXRCommPtr comm, const void *ptr, size_t bytes, TileXRUDMAMemHandle *handle,
                            uint64_t *offset);
+
+// What the device is and how it reaches its peers, detected at initialisation (read-only queries): link kind, peer
+// atomics, multicast support, whether the window is bound to an NVLink multicast object.
+int TileXRGetPhysicalInfo(TileXRCommPtr comm, TileXRPhysicalInfoT *info);
+
+// At least `bytes` of device memory owned by the communicator (one buffer per communicator, grown on demand, kept until
+// the communicator is destroyed): staging for operators that would otherwise allocate per call.  Calls that use it are
+// ordered by the stream they run on; growing it waits for the device.
+int TileXRGetOperatorScratch(TileXRCommPtr comm, size_t bytes, void **ptr);
 
 // Host-initiated local copy on the communicator's copy-engine stream, ordered after the work
 // already queued on `stream` and before work queued on it later (SDMA analogue, host side).

@@ -74,6 +74,8 @@ enum TileXRExtraFlag {
     TILEXR_FLAG_DETERMINISTIC = 1u << 3,  // fixed-order reductions only (env LCCL_DETERMINISTIC)
     TILEXR_FLAG_SAME_PROCESS = 1u << 4,   // thread mode: peers are threads of this process
     TILEXR_FLAG_EMULATED = 1u << 5,       // several ranks share one GPU (test worlds)
+    TILEXR_FLAG_TOPO_NVLINK = 1u << 6,    // every peer link is NVLink (native peer atomics)
+    TILEXR_FLAG_TOPO_PCIE = 1u << 9,      // at least one peer is reached over PCIe peer-to-peer
     TILEXR_FLAG_RMA = 1u << 10,           // registered-memory put/get/signal available (UDMA analogue)
     TILEXR_FLAG_LOCAL_COPY = 1u << 11,    // device-initiated bulk local copy available (SDMA analogue)
     TILEXR_FLAG_MEMORY_ONLY = 1u << 18,   // memory domain: no signal plane users, no registry

@@ -89,6 +89,17 @@ typedef struct TileXREpDispatchParams {
     // topK + g and weight 1.  Per-rank outputs have one entry per expert the rank holds.
     int64_t sharedExpertNum;
     int64_t sharedExpertRankNum;
+    // Tensor parallelism inside expert parallelism (0 or 1 = none).  With tpWorldSize = T > 1 the ranks form R / T
+    // groups of T consecutive ranks that hold the same moeExpertNum / (R / T) experts (each a slice of their weights);
+    // tpRankId must be rank % T.  Every route is delivered to all T ranks of its expert's group, in one hop.  The
+    // per-route outputs and inputs then have T entries per route, slot k * T + l for lane l: routeRowsOut and the k
+    // field of the assist tuples use these slots, and the expert field holds the lane expert
+    // ((group * T + l) * expertsPerGroup + local expert).  expertTokenNumsOut has one entry per expert of the group,
+    // sendCountsOut expertsPerGroup * R.  tpRecvCountsOut [T] (required) receives the rows that came from the ranks
+    // of each lane.  Needs explicit expertIds, no shared-expert ranks, and topK * T <= 32.
+    int64_t tpWorldSize;
+    int64_t tpRankId;
+    int32_t *tpRecvCountsOut;
 } TileXREpDispatchParams;
 
 typedef struct TileXREpCombineParams {
@@ -112,6 +123,11 @@ typedef struct TileXREpCombineParams {
     const int32_t *assistExt;      // [rows, 2] from dispatch
     int64_t sharedExpertNum;       // as given to dispatch
     int64_t sharedExpertRankNum;
+    // As given to dispatch.  With tpWorldSize = T > 1 every rank of a group returns its partial output of each row and
+    // the origin adds the T of them: y = sum_k w[k] * sum_l partial(k, l).  expertIds, expertScales and an
+    // expert-type mask stay [bs, topK]; routeRows is dispatch's [bs, topK * T].
+    int64_t tpWorldSize;
+    int64_t tpRankId;
 } TileXREpCombineParams;
 
 int TileXRMoeEpDispatchFused(const TileXREpDispatchParams *params, TileXRCommPtr comm, TileXRStream stream);

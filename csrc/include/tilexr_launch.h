@@ -14,6 +14,9 @@
 
 #include <stddef.h>
 #include <stdint.h>
+#ifdef __cplusplus
+#include <functional>
+#endif
 
 #include "tilexr_api.h"
 
@@ -44,6 +47,11 @@ uint64_t LaunchCount();
 void NoteLaunch();
 
 // Largest grid of `kernel` that can be co-resident on the communicator's device.
+// Host work (typically a small follow-up kernel launch) that has to come after the launch that `comm` issued last.  On a
+// real communicator that launch is already in its stream and `fn` runs at once; a communicator of an emulated world only
+// queues its launches until the group closes, and `fn` runs right after that queued launch has been issued.
+int RunAfterLaunch(TileXRCommPtr comm, std::function<int()> fn);
+
 int MaxCooperativeGrid(TileXRCommPtr comm, const KernelEntry &kernel, unsigned block, size_t smemBytes, int ranksPerDevice,
                        unsigned *maxGrid);
 

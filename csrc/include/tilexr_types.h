@@ -45,6 +45,29 @@ enum TileXRDataType {
     TILEXR_DATA_TYPE_RESERVED = 255
 };
 
+// What the ranks of a communicator are connected by, and what the device offers (reference: PhysicalInfo with chip
+// name, physical link and core count, src/include/tilexr_types.h:90-94).
+enum TileXRPhysicalLink {
+    TILEXR_LINK_RESERVED = 0,
+    TILEXR_LINK_NVLINK = 1,        // every peer is load / store / atomic reachable over NVLink (one NVSwitch hop on B200)
+    TILEXR_LINK_PCIE = 2,          // peer access exists but without native atomics: PCIe peer-to-peer
+    TILEXR_LINK_SAME_DEVICE = 3,   // all ranks share one GPU (emulated worlds) or there is one rank
+    TILEXR_LINK_HOST_MEMORY = 4,   // CPU plumbing mode
+};
+
+struct TileXRPhysicalInfo {
+    int32_t link;                  // TileXRPhysicalLink, the weakest over all peers
+    int32_t ccMajor, ccMinor;      // compute capability (10.0 on B200)
+    uint32_t smCount;              // streaming multiprocessors ("core count")
+    uint32_t l2Bytes;
+    uint64_t memoryBytes;
+    int32_t p2pNativeAtomics;      // 1: atomics on peer memory are native on every link
+    int32_t p2pPerformanceRank;    // the largest (worst) CUDA performance rank over the peers, 0 = best
+    int32_t multicastSupported;    // the device can join NVLink multicast objects
+    int32_t nvlsBound;             // this communicator's window is bound to one (in-switch reductions are in use)
+    int32_t vmmWindow;             // the window was created with the virtual-memory API
+};
+
 enum TileXRReduceOp {
     TILEXR_REDUCE_SUM = 0,
     TILEXR_REDUCE_PROD = 1,

@@ -368,9 +368,11 @@ py::tuple EpDispatch(const CommPtr &c, const at::Tensor &x, const c10::optional<
                      const c10::optional<at::Tensor> &activeMask, int64_t topK, int64_t numExperts, int64_t quantMode,
                      int64_t scoreFunc, bool renormalize, double routedScale, int64_t tokenNumsType, int64_t maxRecvRows,
                      const c10::optional<at::Tensor> &expandXOut, const c10::optional<at::Tensor> &expertScales, bool dedup,
-                     const c10::optional<at::Tensor> &quantScales, int64_t sharedExpertNum, int64_t sharedExpertRankNum)
+                     const c10::optional<at::Tensor> &quantScales, int64_t sharedExpertNum, int64_t sharedExpertRankNum,
+                     int64_t tpWorldSize)
 {
     RequireContiguous(x, "x");
+    const int64_t T = tpWorldSize > 1 ? tpWorldSize : 1;
     Keep(expertScales);
     Keep(quantScales);
     TORCH_CHECK(x.dim() == 2 && x.is_cuda(), "x must be a 2-D CUDA tensor");
@@ -382,7 +384,8 @@ py::tuple EpDispatch(const CommPtr &c, const at::Tensor &x, const c10::optional<
     const int64_t bs = x.size(0), h = x.size(1);
     const int R = c->rankSize();
     TORCH_CHECK(sharedExpertRankNum >= 0 && sharedExpertRankNum < R, "shared_expert_rank_num must leave ranks for the routed experts");
-    const int64_t localExperts = c->rank() < sharedExpertRankNum ? 1 : numExperts / (R - sharedExpertRankNum);
+    TORCH_CHECK(R % T == 0, "tp_world_size must divide the number of ranks");
+    const int64_t localExperts = c->rank() < sharedExpertRankNum ? 1 : numExperts / (R / T - sharedExpertRankNum);
     auto i32 = x.options().dtype(at::kInt);
     const bool mx = quantMode == TileXREp::TILEXR_EP_QUANT_MXFP8_E4M3 || quantMode == TileXREp::TILEXR_EP_QUANT_MXFP8_E5M2;
     const bool int8 = quantMode == TileXREp::TILEXR_EP_QUANT_STATIC_INT8 || quantMode == TileXREp::TILEXR_EP_QUANT_DYNAMIC_INT8;
@@ -404,11 +407,15 @@ py::tuple EpDispatch(const CommPtr &c, const at::Tensor &x, const c10::optional<
     at::Tensor recvTotal = at::empty({1}, i32);
     at::Tensor topkIds = at::empty({bs, topK}, i32);
     at::Tensor topkWeights = at::empty({bs, topK}, x.options().dtype(at::kFloat));
-    at::Tensor routeRows = at::empty({bs, topK + sharedExpertNum}, i32);
+    at::Tensor routeRows = at::empty({bs, topK * T + sharedExpertNum}, i32);
     at::Tensor assistExt = at::empty({maxRecvRows, 2}, i32);
     at::Tensor expandScales = at::empty({maxRecvRows}, x.options().dtype(at::kFloat));
+    at::Tensor tpRecvCounts = at::zeros({T}, i32);
     TileXREpDispatchParams p;
     std::memset(&p, 0, sizeof(p));
+    p.tpWorldSize = T;
+    p.tpRankId = c->rank() % T;
+    p.tpRecvCountsOut = T > 1 ? tpRecvCounts.data_ptr<int32_t>() : nullptr;
     p.x = x.data_ptr();
     if (expertIds.has_value() && expertIds->defined()) {
         TORCH_CHECK(expertIds->scalar_type() == at::kInt && expertIds->is_contiguous(), "expert_ids must be contiguous int32");
@@ -460,12 +467,12 @@ py::tuple EpDispatch(const CommPtr &c, const at::Tensor &x, const c10::optional<
     p.sharedExpertRankNum = sharedExpertRankNum;
     p.dtype = ToDtype(x.scalar_type());
     for (const at::Tensor &t : {expandX, scales, assist, tokenNums, sendCounts, recvTotal, topkIds, topkWeights, routeRows,
-                                assistExt, expandScales}) {
+                                assistExt, expandScales, tpRecvCounts}) {
         Keep(t);
     }
     Check(TileXRMoeEpDispatchFused(&p, c->ptr(), StreamOf(x)), "TileXRMoeEpDispatchFused");
     return py::make_tuple(expandX, hasScales ? py::cast(scales) : py::none(), assist, tokenNums, sendCounts, recvTotal, topkIds,
-                          topkWeights, routeRows, assistExt, expandScales);
+                          topkWeights, routeRows, assistExt, expandScales, tpRecvCounts);
 }
 
 at::Tensor EpCombine(const CommPtr &c, const at::Tensor &expertOut, const at::Tensor &assist, const at::Tensor &sendCounts,
@@ -473,8 +480,9 @@ at::Tensor EpCombine(const CommPtr &c, const at::Tensor &expertOut, const at::Te
                      const c10::optional<at::Tensor> &activeMask, const c10::optional<at::Tensor> &sharedExpertX, int64_t bs,
                      int64_t topK, int64_t numExperts, const c10::optional<at::Tensor> &yOut,
                      const c10::optional<at::Tensor> &routeRows, const c10::optional<at::Tensor> &assistExt, bool dedup,
-                     int64_t sharedExpertNum, int64_t sharedExpertRankNum)
+                     int64_t sharedExpertNum, int64_t sharedExpertRankNum, int64_t tpWorldSize)
 {
+    const int64_t T = tpWorldSize > 1 ? tpWorldSize : 1;
     Keep(assistExt);
     RequireContiguous(expertOut, "expert_out");
     Keep(routeRows);
@@ -502,8 +510,8 @@ at::Tensor EpCombine(const CommPtr &c, const at::Tensor &expertOut, const at::Te
     p.sharedExpertX = PtrOrNull(sharedExpertX);
     if (routeRows.has_value() && routeRows->defined()) {
         TORCH_CHECK(routeRows->scalar_type() == at::kInt && routeRows->is_contiguous() &&
-                        routeRows->numel() == bs * (topK + sharedExpertNum),
-                    "route_rows must be contiguous int32 [bs, top_k + shared_expert_num]");
+                        routeRows->numel() == bs * (topK * T + sharedExpertNum),
+                    "route_rows must be contiguous int32 [bs, top_k * tp_world_size + shared_expert_num]");
         p.routeRows = routeRows->data_ptr<int32_t>();
     }
     if (assistExt.has_value() && assistExt->defined()) {
@@ -513,6 +521,8 @@ at::Tensor EpCombine(const CommPtr &c, const at::Tensor &expertOut, const at::Te
     p.dedup = dedup ? 1 : 0;
     p.sharedExpertNum = sharedExpertNum;
     p.sharedExpertRankNum = sharedExpertRankNum;
+    p.tpWorldSize = T;
+    p.tpRankId = c->rank() % T;
     p.bs = bs;
     p.h = h;
     p.topK = topK;
@@ -641,6 +651,23 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m)
         .def("is_registered", &Comm::IsRegistered)
         .def("multicast_ptr", &Comm::MulticastPtr)
         .def("nvls_available", &Comm::NvlsAvailable)
+        .def("physical_info", [](const Comm &c) {
+            TileXRPhysicalInfoT ph{};
+            Check(TileXRGetPhysicalInfo(c.ptr(), &ph), "TileXRGetPhysicalInfo");
+            static const char *links[] = {"reserved", "nvlink", "pcie", "same_device", "host_memory"};
+            py::dict d;
+            d["link"] = links[ph.link >= 0 && ph.link <= 4 ? ph.link : 0];
+            d["compute_capability"] = py::make_tuple(ph.ccMajor, ph.ccMinor);
+            d["sm_count"] = ph.smCount;
+            d["l2_bytes"] = ph.l2Bytes;
+            d["memory_bytes"] = ph.memoryBytes;
+            d["p2p_native_atomics"] = ph.p2pNativeAtomics != 0;
+            d["p2p_performance_rank"] = ph.p2pPerformanceRank;
+            d["multicast_supported"] = ph.multicastSupported != 0;
+            d["nvls_bound"] = ph.nvlsBound != 0;
+            d["vmm_window"] = ph.vmmWindow != 0;
+            return d;
+        })
         .def("destroy", &Comm::Destroy);
     m.def("init_process", &InitProcess, py::arg("rank"), py::arg("world_size"), py::arg("comm_id") = "", py::arg("domain") = 0,
           py::arg("buffer_mb") = 0, py::arg("device") = -1);
@@ -673,12 +700,13 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m)
           py::arg("renormalize") = true, py::arg("routed_scale") = 1.0, py::arg("token_nums_type") = 1,
           py::arg("max_recv_rows") = 0, py::arg("expand_x_out") = py::none(), py::arg("expert_scales") = py::none(),
           py::arg("dedup") = false, py::arg("scales") = py::none(), py::arg("shared_expert_num") = 0,
-          py::arg("shared_expert_rank_num") = 0);
+          py::arg("shared_expert_rank_num") = 0, py::arg("tp_world_size") = 1);
     m.def("ep_combine", &EpCombine, py::arg("comm"), py::arg("expert_out"), py::arg("assist"), py::arg("send_counts"),
           py::arg("expert_ids") = py::none(), py::arg("expert_scales") = py::none(), py::arg("active_mask") = py::none(),
           py::arg("shared_expert_x") = py::none(), py::arg("bs") = 0, py::arg("top_k") = 1, py::arg("num_experts") = 1,
           py::arg("y_out") = py::none(), py::arg("route_rows") = py::none(), py::arg("assist_ext") = py::none(),
-          py::arg("dedup") = false, py::arg("shared_expert_num") = 0, py::arg("shared_expert_rank_num") = 0);
+          py::arg("dedup") = false, py::arg("shared_expert_num") = 0, py::arg("shared_expert_rank_num") = 0,
+          py::arg("tp_world_size") = 1);
     m.def("routing_topk", &RoutingTopK, py::arg("gate_logits"), py::arg("selection_bias") = py::none(), py::arg("top_k") = 1,
           py::arg("score_func") = 0, py::arg("renormalize") = true, py::arg("routed_scale") = 1.0);
     m.def("fp8_quant_1x128", &Fp8Quant);

@@ -405,3 +405,63 @@ def test_moe_layer_matches_a_dense_reference(txr, fp8):
     got = y.cpu().float()
     assert torch.allclose(got, want, rtol=3e-2, atol=3e-3), (got - want).abs().max()
     comm.destroy()
+
+
+@pytest.mark.parametrize("dedup", [False, True])
+def test_ep_with_tensor_parallel_groups(txr, dedup):
+    """tpWorldSize 2 on four ranks: two expert groups of two ranks.  Every route reaches both ranks of its group, sorted
+    by local expert; the lane counts come back; combine adds the two partial outputs of every row."""
+    from tilexr_b200.ops import ep
+    from tilexr_b200.utils import oracle
+
+    ranks, T, bs, h, experts, top_k = 4, 2, 24, 512, 8, 2
+    groups, per = ranks // T, experts // (ranks // T)
+    world = txr.init_emulated_world(ranks, device=0, buffer_mb=64)
+    g = torch.Generator().manual_seed(5)
+    xs = [torch.randn(bs, h, generator=g).to(torch.bfloat16) for _ in range(ranks)]
+    routed = [oracle.routing_topk_ref(torch.randn(bs, experts, generator=g), top_k, 1, True, 1.0) for _ in range(ranks)]
+    ids, ws = [r[0] for r in routed], [r[1] for r in routed]
+    ids[1][3, 1] = -1                                     # an inactive route
+    res = world.run(lambda c, r: ep.dispatch(c, xs[r].cuda(), expert_ids=ids[r].cuda(), expert_scales=ws[r].cuda(),
+                                             num_experts=experts, top_k=top_k, tp_world_size=T, dedup=dedup))
+    world.check()
+    # the same dispatch stated on lane experts: route (t, k) -> slots k * T + l on expert ((group * T + l) * per + local)
+    wide = []
+    for r in range(ranks):
+        e = ids[r].long()
+        lane = torch.arange(T).view(1, 1, T)
+        v = ((e // per).unsqueeze(-1) * T + lane) * per + (e % per).unsqueeze(-1)
+        v = torch.where(e.unsqueeze(-1) >= 0, v, torch.full_like(v, -1))
+        wide.append(v.reshape(bs, top_k * T).to(torch.int32))
+    ref = oracle.ep_dispatch_ref(xs, wide, experts * T)
+    for r in range(ranks):
+        d = res[r]
+        n = int(d.recv_total.item())
+        assert n == len(ref[r]["rows"]) and n > 0
+        assert torch.equal(d.assist[:n].cpu(), ref[r]["assist"])
+        assert torch.equal(d.expand_x[:n].cpu(), ref[r]["expand_x"])
+        assert torch.equal(d.expert_token_nums.cpu(), ref[r]["token_nums"]) and d.expert_token_nums.numel() == per
+        assert torch.equal(d.send_counts.cpu(), ref[r]["send_counts"])
+        by_lane = [sum(1 for (s, _, _, _) in ref[r]["rows"] if s % T == l) for l in range(T)]
+        assert d.tp_recv_counts.cpu().tolist() == by_lane
+        # both ranks of a group hold the same rows
+        mate = res[r ^ 1]
+        assert torch.equal(mate.expand_x[:n].cpu(), d.expand_x[:n].cpu())
+    # each rank returns its "partial output": the row scaled by a factor of its own
+    factor = [1.0 + r / 8 for r in range(ranks)]
+    outs = [(res[r].expand_x.float() * factor[r]).to(torch.bfloat16) for r in range(ranks)]
+    ys = world.run(lambda c, r: ep.combine(c, outs[r], res[r], expert_scales=ws[r].cuda()))
+    world.check()
+    for r in range(ranks):
+        want = torch.zeros(bs, h)
+        for t in range(bs):
+            for k in range(top_k):
+                e = int(ids[r][t, k])
+                if e < 0:
+                    continue
+                for l in range(T):
+                    owner = (e // per) * T + l
+                    want[t] += float(ws[r][t, k]) * (xs[r][t].float() * factor[owner]).to(torch.bfloat16).float()
+        got = ys[r].cpu().float()
+        assert torch.allclose(got, want, rtol=2e-2, atol=2e-2), (got - want).abs().max()
+    world.destroy()

@@ -22,6 +22,9 @@ def _worker(rank, world, port, q):
         from tilexr_b200.utils import oracle
 
         comm = txr.init_process(rank, world, comm_id=f"127.0.0.1:{port}", buffer_mb=128, device=rank)
+        info = comm.physical_info()
+        assert info["link"] == "nvlink" and info["p2p_native_atomics"] and info["compute_capability"] == (10, 0) and info["sm_count"] == 148
+        assert info["nvls_bound"] == comm.nvls_available()
         gens = [torch.Generator().manual_seed(100 + r) for r in range(world)]
         xs = [torch.randn(1 << 18, generator=g).to(torch.bfloat16) for g in gens]
         mine = xs[rank].cuda()

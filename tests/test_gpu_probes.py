@@ -20,6 +20,8 @@ def test_put_signal_and_get_between_emulated_ranks(txr):
     C = txr._C
     ranks = 4
     world = txr.init_emulated_world(ranks, device=0, buffer_mb=16)
+    info = world[0].physical_info()
+    assert info["link"] == "same_device" and info["compute_capability"][0] >= 10 and info["sm_count"] > 0 and not info["nvls_bound"]
     n = 1 << 20
     region = world.symm_empty((n,), torch.int32)
     handles = [0] * ranks      # first registration on every rank

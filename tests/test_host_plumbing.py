@@ -26,6 +26,7 @@ def _worker(rank, world, port, scenario, result_queue):
 
         comm = txr.init_from_torch_distributed(host_memory=True, buffer_mb=64)
         assert comm.rank == rank and comm.world_size == world
+        assert comm.physical_info()["link"] == "host_memory" and not comm.physical_info()["nvls_bound"]
         g = torch.Generator().manual_seed(1234 + rank)
         if scenario == "allgather":
             x = torch.randn(1 << 20, generator=g)            # 4 MiB fp32
