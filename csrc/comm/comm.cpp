@@ -332,11 +332,6 @@ int TileXRComm::ExchangeWindows()
     int ret = exchange_->AllGather(&mine, all.data(), sizeof(PeerInfo));
     if (ret != TILEXR_SUCCESS) return ret;
     peerWindows_.assign(rankSize_, nullptr);
-    {
-        std::vector<int> peerDevices(rankSize_);
-        for (int r = 0; r < rankSize_; ++r) peerDevices[r] = all[r].device;
-        DetectTopology(peerDevices);
-    }
     for (int i = 0; i < rankSize_; ++i) {
         const int r = (rank_ + i) % rankSize_;
         const PeerInfo &p = all[r];
@@ -445,6 +440,14 @@ int TileXRComm::Init(std::unique_ptr<Exchange> exchange)
     }
     TXR_CUDA(cudaGetDevice(&device_));
     TXR_CUDA(cudaFree(nullptr));             // the device's context exists before any driver call
+    {
+        // which device every rank sits on, for the link description (both window paths below need it)
+        std::vector<int32_t> devices(rankSize_);
+        const int32_t mine = device_;
+        ret = exchange_->AllGather(&mine, devices.data(), sizeof(int32_t));
+        if (ret != TILEXR_SUCCESS) return ret;
+        DetectTopology(std::vector<int>(devices.begin(), devices.end()));
+    }
     ret = TryVmmWindow();
     if (ret == TILEXR_ERROR_NOT_SUPPORT) {
         ret = AllocateWindow();

@@ -887,7 +887,19 @@ __device__ __forceinline__ void CombineSendPart(const EpCombineArgs &a, CommArgs
 #pragma unroll
             for (int u = 0; u < 8; ++u) st_vec16(dst + static_cast<int64_t>(v + u * 32) * 16, q[u]);
         }
-        for (; v < vEnd; v += 32) st_vec16(dst + static_cast<int64_t>(v) * 16, ld_vec16_stream(src + static_cast<int64_t>(v) * 16));
+        // the rest of the row (fewer than eight vectors per lane) in rounds of four with the missing ones switched off;
+        // one vector at a time it would cost a round trip each
+        for (; v < vEnd; v += 4 * 32) {
+            Vec16 q[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                if (v + u * 32 < vEnd) q[u] = ld_vec16_stream(src + static_cast<int64_t>(v + u * 32) * 16);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                if (v + u * 32 < vEnd) st_vec16(dst + static_cast<int64_t>(v + u * 32) * 16, q[u]);
+            }
+        }
     } else {
         // The rows of this token on this rank, in k order, times their gate weights: lane i keeps member i of
         // the chain, then every 16-byte column is summed in fp32 and rounded once.

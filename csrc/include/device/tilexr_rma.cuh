@@ -88,7 +88,9 @@ TXR_D void CopyLanes(void *dst, const void *src, uint64_t bytes, int lane, int l
 
 // The same copy with eight 16-byte transfers in flight per thread, for stores that cross NVLink while many other
 // ranks do the same (an all-to-all): an acknowledgement then takes several microseconds, and a warp has to cover that
-// time with bytes on the way.  Both addresses 16-byte aligned, `bytes` a multiple of 16.
+// time with bytes on the way.  What is left after the full rounds (fewer than eight vectors per thread) goes in rounds
+// of four with the missing ones switched off: one vector at a time, the second half of a 7 KB row on one warp would
+// cost six round trips.  Both addresses 16-byte aligned, `bytes` a multiple of 16.
 TXR_D void CopyLanesDeep(void *dst, const void *src, uint64_t bytes, int lane, int lanes)
 {
     uint8_t *d = reinterpret_cast<uint8_t *>(dst);
@@ -106,7 +108,23 @@ TXR_D void CopyLanesDeep(void *dst, const void *src, uint64_t bytes, int lane, i
 #endif
         for (int u = 0; u < 8; ++u) st_vec16(d + (i + static_cast<uint64_t>(u) * lanes) * 16, q[u]);
     }
-    for (; i < vecs; i += lanes) st_vec16(d + i * 16, ld_vec16_stream(s + i * 16));
+    for (; i < vecs; i += 4ull * lanes) {
+        Vec16 q[4];
+#if TXR_ON_DEVICE
+#pragma unroll
+#endif
+        for (int u = 0; u < 4; ++u) {
+            const uint64_t k = i + static_cast<uint64_t>(u) * lanes;
+            if (k < vecs) q[u] = ld_vec16_stream(s + k * 16);
+        }
+#if TXR_ON_DEVICE
+#pragma unroll
+#endif
+        for (int u = 0; u < 4; ++u) {
+            const uint64_t k = i + static_cast<uint64_t>(u) * lanes;
+            if (k < vecs) st_vec16(d + k * 16, q[u]);
+        }
+    }
 }
 
 // put: local -> peer region.  Non-blocking: returns when the stores are issued.

@@ -461,7 +461,7 @@ int TileXRMoonEpPrefetchWeightV1(const TileXRMoonEpPrefetchWeightArgsV1 *args, T
     }
     a.comm = reinterpret_cast<CommArgs *>(c.devArgs);
     unsigned grid = 0;
-    ret = CoopGrid(args->comm, c, MoonPrefetchKernelEntry(), 0, EnvLong("TILEXR_MOONEP_PREFETCH_BLOCK_DIM", 64), &grid);
+    ret = CoopGrid(args->comm, c, MoonPrefetchKernelEntry(), 0, EnvLong("TILEXR_MOONEP_PREFETCH_BLOCK_DIM", 128), &grid);
     if (ret != TILEXR_MOONEP_SUCCESS) return ret;
     int64_t magic = 0;
     if (TileXRCommNextMagic(args->comm, &magic) != TILEXR_SUCCESS) return TILEXR_MOONEP_ERROR_INTERNAL;
@@ -495,7 +495,7 @@ static int LaunchReduceGrad(TileXRCommPtr comm, const TileXRMoonEpPlanV1 *p, con
     if (!any) return TILEXR_MOONEP_ERROR_INVALID_ARGUMENT;
     a.comm = reinterpret_cast<CommArgs *>(c.devArgs);
     unsigned grid = 0;
-    ret = CoopGrid(comm, c, MoonReduceGradKernelEntry(), 0, EnvLong("TILEXR_MOONEP_REDUCE_GRAD_BLOCK_DIM", 64), &grid);
+    ret = CoopGrid(comm, c, MoonReduceGradKernelEntry(), 0, EnvLong("TILEXR_MOONEP_REDUCE_GRAD_BLOCK_DIM", 148), &grid);
     if (ret != TILEXR_MOONEP_SUCCESS) return ret;
     int64_t magic = 0;
     if (TileXRCommNextMagic(comm, &magic) != TILEXR_SUCCESS) return TILEXR_MOONEP_ERROR_INTERNAL;
@@ -536,7 +536,7 @@ int TileXRMoonEpReduceGradGetWorkspaceSizeV2(const TileXRMoonEpReduceGradWorkspa
         info->projectionQpCounts[i] = 1;
     }
     info->qpCount = 3;
-    info->blockDim = static_cast<uint32_t>(EnvLong("TILEXR_MOONEP_REDUCE_GRAD_BLOCK_DIM", 64));
+    info->blockDim = static_cast<uint32_t>(EnvLong("TILEXR_MOONEP_REDUCE_GRAD_BLOCK_DIM", 148));
     return TILEXR_MOONEP_SUCCESS;
 }
 

@@ -196,6 +196,7 @@ __device__ void MoonDispatchBody(const MoonDispatchArgs &a)
 {
     __shared__ unsigned int sPeerRows[TILEXR_MAX_RANK_SIZE];     // rows this block sent to each rank (for the trace)
     __shared__ int sBad;                                         // 1 + index of a route whose destination is impossible
+    __shared__ unsigned int sCleared;                            // padding rows this block cleared (for the trace)
     Waiter w;
     bool ok = KernelPrologue(w, a.comm, a.magic, TILEXR_OP_MOONEP_DISPATCH, a.N, true);
     ok = PlanUsable(w, a.status, ok);
@@ -214,6 +215,7 @@ __device__ void MoonDispatchBody(const MoonDispatchArgs &a)
         MoonTraceBegin(trace);
         MoonTraceEnd(trace, TILEXR_MOONEP_TRACE_PLAN_CHECK, TILEXR_MOONEP_TRACE_NO_PEER, 0, 0);
         sBad = 0;
+        sCleared = 0;
     }
     for (int r = threadIdx.x; r < R; r += blockDim.x) sPeerRows[r] = 0;
     __syncthreads();
@@ -221,18 +223,24 @@ __device__ void MoonDispatchBody(const MoonDispatchArgs &a)
     if (ok) {
         // padding rows are cleared by their owner; they never overlap a delivered row
         MoonTraceBegin(trace);
-        uint64_t cleared = 0;
-        for (int g = blockIdx.x; g < a.groups; g += gridDim.x) {
+        // (all warps of the grid share the rows of every range: the range behind the last expert holds the whole unused
+        // capacity, tens of megabytes that one block alone would take longer to clear than the sends take)
+        const int64_t vecsPerRow = a.rowBytes / 16;
+        unsigned int mine = 0;
+        for (int g = 0; g < a.groups; ++g) {
             const int64_t first = a.zeroFill[g * 2];
             const int64_t rows = a.zeroFill[g * 2 + 1];
-            uint8_t *p = a.hiddenOut + first * a.rowBytes;
             const Vec16 z{0, 0, 0, 0};
-            for (int64_t v = threadIdx.x; v < rows * a.rowBytes / 16; v += blockDim.x) st_vec16(p + v * 16, z);
-            if (a.weightsOut != nullptr) {
-                for (int64_t i = threadIdx.x; i < rows; i += blockDim.x) a.weightsOut[first + i] = 0.f;
+            for (int64_t r = gwarp; r < rows; r += nWarps) {
+                uint8_t *p = a.hiddenOut + (first + r) * a.rowBytes;
+                for (int64_t v = lane; v < vecsPerRow; v += 32) st_vec16(p + v * 16, z);
+                if (lane == 0 && a.weightsOut != nullptr) a.weightsOut[first + r] = 0.f;
+                mine += 1;
             }
-            cleared += static_cast<uint64_t>(rows);
         }
+        if (lane == 0 && mine != 0) atomicAdd(&sCleared, mine);
+        __syncthreads();
+        const uint64_t cleared = sCleared;
         MoonTraceEnd(trace, TILEXR_MOONEP_TRACE_ZERO_FILL, rank, cleared * a.rowBytes, static_cast<uint32_t>(cleared));
         MoonTraceBegin(trace);
         for (int64_t i = gwarp; i < a.N; i += nWarps) {
@@ -325,17 +333,35 @@ __device__ void MoonCombineBody(const MoonCombineArgs &a)
     const int K = a.K;
 
     if (ok) {
-        for (int64_t s = gwarp; s < a.NvS; s += nWarps) {
-            const int32_t v = a.dstLocal[s];
-            if (v < 0) continue;
-            const int src = v / a.N;
-            const int64_t route = v - src * a.N;
-            if (src >= comm->rankSize) continue;
-            uint8_t *peerHalf = DataHalf(comm, src, epoch);
-            CopyLanes(peerHalf + route * a.rowBytes, a.hiddenNvs + s * a.rowBytes, a.rowBytes, lane, 32);
-            if (lane == 0 && a.weightsNvs != nullptr) reinterpret_cast<float *>(peerHalf + a.weightWinOff)[route] = a.weightsNvs[s];
+        // A warp returns four rows, then one lane orders them all with ONE system-scope fence and raises their four flags.
+        // (A release store per row makes the warp wait for that row's stores to be acknowledged by the peer before it
+        // may start the next row: several microseconds of an idle warp per 14 KB.)
+        constexpr int ROWS_PER_FENCE = 4;
+        for (int64_t base = gwarp * ROWS_PER_FENCE; base < a.NvS; base += nWarps * ROWS_PER_FENCE) {
+            uint64_t *flags[ROWS_PER_FENCE];
+#pragma unroll
+            for (int g = 0; g < ROWS_PER_FENCE; ++g) {
+                flags[g] = nullptr;
+                const int64_t s = base + g;
+                if (s >= a.NvS) continue;
+                const int32_t v = a.dstLocal[s];
+                if (v < 0) continue;
+                const int src = v / a.N;
+                const int64_t route = v - src * a.N;
+                if (src >= comm->rankSize) continue;
+                uint8_t *peerHalf = DataHalf(comm, src, epoch);
+                CopyLanesDeep(peerHalf + route * a.rowBytes, a.hiddenNvs + s * a.rowBytes, a.rowBytes, lane, 32);
+                if (lane == 0 && a.weightsNvs != nullptr) reinterpret_cast<float *>(peerHalf + a.weightWinOff)[route] = a.weightsNvs[s];
+                flags[g] = FlagSlot(comm, src, TILEXR_FLAG_SLOT_BASE + route);
+            }
             __syncwarp();
-            if (lane == 0) SetFlag(FlagSlot(comm, src, TILEXR_FLAG_SLOT_BASE + route), epoch, 1);
+            if (lane == 0) {
+                fence_acq_rel_sys();
+#pragma unroll
+                for (int g = 0; g < ROWS_PER_FENCE; ++g) {
+                    if (flags[g] != nullptr) st_relaxed_sys_u64(flags[g], MakeFlag(epoch, 1));
+                }
+            }
         }
         const uint8_t *half = DataHalf(comm, rank, epoch);
         const int vecs = a.rowBytes / 16;
@@ -411,7 +437,7 @@ __device__ void MoonPrefetchBody(const MoonPrefetchArgs &a)
                     if (item % gridDim.x != blockIdx.x) continue;
                     const uint64_t off = c * CHUNK;
                     const uint64_t n = min(CHUNK, t.rowBytes - off);
-                    CopyLanes(dst + off, src + off, n, threadIdx.x, blockDim.x);
+                    CopyLanesDeep(dst + off, src + off, n, threadIdx.x, blockDim.x);     // eight 16-byte loads per thread in flight
                 }
             }
         }
@@ -432,7 +458,84 @@ __device__ void MoonReduceGradBody(const MoonReduceGradArgs &a)
     const int rank = comm->rank;
     const int R = comm->rankSize;
     const uint32_t epoch = w.epoch;
-    if (ok) {
+    // Who borrowed which of this rank's experts: per local expert the (source rank, slot) pairs in ascending order, built once
+    // per block in shared memory (the table has R * B entries; scanning it per vector, as a first version did, kept the
+    // kernel at a fifth of the link).
+    constexpr int MAX_SOURCES = 2048, MAX_LOCAL = 256;
+    __shared__ int sFirst[MAX_LOCAL + 1];
+    __shared__ int sSource[MAX_SOURCES];           // source rank << 16 | slot
+    const int entries = R * a.B;
+    const bool tabled = a.L <= MAX_LOCAL && entries <= MAX_SOURCES;
+    if (ok && tabled) {
+        for (int l = threadIdx.x; l < a.L; l += blockDim.x) {
+            int n = 0;
+            for (int i = 0; i < entries; ++i) n += (a.expertsToCopy[i] == rank * a.L + l && i / a.B != rank) ? 1 : 0;
+            sFirst[l + 1] = n;
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            sFirst[0] = 0;
+            for (int l = 0; l < a.L; ++l) sFirst[l + 1] += sFirst[l];
+        }
+        __syncthreads();
+        for (int l = threadIdx.x; l < a.L; l += blockDim.x) {
+            int at = sFirst[l];
+            for (int i = 0; i < entries; ++i) {
+                if (a.expertsToCopy[i] == rank * a.L + l && i / a.B != rank) sSource[at++] = ((i / a.B) << 16) | (i % a.B);
+            }
+        }
+        __syncthreads();
+    }
+    if (ok && tabled) {
+        for (int ti = 0; ti < 3; ++ti) {
+            const MoonTensorRef &t = a.tensors[ti];
+            if (!t.valid) continue;
+            const uint64_t vecsPerRow = t.rowBytes / 16;
+            uint8_t *const *peerBase = comm->registryPtr->regions[t.handle].peerBase;
+            for (int l = 0; l < a.L; ++l) {
+                const int s0 = sFirst[l], s1 = sFirst[l + 1];
+                if (s0 == s1) continue;
+                uint8_t *dst = t.local + static_cast<uint64_t>(l) * t.rowBytes;
+                // four vectors per thread and step: the owner's and every borrower's copy of them are in flight together
+                constexpr int U = 4;
+                const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
+                for (uint64_t v0 = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; v0 < vecsPerRow; v0 += stride * U) {
+                    float f[U][4];
+#pragma unroll
+                    for (int u = 0; u < U; ++u) {
+                        const uint64_t v = min(v0 + u * stride, vecsPerRow - 1);
+                        const Vec16 acc = ld_vec16(dst + v * 16);
+                        f[u][0] = __uint_as_float(acc.x);
+                        f[u][1] = __uint_as_float(acc.y);
+                        f[u][2] = __uint_as_float(acc.z);
+                        f[u][3] = __uint_as_float(acc.w);
+                    }
+                    for (int si = s0; si < s1; ++si) {
+                        const int src = sSource[si] >> 16, slot = sSource[si] & 0xffff;
+                        const uint8_t *p = peerBase[src] + t.offset + static_cast<uint64_t>(a.L + slot) * t.rowBytes;
+                        Vec16 x[U];
+#pragma unroll
+                        for (int u = 0; u < U; ++u) x[u] = ld_vec16_stream(p + min(v0 + u * stride, vecsPerRow - 1) * 16);
+#pragma unroll
+                        for (int u = 0; u < U; ++u) {
+                            f[u][0] += __uint_as_float(x[u].x);
+                            f[u][1] += __uint_as_float(x[u].y);
+                            f[u][2] += __uint_as_float(x[u].z);
+                            f[u][3] += __uint_as_float(x[u].w);
+                        }
+                    }
+#pragma unroll
+                    for (int u = 0; u < U; ++u) {
+                        const uint64_t v = v0 + u * stride;
+                        if (v < vecsPerRow) {
+                            st_vec16(dst + v * 16, Vec16{__float_as_uint(f[u][0]), __float_as_uint(f[u][1]), __float_as_uint(f[u][2]), __float_as_uint(f[u][3])});
+                        }
+                    }
+                }
+            }
+        }
+    } else if (ok) {
+        // tables beyond the shared-memory lists: scan the table per vector
         for (int ti = 0; ti < 3; ++ti) {
             const MoonTensorRef &t = a.tensors[ti];
             if (!t.valid) continue;
@@ -440,14 +543,14 @@ __device__ void MoonReduceGradBody(const MoonReduceGradArgs &a)
             for (int l = 0; l < a.L; ++l) {
                 const int e = rank * a.L + l;
                 bool any = false;
-                for (int i = 0; i < R * a.B && !any; ++i) any = a.expertsToCopy[i] == e && i / a.B != rank;
+                for (int i = 0; i < entries && !any; ++i) any = a.expertsToCopy[i] == e && i / a.B != rank;
                 if (!any) continue;
                 uint8_t *dst = t.local + static_cast<uint64_t>(l) * t.rowBytes;
                 for (uint64_t v = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; v < vecsPerRow;
                      v += static_cast<uint64_t>(gridDim.x) * blockDim.x) {
                     Vec16 acc = ld_vec16(dst + v * 16);
                     float f[4] = {__uint_as_float(acc.x), __uint_as_float(acc.y), __uint_as_float(acc.z), __uint_as_float(acc.w)};
-                    for (int i = 0; i < R * a.B; ++i) {
+                    for (int i = 0; i < entries; ++i) {
                         if (a.expertsToCopy[i] != e) continue;
                         const int src = i / a.B;
                         const int b = i - src * a.B;

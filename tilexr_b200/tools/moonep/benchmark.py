@@ -69,7 +69,9 @@ def summarise(case: MoonEPCase, samples: Mapping[str, Sequence[float]], bytes_by
                       "B": case.prefetch_slots, "dtype": case.dtype}}
 
 
-def benchmark_case(comm, case: MoonEPCase, iters: int = 20, warmup: int = 5, sample_dir: str = "") -> Dict[str, object]:
+def benchmark_case(comm, case: MoonEPCase, iters: int = 20, warmup: int = 5, sample_dir: str = "", trace: bool = False) -> Dict[str, object]:
+    """``trace``: one more dispatch after the timed loop records the kernel's event trace; the result then carries this
+    rank's per-phase summary (``dispatch_phases``: count, mean and longest duration, bytes) beside the stage times."""
     rank = comm.rank
     buf = TileXRMoonEPBuffer(comm, case.tokens, case.hidden, case.top_k, case.experts, token_padding=case.token_padding,
                              B=case.prefetch_slots, dtype=case.torch_dtype())
@@ -116,6 +118,13 @@ def benchmark_case(comm, case: MoonEPCase, iters: int = 20, warmup: int = 5, sam
     grad_row = 0 if grads is None else _row_bytes(grads.gate) + _row_bytes(grads.up) + _row_bytes(grads.down)
     nbytes = algorithm_bytes(plan, rank, case.hidden * esize, 4, proj_row, grad_row)
     out = summarise(case, samples, nbytes, iters, warmup, dev)
+    if trace:
+        from .dispatch_trace import phase_summary
+
+        recorder = buf.dispatch_trace(iterations=1, event_capacity=64, blocks=256)
+        buf.dispatch(inp.hidden_sh, inp.route_weights_sk, plan, trace=recorder)
+        buf.synchronize()
+        out["dispatch_phases"] = phase_summary(recorder.decode())
     if sample_dir:
         report.write_jsonl(f"{sample_dir}/rank{rank}.jsonl", report.rank_sample_rows(case.name, rank, samples, nbytes))
     buf.close()

@@ -33,6 +33,7 @@ def main(argv=None) -> int:
     ap.add_argument("--json", default="")
     ap.add_argument("--csv", default="", help="benchmark modes: one row per (case, stage) with P50 / P99")
     ap.add_argument("--samples", default="", help="benchmark: directory for per-rank sample files; aggregate: where to read them")
+    ap.add_argument("--trace", action="store_true", help="benchmark: also record the dispatch kernel's event trace once per case and print its phases")
     ap.add_argument("--buffer-mb", type=int, default=0, help="communicator window size (default: sized for the largest case)")
     args = ap.parse_args(argv)
 
@@ -96,7 +97,7 @@ def main(argv=None) -> int:
             if rank == 0:
                 print(report.correctness_markdown(results))
         else:
-            run = {"benchmark": lambda c: benchmark_case(comm, c, iters=args.iters, warmup=args.warmup, sample_dir=args.samples),
+            run = {"benchmark": lambda c: benchmark_case(comm, c, iters=args.iters, warmup=args.warmup, sample_dir=args.samples, trace=args.trace),
                    "prefetch": lambda c: prefetch_weight_benchmark(comm, c, iters=args.iters, warmup=args.warmup),
                    "reduce-grad": lambda c: reduce_grad_benchmark(comm, c, iters=args.iters, warmup=args.warmup)}[args.mode]
             for c in cases:
@@ -107,6 +108,10 @@ def main(argv=None) -> int:
                 failed |= r.get("verified") is False
             if rank == 0:
                 print(report.benchmark_markdown(results))
+                for r in results:
+                    for ph in r.get("dispatch_phases", []):
+                        print(f"{r['case']} dispatch phase {ph['phase']}: {ph['count']} events, mean {ph['mean_us']:.1f} us, "
+                              f"longest {ph['max_us']:.1f} us, {ph['bytes'] / 1e6:.1f} MB, {ph['rows']} rows")
                 if args.csv:
                     report.write_stage_csv(args.csv, results)
     if args.json and rank == 0:
