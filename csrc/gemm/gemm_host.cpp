@@ -533,4 +533,163 @@ int TileXRMatmulReduceScatter(const void *a, const void *b, void *partialStaging
     return LaunchKernel(comm, GemmEntry(), &g, cfg, stream);
 }
 
+// ---- block-scaled fp8 with the collectives of a tensor-parallel layer ----------------------------------------------------
+
+static const KernelEntry &GemmFp8BlockEntry()
+{
+    static const KernelEntry e = {GemmFp8BlockKernel(), GemmFp8BlockKernelEmulated(), sizeof(GemmBlockArgs), "TileXRGemmFp8BlockScaled"};
+    return e;
+}
+
+static int Fp8BlockFusedGrid(TileXRCommPtr comm, const TileXRCommArgs *hostArgs, unsigned *grid)
+{
+    const int ranksPerDevice = (hostArgs->extraFlag & TILEXR_FLAG_EMULATED) ? hostArgs->rankSize : 1;
+    unsigned maxGrid = 0;
+    int ret = MaxCooperativeGrid(comm, GemmFp8BlockEntry(), GEMM_FP8_BLOCK_THREADS, GEMM_FP8_BLOCK_SMEM_BYTES, ranksPerDevice, &maxGrid);
+    if (ret != TILEXR_SUCCESS) return ret;
+    maxGrid &= ~1u;
+    if (maxGrid < 2) {
+        TILEXR_LOG(ERROR) << "fused block-scaled GEMM needs at least one co-resident CTA pair per rank";
+        return TILEXR_ERROR_NOT_SUPPORT;
+    }
+    *grid = static_cast<unsigned>(std::min<long>(maxGrid, EnvLong("TILEXR_GEMM_CTAS", maxGrid))) & ~1u;
+    return TILEXR_SUCCESS;
+}
+
+static int Fp8BlockCommon(GemmBlockArgs *g, const void *b, const float *scaleB, int64_t m, int64_t n, int64_t k, TileXRDataType inDtype,
+                          TileXRDataType outDtype, int64_t shardRows, int R, const char *what)
+{
+    if ((inDtype != TILEXR_DATA_TYPE_FP8E4M3 && inDtype != TILEXR_DATA_TYPE_FP8E5M2) ||
+        (outDtype != TILEXR_DATA_TYPE_FP16 && outDtype != TILEXR_DATA_TYPE_BFP16)) {
+        TILEXR_LOG(ERROR) << what << ": operands e4m3 or e5m2, output fp16 or bf16";
+        return TILEXR_ERROR_PARA_CHECK_FAIL;
+    }
+    if (k % 128 != 0 || n % 8 != 0 || shardRows % (2 * GEMM_BM) != 0 || (reinterpret_cast<uintptr_t>(b) & 15u) != 0 || scaleB == nullptr) {
+        TILEXR_LOG(ERROR) << what << ": K a multiple of 128, N a multiple of 8, rows per rank a multiple of " << 2 * GEMM_BM;
+        return TILEXR_ERROR_PARA_CHECK_FAIL;
+    }
+    int ret = MakeMap8(&g->tmapB, b, n, k, GEMM_BN / 2);
+    if (ret != TILEXR_SUCCESS) return ret;
+    g->scaleB = scaleB;
+    g->M = static_cast<int32_t>(m);
+    g->N = static_cast<int32_t>(n);
+    g->K = static_cast<int32_t>(k);
+    g->nBlocks = static_cast<int32_t>((n + GEMM_BN - 1) / GEMM_BN);
+    g->kBlocks = static_cast<int32_t>(k / 128);
+    g->scaleBRows = static_cast<int32_t>((n + 127) / 128);
+    g->rasterGroup = static_cast<int32_t>(std::max<long>(1, EnvLong("TILEXR_GEMM_GROUP", 8)));
+    g->isBf16 = outDtype == TILEXR_DATA_TYPE_BFP16 ? 1u : 0u;
+    g->fp8Format = inDtype == TILEXR_DATA_TYPE_FP8E5M2 ? 2 : 1;
+    g->shardRows = static_cast<int32_t>(shardRows);
+    g->blocksPerShard = static_cast<int32_t>(shardRows / GEMM_BM);
+    g->flagStride = TILEXR_MAX_RANK_SIZE * TILEXR_FLAGS_PER_PAIR / R;
+    return TILEXR_SUCCESS;
+}
+
+int TileXRAllGatherMatmulFp8Block(const void *aShard, const float *scaleAShard, void *aStaging, float *scaleStaging, const void *b,
+                                  const float *scaleB, void *c, int64_t shardRows, int64_t n, int64_t k, TileXRDataType inDtype,
+                                  TileXRDataType outDtype, TileXRCommPtr comm, TileXRStream stream)
+{
+    TileXRCommArgs *hostArgs = nullptr;
+    GM_ADDR devArgs = nullptr;
+    int ret = FusedCommon(comm, &hostArgs, &devArgs);
+    if (ret != TILEXR_SUCCESS) return ret;
+    const int R = hostArgs->rankSize;
+    const int64_t m = shardRows * R;
+    if (aShard == nullptr || scaleAShard == nullptr || aStaging == nullptr || scaleStaging == nullptr || b == nullptr || c == nullptr ||
+        shardRows <= 0 || n <= 0 || k <= 0 ||
+        ((reinterpret_cast<uintptr_t>(aShard) | reinterpret_cast<uintptr_t>(scaleAShard) | reinterpret_cast<uintptr_t>(c)) & 15u) != 0) {
+        TILEXR_LOG(ERROR) << "all-gather block-scaled matmul: null or misaligned tensor";
+        return TILEXR_ERROR_PARA_CHECK_FAIL;
+    }
+    GemmBlockArgs g;
+    std::memset(&g, 0, sizeof(g));
+    ret = Fp8BlockCommon(&g, b, scaleB, m, n, k, inDtype, outDtype, shardRows, R, "all-gather block-scaled matmul");
+    if (ret != TILEXR_SUCCESS) return ret;
+    if ((k / 128 * 4) % 16 != 0) {
+        TILEXR_LOG(ERROR) << "all-gather block-scaled matmul: K must be a multiple of 512 (rows of the scale table travel in 16-byte pieces)";
+        return TILEXR_ERROR_PARA_CHECK_FAIL;
+    }
+    if (g.blocksPerShard >= g.flagStride) {
+        TILEXR_LOG(ERROR) << "all-gather block-scaled matmul: " << shardRows << " rows per rank exceed the per-pair flag space";
+        return TILEXR_ERROR_NOT_SUPPORT;
+    }
+    TileXRUDMAMemHandle aHandle = 0, sHandle = 0;
+    uint64_t aOffset = 0, sOffset = 0;
+    if (TileXRFindRegistration(comm, aStaging, static_cast<size_t>(m) * k, &aHandle, &aOffset) != TILEXR_SUCCESS ||
+        TileXRFindRegistration(comm, scaleStaging, static_cast<size_t>(m) * (k / 128) * 4, &sHandle, &sOffset) != TILEXR_SUCCESS) {
+        TILEXR_LOG(ERROR) << "all-gather block-scaled matmul: both staging buffers must be registered on every rank (TileXRSymmAlloc)";
+        return TILEXR_ERROR_PARA_CHECK_FAIL;
+    }
+    ret = MakeMap8(&g.tmapA, aStaging, m, k, GEMM_BM);
+    if (ret != TILEXR_SUCCESS) return ret;
+    g.scaleA = scaleStaging;
+    g.c = static_cast<uint8_t *>(c);
+    g.mode = GEMM_ALL_GATHER;
+    g.comm = reinterpret_cast<CommArgs *>(devArgs);
+    g.aLocal = static_cast<const uint8_t *>(aShard);
+    g.scaleALocal = scaleAShard;
+    g.aHandle = aHandle;
+    g.aOffset = aOffset;
+    g.sHandle = sHandle;
+    g.sOffset = sOffset;
+    unsigned grid = 0;
+    ret = Fp8BlockFusedGrid(comm, hostArgs, &grid);
+    if (ret != TILEXR_SUCCESS) return ret;
+    int64_t magic = 0;
+    ret = TileXRCommNextMagic(comm, &magic);
+    if (ret != TILEXR_SUCCESS) return ret;
+    g.magic = magic;
+    LaunchConfig cfg{grid, GEMM_FP8_BLOCK_THREADS, GEMM_FP8_BLOCK_SMEM_BYTES, true};
+    return LaunchKernel(comm, GemmFp8BlockEntry(), &g, cfg, stream);
+}
+
+int TileXRMatmulReduceScatterFp8Block(const void *a, const float *scaleA, const void *b, const float *scaleB, void *partialStaging, void *out,
+                                      int64_t shardRows, int64_t n, int64_t k, TileXRDataType inDtype, TileXRDataType outDtype,
+                                      TileXRCommPtr comm, TileXRStream stream)
+{
+    TileXRCommArgs *hostArgs = nullptr;
+    GM_ADDR devArgs = nullptr;
+    int ret = FusedCommon(comm, &hostArgs, &devArgs);
+    if (ret != TILEXR_SUCCESS) return ret;
+    const int R = hostArgs->rankSize;
+    const int64_t m = shardRows * R;
+    if (a == nullptr || scaleA == nullptr || b == nullptr || partialStaging == nullptr || out == nullptr || shardRows <= 0 || n <= 0 || k <= 0 ||
+        ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(out)) & 15u) != 0) {
+        TILEXR_LOG(ERROR) << "block-scaled matmul reduce-scatter: null or misaligned tensor";
+        return TILEXR_ERROR_PARA_CHECK_FAIL;
+    }
+    GemmBlockArgs g;
+    std::memset(&g, 0, sizeof(g));
+    ret = Fp8BlockCommon(&g, b, scaleB, m, n, k, inDtype, outDtype, shardRows, R, "block-scaled matmul reduce-scatter");
+    if (ret != TILEXR_SUCCESS) return ret;
+    if (static_cast<int64_t>(g.blocksPerShard) * g.nBlocks >= g.flagStride) {
+        TILEXR_LOG(ERROR) << "block-scaled matmul reduce-scatter: " << g.blocksPerShard * g.nBlocks << " tiles per owner exceed the per-pair flag space";
+        return TILEXR_ERROR_NOT_SUPPORT;
+    }
+    TileXRUDMAMemHandle handle = 0;
+    uint64_t offset = 0;
+    if (TileXRFindRegistration(comm, partialStaging, static_cast<size_t>(m) * n * 2, &handle, &offset) != TILEXR_SUCCESS) {
+        TILEXR_LOG(ERROR) << "block-scaled matmul reduce-scatter: the staging buffer must be registered on every rank (TileXRSymmAlloc)";
+        return TILEXR_ERROR_PARA_CHECK_FAIL;
+    }
+    ret = MakeMap8(&g.tmapA, a, m, k, GEMM_BM);
+    if (ret != TILEXR_SUCCESS) return ret;
+    g.scaleA = scaleA;
+    g.c = static_cast<uint8_t *>(out);
+    g.mode = GEMM_REDUCE_SCATTER;
+    g.comm = reinterpret_cast<CommArgs *>(devArgs);
+    g.outHandle = handle;
+    g.outOffset = offset;
+    unsigned grid = 0;
+    ret = Fp8BlockFusedGrid(comm, hostArgs, &grid);
+    if (ret != TILEXR_SUCCESS) return ret;
+    int64_t magic = 0;
+    ret = TileXRCommNextMagic(comm, &magic);
+    if (ret != TILEXR_SUCCESS) return ret;
+    g.magic = magic;
+    LaunchConfig cfg{grid, GEMM_FP8_BLOCK_THREADS, GEMM_FP8_BLOCK_SMEM_BYTES, true};
+    return LaunchKernel(comm, GemmFp8BlockEntry(), &g, cfg, stream);
+}
+
 } // extern "C"

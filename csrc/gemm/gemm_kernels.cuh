@@ -96,9 +96,23 @@ struct GemmBlockArgs {
     int32_t rasterGroup;
     uint32_t isBf16;
     int32_t fp8Format;        // 1 = e4m3, 2 = e5m2
+    // Fused modes (GemmMode).  ALL_GATHER: tmapA and scaleA describe THIS rank's staging buffers ([R * shardRows, K] rows,
+    // [R * shardRows, K / 128] scales, both registered on every rank); every rank writes its shard and the shard's
+    // scales into all of them while the tiles are computed, and a tile starts when the flag of its 128 rows is up.
+    // REDUCE_SCATTER: every 128 x 256 partial tile is stored into the row owner's partial staging buffer
+    // ([R, shardRows, N] 16-bit, registered) and the owner adds the R partials in rank order into c [shardRows, N].
+    int32_t mode;
+    CommArgs *comm;
+    int64_t magic;
+    const uint8_t *aLocal;    // all-gather: [shardRows, K]
+    const float *scaleALocal; // all-gather: [shardRows, K / 128]
+    uint32_t aHandle, sHandle, outHandle;
+    uint64_t aOffset, sOffset, outOffset;
+    int32_t shardRows, blocksPerShard, flagStride;
 };
 
 const void *GemmFp8BlockKernel();
+const void *GemmFp8BlockKernelEmulated();
 const void *GemmKernelSingle();
 const void *GemmKernelEmulated();
 const void *GemmPairKernel();

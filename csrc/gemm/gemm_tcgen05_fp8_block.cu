@@ -22,6 +22,20 @@
 //                   registers per thread (one row of the CTA's 128, 128 columns), release the scratch buffer;
 //                   at the end of a tile they round to the output type and store through a swizzled staging tile.
 //
+// Fused with the collectives of a tensor-parallel layer (mode of GemmBlockArgs):
+//
+//   all-gather -> GEMM    warps 2-3 of EVERY CTA, idle otherwise, write this rank's shard of A (fp8 rows and their
+//                   scales) into all ranks' staging buffers, 128 rows at a time, and raise the piece's flag: through
+//                   the NVLink multicast alias of the staging buffer where the runtime has one (multimem.st: one
+//                   store, the switch replicates it), else with one store per peer.  No SM is set aside for
+//                   communication.  The TMA lane of a CTA acquires the flag of its 128 rows before the first load of a
+//                   tile (TMA then reads LOCAL memory, without multicast); each promoter warp acquires it before it
+//                   reads the rows' scales.  Every rank walks the shards starting with its own.
+//   GEMM -> reduce-scatter    the promoters store their 128 x 256 partial tile into the row owner's staging slot and
+//                   raise the tile's flag; when a CTA has run out of tiles its promoters add, in rank order, the
+//                   R partial tiles of the output tiles it owns.  Every rank starts with the rows of the next rank
+//                   and ends with its own.
+//
 // Every mbarrier wait is bounded; on a give-up all roles fall through to the tear-down, tensor memory is released
 // and `status` tells the host.  The numerics reference is the fp32 product of the dequantised operands
 // (reference numerics of the block scales: src/ep/kernels/tilexr_ep_mxfp8_quant.h:36-168 for the exponent form,
@@ -30,6 +44,7 @@
 #include <cuda_fp16.h>
 
 #include "device/tilexr_rma.cuh"
+#include "device/tilexr_sync.cuh"
 #include "gemm_kernels.cuh"
 #include "tilexr_types.h"
 
@@ -44,6 +59,37 @@ constexpr int FB_SCRATCH = 4;               // scratch accumulators: two blocks 
 constexpr uint32_t FB_PEER_BIT_MASK = 0xFEFFFFFFu;
 constexpr int FB_HALF_N = GEMM_BN / 2;       // columns of one scratch accumulator
 constexpr int FB_MAX_KB = 256;               // blocks of K whose weight scales fit the shared-memory copy (K up to 32768)
+constexpr int FB_FLAG_PLANE_A = TILEXR_FLAG_DATA_BASE;    // all-gather: piece (source rank, 128-row block) has landed
+constexpr int FB_FLAG_PLANE_B = TILEXR_FLAG_ACK_BASE;     // reduce-scatter: partial tile (source rank, tile) has landed
+
+__device__ __forceinline__ void FbMultimemSt(uint8_t *p, const Vec16 &v)
+{
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+// `bytes` (a multiple of 16) from local memory to `dst`, four vectors per thread in flight (the pushing warps live on the 88 registers of the first warpgroup); `multicast` stores through
+// an NVLink multicast address (every rank's copy at once).
+__device__ __forceinline__ void FbPush(uint8_t *dst, const uint8_t *src, uint64_t bytes, int lane, int lanes, bool multicast)
+{
+    const uint64_t vecs = bytes / 16;
+    for (uint64_t i = lane; i < vecs; i += 4ull * lanes) {
+        Vec16 q[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const uint64_t k = i + static_cast<uint64_t>(u) * lanes;
+            if (k < vecs) q[u] = ld_vec16_stream(src + k * 16);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const uint64_t k = i + static_cast<uint64_t>(u) * lanes;
+            if (k < vecs) {
+                if (multicast) FbMultimemSt(dst + k * 16, q[u]);
+                else st_vec16(dst + k * 16, q[u]);
+            }
+        }
+    }
+}
+
 
 struct BlockState {
     uint64_t full[GEMM_FP8_BLOCK_STAGES];       // leader: both CTAs' loads of a stage have landed
@@ -52,6 +98,7 @@ struct BlockState {
     uint64_t scratchEmpty[FB_SCRATCH];     // leader: the eight promoter warps of scratch s (four per CTA) have read it
     uint32_t tmemBase;
     volatile int abortFlag;
+    uint32_t epoch;                        // fused modes: the epoch of this launch (kept here, not in every thread's registers)
 };
 
 __device__ __forceinline__ uint32_t FbCtaRank()
@@ -173,6 +220,26 @@ __device__ __forceinline__ bool FbWaitBar(uint64_t *bar, uint32_t parity, BlockS
     }
 }
 
+// Bounded acquire of a flag by one thread that has no Waiter of its own (the promoters are short of registers).
+__device__ __forceinline__ bool FbAcquireFlag(const uint64_t *flag, uint64_t want, BlockState *st, uint64_t budgetNs)
+{
+    uint64_t deadline = 0;
+    uint32_t polls = 0;
+    while (ld_acquire_sys_u64(flag) < want) {
+        if ((++polls & 63u) == 0) {
+            if (st->abortFlag != 0) return false;
+            const uint64_t t = now_ns();
+            if (deadline == 0) {
+                deadline = t + budgetNs;
+            } else if (t > deadline) {
+                st->abortFlag = 1;
+                return false;
+            }
+        }
+    }
+    return true;
+}
+
 __device__ __forceinline__ uint32_t FbPackPair(float lo, float hi, bool bf16)
 {
     if (bf16) {
@@ -195,11 +262,23 @@ __device__ __forceinline__ void FbTileAt(int t, int mTiles, int nBlocks, int GRO
     *nBlock = u / size;
 }
 
+// Tile t of this pair's walk.  In the fused modes the 256-row blocks are rotated so that every rank starts with its own
+// shard (all-gather: its rows are there first) or with the next rank's (reduce-scatter: its own rows come last, when the
+// peers' partial tiles have had time to arrive).
+__device__ __forceinline__ void FbTileOf(const GemmBlockArgs &a, int t, int mTiles, int rank, int *mTile, int *nBlock)
+{
+    FbTileAt(t, mTiles, a.nBlocks, a.rasterGroup, mTile, nBlock);
+    if (a.mode != GEMM_PLAIN) {
+        const int pairsPerShard = a.blocksPerShard / 2;
+        const int first = (a.mode == GEMM_ALL_GATHER ? rank : rank + 1) * pairsPerShard;
+        *mTile = (*mTile + first) % mTiles;
+    }
+}
+
 // Twelve warps start with 168 registers each (the most a block of this size can have); the first warpgroup then
 // shrinks to 88 and the two promoter warpgroups grow to 200, so that 128 accumulators and two 32-register
 // tensor-memory reads fit without spilling.
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_FP8_BLOCK_THREADS, 1)
-TileXRGemmFp8BlockScaled(const __grid_constant__ GemmBlockArgs a)
+__device__ __forceinline__ void FbBody(const GemmBlockArgs &a)
 {
     extern __shared__ uint8_t smemRaw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smemRaw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -211,8 +290,30 @@ TileXRGemmFp8BlockScaled(const __grid_constant__ GemmBlockArgs a)
     const int lane = threadIdx.x & 31;
     const uint32_t ctaRank = FbCtaRank();
     const bool leader = ctaRank == 0;
-    const uint64_t budgetNs = 4000000000ull;
+    const bool fused = a.mode != GEMM_PLAIN;
     const uint32_t peerAbortAddr = FbMapToCta(SmemAddr(const_cast<int *>(&st->abortFlag)), ctaRank ^ 1u);
+
+    // The promoters have no register to spare for values that only the prologue, the TMA lane and the epilogue need: the
+    // launch's epoch lives in shared memory, and rank, rank count and the wait budget are read where they are used.
+    bool ok = true;
+    if (fused) {
+        // The staging buffers are not double buffered: nobody writes into a peer's before that peer has finished the
+        // previous launch on this communicator.
+        Waiter w = MakeWaiter(a.comm, a.magic, blockIdx.x);
+        const int rank = a.comm->rank;
+        const int ranks = a.comm->rankSize;
+        if (threadIdx.x == 0) st->epoch = w.epoch;
+        if (blockIdx.x == 0 && threadIdx.x == 0) {
+            a.comm->dfx[TILEXR_DFX_MAGIC] = w.epoch;
+            a.comm->dfx[TILEXR_DFX_OP] = a.mode == GEMM_ALL_GATHER ? TILEXR_OP_ALL_GATHER_MATMUL : TILEXR_OP_MATMUL_REDUCE_SCATTER;
+            a.comm->dfx[TILEXR_DFX_RUN_STATUS] = TILEXR_RUN_STARTED;
+        }
+        bool g = true;
+        if (w.epoch >= 2 && static_cast<int>(threadIdx.x) < ranks && static_cast<int>(threadIdx.x) != rank) {
+            g = WaitPeerFinished(w, threadIdx.x, w.epoch - 1);
+        }
+        ok = BlockBroadcastOk(g);
+    }
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < GEMM_FP8_BLOCK_STAGES; ++s) {
@@ -223,7 +324,7 @@ TileXRGemmFp8BlockScaled(const __grid_constant__ GemmBlockArgs a)
             MbarInit(&st->scratchFull[h], 1);     // one commit
             MbarInit(&st->scratchEmpty[h], 8);    // four promoter warps in each of the two CTAs
         }
-        st->abortFlag = 0;
+        st->abortFlag = ok ? 0 : 1;
         MbarInitFence();
         asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&a.tmapA)) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&a.tmapB)) : "memory");
@@ -251,12 +352,26 @@ TileXRGemmFp8BlockScaled(const __grid_constant__ GemmBlockArgs a)
     if (warp == 0) {
         // ---- TMA producer -----------------------------------------------------------------------------------------
         if (lane == 0) {
+            const uint64_t budgetNs = fused ? a.comm->waitTimeoutNs : 4000000000ull;
+            const int rank = fused ? a.comm->rank : 0;
+            Waiter w{fused ? a.comm : nullptr, st->epoch, static_cast<int32_t>(blockIdx.x), TILEXR_DEV_OK, 0};
             uint32_t stage = 0, phase = 0;
             for (int t = pair; t < totalTiles && st->abortFlag == 0; t += nPairs) {
                 int mTile, nBlock;
-                FbTileAt(t, mTiles, a.nBlocks, a.rasterGroup, &mTile, &nBlock);
+                FbTileOf(a, t, mTiles, rank, &mTile, &nBlock);
                 const int rowA = mTile * 2 * GEMM_BM + static_cast<int>(ctaRank) * GEMM_BM;
                 const int rowB = nBlock * GEMM_BN + static_cast<int>(ctaRank) * (GEMM_BN / 2);
+                if (a.mode == GEMM_ALL_GATHER) {
+                    // this CTA's 128 rows of the gathered A: wait until their owner has written them here
+                    const int block = rowA / GEMM_BM;
+                    const int shard = block / a.blocksPerShard;
+                    const int64_t slot = FB_FLAG_PLANE_A + static_cast<int64_t>(shard) * a.flagStride + (block - shard * a.blocksPerShard);
+                    if (!WaitFlagGE(w, FlagSlot(a.comm, rank, slot), 1, shard, slot)) {
+                        st->abortFlag = 1;
+                        break;
+                    }
+                    fence_proxy_async();       // the rows were written by generic-proxy stores, TMA reads them next
+                }
                 bool broke = false;
                 for (int kb = 0; kb < a.kBlocks; ++kb) {
                     if (!FbWaitBar(&st->empty[stage], phase ^ 1u, st, peerAbortAddr, budgetNs)) {
@@ -279,6 +394,7 @@ TileXRGemmFp8BlockScaled(const __grid_constant__ GemmBlockArgs a)
     } else if (warp == 1) {
         // ---- MMA issuer: per block of K, one N = 128 group into each scratch accumulator ----------------------------
         if (leader && lane == 0) {
+            const uint64_t budgetNs = fused ? a.comm->waitTimeoutNs : 4000000000ull;
             const uint32_t idesc = FbInstrDesc(a.fp8Format);
             uint32_t stage = 0, phase = 0;
             uint32_t sPhase = 0;                   // bit s: parity of the next wait on scratchEmpty[s]
@@ -320,6 +436,41 @@ TileXRGemmFp8BlockScaled(const __grid_constant__ GemmBlockArgs a)
                 if (broke) break;
             }
         }
+    } else if (a.mode == GEMM_ALL_GATHER && ok) {
+        // ---- warps 2-3: write this rank's shard, rows and scales, into every rank's staging buffers -------------------
+        const int pt2 = static_cast<int>(threadIdx.x) - 64;           // 0..63
+        const int rank = a.comm->rank, ranks = a.comm->rankSize;
+        const uint32_t epoch = st->epoch;
+        const TileXRRegistry *reg = a.comm->registryPtr;
+        uint8_t *mcRows = reg->regions[a.aHandle].mcBase;
+        uint8_t *mcScales = reg->regions[a.sHandle].mcBase;
+        const bool multicast = ranks > 1 && mcRows != nullptr && mcScales != nullptr;
+        const int pieces = a.blocksPerShard;
+        const int items = multicast ? pieces : ranks * pieces;
+        const uint64_t rowBytes = static_cast<uint64_t>(a.K);
+        const uint64_t scaleRowBytes = static_cast<uint64_t>(a.kBlocks) * 4;
+        for (int it = blockIdx.x; it < items; it += gridDim.x) {
+            const int piece = it % pieces;
+            const int peer = (rank - it / pieces + ranks) % ranks;          // itself first, then rank-1 (which needs it next), ...
+            const uint64_t srcRow = static_cast<uint64_t>(piece) * GEMM_BM;
+            const uint64_t dstRow = static_cast<uint64_t>(rank) * a.shardRows + srcRow;
+            uint8_t *rowsTo = (multicast ? mcRows : reg->regions[a.aHandle].peerBase[peer]) + a.aOffset + dstRow * rowBytes;
+            uint8_t *scalesTo = (multicast ? mcScales : reg->regions[a.sHandle].peerBase[peer]) + a.sOffset + dstRow * scaleRowBytes;
+            FbPush(rowsTo, a.aLocal + srcRow * rowBytes, GEMM_BM * rowBytes, pt2, 64, multicast);
+            FbPush(scalesTo, reinterpret_cast<const uint8_t *>(a.scaleALocal) + srcRow * scaleRowBytes, GEMM_BM * scaleRowBytes, pt2, 64, multicast);
+            asm volatile("bar.sync 2, 64;" ::: "memory");
+            if (pt2 == 0) {
+                fence_acq_rel_sys();
+                const uint64_t up = MakeFlag(epoch, 1);
+                const int64_t slot = FB_FLAG_PLANE_A + static_cast<int64_t>(rank) * a.flagStride + piece;
+                if (multicast) {
+                    for (int r = 0; r < ranks; ++r) st_relaxed_sys_u64(FlagSlot(a.comm, r, slot), up);
+                } else {
+                    st_relaxed_sys_u64(FlagSlot(a.comm, peer, slot), up);
+                }
+            }
+            asm volatile("bar.sync 2, 64;" ::: "memory");
+        }
     }
     } else {
         asm volatile("setmaxnreg.inc.sync.aligned.u32 200;" ::: "memory");
@@ -335,9 +486,11 @@ TileXRGemmFp8BlockScaled(const __grid_constant__ GemmBlockArgs a)
         int kbAll = 0;
         const int KB = a.kBlocks;
         const bool vec4 = (KB & 3) == 0;           // rows of the scale tables are 16-byte aligned: four blocks per load
+        const bool gathered = a.mode == GEMM_ALL_GATHER;
+        const uint64_t budgetNs = fused ? a.comm->waitTimeoutNs : 4000000000ull;
         for (int t = pair; t < totalTiles; t += nPairs) {
             int mTile, nBlock;
-            FbTileAt(t, mTiles, a.nBlocks, a.rasterGroup, &mTile, &nBlock);
+            FbTileOf(a, t, mTiles, fused ? a.comm->rank : 0, &mTile, &nBlock);
             const int64_t row0 = static_cast<int64_t>(mTile) * 2 * GEMM_BM + static_cast<int64_t>(ctaRank) * GEMM_BM;
             const int64_t gRow = row0 + myRow;
             const bool rowValid = gRow < a.M;
@@ -357,12 +510,30 @@ TileXRGemmFp8BlockScaled(const __grid_constant__ GemmBlockArgs a)
             for (int i = pt; i < 2 * KB && i < 2 * FB_MAX_KB; i += 256) {
                 sScaleB[i] = __ldg((i < KB ? sb0 + i : sb1 + (i - KB)));
             }
+            if (gathered) {
+                // the scales of these 128 rows were written by their owner during this launch: acquire the rows' flag first
+                if (lane == 0) {
+                    const int block = static_cast<int>(row0 / GEMM_BM);
+                    const int shard = block / a.blocksPerShard;
+                    const int64_t slot = FB_FLAG_PLANE_A + static_cast<int64_t>(shard) * a.flagStride + (block - shard * a.blocksPerShard);
+                    FbAcquireFlag(FlagSlot(a.comm, a.comm->rank, slot), MakeFlag(st->epoch, 1), st, budgetNs);
+                }
+                __syncwarp();
+            }
             asm volatile("bar.sync 1, 256;" ::: "memory");
             const bool bInSmem = KB <= FB_MAX_KB;
             float4 curA = make_float4(0.f, 0.f, 0.f, 0.f), nxtA = curA;
             auto loadGroup = [&](int kb0, float4 &ga) {
                 if (!rowValid) {
                     ga = make_float4(0.f, 0.f, 0.f, 0.f);
+                } else if (gathered) {
+                    // written during this launch: through L2, never through the read-only path
+                    if (vec4) {
+                        ga = __ldcg(reinterpret_cast<const float4 *>(saRow + kb0));
+                    } else {
+                        ga = make_float4(__ldcg(saRow + min(kb0, KB - 1)), __ldcg(saRow + min(kb0 + 1, KB - 1)), __ldcg(saRow + min(kb0 + 2, KB - 1)),
+                                         __ldcg(saRow + min(kb0 + 3, KB - 1)));
+                    }
                 } else if (vec4) {
                     ga = __ldg(reinterpret_cast<const float4 *>(saRow + kb0));
                 } else {
@@ -421,8 +592,19 @@ TileXRGemmFp8BlockScaled(const __grid_constant__ GemmBlockArgs a)
             if (sExit != 0) break;
             (void)alive;
             // ---- store the tile: the two groups take turns with the staging tile, everybody stores ---------------------
-            const int rowsValid = static_cast<int>(max(static_cast<int64_t>(0), min(static_cast<int64_t>(GEMM_BM), a.M - row0)));
+            int rowsValid = static_cast<int>(max(static_cast<int64_t>(0), min(static_cast<int64_t>(GEMM_BM), a.M - row0)));
             uint8_t *rowBase = a.c + static_cast<uint64_t>(row0) * a.N * 2;
+            int owner = 0, tileLocal = 0;
+            if (a.mode == GEMM_REDUCE_SCATTER) {
+                // the partial tile goes into the row owner's staging slot for this rank
+                const int block = static_cast<int>(row0 / GEMM_BM);
+                owner = block / a.blocksPerShard;
+                const int localBlock = block - owner * a.blocksPerShard;
+                tileLocal = localBlock * a.nBlocks + nBlock;
+                rowBase = a.comm->registryPtr->regions[a.outHandle].peerBase[owner] + a.outOffset +
+                          (static_cast<uint64_t>(a.comm->rank) * a.shardRows + static_cast<uint64_t>(localBlock) * GEMM_BM) * a.N * 2;
+                rowsValid = GEMM_BM;
+            }
             const int col0 = nBlock * GEMM_BN;
 #pragma unroll 1
             for (int pass = 0; pass < 2; ++pass) {
@@ -450,6 +632,77 @@ TileXRGemmFp8BlockScaled(const __grid_constant__ GemmBlockArgs a)
                 }
                 asm volatile("bar.sync 1, 256;" ::: "memory");
             }
+            if (a.mode == GEMM_REDUCE_SCATTER && pt == 0) {
+                // all 256 promoter threads have stored (the barrier above): order their stores, then tell the owner
+                fence_acq_rel_sys();
+                st_relaxed_sys_u64(FlagSlot(a.comm, owner, FB_FLAG_PLANE_B + static_cast<int64_t>(a.comm->rank) * a.flagStride + tileLocal),
+                                   MakeFlag(st->epoch, 1));
+            }
+        }
+        // ---- reduce-scatter: add the partial tiles of the output tiles this CTA owns, in rank order ---------------------
+        if (a.mode == GEMM_REDUCE_SCATTER) {
+            const int owned = a.blocksPerShard * a.nBlocks;
+            const int rank = a.comm->rank, ranks = a.comm->rankSize;
+            const uint32_t epoch = st->epoch;
+            const uint8_t *stage = a.comm->registryPtr->regions[a.outHandle].peerBase[rank] + a.outOffset;
+            const uint64_t rowBytes = static_cast<uint64_t>(a.N) * 2;
+            for (int tl = static_cast<int>(blockIdx.x); tl < owned; tl += static_cast<int>(gridDim.x)) {
+                asm volatile("bar.sync 1, 256;" ::: "memory");          // sExit of the previous round has been read
+                if (pt == 0) sExit = (st->abortFlag != 0) ? 1 : 0;
+                asm volatile("bar.sync 1, 256;" ::: "memory");
+                if (sExit != 0) break;
+                if (pt < ranks) {
+                    const int64_t slot = FB_FLAG_PLANE_B + static_cast<int64_t>(pt) * a.flagStride + tl;
+                    FbAcquireFlag(FlagSlot(a.comm, rank, slot), MakeFlag(epoch, 1), st, budgetNs);
+                }
+                asm volatile("bar.sync 1, 256;" ::: "memory");
+                if (st->abortFlag != 0) continue;                       // uniform after the barrier: the next round leaves
+                const int mLocal = tl / a.nBlocks;
+                const int nBlock = tl % a.nBlocks;
+                const int cols = min(GEMM_BN, a.N - nBlock * GEMM_BN);
+                const int vecsPerRow = cols / 8;
+                const int total = GEMM_BM * vecsPerRow;
+                for (int i0 = pt; i0 < total; i0 += 256 * 2) {
+                    float accv[2][8];
+                    uint64_t off[2];
+#pragma unroll
+                    for (int q = 0; q < 2; ++q) {
+                        const int i = min(i0 + q * 256, total - 1);
+                        off[q] = (static_cast<uint64_t>(mLocal) * GEMM_BM + i / vecsPerRow) * rowBytes +
+                                 (static_cast<uint64_t>(nBlock) * GEMM_BN + (i % vecsPerRow) * 8) * 2;
+                    }
+                    for (int s = 0; s < ranks; ++s) {
+                        Vec16 x[2];
+#pragma unroll
+                        for (int q = 0; q < 2; ++q) x[q] = ld_vec16_stream(stage + static_cast<uint64_t>(s) * a.shardRows * rowBytes + off[q]);
+#pragma unroll
+                        for (int q = 0; q < 2; ++q) {
+                            const uint32_t wds[4] = {x[q].x, x[q].y, x[q].z, x[q].w};
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                float lo, hi;
+                                if (bf16) {
+                                    lo = __uint_as_float(wds[j] << 16);
+                                    hi = __uint_as_float(wds[j] & 0xffff0000u);
+                                } else {
+                                    const float2 f2 = __half22float2(*reinterpret_cast<const __half2 *>(&wds[j]));
+                                    lo = f2.x;
+                                    hi = f2.y;
+                                }
+                                accv[q][2 * j] = s == 0 ? lo : accv[q][2 * j] + lo;
+                                accv[q][2 * j + 1] = s == 0 ? hi : accv[q][2 * j + 1] + hi;
+                            }
+                        }
+                    }
+#pragma unroll
+                    for (int q = 0; q < 2; ++q) {
+                        if (i0 + q * 256 < total) {
+                            st_vec16(a.c + off[q], Vec16{FbPackPair(accv[q][0], accv[q][1], bf16), FbPackPair(accv[q][2], accv[q][3], bf16),
+                                                         FbPackPair(accv[q][4], accv[q][5], bf16), FbPackPair(accv[q][6], accv[q][7], bf16)});
+                        }
+                    }
+                }
+            }
         }
     }
 
@@ -461,11 +714,24 @@ TileXRGemmFp8BlockScaled(const __grid_constant__ GemmBlockArgs a)
     if (warp == 1) {
         asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmemBase), "r"(FB_TMEM_COLS) : "memory");
     }
-    if (st->abortFlag != 0 && threadIdx.x == 0 && a.status != nullptr) atomicExch(a.status, TILEXR_DEV_MBARRIER_TIMEOUT);
+    const bool failed = st->abortFlag != 0;
+    if (failed && threadIdx.x == 0 && a.status != nullptr) atomicExch(a.status, TILEXR_DEV_MBARRIER_TIMEOUT);
+    if (fused) {
+        Waiter w{a.comm, st->epoch, static_cast<int32_t>(blockIdx.x), TILEXR_DEV_OK, 0};
+        if (failed && threadIdx.x == 0) RaiseFailure(w, TILEXR_DEV_MBARRIER_TIMEOUT, a.comm->rank, blockIdx.x, 0, 0);
+        KernelEpilogue(w, !failed);
+    }
 }
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_FP8_BLOCK_THREADS, 1)
+TileXRGemmFp8BlockScaled(const __grid_constant__ GemmBlockArgs a) { FbBody(a); }
+// Emulated worlds: one argument block per rank in global memory, rank = blockIdx.y.
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_FP8_BLOCK_THREADS, 1)
+TileXRGemmFp8BlockScaled_emulated(const GemmBlockArgs *perRank) { FbBody(perRank[blockIdx.y]); }
 
 } // namespace
 
 const void *GemmFp8BlockKernel() { return reinterpret_cast<const void *>(&TileXRGemmFp8BlockScaled); }
+const void *GemmFp8BlockKernelEmulated() { return reinterpret_cast<const void *>(&TileXRGemmFp8BlockScaled_emulated); }
 
 } // namespace TileXR

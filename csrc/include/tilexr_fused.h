@@ -67,6 +67,20 @@ int TileXRMatmulFp8(const void *a, const void *b, void *c, int64_t m, int64_t n,
 int TileXRMatmulFp8BlockScaled(const void *a, const float *scaleA, const void *b, const float *scaleB, void *c, int64_t m, int64_t n,
                                int64_t k, TXR_DT inDtype, TXR_DT outDtype, int32_t *status, TileXRStream stream);
 
+// The block-scaled fp8 GEMM fused with the collectives of a tensor-parallel layer (same scale layouts as above; rows per
+// rank a multiple of 256).
+//   AllGather: A = all_gather(aShard) along rows, with its scales; aStaging [R * shardRows, K] (8-bit) and scaleStaging
+//   [R * shardRows, K / 128] (fp32) are registered buffers (TileXRSymmAlloc) that every rank fills on every other rank while
+//   the tiles are computed; K a multiple of 512.  C [R * shardRows, N].
+//   ReduceScatter: out [shardRows, N] = this rank's rows of the sum over ranks of A x B^T (A [R * shardRows, K] holds this
+//   rank's K slice); partialStaging [R * shardRows, N] 16-bit, registered.  The R partial tiles are added in rank order in fp32.
+int TileXRAllGatherMatmulFp8Block(const void *aShard, const float *scaleAShard, void *aStaging, float *scaleStaging, const void *b,
+                                  const float *scaleB, void *c, int64_t shardRows, int64_t n, int64_t k, TXR_DT inDtype, TXR_DT outDtype,
+                                  TileXRCommPtr comm, TileXRStream stream);
+int TileXRMatmulReduceScatterFp8Block(const void *a, const float *scaleA, const void *b, const float *scaleB, void *partialStaging, void *out,
+                                      int64_t shardRows, int64_t n, int64_t k, TXR_DT inDtype, TXR_DT outDtype, TileXRCommPtr comm,
+                                      TileXRStream stream);
+
 // C[R*shardRows, N] = all_gather(aShard)[R*shardRows, K] x B[N,K]^T.  `aStaging` is a registered
 // buffer of R*shardRows*K elements at the same offset on every rank (TileXRSymmAlloc): the
 // kernel pushes aShard into every peer's staging buffer and multiplies as rows arrive.  Row

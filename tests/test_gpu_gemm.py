@@ -142,3 +142,63 @@ def test_grouped_matmul(txr, counts, n, k, swiglu):
     want = txr.gemm.grouped_matmul_ref(rows, w, group_rows, epi)
     _close(got[:total], want[:total], k)
     assert torch.all(got[total:] == 7.0)
+
+
+def _block_operands(txr, rows, n, k, seed):
+    g = torch.Generator().manual_seed(seed)
+    a = torch.randn(rows, k, generator=g) * (0.25 + 4.0 * torch.rand(rows, 1, generator=g))
+    w = torch.randn(n, k, generator=g) * 0.5
+    qa, sa = txr.quant.fp8_quant_1x128(a.to(torch.bfloat16).cuda())
+    qw, sw = txr.gemm.quantize_weight_128x128(w.cuda())
+    return qa, sa, qw, sw
+
+
+def _block_product(qa, sa, qw, sw):
+    k = qa.shape[1]
+    da = qa.float().cpu().view(qa.shape[0], k // 128, 128) * sa.cpu().unsqueeze(-1)
+    dw = qw.float().cpu() * sw.cpu().repeat_interleave(128, dim=0)[:qw.shape[0]].repeat_interleave(128, dim=1)
+    return da.view(qa.shape[0], k) @ dw.t()
+
+
+@pytest.mark.parametrize("ranks,shard_rows,n,k", [(2, 256, 256, 512), (2, 512, 640, 1024), (4, 256, 512, 1536)])
+def test_all_gather_matmul_fp8_block(txr, ranks, shard_rows, n, k):
+    """Block-scaled fp8 GEMM fused with the all-gather of A: every rank's rows AND scales travel into the others' staging
+    buffers during the launch; three launches in a row reuse the buffers behind the reuse guard."""
+    world = txr.init_emulated_world(ranks, device=0, buffer_mb=16)
+    ops = [_block_operands(txr, shard_rows, n, k, 50 + r) for r in range(ranks)]
+    a_staging = world.symm_empty((ranks * shard_rows, k), torch.float8_e4m3fn)
+    s_staging = world.symm_empty((ranks * shard_rows, k // 128), torch.float32)
+    for _ in range(3):
+        outs = world.run(lambda c, r: txr.gemm.all_gather_matmul_fp8_block(c, ops[r][0], ops[r][1], a_staging[r], s_staging[r], ops[r][2], ops[r][3]))
+        world.check()
+    qa_all = torch.cat([o[0] for o in ops])
+    sa_all = torch.cat([o[1] for o in ops])
+    for r in range(ranks):
+        want = _block_product(qa_all, sa_all, ops[r][2], ops[r][3])
+        got = outs[r].float().cpu()
+        assert torch.allclose(got, want, rtol=1e-2, atol=1e-2 * want.abs().max().item()), (got - want).abs().max()
+        assert (got - want).abs().mean() < 4e-3 * want.abs().mean() + 1e-4
+    world.destroy()
+
+
+@pytest.mark.parametrize("ranks,shard_rows,n,k", [(2, 256, 256, 256), (2, 256, 768, 1024), (4, 256, 512, 512)])
+def test_matmul_reduce_scatter_fp8_block(txr, ranks, shard_rows, n, k):
+    """Block-scaled fp8 GEMM fused with the reduce-scatter of its result: partial tiles travel as bf16 and are added in
+    rank order in fp32."""
+    world = txr.init_emulated_world(ranks, device=0, buffer_mb=16)
+    m = ranks * shard_rows
+    ops = [_block_operands(txr, m, n, k, 70 + r) for r in range(ranks)]
+    staging = world.symm_empty((m, n), torch.bfloat16)
+    partial = [_block_product(*ops[r]).to(torch.bfloat16).float() for r in range(ranks)]
+    want = partial[0]
+    for p in partial[1:]:
+        want = want + p
+    for _ in range(3):
+        outs = world.run(lambda c, r: txr.gemm.matmul_reduce_scatter_fp8_block(c, ops[r][0], ops[r][1], ops[r][2], ops[r][3], staging[r]))
+        world.check()
+    for r in range(ranks):
+        got = outs[r].float().cpu()
+        ref = want[r * shard_rows:(r + 1) * shard_rows]
+        assert torch.allclose(got, ref, rtol=2e-2, atol=2e-2 * ref.abs().max().item()), (got - ref).abs().max()
+        assert (got - ref).abs().mean() < 6e-3 * ref.abs().mean() + 1e-4
+    world.destroy()

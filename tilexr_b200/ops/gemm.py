@@ -95,3 +95,20 @@ def all_gather_matmul(comm, a_shard: torch.Tensor, b: torch.Tensor, staging: tor
 def matmul_reduce_scatter(comm, a: torch.Tensor, b: torch.Tensor, staging: torch.Tensor) -> torch.Tensor:
     """``reduce_scatter(a @ b.T)`` along rows; ``staging`` is ``comm.symm_empty([M, N], dtype)``."""
     return _C.matmul_reduce_scatter(comm, a.contiguous(), b.contiguous(), staging)
+
+
+def all_gather_matmul_fp8_block(comm, a_shard: torch.Tensor, scale_a_shard: torch.Tensor, a_staging: torch.Tensor, scale_staging: torch.Tensor,
+                                b: torch.Tensor, scale_b: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """``all_gather(a_shard) @ b.T`` with block scales (see :func:`matmul_fp8_block`): the shard's fp8 rows and their 1 x 128
+    scales are written into every rank's staging buffers (``comm.symm_empty([world * rows, K], fp8)`` and
+    ``comm.symm_empty([world * rows, K // 128], float32)``) by otherwise idle warps of the GEMM's own CTAs, through the NVLink
+    multicast alias of the buffers where there is one, and each tile starts when its rows have landed."""
+    return _C.all_gather_matmul_fp8_block(comm, a_shard.contiguous(), scale_a_shard.contiguous(), a_staging, scale_staging, b.contiguous(),
+                                          scale_b.contiguous(), out_dtype)
+
+
+def matmul_reduce_scatter_fp8_block(comm, a: torch.Tensor, scale_a: torch.Tensor, b: torch.Tensor, scale_b: torch.Tensor,
+                                    staging: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """``reduce_scatter(a @ b.T)`` along rows with block scales; ``staging`` is ``comm.symm_empty([M, N], out_dtype)``.  Partial
+    tiles are stored into the row owner's staging slots from the GEMM's epilogue and added there in rank order in fp32."""
+    return _C.matmul_reduce_scatter_fp8_block(comm, a.contiguous(), scale_a.contiguous(), b.contiguous(), scale_b.contiguous(), staging, out_dtype)
