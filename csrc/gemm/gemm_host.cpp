@@ -164,7 +164,7 @@ int TileXRMatmul(const void *a, const void *b, void *c, int64_t m, int64_t n, in
             cudaFuncSetAttribute(GemmPairKernel(), cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(GEMM_PAIR_SMEM_BYTES));
         });
         void *pairParams[] = {&g};
-        const cudaError_t pe = cudaLaunchKernel(GemmPairKernel(), dim3(2 * pairs), dim3(GEMM_THREADS), pairParams,
+        const cudaError_t pe = cudaLaunchKernel(GemmPairKernel(), dim3(2 * pairs), dim3(GEMM_PAIR_THREADS), pairParams,
                                                 GEMM_PAIR_SMEM_BYTES, static_cast<cudaStream_t>(stream));
         if (pe != cudaSuccess) {
             TILEXR_LOG(ERROR) << "matmul (CTA pairs) launch failed: " << cudaGetErrorString(pe);
@@ -238,7 +238,7 @@ int TileXRGroupedMatmul(const void *a, const void *b, const int64_t *groupRows, 
         const int64_t tilesAtMost = ((maxRows + 2 * GEMM_BM - 1) / (2 * GEMM_BM) + g.groups) * g.nBlocks;
         const int pairs = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(tilesAtMost, EnvLong("TILEXR_GEMM_CTAS", sms) / 2)));
         void *params[] = {&g};
-        const cudaError_t e = cudaLaunchKernel(GemmPairKernel(), dim3(2 * pairs), dim3(GEMM_THREADS), params, GEMM_PAIR_SMEM_BYTES,
+        const cudaError_t e = cudaLaunchKernel(GemmPairKernel(), dim3(2 * pairs), dim3(GEMM_PAIR_THREADS), params, GEMM_PAIR_SMEM_BYTES,
                                                static_cast<cudaStream_t>(stream));
         if (e != cudaSuccess) {
             TILEXR_LOG(ERROR) << "grouped matmul launch failed: " << cudaGetErrorString(e);
@@ -290,7 +290,7 @@ int TileXRMatmulFp8(const void *a, const void *b, void *c, int64_t m, int64_t n,
         cudaFuncSetAttribute(GemmPairKernel(), cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(GEMM_PAIR_SMEM_BYTES));
     });
     void *params[] = {&g};
-    const cudaError_t e = cudaLaunchKernel(GemmPairKernel(), dim3(2 * pairs), dim3(GEMM_THREADS), params, GEMM_PAIR_SMEM_BYTES,
+    const cudaError_t e = cudaLaunchKernel(GemmPairKernel(), dim3(2 * pairs), dim3(GEMM_PAIR_THREADS), params, GEMM_PAIR_SMEM_BYTES,
                                            static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) {
         TILEXR_LOG(ERROR) << "fp8 matmul launch failed: " << cudaGetErrorString(e);
@@ -381,7 +381,7 @@ static int FusedGrid(TileXRCommPtr comm, const TileXRCommArgs *hostArgs, unsigne
 {
     const int ranksPerDevice = (hostArgs->extraFlag & TILEXR_FLAG_EMULATED) ? hostArgs->rankSize : 1;
     unsigned maxGrid = 0;
-    int ret = pairs ? MaxCooperativeGrid(comm, GemmPairEntry(), GEMM_THREADS, GEMM_PAIR_SMEM_BYTES, ranksPerDevice, &maxGrid)
+    int ret = pairs ? MaxCooperativeGrid(comm, GemmPairEntry(), GEMM_PAIR_THREADS, GEMM_PAIR_SMEM_BYTES, ranksPerDevice, &maxGrid)
                     : MaxCooperativeGrid(comm, GemmEntry(), GEMM_THREADS, GEMM_SMEM_BYTES, ranksPerDevice, &maxGrid);
     if (ret != TILEXR_SUCCESS) return ret;
     if (pairs) maxGrid &= ~1u;
@@ -451,6 +451,14 @@ int TileXRAllGatherMatmul(const void *aShard, void *aStaging, const void *b, voi
     ret = TileXRCommNextMagic(comm, &magic);
     if (ret != TILEXR_SUCCESS) return ret;
     g.magic = magic;
+    if (pairs && EnvLong("TILEXR_AG_GEMM_COMM_CTAS", 0) <= 0) {
+        // two otherwise idle warps of every CTA push the shard (through the multicast alias of the staging buffer where
+        // there is one): no CTA is set aside
+        g.rasterGroup = static_cast<int32_t>(std::max<long>(1, EnvLong("TILEXR_GEMM_GROUP", 8)));
+        g.commBlocks = 0;
+        LaunchConfig pairCfg{grid, GEMM_PAIR_THREADS, GEMM_PAIR_SMEM_BYTES, true};
+        return LaunchKernel(comm, GemmPairEntry(), &g, pairCfg, stream);
+    }
     if (pairs) {
         g.rasterGroup = static_cast<int32_t>(std::max<long>(1, EnvLong("TILEXR_GEMM_GROUP", 8)));
         g.commBlocks = (g.commBlocks + 1) & ~1u;          // whole pairs push, whole pairs compute
@@ -466,7 +474,7 @@ int TileXRAllGatherMatmul(const void *aShard, void *aStaging, const void *b, voi
             const double totalUs = tiles * tileUs / (grid / 2);
             g.commTilesPerPair = totalUs > pushUs ? static_cast<uint32_t>((totalUs - pushUs) / tileUs) : 0u;
         }
-        LaunchConfig pairCfg{grid, GEMM_THREADS, GEMM_PAIR_SMEM_BYTES, true};
+        LaunchConfig pairCfg{grid, GEMM_PAIR_THREADS, GEMM_PAIR_SMEM_BYTES, true};
         return LaunchKernel(comm, GemmPairEntry(), &g, pairCfg, stream);
     }
     LaunchConfig cfg{grid, GEMM_THREADS, GEMM_SMEM_BYTES, true};
@@ -526,7 +534,7 @@ int TileXRMatmulReduceScatter(const void *a, const void *b, void *partialStaging
     g.magic = magic;
     if (pairs) {
         g.rasterGroup = static_cast<int32_t>(std::max<long>(1, EnvLong("TILEXR_GEMM_GROUP", 8)));
-        LaunchConfig pairCfg{grid, GEMM_THREADS, GEMM_PAIR_SMEM_BYTES, true};
+        LaunchConfig pairCfg{grid, GEMM_PAIR_THREADS, GEMM_PAIR_SMEM_BYTES, true};
         return LaunchKernel(comm, GemmPairEntry(), &g, pairCfg, stream);
     }
     LaunchConfig cfg{grid, GEMM_THREADS, GEMM_SMEM_BYTES, true};

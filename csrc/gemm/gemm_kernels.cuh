@@ -16,6 +16,7 @@ constexpr int GEMM_BK = 64;         // K per pipeline stage = one 128-byte swizz
 constexpr int GEMM_UMMA_K = 16;     // K of one tcgen05.mma for 16-bit inputs
 constexpr int GEMM_STAGES = 4;
 constexpr unsigned GEMM_THREADS = 192;   // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-5: epilogue
+constexpr unsigned GEMM_PAIR_THREADS = 256;   // CTA-pair kernel: two more warps that push this rank's shard in the all-gather mode
 constexpr uint32_t GEMM_STAGE_A_BYTES = GEMM_BM * GEMM_BK * 2;
 constexpr uint32_t GEMM_STAGE_B_BYTES = GEMM_BN * GEMM_BK * 2;
 constexpr uint32_t GEMM_STAGE_BYTES = GEMM_STAGE_A_BYTES + GEMM_STAGE_B_BYTES;

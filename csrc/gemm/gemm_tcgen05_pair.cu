@@ -9,15 +9,18 @@
 // (cluster rank 0) issues every tcgen05.mma for the pair; the accumulator of each CTA's 128 rows lives in that
 // CTA's own tensor memory, 2 x 256 columns, so epilogue and main loop overlap.
 //
-// Roles per CTA (192 threads): warp 0 lane 0 issues TMA loads (cp.async.bulk.tensor with cta_group::2 and no
+// Roles per CTA (256 threads; warps 6-7 only work in the all-gather mode, see below): warp 0 lane 0 issues TMA loads (cp.async.bulk.tensor with cta_group::2 and no
 // multicast: both CTAs signal the LEADER's "full" barrier); warp 1 owns tensor memory and, in the leader, issues
 // the MMAs and commits them to both CTAs' barriers; warps 2-5 read the accumulator with tcgen05.ld and store C.
 // Every mbarrier wait is bounded and checks the pair's abort flags; on a give-up all roles fall through to the
 // tear-down, both CTAs meet at the cluster barrier, tensor memory is released and `status` tells the host.
 //
-// Fused modes work as in the one-CTA kernel (all-gather -> GEMM: leading CTA pairs only push this rank's A shard
-// to the peers' staging buffers, and each TMA lane acquires the flag of a remote 128-row piece before loading it
-// from LOCAL staging memory; GEMM -> reduce-scatter: every CTA's epilogue stores its 128x256 partial tile into
+// Fused modes: all-gather -> GEMM: warps 6-7 of EVERY CTA write this rank's A shard into the peers' staging buffers
+// piece by piece (128 rows x a chunk of K) and raise each piece's flag -- through the NVLink multicast alias of the
+// staging buffer where the runtime has one (multimem.st: one store, the switch replicates it), else one store per
+// peer -- so no SM is taken from the GEMM (with commBlocks > 0 leading CTA pairs push instead and compute afterwards,
+// the earlier scheme); each TMA lane acquires the flag of a remote 128-row piece before loading it from LOCAL staging
+// memory; GEMM -> reduce-scatter: every CTA's epilogue stores its 128x256 partial tile into
 // the row owner's staging slot and raises the tile's flag, then the epilogue warps sum the tiles this rank owns
 // in rank order).  They need shards of a multiple of 256 rows, so that a pair's tile lies within one shard.
 //
@@ -335,18 +338,18 @@ __device__ void PairBody(const GemmArgs &a)
                 // pushing CTA has 24 KB on the way instead of the few KB of a row-by-row copy
                 const int vecsPerRow = static_cast<int>(n / 16);
                 const int total = rows * vecsPerRow;
-                for (int i0 = static_cast<int>(threadIdx.x); i0 < total; i0 += static_cast<int>(GEMM_THREADS) * 8) {
+                for (int i0 = static_cast<int>(threadIdx.x); i0 < total; i0 += static_cast<int>(GEMM_PAIR_THREADS) * 8) {
                     Vec16 v[8];
                     uint64_t off[8];
 #pragma unroll
                     for (int q = 0; q < 8; ++q) {
-                        const int i = min(i0 + q * static_cast<int>(GEMM_THREADS), total - 1);
+                        const int i = min(i0 + q * static_cast<int>(GEMM_PAIR_THREADS), total - 1);
                         off[q] = static_cast<uint64_t>(i / vecsPerRow) * rowBytes + static_cast<uint64_t>(i % vecsPerRow) * 16;
                         v[q] = ld_vec16_stream(srcBase + off[q]);
                     }
 #pragma unroll
                     for (int q = 0; q < 8; ++q) {
-                        if (i0 + q * static_cast<int>(GEMM_THREADS) < total) st_vec16(dstBase + off[q], v[q]);
+                        if (i0 + q * static_cast<int>(GEMM_PAIR_THREADS) < total) st_vec16(dstBase + off[q], v[q]);
                     }
                 }
                 __syncthreads();
@@ -518,6 +521,67 @@ __device__ void PairBody(const GemmArgs &a)
                 }
                 if (broke) break;
                 UmmaCommitPair(&st->tmemFull[acc]);
+            }
+        }
+    } else if (warp >= 6) {
+        // ---- warps 6-7: in the all-gather mode (without pushing CTAs) write this rank's shard into every peer's staging buffer ----
+        if (fused && a.mode == GEMM_ALL_GATHER && a.commBlocks == 0 && ok && ranks > 1) {
+            const int pt = static_cast<int>(threadIdx.x) - 192;          // 0..63
+            const TileXRRegistry *reg = a.comm->registryPtr;
+            uint8_t *mc = reg->regions[a.stageHandle].mcBase;
+            const bool multicast = mc != nullptr;
+            const int pieces = a.blocksPerShard * a.kChunks;
+            const int items = multicast ? pieces : (ranks - 1) * pieces;
+            const uint64_t rowBytes = static_cast<uint64_t>(a.K) * 2;
+            const uint64_t chunkBytes = static_cast<uint64_t>(a.kBlocksPerChunk) * GEMM_BK * 2;
+            for (int it = blockIdx.x; it < items; it += gridDim.x) {
+                const int peer = (rank - 1 - it / pieces + 2 * ranks) % ranks;      // rank-1 needs it first
+                const int piece = it % pieces;
+                const int mLocal = piece / a.kChunks;
+                const int kc = piece % a.kChunks;
+                const uint64_t colOff = kc * chunkBytes;
+                const uint64_t n = min(chunkBytes, rowBytes > colOff ? rowBytes - colOff : 0);
+                uint8_t *dstBase = (multicast ? mc : reg->regions[a.stageHandle].peerBase[peer]) + a.stageOffset +
+                                   (static_cast<uint64_t>(rank) * a.shardRows + static_cast<uint64_t>(mLocal) * GEMM_BM) * rowBytes + colOff;
+                const uint8_t *srcBase = a.aLocal + static_cast<uint64_t>(mLocal) * GEMM_BM * rowBytes + colOff;
+                const int rows = min(GEMM_BM, a.shardRows - mLocal * GEMM_BM);
+                const int vecsPerRow = static_cast<int>(n / 16);
+                const int total = rows * vecsPerRow;
+                for (int i0 = pt; i0 < total; i0 += 64 * 8) {
+                    Vec16 v[8];
+                    uint64_t off[8];
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) {
+                        const int i = min(i0 + q * 64, total - 1);
+                        off[q] = static_cast<uint64_t>(i / vecsPerRow) * rowBytes + static_cast<uint64_t>(i % vecsPerRow) * 16;
+                        v[q] = ld_vec16_stream(srcBase + off[q]);
+                    }
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) {
+                        if (i0 + q * 64 < total) {
+                            if (multicast) {
+                                asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dstBase + off[q]), "r"(v[q].x),
+                                             "r"(v[q].y), "r"(v[q].z), "r"(v[q].w) : "memory");
+                            } else {
+                                st_vec16(dstBase + off[q], v[q]);
+                            }
+                        }
+                    }
+                }
+                asm volatile("bar.sync 2, 64;" ::: "memory");
+                if (pt == 0) {
+                    fence_acq_rel_sys();
+                    const uint64_t up = MakeFlag(epoch, 1);
+                    const int64_t slot = FLAG_PLANE_A + static_cast<int64_t>(rank) * a.flagStride + piece;
+                    if (multicast) {
+                        for (int r = 0; r < ranks; ++r) {
+                            if (r != rank) st_relaxed_sys_u64(FlagSlot(a.comm, r, slot), up);
+                        }
+                    } else {
+                        st_relaxed_sys_u64(FlagSlot(a.comm, peer, slot), up);
+                    }
+                }
+                asm volatile("bar.sync 2, 64;" ::: "memory");
             }
         }
     } else {
@@ -744,10 +808,10 @@ __device__ void PairBody(const GemmArgs &a)
     }
 }
 
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_PAIR_THREADS, 1)
 TileXRGemmTcgen05Pair_single(const __grid_constant__ GemmArgs a) { PairBody(a); }
 // Emulated worlds: one argument block per rank in global memory, rank = blockIdx.y.
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_PAIR_THREADS, 1)
 TileXRGemmTcgen05Pair_emulated(const GemmArgs *perRank) { PairBody(perRank[blockIdx.y]); }
 
 } // namespace

@@ -43,6 +43,9 @@ def main():
     p.add_argument("--hidden", type=int, default=8192)
     p.add_argument("--ffn", type=int, default=28672)
     p.add_argument("--iters", type=int, default=10)
+    p.add_argument("--fp8-block", type=int, default=1,
+                   help="also time the block-scaled fp8 variants (1 x 128 activation scales, 128 x 128 weight scales) of both fusions "
+                        "against the same GEMM behind an NCCL all-gather of rows and scales / in front of an NCCL reduce-scatter")
     args = p.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -104,7 +107,10 @@ def main():
     out["ag_gemm_us"] = timed(lambda: txr.gemm.all_gather_matmul(comm, x, w13, stage_a), args.iters, 3, world)
     out["nccl_ag_gemm_us"] = timed(nccl_ag_gemm, args.iters, 3, world)
     out["gemm_only_us"] = timed(lambda: torch.matmul(gathered, w13.t()), args.iters, 3, world)
+    out["tilexr_gemm_only_us"] = timed(lambda: txr.gemm.matmul(gathered, w13), args.iters, 3, world)
     out["gemm_rs_us"] = timed(lambda: txr.gemm.matmul_reduce_scatter(comm, act, w2, stage_c), args.iters, 3, world)
+    out["rs_tilexr_gemm_only_us"] = timed(lambda: txr.gemm.matmul(act, w2), args.iters, 3, world)
+    out["rs_cublas_gemm_only_us"] = timed(lambda: torch.matmul(act, w2.t()), args.iters, 3, world)
     out["nccl_gemm_rs_us"] = timed(nccl_gemm_rs, args.iters, 3, world)
     fl_ag = 2.0 * T * 2 * fl_loc * H
     fl_rs = 2.0 * T * H * fl_loc
@@ -112,6 +118,44 @@ def main():
     out["gemm_rs_tflops"] = fl_rs / out["gemm_rs_us"] / 1e6
     out["ag_bytes_per_rank"] = (world - 1) * rows * H * 2
     out["rs_bytes_per_rank"] = (world - 1) * rows * H * 2
+    if args.fp8_block and rows % 256 == 0 and H % 512 == 0 and fl_loc % 128 == 0:
+        qx, sx = txr.quant.fp8_quant_1x128(x)
+        qact, sact = txr.quant.fp8_quant_1x128(act)
+        qw13, sw13 = txr.gemm.quantize_weight_128x128(w13.float())
+        qw2, sw2 = txr.gemm.quantize_weight_128x128(w2.float())
+        stage_q = comm.symm_empty([T, H], torch.float8_e4m3fn)
+        stage_s = comm.symm_empty([T, H // 128], torch.float32)
+        gathered_q = torch.empty(T, H, dtype=torch.float8_e4m3fn, device="cuda")
+        gathered_s = torch.empty(T, H // 128, dtype=torch.float32, device="cuda")
+
+        def nccl_ag_block():
+            dist.all_gather_into_tensor(gathered_q.view(torch.uint8), qx.view(torch.uint8))
+            dist.all_gather_into_tensor(gathered_s, sx)
+            return txr.gemm.matmul_fp8_block(gathered_q, gathered_s, qw13, sw13)
+
+        def nccl_block_rs():
+            full = txr.gemm.matmul_fp8_block(qact, sact, qw2, sw2)
+            dist.reduce_scatter_tensor(red, full)
+            return red
+
+        fused_ag = txr.gemm.all_gather_matmul_fp8_block(comm, qx, sx, stage_q, stage_s, qw13, sw13)
+        two_step_ag = nccl_ag_block()
+        fused_rs = txr.gemm.matmul_reduce_scatter_fp8_block(comm, qact, sact, qw2, sw2, stage_c)
+        two_step_rs = nccl_block_rs().clone()
+        torch.cuda.synchronize()
+        out["fp8_block"] = {
+            "ag_gemm_identical_to_two_step": bool(torch.equal(fused_ag, two_step_ag)),
+            "gemm_rs_max_diff_vs_two_step": (fused_rs.float() - two_step_rs.float()).abs().max().item(),
+            "status": comm.device_status(),
+            "ag_gemm_us": timed(lambda: txr.gemm.all_gather_matmul_fp8_block(comm, qx, sx, stage_q, stage_s, qw13, sw13), args.iters, 3, world),
+            "nccl_ag_then_gemm_us": timed(nccl_ag_block, args.iters, 3, world),
+            "gemm_only_us": timed(lambda: txr.gemm.matmul_fp8_block(gathered_q, gathered_s, qw13, sw13), args.iters, 3, world),
+            "gemm_rs_us": timed(lambda: txr.gemm.matmul_reduce_scatter_fp8_block(comm, qact, sact, qw2, sw2, stage_c), args.iters, 3, world),
+            "gemm_then_nccl_rs_us": timed(nccl_block_rs, args.iters, 3, world),
+            "rs_gemm_only_us": timed(lambda: txr.gemm.matmul_fp8_block(qact, sact, qw2, sw2), args.iters, 3, world),
+        }
+        out["fp8_block"]["ag_gemm_tflops"] = fl_ag / out["fp8_block"]["ag_gemm_us"] / 1e6
+        out["fp8_block"]["gemm_rs_tflops"] = fl_rs / out["fp8_block"]["gemm_rs_us"] / 1e6
     if rank == 0:
         print(json.dumps(out))
     comm.destroy()
