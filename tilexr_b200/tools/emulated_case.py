@@ -6,6 +6,9 @@ a single GPU.
     python -m tilexr_b200.tools.emulated_case --op ep --ranks 4 --tokens 1024 --hidden 7168
     python -m tilexr_b200.tools.emulated_case --op ar_norm --ranks 8 --tokens 64 --hidden 8192
     python -m tilexr_b200.tools.emulated_case --op gemm --m 4096 --n 4096 --k 4096
+    python -m tilexr_b200.tools.emulated_case --op gemm_fp8_block --m 4096 --n 4096 --k 4096
+    python -m tilexr_b200.tools.emulated_case --op grouped_gemm --m 8192 --n 4096 --k 2048 --groups 8
+    python -m tilexr_b200.tools.emulated_case --op ag_gemm_fp8_block --ranks 2 --m 4096 --n 4096 --k 4096
 """
 from __future__ import annotations
 
@@ -19,7 +22,9 @@ import torch
 def main(argv=None) -> int:
     p = argparse.ArgumentParser()
     p.add_argument("--op", default="all_gather",
-                   choices=["all_gather", "all_to_all", "all_reduce", "reduce_scatter", "ep", "ar_norm", "gemm", "ag_gemm", "gemm_rs"])
+                   choices=["all_gather", "all_to_all", "all_reduce", "reduce_scatter", "ep", "ar_norm", "gemm", "ag_gemm", "gemm_rs", "gemm_fp8_block",
+                            "grouped_gemm", "ag_gemm_fp8_block", "gemm_rs_fp8_block"])
+    p.add_argument("--groups", type=int, default=8, help="grouped_gemm: experts; the m rows are split evenly, SwiGLU epilogue on")
     p.add_argument("--ranks", type=int, default=4)
     p.add_argument("--mbytes", type=float, default=64.0, help="per-rank message for the collectives")
     p.add_argument("--tokens", type=int, default=1024)
@@ -55,6 +60,23 @@ def main(argv=None) -> int:
         for _ in range(a.launches):
             timed(lambda: txr.gemm.matmul(x, w))
         print(json.dumps({"op": a.op, "us": times, "tflops": 2.0 * a.m * a.n * a.k / times[-1] / 1e6}))
+        return 0
+
+    if a.op == "gemm_fp8_block":
+        qx, sx = quant.fp8_quant_1x128((torch.randn(a.m, a.k, device="cuda", generator=g) * 0.5).to(torch.bfloat16))
+        qw, sw = txr.gemm.quantize_weight_128x128(torch.randn(a.n, a.k, device="cuda", generator=g) * 0.5)
+        for _ in range(a.launches):
+            timed(lambda: txr.gemm.matmul_fp8_block(qx, sx, qw, sw))
+        print(json.dumps({"op": a.op, "us": times, "tflops": 2.0 * a.m * a.n * a.k / times[-1] / 1e6}))
+        return 0
+    if a.op == "grouped_gemm":
+        per = a.m // a.groups
+        x = (torch.randn(per * a.groups, a.k, device="cuda", generator=g) * 0.1).to(torch.bfloat16)
+        w = (torch.randn(a.groups, a.n, a.k, device="cuda", generator=g) * 0.1).to(torch.bfloat16)
+        counts = torch.full((a.groups,), per, dtype=torch.int64, device="cuda")
+        for _ in range(a.launches):
+            timed(lambda: txr.gemm.grouped_matmul(x, w, counts, epilogue=txr.gemm.EPILOGUE_SWIGLU))
+        print(json.dumps({"op": a.op, "us": times, "tflops": 2.0 * per * a.groups * a.n * a.k / times[-1] / 1e6}))
         return 0
 
     world = txr.init_emulated_world(R, device=0, buffer_mb=a.buffer_mb)
@@ -97,6 +119,22 @@ def main(argv=None) -> int:
         st = world.symm_empty((R * rows, a.n), torch.bfloat16)
         for _ in range(a.launches):
             timed(lambda: world.run(lambda c, r: txr.gemm.matmul_reduce_scatter(c, x[r], w[r], st[r])))
+    elif a.op in ("ag_gemm_fp8_block", "gemm_rs_fp8_block"):
+        rows = a.m // R // 256 * 256
+        total = R * rows
+        ops = []
+        for r in range(R):
+            acts = (torch.randn(rows if a.op == "ag_gemm_fp8_block" else total, a.k, device="cuda", generator=g) * 0.5).to(torch.bfloat16)
+            ops.append(quant.fp8_quant_1x128(acts) + txr.gemm.quantize_weight_128x128(torch.randn(a.n, a.k, device="cuda", generator=g) * 0.5))
+        if a.op == "ag_gemm_fp8_block":
+            st_q = world.symm_empty((total, a.k), torch.float8_e4m3fn)
+            st_s = world.symm_empty((total, a.k // 128), torch.float32)
+            for _ in range(a.launches):
+                timed(lambda: world.run(lambda c, r: txr.gemm.all_gather_matmul_fp8_block(c, ops[r][0], ops[r][1], st_q[r], st_s[r], ops[r][2], ops[r][3])))
+        else:
+            st = world.symm_empty((total, a.n), torch.bfloat16)
+            for _ in range(a.launches):
+                timed(lambda: world.run(lambda c, r: txr.gemm.matmul_reduce_scatter_fp8_block(c, ops[r][0], ops[r][1], ops[r][2], ops[r][3], st[r])))
     world.check()
     print(json.dumps({"op": a.op, "ranks": R, "us": times}))
     world.destroy()
