@@ -99,7 +99,15 @@ int LaunchPlan(const int32_t *topk, const int32_t *tpe, const int32_t *globalIds
     ret = TileXRCommNextMagic(comm, &magic);
     if (ret != TILEXR_SUCCESS) return ret;
     a.magic = magic;
-    LaunchConfig cfg{1, PLAN_V2_THREADS, 0, true};
+    // shared memory for the balancing tables, the histogram table and the segment list, when they fit
+    const int64_t stagedWords = 6ll * R + 5ll * R * e + static_cast<int64_t>(R) * a.dims.B + 2ll * R * R + e + static_cast<int64_t>(R) * e +
+                                static_cast<int64_t>(a.dims.segCapacity) * (sizeof(plan2::Segment) / 4);
+    size_t smem = 0;
+    if (stagedWords * 4 <= 200 * 1024) {
+        smem = static_cast<size_t>(stagedWords) * 4;
+        a.stagedWords = static_cast<uint32_t>(stagedWords);
+    }
+    LaunchConfig cfg{1, PLAN_V2_THREADS, smem, true};
     return LaunchKernel(comm, PlanV2KernelEntry(), &a, cfg, stream);
 }
 

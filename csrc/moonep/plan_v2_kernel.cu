@@ -147,14 +147,47 @@ __device__ void PlanV2Body(const PlanV2Args &a)
         plan2::PlanInitC(d, t, tid, nt);
         __syncthreads();
     }
+    // The balancing is one thread walking small tables with dependent accesses: from global memory every step costs an L2
+    // round trip.  When the tables fit (they do for the usual 8 ranks x 256 experts: about 90 KB), the block copies them,
+    // the histogram table and the segment list into shared memory, thread 0 balances there, and the block copies the
+    // result back for the per-route phase.
+    extern __shared__ __align__(16) int32_t planShared[];
+    const int64_t prefixWords = 6ll * d.R + 5ll * d.R * d.E + static_cast<int64_t>(d.R) * d.B + 2ll * d.R * d.R + d.E;   // load .. expertList
+    const int64_t tpeWords = static_cast<int64_t>(d.R) * d.E;
+    const int64_t segWords = static_cast<int64_t>(d.segCapacity) * (sizeof(plan2::Segment) / 4);
+    const bool staged = a.stagedWords != 0 && prefixWords + tpeWords + segWords <= static_cast<int64_t>(a.stagedWords);
+    const bool balance = ok && mismatch == 0 && bad == 0;      // block-uniform
+    if (balance && staged) {
+        for (int64_t i = tid; i < prefixWords; i += nt) planShared[i] = a.tables[i];
+        for (int64_t i = tid; i < tpeWords; i += nt) planShared[prefixWords + i] = a.tpe[i];
+    }
+    __syncthreads();
     if (tid == 0) {
         int32_t v = (mismatch & 2) ? PLAN_ERROR_CONFIG_MISMATCH : (mismatch & 1) ? PLAN_ERROR_TPE_MISMATCH : PLAN_OK;
         if (ok && v == PLAN_OK) v = (bad & 2) ? PLAN_ERROR_CONFIG_MISMATCH : (bad & 1) ? PLAN_ERROR_TPE_MISMATCH : PLAN_OK;
         sValidate = v;
         g = plan2::Progress{};
-        if (ok && v == PLAN_OK) plan2::PlanBalance(d, in, a.out, t, g);
+        if (ok && v == PLAN_OK) {
+            if (staged) {
+                plan2::Tables ts;
+                plan2::Carve(d, planShared, &ts);
+                ts.ordinal = t.ordinal;                                             // not touched by the balancing
+                ts.segments = reinterpret_cast<plan2::Segment *>(planShared + prefixWords + tpeWords);
+                const plan2::Inputs ins{a.topk, planShared + prefixWords, a.globalIds};
+                plan2::PlanBalance(d, ins, a.out, ts, g);
+            } else {
+                plan2::PlanBalance(d, in, a.out, t, g);
+            }
+        }
     }
     __syncthreads();
+    if (balance && staged) {
+        for (int64_t i = tid; i < prefixWords; i += nt) a.tables[i] = planShared[i];
+        const int32_t *segs = planShared + prefixWords + tpeWords;
+        int32_t *segsOut = reinterpret_cast<int32_t *>(t.segments);
+        for (int64_t i = tid; i < segWords; i += nt) segsOut[i] = segs[i];
+        __syncthreads();
+    }
     const bool planned = ok && sValidate == PLAN_OK;
     if (planned && plan2::PlanHasDestinations(g)) {
         for (int e = tid; e < d.E; e += nt) plan2::PlanOrdinalsOfExpert(d, in, t, e);

@@ -23,7 +23,7 @@ struct PlanV2Args {
     plan2::Dims dims;
     uint64_t headerHash;        // dimensions, configuration and global ids as seen by the host of this rank
     uint32_t mailStride;        // bytes per sender in a window: header + E int32, rounded up to 16
-    uint32_t pad;
+    uint32_t stagedWords;       // int32 words of dynamic shared memory given to the kernel for the balancing tables, 0 = none
     // Optional tables in the form the dispatch / combine stage kernels take (all null or all set):
     int32_t *stageDst;          // [cap] raw destinations, duplicates decoded (every route carries its hidden state)
     int32_t *stageZeroFill;     // [(E + B) * 2]

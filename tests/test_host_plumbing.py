@@ -111,6 +111,21 @@ def _worker(rank, world, port, scenario, result_queue):
                 assert comm.device_status() == 1             # TILEXR_DEV_WAIT_TIMEOUT
                 d = comm.dfx()
                 assert d[3] == 0xDEAD and d[5] == 1           # failed, waiting for peer 1
+                # the dump-on-failure record says the same, in a file
+                import json
+                import tempfile
+
+                from tilexr_b200.utils import failure_dump
+                with tempfile.TemporaryDirectory() as tmp:
+                    os.environ["TILEXR_DUMP_DIR"] = tmp
+                    try:
+                        with pytest.raises(RuntimeError, match="device status 1"):
+                            failure_dump.check(comm, "lost-flag all-gather", {"bytes": 4096 * 4})
+                    finally:
+                        os.environ.pop("TILEXR_DUMP_DIR")
+                    rec = json.load(open(os.path.join(tmp, os.listdir(tmp)[0])))
+                    assert rec["dfx"]["run_status_name"] == "failed" and rec["dfx"]["fail_peer"] == 1 and rec["device_status"] == 1
+                    assert rec["context"]["what"] == "lost-flag all-gather" and rec["physical_info"]["link"] == "host_memory"
         dist.barrier()
         comm.destroy()
         dist.destroy_process_group()

@@ -199,6 +199,10 @@ class TileXRMoonEPBuffer:
         plan_status = int(plan.status.item()) if plan is not None and plan.status is not None else 0
         if status != 0 or plan_status != 0:
             self._poisoned = True
+            from ..utils import failure_dump
+
+            failure_dump.dump(self.comm, None, {"what": "MoonEP stage", "plan_status": plan_status, "S": self.S, "H": self.H, "K": self.K,
+                                                "E": self.E})
             self.comm.print_dfx()
             raise RuntimeError(f"MoonEP stage failed: device status {status}, plan status {plan_status}")
 

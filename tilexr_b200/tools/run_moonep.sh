@@ -1,0 +1,27 @@
+#!/bin/bash
+# MoonEP harness from end to end on N GPUs of one node (reference: scripts/run_moonep.sh and tools/moonep/launcher.py):
+# correctness against the torch + NCCL reference backend, the stage benchmark with per-rank samples, the standalone
+# PrefetchWeight and ReduceGrad benchmarks, and the cross-rank aggregation of the samples into P50 / P99 tables.
+#   usage: run_moonep.sh N OUT [correctness-cases] [perf-cases]      (case files under tilexr_b200/tools/moonep/cases/)
+# Several nodes: run it on each node with the same OUT on a shared file system (or copy OUT/samples together) and
+# finish with   python -m tilexr_b200.tools.moonep.launcher --mode aggregate --samples OUT/samples --json OUT/aggregate.json
+set -u
+if [ $# -lt 2 ]; then echo "usage: $0 N OUT [correctness-cases] [perf-cases]" >&2; exit 2; fi
+N=$1
+OUT=$2
+CORRECT=${3:-correctness}
+PERF=${4:-perf}
+mkdir -p "$OUT/samples"
+RUN="python -m torch.distributed.run --nnodes=1 --nproc-per-node $N --master-addr 127.0.0.1"
+rc=0
+timeout 900 $RUN --master-port 29621 -m tilexr_b200.tools.moonep.launcher --mode correctness --cases "$CORRECT" \
+    --json "$OUT/correctness.json" > "$OUT/correctness.md" 2> "$OUT/correctness.err" || rc=1
+timeout 600 $RUN --master-port 29622 -m tilexr_b200.tools.moonep.launcher --mode benchmark --cases "$PERF" --iters 20 --warmup 5 --trace \
+    --samples "$OUT/samples" --json "$OUT/benchmark.json" --csv "$OUT/benchmark.csv" > "$OUT/benchmark.md" 2> "$OUT/benchmark.err" || rc=1
+timeout 300 $RUN --master-port 29623 -m tilexr_b200.tools.moonep.launcher --mode prefetch --cases "$PERF" --iters 20 --warmup 5 \
+    --json "$OUT/prefetch.json" --csv "$OUT/prefetch.csv" > "$OUT/prefetch.md" 2> "$OUT/prefetch.err" || rc=1
+timeout 300 $RUN --master-port 29624 -m tilexr_b200.tools.moonep.launcher --mode reduce-grad --cases "$PERF" --iters 20 --warmup 5 \
+    --json "$OUT/reduce_grad.json" --csv "$OUT/reduce_grad.csv" > "$OUT/reduce_grad.md" 2> "$OUT/reduce_grad.err" || rc=1
+python -m tilexr_b200.tools.moonep.launcher --mode aggregate --samples "$OUT/samples" --json "$OUT/aggregate.json" > "$OUT/aggregate.txt" 2>&1 || rc=1
+tail -n 2 "$OUT"/*.err | cut -c1-300
+exit $rc

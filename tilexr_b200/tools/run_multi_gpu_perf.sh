@@ -1,7 +1,8 @@
 #!/bin/bash
 # Runs every multi-GPU measurement of this repository on N GPUs of one node and leaves the
 # results under OUT: bench (this library and the NCCL baseline), the collective sweep, the
-# tensor-parallel MLP fusions and the fused all-reduce.
+# tensor-parallel MLP fusions (bf16 and block-scaled fp8), the fused all-reduce and the MoonEP stages at the
+# shapes of cases/perf.json that are written for N ranks.
 #   usage: run_multi_gpu_perf.sh N OUT
 set -u
 if [ $# -lt 2 ]; then echo "usage: $0 N OUT" >&2; exit 2; fi
@@ -26,5 +27,9 @@ for op in all_reduce reduce_scatter broadcast; do
 done
 timeout 300 $RUN --master-port 29608 -m tilexr_b200.tools.tp_mlp_perf --tokens 8192 > "$OUT/tp_mlp.json" 2> "$OUT/tp_mlp.err"
 timeout 300 $RUN --master-port 29609 -m tilexr_b200.tools.ar_norm_perf --hidden 8192 --batches 1,4,16,64,256,1024,4096,16384 > "$OUT/ar_norm.jsonl" 2> "$OUT/ar_norm.err"
+for mode in benchmark prefetch reduce-grad; do
+  timeout 300 $RUN --master-port 29610 -m tilexr_b200.tools.moonep.launcher --mode $mode --cases perf --iters 20 --warmup 5 \
+      --json "$OUT/moonep_$mode.json" --csv "$OUT/moonep_$mode.csv" > "$OUT/moonep_$mode.txt" 2> "$OUT/moonep_$mode.err"
+done
 tail -n 3 "$OUT"/*.err | cut -c1-300
 ls -la "$OUT"
