@@ -316,28 +316,11 @@ __device__ void MoonCombineV2Body(const MoonCombineV2Args &a)
             const uint32_t have = __ballot_sync(0xffffffffu, carries);
             uint8_t *y = a.hiddenOut + static_cast<uint64_t>(t) * a.rowBytes;
             for (int v = lane; v < vecs; v += 32) {
+                float acc[8];
+                SumRowsColumn(half + static_cast<uint64_t>(t) * K * a.rowBytes, a.rowBytes, K, have, static_cast<uint64_t>(v), fp32Rows ? 2 : (bf16 ? 1 : 0), acc);
                 if (fp32Rows) {
-                    float acc[4] = {0.f, 0.f, 0.f, 0.f};
-                    for (int k = 0; k < K; ++k) {
-                        if (((have >> k) & 1u) == 0) continue;
-                        const Vec16 x = ld_vec16_stream(half + (static_cast<uint64_t>(t) * K + k) * a.rowBytes + static_cast<int64_t>(v) * 16);
-                        acc[0] += __uint_as_float(x.x);
-                        acc[1] += __uint_as_float(x.y);
-                        acc[2] += __uint_as_float(x.z);
-                        acc[3] += __uint_as_float(x.w);
-                    }
                     st_vec16(y + static_cast<int64_t>(v) * 16, Vec16{__float_as_uint(acc[0]), __float_as_uint(acc[1]), __float_as_uint(acc[2]), __float_as_uint(acc[3])});
                 } else {
-                    float acc[8];
-#pragma unroll
-                    for (int q = 0; q < 8; ++q) acc[q] = 0.f;
-                    for (int k = 0; k < K; ++k) {
-                        if (((have >> k) & 1u) == 0) continue;
-                        float f[8];
-                        Unpack8(ld_vec16_stream(half + (static_cast<uint64_t>(t) * K + k) * a.rowBytes + static_cast<int64_t>(v) * 16), bf16, f);
-#pragma unroll
-                        for (int q = 0; q < 8; ++q) acc[q] += f[q];
-                    }
                     st_vec16(y + static_cast<int64_t>(v) * 16, Pack8(acc, bf16));
                 }
             }

@@ -406,7 +406,7 @@ static int LaunchCombine(TileXRCommPtr comm, const int32_t *dstLocal, const int3
         return TILEXR_MOONEP_ERROR_INVALID_ARGUMENT;
     }
     unsigned grid = 0;
-    ret = CoopGrid(comm, c, MoonCombineKernelEntry(), 0, std::min<long>(EnvLong("TILEXR_MOONEP_COMBINE_BLOCKS", 128), (nvS + 15) / 16), &grid);
+    ret = CoopGrid(comm, c, MoonCombineKernelEntry(), 0, std::min<long>(EnvLong("TILEXR_MOONEP_COMBINE_BLOCKS", 148), (nvS + 15) / 16), &grid);
     if (ret != TILEXR_MOONEP_SUCCESS) return ret;
     int64_t magic = 0;
     if (TileXRCommNextMagic(comm, &magic) != TILEXR_SUCCESS) return TILEXR_MOONEP_ERROR_INTERNAL;

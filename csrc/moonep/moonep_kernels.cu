@@ -376,26 +376,11 @@ __device__ void MoonCombineBody(const MoonCombineArgs &a)
             }
             uint8_t *y = a.hiddenOut + t * a.rowBytes;
             for (int v = lane; v < vecs; v += 32) {
+                float acc[8];
+                SumRowsColumn(half + static_cast<uint64_t>(t) * K * a.rowBytes, a.rowBytes, K, 0xffffffffu, static_cast<uint64_t>(v), a.elemKind, acc);
                 if (a.elemKind == 2) {
-                    float acc[4] = {0.f, 0.f, 0.f, 0.f};
-                    for (int k = 0; k < K; ++k) {
-                        const Vec16 x = ld_vec16_stream(half + (t * K + k) * a.rowBytes + v * 16);
-                        acc[0] += __uint_as_float(x.x);
-                        acc[1] += __uint_as_float(x.y);
-                        acc[2] += __uint_as_float(x.z);
-                        acc[3] += __uint_as_float(x.w);
-                    }
                     st_vec16(y + v * 16, Vec16{__float_as_uint(acc[0]), __float_as_uint(acc[1]), __float_as_uint(acc[2]), __float_as_uint(acc[3])});
                 } else {
-                    float acc[8];
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-                    for (int k = 0; k < K; ++k) {
-                        float f[8];
-                        Unpack8(ld_vec16_stream(half + (t * K + k) * a.rowBytes + v * 16), a.elemKind == 1, f);
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) acc[j] += f[j];
-                    }
                     st_vec16(y + v * 16, Pack8(acc, a.elemKind == 1));
                 }
             }
