@@ -88,13 +88,24 @@ __device__ __forceinline__ void ReduceNormRow(const ArNormArgs &a, SrcFn srcOf, 
     for (int i = 0; i < ARN_MAX_VECS; ++i) {
         const int v = i * ARN_THREADS + threadIdx.x;
         if (v < vecs) {
+            // Four ranks' copies of the column are fetched before the first is added (in rank order, so the sum does not
+            // depend on the batching): one at a time, every rank costs the thread a memory round trip of its own.
             float acc[8];
-            Unpack8(ld_vec16_stream(srcOf(0) + v * 16), bf16, acc);
-            for (int s = 1; s < R; ++s) {
-                float f[8];
-                Unpack8(ld_vec16_stream(srcOf(s) + v * 16), bf16, f);
+            for (int s0 = 0; s0 < R; s0 += 4) {
+                Vec16 q[4];
 #pragma unroll
-                for (int j = 0; j < 8; ++j) acc[j] += f[j];
+                for (int u = 0; u < 4; ++u) {
+                    if (s0 + u < R) q[u] = ld_vec16_stream(srcOf(s0 + u) + v * 16);
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    if (s0 + u < R) {
+                        float f[8];
+                        Unpack8(q[u], bf16, f);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) acc[j] = (s0 + u == 0) ? f[j] : acc[j] + f[j];
+                    }
+                }
             }
             if (resSrc != nullptr) {
                 float r[8];
