@@ -55,24 +55,42 @@ __device__ __forceinline__ LocalCopyEvent LocalCopyNbi(const CommArgs *args, Loc
         ev.status = RMA_MISALIGNED;
         return ev;
     }
-    uint64_t done = 0;
-    uint32_t s = 0;
-    while (done < bytes) {
-        const uint32_t n = static_cast<uint32_t>(bytes - done < LOCAL_COPY_STAGE_BYTES ? bytes - done : LOCAL_COPY_STAGE_BYTES);
-        // the store that last read this stage must have finished reading shared memory
-        BulkWaitRead<LOCAL_COPY_STAGES - 1>();
-        MbarExpectTx(&lane->full[s], n);
-        BulkLoadToSmem(lane->stage[s], reinterpret_cast<const uint8_t *>(src) + done, n, &lane->full[s]);
-        if (!MbarWait(&lane->full[s], lane->phase[s], args->waitTimeoutNs)) {
+    // Loads run LOCAL_COPY_STAGES - 1 chunks ahead of the stores: the load of chunk c + A is issued before the wait for
+    // chunk c, so several loads are in flight at once and they overlap the stores (waiting for every load right after
+    // issuing it left one transfer in flight per direction).
+    const uint64_t chunks = (bytes + LOCAL_COPY_STAGE_BYTES - 1) / LOCAL_COPY_STAGE_BYTES;
+    constexpr uint64_t AHEAD = LOCAL_COPY_STAGES - 1;
+    auto issueLoad = [&](uint64_t c) {
+        const uint32_t st = static_cast<uint32_t>(c % LOCAL_COPY_STAGES);
+        const uint64_t off = c * LOCAL_COPY_STAGE_BYTES;
+        const uint32_t n = static_cast<uint32_t>(bytes - off < LOCAL_COPY_STAGE_BYTES ? bytes - off : LOCAL_COPY_STAGE_BYTES);
+        MbarExpectTx(&lane->full[st], n);
+        BulkLoadToSmem(lane->stage[st], reinterpret_cast<const uint8_t *>(src) + off, n, &lane->full[st]);
+    };
+    BulkWaitRead<0>();                         // the stores of an earlier copy on this lane have finished reading the stages
+    for (uint64_t c = 0; c < chunks && c < AHEAD; ++c) issueLoad(c);
+    for (uint64_t c = 0; c < chunks; ++c) {
+        if (c + AHEAD < chunks) {
+            // its stage was last read by the store of chunk c - 1, the most recent bulk group
+            if (c > 0) BulkWaitRead<0>();
+            issueLoad(c + AHEAD);
+        }
+        const uint32_t st = static_cast<uint32_t>(c % LOCAL_COPY_STAGES);
+        const uint64_t off = c * LOCAL_COPY_STAGE_BYTES;
+        const uint32_t n = static_cast<uint32_t>(bytes - off < LOCAL_COPY_STAGE_BYTES ? bytes - off : LOCAL_COPY_STAGE_BYTES);
+        if (!MbarWait(&lane->full[st], lane->phase[st], args->waitTimeoutNs)) {
+            // the loads issued ahead are given the same (bounded) time to land before the caller may leave the kernel
+            for (uint64_t k = c + 1; k < chunks && k <= c + AHEAD; ++k) {
+                const uint32_t sk = static_cast<uint32_t>(k % LOCAL_COPY_STAGES);
+                if (MbarWait(&lane->full[sk], lane->phase[sk], args->waitTimeoutNs)) lane->phase[sk] ^= 1u;
+            }
             ev.status = RMA_TIMEOUT;
             break;
         }
-        lane->phase[s] ^= 1u;
-        BulkStoreFromSmem(reinterpret_cast<uint8_t *>(dst) + done, lane->stage[s], n);
+        lane->phase[st] ^= 1u;
+        BulkStoreFromSmem(reinterpret_cast<uint8_t *>(dst) + off, lane->stage[st], n);
         BulkCommit();
         ev.groups++;
-        done += n;
-        s = (s + 1) % LOCAL_COPY_STAGES;
     }
     return ev;
 }
