@@ -1,5 +1,6 @@
 #include <cstring>
 
+#include "device/tilexr_data_as_flag.cuh"
 #include "device/tilexr_local_copy.cuh"
 #include "device/tilexr_rma.cuh"
 #include "device/tilexr_sync.cuh"
@@ -27,14 +28,16 @@ struct ProbeArgs {
     uint64_t signalValue;
     uint32_t handle;
     uint32_t signalIndex;
-    int32_t mode;     // 0 put+signal, 1 get, 2 local copy, 3 signal wait, 4 range check
+    int32_t mode;     // 0 put+signal, 1 get, 2 local copy, 3 signal wait, 4 range check, 5 data-as-flag round trip
 };
 
 __device__ void ProbeBody(const ProbeArgs &a)
 {
     extern __shared__ __align__(128) uint8_t smemRaw[];
     Waiter w;
-    bool ok = KernelPrologue(w, a.comm, a.magic, TILEXR_OP_BANDWIDTH, static_cast<int64_t>(a.bytes), false);
+    // the data-as-flag probe writes into its peer's low-latency plane, whose halves alternate with the launch epoch: the
+    // reuse guard (the peer has finished the launch before last) applies to it as to every operator
+    bool ok = KernelPrologue(w, a.comm, a.magic, TILEXR_OP_BANDWIDTH, static_cast<int64_t>(a.bytes), a.mode == 5);
     CommArgs *comm = a.comm;
     const int rank = comm->rank;
     const int R = comm->rankSize;
@@ -73,6 +76,21 @@ __device__ void ProbeBody(const ProbeArgs &a)
     } else if (a.mode == 3) {
         if (blockIdx.x == 0 && threadIdx.x == 0) WaitSignalGE(w, a.signalIndex, a.signalValue);
         ok = BlockBroadcastOk(w.ok());
+    } else if (a.mode == 5) {
+        // Every block sends its share of the payload to the next rank as 16-byte units that carry the launch epoch in
+        // their last word (payload and flag in ONE transaction), and receives the previous rank's share the same way.
+        // Block `signalIndex` sends nothing: its counterpart's wait runs out of budget and the kernel reports it.
+        const int from = (rank - 1 + R) % R;
+        const uint64_t words = a.bytes / 4;
+        const uint64_t wordsPerBlock = ((words + gridDim.x - 1) / gridDim.x + 2) / 3 * 3;      // whole units per block
+        const uint64_t w0 = min(words, wordsPerBlock * blockIdx.x);
+        const uint64_t nw = min(words - w0, wordsPerBlock);
+        const uint64_t unit0 = w0 / 3;
+        if (ok && blockIdx.x != a.signalIndex) {
+            Ll16Send(LlHalf(comm, peer, w.epoch) + unit0 * LL16_UNIT_BYTES, a.localSrc + w0 * 4, nw * 4, w.epoch, threadIdx.x, blockDim.x);
+        }
+        const bool got = ok && Ll16Recv(w, a.local + w0 * 4, LlHalf(comm, rank, w.epoch) + unit0 * LL16_UNIT_BYTES, nw * 4, from, threadIdx.x, blockDim.x);
+        ok = BlockBroadcastOk(got);
     } else if (a.mode == 4) {
         if (blockIdx.x == 0 && threadIdx.x == 0) {
             int st = RMA_OK;
@@ -155,6 +173,25 @@ int TileXRLocalCopyProbe(TileXRCommPtr comm, void *dst, const void *src, uint64_
     a.localSrc = static_cast<const uint8_t *>(src);
     a.bytes = bytes;
     return Launch(comm, a, blocks, sizeof(LocalCopyLane) + 128, stream);
+}
+
+int TileXRDataAsFlagProbe(TileXRCommPtr comm, void *dst, const void *src, uint64_t bytes, uint32_t withheldBlock, uint32_t blocks,
+                          TileXRStream stream)
+{
+    if (dst == nullptr || src == nullptr || bytes == 0 || bytes % 4 != 0 || blocks == 0) return TILEXR_ERROR_PARA_CHECK_FAIL;
+    // every block's share is rounded up to whole units
+    if (tilexr::Ll16PackedBytes(bytes) + static_cast<uint64_t>(blocks) * tilexr::LL16_UNIT_BYTES > TILEXR_WIN_LL_HALF_BYTES) {
+        TILEXR_LOG(ERROR) << "data-as-flag probe: " << bytes << " payload bytes do not fit one half of the low-latency plane";
+        return TILEXR_ERROR_PARA_CHECK_FAIL;
+    }
+    ProbeArgs a;
+    std::memset(&a, 0, sizeof(a));
+    a.mode = 5;
+    a.local = static_cast<uint8_t *>(dst);
+    a.localSrc = static_cast<const uint8_t *>(src);
+    a.bytes = bytes;
+    a.signalIndex = withheldBlock;
+    return Launch(comm, a, blocks, 0, stream);
 }
 
 int TileXRSignalWaitProbe(TileXRCommPtr comm, uint32_t signalIndex, uint64_t value, TileXRStream stream)

@@ -13,6 +13,13 @@ extern "C" {
 // Every rank writes `bytes` from `localSrc` into region `handle` of rank (rank+1) % R at
 // `dstOffset`; each block then adds 1 to signal word `signalIndex` of that rank and waits until
 // this rank's own word reaches `expectedSignal` (blocks x number of calls so far).
+// Data-as-flag round trip on the low-latency plane of the windows: every rank sends `bytes` (a multiple of 4) from src to the
+// next rank as 16-byte units carrying the launch epoch, and receives the previous rank's bytes into dst.  Block
+// `withheldBlock` of every rank sends nothing (pass 0xffffffff for a complete exchange): the receiver's wait then runs out
+// of its budget and the communicator's device status says so.
+int TileXRDataAsFlagProbe(TileXRCommPtr comm, void *dst, const void *src, uint64_t bytes, uint32_t withheldBlock, uint32_t blocks,
+                          TileXRStream stream);
+
 int TileXRPutSignalProbe(TileXRCommPtr comm, TileXRUDMAMemHandle handle, uint64_t dstOffset, const void *localSrc,
                          uint64_t bytes, uint32_t signalIndex, uint64_t expectedSignal, uint32_t blocks, TileXRStream stream);
 // Every rank reads `bytes` of region `handle` of rank (rank+1) % R at `srcOffset` into `localDst`.

@@ -77,3 +77,37 @@ def test_wait_that_nobody_satisfies_times_out_cleanly(txr, port):
     torch.cuda.synchronize()
     assert comm.device_status() == 0 and torch.equal(x, y)
     comm.destroy()
+
+
+def test_data_as_flag_round_trip_and_a_withheld_block(txr):
+    """16-byte units that carry their launch epoch (payload and flag in one transaction) between the ranks of an emulated
+    world; then one block of every rank sends nothing, its counterpart's wait runs out of a 200 ms budget, the kernel ends
+    by itself, the host reads the status, and the communicator works again after a reset."""
+    ranks, n = 4, 30000                                              # 120000 bytes: 10000 units over 8 blocks
+    world = txr.init_emulated_world(ranks, device=0, buffer_mb=16)
+    g = torch.Generator().manual_seed(12)
+    src = [torch.randint(-2 ** 31, 2 ** 31 - 1, (n,), generator=g, dtype=torch.int64).to(torch.int32).cuda() for _ in range(ranks)]
+    for _ in range(3):                                               # both halves of the low-latency plane, and the reuse guard
+        dst = [torch.zeros(n, dtype=torch.int32, device="cuda") for _ in range(ranks)]
+        world.run(lambda c, r: txr._C.data_as_flag_probe(c, src[r], dst[r], -1, 8))
+        world.check()
+        for r in range(ranks):
+            assert torch.equal(dst[r], src[(r - 1) % ranks])
+    for r in range(ranks):
+        world[r].set_wait_timeout_ms(200)
+    dst = [torch.zeros(n, dtype=torch.int32, device="cuda") for _ in range(ranks)]
+    world.run(lambda c, r: txr._C.data_as_flag_probe(c, src[r], dst[r], 3, 8))
+    torch.cuda.synchronize()
+    statuses = [world[r].device_status() for r in range(ranks)]
+    assert all(s in (1, 2) for s in statuses), statuses              # wait timeout, or aborted by a peer that timed out first
+    assert all(world[r].dfx()[3] == 0xDEAD for r in range(ranks))
+    # the blocks that did get their units delivered them
+    per_block = ((n + 7) // 8 + 2) // 3 * 3
+    assert torch.equal(dst[1][:3 * per_block], src[0][:3 * per_block])
+    for r in range(ranks):
+        world[r].reset_status()
+    dst = [torch.zeros(n, dtype=torch.int32, device="cuda") for _ in range(ranks)]
+    world.run(lambda c, r: txr._C.data_as_flag_probe(c, src[r], dst[r], -1, 8))
+    world.check()
+    assert all(torch.equal(dst[r], src[(r - 1) % ranks]) for r in range(ranks))
+    world.destroy()
