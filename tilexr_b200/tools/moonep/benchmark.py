@@ -69,7 +69,57 @@ def summarise(case: MoonEPCase, samples: Mapping[str, Sequence[float]], bytes_by
                       "B": case.prefetch_slots, "dtype": case.dtype}}
 
 
-def benchmark_case(comm, case: MoonEPCase, iters: int = 20, warmup: int = 5, sample_dir: str = "", trace: bool = False) -> Dict[str, object]:
+def nccl_stage_baseline(plan, hidden_sh: torch.Tensor, iters: int, warmup: int) -> Dict[str, float]:
+    """The same dispatch and combine as a torch + NCCL program, timed on this rank (us, median): rows gathered in destination
+    order, `all_to_all_single` with the plan's split sizes, an indexed store into the [NvS, H] buffer; and back: an indexed load,
+    `all_to_all_single`, a per-token `index_add_` in fp32 and a cast.  Split sizes and the receivers' slot lists are exchanged
+    once outside the timed region (they are fixed for a plan), so nothing in the timed region waits for the host."""
+    R, NvS, K = int(plan.R), int(plan.NvS), int(plan.K)
+    dst = plan.dst.to(torch.int64)
+    raw = torch.where(dst < 0, -dst - 1, dst)
+    dest_rank = raw // NvS
+    order = torch.argsort(dest_rank, stable=True)
+    send_tokens = (order // K)
+    send_slots = (raw % NvS)[order].contiguous()
+    send_counts = torch.bincount(dest_rank, minlength=R)
+    recv_counts = torch.empty_like(send_counts)
+    dist.all_to_all_single(recv_counts, send_counts)
+    send_splits, recv_splits = send_counts.tolist(), recv_counts.tolist()
+    recv_slots = torch.empty(sum(recv_splits), dtype=torch.int64, device=dst.device)
+    dist.all_to_all_single(recv_slots, send_slots, recv_splits, send_splits)
+    rows_nvs = torch.zeros(NvS, hidden_sh.shape[1], dtype=hidden_sh.dtype, device=hidden_sh.device)
+    arrived = torch.empty(sum(recv_splits), hidden_sh.shape[1], dtype=hidden_sh.dtype, device=hidden_sh.device)
+    back = torch.empty(order.numel(), hidden_sh.shape[1], dtype=hidden_sh.dtype, device=hidden_sh.device)
+
+    def dispatch():
+        dist.all_to_all_single(arrived, hidden_sh.index_select(0, send_tokens), recv_splits, send_splits)
+        rows_nvs.index_copy_(0, recv_slots, arrived)
+
+    def combine():
+        dist.all_to_all_single(back, rows_nvs.index_select(0, recv_slots), send_splits, recv_splits)
+        acc = torch.zeros(hidden_sh.shape[0], hidden_sh.shape[1], dtype=torch.float32, device=hidden_sh.device)
+        acc.index_add_(0, send_tokens, back.float())
+        return acc.to(hidden_sh.dtype)
+
+    out = {}
+    for name, fn in (("dispatch", dispatch), ("combine", combine)):
+        times = []
+        for it in range(warmup + iters):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            if it >= warmup:
+                times.append(e0.elapsed_time(e1) * 1e3)
+        times.sort()
+        t = torch.tensor([times[len(times) // 2]], dtype=torch.float64, device=hidden_sh.device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        out[name] = float(t.item())
+    return out
+
+
+def benchmark_case(comm, case: MoonEPCase, iters: int = 20, warmup: int = 5, sample_dir: str = "", trace: bool = False, nccl_baseline: bool = False) -> Dict[str, object]:
     """``trace``: one more dispatch after the timed loop records the kernel's event trace; the result then carries this
     rank's per-phase summary (``dispatch_phases``: count, mean and longest duration, bytes) beside the stage times."""
     rank = comm.rank
@@ -118,6 +168,8 @@ def benchmark_case(comm, case: MoonEPCase, iters: int = 20, warmup: int = 5, sam
     grad_row = 0 if grads is None else _row_bytes(grads.gate) + _row_bytes(grads.up) + _row_bytes(grads.down)
     nbytes = algorithm_bytes(plan, rank, case.hidden * esize, 4, proj_row, grad_row)
     out = summarise(case, samples, nbytes, iters, warmup, dev)
+    if nccl_baseline and dist.is_initialized() and dist.get_world_size() > 1:
+        out["nccl_baseline_us"] = nccl_stage_baseline(plan, inp.hidden_sh, max(3, iters // 2), 2)
     if trace:
         from .dispatch_trace import phase_summary
 

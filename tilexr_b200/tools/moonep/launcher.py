@@ -33,6 +33,8 @@ def main(argv=None) -> int:
     ap.add_argument("--json", default="")
     ap.add_argument("--csv", default="", help="benchmark modes: one row per (case, stage) with P50 / P99")
     ap.add_argument("--samples", default="", help="benchmark: directory for per-rank sample files; aggregate: where to read them")
+    ap.add_argument("--nccl-baseline", action="store_true",
+                    help="benchmark: also time dispatch and combine as a torch + NCCL program (index_select, all_to_all_single with the plan's splits, index_add_)")
     ap.add_argument("--trace", action="store_true", help="benchmark: also record the dispatch kernel's event trace once per case and print its phases")
     ap.add_argument("--buffer-mb", type=int, default=0, help="communicator window size (default: sized for the largest case)")
     args = ap.parse_args(argv)
@@ -97,7 +99,7 @@ def main(argv=None) -> int:
             if rank == 0:
                 print(report.correctness_markdown(results))
         else:
-            run = {"benchmark": lambda c: benchmark_case(comm, c, iters=args.iters, warmup=args.warmup, sample_dir=args.samples, trace=args.trace),
+            run = {"benchmark": lambda c: benchmark_case(comm, c, iters=args.iters, warmup=args.warmup, sample_dir=args.samples, trace=args.trace, nccl_baseline=args.nccl_baseline),
                    "prefetch": lambda c: prefetch_weight_benchmark(comm, c, iters=args.iters, warmup=args.warmup),
                    "reduce-grad": lambda c: reduce_grad_benchmark(comm, c, iters=args.iters, warmup=args.warmup)}[args.mode]
             for c in cases:
@@ -109,6 +111,10 @@ def main(argv=None) -> int:
             if rank == 0:
                 print(report.benchmark_markdown(results))
                 for r in results:
+                    if "nccl_baseline_us" in r:
+                        b = r["nccl_baseline_us"]
+                        print(f"{r['case']} torch + NCCL: dispatch {b['dispatch']:.1f} us, combine {b['combine']:.1f} us "
+                              f"(this library: {r['stage_us']['dispatch']:.1f} / {r['stage_us']['combine']:.1f})")
                     for ph in r.get("dispatch_phases", []):
                         print(f"{r['case']} dispatch phase {ph['phase']}: {ph['count']} events, mean {ph['mean_us']:.1f} us, "
                               f"longest {ph['max_us']:.1f} us, {ph['bytes'] / 1e6:.1f} MB, {ph['rows']} rows")
