@@ -119,9 +119,17 @@ def nccl_stage_baseline(plan, hidden_sh: torch.Tensor, iters: int, warmup: int) 
     return out
 
 
-def benchmark_case(comm, case: MoonEPCase, iters: int = 20, warmup: int = 5, sample_dir: str = "", trace: bool = False, nccl_baseline: bool = False) -> Dict[str, object]:
+def benchmark_case(comm, case: MoonEPCase, iters: int = 20, warmup: int = 5, sample_dir: str = "", trace: bool = False, nccl_baseline: bool = False,
+                   stage_barrier: bool = False) -> Dict[str, object]:
     """``trace``: one more dispatch after the timed loop records the kernel's event trace; the result then carries this
     rank's per-phase summary (``dispatch_phases``: count, mean and longest duration, bytes) beside the stage times."""
+    # ``stage_barrier``: a device synchronisation and a host barrier of the ranks in front of every stage (the reference's
+    # mindspeed_stage_barrier): a stage's time is then the kernel's own and not the skew its peers arrived with.
+    def align():
+        if stage_barrier:
+            torch.cuda.synchronize()
+            comm.barrier()
+
     rank = comm.rank
     buf = TileXRMoonEPBuffer(comm, case.tokens, case.hidden, case.top_k, case.experts, token_padding=case.token_padding,
                              B=case.prefetch_slots, dtype=case.torch_dtype())
@@ -142,20 +150,25 @@ def benchmark_case(comm, case: MoonEPCase, iters: int = 20, warmup: int = 5, sam
     plan = None
     for it in range(warmup + iters):
         ev = {s: (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for s in stages}
+        align()
         ev["planning"][0].record()
         plan = buf.planning(inp.topk_experts_sk)
         ev["planning"][1].record()
+        align()
         ev["dispatch"][0].record()
         rows, w = buf.dispatch(inp.hidden_sh, inp.route_weights_sk, plan)
         ev["dispatch"][1].record()
         if proj is not None:
+            align()
             ev["prefetch_weight"][0].record()
             buf.prefetch_weight(plan, proj)
             ev["prefetch_weight"][1].record()
+        align()
         ev["combine"][0].record()
         buf.combine(plan, rows, w)
         ev["combine"][1].record()
         if grads is not None:
+            align()
             ev["reduce_grad"][0].record()
             buf.reduce_grad(plan, ProjectionBuffers(grads.gate, grads.up, grads.down))
             ev["reduce_grad"][1].record()

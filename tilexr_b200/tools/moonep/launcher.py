@@ -33,6 +33,8 @@ def main(argv=None) -> int:
     ap.add_argument("--json", default="")
     ap.add_argument("--csv", default="", help="benchmark modes: one row per (case, stage) with P50 / P99")
     ap.add_argument("--samples", default="", help="benchmark: directory for per-rank sample files; aggregate: where to read them")
+    ap.add_argument("--stage-barrier", action="store_true",
+                    help="benchmark: synchronise the device and the ranks in front of every stage, so that a stage's time excludes the skew of the one before")
     ap.add_argument("--nccl-baseline", action="store_true",
                     help="benchmark: also time dispatch and combine as a torch + NCCL program (index_select, all_to_all_single with the plan's splits, index_add_)")
     ap.add_argument("--trace", action="store_true", help="benchmark: also record the dispatch kernel's event trace once per case and print its phases")
@@ -99,7 +101,8 @@ def main(argv=None) -> int:
             if rank == 0:
                 print(report.correctness_markdown(results))
         else:
-            run = {"benchmark": lambda c: benchmark_case(comm, c, iters=args.iters, warmup=args.warmup, sample_dir=args.samples, trace=args.trace, nccl_baseline=args.nccl_baseline),
+            run = {"benchmark": lambda c: benchmark_case(comm, c, iters=args.iters, warmup=args.warmup, sample_dir=args.samples, trace=args.trace, nccl_baseline=args.nccl_baseline,
+                                                      stage_barrier=args.stage_barrier),
                    "prefetch": lambda c: prefetch_weight_benchmark(comm, c, iters=args.iters, warmup=args.warmup),
                    "reduce-grad": lambda c: reduce_grad_benchmark(comm, c, iters=args.iters, warmup=args.warmup)}[args.mode]
             for c in cases:
