@@ -26,6 +26,32 @@ __device__ __forceinline__ void RankRoutesByWarp(const int32_t *experts, int32_t
     }
 }
 
+// The same ranks for `experts` in global memory: the expert ids of four steps are fetched before the first of them is
+// ranked, so that the four loads are in flight together (one step's load would otherwise sit in front of every step).
+__device__ __forceinline__ void RankRoutesByWarpDeep(const int32_t *experts, int32_t *rank, int32_t *hist, int n, int lane)
+{
+    const unsigned below = (1u << lane) - 1u;
+    for (int base = 0; base < n; base += 128) {
+        int e4[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int i = base + u * 32 + lane;
+            e4[u] = i < n ? experts[i] : -1;
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int i = base + u * 32 + lane;
+            if (base + u * 32 >= n) break;      // warp-uniform
+            const int e = e4[u];
+            const unsigned same = __match_any_sync(0xffffffffu, e);
+            if (i < n) rank[i] = e >= 0 ? hist[e] + __popc(same & below) : 0;
+            __syncwarp();
+            if (e >= 0 && (same & below) == 0) hist[e] += __popc(same);
+            __syncwarp();
+        }
+    }
+}
+
 } // namespace tilexr
 
 #endif

@@ -329,27 +329,25 @@ TXR_PLAN2_FN void NoteShortfall(const Dims &d, const Tables &t, Progress &g, int
 TXR_PLAN2_FN int32_t MoveShare(const Dims &d, Tables &t, Progress &g, int32_t home, int32_t dst, int32_t requested)
 {
     if (requested <= 0 || home == dst || g.fatal != PLAN_OK) return 0;
-    // home's experts with a share left, largest share first, lower id on ties
-    int32_t n = 0;
-    for (int32_t e = home * d.L; e < (home + 1) * d.L; ++e) {
-        const int32_t share = t.alloc[At(d, home, e)];
-        if (share <= 0) continue;
-        int32_t j = n++;
-        while (j > 0) {
-            const int32_t prev = t.expertList[j - 1];
-            const int32_t prevShare = t.alloc[At(d, home, prev)];
-            if (share < prevShare || (share == prevShare && e > prev)) break;
-            t.expertList[j] = prev;
-            --j;
-        }
-        t.expertList[j] = e;
-    }
+    // home's experts with a share left are visited largest share first, lower id on ties.  Usually the first one or two
+    // cover the request, so the next expert is selected when it is needed (one pass over home's L experts) instead of
+    // sorting all of them first; the shares of the experts not yet visited do not change in between, so the order is
+    // that of the sorted list.  expertList[0, L) marks the visited ones.
+    const int32_t first = home * d.L;
+    for (int32_t i = 0; i < d.L; ++i) t.expertList[i] = 0;
     int32_t open = requested;
     bool usable = false;
-    for (int32_t i = 0; i < n && open > 0; ++i) {
-        const int32_t expert = t.expertList[i];
-        const int32_t share = t.alloc[At(d, home, expert)];
-        if (share <= 0) continue;
+    while (open > 0) {
+        int32_t expert = -1, share = 0;
+        for (int32_t i = 0; i < d.L; ++i) {
+            const int32_t v = t.alloc[At(d, home, first + i)];
+            if (v > share && t.expertList[i] == 0) {
+                expert = first + i;
+                share = v;
+            }
+        }
+        if (expert < 0) break;
+        t.expertList[expert - first] = 1;
         const bool held = HoldsExpert(d, t, dst, expert);
         if (!held && t.slotsUsed[dst] >= d.B) {
             g.slotBlock = 1;
@@ -469,103 +467,186 @@ TXR_PLAN2_FN void BalanceAcrossServers(const Dims &d, const Inputs &in, Tables &
     }
 }
 
-// What nobody moved is computed at home.
+// What nobody moved is computed at home.  The routes of one expert: every source's remainder goes to the expert's home
+// rank, in source order.  Returns true when this rank is one of the sources; *seg is then its segment, which the caller
+// appends to the list (in expert order).  Experts touch disjoint cells, so they can be handled in parallel.
+TXR_PLAN2_FN bool RemainderOfExpert(const Dims &d, Tables &t, int32_t e, Segment *seg)
+{
+    const int32_t home = e / d.L;
+    const int64_t homeCell = At(d, home, e);
+    int32_t cursor = t.dstCursor[homeCell];
+    bool mine = false;
+    for (int32_t src = 0; src < d.R; ++src) {
+        const int64_t cell = At(d, src, e);
+        const int32_t n = t.remaining[cell];
+        if (n <= 0) continue;
+        if (src == d.rank) {
+            seg->expert = e;
+            seg->src = src;
+            seg->dst = home;
+            seg->srcBegin = t.srcCursor[cell];
+            seg->dstBegin = cursor;
+            seg->count = n;
+            mine = true;
+        }
+        t.remaining[cell] = 0;
+        t.srcCursor[cell] += n;
+        cursor += n;
+    }
+    t.dstCursor[homeCell] = cursor;
+    return mine;
+}
+
+// true when RemainderOfExpert(e) will return a segment of this rank (asked before it runs)
+TXR_PLAN2_FN bool RemainderIsMine(const Dims &d, const Tables &t, int32_t e) { return t.remaining[At(d, d.rank, e)] > 0; }
+
 TXR_PLAN2_FN void SendRemaindersHome(const Dims &d, Tables &t, Progress &g)
 {
     for (int32_t e = 0; e < d.E; ++e) {
-        const int32_t home = e / d.L;
-        const int64_t homeCell = At(d, home, e);
-        for (int32_t src = 0; src < d.R; ++src) {
-            const int64_t cell = At(d, src, e);
-            const int32_t n = t.remaining[cell];
-            if (n <= 0) continue;
-            if (!RecordSegment(d, t, g, e, src, home, t.srcCursor[cell], t.dstCursor[homeCell], n)) return;
-            t.remaining[cell] = 0;
-            t.srcCursor[cell] += n;
-            t.dstCursor[homeCell] += n;
+        Segment seg;
+        if (!RemainderOfExpert(d, t, e, &seg)) continue;
+        if (g.localSegments >= d.segCapacity) {
+            g.fatal = PLAN_ERROR_MOVE_RECORD_OVERFLOW;
+            return;
         }
+        t.segments[g.localSegments++] = seg;
     }
 }
 
 // ---- layouts --------------------------------------------------------------------------------------------------------
 // Per destination: its foreign experts ordered by share (descending, lower id first) take the weight slots; rows are
 // laid out as the experts computed from home weights (groups 0..E-1, foreign ones empty) followed by the slots
-// (groups E..E+B-1), every group padded.
-TXR_PLAN2_FN int32_t BuildLayouts(const Dims &d, const Outputs &out, Tables &t, Progress &g)
+// (groups E..E+B-1), every group padded.  Cut into a clearing step, a step per destination that fills the slots and a
+// step per destination that lays out the rows, so that the kernel can spread each step over its threads; between the
+// steps the per-destination results (t.listA: slots used, t.listB: slots whose expert lives here, t.listC: status) are
+// folded by one thread.
+#if defined(__CUDA_ARCH__)
+#define TXR_PLAN2_OR64(ptr, value) atomicOr(reinterpret_cast<unsigned long long *>(ptr), static_cast<unsigned long long>(value))
+#else
+#define TXR_PLAN2_OR64(ptr, value) (*(ptr) |= (value))
+#endif
+
+TXR_PLAN2_FN void LayoutClear(const Dims &d, const Outputs &out, Tables &t, int32_t first, int32_t stride)
 {
     const int32_t groups = d.E + d.B;
     const int32_t words = (d.R + 63) / 64;
-    for (int64_t i = 0; i < static_cast<int64_t>(d.R) * d.B; ++i) t.slots[i] = -1;
-    for (int32_t i = 0; i < d.B; ++i) out.expertsToCopy[i] = -1;
+    for (int64_t i = first; i < static_cast<int64_t>(d.R) * d.B; i += stride) t.slots[i] = -1;
+    for (int32_t i = first; i < d.B; i += stride) out.expertsToCopy[i] = -1;
     if (out.remoteExperts != nullptr) {
-        for (int64_t i = 0; i < static_cast<int64_t>(d.R) * d.B; ++i) out.remoteExperts[i] = -1;
-        for (int64_t i = 0; i < static_cast<int64_t>(d.L) * words; ++i) out.expertTargets[i] = 0;
+        for (int64_t i = first; i < static_cast<int64_t>(d.R) * d.B; i += stride) out.remoteExperts[i] = -1;
+        for (int64_t i = first; i < static_cast<int64_t>(d.L) * words; i += stride) out.expertTargets[i] = 0;
     }
-    for (int32_t i = 0; i < groups; ++i) out.cuSeqlens[i] = 0;
-    out.remoteStats[0] = 0;
-    out.remoteStats[1] = 0;
+    for (int32_t i = first; i < groups; i += stride) out.cuSeqlens[i] = 0;
+}
+
+TXR_PLAN2_FN void LayoutSlotsOfDst(const Dims &d, const Outputs &out, Tables &t, int32_t dst)
+{
+    const int32_t words = (d.R + 63) / 64;
+    int32_t *row = t.slots + static_cast<int64_t>(dst) * d.B;
+    int32_t n = 0;
+    t.listA[dst] = 0;
+    t.listB[dst] = 0;
+    t.listC[dst] = PLAN_OK;
+    for (int32_t e = 0; e < d.E; ++e) {
+        const int32_t share = t.alloc[At(d, dst, e)];
+        if (share <= 0 || e / d.L == dst) continue;
+        if (n >= d.B) {
+            t.listC[dst] = PLAN_PARTIAL_PREFETCH_SLOT_EXHAUSTED;
+            return;
+        }
+        int32_t j = n++;
+        while (j > 0) {
+            const int32_t prevShare = t.alloc[At(d, dst, row[j - 1])];
+            if (!(share > prevShare || (share == prevShare && e < row[j - 1]))) break;
+            row[j] = row[j - 1];
+            --j;
+        }
+        row[j] = e;
+    }
+    int32_t mine = 0;
+    for (int32_t i = 0; i < d.B; ++i) {
+        const int32_t e = row[i];
+        if (dst == d.rank) out.expertsToCopy[i] = e;
+        if (out.remoteExperts != nullptr) out.remoteExperts[static_cast<int64_t>(dst) * d.B + i] = e;
+        if (e >= 0 && e / d.L == d.rank) {
+            ++mine;
+            if (out.expertTargets != nullptr) {
+                TXR_PLAN2_OR64(&out.expertTargets[static_cast<int64_t>(e - d.rank * d.L) * words + dst / 64], 1ull << (dst % 64));
+            }
+        }
+    }
+    t.listA[dst] = n;
+    t.listB[dst] = mine;
+}
+
+// Folds the slot step; returns its status.
+TXR_PLAN2_FN int32_t LayoutFoldSlots(const Dims &d, const Outputs &out, const Tables &t, Progress &g)
+{
+    int32_t status = PLAN_OK, mine = 0;
     g.maxRemote = 0;
     g.localEnd = 0;
-
     for (int32_t dst = 0; dst < d.R; ++dst) {
-        int32_t *row = t.slots + static_cast<int64_t>(dst) * d.B;
-        int32_t n = 0;
-        for (int32_t e = 0; e < d.E; ++e) {
-            const int32_t share = t.alloc[At(d, dst, e)];
-            if (e / d.L == dst || share <= 0) continue;
-            if (n >= d.B) return PLAN_PARTIAL_PREFETCH_SLOT_EXHAUSTED;
-            int32_t j = n++;
-            while (j > 0) {
-                const int32_t prevShare = t.alloc[At(d, dst, row[j - 1])];
-                if (!(share > prevShare || (share == prevShare && e < row[j - 1]))) break;
-                row[j] = row[j - 1];
-                --j;
-            }
-            row[j] = e;
-        }
-        if (n > g.maxRemote) g.maxRemote = n;
-        if (dst == d.rank) out.remoteStats[0] = n;
-        for (int32_t i = 0; i < d.B; ++i) {
-            const int32_t e = row[i];
-            if (dst == d.rank) out.expertsToCopy[i] = e;
-            if (out.remoteExperts != nullptr) out.remoteExperts[static_cast<int64_t>(dst) * d.B + i] = e;
-            if (e >= 0 && e / d.L == d.rank) {
-                ++out.remoteStats[1];
-                if (out.expertTargets != nullptr) {
-                    out.expertTargets[static_cast<int64_t>(e - d.rank * d.L) * words + dst / 64] |= 1ull << (dst % 64);
-                }
-            }
-        }
+        if (t.listC[dst] != PLAN_OK) status = t.listC[dst];
+        if (t.listA[dst] > g.maxRemote) g.maxRemote = t.listA[dst];
+        mine += t.listB[dst];
     }
+    out.remoteStats[0] = t.listA[d.rank];
+    out.remoteStats[1] = mine;
+    return status;
+}
 
-    int32_t *inSlot = t.expertList;   // scratch: 1 for the experts that sit in a slot of the current destination
-    for (int32_t dst = 0; dst < d.R; ++dst) {
-        const int32_t *row = t.slots + static_cast<int64_t>(dst) * d.B;
-        for (int32_t e = 0; e < d.E; ++e) inSlot[e] = 0;
-        for (int32_t i = 0; i < d.B; ++i) {
-            if (row[i] >= 0) inSlot[row[i]] = 1;
+// After the slot step succeeded everywhere, a foreign expert with a share on dst sits in one of dst's slots.
+TXR_PLAN2_FN void LayoutRowsOfDst(const Dims &d, const Outputs &out, Tables &t, Progress &g, int32_t dst)
+{
+    const int32_t groups = d.E + d.B;
+    const int32_t *row = t.slots + static_cast<int64_t>(dst) * d.B;
+    const int32_t homeBegin = dst * d.L, homeEnd = homeBegin + d.L;
+    // count <= nvS < 2^31 and padding <= nvS, so count + padding fits 32 unsigned bits: a 32-bit division (the 64-bit one
+    // is a subroutine of a hundred cycles on the GPU)
+    const uint32_t pad = static_cast<uint32_t>(d.padding);
+    int64_t end = 0;
+    t.listC[dst] = PLAN_OK;
+    for (int32_t group = 0; group < groups; ++group) {
+        int32_t expert = -1;
+        if (group < d.E) {
+            const bool foreign = group < homeBegin || group >= homeEnd;
+            if (!(foreign && t.alloc[At(d, dst, group)] > 0)) expert = group;      // else it is computed in its slot
+        } else {
+            expert = row[group - d.E];
         }
-        int64_t end = 0;
-        for (int32_t group = 0; group < groups; ++group) {
-            int32_t expert = -1;
-            if (group < d.E) {
-                if (!inSlot[group]) expert = group;
-            } else {
-                expert = row[group - d.E];
-            }
-            int32_t count = 0;
-            if (expert >= 0) {
-                count = t.alloc[At(d, dst, expert)];
-                t.base[At(d, dst, expert)] = static_cast<int32_t>(end);
-            }
-            const int64_t padded = count == 0 ? 0 : (static_cast<int64_t>(count) + d.padding - 1) / d.padding * d.padding;
-            if (padded > static_cast<int64_t>(d.nvS) - end) return PLAN_ERROR_LAYOUT_EXCEEDS_NVS;
-            end += padded;
-            if (dst == d.rank) out.cuSeqlens[group] = static_cast<int32_t>(end);
+        int32_t count = 0;
+        if (expert >= 0) {
+            count = t.alloc[At(d, dst, expert)];
+            t.base[At(d, dst, expert)] = static_cast<int32_t>(end);
         }
-        if (dst == d.rank) g.localEnd = static_cast<int32_t>(end);
+        const int64_t padded = count <= 0 ? 0 : static_cast<int64_t>((static_cast<uint32_t>(count) + pad - 1u) / pad) * pad;
+        if (padded > static_cast<int64_t>(d.nvS) - end) {
+            t.listC[dst] = PLAN_ERROR_LAYOUT_EXCEEDS_NVS;
+            return;
+        }
+        end += padded;
+        if (dst == d.rank) out.cuSeqlens[group] = static_cast<int32_t>(end);
     }
-    return PLAN_OK;
+    if (dst == d.rank) g.localEnd = static_cast<int32_t>(end);
+}
+
+TXR_PLAN2_FN int32_t LayoutFoldRows(const Dims &d, const Tables &t)
+{
+    int32_t status = PLAN_OK;
+    for (int32_t dst = 0; dst < d.R; ++dst) {
+        if (t.listC[dst] != PLAN_OK) status = t.listC[dst];
+    }
+    return status;
+}
+
+TXR_PLAN2_FN int32_t BuildLayouts(const Dims &d, const Outputs &out, Tables &t, Progress &g)
+{
+    LayoutClear(d, out, t, 0, 1);
+    for (int32_t dst = 0; dst < d.R; ++dst) LayoutSlotsOfDst(d, out, t, dst);
+    int32_t status = LayoutFoldSlots(d, out, t, g);
+    if (status != PLAN_OK) return status;
+    for (int32_t dst = 0; dst < d.R; ++dst) LayoutRowsOfDst(d, out, t, g, dst);
+    return LayoutFoldRows(d, t);
 }
 
 // Table initialisation, cut so that the kernel can spread it over its threads: every function handles the items
@@ -613,18 +694,29 @@ TXR_PLAN2_FN void PlanInitSerial(const Dims &d, const Inputs &in, Tables &t)
 // ---- the sequential part ----------------------------------------------------------------------------------------------
 // Runs on one thread, after the initialisation above.  Afterwards g.fatal / g.balanced / g.layoutStatus say whether
 // destinations can be computed.
-TXR_PLAN2_FN void PlanBalance(const Dims &d, const Inputs &in, const Outputs &out, Tables &t, Progress &g)
+TXR_PLAN2_FN void PlanMoves(const Dims &d, const Inputs &in, Tables &t, Progress &g)
 {
     g = Progress{};
     BuildAffinity(d, in, t);
     BalanceWithinServers(d, in, t, g);
     if (g.fatal == PLAN_OK) BalanceAcrossServers(d, in, t, g);
-    if (g.fatal == PLAN_OK) SendRemaindersHome(d, t, g);
-    if (g.fatal != PLAN_OK) return;
+}
+
+TXR_PLAN2_FN void PlanNoteBalanced(const Dims &d, const Tables &t, Progress &g)
+{
     g.balanced = 1;
     for (int32_t r = 0; r < d.R; ++r) {
         if (t.load[r] != d.cap) g.balanced = 0;
     }
+}
+
+// The whole of it on one thread (the CPU form; the kernel runs PlanMoves on one thread and spreads the rest).
+TXR_PLAN2_FN void PlanBalance(const Dims &d, const Inputs &in, const Outputs &out, Tables &t, Progress &g)
+{
+    PlanMoves(d, in, t, g);
+    if (g.fatal == PLAN_OK) SendRemaindersHome(d, t, g);
+    if (g.fatal != PLAN_OK) return;
+    PlanNoteBalanced(d, t, g);
     g.layoutStatus = BuildLayouts(d, out, t, g);
 }
 
@@ -648,6 +740,15 @@ TXR_PLAN2_FN void PlanOrdinalsOfExpert(const Dims &d, const Inputs &in, Tables &
     }
 }
 
+// Raw destination of the route with this ordinal inside segment m (which covers it), or -1 when the row is out of range.
+TXR_PLAN2_FN int32_t RouteRawInSegment(const Dims &d, const Tables &t, const Segment &m, int32_t ordinal)
+{
+    const int64_t row = static_cast<int64_t>(t.base[At(d, m.dst, m.expert)]) + m.dstBegin + (ordinal - m.srcBegin);
+    const int64_t raw = static_cast<int64_t>(m.dst) * d.nvS + row;
+    if (row < 0 || row >= d.nvS || raw > 0x7fffffff) return -1;
+    return static_cast<int32_t>(raw);
+}
+
 // Raw destination of one route, or -1 when no segment covers it (an internal error).
 TXR_PLAN2_FN int32_t PlanRouteDst(const Dims &d, const Inputs &in, const Tables &t, const Progress &g, int32_t route)
 {
@@ -656,10 +757,20 @@ TXR_PLAN2_FN int32_t PlanRouteDst(const Dims &d, const Inputs &in, const Tables 
     for (int32_t i = 0; i < g.localSegments; ++i) {
         const Segment &m = t.segments[i];
         if (m.expert != expert || ordinal < m.srcBegin || ordinal >= m.srcBegin + m.count) continue;
-        const int64_t row = static_cast<int64_t>(t.base[At(d, m.dst, expert)]) + m.dstBegin + (ordinal - m.srcBegin);
-        const int64_t raw = static_cast<int64_t>(m.dst) * d.nvS + row;
-        if (row < 0 || row >= d.nvS || raw > 0x7fffffff) return -1;
-        return static_cast<int32_t>(raw);
+        return RouteRawInSegment(d, t, m, ordinal);
+    }
+    return -1;
+}
+
+// The same through per-expert lists of the segments (head[expert] = one segment of the expert or -1, next[i] = another
+// one or -1): the segments of an expert cover disjoint ordinals, so the order of a list does not matter.
+TXR_PLAN2_FN int32_t PlanRouteDstListed(const Dims &d, const Tables &t, const int32_t *head, const int32_t *next, int32_t expert,
+                                        int32_t ordinal)
+{
+    for (int32_t i = head[expert]; i >= 0; i = next[i]) {
+        const Segment &m = t.segments[i];
+        if (ordinal < m.srcBegin || ordinal >= m.srcBegin + m.count) continue;
+        return RouteRawInSegment(d, t, m, ordinal);
     }
     return -1;
 }

@@ -11,6 +11,7 @@
 //
 // Reference: src/moonep/planner_v2/kernels/tilexr_moonep_planner_kernel.cpp:232-366 (mailbox phases), 542-695.
 #include "device/tilexr_rma.cuh"
+#include "device/tilexr_route_rank.cuh"
 #include "device/tilexr_sync.cuh"
 #include "plan_v2_kernel.h"
 #include "tilexr_types.h"
@@ -57,11 +58,20 @@ __device__ void PlanV2Body(const PlanV2Args &a)
     __shared__ plan2::Progress g;
     __shared__ int sValidate;
     __shared__ int sBadRoute;
+    __shared__ int sRemainders;
     __shared__ int sFinal;
     __shared__ uint64_t sHash;
 
     Waiter w;
     bool ok = KernelPrologue(w, a.comm, a.magic, TILEXR_OP_MOONEP_PLANNING, a.dims.cap, true);
+    uint64_t phaseStart = now_ns();
+    auto phaseDone = [&](int index) {      // thread 0 leaves the phase's duration in the DFX block (read with TileXRGetCommArgsHost)
+        if (threadIdx.x == 0) {
+            const uint64_t t1 = now_ns();
+            a.comm->dfx[TILEXR_DFX_PLAN_PHASE_NS + index] = static_cast<int64_t>(t1 - phaseStart);
+            phaseStart = t1;
+        }
+    };
     const plan2::Dims d = a.dims;
     const int tid = threadIdx.x, nt = blockDim.x;
     const plan2::Inputs in{a.topk, a.tpe, a.globalIds};
@@ -95,6 +105,7 @@ __device__ void PlanV2Body(const PlanV2Args &a)
         }
         ok = MeetRanks(w, a, 1);
     }
+    phaseDone(0);
     // 2. check what arrived against the caller's table
     int mismatch = 0;
     if (ok) {
@@ -162,21 +173,59 @@ __device__ void PlanV2Body(const PlanV2Args &a)
         for (int64_t i = tid; i < tpeWords; i += nt) planShared[prefixWords + i] = a.tpe[i];
     }
     __syncthreads();
+    phaseDone(1);
+    // the tables the balancing works on: the shared-memory copy when there is one
+    plan2::Tables tb = t;
+    plan2::Inputs inb = in;
+    if (staged) {
+        plan2::Carve(d, planShared, &tb);
+        tb.ordinal = t.ordinal;                                             // not touched by the balancing
+        tb.segments = reinterpret_cast<plan2::Segment *>(planShared + prefixWords + tpeWords);
+        inb.tpe = planShared + prefixWords;
+    }
     if (tid == 0) {
         int32_t v = (mismatch & 2) ? PLAN_ERROR_CONFIG_MISMATCH : (mismatch & 1) ? PLAN_ERROR_TPE_MISMATCH : PLAN_OK;
         if (ok && v == PLAN_OK) v = (bad & 2) ? PLAN_ERROR_CONFIG_MISMATCH : (bad & 1) ? PLAN_ERROR_TPE_MISMATCH : PLAN_OK;
         sValidate = v;
         g = plan2::Progress{};
-        if (ok && v == PLAN_OK) {
-            if (staged) {
-                plan2::Tables ts;
-                plan2::Carve(d, planShared, &ts);
-                ts.ordinal = t.ordinal;                                             // not touched by the balancing
-                ts.segments = reinterpret_cast<plan2::Segment *>(planShared + prefixWords + tpeWords);
-                const plan2::Inputs ins{a.topk, planShared + prefixWords, a.globalIds};
-                plan2::PlanBalance(d, ins, a.out, ts, g);
+        if (ok && v == PLAN_OK) plan2::PlanMoves(d, inb, tb, g);           // the moves between ranks: sequential by nature
+    }
+    __syncthreads();
+    // What follows the moves has no order between experts (the remainders) or between destinations (the layouts), so the
+    // block spreads it: plan2::PlanBalance is the same steps on one thread.
+    if (balance && g.fatal == PLAN_OK) {                                   // block-uniform: g is shared
+        for (int e = tid; e < d.E; e += nt) tb.expertList[e] = plan2::RemainderIsMine(d, tb, e) ? 1 : 0;
+        __syncthreads();
+        const int32_t firstSegment = g.localSegments;
+        for (int e = tid; e < d.E; e += nt) {
+            int32_t before = 0;                                            // this rank's remainder segments are listed in expert order
+            for (int f = 0; f < e; ++f) before += tb.expertList[f];
+            plan2::Segment seg;
+            if (plan2::RemainderOfExpert(d, tb, e, &seg) && firstSegment + before < d.segCapacity) tb.segments[firstSegment + before] = seg;
+            if (e == d.E - 1) sRemainders = before + tb.expertList[e];
+        }
+        __syncthreads();
+        if (tid == 0) {
+            if (firstSegment + sRemainders > d.segCapacity) {
+                g.fatal = PLAN_ERROR_MOVE_RECORD_OVERFLOW;
+                g.localSegments = d.segCapacity;
             } else {
-                plan2::PlanBalance(d, in, a.out, t, g);
+                g.localSegments = firstSegment + sRemainders;
+                plan2::PlanNoteBalanced(d, tb, g);
+            }
+        }
+        __syncthreads();
+        if (g.fatal == PLAN_OK) {
+            plan2::LayoutClear(d, a.out, tb, tid, nt);
+            __syncthreads();
+            for (int dst = tid; dst < d.R; dst += nt) plan2::LayoutSlotsOfDst(d, a.out, tb, dst);
+            __syncthreads();
+            if (tid == 0) g.layoutStatus = plan2::LayoutFoldSlots(d, a.out, tb, g);
+            __syncthreads();
+            if (g.layoutStatus == PLAN_OK) {
+                for (int dst = tid; dst < d.R; dst += nt) plan2::LayoutRowsOfDst(d, a.out, tb, g, dst);
+                __syncthreads();
+                if (tid == 0) g.layoutStatus = plan2::LayoutFoldRows(d, tb);
             }
         }
     }
@@ -188,12 +237,50 @@ __device__ void PlanV2Body(const PlanV2Args &a)
         for (int64_t i = tid; i < segWords; i += nt) segsOut[i] = segs[i];
         __syncthreads();
     }
+    phaseDone(2);
     const bool planned = ok && sValidate == PLAN_OK;
     if (planned && plan2::PlanHasDestinations(g)) {
-        for (int e = tid; e < d.E; e += nt) plan2::PlanOrdinalsOfExpert(d, in, t, e);
+        // Ordinal of a route among this rank's routes to the same expert, in route order, then its destination.  The
+        // routes are cut into one contiguous piece per warp; every warp ranks its piece against a histogram of its own
+        // (32 routes a step), the histograms are turned into per-piece offsets, and the pass that computes the
+        // destinations adds the offset.  A route finds its segment through per-expert lists.  The tables of the balancing
+        // that are no longer needed hold all of it: srcCursor and dstCursor (adjacent) the histograms, expertList the list
+        // heads, remaining the links.
+        const int pieces = min(nt / 32, 2 * d.R);
+        const int pieceRoutes = ((d.cap + pieces - 1) / pieces + 31) / 32 * 32;
+        int32_t *hists = tb.srcCursor;
+        int32_t *head = tb.expertList;
+        int32_t *next = tb.remaining;
+        const bool listed = g.localSegments <= d.R * d.E;
+        for (int i = tid; i < pieces * d.E; i += nt) hists[i] = 0;
+        for (int e = tid; e < d.E; e += nt) head[e] = -1;
         __syncthreads();
+        if (tid / 32 < pieces) {
+            const int begin = (tid / 32) * pieceRoutes;
+            const int n = min(pieceRoutes, d.cap - begin);
+            if (n > 0) RankRoutesByWarpDeep(a.topk + begin, t.ordinal + begin, hists + (tid / 32) * d.E, n, tid % 32);
+        }
+        if (listed) {
+            for (int i = tid; i < g.localSegments; i += nt) next[i] = atomicExch(&head[tb.segments[i].expert], i);
+        }
+        __syncthreads();
+        for (int e = tid; e < d.E; e += nt) {
+            int32_t before = 0;
+            for (int w = 0; w < pieces; ++w) {
+                const int32_t v = hists[w * d.E + e];
+                hists[w * d.E + e] = before;
+                before += v;
+            }
+        }
+        __syncthreads();
+        plan2::Tables tr = t;
+        tr.base = tb.base;
+        tr.segments = tb.segments;
         for (int r = tid; r < d.cap; r += nt) {
-            const int32_t raw = plan2::PlanRouteDst(d, in, t, g, r);
+            const int32_t expert = a.topk[r];
+            const int32_t ordinal = t.ordinal[r] + hists[(r / pieceRoutes) * d.E + expert];
+            t.ordinal[r] = ordinal;
+            const int32_t raw = listed ? plan2::PlanRouteDstListed(d, tr, head, next, expert, ordinal) : plan2::PlanRouteDst(d, in, tr, g, r);
             if (raw < 0) sBadRoute = 1;
             a.out.dst[r] = raw < 0 ? 0 : raw;
         }
@@ -205,6 +292,7 @@ __device__ void PlanV2Body(const PlanV2Args &a)
         for (int r = tid; r < d.cap; r += nt) a.out.dst[r] = 0;
     }
     __syncthreads();
+    phaseDone(3);
     const bool routed = planned && plan2::PlanHasDestinations(g) && sBadRoute == 0;
     if (a.stageDst != nullptr) {
         // every route tells its destination which row it fills (the combine stage walks the rows)
@@ -257,6 +345,7 @@ __device__ void PlanV2Body(const PlanV2Args &a)
         }
         if (tid == 0) *a.stageStatus = usable ? 0 : (sFinal != PLAN_OK ? sFinal : PLAN_ERROR_INTERNAL_INVARIANT);
     }
+    phaseDone(4);
     KernelEpilogue(w, ok);
 }
 

@@ -59,12 +59,16 @@ def main():
     world.check()
     status = plans[0]["status"].cpu().tolist()
     v2_us = timed(lambda: world.run(lambda c, r: _C.moonep_plan_v2(c, dev_topk[r], dev_tpe, gids, B, nvs, args.padding, 0)))
+    torch.cuda.synchronize()
+    phases = [v / 1e3 for v in world[0].dfx()[16:21]]      # rank 0's last launch: mail, validate + set-up, balance, routes, consensus (us)
     v3_us = timed(lambda: world.run(lambda c, r: _C.moonep_planning(c, dev_topk[r], E, B, args.padding)))
     world.check()
     loads_before = tpe.sum(0).reshape(R, E // R).sum(1)
     dup = int(sum((pl["dst"] < 0).sum().item() for pl in plans))
     print(json.dumps({"ranks": R, "tokens_per_rank": S, "top_k": K, "experts": E, "slots": B, "skew": args.skew,
                       "plan_v2_us": v2_us, "plan_v3_us": v3_us, "status": status,
+                      "plan_v2_phases_us": dict(zip(("mail", "validate_setup", "balance", "routes", "consensus"), phases)),
+                      "plan_v2_kernel_us": sum(phases),      # rank 0's block, first to last phase; plan_v2_us also holds the host's work for R ranks
                       "load_before_max_over_cap": float(loads_before.max()) / (S * K),
                       "deficit_after": status[3], "intra_rounds": status[1], "inter_rounds": status[2], "expert_moves": status[6],
                       "max_remote_experts": status[4], "duplicate_routes": dup, "routes": R * S * K,
