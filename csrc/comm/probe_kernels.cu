@@ -4,6 +4,7 @@
 #include "device/tilexr_local_copy.cuh"
 #include "device/tilexr_rma.cuh"
 #include "device/tilexr_sync.cuh"
+#include "device/tilexr_udma.cuh"
 #include "tilexr_launch.h"
 #include "tilexr_log.h"
 #include "tilexr_probes.h"
@@ -28,7 +29,7 @@ struct ProbeArgs {
     uint64_t signalValue;
     uint32_t handle;
     uint32_t signalIndex;
-    int32_t mode;     // 0 put+signal, 1 get, 2 local copy, 3 signal wait, 4 range check, 5 data-as-flag round trip
+    int32_t mode;     // 0 put+signal, 1 get, 2 local copy, 3 signal wait, 4 range check, 5 data-as-flag round trip, 6 reference-named verbs
 };
 
 __device__ void ProbeBody(const ProbeArgs &a)
@@ -91,6 +92,36 @@ __device__ void ProbeBody(const ProbeArgs &a)
         }
         const bool got = ok && Ll16Recv(w, a.local + w0 * 4, LlHalf(comm, rank, w.epoch) + unit0 * LL16_UNIT_BYTES, nw * 4, from, threadIdx.x, blockDim.x);
         ok = BlockBroadcastOk(got);
+    } else if (a.mode == 6) {
+        // The reference's verb names (device/tilexr_udma.cuh).  Warp g of the launch puts its share of the payload into the
+        // next rank's region 0 and raises signal word g of that region behind it (put with signal), waits for its own
+        // word g, which the previous rank's warp g raises, and reads its share back from the next rank (get).  The signal
+        // words follow the payload at a.offset.  A put that leaves the region must be refused.
+        const uint64_t warps = blockDim.x / 32;
+        const uint64_t g = blockIdx.x * warps + threadIdx.x / 32;
+        const uint64_t G = gridDim.x * warps;
+        const uint64_t share = ((a.bytes + G - 1) / G + 15) & ~15ull;
+        const uint64_t b0 = min(a.bytes, share * g);
+        const uint32_t nb = static_cast<uint32_t>(min(a.bytes - b0, share));
+        const int from = (rank - 1 + R) % R;
+        bool good = ok;
+        if (good) {
+            const uint32_t qp = static_cast<uint32_t>(g % UDMAQpCount(comm));
+            good = UDMAPutSignalNbiOnQp<uint8_t>(comm, peer, qp, a.localSrc + b0, b0, nb, a.offset + g * 8, MakeFlag(w.epoch, 1)) ==
+                   TILEXR_UDMA_STATUS_SUCCESS;
+            good = good && UDMAPutNbiOnQp<uint8_t>(comm, peer, 0, a.localSrc, a.offset + G * 8, 16) == TILEXR_UDMA_STATUS_INVALID;
+            if (!good && (threadIdx.x & 31u) == 0) RaiseFailure(w, TILEXR_DEV_BAD_RANGE, peer, static_cast<int64_t>(g), a.offset, nb);
+        }
+        if (good && (threadIdx.x & 31u) == 0) {
+            const uint64_t *word = reinterpret_cast<const uint64_t *>(UDMARegisteredRemoteAddr(comm, rank, a.offset + g * 8, 8));
+            good = word != nullptr && WaitFlagGE(w, word, 1, from, static_cast<int64_t>(g));
+        }
+        good = __shfl_sync(0xffffffffu, good ? 1 : 0, 0) != 0;
+        if (good) {
+            good = UDMAGetNbiOnQp<uint8_t>(comm, peer, 0, a.local + b0, b0, nb) == TILEXR_UDMA_STATUS_SUCCESS;
+            UDMAQuiet(comm, peer);
+        }
+        ok = BlockBroadcastOk(good);
     } else if (a.mode == 4) {
         if (blockIdx.x == 0 && threadIdx.x == 0) {
             int st = RMA_OK;
@@ -191,6 +222,22 @@ int TileXRDataAsFlagProbe(TileXRCommPtr comm, void *dst, const void *src, uint64
     a.localSrc = static_cast<const uint8_t *>(src);
     a.bytes = bytes;
     a.signalIndex = withheldBlock;
+    return Launch(comm, a, blocks, 0, stream);
+}
+
+int TileXRNamedVerbsProbe(TileXRCommPtr comm, void *dst, const void *src, uint64_t bytes, uint64_t signalOffset, uint32_t blocks,
+                          TileXRStream stream)
+{
+    if (dst == nullptr || src == nullptr || bytes == 0 || bytes % 16 != 0 || signalOffset % 8 != 0 || signalOffset < bytes || blocks == 0) {
+        return TILEXR_ERROR_PARA_CHECK_FAIL;
+    }
+    ProbeArgs a;
+    std::memset(&a, 0, sizeof(a));
+    a.mode = 6;
+    a.local = static_cast<uint8_t *>(dst);
+    a.localSrc = static_cast<const uint8_t *>(src);
+    a.bytes = bytes;
+    a.offset = signalOffset;
     return Launch(comm, a, blocks, 0, stream);
 }
 

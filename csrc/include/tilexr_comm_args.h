@@ -134,7 +134,7 @@ enum TileXRDfxSlot {
     TILEXR_DFX_FAIL_BLOCK = 9,
     TILEXR_DFX_LAUNCHES = 10,
     // Phase times of the last topology-aware planner launch on this rank, ns: mail exchange, validation and table set-up,
-    // balancing (one thread), per-route destinations, consensus and stage tables.
+    // balancing, per-route destinations, consensus and stage tables.
     TILEXR_DFX_PLAN_PHASE_NS = 16,     // five entries
 };
 

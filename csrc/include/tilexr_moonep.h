@@ -23,6 +23,7 @@
 #include <stdint.h>
 
 #include "tilexr_api.h"
+#include "tilexr_moonep_planner.h"
 
 #ifdef __cplusplus
 extern "C" {
@@ -263,18 +264,7 @@ int TileXRMoonEpReduceGradPrepareV2(const TileXRMoonEpReduceGradPrepareArgsV2 *a
 int TileXRMoonEpReduceGradDestroyPreparedV2(TileXRMoonEpReduceGradPreparedV2 prepared);
 int TileXRMoonEpReduceGradV2(const TileXRMoonEpReduceGradArgsV2 *args, TileXRStream stream);
 
-// ---- planner, direct form (reference: src/include/tilexr_moonep_planner.h:18-40) ---------------------
-int TileXRMoonEpPlannerGetWorkspaceSizeV3(int64_t s, int64_t k, int64_t e, int64_t b, int64_t r, int64_t tokenPadding,
-                                          uint64_t *workspaceBytes, int64_t *nvS);
-int TileXRMoonEpPlannerGetDstLocalOffsetV3(int64_t s, int64_t k, int64_t e, int64_t b, int64_t r, int64_t tokenPadding,
-                                           uint64_t *offsetBytes);
-// workspace: at least ...GetWorkspaceSizeV3 bytes of device memory; dstLocal (int32 [nvS]) is
-// written at ...GetDstLocalOffsetV3 inside it.
-int TileXRMoonEpPlannerV3(const int32_t *topkExperts, const int32_t *tokensPerExpert, TileXRCommPtr comm, int64_t s,
-                          int64_t k, int64_t e, int64_t b, int64_t tokenPadding, void *workspace, uint64_t workspaceBytes,
-                          int32_t *dst, int32_t *cuSeqlens, int32_t *expertsToCopy, int32_t *zeroFillRanges,
-                          int32_t *remoteStats, int32_t *dupCounts, int32_t *status, uint64_t waitIterations,
-                          TileXRStream stream);
+// The planners' direct entry points (TileXRMoonEpPlannerV2 / V3 and their size queries) are in tilexr_moonep_planner.h.
 
 // ---- CPU reference of the whole protocol (single process, all ranks) --------------------------------------
 // allTopk int32 [r, s*k].  Outputs for rank `rank`; any output pointer may be null.

@@ -10,9 +10,6 @@
 extern "C" {
 #endif
 
-// Every rank writes `bytes` from `localSrc` into region `handle` of rank (rank+1) % R at
-// `dstOffset`; each block then adds 1 to signal word `signalIndex` of that rank and waits until
-// this rank's own word reaches `expectedSignal` (blocks x number of calls so far).
 // Data-as-flag round trip on the low-latency plane of the windows: every rank sends `bytes` (a multiple of 4) from src to the
 // next rank as 16-byte units carrying the launch epoch, and receives the previous rank's bytes into dst.  Block
 // `withheldBlock` of every rank sends nothing (pass 0xffffffff for a complete exchange): the receiver's wait then runs out
@@ -20,6 +17,16 @@ extern "C" {
 int TileXRDataAsFlagProbe(TileXRCommPtr comm, void *dst, const void *src, uint64_t bytes, uint32_t withheldBlock, uint32_t blocks,
                           TileXRStream stream);
 
+// The reference's device verb names (device/tilexr_udma.cuh) between neighbours: every warp of the launch puts its share of
+// `bytes` (a multiple of 16) from src into registered region 0 of the next rank with a signal word behind it (the words start
+// at `signalOffset` of the region, 8 bytes per warp, `blocks` x 16 warps), waits for its own word and gets the share back
+// from the next rank into dst.
+int TileXRNamedVerbsProbe(TileXRCommPtr comm, void *dst, const void *src, uint64_t bytes, uint64_t signalOffset, uint32_t blocks,
+                          TileXRStream stream);
+
+// Every rank writes `bytes` from `localSrc` into region `handle` of rank (rank+1) % R at
+// `dstOffset`; each block then adds 1 to signal word `signalIndex` of that rank and waits until
+// this rank's own word reaches `expectedSignal` (blocks x number of calls so far).
 int TileXRPutSignalProbe(TileXRCommPtr comm, TileXRUDMAMemHandle handle, uint64_t dstOffset, const void *localSrc,
                          uint64_t bytes, uint32_t signalIndex, uint64_t expectedSignal, uint32_t blocks, TileXRStream stream);
 // Every rank reads `bytes` of region `handle` of rank (rank+1) % R at `srcOffset` into `localDst`.

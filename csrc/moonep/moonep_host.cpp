@@ -159,20 +159,26 @@ int TileXRMoonEpGetCapabilitiesV2(uint64_t *nativeStages, uint64_t *stubStages)
     return TileXRMoonEpGetCapabilitiesV1(nativeStages, stubStages);
 }
 
-int TileXRMoonEpPlannerGetWorkspaceSizeV3(int64_t s, int64_t k, int64_t e, int64_t b, int64_t r, int64_t tokenPadding,
+int TileXRMoonEpPlannerGetWorkspaceSizeV3(TileXRCommPtr comm, int64_t s, int64_t k, int64_t e, int64_t b, int64_t tokenPadding,
                                           uint64_t *workspaceBytes, int64_t *nvS)
 {
-    if (!ValidDims(s, k, e, b, r, tokenPadding) || workspaceBytes == nullptr) return TILEXR_MOONEP_ERROR_INVALID_ARGUMENT;
-    const PlanDims d = MakeDims(s, k, e, b, r, tokenPadding);
+    Ctx c;
+    const int ret = Prepare(comm, &c);
+    if (ret != TILEXR_MOONEP_SUCCESS) return ret;
+    if (!ValidDims(s, k, e, b, c.R, tokenPadding) || workspaceBytes == nullptr) return TILEXR_MOONEP_ERROR_INVALID_ARGUMENT;
+    const PlanDims d = MakeDims(s, k, e, b, c.R, tokenPadding);
     *workspaceBytes = Align(static_cast<uint64_t>(d.NvS) * 4, 256);   // dstLocal; the tables live in the window
     if (nvS != nullptr) *nvS = d.NvS;
     return TILEXR_MOONEP_SUCCESS;
 }
 
-int TileXRMoonEpPlannerGetDstLocalOffsetV3(int64_t s, int64_t k, int64_t e, int64_t b, int64_t r, int64_t tokenPadding,
+int TileXRMoonEpPlannerGetDstLocalOffsetV3(TileXRCommPtr comm, int64_t s, int64_t k, int64_t e, int64_t b, int64_t tokenPadding,
                                            uint64_t *offsetBytes)
 {
-    if (!ValidDims(s, k, e, b, r, tokenPadding) || offsetBytes == nullptr) return TILEXR_MOONEP_ERROR_INVALID_ARGUMENT;
+    Ctx c;
+    const int ret = Prepare(comm, &c);
+    if (ret != TILEXR_MOONEP_SUCCESS) return ret;
+    if (!ValidDims(s, k, e, b, c.R, tokenPadding) || offsetBytes == nullptr) return TILEXR_MOONEP_ERROR_INVALID_ARGUMENT;
     *offsetBytes = 0;
     return TILEXR_MOONEP_SUCCESS;
 }
@@ -180,10 +186,7 @@ int TileXRMoonEpPlannerGetDstLocalOffsetV3(int64_t s, int64_t k, int64_t e, int6
 int TileXRMoonEpPlanningGetWorkspaceSizeV1(TileXRCommPtr comm, int64_t s, int64_t k, int64_t e, int64_t b,
                                            int64_t tokenPadding, uint64_t *workspaceBytes, int64_t *nvS)
 {
-    Ctx c;
-    int ret = Prepare(comm, &c);
-    if (ret != TILEXR_MOONEP_SUCCESS) return ret;
-    return TileXRMoonEpPlannerGetWorkspaceSizeV3(s, k, e, b, c.R, tokenPadding, workspaceBytes, nvS);
+    return TileXRMoonEpPlannerGetWorkspaceSizeV3(comm, s, k, e, b, tokenPadding, workspaceBytes, nvS);
 }
 
 int TileXRMoonEpPlannerV3(const int32_t *topkExperts, const int32_t *tokensPerExpert, TileXRCommPtr comm, int64_t s,

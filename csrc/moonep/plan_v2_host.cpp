@@ -4,8 +4,11 @@
 #include <cstring>
 #include <vector>
 
+#include <cuda_runtime_api.h>
+
 #include "plan_v2_kernel.h"
 #include "tilexr_log.h"
+#include "tilexr_moonep_planner.h"
 #include "tilexr_types.h"
 
 using namespace TileXR;
@@ -403,6 +406,104 @@ int TileXRMoeEpPlanV2WithStageTables(const int32_t *topkExperts, const int32_t *
     m->b = config->prefetchSlots;
     m->nvS = config->nvS;
     m->epoch += 1;
+    return TILEXR_SUCCESS;
+}
+
+} // extern "C"
+
+// ---- the older call shape: one workspace, no configuration (tilexr_moonep_planner.h) ------------------------------------------
+namespace {
+
+struct CompatLayout {
+    uint64_t tablesBytes, rankIdsOff, statusOff, totalBytes;
+};
+
+TileXRMoonEPPlanConfig CompatConfig(int64_t rankSize, int64_t s, int64_t k, int64_t expertCount)
+{
+    TileXRMoonEPPlanConfig c;
+    std::memset(&c, 0, sizeof(c));
+    c.prefetchSlots = expertCount / rankSize;
+    c.rankTokenCapacity = s * k;
+    c.nvS = c.rankTokenCapacity;
+    c.tokenPadding = 1;
+    c.tokenRouteLimitPerPair = 0;
+    c.cardsPerServer = TILEXR_MOONEP_PLAN_CARDS_PER_SERVER;
+    c.cardsPerCabinet = TILEXR_MOONEP_PLAN_CARDS_PER_CABINET;
+    c.crossCandidateCount = TILEXR_MOONEP_PLAN_CROSS_CANDIDATES;
+    return c;
+}
+
+int CompatLayoutOf(int64_t rankSize, int64_t s, int64_t k, int64_t expertCount, CompatLayout *out)
+{
+    if (rankSize <= 0 || s <= 0 || k <= 0 || expertCount <= 0 || expertCount % rankSize != 0 || s > kI32Max / k) return TILEXR_ERROR_PARA_CHECK_FAIL;
+    const TileXRMoonEPPlanConfig c = CompatConfig(rankSize, s, k, expertCount);
+    uint64_t tables = 0;
+    const int ret = TileXRMoeEpPlanV2GetWorkspaceSize(rankSize, s, k, expertCount, &c, &tables, nullptr);
+    if (ret != TILEXR_SUCCESS) return ret;
+    auto align = [](uint64_t v) { return (v + 63) / 64 * 64; };
+    out->tablesBytes = tables;
+    out->rankIdsOff = align(tables);
+    out->statusOff = align(out->rankIdsOff + static_cast<uint64_t>(rankSize) * sizeof(int32_t));
+    out->totalBytes = align(out->statusOff + TILEXR_MOONEP_PLAN_STATUS_WORDS * sizeof(int32_t));
+    return TILEXR_SUCCESS;
+}
+
+} // namespace
+
+extern "C" {
+
+int TileXRMoonEpPlannerGetWorkspaceSizeV2(TileXRCommPtr comm, int64_t s, int64_t k, int64_t expertCount, uint64_t *workspaceBytes,
+                                          int64_t *dispatchedCapacity)
+{
+    if (workspaceBytes == nullptr || dispatchedCapacity == nullptr) return TILEXR_ERROR_PARA_CHECK_FAIL;
+    *workspaceBytes = 0;
+    *dispatchedCapacity = 0;
+    int rank = 0, rankSize = 0;
+    int ret = RankOf(comm, &rank, &rankSize);
+    if (ret != TILEXR_SUCCESS) return ret;
+    CompatLayout layout;
+    ret = CompatLayoutOf(rankSize, s, k, expertCount, &layout);
+    if (ret != TILEXR_SUCCESS) return ret;
+    *workspaceBytes = layout.totalBytes;
+    *dispatchedCapacity = s * k;
+    return TILEXR_SUCCESS;
+}
+
+int TileXRMoonEpPlannerV2(const int32_t *topkExpertIds, const int32_t *tokensPerExpert, TileXRCommPtr comm, int64_t s, int64_t k,
+                          int64_t expertCount, void *workspace, uint64_t workspaceBytes, int32_t *dst, int32_t *cuSeqlens,
+                          int32_t *expertsToCopy, int32_t *remoteStats, int32_t *plannerStatus, uint64_t waitIterations,
+                          TileXRStream stream)
+{
+    if (topkExpertIds == nullptr || tokensPerExpert == nullptr || workspace == nullptr || dst == nullptr || cuSeqlens == nullptr ||
+        expertsToCopy == nullptr || remoteStats == nullptr || plannerStatus == nullptr || waitIterations == 0 ||
+        reinterpret_cast<uintptr_t>(workspace) % 64 != 0) {
+        return TILEXR_ERROR_PARA_CHECK_FAIL;
+    }
+    if (comm == nullptr) return TILEXR_ERROR_NOT_INITIALIZED;
+    TileXRCommArgs *hostArgs = nullptr;
+    int ret = TileXRGetCommArgsHost(comm, &hostArgs);
+    if (ret != TILEXR_SUCCESS) return ret;
+    const int rankSize = hostArgs->rankSize, local = hostArgs->localRankSize;
+    CompatLayout layout;
+    ret = CompatLayoutOf(rankSize, s, k, expertCount, &layout);
+    if (ret != TILEXR_SUCCESS || workspaceBytes < layout.totalBytes || local <= 0 || rankSize % local != 0) return TILEXR_ERROR_PARA_CHECK_FAIL;
+    // a rank's place in its server decides the balancing order: local ranks fill a server of eight cards from its first card
+    std::vector<int32_t> ids(static_cast<size_t>(rankSize));
+    for (int r = 0; r < rankSize; ++r) ids[static_cast<size_t>(r)] = (r / local) * TILEXR_MOONEP_PLAN_CARDS_PER_SERVER + r % local;
+    uint8_t *base = static_cast<uint8_t *>(workspace);
+    int32_t *idsDev = reinterpret_cast<int32_t *>(base + layout.rankIdsOff);
+    int32_t *statusDev = reinterpret_cast<int32_t *>(base + layout.statusOff);
+    // pageable source: the call returns once the ids are staged, so the vector may go
+    if (cudaMemcpyAsync(idsDev, ids.data(), ids.size() * sizeof(int32_t), cudaMemcpyHostToDevice, static_cast<cudaStream_t>(stream)) != cudaSuccess) {
+        return TILEXR_ERROR_MKIRT;
+    }
+    const TileXRMoonEPPlanConfig config = CompatConfig(rankSize, s, k, expertCount);
+    const plan2::Outputs out{dst, cuSeqlens, expertsToCopy, remoteStats, nullptr, nullptr, statusDev};
+    ret = LaunchPlan(topkExpertIds, tokensPerExpert, idsDev, comm, s, k, expertCount, &config, out, base, layout.tablesBytes, stream);
+    if (ret != TILEXR_SUCCESS) return ret;
+    if (cudaMemcpyAsync(plannerStatus, statusDev, sizeof(int32_t), cudaMemcpyDeviceToDevice, static_cast<cudaStream_t>(stream)) != cudaSuccess) {
+        return TILEXR_ERROR_MKIRT;
+    }
     return TILEXR_SUCCESS;
 }
 

@@ -66,3 +66,81 @@ def test_data_as_flag_layout_and_round_trip_on_the_host(tmp_path):
     assert proc.returncode == 0, proc.stderr[-3000:]
     run = subprocess.run([str(exe)], capture_output=True, text=True, timeout=60)
     assert run.returncode == 0 and run.stdout.strip() == "ok", (run.returncode, run.stdout, run.stderr)
+
+
+UDMA_PROGRAM = r'''
+#include <cstdio>
+#include <cstring>
+#include <vector>
+#include "device/tilexr_udma.cuh"
+using namespace tilexr;
+int main()
+{
+    // two ranks whose registered regions live in this process; the program plays rank 0
+    constexpr uint64_t BYTES = 4096;
+    std::vector<unsigned char> region0(BYTES, 0), region1(BYTES, 0);
+    uint8_t *peers[2] = {region0.data(), region1.data()};
+    TileXR::TileXRRegistry reg;
+    std::memset(&reg, 0, sizeof(reg));
+    reg.magic = TILEXR_REGISTRY_MAGIC;
+    reg.rankSize = 2;
+    reg.regionCount = 1;
+    reg.regions[0].bytes = BYTES;
+    reg.regions[0].localBase = peers[0];
+    reg.regions[0].peerBase = peers;
+    CommArgs args;
+    std::memset(&args, 0, sizeof(args));
+    args.rank = 0;
+    args.rankSize = 2;
+    args.extraFlag = TileXR::TILEXR_FLAG_HOST_MEMORY;
+    if (UDMAEnabled(&args) || UDMAQpCount(&args) != 0) return 1;                   // no registry, no verbs
+    args.extraFlag |= TileXR::TILEXR_FLAG_RMA;
+    args.registryPtr = &reg;
+    if (!UDMAEnabled(&args) || !UDMARegistryEnabled(&args) || UDMAQpCount(&args) == 0) return 2;
+    if (!UDMARankValid(&args, 1) || UDMARankValid(&args, 0) || UDMARankValid(&args, 2)) return 3;   // a peer, never itself
+    std::vector<unsigned char> src(512), back(512, 0);
+    for (size_t i = 0; i < src.size(); ++i) src[i] = static_cast<unsigned char>(i * 5 + 1);
+    if (UDMAPutNbiOnQp<unsigned char>(&args, 1, 0, src.data(), 1024, 512) != TILEXR_UDMA_STATUS_SUCCESS) return 4;
+    UDMAQuiet(&args, 1);
+    if (std::memcmp(region1.data() + 1024, src.data(), 512) != 0) return 5;
+    if (UDMAGetNbiOnQp<unsigned char>(&args, 1, 3, back.data(), 1024, 512) != TILEXR_UDMA_STATUS_SUCCESS) return 6;
+    if (UDMAQuietStatus(&args, 1) != TILEXR_UDMA_STATUS_SUCCESS || std::memcmp(back.data(), src.data(), 512) != 0) return 7;
+    // payload, then the signal word
+    if (UDMAPutSignalNbiOnQp<unsigned char>(&args, 1, 1, src.data(), 2048, 256, 4088, 77) != TILEXR_UDMA_STATUS_SUCCESS) return 8;
+    uint64_t word = 0;
+    std::memcpy(&word, region1.data() + 4088, 8);
+    if (word != 77 || std::memcmp(region1.data() + 2048, src.data(), 256) != 0) return 9;
+    // refused before a byte moves: range, rank, lane, signal alignment, signal range
+    std::memset(region1.data(), 0, BYTES);
+    if (UDMAPutNbiOnQp<unsigned char>(&args, 1, 0, src.data(), 4000, 512) != TILEXR_UDMA_STATUS_INVALID) return 10;
+    if (UDMAPutNbiOnQp<unsigned char>(&args, 0, 0, src.data(), 0, 16) != TILEXR_UDMA_STATUS_INVALID) return 11;
+    if (UDMAPutNbiOnQp<unsigned char>(&args, 1, 99, src.data(), 0, 16) != TILEXR_UDMA_STATUS_INVALID) return 12;
+    if (UDMAPutSignalNbiOnQp<unsigned char>(&args, 1, 0, src.data(), 0, 16, 4, 1) != TILEXR_UDMA_STATUS_INVALID) return 13;
+    if (UDMAPutSignalNbiOnQp<unsigned char>(&args, 1, 0, src.data(), 0, 16, 4096, 1) != TILEXR_UDMA_STATUS_INVALID) return 14;
+    if (UDMAGetNbiOnQp<unsigned char>(&args, 1, 0, back.data(), 4090, 16) != TILEXR_UDMA_STATUS_INVALID) return 15;
+    for (uint64_t i = 0; i < BYTES; ++i) {
+        if (region1[i] != 0) return 16;
+    }
+    if (SDMAEnabled(&args)) return 17;
+    args.extraFlag |= TileXR::TILEXR_FLAG_LOCAL_COPY;
+    if (!SDMAEnabled(&args)) return 18;
+    std::puts("ok");
+    return 0;
+}
+'''
+
+
+def test_reference_named_verbs_on_the_host(tmp_path):
+    """The reference's device verb names (UDMAPutNbi, UDMAGetNbi, UDMAPutSignalNbi, UDMAQuiet, ...) over the registered-memory
+    verbs: round trips between two regions, and every bad rank, lane or range refused before a byte moves.
+    (Reference: src/include/tilexr_udma.h:748-1046.)"""
+    if shutil.which("g++") is None:
+        pytest.skip("no C++ compiler")
+    src = tmp_path / "udma.cpp"
+    src.write_text(UDMA_PROGRAM)
+    exe = tmp_path / "udma"
+    proc = subprocess.run(["g++", "-std=c++17", "-O1", f"-I{ROOT / 'csrc' / 'include'}", str(src), "-o", str(exe)],
+                          capture_output=True, text=True)
+    assert proc.returncode == 0, proc.stderr[-3000:]
+    run = subprocess.run([str(exe)], capture_output=True, text=True, timeout=60)
+    assert run.returncode == 0 and run.stdout.strip() == "ok", (run.returncode, run.stdout, run.stderr)

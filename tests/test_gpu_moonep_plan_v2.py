@@ -40,6 +40,27 @@ def test_kernel_matches_oracle(R, S, K, E, B, skew):
         world.destroy()
 
 
+@pytest.mark.parametrize("R,S,K,E,skew", [(4, 32, 4, 32, None), (8, 64, 8, 64, 0.5)])
+def test_older_call_shape_plans_like_the_configured_call(R, S, K, E, skew):
+    """TileXRMoonEpPlannerV2 (one workspace, no configuration; reference src/include/tilexr_moonep_planner.h:18-25) is the
+    topology-aware planner with experts-per-rank slots, s * k rows per rank, padding 1 and server-local global ids."""
+    world = txr.init_emulated_world(R, device=0, buffer_mb=16)
+    try:
+        topk, tpe = make_routing(R, S, K, E, seed=11 + R, skew=skew)
+        ref = plan_all(topk, tpe, list(range(R)), E // R, S * K, padding=1)
+        dev_topk = [torch.from_numpy(topk[r]).cuda() for r in range(R)]
+        dev_tpe = torch.from_numpy(tpe).cuda()
+        got = world.run(lambda c, rank: _C.moonep_planner_v2_compat(c, dev_topk[rank], dev_tpe))
+        world.check()
+        for r in range(R):
+            assert got[r]["dispatched_capacity"] == S * K
+            for key in ("dst", "cu_seqlens", "experts_to_copy", "remote_stats"):
+                assert torch.equal(got[r][key].cpu(), ref[r][key]), (r, key)
+            assert int(got[r]["planner_status"].item()) == int(ref[r]["status"][0])
+    finally:
+        world.destroy()
+
+
 def test_wrong_table_on_one_rank_is_seen_by_all():
     R, S, K, E, B = 4, 16, 2, 16, 4
     world = txr.init_emulated_world(R, device=0, buffer_mb=16)

@@ -111,3 +111,26 @@ def test_data_as_flag_round_trip_and_a_withheld_block(txr):
     world.check()
     assert all(torch.equal(dst[r], src[(r - 1) % ranks]) for r in range(ranks))
     world.destroy()
+
+
+def test_reference_named_verbs_between_emulated_ranks(txr):
+    """Kernels written against the reference's device verbs (UDMAPutSignalNbi, UDMAGetNbi, UDMAQuiet; its
+    src/include/tilexr_udma.h:748-1046) run on the registered-memory verbs: every warp puts its share into the next rank's
+    region with a signal word behind it, waits for its own word, and gets the share back; a put that leaves the region is
+    refused on the device."""
+    ranks, blocks = 4, 4
+    world = txr.init_emulated_world(ranks, device=0, buffer_mb=16)
+    n = 1 << 18                                         # payload bytes
+    words = blocks * 16                                 # one signal word per warp of the launch
+    region = world.symm_empty((n + words * 8,), torch.uint8)
+    for r in range(ranks):
+        region[r].zero_()
+    src = [torch.randint(0, 255, (n,), dtype=torch.uint8, device="cuda") for _ in range(ranks)]
+    dst = [torch.zeros(n, dtype=torch.uint8, device="cuda") for _ in range(ranks)]
+    for _ in range(2):                                  # the second launch waits for a later epoch in the same words
+        world.run(lambda c, r: txr._C.named_verbs_probe(c, src[r], dst[r], n, blocks))
+        world.check()
+    for r in range(ranks):
+        assert torch.equal(region[(r + 1) % ranks][:n], src[r])
+        assert torch.equal(dst[r], src[r])
+    world.destroy()
