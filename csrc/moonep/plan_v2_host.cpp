@@ -7,6 +7,7 @@
 #include <cuda_runtime_api.h>
 
 #include "plan_v2_kernel.h"
+#include "tilexr_launch.h"
 #include "tilexr_log.h"
 #include "tilexr_moonep_planner.h"
 #include "tilexr_types.h"
@@ -501,10 +502,11 @@ int TileXRMoonEpPlannerV2(const int32_t *topkExpertIds, const int32_t *tokensPer
     const plan2::Outputs out{dst, cuSeqlens, expertsToCopy, remoteStats, nullptr, nullptr, statusDev};
     ret = LaunchPlan(topkExpertIds, tokensPerExpert, idsDev, comm, s, k, expertCount, &config, out, base, layout.tablesBytes, stream);
     if (ret != TILEXR_SUCCESS) return ret;
-    if (cudaMemcpyAsync(plannerStatus, statusDev, sizeof(int32_t), cudaMemcpyDeviceToDevice, static_cast<cudaStream_t>(stream)) != cudaSuccess) {
-        return TILEXR_ERROR_MKIRT;
-    }
-    return TILEXR_SUCCESS;
+    // behind the planner's launch (a communicator of an emulated world only queues it until its group closes)
+    cudaStream_t cs = static_cast<cudaStream_t>(stream);
+    return RunAfterLaunch(comm, [=]() {
+        return cudaMemcpyAsync(plannerStatus, statusDev, sizeof(int32_t), cudaMemcpyDeviceToDevice, cs) == cudaSuccess ? TILEXR_SUCCESS : TILEXR_ERROR_MKIRT;
+    });
 }
 
 } // extern "C"
