@@ -26,12 +26,17 @@
 #define TILEXR_PING_PONG_SIZE 2
 #define TILEXR_COMM_BUFFER_SIZE_MB 1024          /* default 2*D */
 #define TILEXR_MEMORY_DOMAIN_BUFFER_SIZE_MB 8    /* isolated small domain (reference: MemoryDomain) */
+/* the same two sizes and the flag area under the reference's names (src/include/tilexr_types.h:25-31) */
+#define TILEXR_COMM_BUFFER_SIZE TILEXR_COMM_BUFFER_SIZE_MB
+#define TILEXR_MEMORY_DOMAIN_BUFFER_SIZE TILEXR_MEMORY_DOMAIN_BUFFER_SIZE_MB
+#define TILEXR_INVALID_VALUE (-1LL)
 #define TILEXR_MAX_REGISTERED_REGIONS 64
 
 #define TILEXR_WIN_CTRL_OFFSET   0LL
 #define TILEXR_WIN_CTRL_BYTES    (1LL << 20)
 #define TILEXR_WIN_FLAG_OFFSET   (1LL << 20)
 #define TILEXR_WIN_FLAG_BYTES    (4LL << 20)
+#define TILEXR_FLAG_BUFF_BYTES TILEXR_WIN_FLAG_BYTES   /* the reference's name for the flag area */
 #define TILEXR_WIN_LL_OFFSET     (5LL << 20)
 #define TILEXR_WIN_LL_HALF_BYTES (1LL << 20)
 #define TILEXR_WIN_DATA_OFFSET   (7LL << 20)

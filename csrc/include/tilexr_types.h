@@ -76,8 +76,10 @@ enum TileXRReduceOp {
     TILEXR_REDUCE_RESERVED = 255
 };
 
-// Operator ids.  Ids >= 100 are the compute+collective fusions; the reference keeps only
-// their names, this runtime implements ALL_GATHER_MATMUL and MATMUL_REDUCE_SCATTER.
+// Operator ids (values as in the reference's TileXRType, src/include/tilexr_types.h:96-126).  Ids >= 100 are the
+// compute+collective fusions; the reference keeps only their names, this runtime implements PURE_MATMUL,
+// ALL_GATHER_MATMUL and MATMUL_REDUCE_SCATTER (MATMUL_ALL_REDUCE is the latter followed by an all-gather:
+// tilexr_b200.ops.gemm.matmul_all_reduce).  The all-to-all fusions from 105 on are identifiers only here as there.
 enum TileXROpType {
     TILEXR_OP_ALL_REDUCE = 1,
     TILEXR_OP_REDUCE_SCATTER = 2,
@@ -102,7 +104,19 @@ enum TileXROpType {
     TILEXR_OP_MATMUL_ALL_REDUCE = 102,
     TILEXR_OP_MATMUL_REDUCE_SCATTER = 103,
     TILEXR_OP_ALL_GATHER_MATMUL = 104,
+    TILEXR_OP_ALL_GATHER_MATMUL_V2 = 105,
+    TILEXR_OP_ALL2ALL_MATMUL = 106,
+    TILEXR_OP_MATMUL_ALL2ALL = 107,
+    TILEXR_OP_MTE2_TEST = 108,
+    TILEXR_OP_ALL_GATHER_MATMUL_REDUCE_SCATTER = 111,
     TILEXR_OP_BANDWIDTH = 201,
+    TILEXR_OP_ALLTOALLV_ALLGATHER_MATMUL = 305,
+    TILEXR_OP_MATMUL_REDUCESCATTER_ALLTOALLV = 306,
+    TILEXR_OP_ALLTOALLVC_ALLGATHER_MATMUL = 307,
+    TILEXR_OP_MATMUL_REDUCESCATTER_ALLTOALLVC = 308,
+    TILEXR_OP_ALLTOALLVC_ALLGATHER_MATMUL_HIDDEN = 309,
+    TILEXR_OP_MATMUL_REDUCESCATTER_ALLTOALLVC_HIDDEN = 310,
+    TILEXR_TYPE_MAX = 311,
 };
 
 static inline size_t TileXRDataTypeSize(int dtype)
@@ -151,6 +165,15 @@ static inline const char *TileXROpName(int op)
         case TILEXR_OP_MATMUL_ALL_REDUCE: return "TileXRMatmulAllReduce";
         case TILEXR_OP_MATMUL_REDUCE_SCATTER: return "TileXRMatmulReduceScatter";
         case TILEXR_OP_ALL_GATHER_MATMUL: return "TileXRAllGatherMatmul";
+        case TILEXR_OP_ALL_GATHER_MATMUL_V2: return "TileXRAllGatherMatmulV2";
+        case TILEXR_OP_ALL2ALL_MATMUL: return "TileXRAll2AllMatmul";
+        case TILEXR_OP_MATMUL_ALL2ALL: return "TileXRMatmulAll2All";
+        case TILEXR_OP_MTE2_TEST: return "TileXRMTE2Test";
+        case TILEXR_OP_ALL_GATHER_MATMUL_REDUCE_SCATTER: return "TileXRAllGatherMatmulReduceScatter";
+        case TILEXR_OP_ALLTOALLV_ALLGATHER_MATMUL: case TILEXR_OP_ALLTOALLVC_ALLGATHER_MATMUL:
+        case TILEXR_OP_ALLTOALLVC_ALLGATHER_MATMUL_HIDDEN: return "TileXRAllToAllVAllGatherMatmul";
+        case TILEXR_OP_MATMUL_REDUCESCATTER_ALLTOALLV: case TILEXR_OP_MATMUL_REDUCESCATTER_ALLTOALLVC:
+        case TILEXR_OP_MATMUL_REDUCESCATTER_ALLTOALLVC_HIDDEN: return "TileXRMatmulReduceScatterAllToAllV";
         case TILEXR_OP_BANDWIDTH: return "TileXRBandwidthTest";
         default: return "TileXRUnknown";
     }

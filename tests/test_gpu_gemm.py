@@ -98,6 +98,24 @@ def test_matmul_reduce_scatter(txr, ranks, shard_rows, n, k):
     world.destroy()
 
 
+def test_matmul_all_reduce(txr):
+    """GEMM with the reduce-scatter in its epilogue, then an all-gather of the reduced shards: every rank ends with the sum."""
+    ranks, shard_rows, n, k = 2, 128, 256, 256
+    world = txr.init_emulated_world(ranks, device=0, buffer_mb=16)
+    g = torch.Generator().manual_seed(21)
+    m = ranks * shard_rows
+    a = [(torch.randn(m, k, generator=g) * 0.5).to(torch.bfloat16).cuda() for _ in range(ranks)]
+    b = [(torch.randn(n, k, generator=g) * 0.5).to(torch.bfloat16).cuda() for _ in range(ranks)]
+    staging = world.symm_empty((m, n), torch.bfloat16)
+    want = sum((a[r].float() @ b[r].float().t()).to(torch.bfloat16).float() for r in range(ranks))
+    for _ in range(2):
+        outs = world.run(lambda c, r: txr.gemm.matmul_all_reduce(c, a[r], b[r], staging[r]))
+        world.check()
+    for r in range(ranks):
+        _close(outs[r], want, k * ranks)
+    world.destroy()
+
+
 @pytest.mark.parametrize("m,n,k", [(128, 256, 128), (256, 256, 512), (300, 384, 1024), (1024, 2048, 7168), (96, 128, 256)])
 def test_matmul_fp8_block_scaled(txr, m, n, k):
     """Block-scaled fp8 (1 x 128 activation scales, 128 x 128 weight scales, fp32) against the fp32 product of the

@@ -148,6 +148,38 @@ def test_buffer_facade_single_rank(txr, port):
     comm.destroy()
 
 
+def test_context_owned_buffer_forward_and_backward(txr, port):
+    """The reference's construction order: a context from the launcher's environment, a buffer that owns it, forward and
+    backward with state objects (integrations/moonep_torch/tilexr_moonep/torch_api.py:284-304, 388-443, 1612-1683)."""
+    from tilexr_b200.integrations import moonep
+
+    comm = txr.init_process(0, 1, comm_id=f"127.0.0.1:{port}", buffer_mb=64, device=0)
+    S, H, K, E = 32, 128, 2, 8
+    ctx = moonep.TileXRMoonEPContext.from_env(tokens_per_rank=S, hidden_size=H, topk=K, expert_count=E, dtype=torch.bfloat16,
+                                              token_padding=4, runtime=comm)
+    buf = moonep.TileXRMoonEPBuffer.from_context(ctx)
+    assert buf.NvS == ctx.nv_s and buf.B == ctx.prefetch_slots == E
+    with pytest.raises(RuntimeError):
+        moonep.TileXRMoonEPBuffer.from_context(ctx)                   # one owner at a time
+    g = torch.Generator().manual_seed(4)
+    hidden = torch.randn(S, H, generator=g).to(torch.bfloat16).cuda()
+    w = torch.rand(S, K, generator=g).cuda()
+    topk = torch.randint(0, E, (S, K), generator=g, dtype=torch.int32).cuda()
+    fwd = buf.forward_state(hidden, w, topk, None, None, lambda rows, cu, proj: rows.clone())
+    torch.cuda.synchronize()
+    buf.check_pending_status(fwd.state.plan)
+    want = hidden.float() * w.sum(dim=1, keepdim=True)                 # identity experts, rows weighted before the sum
+    assert torch.allclose(fwd.hidden.float(), want, rtol=2e-2, atol=2e-2)
+    bwd = buf.backward_state(hidden, fwd.state, lambda rows, cu: rows.clone())
+    torch.cuda.synchronize()
+    buf.check_pending_status(bwd.plan)
+    assert torch.allclose(bwd.grad_hidden.float(), hidden.float() * K, rtol=1e-2, atol=1e-2)
+    assert buf.reduce_grad_info()["owned_rows"] == E
+    buf.close()
+    ctx.close()
+    comm.destroy()
+
+
 def test_harness_correctness_runner_single_rank(txr, port):
     """The harness compares the library with the torch reference, artifact by artifact."""
     from tilexr_b200.tools.moonep.contracts import MoonEPCase

@@ -64,3 +64,56 @@ def test_capabilities():
 
     abi, native, stub = txr._C.moonep_capabilities()
     assert abi == 2 and native == 0b11111 and stub == 0
+
+
+def test_context_and_capability_objects(monkeypatch):
+    """The context validates its shape like the reference's (integrations/moonep_torch/tilexr_moonep/torch_api.py:306-443),
+    reads the launcher's environment, belongs to one buffer at a time and stays refused once poisoned."""
+    import torch
+    from tilexr_b200.integrations import moonep
+
+    caps = moonep.NativeCapabilities.query()
+    assert caps.abi_version == 2 and caps.transport_correctness_valid and not caps.transport_performance_valid
+    assert all(caps.implementation(s) == "native" for s in moonep.STAGE_BITS)
+    assert moonep.NativeCapabilities(2, 0b00111, 0b00100).implementation("prefetch_weight") == "stub"
+    assert moonep.NativeCapabilities(2, 0b00111, 0).implementation("combine") == "unavailable"
+    with pytest.raises(KeyError):
+        caps.implementation("scatter")
+
+    class FakeComm:
+        rank, world_size = 3, 8
+
+    for key, value in {"RANK": "3", "WORLD_SIZE": "8", "LOCAL_RANK": "0", "LOCAL_WORLD_SIZE": "8", "NODE_RANK": "0", "NODE_COUNT": "1"}.items():
+        monkeypatch.setenv(key, value)
+    monkeypatch.setattr(torch.cuda, "is_available", lambda: False)
+    ctx = moonep.TileXRMoonEPContext.from_env(tokens_per_rank=4096, hidden_size=7168, topk=8, expert_count=256, dtype=torch.bfloat16,
+                                              token_padding=16, runtime=FakeComm())
+    assert (ctx.planner_group_rank, ctx.planner_group_size, ctx.experts_per_rank, ctx.prefetch_slots) == (3, 8, 32, 32)
+    assert ctx.route_count == 32768 and ctx.nv_s == 32768 + 15 * 2 * 32 and ctx.dispatched_capacity == ctx.nv_s
+    a, b = object(), object()
+    ctx.attach_buffer(a)
+    with pytest.raises(RuntimeError):
+        ctx.attach_buffer(b)
+    ctx.bind_stream(a, 7)
+    with pytest.raises(RuntimeError):
+        ctx.bind_stream(a, 9)
+    with pytest.raises(RuntimeError):
+        ctx.close()                       # its buffer first
+    ctx.detach_buffer(a)
+    ctx.mark_poisoned()
+    with pytest.raises(RuntimeError):
+        ctx.attach_buffer(b)
+    ctx.close()
+
+    def make(**kw):
+        base = dict(runtime=FakeComm(), global_rank=3, global_world_size=8, node_rank=0, node_count=1, local_rank=3, local_world_size=8,
+                    planner_group_rank=3, planner_group_size=8, lane_group_rank=0, lane_group_size=1, device_index=3, tokens_per_rank=64,
+                    hidden_size=128, topk=4, expert_count=32, dtype=torch.bfloat16)
+        base.update(kw)
+        return moonep.TileXRMoonEPContext(**base)
+
+    assert make().prefetch_slots == 4
+    for bad in (dict(topk=33), dict(expert_count=30), dict(prefetch_slots=5), dict(token_padding=0), dict(planner_group_rank=8),
+                dict(planner_group_rank=2), dict(tokens_per_rank=1 << 28, topk=8)):
+        with pytest.raises((ValueError, OverflowError)):
+            make(**bad)

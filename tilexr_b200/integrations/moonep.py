@@ -58,6 +58,226 @@ class MoonEPCommPlan:
                               d["B"], d["NvS"], d["K"], None, None, d["dup_counts"], d["status"], d["dst_local"], d["cu_seqlens"])
 
 
+class TileXRMoonEPError(RuntimeError):
+    """A native MoonEP call refused its arguments or a stage failed on the device."""
+
+
+STAGE_BITS = {"planning": 1 << 0, "dispatch": 1 << 1, "prefetch_weight": 1 << 2, "combine": 1 << 3, "reduce_grad": 1 << 4}
+
+
+@dataclasses.dataclass(frozen=True)
+class NativeCapabilities:
+    """What the native library serves itself (reference: integrations/moonep_torch/tilexr_moonep/runtime.py:54-112):
+    ``stage_mask`` has a bit per stage with a kernel of its own, ``stub_mask`` a bit per stage that only has a stand-in."""
+    abi_version: int
+    stage_mask: int
+    stub_mask: int
+
+    @staticmethod
+    def query() -> "NativeCapabilities":
+        abi, native, stub = _C.moonep_capabilities()
+        return NativeCapabilities(int(abi), int(native), int(stub))
+
+    def implementation(self, stage: str) -> str:
+        if stage not in STAGE_BITS:
+            raise KeyError(f"unknown MoonEP stage: {stage}")
+        bit = STAGE_BITS[stage]
+        return "stub" if self.stub_mask & bit else "native" if self.stage_mask & bit else "unavailable"
+
+    @property
+    def transport_correctness_valid(self) -> bool:
+        """Every stage moves its data with a kernel of the library (no stand-in), so a correctness run judges the transport."""
+        every = sum(STAGE_BITS.values())
+        return (self.stage_mask & every) == every and (self.stub_mask & every) == 0
+
+    @property
+    def transport_performance_valid(self) -> bool:
+        """Native coverage alone does not make a number publishable: the harness gates on precision and on its sample filter."""
+        return False
+
+    def as_dict(self) -> dict:
+        return {"abi_version": self.abi_version, "stage_mask": self.stage_mask, "stub_mask": self.stub_mask,
+                "implementations": {stage: self.implementation(stage) for stage in STAGE_BITS},
+                "transport_correctness_valid": self.transport_correctness_valid,
+                "transport_performance_valid": self.transport_performance_valid}
+
+
+@dataclasses.dataclass
+class TileXRMoonEPContext:
+    """Shape and placement of one MoonEP instance, with the fields and checks of the reference's context
+    (integrations/moonep_torch/tilexr_moonep/torch_api.py:306-590).  ``runtime`` is a communicator of this package
+    (``tilexr_b200.init_from_torch_distributed`` or an emulated world's rank); the planner group is the set of ranks that
+    plan together (the communicator's ranks), the lane group the tensor-parallel lanes of one expert group.
+
+    One buffer at a time may own a context (``attach_buffer``); a context whose buffer saw a failed stage is poisoned and
+    refuses further owners, because the windows' contents are then undefined for the other ranks too."""
+    runtime: object
+    global_rank: int
+    global_world_size: int
+    node_rank: int
+    node_count: int
+    local_rank: int
+    local_world_size: int
+    planner_group_rank: int
+    planner_group_size: int
+    lane_group_rank: int
+    lane_group_size: int
+    device_index: int
+    tokens_per_rank: int
+    hidden_size: int
+    topk: int
+    expert_count: int
+    dtype: object
+    token_padding: int = 1
+    prefetch_slots: Optional[int] = None
+
+    def __post_init__(self) -> None:
+        self._owner = None
+        self._stream = None
+        self._poisoned = False
+        self._closed = False
+        if not 1 <= self.planner_group_size <= 128:
+            raise ValueError(f"planner_group_size must be in [1, 128], got {self.planner_group_size}")
+        if not 0 <= self.planner_group_rank < self.planner_group_size:
+            raise ValueError("planner_group_rank is outside the planner group")
+        if self.tokens_per_rank <= 0 or self.hidden_size <= 0 or not 1 <= self.topk <= 32:
+            raise ValueError("tokens_per_rank and hidden_size must be positive; topk must be in [1, 32]")
+        if self.expert_count <= 0 or self.expert_count % self.planner_group_size != 0:
+            raise ValueError("expert_count must be positive and divisible by planner_group_size")
+        if self.token_padding <= 0:
+            raise ValueError("token_padding must be positive")
+        if self.prefetch_slots is None:
+            self.prefetch_slots = self.experts_per_rank
+        if not 1 <= self.prefetch_slots <= self.experts_per_rank:
+            raise ValueError("prefetch_slots must be in [1, E/R]")
+        if self.planner_group_size * self.nv_s > 2 ** 31:
+            raise OverflowError("the int32 destination encoding needs planner_group_size * NvS <= 2^31")
+        rank = getattr(self.runtime, "rank", self.planner_group_rank)
+        world = getattr(self.runtime, "world_size", self.planner_group_size)
+        if int(rank) != self.planner_group_rank or int(world) != self.planner_group_size:
+            raise ValueError("the communicator's rank and size do not match the planner group")
+
+    @property
+    def experts_per_rank(self) -> int:
+        return self.expert_count // self.planner_group_size
+
+    @property
+    def route_count(self) -> int:
+        return self.tokens_per_rank * self.topk
+
+    @property
+    def nv_s(self) -> int:
+        """Rows of a rank's receive buffer: its routes plus the padding behind every local group and slot."""
+        return self.route_count + (self.token_padding - 1) * 2 * self.experts_per_rank
+
+    @property
+    def dispatched_capacity(self) -> int:
+        return self.nv_s
+
+    @classmethod
+    def from_env(cls, *, tokens_per_rank: int, hidden_size: int, topk: int, expert_count: int, dtype, token_padding: int = 1,
+                 prefetch_slots: Optional[int] = None, runtime=None, buffer_mb: Optional[int] = None) -> "TileXRMoonEPContext":
+        """Ranks from the launcher's environment (RANK, WORLD_SIZE, LOCAL_RANK, LOCAL_WORLD_SIZE, NODE_RANK, NODE_COUNT,
+        TILEXR_PLANNER_GROUP_RANK / _SIZE, TILEXR_LANE_GROUP_RANK / _SIZE).  Without ``runtime`` a communicator is created
+        over the initialised ``torch.distributed`` world."""
+        import os
+
+        env = os.environ
+        global_rank, global_world = int(env.get("RANK", "0")), int(env.get("WORLD_SIZE", "1"))
+        local_rank = int(env.get("LOCAL_RANK", str(global_rank)))
+        device = torch.cuda.current_device() if torch.cuda.is_available() else local_rank
+        if local_rank != device:
+            raise ValueError(f"LOCAL_RANK={local_rank} does not match the current CUDA device {device}")
+        group_rank = int(env.get("TILEXR_PLANNER_GROUP_RANK", str(global_rank)))
+        group_size = int(env.get("TILEXR_PLANNER_GROUP_SIZE", str(global_world)))
+        if runtime is None:
+            from ..parallel.comm import init_from_torch_distributed
+
+            per = tokens_per_rank * topk * hidden_size * torch.empty((), dtype=dtype).element_size()
+            runtime = init_from_torch_distributed(buffer_mb=buffer_mb if buffer_mb is not None else max(64, int(3 * per / (1 << 20)) + 16))
+        return cls(runtime=runtime, global_rank=global_rank, global_world_size=global_world, node_rank=int(env.get("NODE_RANK", "0")),
+                   node_count=int(env.get("NODE_COUNT", "1")), local_rank=local_rank,
+                   local_world_size=int(env.get("LOCAL_WORLD_SIZE", str(global_world))), planner_group_rank=group_rank,
+                   planner_group_size=group_size, lane_group_rank=int(env.get("TILEXR_LANE_GROUP_RANK", "0")),
+                   lane_group_size=int(env.get("TILEXR_LANE_GROUP_SIZE", "1")), device_index=int(device),
+                   tokens_per_rank=int(tokens_per_rank), hidden_size=int(hidden_size), topk=int(topk), expert_count=int(expert_count),
+                   dtype=dtype, token_padding=int(token_padding), prefetch_slots=None if prefetch_slots is None else int(prefetch_slots))
+
+    # -- ownership ---------------------------------------------------------------------------------------
+    def attach_buffer(self, owner) -> None:
+        if self._closed or self._poisoned:
+            raise RuntimeError("this MoonEP context is closed or saw a failed stage; create a new one")
+        if self._owner is not None and self._owner is not owner:
+            raise RuntimeError("this MoonEP context already belongs to a buffer")
+        self._owner = owner
+
+    def detach_buffer(self, owner) -> None:
+        if self._owner is owner:
+            self._owner = None
+            self._stream = None
+
+    def bind_stream(self, owner, stream_ptr: int) -> None:
+        """All stages of one buffer run on one stream: the flag epochs of the windows follow that stream's order."""
+        if self._owner is not owner:
+            raise RuntimeError("only the owning buffer binds a stream")
+        if self._stream is not None and self._stream != int(stream_ptr):
+            raise RuntimeError("this MoonEP context is bound to another stream; release it first")
+        self._stream = int(stream_ptr)
+
+    def release_stream(self, owner) -> None:
+        if self._owner is owner:
+            self._stream = None
+
+    def mark_poisoned(self) -> None:
+        self._poisoned = True
+
+    def capabilities(self) -> NativeCapabilities:
+        return NativeCapabilities.query()
+
+    def close(self) -> None:
+        if self._closed:
+            return
+        if self._owner is not None:
+            raise RuntimeError("close the owning MoonEP buffer before its context")
+        self._closed = True
+
+
+@dataclasses.dataclass
+class DispatchResult:
+    hidden: torch.Tensor
+    route_weights: Optional[torch.Tensor]
+    plan: "MoonEPCommPlan"
+
+
+@dataclasses.dataclass
+class CombineResult:
+    hidden: torch.Tensor
+    route_weights: Optional[torch.Tensor]
+
+
+@dataclasses.dataclass
+class ForwardState:
+    """What backward needs from forward: the plan, the weight buffers and the route weights as dispatched."""
+    plan: "MoonEPCommPlan"
+    projections: Optional["ProjectionBuffers"]
+    dispatched_route_weights: Optional[torch.Tensor] = None
+    apply_route_weights: bool = True
+    expert_cache: object = None
+
+
+@dataclasses.dataclass
+class ForwardResult:
+    hidden: torch.Tensor
+    route_weights: Optional[torch.Tensor]
+    state: ForwardState
+
+
+@dataclasses.dataclass
+class BackwardResult:
+    grad_hidden: torch.Tensor
+    plan: "MoonEPCommPlan"
+
+
 @dataclasses.dataclass
 class ProjectionBuffers:
     """gate / up / down as ``[E/R + B, ...]`` tensors in symmetric memory: rows ``[0, E/R)`` are the
@@ -82,10 +302,45 @@ class TileXRMoonEPBuffer:
         self.NvS = S * K + (token_padding - 1) * 2 * (E // self.R)
         self.dtype = dtype
         self._poisoned = False
+        self.context: Optional[TileXRMoonEPContext] = None
         # persistent receive tensors: peers write into them directly
         self.hidden_nvsh = comm.symm_empty([self.NvS, H], dtype)
         self.weights_nvs = comm.symm_empty([self.NvS], torch.float32)
         self._grad_nvsh = None
+
+    @classmethod
+    def from_context(cls, context: TileXRMoonEPContext) -> "TileXRMoonEPBuffer":
+        """The buffer of a :class:`TileXRMoonEPContext` (the reference's constructor form, torch_api.py:591-640): the context
+        gives the shape, the buffer becomes its owner until :meth:`close`."""
+        self = cls(context.runtime, context.tokens_per_rank, context.hidden_size, context.topk, context.expert_count,
+                   token_padding=context.token_padding, B=context.prefetch_slots, dtype=context.dtype)
+        context.attach_buffer(self)
+        if torch.cuda.is_available():
+            context.bind_stream(self, torch.cuda.current_stream().cuda_stream)
+        self.context = context
+        return self
+
+    def forward_state(self, hidden, route_weights, topk_experts, tokens_per_expert, projections: Optional[ProjectionBuffers],
+                      expert_forward: Callable, apply_route_weights: bool = True) -> ForwardResult:
+        """:meth:`forward` with the reference's result objects (torch_api.py:284-304): the state goes to
+        :meth:`backward_state`."""
+        plan = self.planning(topk_experts, tokens_per_expert)
+        rows, w = self.dispatch(hidden, route_weights, plan)
+        if projections is not None:
+            self.prefetch_weight(plan, projections)
+        out = expert_forward(rows, plan.cu_seqlens, projections)
+        if apply_route_weights and w is not None:
+            out = (out.float() * w.unsqueeze(1)).to(out.dtype)
+        y, wy = self.combine(plan, out, None if apply_route_weights else w)
+        return ForwardResult(y, wy, ForwardState(plan, projections, w, apply_route_weights))
+
+    def backward_state(self, grad_output, state: ForwardState, expert_backward: Callable, grads: Optional[ProjectionBuffers] = None) -> BackwardResult:
+        return BackwardResult(self.backward(grad_output, state.plan, expert_backward, grads), state.plan)
+
+    def reduce_grad_info(self) -> dict:
+        """Sizes of the gradient reduction of this shape: per projection, rows a rank owns and rows it may borrow."""
+        L = self.E // self.R
+        return {"owned_rows": L, "slot_rows": self.B, "ranks": self.R, "dtype": "float32"}
 
     # -- stages ------------------------------------------------------------------------------------
     def planning(self, topk_experts_sk: torch.Tensor, tokens_per_expert: Optional[torch.Tensor] = None) -> MoonEPCommPlan:
@@ -199,12 +454,14 @@ class TileXRMoonEPBuffer:
         plan_status = int(plan.status.item()) if plan is not None and plan.status is not None else 0
         if status != 0 or plan_status != 0:
             self._poisoned = True
+            if self.context is not None:
+                self.context.mark_poisoned()
             from ..utils import failure_dump
 
             failure_dump.dump(self.comm, None, {"what": "MoonEP stage", "plan_status": plan_status, "S": self.S, "H": self.H, "K": self.K,
                                                 "E": self.E})
             self.comm.print_dfx()
-            raise RuntimeError(f"MoonEP stage failed: device status {status}, plan status {plan_status}")
+            raise TileXRMoonEPError(f"MoonEP stage failed: device status {status}, plan status {plan_status}")
 
     def synchronize(self) -> None:
         torch.cuda.synchronize()
@@ -218,6 +475,10 @@ class TileXRMoonEPBuffer:
 
     def close(self) -> None:
         self._poisoned = True
+        if self.context is not None:
+            self.context.release_stream(self)
+            self.context.detach_buffer(self)
+            self.context = None
 
 
 class DispatchTrace:
@@ -331,6 +592,11 @@ class Buffer:
 
     def destroy(self):
         self.native.close()
+        self._destroyed = True
+
+    @property
+    def destroyed(self) -> bool:
+        return getattr(self, "_destroyed", False)
 
     def __enter__(self):
         return self

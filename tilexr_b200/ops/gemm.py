@@ -5,6 +5,8 @@ Weights follow the ``torch.nn.Linear`` convention: ``b`` is ``[N, K]`` and the p
 """
 from __future__ import annotations
 
+from typing import Optional
+
 import torch
 
 from .. import _C
@@ -95,6 +97,19 @@ def all_gather_matmul(comm, a_shard: torch.Tensor, b: torch.Tensor, staging: tor
 def matmul_reduce_scatter(comm, a: torch.Tensor, b: torch.Tensor, staging: torch.Tensor) -> torch.Tensor:
     """``reduce_scatter(a @ b.T)`` along rows; ``staging`` is ``comm.symm_empty([M, N], dtype)``."""
     return _C.matmul_reduce_scatter(comm, a.contiguous(), b.contiguous(), staging)
+
+
+def matmul_all_reduce(comm, a: torch.Tensor, b: torch.Tensor, staging: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``all_reduce(a @ b.T)`` (the reference's MATMUL_ALL_REDUCE operator id): the reduce-scatter runs in the GEMM's epilogue
+    (:func:`matmul_reduce_scatter`), the reduced row shards are then all-gathered.  A registered ``out``
+    (``comm.symm_empty([M, N], dtype)``) is written by the peers directly."""
+    from .collectives import all_gather
+    shard = matmul_reduce_scatter(comm, a, b, staging)
+    world = comm.world_size
+    if out is None:
+        out = torch.empty((world * shard.shape[0], shard.shape[1]), dtype=shard.dtype, device=shard.device)
+    all_gather(comm, shard, out=out.view(world, shard.shape[0], shard.shape[1]))
+    return out
 
 
 def all_gather_matmul_fp8_block(comm, a_shard: torch.Tensor, scale_a_shard: torch.Tensor, a_staging: torch.Tensor, scale_staging: torch.Tensor,
