@@ -111,6 +111,65 @@ def all_to_all(comm, t: torch.Tensor, scatter_dim: int = 0, gather_dim: int = 0)
     return out.movedim(0, scatter_dim).contiguous()
 
 
+class TileXRCollectivesError(RuntimeError):
+    """A collective of this library refused its arguments or failed on the device."""
+
+    def __init__(self, operation: str, ret: int, detail: str = ""):
+        super().__init__(f"{operation} failed with {ret}" + (f": {detail}" if detail else ""))
+        self.operation, self.ret, self.detail = operation, ret, detail
+
+
+class TileXRVllmCollectivesAdapter:
+    """The collectives with "None means use your own path" semantics, for callers that keep their stock implementation
+    beside this one (the reference's adapter: integrations/vllm_ascend/tilexr_collectives/vllm_adapter.py:34-117).
+    Every method returns the result, or None when the fast path does not apply (gate off, not a contiguous CUDA tensor,
+    uneven split sizes, different scatter and gather dimensions) or raised; the exception is kept in ``last_error``."""
+
+    def __init__(self, comm):
+        self.comm = comm
+        self.rank, self.world_size = comm.rank, comm.world_size
+        self.last_error: Optional[BaseException] = None
+
+    def should_fallback(self, tensor=None, *, scatter_sizes=None, gather_sizes=None) -> bool:
+        self.last_error = None
+        if not enabled() or tensor is None or not getattr(tensor, "is_cuda", False):
+            return True
+        contiguous = getattr(tensor, "is_contiguous", None)
+        if not callable(contiguous) or not contiguous():
+            return True
+        return scatter_sizes is not None or gather_sizes is not None      # ragged exchanges stay on the stock path
+
+    def _try(self, fn: Callable):
+        try:
+            return fn()
+        except (OSError, RuntimeError, TypeError, ValueError) as exc:
+            self.last_error = exc
+            return None
+
+    def all_reduce(self, input_):
+        return None if self.should_fallback(input_) else self._try(lambda: all_reduce(self.comm, input_))
+
+    def all_gather(self, input_, dim: int = -1):
+        return None if self.should_fallback(input_) else self._try(lambda: all_gather(self.comm, input_, dim))
+
+    def reduce_scatter(self, input_, dim: int = -1):
+        return None if self.should_fallback(input_) else self._try(lambda: reduce_scatter(self.comm, input_, dim))
+
+    def broadcast(self, tensor, src: int = 0):
+        return None if self.should_fallback(tensor) else self._try(lambda: broadcast(self.comm, tensor, src))
+
+    def all_to_all(self, input_, scatter_dim: int = 0, gather_dim: int = -1, scatter_sizes=None, gather_sizes=None):
+        if self.should_fallback(input_, scatter_sizes=scatter_sizes, gather_sizes=gather_sizes):
+            return None
+        try:
+            if scatter_dim % input_.dim() != gather_dim % input_.dim():
+                return None
+        except (AttributeError, TypeError, ZeroDivisionError) as exc:
+            self.last_error = exc
+            return None
+        return self._try(lambda: all_to_all(self.comm, input_, scatter_dim, gather_dim))
+
+
 def _wrap(name: str, fast: Callable, original: Callable, get_comm: Callable):
     def method(self, tensor, *args, **kwargs):
         counters = route_counters[name]
@@ -134,7 +193,7 @@ def _wrap(name: str, fast: Callable, original: Callable, get_comm: Callable):
 
 
 def patch_communicator(communicator_cls=None, get_comm: Optional[Callable] = None) -> bool:
-    """Patches ``all_reduce``, ``all_gather``, ``reduce_scatter`` and ``broadcast`` of vLLM's
+    """Patches ``all_reduce``, ``all_gather``, ``reduce_scatter``, ``broadcast`` and (where the class has one) ``all_to_all`` of vLLM's
     ``CudaCommunicator`` (or of ``communicator_cls``).  Returns False when vLLM is absent."""
     if communicator_cls is None:
         try:
@@ -144,7 +203,13 @@ def patch_communicator(communicator_cls=None, get_comm: Optional[Callable] = Non
     if get_comm is None:
         def get_comm(self, tensor):
             return runtime_for(self.device_group, tensor.device, getattr(self, "unique_name", "vllm"))
-    table = {"all_reduce": all_reduce, "all_gather": all_gather, "reduce_scatter": reduce_scatter, "broadcast": broadcast}
+    def equal_all_to_all(comm, t, scatter_dim: int = 0, gather_dim: int = -1, scatter_sizes=None, gather_sizes=None):
+        if scatter_sizes is not None or gather_sizes is not None:
+            raise ValueError("ragged all_to_all stays on the stock path")
+        return all_to_all(comm, t, scatter_dim, gather_dim)
+
+    table = {"all_reduce": all_reduce, "all_gather": all_gather, "reduce_scatter": reduce_scatter, "broadcast": broadcast,
+             "all_to_all": equal_all_to_all}
     for name, fast in table.items():
         original = getattr(communicator_cls, name, None)
         if original is None or getattr(original, "_tilexr_patched", False):

@@ -31,5 +31,6 @@ for mode in benchmark prefetch reduce-grad; do
   timeout 300 $RUN --master-port 29610 -m tilexr_b200.tools.moonep.launcher --mode $mode --cases perf --iters 20 --warmup 5 \
       --json "$OUT/moonep_$mode.json" --csv "$OUT/moonep_$mode.csv" > "$OUT/moonep_$mode.txt" 2> "$OUT/moonep_$mode.err"
 done
+VLLM_TILEXR_COLLECTIVES=1 timeout 120 $RUN --master-port 29611 -m tilexr_b200.tools.vllm_collectives_smoke --count 65536 > "$OUT/vllm_smoke.json" 2> "$OUT/vllm_smoke.err"
 tail -n 3 "$OUT"/*.err | cut -c1-300
 ls -la "$OUT"
