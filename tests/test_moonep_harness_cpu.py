@@ -241,3 +241,118 @@ def test_algorithm_bytes_follow_the_plan():
     for r in range(4):
         assert all(int(e) // 2 != r and 0 <= int(e) < 8 for e in t[r])          # always a remote owner
     assert (synthetic_borrow_table(1, 2, 2) == -1).all()
+
+
+def test_tensor_dump_round_trip_and_offline_compare(tmp_path):
+    """Stage tensors dumped by the correctness runner (single rank, the reference backend on both sides), then compared
+    offline: equal by digest, a changed element found with its index, a tolerance that accepts it, a missing rank."""
+    from tilexr_b200.tools.moonep import tensor_dump
+    from tilexr_b200.tools.moonep.contracts import MoonEPCase
+    from tilexr_b200.tools.moonep.correctness import CorrectnessRunner
+    from tilexr_b200.tools.moonep.torch_reference_backend import TorchReferenceBackend
+
+    case = MoonEPCase(name="dump-case", ranks=1, tokens=16, hidden=32, top_k=2, experts=4, prefetch_slots=2, token_padding=4, ffn=8)
+    case.validate()
+    r = CorrectnessRunner(TorchReferenceBackend(), TorchReferenceBackend(), dump_dir=str(tmp_path / "run")).run_case(case)
+    assert r["ok"]
+    ref_dir, cand_dir = tmp_path / "run" / "reference", tmp_path / "run" / "candidate"
+    names = {n for m in tensor_dump.manifests(str(ref_dir)) for n in m["tensors"]}
+    assert {"plan.dst", "dispatched_hidden", "combined_hidden", "prefetched_gate", "reduced_grad", "input.hidden_sh"} <= names
+    rows = tensor_dump.compare_dumps(str(cand_dir), str(ref_dir))
+    shared = [x for x in rows if not x["tensor"].startswith("input.")]
+    assert all(x["verdict"] == "equal" for x in shared)
+    assert all(x["verdict"] == "missing" and x["only_in"] == "b" for x in rows if x["tensor"].startswith("input."))
+    # one element of one tensor changed in a copy of the candidate dump
+    other = tmp_path / "other"
+    tensors = tensor_dump.load_rank(str(cand_dir), case.name, 0)
+    from tilexr_b200.tools.moonep.contracts import StageArtifacts
+
+    changed = tensors["combined_hidden"].clone()
+    changed[3, 5] += 0.5
+    art = StageArtifacts(plan={k[5:]: v for k, v in tensors.items() if k.startswith("plan.")}, dispatched_hidden=tensors["dispatched_hidden"],
+                         dispatched_weights=tensors["dispatched_weights"], prefetched_gate=tensors["prefetched_gate"], combined_hidden=changed,
+                         combined_weights=tensors["combined_weights"], reduced_grad=tensors["reduced_grad"])
+    tensor_dump.dump_rank(str(other), case, 0, art)
+    rows = tensor_dump.compare_dumps(str(cand_dir), str(other))
+    diff = [x for x in rows if x["verdict"] != "equal"]
+    assert len(diff) == 1 and diff[0]["tensor"] == "combined_hidden" and diff[0]["verdict"] == "differs"
+    assert diff[0]["first_index"] == 3 * 32 + 5 and diff[0]["mismatched"] == 1 and abs(diff[0]["max_abs"] - 0.5) < 0.01
+    assert not tensor_dump.summarize(rows)["ok"]
+    assert tensor_dump.summarize(tensor_dump.compare_dumps(str(cand_dir), str(other), atol=1.0))["ok"]
+    assert tensor_dump.main(["compare", str(cand_dir), str(other)]) == 1 and tensor_dump.main(["compare", str(cand_dir), str(cand_dir)]) == 0
+    (other / case.name / "rank0.manifest.json").unlink()
+    assert [x["verdict"] for x in tensor_dump.compare_dumps(str(cand_dir), str(other))] == ["missing"]
+
+
+def test_model_flow_operator_order_routes_and_document():
+    """The training step's operator sequence (reference: tools/moonep/model_flow.py:55-165): 2L forward and L backward calls
+    with recomputation; routes rebuilt from a histogram; the per-operator document and its comparison table."""
+    import types
+
+    from tilexr_b200.tools.moonep import model_flow as mf
+    from tilexr_b200.tools.moonep.contracts import MoonEPCase
+
+    order = mf.operator_order(5)
+    assert len(order) == 55 and [o["sequence"] for o in order] == list(range(55))
+    count = lambda stage: sum(o["stage"] == stage for o in order)
+    assert all(count(s) == 10 for s in mf.FORWARD_STAGES) and all(count(s) == 5 for s in mf.BACKWARD_STAGES)
+    assert [o["layer"] for o in order if o["stage"] == "reduce_grad"] == [4, 3, 2, 1, 0]
+    assert order[20]["phase"] == "recompute_backward" and order[20]["stage"] == "planning" and order[20]["stage_occurrence"] == 5
+    assert len(mf.operator_order(3, recompute=False)) == 3 * 4 + 3 * 3
+
+    counts = [9, 0, 7, 16, 3, 5, 8, 16]                      # 16 tokens x top-4
+    routes = mf.routes_from_expert_counts(counts, 16, 4)
+    assert torch.bincount(routes.reshape(-1).long(), minlength=8).tolist() == counts
+    assert all(len(set(row.tolist())) == 4 for row in routes)
+    for bad in ([17, 15, 16, 16], [64, 0, 0, 0], [16, 16, 16, 15]):
+        with pytest.raises(ValueError):
+            mf.routes_from_expert_counts(bad, 16, 4)
+    with pytest.raises(ValueError):
+        mf.routes_from_expert_counts([16, 16, 16, 0, 0, 16], 16, 4 + 1)
+
+    case = MoonEPCase(name="flow", ranks=2, tokens=16, hidden=32, top_k=4, experts=8, prefetch_slots=2, ffn=8)
+    log = []
+
+    class FakeBuffer:
+        weights_nvs = torch.zeros(4)
+
+        def planning(self, topk):
+            log.append("planning")
+            return types.SimpleNamespace(remote_stats=torch.tensor([2, 1]))
+
+        def dispatch(self, hidden, weights, plan):
+            log.append("dispatch_forward" if weights is not None else "dispatch_backward")
+            return hidden, weights
+
+        def prefetch_weight(self, plan, proj):
+            log.append("prefetch_weight")
+
+        def combine(self, plan, rows, weights=None):
+            log.append("combine_backward" if weights is not None else "combine_forward")
+            return rows, None
+
+        def reduce_grad(self, plan, grads):
+            log.append("reduce_grad")
+
+    hidden = torch.zeros(16, 32)
+    flow = mf.ModelFlow(FakeBuffer(), case, [torch.zeros(16, 4, dtype=torch.int32)] * 2, hidden, torch.ones(16, 4), projections=object(), grads=object())
+    runs = [flow.run_iteration() for _ in range(3)]
+    assert log[:22] == [o["stage"] for o in mf.operator_order(2)] and len(log) == 3 * 22
+    doc0 = mf.performance_document(case, 0, runs, projection_row_bytes=3 * 8 * 32 * 2)
+    doc1 = mf.performance_document(case, 1, runs, projection_row_bytes=3 * 8 * 32 * 2)
+    doc = mf.merge_rank_documents([doc0, doc1])
+    ops = doc["ranks"]["1"]["operators"]
+    assert len(ops) == 22 and ops[0]["algorithm_bytes"] is None                      # planning moves no payload
+    assert ops[1]["algorithm_bytes"] == 64 * 32 * 2 + 64 * 4                          # rows and route weights
+    assert [o for o in ops if o["stage"] == "prefetch_weight"][0]["algorithm_bytes"] == 2 * 3 * 8 * 32 * 2
+    assert [o for o in ops if o["stage"] == "reduce_grad"][0]["algorithm_bytes"] == 1 * 3 * 8 * 32 * 2
+    med = mf.stage_medians(doc)
+    assert set(med) == set(mf.FORWARD_STAGES + mf.BACKWARD_STAGES) and med["planning"]["operators"] == 4
+    rows = mf.compare_with_published(doc)
+    assert {r["stage"] for r in rows} == set(med) and all(r["published_us"] and r["speedup"] > 0 for r in rows)
+    assert "| reduce_grad | 2 |" in mf.markdown(doc)
+    # stages without buffers are skipped, not timed
+    flow2 = mf.ModelFlow(FakeBuffer(), case, [torch.zeros(16, 4, dtype=torch.int32)], hidden, torch.ones(16, 4))
+    rec = flow2.run_iteration()
+    assert [r["stage"] for r in rec if r["skipped"]] == ["prefetch_weight", "prefetch_weight", "reduce_grad"]
+    assert "prefetch_weight" not in mf.stage_medians(mf.performance_document(case, 0, [rec]))

@@ -73,8 +73,11 @@ def compare(stage: str, want, got) -> StageVerdict:
 
 
 class CorrectnessRunner:
-    def __init__(self, reference: MoonEPBackend, candidate: MoonEPBackend, group=None, device: str = "cpu"):
+    def __init__(self, reference: MoonEPBackend, candidate: MoonEPBackend, group=None, device: str = "cpu", dump_dir: str = ""):
+        """``dump_dir``: both sides' artifacts of every case go to ``<dump_dir>/reference`` and ``<dump_dir>/candidate``
+        (tensor_dump.py), for an offline look at a failure or a comparison with another build's run."""
         self.reference, self.candidate, self.group, self.device = reference, candidate, group, device
+        self.dump_dir = dump_dir
 
     def run_case(self, case: MoonEPCase) -> Dict[str, object]:
         rank = dist.get_rank(self.group) if dist.is_initialized() else 0
@@ -84,6 +87,11 @@ class CorrectnessRunner:
         touched = unchanged(inputs, snap)
         got: StageArtifacts = self.candidate.run(case, inputs)
         touched += [f"{k} (candidate)" for k in unchanged(inputs, snap)]
+        if self.dump_dir:
+            from . import tensor_dump
+
+            tensor_dump.dump_rank(f"{self.dump_dir}/reference", case, rank, want, inputs, getattr(self.reference, "name", "reference"))
+            tensor_dump.dump_rank(f"{self.dump_dir}/candidate", case, rank, got, None, getattr(self.candidate, "name", "candidate"))
         verdicts: List[StageVerdict] = [compare(s, getattr(want, s), getattr(got, s)) for s in StageArtifacts.STAGES]
         if touched:
             verdicts.append(StageVerdict("inputs_immutable", False, "modified: " + ", ".join(touched)))

@@ -3,11 +3,12 @@
 Run under torchrun, one process per GPU:
 
     python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 -m tilexr_b200.tools.moonep.launcher \\
-        --mode correctness --cases smoke
+        --mode correctness --cases smoke [--dump DIR]
     ... --mode benchmark --cases perf --json out.json --csv out.csv --samples DIR
     ... --mode prefetch --cases perf          (PrefetchWeight on its own, synthetic borrow table)
     ... --mode reduce-grad --cases perf       (ReduceGrad on its own)
     ... --mode replay --capture DIR
+    ... --mode model-flow --cases perf --layers 5 --iters 5 --json performance.json   (the operator sequence of a training step)
     python -m tilexr_b200.tools.moonep.launcher --mode aggregate --samples DIR   (no GPU: folds rank*.jsonl of several nodes)
 
 Cases whose rank count differs from the world size are skipped.
@@ -25,9 +26,11 @@ import torch.distributed as dist
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--mode", choices=["correctness", "benchmark", "prefetch", "reduce-grad", "replay", "aggregate"], default="correctness")
+    ap.add_argument("--mode", choices=["correctness", "benchmark", "prefetch", "reduce-grad", "replay", "model-flow", "aggregate"], default="correctness")
     ap.add_argument("--cases", default="smoke", help="name of a case file under cases/ or a path")
     ap.add_argument("--capture", default="", help="replay: directory written by RouteRecorder")
+    ap.add_argument("--layers", type=int, default=5, help="model-flow: MoE layers of the step")
+    ap.add_argument("--no-recompute", action="store_true", help="model-flow: backward without recomputing the forward operators")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--json", default="")
@@ -37,6 +40,7 @@ def main(argv=None) -> int:
                     help="benchmark: synchronise the device and the ranks in front of every stage, so that a stage's time excludes the skew of the one before")
     ap.add_argument("--nccl-baseline", action="store_true",
                     help="benchmark: also time dispatch and combine as a torch + NCCL program (index_select, all_to_all_single with the plan's splits, index_add_)")
+    ap.add_argument("--dump", default="", help="correctness: directory for both sides' stage tensors (compare offline with tools.moonep.tensor_dump)")
     ap.add_argument("--trace", action="store_true", help="benchmark: also record the dispatch kernel's event trace once per case and print its phases")
     ap.add_argument("--buffer-mb", type=int, default=0, help="communicator window size (default: sized for the largest case)")
     args = ap.parse_args(argv)
@@ -92,8 +96,20 @@ def main(argv=None) -> int:
         cases = [c for c in load_cases(args.cases) if c.ranks == world]
         if not cases and rank == 0:
             print(f"no case of {args.cases} is written for {world} ranks", file=sys.stderr)
-        if args.mode == "correctness":
-            runner = CorrectnessRunner(TorchReferenceBackend(), TileXRBackend(comm), device="cpu")
+        if args.mode == "model-flow":
+            from . import model_flow
+
+            for c in cases:
+                doc = model_flow.run_case(comm, c, layers=args.layers, iters=max(1, args.iters), warmup=max(1, args.warmup), recompute=not args.no_recompute)
+                if world > 1:
+                    docs = [None] * world
+                    dist.all_gather_object(docs, doc)
+                    doc = model_flow.merge_rank_documents(docs)
+                results.append(doc)
+                if rank == 0:
+                    print(model_flow.markdown(doc))
+        elif args.mode == "correctness":
+            runner = CorrectnessRunner(TorchReferenceBackend(), TileXRBackend(comm), device="cpu", dump_dir=args.dump)
             for c in cases:
                 r = runner.run_case(c)
                 results.append(r)

@@ -48,7 +48,7 @@ class TorchReferenceBackend:
         plans = [reference_plan(case, topk, r) for r in range(R)]
         plan = plans[rank]
         dsts = [p["dst"] for p in plans]
-        plan["dst_local"] = dst_local_from_plans(case, dsts, rank)
+        plan["dst_local"] = dst_local_from_plans(case, dsts, rank).to(torch.int32)      # the dtype of the planner kernel's table
 
         # dispatch, for every rank (combine needs what the others hold)
         rows = [torch.zeros(nvs, case.hidden, dtype=case.torch_dtype()) for _ in range(R)]
