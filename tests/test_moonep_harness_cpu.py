@@ -356,3 +356,55 @@ def test_model_flow_operator_order_routes_and_document():
     rec = flow2.run_iteration()
     assert [r["stage"] for r in rec if r["skipped"]] == ["prefetch_weight", "prefetch_weight", "reduce_grad"]
     assert "prefetch_weight" not in mf.stage_medians(mf.performance_document(case, 0, [rec]))
+
+
+def test_case_selection_overrides_flowchart_and_hot_loop_helpers(tmp_path):
+    from tilexr_b200.tools.moonep import dispatch_hot_loop as hl, flowcharts, tensor_dump
+    from tilexr_b200.tools.moonep.case_factory import apply_overrides, load_cases, make_inputs, routing, select_cases
+    from tilexr_b200.tools.moonep.contracts import MoonEPCase
+    from tilexr_b200.tools.moonep.correctness import CorrectnessRunner
+    from tilexr_b200.tools.moonep.planner_reference import reference_plan
+    from tilexr_b200.tools.moonep.torch_reference_backend import TorchReferenceBackend
+
+    cases = load_cases("correctness")
+    assert [c.name for c in select_cases(cases, "2,uniform_r2_k1")] == [cases[1].name, "uniform_r2_k1"]
+    assert select_cases(cases, "") == cases
+    for bad in ("0", "999", "no_such_case"):
+        with pytest.raises(ValueError):
+            select_cases(cases, bad)
+    c = apply_overrides(cases[0], {"tokens": 48, "hidden": None, "seed": 9})
+    assert (c.tokens, c.seed, c.hidden) == (48, 9, cases[0].hidden) and "tokens=48" in c.name and apply_overrides(cases[0], {}) is cases[0]
+    with pytest.raises(ValueError):
+        apply_overrides(cases[0], {"ranks": 4})
+    with pytest.raises(ValueError):
+        apply_overrides(cases[0], {"prefetch_slots": 10 ** 6})                 # validated again
+
+    # a chart from a dump
+    case = MoonEPCase(name="chart", ranks=1, tokens=8, hidden=16, top_k=2, experts=4, prefetch_slots=2, ffn=4)
+    CorrectnessRunner(TorchReferenceBackend(), TorchReferenceBackend(), dump_dir=str(tmp_path / "d")).run_case(case)
+    text = flowcharts.chart_from_dump(str(tmp_path / "d" / "reference"), "chart", 0)
+    assert text.startswith("flowchart TD") and all(f"  {s}[" in text for s in ("planning", "dispatch", "prefetch_weight", "combine", "reduce_grad"))
+    assert "dispatched_hidden [16, 16] bfloat16" in text and "planning_out --> dispatch_in" in text
+    no_ffn = {k: v for k, v in tensor_dump.load_rank(str(tmp_path / "d" / "reference"), "chart", 0).items() if k not in ("prefetched_gate", "reduced_grad")}
+    assert "prefetch_weight[" not in flowcharts.mermaid(no_ffn) and "combine[" in flowcharts.mermaid(no_ffn)
+    assert flowcharts.main([str(tmp_path / "d" / "reference"), "--case", "chart", "--out", str(tmp_path / "c.mmd")]) == 0 and (tmp_path / "c.mmd").exists()
+
+    # what a rank must hold after a dispatch, and where a wrong row is reported
+    case = [x for x in cases if x.ranks == 2][1]
+    topk = [routing(case, r) for r in range(2)]
+    plans = [reference_plan(case, topk, r) for r in range(2)]
+    inputs = [make_inputs(case, r) for r in range(2)]
+    want = TorchReferenceBackend()
+    for r in range(2):
+        rows, wrow, source = hl.expected_rows(case, [p["dst"] for p in plans], [i.hidden_sh for i in inputs], [i.route_weights_sk for i in inputs], r)
+        filled = int((source >= 0).sum())
+        assert filled == sum(int(((p["dst"] >= 0) & (p["dst"] // case.nvs == r)).sum()) for p in plans)
+        assert bool((rows[source < 0] == 0).all()) and bool((wrow[source < 0] == 0).all())
+        assert hl.first_mismatch(rows, rows.clone(), source) is None
+        wrong = rows.clone()
+        victim = int(torch.nonzero(source >= 0)[3])
+        wrong[victim] = 0
+        m = hl.first_mismatch(wrong, rows, source)
+        assert m["first_row"] == victim and m["rows_differ"] == 1 and m["got_row_is_zero"] and m["expected_source_rank"] == int(source[victim])
+    p = hl.percentiles([float(i) for i in range(1, 101)])
+    assert p["count"] == 100 and p["max"] == 100.0 and 50.0 <= p["p50"] <= 51.0 and p["p99"] >= 99.0 and hl.percentiles([])["count"] == 0

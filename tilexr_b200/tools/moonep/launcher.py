@@ -28,6 +28,9 @@ def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--mode", choices=["correctness", "benchmark", "prefetch", "reduce-grad", "replay", "model-flow", "aggregate"], default="correctness")
     ap.add_argument("--cases", default="smoke", help="name of a case file under cases/ or a path")
+    from .case_factory import add_case_arguments, apply_overrides, overrides_from_args, select_cases
+
+    add_case_arguments(ap)
     ap.add_argument("--capture", default="", help="replay: directory written by RouteRecorder")
     ap.add_argument("--layers", type=int, default=5, help="model-flow: MoE layers of the step")
     ap.add_argument("--no-recompute", action="store_true", help="model-flow: backward without recomputing the forward operators")
@@ -77,8 +80,9 @@ def main(argv=None) -> int:
         # two halves, each holding the K rows per token that a combine receives, of the largest case that will run
         buffer_mb = 256
         if args.mode != "replay":
-            for c in load_cases(args.cases):
+            for c in select_cases(load_cases(args.cases), args.case_ids):
                 if c.ranks == world:
+                    c = apply_overrides(c, overrides_from_args(args))
                     need = c.nvs * c.hidden * 2 + c.nvs * 4
                     buffer_mb = max(buffer_mb, int(2 * need / (1 << 20)) + 64)
     if world > 1:
@@ -93,7 +97,7 @@ def main(argv=None) -> int:
         if rank == 0:
             print(json.dumps(results["total_us"]))
     else:
-        cases = [c for c in load_cases(args.cases) if c.ranks == world]
+        cases = [apply_overrides(c, overrides_from_args(args)) for c in select_cases(load_cases(args.cases), args.case_ids) if c.ranks == world]
         if not cases and rank == 0:
             print(f"no case of {args.cases} is written for {world} ranks", file=sys.stderr)
         if args.mode == "model-flow":
