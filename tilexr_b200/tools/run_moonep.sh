@@ -1,10 +1,16 @@
 #!/bin/bash
 # MoonEP harness from end to end on N GPUs of one node (reference: scripts/run_moonep.sh and tools/moonep/launcher.py):
 # correctness against the torch + NCCL reference backend, the stage benchmark with per-rank samples, the standalone
-# PrefetchWeight and ReduceGrad benchmarks, and the cross-rank aggregation of the samples into P50 / P99 tables.
+# PrefetchWeight and ReduceGrad benchmarks, the operator sequence of a training step (model flow), the dispatch hot loop, and
+# the cross-rank aggregation of the samples into P50 / P99 tables.  `launcher --mode correctness --dump DIR` also leaves both
+# sides' stage tensors for tools.moonep.tensor_dump (offline comparison) and tools.moonep.flowcharts (a chart of the stages).
 #   usage: run_moonep.sh N OUT [correctness-cases] [perf-cases]      (case files under tilexr_b200/tools/moonep/cases/)
 # Several nodes: run it on each node with the same OUT on a shared file system (or copy OUT/samples together) and
-# finish with   python -m tilexr_b200.tools.moonep.launcher --mode aggregate --samples OUT/samples --json OUT/aggregate.json
+# finish with   timeout 600 $RUN --master-port 29625 -m tilexr_b200.tools.moonep.launcher --mode model-flow --cases "$PERF" --layers 5 --iters 5 --warmup 1 \
+    --json "$OUT/model_flow.json" > "$OUT/model_flow.md" 2> "$OUT/model_flow.err" || rc=1
+timeout 600 $RUN --master-port 29626 -m tilexr_b200.tools.moonep.dispatch_hot_loop --cases "$PERF" --iters 100 --check-every 10 \
+    --json "$OUT/dispatch_hot_loop.json" > "$OUT/dispatch_hot_loop.txt" 2> "$OUT/dispatch_hot_loop.err" || rc=1
+python -m tilexr_b200.tools.moonep.launcher --mode aggregate --samples OUT/samples --json OUT/aggregate.json
 set -u
 if [ $# -lt 2 ]; then echo "usage: $0 N OUT [correctness-cases] [perf-cases]" >&2; exit 2; fi
 N=$1
