@@ -81,3 +81,31 @@ def test_cli_writes_reports(tmp_path):
     assert r.returncode == 1 and "FATAL DEADLOCK" in r.stdout
     r = subprocess.run([str(exe), "--trace", str(tmp_path / "events.jsonl")], capture_output=True, text=True)
     assert r.returncode == 0
+
+
+def test_installed_traces_are_recorded_judged_and_covered(tmp_path):
+    """An installed trace: host kernels run between two real processes under the recorder, the checker judges the events and
+    the manifest's event coverage is met; a recording that lost one kind of event fails the coverage check (reference:
+    tools/checker/installed_traces/*_trace_manifest.json, `--verify-installed-traces`)."""
+    import json
+
+    from tilexr_b200.tools import checker
+
+    names = {m["name"] for m in checker.load_manifests()}
+    assert {"host_all_gather", "host_all_reduce", "host_ep_dispatch_combine"} <= names
+    for m in checker.load_manifests():
+        assert m["recipe"] in checker.RECIPES and m["ranks"] >= 2 and m["required_event_coverage"]
+    rows = checker.verify_installed_traces("host_all_reduce", keep_dir=str(tmp_path))
+    assert len(rows) == 1 and rows[0]["ok"] and rows[0]["events"] > 10 and rows[0]["findings"] == []
+    manifest = checker.load_manifests("host_all_reduce")[0]
+    paths = [str(tmp_path / "host_all_reduce" / f"rank{r}.jsonl") for r in range(2)]
+    assert checker.missing_coverage(manifest, paths) == []
+    # rank 1's recorder "lost" its waits
+    lines = [l for l in open(paths[1]) if json.loads(l)["kind"] != "FlagWait"]
+    open(paths[1], "w").writelines(lines)
+    gaps = checker.missing_coverage(manifest, paths)
+    assert gaps and all(g["rank"] == 1 and g["kind"] == "FlagWait" and g["have"] == 0 for g in gaps)
+    with pytest.raises(ValueError):
+        checker.load_manifests("no_such_trace")
+    with pytest.raises(ValueError):
+        checker.record_installed_trace("no_such_recipe", 2, str(tmp_path / "x"))
