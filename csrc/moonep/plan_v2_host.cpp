@@ -484,6 +484,7 @@ int TileXRMoonEpPlannerV2(const int32_t *topkExpertIds, const int32_t *tokensPer
     TileXRCommArgs *hostArgs = nullptr;
     int ret = TileXRGetCommArgsHost(comm, &hostArgs);
     if (ret != TILEXR_SUCCESS) return ret;
+    if (hostArgs->extraFlag & TILEXR_FLAG_HOST_MEMORY) return TILEXR_ERROR_NOT_SUPPORT;      // the planner is a CUDA kernel
     const int rankSize = hostArgs->rankSize, local = hostArgs->localRankSize;
     CompatLayout layout;
     ret = CompatLayoutOf(rankSize, s, k, expertCount, &layout);
