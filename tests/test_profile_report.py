@@ -38,3 +38,42 @@ def test_aggregator_outputs(tmp_path):
     slices = [e for e in pf["traceEvents"] if e["ph"] == "X"]
     assert len(slices) == 18 and min(e["ts"] for e in slices) == 0
     assert "<table>" in (out / "report.html").read_text()
+
+
+def test_groups_diagnostics_and_prompt(tmp_path):
+    """Launches grouped across ranks (span, skew, slowest rank), input problems named (a rank that did not record a launch, a
+    launch missing from the sampling pattern, an inconsistent record, a trace without keys), the assistant prompt."""
+    for rank in range(2):
+        for launch in (0, 2, 4):
+            if rank == 1 and launch == 4:
+                continue                                  # rank 1 did not record launch 4
+            d = tmp_path / f"rank{rank}" / f"launch{launch}"
+            d.mkdir(parents=True)
+            (d / "trace.json").write_text(json.dumps(_trace(rank, launch, 100_000 * launch + 5_000 * rank, 50_000 + 10_000 * rank, 30_000)))
+    bad = _trace(0, 6, 600_000, 50_000, 30_000)
+    bad["records"][1]["lastEnd"] = bad["records"][1]["firstStart"] - 10          # ends before it starts
+    (tmp_path / "rank0" / "launch6").mkdir()
+    (tmp_path / "rank0" / "launch6" / "trace.json").write_text(json.dumps(bad))
+    (tmp_path / "rank0" / "launch7").mkdir()
+    (tmp_path / "rank0" / "launch7" / "trace.json").write_text(json.dumps({"op": "TileXRAllGather"}))
+    assert profile_report.main([str(tmp_path), "--measured-iters", "10", "--sample-every", "2", "--ai-prompt"]) == 0
+    out = tmp_path / "report"
+    groups = json.loads((out / "launch_groups.json").read_text())
+    g0 = [g for g in groups if g["launchId"] == 0][0]
+    assert g0["ranks"] == [0, 1] and g0["missing_ranks"] == [] and g0["slowest_rank"] == 1
+    assert abs(g0["start_skew_us"] - 5.0) < 1e-6 and abs(g0["group_span_us"] - 65.0) < 1e-6 and abs(g0["end_skew_us"] - 15.0) < 1e-6
+    kinds = {}
+    for d in json.loads((out / "diagnostics.json").read_text()):
+        kinds.setdefault(d["kind"], []).append(d)
+    assert any("[1]" in d["detail"] and d["launchId"] == 4 for d in kinds["missing_rank"])
+    assert any("ends before it starts" in d["detail"] for d in kinds["inconsistent"])
+    assert any("missing keys" in d["detail"] for d in kinds["inconsistent"])
+    assert any("[8]" in d["detail"] for d in kinds["missing_launch"])              # 0, 2, 4, 6 recorded; 8 is not
+    text = (out / "analysis.md").read_text()
+    assert "## Launches across ranks" in text and "## Problems with the input" in text
+    prompt = (out / "ai_prompt.md").read_text()
+    assert prompt.startswith("# Question") and "missing_rank" in prompt and "| TileXRAllGather |" in prompt
+    index = json.loads((out / "trace_index.json").read_text())
+    stage = [e for e in index if "error" not in e][0]["stages"]["local_input_to_ipc"]
+    assert stage["GBps_per_block_time"] > 0
+    assert profile_report.sanitize(_trace(0, 0, 0, 50_000, 30_000)) == [] and profile_report.expected_launch_ids(7, 3) == [0, 3, 6]
