@@ -49,6 +49,22 @@ __device__ __forceinline__ bool WaitAllBlockFlags(Waiter &w, CommArgs *comm, int
     return BlockBroadcastOk(got) && ok;
 }
 
+// A kernel that writes into (or reads from) a peer's own tensors, not its window, meets the peers first: every rank
+// announces that it has entered this launch (all earlier work of its stream is finished by then) and touches a peer's
+// tensors only after that peer's announcement.  The window guard (the peer has finished the launch before last) says
+// nothing about tensors that the peer's other kernels read or write: its expert GEMM on the rows of the previous
+// dispatch, its optimizer step on the weights that a prefetch pulls, its backward GEMM into the gradient slots.
+__device__ __forceinline__ bool MeetPeersOnEntry(Waiter &w, CommArgs *comm, int rank, int R, uint32_t epoch, bool ok)
+{
+    constexpr uint32_t READY = MOONEP_DONE_FLAG_SLOT - 1;      // far above the per-block flags of the same plane, beside the "done" flag
+    if (R <= 1) return ok;
+    const int t = static_cast<int>(threadIdx.x);
+    if (ok && blockIdx.x == 0 && t < R && t != rank) SetFlag(BlockFlag(comm, t, rank, READY), epoch, 1);
+    bool got = true;
+    if (ok && t < R && t != rank) got = WaitFlagGE(w, BlockFlag(comm, rank, t, READY), 1, t, READY);
+    return BlockBroadcastOk(got) && ok;
+}
+
 // A stage refuses to run on a plan whose planner reported a problem.
 __device__ __forceinline__ bool PlanUsable(Waiter &w, const int32_t *status, bool ok)
 {
@@ -219,6 +235,8 @@ __device__ void MoonDispatchBody(const MoonDispatchArgs &a)
     }
     for (int r = threadIdx.x; r < R; r += blockDim.x) sPeerRows[r] = 0;
     __syncthreads();
+    // rows that go straight into the peers' receive tensors wait for the peers to have entered this launch
+    if (a.zeroCopy) ok = MeetPeersOnEntry(w, comm, rank, R, epoch, ok);
 
     if (ok) {
         // padding rows are cleared by their owner; they never overlap a delivered row
@@ -404,6 +422,8 @@ __device__ void MoonPrefetchBody(const MoonPrefetchArgs &a)
     CommArgs *comm = a.comm;
     const int rank = comm->rank;
     constexpr uint64_t CHUNK = 256 * 1024;
+    // the owners' weight rows are pulled from their own tensors: not before the owner has entered this launch
+    ok = MeetPeersOnEntry(w, comm, rank, comm->rankSize, w.epoch, ok);
     if (ok) {
         // work items: (tensor, slot, chunk), walked by all blocks
         uint64_t item = 0;
@@ -443,6 +463,8 @@ __device__ void MoonReduceGradBody(const MoonReduceGradArgs &a)
     const int rank = comm->rank;
     const int R = comm->rankSize;
     const uint32_t epoch = w.epoch;
+    // the borrowers' gradient slots are pulled from their own tensors: not before the borrower has entered this launch
+    ok = MeetPeersOnEntry(w, comm, rank, R, epoch, ok);
     // Who borrowed which of this rank's experts: per local expert the (source rank, slot) pairs in ascending order, built once
     // per block in shared memory (the table has R * B entries; scanning it per vector, as a first version did, kept the
     // kernel at a fifth of the link).

@@ -11,6 +11,12 @@ Three things are looked at, for hidden rows alone (`hidden`), or rows with their
   missed zero-fill show up as a mismatch with the index of the first bad row and the rank it should have come from.
 * **latency**: the launches' device times, P50 / P99 / longest, with the bytes the plan moves.
 
+The receive tensors are symmetric memory that the peers write directly.  The dispatch kernel lets a peer write them only
+after this rank has entered the same launch, so what a launch delivered stays valid until this rank's own next dispatch:
+the checks read the tensors on the host while faster ranks may already have launched again.  (A first version of the
+kernel had no such meeting, and on two GPUs this tool caught a rank's route weights overwritten by its peer's next launch
+while the host was still comparing the rows.)
+
     python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 -m tilexr_b200.tools.moonep.dispatch_hot_loop \\
         --cases perf --case-ids flow_r8_s4096_k8_h7168 --iters 200 --check-every 10
 """
@@ -109,6 +115,8 @@ def run_case(comm, case: MoonEPCase, mode: str = "pair", iters: int = 100, warmu
         return buf.dispatch(s["hidden"], s["weights"], s["plan"])
 
     def check(s, rows, wn, what: str, i: int):
+        # No meeting of the ranks here: a peer that is already in its next launch must not touch these tensors before this
+        # rank launches again (the kernel's entry meeting), and the comparison of the rows takes long enough to show it.
         torch.cuda.synchronize()
         bad = first_mismatch(rows.cpu(), s["want"], s["source"])
         if bad is None and s["want_w"] is not None:
