@@ -110,6 +110,19 @@ Step CopyToPeer(int peer, int64_t region, int64_t epoch, uint64_t dstOff, std::f
     };
 }
 
+// Zero-copy: the words land in the peer's own (registered) output tensor, not in its window.
+Step CopyToPeerOutput(int peer, int64_t epoch, uint64_t dstOff, std::function<std::vector<int32_t>(World &, int)> words, const char *src)
+{
+    return [=](World &w, int rank) {
+        const std::vector<int32_t> v = words(w, rank);
+        std::vector<int32_t> &dst = w.ranks[peer].output;
+        if (dst.size() < dstOff + v.size()) dst.resize(dstOff + v.size(), 0);
+        std::copy(v.begin(), v.end(), dst.begin() + dstOff);
+        w.Log(EventKind::Copy, rank, peer, BufferRole::RegisteredBuffer, 0, epoch, dstOff * 4, v.size() * 4, src);
+        return true;
+    };
+}
+
 Step StoreFlag(int peer, int64_t slot, int64_t epoch, int64_t value, const char *src)
 {
     return [=](World &w, int rank) {
@@ -191,6 +204,17 @@ Program BuildCollective(const CheckerCase &c, int rank)
             return true;
         });
         AddGuard(p, c, rank, epoch);
+        const bool direct = gather && c.zeroCopy;
+        if (direct) {
+            // every rank announces that it has entered the launch; a producer writes a peer's tensor only after that peer's
+            // announcement (its earlier stream work, which may still read the tensor, is finished by then)
+            for (int i = 1; i < R; ++i) p.steps.push_back(StoreFlag((rank + i) % R, rank * FLAGS_PER_PAIR + FLAGS_PER_PAIR - 2, epoch, 1, "coll_kernels.cu:announce entry"));
+            for (int i = 1; i < R; ++i) {
+                const int peer = (rank + i) % R;
+                if (c.inject.skipEntryMeeting && rank == 0 && peer == 1) continue;
+                p.steps.push_back(WaitFlag(peer, peer * FLAGS_PER_PAIR + FLAGS_PER_PAIR - 2, epoch, 1, "coll_kernels.cu:wait for the peer's entry"));
+            }
+        }
         if (c.inject.deadlock && launch == 0 && rank < 2) {
             // both ranks wait for the other's first tile before producing their own
             p.steps.push_back(WaitFlag(1 - rank, (1 - rank) * FLAGS_PER_PAIR, epoch, 1, "injected: wait before produce"));
@@ -201,10 +225,12 @@ Program BuildCollective(const CheckerCase &c, int rank)
             for (int i = 1; i < R; ++i) {
                 const int peer = (rank + i) % R;
                 const int64_t srcOff = (gather || reduce) ? off : peer * perPeer + off;
-                p.steps.push_back(CopyToPeer(peer, rank, epoch, off, [=](World &w, int r) {
+                auto tile = [=](World &w, int r) {
                     const std::vector<int32_t> &in = w.ranks[r].input;
                     return std::vector<int32_t>(in.begin() + srcOff, in.begin() + srcOff + n);
-                }, BufferRole::CommData, "coll_kernels.cu:PushBody"));
+                };
+                if (direct) p.steps.push_back(CopyToPeerOutput(peer, epoch, static_cast<uint64_t>(rank) * c.count + off, tile, "coll_kernels.cu:PushBody (zero copy)"));
+                else p.steps.push_back(CopyToPeer(peer, rank, epoch, off, tile, BufferRole::CommData, "coll_kernels.cu:PushBody"));
                 const bool skip = c.inject.missingFlag && rank == 0 && peer == 1 && t == 0 && launch == 0;
                 if (!skip) {
                     const int64_t tag = (c.inject.staleMagic && rank == 0 && peer == 1 && t == 0 && launch == 0) ? epoch - 1 : epoch;
@@ -253,7 +279,9 @@ Program BuildCollective(const CheckerCase &c, int rank)
                         return true;
                     });
                 }
-                if (early) {
+                if (direct) {
+                    p.steps.push_back(wait);          // the tile is in the output already: its flag is all there is to wait for
+                } else if (early) {
                     p.steps.push_back(read);
                     p.steps.push_back(wait);
                 } else {
@@ -572,6 +600,23 @@ std::vector<Finding> CheckOrdering(const std::vector<Event> &events)
         }
         if (!guarded && reported.insert({c.rank, c.peer}).second) {
             add(FindingKind::BUFFER_LIFETIME, c, "data half reused without checking that the peer finished the launch two epochs ago");
+        }
+    }
+    // a peer's own tensor (registered memory, not a window half) may be written only after that peer is known to have
+    // entered this launch: an earlier satisfied wait of the writer for a flag that the peer raised in this epoch or later
+    std::set<std::pair<int, int>> early;
+    for (const Event &c : events) {
+        if (c.kind != EventKind::Copy || c.role != BufferRole::RegisteredBuffer || c.peer == c.rank) continue;
+        bool met = false;
+        for (const Event &w : events) {
+            if (w.id >= c.id) break;
+            if (w.kind == EventKind::FlagWait && w.rank == c.rank && w.peer == c.peer && w.satisfied && w.slot < SLOT_DONE_BASE &&
+                (static_cast<uint64_t>(w.magic) >> 32) >= static_cast<uint64_t>(c.magic)) {
+                met = true;
+            }
+        }
+        if (!met && early.insert({c.rank, c.peer}).second) {
+            add(FindingKind::BUFFER_LIFETIME, c, "a peer's own tensor was written before that peer was known to have entered this launch (its earlier work may still read it)");
         }
     }
     // coverage

@@ -76,6 +76,7 @@ struct Injection {
     bool deadlock = false;           // two ranks wait for each other before producing
     bool skipReuseGuard = false;     // a launch overwrites a half a slow peer still reads
     bool corruptOutput = false;      // one output word is flipped
+    bool skipEntryMeeting = false;   // zero-copy: a producer writes a peer's own tensor before that peer entered the launch
 };
 
 struct CheckerCase {
@@ -88,6 +89,7 @@ struct CheckerCase {
     std::string scheduler = "round_robin";   // serial | round_robin
     int64_t magic = 1;
     int launches = 1;                // consecutive launches (exercises ping-pong and the reuse guard)
+    bool zeroCopy = false;           // allgather: tiles go straight into the peers' registered output tensors, behind an entry meeting
     Injection inject;
 };
 

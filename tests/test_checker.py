@@ -109,3 +109,21 @@ def test_installed_traces_are_recorded_judged_and_covered(tmp_path):
         checker.load_manifests("no_such_trace")
     with pytest.raises(ValueError):
         checker.record_installed_trace("no_such_recipe", 2, str(tmp_path / "x"))
+
+
+def test_zero_copy_gather_needs_the_entry_meeting():
+    """Tiles that go straight into the peers' own output tensors: clean with the entry meeting (several ranks, several launches,
+    both schedulers), and a BUFFER_LIFETIME finding when one producer writes without having waited for its peer's entry."""
+    for ranks, sched in ((2, "round_robin"), (4, "serial"), (4, "round_robin")):
+        rep = checker.run_case(op="allgather", rank_size=ranks, count=512, tile_elems=128, launches=3, zero_copy=True, scheduler=sched)
+        assert rep["passed"] and rep["outputs_match"], rep["summary"]
+    rep = checker.run_case(op="allgather", rank_size=2, count=512, tile_elems=128, zero_copy=True, inject_skip_entry_meeting=True)
+    assert not rep["passed"] and "BUFFER_LIFETIME" in rep["findings"], rep["summary"]
+    assert "entered this launch" in rep["summary"]
+    # the window path has no such meeting and needs none
+    assert checker.run_case(op="allgather", rank_size=2, count=512, tile_elems=128, launches=3)["passed"]
+    cli = Path(__file__).resolve().parent.parent / "tilexr_b200" / "bin" / "tilexr_checker"
+    if cli.exists():
+        ok = subprocess.run([str(cli), "--op", "allgather", "--ranks", "2", "--zero-copy"], capture_output=True, text=True)
+        bad = subprocess.run([str(cli), "--op", "allgather", "--ranks", "2", "--zero-copy", "--inject-skip-entry-meeting"], capture_output=True, text=True)
+        assert ok.returncode == 0 and bad.returncode != 0 and "BUFFER_LIFETIME" in bad.stdout

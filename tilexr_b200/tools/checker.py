@@ -17,7 +17,7 @@ import sys
 from .. import _C
 
 INJECTIONS = ("read_before_copy", "stale_magic", "missing_flag", "peer_user_read", "pipe_wait", "deadlock", "skip_reuse_guard",
-              "corrupt_output")
+              "corrupt_output", "skip_entry_meeting")
 
 
 def run_case(**spec) -> dict:
@@ -203,6 +203,7 @@ def main(argv=None) -> int:
     p.add_argument("--experts", type=int, default=4)
     p.add_argument("--launches", type=int, default=1)
     p.add_argument("--scheduler", default="round_robin")
+    p.add_argument("--zero-copy", action="store_true", help="allgather: tiles go straight into the peers' registered outputs, behind an entry meeting")
     p.add_argument("--out", default="")
     p.add_argument("--trace", default="", help="event file(s) to analyse, comma separated (one per rank of a recorded run)")
     p.add_argument("--verify-installed-traces", action="store_true",
@@ -228,7 +229,7 @@ def main(argv=None) -> int:
             print(*f)
         return 1 if findings else 0
     spec = dict(op=a.op, rank_size=a.ranks, server_count=a.servers, count=a.count, tile_elems=a.tile, bs=a.bs, h=a.h, top_k=a.topk,
-                moe_expert_num=a.experts, launches=a.launches, scheduler=a.scheduler)
+                moe_expert_num=a.experts, launches=a.launches, scheduler=a.scheduler, zero_copy=a.zero_copy)
     for name in INJECTIONS:
         spec["inject_" + name] = getattr(a, "inject_" + name)
     if a.out:
