@@ -408,3 +408,29 @@ def test_case_selection_overrides_flowchart_and_hot_loop_helpers(tmp_path):
         assert m["first_row"] == victim and m["rows_differ"] == 1 and m["got_row_is_zero"] and m["expected_source_rank"] == int(source[victim])
     p = hl.percentiles([float(i) for i in range(1, 101)])
     assert p["count"] == 100 and p["max"] == 100.0 and 50.0 <= p["p50"] <= 51.0 and p["p99"] >= 99.0 and hl.percentiles([])["count"] == 0
+
+
+def test_model_flow_documents_compare_stage_by_stage(tmp_path):
+    """Two runs side by side; a document in the reference's layout (no sequence numbers, no byte counts) is read too."""
+    import json
+
+    from tilexr_b200.tools.moonep import model_flow as mf
+
+    def doc(scale, stages):
+        ops = [{"stage": s, "phase": "initial_forward", "layer": 0, "latency_us": scale * (i + 1) * 10.0} for i, s in enumerate(stages)]
+        return {"ranks": {"0": {"operators": ops}, "1": {"operators": [dict(o, latency_us=o["latency_us"] * 1.5) for o in ops]}}}
+
+    a, b = tmp_path / "a.json", tmp_path / "b.json"
+    a.write_text(json.dumps(doc(2.0, mf.FORWARD_STAGES + mf.BACKWARD_STAGES)))
+    b.write_text(json.dumps([doc(1.0, mf.FORWARD_STAGES)]))                        # the launcher writes a list of documents
+    rows = mf.compare_documents(mf.load_document(str(a)), mf.load_document(str(b)))
+    by = {r["stage"]: r for r in rows}
+    assert by["planning"]["a_us"] == 30.0 and by["planning"]["b_us"] == 15.0 and abs(by["planning"]["speedup_b_over_a"] - 2.0) < 1e-9   # slowest rank
+    assert by["reduce_grad"]["b_us"] is None and by["reduce_grad"]["speedup_b_over_a"] is None
+    step = rows[-1]
+    assert step["stage"].startswith("step") and abs(step["speedup_b_over_a"] - 2.0) < 1e-9
+    assert mf.main(["compare", str(a), str(b)]) == 0 and mf.main(["show", str(a)]) == 0
+    bad = tmp_path / "bad.json"
+    bad.write_text("{}")
+    with pytest.raises(ValueError):
+        mf.load_document(str(bad))

@@ -20,6 +20,7 @@ communication).
 
     python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 -m tilexr_b200.tools.moonep.launcher \\
         --mode model-flow --cases perf --layers 5 --iters 5 --json performance.json
+    python -m tilexr_b200.tools.moonep.model_flow compare before.json after.json     (also reads the reference's performance.json)
 """
 from __future__ import annotations
 
@@ -318,6 +319,74 @@ def markdown(doc: dict) -> str:
     return "\n".join(lines)
 
 
+def compare_documents(a: dict, b: dict) -> List[dict]:
+    """Stage by stage: the slowest rank's median of two runs and b's speed-up over a (reference:
+    tools/moonep/model_replay_compare.py).  The documents may come from different builds, machines or backends; stages
+    that only one of them timed are listed with the other side empty."""
+    ma, mb = stage_medians(a), stage_medians(b)
+    rows = []
+    for stage in FORWARD_STAGES + BACKWARD_STAGES:
+        sa, sb = ma.get(stage), mb.get(stage)
+        if sa is None and sb is None:
+            continue
+        rows.append({"stage": stage, "a_us": None if sa is None else sa["median_us"], "b_us": None if sb is None else sb["median_us"],
+                     "a_operators": 0 if sa is None else sa["operators"], "b_operators": 0 if sb is None else sb["operators"],
+                     "speedup_b_over_a": None if not sa or not sb or sb["median_us"] <= 0 else sa["median_us"] / sb["median_us"]})
+    total_a = sum(r["a_us"] * r["a_operators"] for r in rows if r["a_us"] is not None and r["b_us"] is not None)
+    total_b = sum(r["b_us"] * r["b_operators"] for r in rows if r["a_us"] is not None and r["b_us"] is not None)
+    rows.append({"stage": "step (stages both runs timed, median x operators)", "a_us": total_a, "b_us": total_b, "a_operators": None, "b_operators": None,
+                 "speedup_b_over_a": None if total_b <= 0 else total_a / total_b})
+    return rows
+
+
+def load_document(path: str) -> dict:
+    """A document written by the launcher's model-flow mode (`--json` holds a list with one document per case; the first is
+    taken), or one in the reference's layout (`ranks.<r>.operators[]` with `stage` and `latency_us`)."""
+    with open(path) as f:
+        doc = json.load(f)
+    if isinstance(doc, list):
+        doc = doc[0]
+    if "ranks" not in doc:
+        raise ValueError(f"{path}: no per-rank operator list")
+    for entry in doc["ranks"].values():
+        for op in entry["operators"]:
+            op.setdefault("algorithm_bytes", None)
+            op.setdefault("sequence", entry["operators"].index(op))
+    return doc
+
+
+def main(argv=None) -> int:
+    import argparse
+
+    p = argparse.ArgumentParser(description="Compare two model-flow documents stage by stage, or show one against the published medians.")
+    sub = p.add_subparsers(dest="cmd", required=True)
+    c = sub.add_parser("compare")
+    c.add_argument("a")
+    c.add_argument("b")
+    s1 = sub.add_parser("show")
+    s1.add_argument("doc")
+    args = p.parse_args(argv)
+    if args.cmd == "show":
+        doc = load_document(args.doc)
+        doc.setdefault("case", args.doc)
+        doc.setdefault("operator_order", [o["stage"] for o in next(iter(doc["ranks"].values()))["operators"]])
+        doc.setdefault("iterations", 1)
+        doc.setdefault("world_size", len(doc["ranks"]))
+        print(markdown(doc))
+        return 0
+    rows = compare_documents(load_document(args.a), load_document(args.b))
+    print("| stage | a us | b us | b over a |\n|---|---|---|---|")
+    for r in rows:
+        fmt = lambda v: "-" if v is None else f"{v:.1f}"
+        sp = "-" if r["speedup_b_over_a"] is None else f"{r['speedup_b_over_a']:.2f}x"
+        print(f"| {r['stage']} | {fmt(r['a_us'])} | {fmt(r['b_us'])} | {sp} |")
+    return 0
+
+
 def write_json(path: str, doc: dict) -> None:
     with open(path, "w") as f:
         json.dump(doc, f, indent=1)
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())
