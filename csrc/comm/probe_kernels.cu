@@ -106,7 +106,8 @@ __device__ void ProbeBody(const ProbeArgs &a)
         const int from = (rank - 1 + R) % R;
         bool good = ok;
         if (good) {
-            const uint32_t qp = static_cast<uint32_t>(g % UDMAQpCount(comm));
+            const uint32_t lanes = UDMAQpCount(comm);      // 0 on a communicator without registered memory: the verbs then refuse
+            const uint32_t qp = lanes != 0 ? static_cast<uint32_t>(g % lanes) : 0u;
             good = UDMAPutSignalNbiOnQp<uint8_t>(comm, peer, qp, a.localSrc + b0, b0, nb, a.offset + g * 8, MakeFlag(w.epoch, 1)) ==
                    TILEXR_UDMA_STATUS_SUCCESS;
             good = good && UDMAPutNbiOnQp<uint8_t>(comm, peer, 0, a.localSrc, a.offset + G * 8, 16) == TILEXR_UDMA_STATUS_INVALID;
