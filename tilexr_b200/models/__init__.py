@@ -2,3 +2,4 @@
 from .moe import ExpertParallelMoE, MoEConfig
 
 __all__ = ["ExpertParallelMoE", "MoEConfig"]
+from .tp_mlp import SequenceParallelMLP, TPMlpConfig, shard_weights  # noqa: F401
