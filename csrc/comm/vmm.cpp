@@ -441,3 +441,75 @@ int VmmFree(Exchange *ex, VmmAllocation *a)
 }
 
 } // namespace TileXR
+
+// ---- host-side self tests (no GPU involved) ------------------------------------------------------------------------------
+
+extern "C" {
+
+// What this host offers the symmetric allocator: *vmm / *multicast are 0 on a machine without a CUDA driver (the library
+// resolves the driver's entry points at run time and loads anywhere), and the caller then takes cudaMalloc + CUDA IPC.
+int TileXRVmmQuerySupport(int device, int *vmm, int *multicast)
+{
+    if (vmm == nullptr || multicast == nullptr) return TileXR::TILEXR_ERROR_PARA_CHECK_FAIL;
+    bool v = false, m = false;
+    const int ret = TileXR::VmmDeviceSupport(device, &v, &m);
+    *vmm = v ? 1 : 0;
+    *multicast = m ? 1 : 0;
+    return ret;
+}
+
+// The descriptor hand-over that carries a rank's memory to its peers, run inside one process: a listener named after
+// (tag, rank), a sender that passes `fd` with the (source rank, kind) header, and the received descriptor written to
+// *received (the caller closes it).  Returns 0, or which step failed (1 listen, 2 send, 3 receive, 4 header).  A second
+// listener on the same name must be refused (5 when it is not): the name is the rendezvous.
+int TileXRVmmDescriptorSelfTest(uint64_t tag, int rank, int fd, int srcRank, int kind, int *received)
+{
+    using namespace TileXR;
+    if (received == nullptr) return TILEXR_ERROR_PARA_CHECK_FAIL;
+    *received = -1;
+    const int listener = Listen(tag, rank, 4);
+    if (listener < 0) return 1;
+    const int second = Listen(tag, rank, 4);
+    if (second >= 0) {
+        close(second);
+        close(listener);
+        return 5;
+    }
+    int step = 0;
+    if (!SendFd(tag, rank, fd, srcRank, kind)) {
+        step = 2;
+    } else {
+        FdMessage body{-1, -1};
+        int got = -1;
+        if (!RecvFd(listener, 2000, &got, &body)) {
+            step = 3;
+        } else if (body.srcRank != srcRank || body.kind != kind) {
+            close(got);
+            step = 4;
+        } else {
+            *received = got;
+        }
+    }
+    close(listener);
+    return step;
+}
+
+// Nobody listens on (tag, rank): the send must fail at once instead of blocking, and a receive must give up after its budget.
+int TileXRVmmDescriptorNobodyThere(uint64_t tag, int rank, int fd)
+{
+    using namespace TileXR;
+    if (SendFd(tag, rank, fd, 0, 0)) return 1;
+    const int listener = Listen(tag, rank, 1);
+    if (listener < 0) return 2;
+    FdMessage body{-1, -1};
+    int got = -1;
+    const bool received = RecvFd(listener, 50, &got, &body);
+    close(listener);
+    if (received) {
+        close(got);
+        return 3;
+    }
+    return 0;
+}
+
+} // extern "C"

@@ -27,6 +27,11 @@ int TileXRNamedVerbsProbe(TileXRCommPtr comm, void *dst, const void *src, uint64
 // Every rank writes `bytes` from `localSrc` into region `handle` of rank (rank+1) % R at
 // `dstOffset`; each block then adds 1 to signal word `signalIndex` of that rank and waits until
 // this rank's own word reaches `expectedSignal` (blocks x number of calls so far).
+// Host-side self tests of the symmetric allocator's plumbing (csrc/comm/vmm.cpp); no GPU is involved.
+int TileXRVmmQuerySupport(int device, int *vmm, int *multicast);
+int TileXRVmmDescriptorSelfTest(uint64_t tag, int rank, int fd, int srcRank, int kind, int *received);
+int TileXRVmmDescriptorNobodyThere(uint64_t tag, int rank, int fd);
+
 int TileXRPutSignalProbe(TileXRCommPtr comm, TileXRUDMAMemHandle handle, uint64_t dstOffset, const void *localSrc,
                          uint64_t bytes, uint32_t signalIndex, uint64_t expectedSignal, uint32_t blocks, TileXRStream stream);
 // Every rank reads `bytes` of region `handle` of rank (rank+1) % R at `srcOffset` into `localDst`.

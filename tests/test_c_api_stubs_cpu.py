@@ -81,3 +81,31 @@ def test_host_memory_communicator_refuses_the_cuda_entry_points_and_serves_host_
         comm.destroy()
     finally:
         dist.destroy_process_group()
+
+
+def test_symmetric_allocator_plumbing_without_a_gpu(lib, tmp_path):
+    """What the runtime-owned symmetric memory needs from the host, checked without a GPU: the support query answers "no" on a
+    machine without a driver (the caller then takes cudaMalloc + CUDA IPC), and a descriptor passed through the allocator's own
+    Unix-socket hand-over arrives as a descriptor of the same file, with its header; nobody listening is an error, not a hang."""
+    vmm, mc = ctypes.c_int(7), ctypes.c_int(7)
+    assert lib.TileXRVmmQuerySupport(0, ctypes.byref(vmm), ctypes.byref(mc)) == 0
+    if not torch.cuda.is_available():
+        assert (vmm.value, mc.value) == (0, 0)
+    assert lib.TileXRVmmQuerySupport(0, None, None) == PARA_CHECK_FAIL
+    path = tmp_path / "payload.bin"
+    path.write_bytes(b"rank memory stands in here")
+    fd = os.open(path, os.O_RDONLY)
+    try:
+        tag = ctypes.c_uint64(0x7E57000000000000 | os.getpid())
+        got = ctypes.c_int(-1)
+        assert lib.TileXRVmmDescriptorSelfTest(tag, 3, fd, 5, 1, ctypes.byref(got)) == 0
+        assert got.value >= 0 and got.value != fd
+        try:
+            assert os.fstat(got.value).st_ino == os.fstat(fd).st_ino              # the same open file, another descriptor
+            assert os.pread(got.value, 100, 0) == b"rank memory stands in here"
+        finally:
+            os.close(got.value)
+        assert lib.TileXRVmmDescriptorNobodyThere(ctypes.c_uint64(tag.value + 1), 0, fd) == 0
+        assert lib.TileXRVmmDescriptorSelfTest(tag, 3, fd, 5, 1, None) == PARA_CHECK_FAIL
+    finally:
+        os.close(fd)
