@@ -174,6 +174,112 @@ int TileXRHostAllReduceSumF32(const float *send, float *recv, uint64_t count, Ti
     return End(c);
 }
 
+// Equal all-to-all: slice p of `send` goes to rank p and lands as slice `rank` of its `recv`, tile by tile behind flags.
+int TileXRHostAllToAll(const void *send, void *recv, uint64_t bytesPerPeer, uint32_t tileBytes, TileXRCommPtr comm)
+{
+    if (send == nullptr || recv == nullptr || send == recv || bytesPerPeer == 0 || tileBytes == 0) return TILEXR_ERROR_PARA_CHECK_FAIL;
+    HostCtx c;
+    int ret = Begin(comm, TILEXR_OP_ALL2ALL, static_cast<int64_t>(bytesPerPeer), &c);
+    if (ret != TILEXR_SUCCESS) return ret;
+    const uint64_t pairStride = (c.args->dataHalfBytes / c.R) & ~255ull;
+    const uint64_t tiles = (bytesPerPeer + tileBytes - 1) / tileBytes;
+    if (bytesPerPeer > pairStride || tiles > TILEXR_FLAGS_PER_PAIR) return TILEXR_ERROR_PARA_CHECK_FAIL;
+    const uint8_t *in = static_cast<const uint8_t *>(send);
+    uint8_t *out = static_cast<uint8_t *>(recv);
+    for (uint64_t t = 0; t < tiles; ++t) {
+        const uint64_t off = t * tileBytes;
+        const uint64_t n = std::min<uint64_t>(tileBytes, bytesPerPeer - off);
+        for (int i = 1; i < c.R; ++i) {
+            const int peer = (c.rank + i) % c.R;
+            WindowStore(DataHalf(c.args, peer, c.epoch) + c.rank * pairStride + off, in + peer * bytesPerPeer + off, n);
+            if (!g_skipFlags) {
+                SetFlag(FlagSlot(c.args, peer, TILEXR_FLAG_DATA_BASE + static_cast<int64_t>(c.rank) * TILEXR_FLAGS_PER_PAIR + t),
+                        c.epoch, static_cast<uint32_t>(t + 1));
+            }
+        }
+        std::memcpy(out + c.rank * bytesPerPeer + off, in + c.rank * bytesPerPeer + off, n);
+    }
+    for (uint64_t t = 0; t < tiles && c.w.ok(); ++t) {
+        const uint64_t off = t * tileBytes;
+        const uint64_t n = std::min<uint64_t>(tileBytes, bytesPerPeer - off);
+        for (int i = 1; i < c.R; ++i) {
+            const int src = (c.rank + i) % c.R;
+            const int64_t slot = TILEXR_FLAG_DATA_BASE + static_cast<int64_t>(src) * TILEXR_FLAGS_PER_PAIR + t;
+            if (!WaitFlagGE(c.w, FlagSlot(c.args, c.rank, slot), static_cast<uint32_t>(t + 1), src, slot)) break;
+            WindowLoad(out + src * bytesPerPeer + off, DataHalf(c.args, c.rank, c.epoch) + src * pairStride + off, n);
+        }
+    }
+    return End(c);
+}
+
+// Reduce-scatter: slice p of every rank's `send` (recvCount floats) is summed on rank p in rank order.
+int TileXRHostReduceScatterSumF32(const float *send, float *recv, uint64_t recvCount, TileXRCommPtr comm)
+{
+    if (send == nullptr || recv == nullptr || recvCount == 0) return TILEXR_ERROR_PARA_CHECK_FAIL;
+    HostCtx c;
+    int ret = Begin(comm, TILEXR_OP_REDUCE_SCATTER, static_cast<int64_t>(recvCount), &c);
+    if (ret != TILEXR_SUCCESS) return ret;
+    const uint64_t pairStride = (c.args->dataHalfBytes / c.R) & ~255ull;
+    const uint64_t bytes = recvCount * sizeof(float);
+    if (bytes > pairStride) return TILEXR_ERROR_PARA_CHECK_FAIL;
+    for (int i = 1; i < c.R; ++i) {
+        const int peer = (c.rank + i) % c.R;
+        WindowStore(DataHalf(c.args, peer, c.epoch) + c.rank * pairStride, send + static_cast<uint64_t>(peer) * recvCount, bytes);
+        if (!g_skipFlags) {
+            SetFlag(FlagSlot(c.args, peer, TILEXR_FLAG_DATA_BASE + static_cast<int64_t>(c.rank) * TILEXR_FLAGS_PER_PAIR), c.epoch, 1);
+        }
+    }
+    for (int s = 0; s < c.R && c.w.ok(); ++s) {
+        if (s == c.rank) continue;
+        const int64_t slot = TILEXR_FLAG_DATA_BASE + static_cast<int64_t>(s) * TILEXR_FLAGS_PER_PAIR;
+        WaitFlagGE(c.w, FlagSlot(c.args, c.rank, slot), 1, s, slot);
+    }
+    if (c.w.ok()) {
+        for (int s = 0; s < c.R; ++s) {
+            if (s != c.rank) WindowRead(DataHalf(c.args, c.rank, c.epoch) + s * pairStride, bytes);
+        }
+        for (uint64_t i = 0; i < recvCount; ++i) {
+            float acc = 0.f;
+            for (int s = 0; s < c.R; ++s) {
+                const float v = s == c.rank ? send[static_cast<uint64_t>(c.rank) * recvCount + i]
+                                            : reinterpret_cast<const float *>(DataHalf(c.args, c.rank, c.epoch) + s * pairStride)[i];
+                acc = s == 0 ? v : acc + v;
+            }
+            recv[i] = acc;
+        }
+    }
+    return End(c);
+}
+
+// Broadcast: the root pushes its buffer into every peer's window tile by tile; the others copy tiles out as their flags show up.
+int TileXRHostBroadcast(void *buf, uint64_t bytes, int root, uint32_t tileBytes, TileXRCommPtr comm)
+{
+    if (buf == nullptr || bytes == 0 || tileBytes == 0) return TILEXR_ERROR_PARA_CHECK_FAIL;
+    HostCtx c;
+    int ret = Begin(comm, TILEXR_OP_BROADCAST, static_cast<int64_t>(bytes), &c);
+    if (ret != TILEXR_SUCCESS) return ret;
+    const uint64_t pairStride = (c.args->dataHalfBytes / c.R) & ~255ull;
+    const uint64_t tiles = (bytes + tileBytes - 1) / tileBytes;
+    if (root < 0 || root >= c.R || bytes > pairStride || tiles > TILEXR_FLAGS_PER_PAIR) return TILEXR_ERROR_PARA_CHECK_FAIL;
+    uint8_t *data = static_cast<uint8_t *>(buf);
+    for (uint64_t t = 0; t < tiles && c.w.ok(); ++t) {
+        const uint64_t off = t * tileBytes;
+        const uint64_t n = std::min<uint64_t>(tileBytes, bytes - off);
+        const int64_t slot = TILEXR_FLAG_DATA_BASE + static_cast<int64_t>(root) * TILEXR_FLAGS_PER_PAIR + t;
+        if (c.rank == root) {
+            for (int i = 1; i < c.R; ++i) {
+                const int peer = (c.rank + i) % c.R;
+                WindowStore(DataHalf(c.args, peer, c.epoch) + root * pairStride + off, data + off, n);
+                if (!g_skipFlags) SetFlag(FlagSlot(c.args, peer, slot), c.epoch, static_cast<uint32_t>(t + 1));
+            }
+        } else {
+            if (!WaitFlagGE(c.w, FlagSlot(c.args, c.rank, slot), static_cast<uint32_t>(t + 1), root, slot)) break;
+            WindowLoad(data + off, DataHalf(c.args, c.rank, c.epoch) + root * pairStride + off, n);
+        }
+    }
+    return End(c);
+}
+
 int TileXRHostEpDispatch(const float *x, const int32_t *expertIds, int64_t bs, int64_t h, int64_t topK,
                          int64_t moeExpertNum, int64_t maxRecvRows, float *expandXOut, int32_t *assistOut,
                          int64_t *expertTokenNumsOut, int32_t *sendCountsOut, int32_t *recvTotalOut, TileXRCommPtr comm)

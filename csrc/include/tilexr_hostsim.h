@@ -17,6 +17,11 @@ extern "C" {
 // magic-tagged flag; consumers copy a tile as soon as its flag shows up.
 int TileXRHostAllGather(const void *send, void *recv, uint64_t bytes, uint32_t tileBytes, TileXRCommPtr comm);
 int TileXRHostAllReduceSumF32(const float *send, float *recv, uint64_t count, TileXRCommPtr comm);
+// Equal all-to-all (slice p of `send`, `bytesPerPeer` long, becomes slice `rank` of rank p's `recv`), reduce-scatter (slice p
+// of every rank's `send` summed on rank p in rank order) and broadcast from `root`, over the same tiles and flags.
+int TileXRHostAllToAll(const void *send, void *recv, uint64_t bytesPerPeer, uint32_t tileBytes, TileXRCommPtr comm);
+int TileXRHostReduceScatterSumF32(const float *send, float *recv, uint64_t recvCount, TileXRCommPtr comm);
+int TileXRHostBroadcast(void *buf, uint64_t bytes, int root, uint32_t tileBytes, TileXRCommPtr comm);
 
 // fp32 expert-parallel dispatch / combine with the semantics of tilexr_ep.h.
 int TileXRHostEpDispatch(const float *x, const int32_t *expertIds, int64_t bs, int64_t h, int64_t topK,

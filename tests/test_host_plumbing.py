@@ -40,6 +40,31 @@ def _worker(rank, world, port, scenario, result_queue):
             ref = x[:4096].clone()
             dist.all_reduce(ref)
             assert torch.allclose(red, ref, atol=1e-6)
+        elif scenario == "collectives":
+            # all-to-all, reduce-scatter and broadcast over the same tiles and flags, several launches each (both halves,
+            # the reuse guard), against torch.distributed on the same data
+            for it in range(3):
+                n = 3 * 4096 + 7                                      # not a whole number of tiles
+                x = torch.randn(world * n, generator=g)
+                got = txr._C.host_all_to_all(comm, x, 4096)
+                want = torch.empty_like(x)
+                dist.all_to_all_single(want, x)
+                assert torch.equal(got, want)
+                red = txr._C.host_reduce_scatter(comm, x)
+                parts = [torch.empty_like(x) for _ in range(world)]
+                dist.all_gather(parts, x)
+                acc = parts[0][rank * n:(rank + 1) * n].clone()
+                for p in parts[1:]:
+                    acc = acc + p[rank * n:(rank + 1) * n]           # rank order, like the kernel
+                assert torch.equal(red, acc)
+                root = it % world
+                b = torch.randn(n, generator=g)
+                ref = b.clone()
+                dist.broadcast(ref, src=root)
+                txr._C.host_broadcast(comm, b, root, 4096)
+                assert torch.equal(b, ref)
+            with pytest.raises(RuntimeError):
+                txr._C.host_broadcast(comm, torch.zeros(8), world, 4096)      # a root outside the communicator
         elif scenario == "ep":
             bs, h, E, K = 128, 1024, 8, 2
             x = torch.randn(bs, h, generator=g)
@@ -188,6 +213,11 @@ def test_tile_flag_all_gather_two_ranks():
 
 def test_ep_dispatch_combine_two_ranks():
     _run("ep")
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_all_to_all_reduce_scatter_broadcast(world):
+    _run("collectives", world)
 
 
 def test_lost_flag_is_detected_on_the_host():

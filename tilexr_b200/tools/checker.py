@@ -87,7 +87,19 @@ def _recipe_ep(txr, comm, rank, world):
     txr._C.host_ep_combine(comm, expand[:total].contiguous(), assist, total, ids, w, E)
 
 
-RECIPES = {"host_all_gather": _recipe_all_gather, "host_all_reduce": _recipe_all_reduce, "host_ep_dispatch_combine": _recipe_ep}
+def _recipe_exchange(txr, comm, rank, world):
+    import torch
+
+    x = torch.arange(world * 5000, dtype=torch.float32) + 10000 * rank
+    for root in range(world):
+        txr._C.host_all_to_all(comm, x, 4096)
+        txr._C.host_reduce_scatter(comm, x)
+        b = torch.full((5000,), float(rank))
+        txr._C.host_broadcast(comm, b, root, 4096)
+
+
+RECIPES = {"host_all_gather": _recipe_all_gather, "host_all_reduce": _recipe_all_reduce, "host_ep_dispatch_combine": _recipe_ep,
+           "host_all_to_all_reduce_scatter_broadcast": _recipe_exchange}
 
 
 def _trace_worker(rank: int, world: int, port: int, recipe: str, out_dir: str, errors) -> None:
