@@ -117,3 +117,60 @@ def test_context_and_capability_objects(monkeypatch):
                 dict(planner_group_rank=2), dict(tokens_per_rank=1 << 28, topk=8)):
         with pytest.raises((ValueError, OverflowError)):
             make(**bad)
+
+
+def test_stage_tracing_and_latency_capture_from_the_environment(monkeypatch, tmp_path, capsys):
+    """TILEXR_MOONEP_TRACE_STAGES / TILEXR_MOONEP_PERF_CAPTURE_* on a buffer whose native calls are replaced by no-ops: the stage
+    names of a forward and a backward pass in call order, skipped warm-up calls, the per-rank file and its merge into one
+    document (reference: integrations/moonep_torch/tilexr_moonep/torch_api.py:669-790)."""
+    import json
+
+    import torch
+    from tilexr_b200.integrations import moonep, moonep_capture
+    from tilexr_b200.tools.moonep import model_flow
+
+    class FakeComm:
+        rank, world_size = 1, 2
+
+        def symm_empty(self, shape, dtype):
+            return torch.zeros(shape, dtype=dtype)
+
+    plan_dict = {"dst": torch.zeros(8, dtype=torch.int32), "experts_to_copy": torch.zeros(2, 2, dtype=torch.int32), "zero_fill_ranges": torch.zeros(6, 2, dtype=torch.int32),
+                 "remote_stats": torch.zeros(2, dtype=torch.int32), "N": 8, "R": 2, "E": 4, "B": 2, "NvS": 8, "K": 2, "dup_counts": None, "status": None,
+                 "dst_local": None, "cu_seqlens": torch.zeros(6, dtype=torch.int32)}
+    monkeypatch.setattr(moonep._C, "moonep_planning", lambda *a, **k: dict(plan_dict), raising=False)
+    for name in ("moonep_dispatch", "moonep_prefetch_weight", "moonep_combine", "moonep_reduce_grad"):
+        monkeypatch.setattr(moonep._C, name, lambda *a, **k: None, raising=False)
+    monkeypatch.setattr(torch.cuda, "is_available", lambda: False)
+    monkeypatch.setenv("TILEXR_MOONEP_TRACE_STAGES", "1")
+    monkeypatch.setenv("TILEXR_MOONEP_PERF_CAPTURE_DIR", str(tmp_path))
+    monkeypatch.setenv("TILEXR_MOONEP_PERF_CAPTURE_ID", "unit")
+    monkeypatch.setenv("TILEXR_MOONEP_PERF_CAPTURE_OPERATORS", "7")
+    monkeypatch.setenv("TILEXR_MOONEP_PERF_CAPTURE_SKIP_OPERATORS", "4")
+    buf = moonep.TileXRMoonEPBuffer(FakeComm(), S=4, H=8, K=2, E=4, token_padding=1, dtype=torch.float32)
+    hidden, w, topk = torch.zeros(4, 8), torch.ones(4, 2), torch.zeros(4, 2, dtype=torch.int32)
+    proj = moonep.ProjectionBuffers(torch.zeros(4, 2, 8), torch.zeros(4, 2, 8), torch.zeros(4, 2, 8))
+    for _ in range(2):                                            # the first forward (4 calls) is the skipped warm-up
+        y, plan = buf.forward(hidden, w, topk, None, proj, lambda rows, cu, p: rows)
+    buf.backward(hidden, plan, lambda rows, cu: rows, grads=proj)
+    buf.close()
+    traced = [line for line in capsys.readouterr().err.splitlines() if "TileXR MoonEP rank 1" in line]
+    assert len(traced) == 11 and "planning (call 0)" in traced[0] and "reduce_grad (call 10)" in traced[-1]
+    doc = json.loads((tmp_path / "rank1_performance.json").read_text())
+    assert doc["capture_id"] == "unit" and doc["complete"] and doc["rank"] == 1
+    assert [o["stage"] for o in doc["operators"]] == ["planning", "dispatch_forward", "prefetch_weight", "combine_forward", "dispatch_backward",
+                                                      "combine_backward", "reduce_grad"]
+    assert [o["source_operator"] for o in doc["operators"]] == list(range(4, 11)) and all(o["latency_us"] >= 0 for o in doc["operators"])
+    merged = moonep_capture.merge_capture_files(str(tmp_path))
+    assert set(model_flow.stage_medians(merged)) == set(model_flow.FORWARD_STAGES + model_flow.BACKWARD_STAGES)
+    # a directory without an id is refused when the buffer is made
+    monkeypatch.delenv("TILEXR_MOONEP_PERF_CAPTURE_ID")
+    with pytest.raises(ValueError):
+        moonep.TileXRMoonEPBuffer(FakeComm(), S=4, H=8, K=2, E=4, token_padding=1, dtype=torch.float32)
+    # off by default: nothing is timed, nothing is written
+    for name in ("TILEXR_MOONEP_TRACE_STAGES", "TILEXR_MOONEP_PERF_CAPTURE_DIR"):
+        monkeypatch.delenv(name)
+    quiet = moonep.TileXRMoonEPBuffer(FakeComm(), S=4, H=8, K=2, E=4, token_padding=1, dtype=torch.float32)
+    assert not quiet._capture.active
+    quiet.forward(hidden, w, topk, None, None, lambda rows, cu, p: rows)
+    assert quiet._capture.seen == 0

@@ -303,6 +303,10 @@ class TileXRMoonEPBuffer:
         self.dtype = dtype
         self._poisoned = False
         self.context: Optional[TileXRMoonEPContext] = None
+        from .moonep_capture import StageCapture
+
+        self._capture = StageCapture(comm.rank)          # stage tracing / latency capture, switched on from the environment
+        self._direction = "forward"
         # persistent receive tensors: peers write into them directly
         self.hidden_nvsh = comm.symm_empty([self.NvS, H], dtype)
         self.weights_nvs = comm.symm_empty([self.NvS], torch.float32)
@@ -346,7 +350,10 @@ class TileXRMoonEPBuffer:
     def planning(self, topk_experts_sk: torch.Tensor, tokens_per_expert: Optional[torch.Tensor] = None) -> MoonEPCommPlan:
         self._check_alive()
         topk = topk_experts_sk.to(torch.int32).contiguous()
-        return MoonEPCommPlan.from_dict(_C.moonep_planning(self.comm, topk, self.E, self.B, self.token_padding))
+        token = self._capture.begin("planning") if self._capture.active else None
+        plan = MoonEPCommPlan.from_dict(_C.moonep_planning(self.comm, topk, self.E, self.B, self.token_padding))
+        self._capture.end(token)
+        return plan
 
     def dispatch(self, hidden_sh: torch.Tensor, route_weights_sk: Optional[torch.Tensor], plan: MoonEPCommPlan,
                  out: Optional[torch.Tensor] = None, trace: Optional["DispatchTrace"] = None):
@@ -360,8 +367,10 @@ class TileXRMoonEPBuffer:
             kw = dict(trace_buffer=trace.buffer, trace_iteration=trace.iteration, trace_iterations=trace.iterations,
                       trace_event_capacity=trace.event_capacity)
             trace.iteration += 1
+        token = self._capture.begin(f"dispatch_{self._direction}") if self._capture.active else None
         _C.moonep_dispatch(self.comm, plan.as_dict(), hidden_sh.contiguous(),
                            None if route_weights_sk is None else route_weights_sk.float().contiguous(), hidden_out, w_out, **kw)
+        self._capture.end(token)
         return hidden_out, w_out
 
     def dispatch_trace(self, iterations: int = 1, event_capacity: int = 64, blocks: int = 128) -> "DispatchTrace":
@@ -376,7 +385,9 @@ class TileXRMoonEPBuffer:
 
     def prefetch_weight(self, plan: MoonEPCommPlan, projections: ProjectionBuffers) -> None:
         self._check_alive()
+        token = self._capture.begin("prefetch_weight") if self._capture.active else None
         _C.moonep_prefetch_weight(self.comm, plan.as_dict(), projections.gate, projections.up, projections.down)
+        self._capture.end(token)
 
     def combine(self, plan: MoonEPCommPlan, hidden_nvsh: torch.Tensor, route_weights_nvs: Optional[torch.Tensor] = None,
                 fold_duplicates: bool = False):
@@ -389,11 +400,13 @@ class TileXRMoonEPBuffer:
         w_sk = None
         if route_weights_nvs is not None:
             w_sk = torch.empty(self.S, self.K, dtype=torch.float32, device=hidden_nvsh.device)
+        token = self._capture.begin(f"combine_{self._direction}") if self._capture.active else None
         if fold_duplicates:
             ws = self._combine_workspace(hidden_nvsh.shape[1], hidden_nvsh.dtype)
             _C.moonep_combine_v2(self.comm, plan.dst_local, hidden_nvsh.contiguous(), route_weights_nvs, hidden_sh, w_sk, ws, self.K)
         else:
             _C.moonep_combine(self.comm, plan.as_dict(), hidden_nvsh.contiguous(), route_weights_nvs, hidden_sh, w_sk)
+        self._capture.end(token)
         return hidden_sh, w_sk
 
     def _combine_workspace(self, h: int, dtype) -> torch.Tensor:
@@ -422,7 +435,9 @@ class TileXRMoonEPBuffer:
 
     def reduce_grad(self, plan: MoonEPCommPlan, grads: ProjectionBuffers) -> None:
         self._check_alive()
+        token = self._capture.begin("reduce_grad") if self._capture.active else None
         _C.moonep_reduce_grad(self.comm, plan.as_dict(), grads.gate, grads.up, grads.down)
+        self._capture.end(token)
 
     # -- composed flows -------------------------------------------------------------------------------
     def forward(self, hidden, route_weights, topk_experts, tokens_per_expert, projections: Optional[ProjectionBuffers],
@@ -440,11 +455,15 @@ class TileXRMoonEPBuffer:
     def backward(self, grad_output, plan: MoonEPCommPlan, expert_backward: Callable, grads: Optional[ProjectionBuffers] = None):
         if self._grad_nvsh is None or self._grad_nvsh.dtype != grad_output.dtype:
             self._grad_nvsh = self.comm.symm_empty([self.NvS, self.H], grad_output.dtype)
-        rows, _ = self.dispatch(grad_output, None, plan, out=self._grad_nvsh)
-        grad_rows = expert_backward(rows, plan.cu_seqlens)
-        gx, _ = self.combine(plan, grad_rows)
-        if grads is not None:
-            self.reduce_grad(plan, grads)
+        self._direction = "backward"
+        try:
+            rows, _ = self.dispatch(grad_output, None, plan, out=self._grad_nvsh)
+            grad_rows = expert_backward(rows, plan.cu_seqlens)
+            gx, _ = self.combine(plan, grad_rows)
+            if grads is not None:
+                self.reduce_grad(plan, grads)
+        finally:
+            self._direction = "forward"
         return gx
 
     # -- housekeeping ------------------------------------------------------------------------------------
@@ -474,6 +493,10 @@ class TileXRMoonEPBuffer:
             raise RuntimeError("this MoonEP buffer saw a failed stage; create a new one")
 
     def close(self) -> None:
+        if self._capture.dir and not self._poisoned:
+            if torch.cuda.is_available():
+                torch.cuda.synchronize()
+            self._capture.write()
         self._poisoned = True
         if self.context is not None:
             self.context.release_stream(self)
@@ -560,7 +583,12 @@ class Buffer:
     def combine(self, plan, hidden_nvsh, route_weights_nvs=None, async_finish=False, inter_rank_sync=True, *, zero_copy=False):
         if not inter_rank_sync or zero_copy:
             raise NotImplementedError("inter_rank_sync=False and zero_copy=True are not supported")
-        y, w = self.native.combine(plan, hidden_nvsh, route_weights_nvs)
+        # TILEXR_MOONEP_COMBINE_VERSION=2 selects the second-generation kernel (duplicates folded on the expert rank); the
+        # default here is the first, whose sum is rounded once
+        import os
+
+        fold = os.environ.get("TILEXR_MOONEP_COMBINE_VERSION", "1").strip() == "2"
+        y, w = self.native.combine(plan, hidden_nvsh, route_weights_nvs, fold_duplicates=fold)
         ev = None
         if async_finish:
             ev = torch.cuda.Event()

@@ -22,8 +22,11 @@ ENV_TRACE = "TILEXR_VLLM_TRACE"
 route_counters: Dict[str, Dict[str, int]] = defaultdict(lambda: {"tilexr": 0, "fallback": 0, "error": 0})
 
 
+ENV_GATE_REFERENCE = "VLLM_ASCEND_TILEXR_COLLECTIVES"      # the reference's name for the same gate: honoured too
+
+
 def enabled() -> bool:
-    return os.environ.get(ENV_GATE, "0") not in ("", "0", "false", "False")
+    return any(os.environ.get(name, "0").strip().lower() not in ("", "0", "false", "no", "off") for name in (ENV_GATE, ENV_GATE_REFERENCE))
 
 
 def _trace(msg: str) -> None:

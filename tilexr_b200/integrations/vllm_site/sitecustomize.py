@@ -10,7 +10,7 @@ def _on(name: str) -> bool:
     return os.environ.get(name, "0").strip().lower() in ("1", "true", "yes", "on")
 
 
-if _on("VLLM_TILEXR_COLLECTIVES"):
+if _on("VLLM_TILEXR_COLLECTIVES") or _on("VLLM_ASCEND_TILEXR_COLLECTIVES"):
     try:
         from tilexr_b200.integrations.vllm_collectives import autopatch
 

@@ -235,7 +235,7 @@ def stage_medians(doc: dict) -> Dict[str, dict]:
                 continue
             per_op.setdefault(op["sequence"], []).append(op["latency_us"])
             stage_of[op["sequence"]] = op["stage"]
-            nbytes[op["sequence"]] = op["algorithm_bytes"]
+            nbytes[op["sequence"]] = op.get("algorithm_bytes")
     out: Dict[str, dict] = {}
     for stage in FORWARD_STAGES + BACKWARD_STAGES:
         seqs = [s for s, st in stage_of.items() if st == stage]
