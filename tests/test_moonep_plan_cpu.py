@@ -174,3 +174,40 @@ def test_stage_tracing_and_latency_capture_from_the_environment(monkeypatch, tmp
     assert not quiet._capture.active
     quiet.forward(hidden, w, topk, None, None, lambda rows, cu, p: rows)
     assert quiet._capture.seen == 0
+
+
+def test_drop_in_buffer_accepts_the_zero_copy_and_sync_switches(monkeypatch):
+    """`zero_copy` / `inter_rank_sync` of the drop-in Buffer (reference: integrations/moonep_torch/tilexr_moonep/compat.py:264-330,
+    407-458): accepted; a zero-copy combine wants exactly the tensors of the latest zero-copy dispatch of the same plan."""
+    import torch
+    from tilexr_b200.integrations import moonep
+
+    class FakeComm:
+        rank, world_size = 0, 1
+
+        def symm_empty(self, shape, dtype):
+            return torch.zeros(shape, dtype=dtype)
+
+    plan_dict = {"dst": torch.zeros(8, dtype=torch.int32), "experts_to_copy": torch.zeros(1, 4, dtype=torch.int32), "zero_fill_ranges": torch.zeros(8, 2, dtype=torch.int32),
+                 "remote_stats": torch.zeros(2, dtype=torch.int32), "N": 8, "R": 1, "E": 4, "B": 4, "NvS": 8, "K": 2, "dup_counts": None, "status": None,
+                 "dst_local": None, "cu_seqlens": torch.zeros(8, dtype=torch.int32)}
+    monkeypatch.setattr(moonep._C, "moonep_planning", lambda *a, **k: dict(plan_dict), raising=False)
+    for name in ("moonep_dispatch", "moonep_combine"):
+        monkeypatch.setattr(moonep._C, name, lambda *a, **k: None, raising=False)
+    monkeypatch.setattr(torch.cuda, "is_available", lambda: False)
+    buf = moonep.Buffer(4, 8, 2, 4, 1, token_padding=1, comm=FakeComm(), dtype=torch.float32)
+    hidden, w, topk = torch.zeros(4, 8), torch.ones(4, 2), torch.zeros(4, 2, dtype=torch.int32)
+    rows, wn, cu, plan = buf.dispatch(hidden, w, topk, zero_copy=True, inter_rank_sync=False)
+    y, wk, ev = buf.combine(plan, rows, wn, zero_copy=True, inter_rank_sync=False)
+    assert y.shape == (4, 8) and ev is None
+    with pytest.raises(AssertionError):
+        buf.combine(plan, rows, wn, zero_copy=True)               # the aliases are used up
+    rows, wn, cu, plan = buf.dispatch(hidden, w, plan=plan, zero_copy=True)
+    with pytest.raises(AssertionError):
+        buf.combine(plan, rows.clone(), wn, zero_copy=True)       # another tensor
+    rows, wn, cu, plan = buf.dispatch(hidden, w, plan=plan, zero_copy=True)
+    with pytest.raises(AssertionError):
+        buf.combine(plan.clone(), rows, wn, zero_copy=True)       # another plan
+    buf.combine(plan, rows, wn)                                   # without the switch nothing is checked
+    buf.destroy()
+    assert buf.destroyed

@@ -550,13 +550,19 @@ class Buffer:
 
     def dispatch(self, hidden_sh, route_weights_sk=None, topk_experts_sk=None, tokens_per_expert=None, plan=None,
                  async_finish=False, *, inter_rank_sync=True, zero_copy=False):
-        if not inter_rank_sync or zero_copy:
-            raise NotImplementedError("inter_rank_sync=False and zero_copy=True are not supported")
+        """``zero_copy`` and ``inter_rank_sync`` are accepted as in the reference's drop-in (compat.py:264-330): the rows always
+        land directly in the returned tensors (there is no boundary copy to leave out), and the kernels meet their peers through
+        flags whether or not the caller asks for a synchronisation.  With ``zero_copy=True`` the returned tensors are remembered,
+        and ``combine(zero_copy=True)`` insists on getting exactly them."""
+        del inter_rank_sync
+        self._zero_copy_aliases = None
         if plan is None:
             if topk_experts_sk is None:
                 raise ValueError("a fresh dispatch needs topk_experts_sk")
             plan = self.native.planning(topk_experts_sk, tokens_per_expert)
         rows, w = self.native.dispatch(hidden_sh, route_weights_sk, plan)
+        if zero_copy:
+            self._zero_copy_aliases = (plan, rows, w)
         out = (rows, w, plan.cu_seqlens, plan)
         if async_finish:
             ev = torch.cuda.Event()
@@ -581,8 +587,14 @@ class Buffer:
         return None
 
     def combine(self, plan, hidden_nvsh, route_weights_nvs=None, async_finish=False, inter_rank_sync=True, *, zero_copy=False):
-        if not inter_rank_sync or zero_copy:
-            raise NotImplementedError("inter_rank_sync=False and zero_copy=True are not supported")
+        del inter_rank_sync
+        if zero_copy:
+            aliases = getattr(self, "_zero_copy_aliases", None)
+            if aliases is None or aliases[0] is not plan or hidden_nvsh.data_ptr() != aliases[1].data_ptr():
+                raise AssertionError("combine(zero_copy=True): hidden_nvsh must be the output of the latest zero-copy dispatch of this plan")
+            if route_weights_nvs is not None and (aliases[2] is None or route_weights_nvs.data_ptr() != aliases[2].data_ptr()):
+                raise AssertionError("combine(zero_copy=True): route_weights_nvs must be the weights of the latest zero-copy dispatch")
+        self._zero_copy_aliases = None
         # TILEXR_MOONEP_COMBINE_VERSION=2 selects the second-generation kernel (duplicates folded on the expert rank); the
         # default here is the first, whose sum is rounded once
         import os
