@@ -67,3 +67,26 @@ def test_no_build_note_names_in_sources():
         text = p.read_text()
         for b in banned:
             assert b not in text, f"{p} mentions {b}"
+
+
+def test_no_bulk_load_with_cluster_multicast():
+    # a TMA or bulk LOAD with cluster multicast may reach a peer's memory through a tensor map; none is used anywhere.
+    # (tcgen05.commit's multicast is an mbarrier arrive, not a load, and is allowed.)
+    for p in _sources(".cu", ".cuh", ".h", ".cpp", ".inc"):
+        for line in p.read_text().splitlines():
+            if "multicast::cluster" in line:
+                assert "tcgen05.commit" in line and "cp.async" not in line, f"{p}: {line.strip()}"
+
+
+def test_kernels_that_touch_a_peers_own_tensors_meet_it_first():
+    # the MoonEP kernels that write or read a peer's registered tensors (not its window) call the entry meeting before they do
+    text = (CSRC / "moonep" / "moonep_kernels.cu").read_text()
+    bodies = {name: text[text.index(f"__device__ void {name}("):] for name in ("MoonDispatchBody", "MoonPrefetchBody", "MoonReduceGradBody")}
+    for name, body in bodies.items():
+        body = body[: body.index("\n}\n")]
+        meet = body.find("MeetPeersOnEntry(")
+        touch = body.find("peerBase[")
+        assert meet >= 0 and touch >= 0 and meet < touch, name
+    # the zero-copy push of the collectives announces and waits as well
+    coll = (CSRC / "collectives" / "coll_kernels.cu").read_text()
+    assert "READY_SLOT" in coll and coll.index("READY_SLOT") < coll.index("PeerOut(a, peer")
