@@ -9,7 +9,8 @@ import pytest
 ROOT = Path(__file__).resolve().parent.parent
 INCLUDE = ROOT / "csrc" / "include"
 C_HEADERS = ["tilexr_api.h", "tilexr_collectives.h", "tilexr_collectives_perf.h", "tilexr_comm_args.h", "tilexr_ep.h", "tilexr_ep_plan.h",
-             "tilexr_fused.h", "tilexr_hostsim.h", "tilexr_moonep.h", "tilexr_noalloc.h", "tilexr_perf_trace.h", "tilexr_probes.h"]
+             "tilexr_fused.h", "tilexr_hostsim.h", "tilexr_moonep.h", "tilexr_moonep_planner.h", "tilexr_moonep_combine_v2.h", "tilexr_moonep_trace.h",
+             "tilexr_noalloc.h", "tilexr_perf_trace.h", "tilexr_probes.h", "tilexr_types.h"]
 
 
 @pytest.mark.parametrize("header", C_HEADERS)
