@@ -426,4 +426,106 @@ int TileXRHostEpCombine(const float *expertOut, const int32_t *assist, int32_t r
     return End(c);
 }
 
+// ---- MoonEP stages by plan (fp32 rows) ---------------------------------------------------------------------------------------
+// dst[i] = r * nvS + row for route i of this rank (token i / topK), negative = the route sends nothing; dstLocal[row] >= 0 marks
+// the rows of this rank that some route fills.  Rows and their route weights land in the destination's window; one flag per
+// source says "all my rows for you are there"; filled rows are copied out, the others are zero.
+int TileXRHostMoonDispatch(const float *hidden, const float *routeWeights, const int32_t *dst, const int32_t *dstLocal, int64_t routes,
+                           int64_t topK, int64_t h, int64_t nvS, float *hiddenOut, float *weightsOut, TileXRCommPtr comm)
+{
+    if (hidden == nullptr || dst == nullptr || dstLocal == nullptr || hiddenOut == nullptr || routes <= 0 || topK <= 0 || h <= 0 || nvS <= 0) {
+        return TILEXR_ERROR_PARA_CHECK_FAIL;
+    }
+    if ((routeWeights == nullptr) != (weightsOut == nullptr)) return TILEXR_ERROR_PARA_CHECK_FAIL;
+    HostCtx c;
+    int ret = Begin(comm, TILEXR_OP_MOONEP_DISPATCH, routes, &c);
+    if (ret != TILEXR_SUCCESS) return ret;
+    const uint64_t rowBytes = static_cast<uint64_t>(h) * sizeof(float);
+    const uint64_t weightOff = static_cast<uint64_t>(nvS) * rowBytes;
+    if (weightOff + static_cast<uint64_t>(nvS) * sizeof(float) > c.args->dataHalfBytes) {
+        TILEXR_LOG(ERROR) << "host MoonEP dispatch needs " << weightOff + nvS * sizeof(float) << " window bytes, have " << c.args->dataHalfBytes;
+        return TILEXR_ERROR_PARA_CHECK_FAIL;
+    }
+    for (int64_t i = 0; i < routes && c.w.ok(); ++i) {
+        const int32_t raw = dst[i];
+        if (raw < 0) continue;
+        const int dstRank = static_cast<int>(raw / nvS);
+        const int64_t row = raw - static_cast<int64_t>(dstRank) * nvS;
+        if (dstRank >= c.R) {
+            RaiseFailure(c.w, TILEXR_DEV_BAD_ARGUMENT, c.rank, i, static_cast<uint64_t>(c.R), static_cast<uint64_t>(raw));
+            return End(c);
+        }
+        uint8_t *half = DataHalf(c.args, dstRank, c.epoch);
+        WindowStore(half + row * rowBytes, hidden + (i / topK) * h, rowBytes);
+        if (routeWeights != nullptr) WindowStore(half + weightOff + row * sizeof(float), routeWeights + i, sizeof(float));
+    }
+    if (!g_skipFlags) {
+        for (int p = 0; p < c.R; ++p) {
+            SetFlag(FlagSlot(c.args, p, TILEXR_FLAG_OP_BASE + static_cast<int64_t>(c.rank) * TILEXR_FLAGS_PER_PAIR), c.epoch, 1);
+        }
+    }
+    for (int s = 0; s < c.R; ++s) {
+        const int64_t slot = TILEXR_FLAG_OP_BASE + static_cast<int64_t>(s) * TILEXR_FLAGS_PER_PAIR;
+        if (!WaitFlagGE(c.w, FlagSlot(c.args, c.rank, slot), 1, s, slot)) return End(c);
+    }
+    const uint8_t *half = DataHalf(c.args, c.rank, c.epoch);
+    for (int64_t row = 0; row < nvS; ++row) {
+        if (dstLocal[row] >= 0) {
+            WindowLoad(hiddenOut + row * h, half + row * rowBytes, rowBytes);
+            if (weightsOut != nullptr) WindowLoad(weightsOut + row, half + weightOff + row * sizeof(float), sizeof(float));
+        } else {
+            std::fill(hiddenOut + row * h, hiddenOut + (row + 1) * h, 0.f);
+            if (weightsOut != nullptr) weightsOut[row] = 0.f;
+        }
+    }
+    return End(c);
+}
+
+// Combine: dstLocal[row] = source rank * routesPerRank + route for the rows this rank holds (negative: padding).  Every row goes
+// back to its source's window at its route's position behind a flag per route; the source adds a token's topK rows in route
+// order in fp32.  Route weights travel back unchanged when given.
+int TileXRHostMoonCombine(const float *rows, const float *weightsNvs, const int32_t *dstLocal, const int32_t *dst, int64_t nvS, int64_t tokens,
+                          int64_t topK, int64_t h, float *hiddenOut, float *weightsOut, TileXRCommPtr comm)
+{
+    if (rows == nullptr || dstLocal == nullptr || dst == nullptr || hiddenOut == nullptr || nvS <= 0 || tokens <= 0 || topK <= 0 || h <= 0) {
+        return TILEXR_ERROR_PARA_CHECK_FAIL;
+    }
+    HostCtx c;
+    int ret = Begin(comm, TILEXR_OP_MOONEP_COMBINE, tokens, &c);
+    if (ret != TILEXR_SUCCESS) return ret;
+    const int64_t routes = tokens * topK;
+    const uint64_t rowBytes = static_cast<uint64_t>(h) * sizeof(float);
+    const uint64_t weightOff = static_cast<uint64_t>(routes) * rowBytes;
+    if (weightOff + static_cast<uint64_t>(routes) * sizeof(float) > c.args->dataHalfBytes || routes > TILEXR_FLAG_SLOT_SLOTS) return TILEXR_ERROR_PARA_CHECK_FAIL;
+    for (int64_t row = 0; row < nvS; ++row) {
+        const int32_t v = dstLocal[row];
+        if (v < 0) continue;
+        const int src = static_cast<int>(v / routes);
+        const int64_t route = v - static_cast<int64_t>(src) * routes;
+        if (src >= c.R) continue;
+        uint8_t *half = DataHalf(c.args, src, c.epoch);
+        WindowStore(half + route * rowBytes, rows + row * h, rowBytes);
+        if (weightsNvs != nullptr) WindowStore(half + weightOff + route * sizeof(float), weightsNvs + row, sizeof(float));
+        if (!g_skipFlags) SetFlag(FlagSlot(c.args, src, TILEXR_FLAG_SLOT_BASE + route), c.epoch, 1);
+    }
+    const uint8_t *half = DataHalf(c.args, c.rank, c.epoch);
+    for (int64_t t = 0; t < tokens && c.w.ok(); ++t) {
+        float *y = hiddenOut + t * h;
+        std::fill(y, y + h, 0.f);
+        for (int64_t k = 0; k < topK; ++k) {
+            const int64_t route = t * topK + k;
+            const int32_t raw = dst[route];
+            if (weightsOut != nullptr) weightsOut[route] = 0.f;
+            if (raw < 0) continue;
+            const int producer = static_cast<int>(raw / nvS);
+            if (!WaitFlagGE(c.w, FlagSlot(c.args, c.rank, TILEXR_FLAG_SLOT_BASE + route), 1, producer, route)) break;
+            const float *row = reinterpret_cast<const float *>(half + route * rowBytes);
+            WindowRead(row, rowBytes);
+            for (int64_t j = 0; j < h; ++j) y[j] += row[j];
+            if (weightsOut != nullptr) weightsOut[route] = reinterpret_cast<const float *>(half + weightOff)[route];
+        }
+    }
+    return End(c);
+}
+
 } // extern "C"

@@ -31,6 +31,14 @@ int TileXRHostEpCombine(const float *expertOut, const int32_t *assist, int32_t r
                         const float *expertScales, int64_t bs, int64_t h, int64_t topK, int64_t moeExpertNum, float *yOut,
                         TileXRCommPtr comm);
 
+// MoonEP dispatch and combine by plan on fp32 rows (plan tables as in tilexr_moonep.h: dst[i] = rank * nvS + row, dstLocal[row] =
+// source rank * routes + route, negative where no route fills the row).  Dispatch delivers rows and route weights and leaves zeros
+// in the rows nobody fills; Combine returns every row to its source, which adds a token's topK rows in route order.
+int TileXRHostMoonDispatch(const float *hidden, const float *routeWeights, const int32_t *dst, const int32_t *dstLocal, int64_t routes,
+                           int64_t topK, int64_t h, int64_t nvS, float *hiddenOut, float *weightsOut, TileXRCommPtr comm);
+int TileXRHostMoonCombine(const float *rows, const float *weightsNvs, const int32_t *dstLocal, const int32_t *dst, int64_t nvS, int64_t tokens,
+                          int64_t topK, int64_t h, float *hiddenOut, float *weightsOut, TileXRCommPtr comm);
+
 // Test hook: the next host kernel of this process skips raising its flags, so that peers run
 // into their wait budget (failure-detection tests make the failure on the host).
 int TileXRHostInjectSkipFlags(int enable);

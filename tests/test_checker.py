@@ -92,7 +92,7 @@ def test_installed_traces_are_recorded_judged_and_covered(tmp_path):
     from tilexr_b200.tools import checker
 
     names = {m["name"] for m in checker.load_manifests()}
-    assert {"host_all_gather", "host_all_reduce", "host_ep_dispatch_combine"} <= names
+    assert {"host_all_gather", "host_all_reduce", "host_ep_dispatch_combine", "host_moonep_stages"} <= names
     for m in checker.load_manifests():
         assert m["recipe"] in checker.RECIPES and m["ranks"] >= 2 and m["required_event_coverage"]
     rows = checker.verify_installed_traces("host_all_reduce", keep_dir=str(tmp_path))
@@ -109,6 +109,9 @@ def test_installed_traces_are_recorded_judged_and_covered(tmp_path):
         checker.load_manifests("no_such_trace")
     with pytest.raises(ValueError):
         checker.record_installed_trace("no_such_recipe", 2, str(tmp_path / "x"))
+    # the MoonEP stages by plan between three processes: two plans over the same windows
+    rows = checker.verify_installed_traces("host_moonep_stages")
+    assert len(rows) == 1 and rows[0]["ok"] and rows[0]["ranks"] == 3 and rows[0]["findings"] == [], rows
 
 
 def test_zero_copy_gather_needs_the_entry_meeting():

@@ -1,6 +1,7 @@
 """MoonEP harness on the CPU: the torch reference backend over gloo, the correctness runner's verdicts, plan
 invariants, the HMAC completion barrier and the route capture format."""
 import dataclasses
+import os
 import threading
 
 import pytest
@@ -67,6 +68,74 @@ def test_reference_backend_and_runner_verdicts_over_gloo():
         failing = [s["stage"] for s in bad["stages"] if not s["ok"]]
         assert failing == (["combined_hidden"] if rank == 1 else [])
         assert [s["stage"] for s in scribble["stages"] if not s["ok"]] == ["inputs_immutable"]
+
+
+def _host_backend_worker(rank, world, port, q):
+    try:
+        os.environ["MASTER_ADDR"] = "127.0.0.1"
+        os.environ["MASTER_PORT"] = str(port)
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        import tilexr_b200 as txr
+        from tilexr_b200.tools.moonep.case_factory import load_cases, make_inputs
+        from tilexr_b200.tools.moonep.correctness import CorrectnessRunner
+        from tilexr_b200.tools.moonep.host_backend import HostMemoryBackend
+        from tilexr_b200.tools.moonep.torch_reference_backend import TorchReferenceBackend
+
+        comm = txr.init_from_torch_distributed(host_memory=True, buffer_mb=32)
+        case = [c for c in load_cases("smoke") if c.ranks == world][0]
+        backend = HostMemoryBackend(comm)
+        runner = CorrectnessRunner(TorchReferenceBackend(), backend)
+        first = runner.run_case(case)
+        again = runner.run_case(dataclasses.replace(case, seed=case.seed + 5))      # other routing, same windows: both halves, the reuse guard
+        padded = runner.run_case(dataclasses.replace(case, token_padding=4, seed=9))
+        # an expert function between dispatch and combine: the sum is of what the experts returned
+        inputs = make_inputs(case, rank)
+        art = backend.run(case, inputs, expert_fn=lambda rows, plan: rows * 2)
+        doubled = torch.equal(art.combined_hidden.float(), (backend.run(case, inputs).combined_hidden.float() * 2))
+        # a rank that raises no flag: the others' dispatch ends with a status instead of waiting for ever
+        status = None
+        if world > 1:
+            comm.set_wait_timeout_ms(300)
+            dist.barrier()
+            if rank == 0:
+                # one launch without flags and nothing after it (flags are compared with >=: a later launch's flags would
+                # release the waiting ranks)
+                txr._C.host_inject_skip_flags(True)
+                backend._all_gather(inputs.topk_experts_sk.to(torch.int32))
+                status = "withheld"
+            else:
+                try:
+                    backend.run(case, inputs)
+                    status = "finished"
+                except RuntimeError as e:
+                    status = str(e)
+        q.put((rank, first, again, padded, doubled, status))
+        dist.destroy_process_group()
+    except Exception:
+        import traceback
+
+        q.put((rank, traceback.format_exc(), None, None, None, None))
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_host_memory_backend_matches_the_reference_backend(world):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = free_port()
+    procs = [ctx.Process(target=_host_backend_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = sorted((q.get(timeout=240) for _ in procs), key=lambda r: r[0])
+    for p in procs:
+        p.join(timeout=30)
+    for rank, first, again, padded, doubled, status in results:
+        assert isinstance(first, dict), first
+        for verdict in (first, again, padded):
+            assert verdict["ok_all_ranks"], [s for s in verdict["stages"] if not s["ok"]]
+        assert doubled
+    # every rank but the one that withheld its flags reports the wait that ran out
+    assert results[0][5] == "withheld"
+    assert all("timeout" in r[5] for r in results[1:]), [r[5] for r in results]
 
 
 def test_plan_invariants_hold_for_reference_plans_and_catch_a_collision():
@@ -434,3 +503,28 @@ def test_model_flow_documents_compare_stage_by_stage(tmp_path):
     bad.write_text("{}")
     with pytest.raises(ValueError):
         mf.load_document(str(bad))
+
+
+def test_orchestrator_script_runs_the_correctness_mode_on_host_memory(tmp_path):
+    """`run_moonep.sh N OUT smoke host`: two gloo ranks, the stages through host-memory windows, the verdict table written.  Also
+    keeps the script itself sound: every line outside its comments must parse, and nothing runs before the arguments are read."""
+    import pathlib
+    import subprocess
+    import sys
+
+    script = pathlib.Path(__file__).resolve().parents[1] / "tilexr_b200" / "tools" / "run_moonep.sh"
+    text = script.read_text().splitlines()
+    first_command = next(i for i, line in enumerate(text) if line.strip() and not line.startswith("#"))
+    assert text[first_command].strip() == "set -u"
+    assert subprocess.run(["bash", "-n", str(script)]).returncode == 0
+    env = dict(os.environ, PATH=str(pathlib.Path(sys.executable).parent) + os.pathsep + os.environ.get("PATH", ""),
+               PYTHONPATH=str(script.parents[2]) + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    r = subprocess.run(["bash", str(script), "2", str(tmp_path), "smoke", "host"], env=env, cwd=str(script.parents[2]), capture_output=True, text=True,
+                       timeout=600)
+    table = (tmp_path / "correctness.md").read_text()
+    assert r.returncode == 0, (r.stdout, r.stderr, (tmp_path / "correctness.err").read_text()[-2000:])
+    assert "| smoke_r2 | 0 | pass | - |" in table
+    import json
+
+    rows = json.loads((tmp_path / "correctness.json").read_text())
+    assert rows and all(x["ok_all_ranks"] for x in rows)

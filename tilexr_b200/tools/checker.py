@@ -98,8 +98,22 @@ def _recipe_exchange(txr, comm, rank, world):
         txr._C.host_broadcast(comm, b, root, 4096)
 
 
+def _recipe_moonep(txr, comm, rank, world):
+    import dataclasses
+
+    from .moonep.case_factory import make_inputs
+    from .moonep.contracts import MoonEPCase
+    from .moonep.host_backend import HostMemoryBackend
+
+    case = MoonEPCase(name="trace", ranks=world, tokens=16, hidden=32, top_k=2, experts=4 * world, prefetch_slots=2, token_padding=2, ffn=4, seed=3)
+    backend = HostMemoryBackend(comm, tile_bytes=4096)
+    for launch in range(2):                  # two plans over the same windows: both data halves, the reuse guard, rows left from the plan before
+        c = dataclasses.replace(case, seed=case.seed + launch)
+        backend.run(c, make_inputs(c, rank))
+
+
 RECIPES = {"host_all_gather": _recipe_all_gather, "host_all_reduce": _recipe_all_reduce, "host_ep_dispatch_combine": _recipe_ep,
-           "host_all_to_all_reduce_scatter_broadcast": _recipe_exchange}
+           "host_all_to_all_reduce_scatter_broadcast": _recipe_exchange, "host_moonep_stages": _recipe_moonep}
 
 
 def _trace_worker(rank: int, world: int, port: int, recipe: str, out_dir: str, errors) -> None:

@@ -45,6 +45,9 @@ def main(argv=None) -> int:
                     help="benchmark: also time dispatch and combine as a torch + NCCL program (index_select, all_to_all_single with the plan's splits, index_add_)")
     ap.add_argument("--dump", default="", help="correctness: directory for both sides' stage tensors (compare offline with tools.moonep.tensor_dump)")
     ap.add_argument("--trace", action="store_true", help="benchmark: also record the dispatch kernel's event trace once per case and print its phases")
+    ap.add_argument("--backend", choices=["device", "host"], default="device",
+                    help="correctness: 'host' runs the stages on a host-memory communicator (gloo ranks, no GPU): the same windows, flags and "
+                         "launch epochs with memcpy for the copies")
     ap.add_argument("--buffer-mb", type=int, default=0, help="communicator window size (default: sized for the largest case)")
     args = ap.parse_args(argv)
 
@@ -74,7 +77,11 @@ def main(argv=None) -> int:
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
+    host = args.backend == "host"
+    if host and args.mode != "correctness":
+        ap.error("--backend host runs the correctness mode only")
+    if not host:
+        torch.cuda.set_device(local)
     buffer_mb = args.buffer_mb
     if buffer_mb <= 0:
         # two halves, each holding the K rows per token that a combine receives, of the largest case that will run
@@ -83,9 +90,14 @@ def main(argv=None) -> int:
             for c in select_cases(load_cases(args.cases), args.case_ids):
                 if c.ranks == world:
                     c = apply_overrides(c, overrides_from_args(args))
-                    need = c.nvs * c.hidden * 2 + c.nvs * 4
+                    need = c.nvs * c.hidden * (4 if host else 2) + c.nvs * 4
                     buffer_mb = max(buffer_mb, int(2 * need / (1 << 20)) + 64)
-    if world > 1:
+    if host:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", str(29700 + os.getpid() % 200))
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        comm = txr.init_from_torch_distributed(host_memory=True, buffer_mb=buffer_mb)
+    elif world > 1:
         dist.init_process_group("nccl")
         comm = txr.init_from_torch_distributed(buffer_mb=buffer_mb)
     else:
@@ -113,7 +125,13 @@ def main(argv=None) -> int:
                 if rank == 0:
                     print(model_flow.markdown(doc))
         elif args.mode == "correctness":
-            runner = CorrectnessRunner(TorchReferenceBackend(), TileXRBackend(comm), device="cpu", dump_dir=args.dump)
+            if host:
+                from .host_backend import HostMemoryBackend
+
+                candidate = HostMemoryBackend(comm)
+            else:
+                candidate = TileXRBackend(comm)
+            runner = CorrectnessRunner(TorchReferenceBackend(), candidate, device="cpu", dump_dir=args.dump)
             for c in cases:
                 r = runner.run_case(c)
                 results.append(r)
@@ -150,7 +168,7 @@ def main(argv=None) -> int:
         port = int(os.environ.get("MASTER_PORT", "29500")) + 17
         completion_barrier(rank, world, os.environ.get("MASTER_ADDR", "127.0.0.1"), port, key, f"done-{args.mode}")
     comm.destroy()
-    if world > 1:
+    if dist.is_initialized():
         dist.destroy_process_group()
     return 1 if failed else 0
 
