@@ -26,7 +26,7 @@ EXTRA_OPS = ("all_to_all_transpose",)      # not part of --op all
 TRANSPOSE_BURST = 512                      # elements of one row that go to one peer
 
 
-def parse():
+def parse(argv=None):
     p = argparse.ArgumentParser()
     p.add_argument("--op", default="all_gather", choices=OPS + EXTRA_OPS + ("all",))
     p.add_argument("--min-bytes", type=int, default=4096)
@@ -42,7 +42,9 @@ def parse():
     p.add_argument("--csv", default="")
     p.add_argument("--min-algbw", type=float, default=0.0)
     p.add_argument("--max-latency-us", type=float, default=0.0)
-    return p.parse_args()
+    p.add_argument("--comm-mode", default="device", choices=["device", "host"],
+                   help="host: the same sweep on a host-memory communicator under gloo (fp32, wall-clock times): the plumbing without a GPU")
+    return p.parse_args(argv)
 
 
 def message_elems(op: str, nbytes: int, world: int, esize: int):
@@ -117,8 +119,118 @@ def time_launches(fn, iters, warmup):
     return [float(v) for v in t.tolist()]
 
 
-def main():
-    args = parse()
+def pattern(src: int, n: int) -> torch.Tensor:
+    """Rank `src`'s input: small integers in fp32, so that every sum is exact and a misplaced element shows its origin."""
+    i = torch.arange(n, dtype=torch.int64)
+    return ((i * 7 + src * 13) % 251 - 125).to(torch.float32)
+
+
+def expected_host(op: str, world: int, rank: int, n_in: int) -> torch.Tensor:
+    """What `rank` must hold after `op` when every rank s sends pattern(s, n_in) (root 0 for the broadcast)."""
+    ins = [pattern(s, n_in) for s in range(world)]
+    if op == "all_gather":
+        return torch.cat(ins)
+    if op == "all_to_all":
+        c = n_in // world
+        return torch.cat([ins[s][rank * c:(rank + 1) * c] for s in range(world)])
+    total = torch.stack(ins).sum(0)
+    if op == "all_reduce":
+        return total
+    if op == "reduce_scatter":
+        c = n_in // world
+        return total[rank * c:(rank + 1) * c]
+    return ins[0]
+
+
+def main_host(args) -> int:
+    """The sweep on host-memory windows: the host kernels on the production flag primitives between gloo ranks, checked against
+    the pattern; times are wall clock around each launch (max over ranks of the average), which says how the plumbing behaves,
+    not how a GPU would."""
+    import time
+
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29555")
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    import tilexr_b200 as txr
+
+    comm = txr.init_from_torch_distributed(host_memory=True, buffer_mb=min(args.buffer_mb, 256))
+    C = txr._C
+    tile = 16384
+    ops = [o for o in (OPS if args.op == "all" else (args.op,))]
+    if any(o in EXTRA_OPS for o in ops):
+        raise SystemExit("--comm-mode host has the five plain collectives")
+    rows, failures = [], 0
+    if rank == 0:
+        print(f"# ranks {world}  host memory, fp32  iters {args.iters}")
+        print(f"# {'op':<15}{'bytes':>12}{'avg us':>10}{'min us':>10}{'max us':>10}{'algbw GB/s':>12}{'busbw GB/s':>12}{'errors':>8}")
+    # the window holds one slice per source and at most 1024 tiles per pair
+    limit = min(((comm.data_half_bytes // max(world, 1)) & ~255), 1024 * tile)
+    for op in ops:
+        size = args.min_bytes
+        while size <= args.max_bytes:
+            n_in, n_out = message_elems(op, size, world, 4)
+            per_pair = (n_in if op in ("all_gather", "all_reduce", "broadcast") else n_in // world) * 4      # bytes one source leaves in one window
+            if per_pair > limit:
+                break
+            x = pattern(rank, n_in)
+
+            def launch():
+                if op == "all_gather":
+                    out = torch.empty(n_out)
+                    C.host_all_gather(comm, x, out, tile)
+                    return out
+                if op == "all_to_all":
+                    return C.host_all_to_all(comm, x, tile)
+                if op == "all_reduce":
+                    return C.host_all_reduce(comm, x)
+                if op == "reduce_scatter":
+                    return C.host_reduce_scatter(comm, x)
+                b = x.clone() if rank == 0 else torch.zeros(n_in)
+                C.host_broadcast(comm, b, 0, tile)
+                return b
+
+            errors = 0
+            if args.check:
+                errors = int((launch() != expected_host(op, world, rank, n_in)).sum())
+            for _ in range(args.warmup_iters):
+                launch()
+            dist.barrier()
+            times = []
+            for _ in range(args.iters):
+                t0 = time.perf_counter()
+                launch()
+                times.append((time.perf_counter() - t0) * 1e6)
+            t = torch.tensor([sum(times) / len(times), min(times), max(times), float(errors)], dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            avg, mn, mx, errors = float(t[0]), float(t[1]), float(t[2]), int(t[3])
+            out_bytes = n_out * 4
+            algbw = out_bytes / avg / 1000.0
+            busbw = algbw * (world - 1) / world
+            failures += errors
+            rows.append([op, world, size, out_bytes, avg, mn, mx, algbw, busbw, float("nan"), float("nan"), float("nan"), errors])
+            if rank == 0:
+                print(f"  {op:<15}{size:>12}{avg:>10.1f}{mn:>10.1f}{mx:>10.1f}{algbw:>12.2f}{busbw:>12.2f}{errors:>8}", flush=True)
+            size *= args.step_factor
+    if rank == 0 and args.csv:
+        write_csv(args.csv, rows)
+    comm.destroy()
+    dist.destroy_process_group()
+    return 1 if failures else 0
+
+
+def write_csv(path: str, rows) -> None:
+    with open(path, "w", newline="") as f:
+        wr = csv.writer(f)
+        wr.writerow(["op", "ranks", "bytes_per_rank", "output_bytes", "avg_us", "min_us", "max_us", "algbw_GBps",
+                     "busbw_GBps", "nccl_avg_us", "nccl_busbw_GBps", "speedup_vs_nccl", "errors"])
+        wr.writerows(rows)
+
+
+def main(argv=None):
+    args = parse(argv)
+    if args.comm_mode == "host":
+        return main_host(args)
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -192,11 +304,7 @@ def main():
             del x, out
             size *= args.step_factor
     if rank == 0 and args.csv:
-        with open(args.csv, "w", newline="") as f:
-            wr = csv.writer(f)
-            wr.writerow(["op", "ranks", "bytes_per_rank", "output_bytes", "avg_us", "min_us", "max_us", "algbw_GBps",
-                         "busbw_GBps", "nccl_avg_us", "nccl_busbw_GBps", "speedup_vs_nccl", "errors"])
-            wr.writerows(rows)
+        write_csv(args.csv, rows)
     comm.destroy()
     dist.destroy_process_group()
     return 1 if failures else 0
