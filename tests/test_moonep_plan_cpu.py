@@ -211,3 +211,41 @@ def test_drop_in_buffer_accepts_the_zero_copy_and_sync_switches(monkeypatch):
     buf.combine(plan, rows, wn)                                   # without the switch nothing is checked
     buf.destroy()
     assert buf.destroyed
+
+
+def test_plan_file_round_trip_and_checks(tmp_path):
+    """A plan saved after planning dispatches again later without planning: every table survives the file, a plan made for
+    another shape or a cut table is refused."""
+    import dataclasses
+
+    from tilexr_b200.integrations.moonep import MoonEPCommPlan, TileXRMoonEPError
+    from tilexr_b200.tools.moonep.case_factory import load_cases, routing
+    from tilexr_b200.tools.moonep.planner_reference import dst_local_from_plans, reference_plan
+
+    case = [c for c in load_cases("smoke") if c.ranks == 2][0]
+    topk = [routing(case, r) for r in range(case.ranks)]
+    raw = [reference_plan(case, topk, r) for r in range(case.ranks)]
+    p = raw[0]
+    plan = MoonEPCommPlan(p["dst"].to(torch.int32), p["experts_to_copy"].to(torch.int32), p["zero_fill_ranges"], p["remote_stats"], case.routes, case.ranks,
+                          case.experts, case.prefetch_slots, case.nvs, case.top_k, dup_groups=torch.arange(6, dtype=torch.int32),
+                          dup_loffs=torch.arange(3, dtype=torch.int32), dup_counts=torch.tensor([3], dtype=torch.int32),
+                          status=torch.zeros(4, dtype=torch.int32), dst_local=dst_local_from_plans(case, [x["dst"] for x in raw], 0).to(torch.int32),
+                          cu_seqlens=p.get("cu_seqlens"))
+    path = str(tmp_path / "plan.pt")
+    plan.save(path)
+    shape = {"N": case.routes, "R": case.ranks, "E": case.experts, "B": case.prefetch_slots, "NvS": case.nvs, "K": case.top_k}
+    back = MoonEPCommPlan.load(path, expect=shape)
+    for f in dataclasses.fields(MoonEPCommPlan):
+        a, b = getattr(plan, f.name), getattr(back, f.name)
+        assert (a is None and b is None) or (torch.equal(a, b) and a.dtype == b.dtype) if isinstance(a, torch.Tensor) or a is None else a == b, f.name
+    assert MoonEPCommPlan.load(path, device="cpu").dst.device.type == "cpu"
+    with pytest.raises(TileXRMoonEPError, match="K = 2"):
+        MoonEPCommPlan.load(path, expect=dict(shape, K=4))
+    cut = plan.clone()
+    cut.dst = cut.dst[:-1]
+    cut.save(path)
+    with pytest.raises(TileXRMoonEPError, match="table dst"):
+        MoonEPCommPlan.load(path)
+    torch.save({"version": 99}, path)
+    with pytest.raises(TileXRMoonEPError, match="version"):
+        MoonEPCommPlan.load(path)

@@ -58,6 +58,41 @@ class MoonEPCommPlan:
                               d["B"], d["NvS"], d["K"], None, None, d["dup_counts"], d["status"], d["dst_local"], d["cu_seqlens"])
 
 
+    # -- a plan on disk: the routing of a step, to dispatch again later without planning (a plan holds no pointers) -----------
+    _TENSORS = ("dst", "experts_to_copy", "zero_fill_ranges", "remote_stats", "dup_groups", "dup_loffs", "dup_counts", "status", "dst_local",
+                "cu_seqlens")
+    _SHAPE = ("N", "R", "E", "B", "NvS", "K")
+    FILE_VERSION = 1
+
+    def save(self, path: str) -> None:
+        """Writes every table of the plan (on the CPU) and its shape.  Wait for the planning kernel first: the tables are read
+        as they are."""
+        doc = {"version": self.FILE_VERSION, "shape": {k: int(getattr(self, k)) for k in self._SHAPE},
+               "tensors": {k: (None if getattr(self, k) is None else getattr(self, k).detach().cpu()) for k in self._TENSORS}}
+        torch.save(doc, path)
+
+    @classmethod
+    def load(cls, path: str, device=None, expect: Optional[dict] = None) -> "MoonEPCommPlan":
+        """Reads a plan written by `save`, checks that its tables have the sizes its shape implies and, with `expect`
+        (a dict of N / R / E / B / NvS / K), that it was made for this buffer; moves the tables to `device`."""
+        doc = torch.load(path, map_location="cpu", weights_only=True)
+        if not isinstance(doc, dict) or doc.get("version") != cls.FILE_VERSION:
+            raise TileXRMoonEPError(f"{path}: not a plan file of version {cls.FILE_VERSION}")
+        shape, t = doc["shape"], doc["tensors"]
+        for k, want in (expect or {}).items():
+            if int(shape[k]) != int(want):
+                raise TileXRMoonEPError(f"{path}: the plan was made for {k} = {shape[k]}, this buffer has {want}")
+        sizes = {"dst": shape["N"], "experts_to_copy": shape["R"] * shape["B"], "dst_local": shape["NvS"]}
+        for k, n in sizes.items():
+            if t.get(k) is not None and t[k].numel() != n:
+                raise TileXRMoonEPError(f"{path}: table {k} has {t[k].numel()} entries, its shape implies {n}")
+        if t.get("dst") is None or t.get("experts_to_copy") is None:
+            raise TileXRMoonEPError(f"{path}: the plan has no destination table")
+        move = (lambda x: x) if device is None else (lambda x: None if x is None else x.to(device))
+        return cls(*[move(t.get(k)) for k in ("dst", "experts_to_copy", "zero_fill_ranges", "remote_stats")], *[int(shape[k]) for k in cls._SHAPE],
+                   *[move(t.get(k)) for k in ("dup_groups", "dup_loffs", "dup_counts", "status", "dst_local", "cu_seqlens")])
+
+
 class TileXRMoonEPError(RuntimeError):
     """A native MoonEP call refused its arguments or a stage failed on the device."""
 
