@@ -91,3 +91,46 @@ def test_two_level_dispatch_and_combine_match_a_dense_mixture(world, local):
         p.join(timeout=30)
     for rank, status in results:
         assert status == "ok", f"rank {rank}: {status}"
+
+
+def test_device_adapter_calls_the_ep_ops_with_their_own_signature(monkeypatch):
+    """`DeviceEpOps` cannot run without a GPU; its calls are bound against the real signatures of `ops.ep.dispatch` / `combine`
+    and it must read fields that `DispatchResult` has."""
+    import dataclasses
+    import inspect
+
+    from tilexr_b200.ops import ep
+    from tilexr_b200.parallel.hierarchical_ep import DeviceEpOps
+
+    real_dispatch, real_combine = inspect.signature(ep.dispatch), inspect.signature(ep.combine)
+    seen = {}
+
+    def fake_dispatch(*args, **kwargs):
+        bound = real_dispatch.bind(*args, **kwargs)
+        seen["dispatch"] = bound.arguments
+        x, ids = bound.arguments["x"], bound.arguments["expert_ids"]
+        rows = bound.arguments["max_recv_rows"]
+        empty = torch.zeros(0)
+        fields = {f.name: empty for f in dataclasses.fields(ep.DispatchResult)}
+        fields.update(expand_x=torch.zeros(rows, x.shape[1]), expert_token_nums=torch.tensor([2, 1]), recv_total=torch.tensor([3], dtype=torch.int32),
+                      topk_ids=ids, bs=x.shape[0], top_k=bound.arguments["top_k"], num_experts=bound.arguments["num_experts"], dedup=False,
+                      shared_expert_num=0, shared_expert_rank_num=0, tp_world_size=1)
+        return ep.DispatchResult(**fields)
+
+    def fake_combine(*args, **kwargs):
+        bound = real_combine.bind(*args, **kwargs)
+        seen["combine"] = bound.arguments
+        return torch.ones(bound.arguments["d"].bs, bound.arguments["expert_out"].shape[1])
+
+    monkeypatch.setattr(ep, "dispatch", fake_dispatch)
+    monkeypatch.setattr(ep, "combine", fake_combine)
+    ops = DeviceEpOps()
+    rows, ids = torch.randn(5, 8), torch.tensor([[0], [1], [3], [-1], [2]], dtype=torch.int32)
+    h = ops.dispatch("comm", rows, ids, 4, 10)
+    assert h.recv_total == 3 and h.expand_x.shape == (10, 8) and int(h.expert_token_nums.sum()) == 3
+    d = seen["dispatch"]
+    assert d["comm"] == "comm" and d["top_k"] == 1 and d["num_experts"] == 4 and d["max_recv_rows"] == 10 and d["dedup"] is False
+    y = ops.combine("comm", torch.zeros(10, 8), h)
+    assert y.shape == (5, 8)
+    c = seen["combine"]
+    assert c["d"] is h.state and c["expert_scales"].shape == (5, 1) and c["expert_scales"].dtype == torch.float32
