@@ -528,3 +528,25 @@ def test_orchestrator_script_runs_the_correctness_mode_on_host_memory(tmp_path):
 
     rows = json.loads((tmp_path / "correctness.json").read_text())
     assert rows and all(x["ok_all_ranks"] for x in rows)
+
+
+def test_dispatch_hot_loop_on_host_memory(tmp_path):
+    """Repeated exact and alternating plans through host-memory windows between two gloo ranks: every launch's rows and route
+    weights equal what the plans say, rows that the other plan filled are zero again."""
+    import json
+    import pathlib
+    import subprocess
+    import sys
+
+    root = pathlib.Path(__file__).resolve().parents[1]
+    out = tmp_path / "hot.json"
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nproc-per-node", "2", "--master-addr", "127.0.0.1", "--master-port", str(free_port()),
+           "-m", "tilexr_b200.tools.moonep.dispatch_hot_loop", "--backend", "host", "--cases", "smoke", "--iters", "6", "--check-every", "1",
+           "--json", str(out)]
+    env = dict(os.environ, PYTHONPATH=str(root) + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    r = subprocess.run(cmd, cwd=str(root), env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    doc = json.loads(out.read_text())
+    assert len(doc) == 1 and doc[0]["ok"] and doc[0]["case"] == "smoke_r2" and len(doc[0]["ranks"]) == 2
+    for rank in doc[0]["ranks"]:
+        assert rank["failures"] == [] and rank["device_status"] == 0 and rank["latency_us"]["count"] == 12 and rank["bytes"] > 0

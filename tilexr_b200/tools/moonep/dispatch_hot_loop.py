@@ -158,6 +158,69 @@ def run_case(comm, case: MoonEPCase, mode: str = "pair", iters: int = 100, warmu
             "failures": failures[:8], "latency_us": lat, "bytes": nbytes, "gbps_at_p50": 0.0 if lat["p50"] <= 0 else nbytes / lat["p50"] / 1e3}
 
 
+def run_case_host(comm, case: MoonEPCase, mode: str = "pair", iters: int = 20, check_every: int = 1) -> Dict[str, object]:
+    """The repeated-exact and alternating-plans checks on a host-memory communicator (gloo ranks, no GPU): the rows travel
+    through the same windows, flags and launch epochs, a launch every time into fresh outputs that the kernel fills or
+    zeroes.  Latencies are wall clock around the launch."""
+    import time
+
+    from ... import _C
+    from .case_factory import make_inputs, routing
+    from .host_backend import HostMemoryBackend
+    from .planner_reference import dst_local_from_plans, reference_plan
+
+    if mode not in MODES:
+        raise ValueError(f"mode must be one of {MODES}")
+    rank, K = comm.rank, case.top_k
+    gather = HostMemoryBackend(comm)._all_gather
+    sets = []
+    for variant in range(2):
+        c = dataclasses.replace(case, seed=case.seed + 101 * variant)
+        inp = make_inputs(c, rank)
+        topk = gather(routing(c, rank).to(torch.int32))
+        dst = reference_plan(case, topk, rank)["dst"].to(torch.int32).contiguous()
+        dsts = gather(dst)
+        hidden = inp.hidden_sh.float().contiguous()
+        w = inp.route_weights_sk.float().contiguous().reshape(-1) if mode == "pair" else None
+        want, want_w, source = expected_rows(dataclasses.replace(case, dtype="float32"), dsts, gather(hidden), None if w is None else gather(w), rank)
+        sets.append({"dst": dst, "dst_local": dst_local_from_plans(case, dsts, rank).to(torch.int32), "hidden": hidden, "weights": w, "want": want,
+                     "want_w": want_w, "source": source})
+    failures: List[Dict[str, object]] = []
+    times: List[float] = []
+
+    def launch(s):
+        t0 = time.perf_counter()
+        out = _C.host_moon_dispatch(comm, s["hidden"], s["weights"], s["dst"], s["dst_local"], K)
+        times.append((time.perf_counter() - t0) * 1e6)
+        return out
+
+    def check(s, rows, wn, what: str, i: int):
+        bad = first_mismatch(rows, s["want"], s["source"])
+        if bad is None and s["want_w"] is not None:
+            bad = first_mismatch(wn.reshape(-1, 1), s["want_w"].reshape(-1, 1), s["source"])
+            if bad is not None:
+                bad["tensor"] = "route weights"
+        if bad is not None:
+            bad.update(check=what, iteration=i)
+            failures.append(bad)
+
+    for i in range(iters):
+        rows, wn = launch(sets[0])
+        if check_every > 0 and (i % check_every == 0 or i == iters - 1):
+            check(sets[0], rows, wn, "repeated exact", i)
+    for i in range(iters):
+        s = sets[i & 1]
+        rows, wn = launch(s)
+        if check_every > 0 and (i % check_every <= 1 or i >= iters - 2):
+            check(s, rows, wn, "alternating plans", i)
+    status = comm.device_status()
+    sent = int((sets[0]["dst"] >= 0).sum())
+    nbytes = sent * (case.hidden * 4 + (4 if mode == "pair" else 0))
+    lat = percentiles(times)
+    return {"case": case.name, "mode": mode, "rank": rank, "iterations": iters, "ok": not failures and status == 0, "device_status": status,
+            "failures": failures[:8], "latency_us": lat, "bytes": nbytes, "gbps_at_p50": 0.0 if lat["p50"] <= 0 else nbytes / lat["p50"] / 1e3}
+
+
 def main(argv=None) -> int:
     from .case_factory import add_case_arguments, apply_overrides, load_cases, overrides_from_args, select_cases
 
@@ -169,22 +232,30 @@ def main(argv=None) -> int:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--check-every", type=int, default=10, help="0: no result checks, latency only")
     ap.add_argument("--json", default="")
+    ap.add_argument("--backend", choices=["device", "host"], default="device", help="host: gloo ranks on a host-memory communicator, no GPU")
     args = ap.parse_args(argv)
     import tilexr_b200 as txr
 
     rank, world, local = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
+    host = args.backend == "host"
+    if not host:
+        torch.cuda.set_device(local)
     cases = [apply_overrides(c, overrides_from_args(args)) for c in select_cases(load_cases(args.cases), args.case_ids) if c.ranks == world]
-    need = max([c.nvs * c.hidden * 2 + c.nvs * 4 for c in cases] + [32 << 20])
+    need = max([c.nvs * c.hidden * (4 if host else 2) + c.nvs * 4 for c in cases] + [32 << 20])
     buffer_mb = int(2 * need / (1 << 20)) + 64
-    if world > 1:
+    if host:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", str(29700 + os.getpid() % 200))
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        comm = txr.init_from_torch_distributed(host_memory=True, buffer_mb=buffer_mb)
+    elif world > 1:
         dist.init_process_group("nccl")
         comm = txr.init_from_torch_distributed(buffer_mb=buffer_mb)
     else:
         comm = txr.init_process(0, 1, comm_id=f"127.0.0.1:{29700 + os.getpid() % 200}", buffer_mb=buffer_mb, device=local)
     results = []
     for c in cases:
-        r = run_case(comm, c, args.mode, args.iters, args.warmup, args.check_every)
+        r = run_case_host(comm, c, args.mode, args.iters, args.check_every) if host else run_case(comm, c, args.mode, args.iters, args.warmup, args.check_every)
         if world > 1:
             every: List[Optional[dict]] = [None] * world
             dist.all_gather_object(every, r)
@@ -203,7 +274,7 @@ def main(argv=None) -> int:
         with open(args.json, "w") as f:
             json.dump(results, f, indent=1)
     comm.destroy()
-    if world > 1:
+    if dist.is_initialized():
         dist.destroy_process_group()
     return 0 if all(r["ok"] for r in results) else 1
 

@@ -7,7 +7,7 @@
 #   usage: run_moonep.sh N OUT [correctness-cases] [perf-cases]      (case files under tilexr_b200/tools/moonep/cases/)
 # Several nodes: run it on each node with the same OUT on a shared file system (or copy OUT/samples together) and
 # finish with   python -m tilexr_b200.tools.moonep.launcher --mode aggregate --samples OUT/samples --json OUT/aggregate.json
-# Without a GPU:  run_moonep.sh N OUT smoke host   runs the correctness mode alone, as gloo ranks on a host-memory communicator.
+# Without a GPU:  run_moonep.sh N OUT smoke host   runs the correctness mode and the dispatch hot loop as gloo ranks on a host-memory communicator.
 set -u
 if [ $# -lt 2 ]; then echo "usage: $0 N OUT [correctness-cases] [perf-cases]" >&2; exit 2; fi
 N=$1
@@ -20,7 +20,9 @@ rc=0
 if [ "$PERF" = "host" ]; then
     timeout 900 $RUN --master-port 29621 -m tilexr_b200.tools.moonep.launcher --mode correctness --backend host --cases "$CORRECT" \
         --json "$OUT/correctness.json" > "$OUT/correctness.md" 2> "$OUT/correctness.err" || rc=1
-    tail -n 2 "$OUT"/correctness.err | cut -c1-300
+    timeout 600 $RUN --master-port 29626 -m tilexr_b200.tools.moonep.dispatch_hot_loop --backend host --cases "$CORRECT" --iters 20 --check-every 1 \
+        --json "$OUT/dispatch_hot_loop.json" > "$OUT/dispatch_hot_loop.txt" 2> "$OUT/dispatch_hot_loop.err" || rc=1
+    tail -n 2 "$OUT"/correctness.err "$OUT"/dispatch_hot_loop.err | cut -c1-300
     exit $rc
 fi
 timeout 900 $RUN --master-port 29621 -m tilexr_b200.tools.moonep.launcher --mode correctness --cases "$CORRECT" \
