@@ -10,6 +10,7 @@
 #include <map>
 #include <set>
 #include <sstream>
+#include <tuple>
 #include <sys/stat.h>
 
 namespace TileXR {
@@ -29,6 +30,7 @@ const char *FindingName(FindingKind k)
         case FindingKind::UNSUPPORTED_API: return "UNSUPPORTED_API";
         case FindingKind::EVENT_COVERAGE_GAP: return "EVENT_COVERAGE_GAP";
         case FindingKind::BUFFER_LIFETIME: return "BUFFER_LIFETIME";
+        case FindingKind::AMBIGUOUS_SOURCE: return "AMBIGUOUS_SOURCE";
     }
     return "UNKNOWN";
 }
@@ -230,7 +232,10 @@ Program BuildCollective(const CheckerCase &c, int rank)
                     return std::vector<int32_t>(in.begin() + srcOff, in.begin() + srcOff + n);
                 };
                 if (direct) p.steps.push_back(CopyToPeerOutput(peer, epoch, static_cast<uint64_t>(rank) * c.count + off, tile, "coll_kernels.cu:PushBody (zero copy)"));
-                else p.steps.push_back(CopyToPeer(peer, rank, epoch, off, tile, BufferRole::CommData, "coll_kernels.cu:PushBody"));
+                else {
+                    const bool stray = c.inject.sharedSlice && R >= 3 && rank == R - 1 && peer == 1 && t == 0 && launch == 0;
+                    p.steps.push_back(CopyToPeer(peer, stray ? 0 : rank, epoch, off, tile, BufferRole::CommData, "coll_kernels.cu:PushBody"));
+                }
                 const bool skip = c.inject.missingFlag && rank == 0 && peer == 1 && t == 0 && launch == 0;
                 if (!skip) {
                     const int64_t tag = (c.inject.staleMagic && rank == 0 && peer == 1 && t == 0 && launch == 0) ? epoch - 1 : epoch;
@@ -617,6 +622,40 @@ std::vector<Finding> CheckOrdering(const std::vector<Event> &events)
         }
         if (!met && early.insert({c.rank, c.peer}).second) {
             add(FindingKind::BUFFER_LIFETIME, c, "a peer's own tensor was written before that peer was known to have entered this launch (its earlier work may still read it)");
+        }
+    }
+    // two ranks that write overlapping bytes of one region of one owner in one launch: nothing orders the two stores, so the bytes
+    // a reader finds depend on timing (every protocol here gives each source its own slice or its own rows)
+    {
+        struct Span {
+            uint64_t begin, end;
+            const Event *e;
+        };
+        std::map<std::tuple<int, int, int64_t, int64_t>, std::vector<Span>> regions;
+        for (const Event &c : events) {
+            if ((c.kind != EventKind::Copy && c.kind != EventKind::Write) || c.bytes == 0) continue;
+            if (c.role != BufferRole::CommData && c.role != BufferRole::RegisteredBuffer) continue;
+            regions[std::make_tuple(c.peer, static_cast<int>(c.role), static_cast<int64_t>(c.slot), static_cast<int64_t>(c.magic))].push_back(
+                {c.offset, c.offset + c.bytes, &c});
+        }
+        std::set<std::tuple<int, int, int>> told;
+        for (auto &kv : regions) {
+            std::vector<Span> &v = kv.second;
+            std::sort(v.begin(), v.end(), [](const Span &a, const Span &b) { return a.begin < b.begin; });
+            // sweep: the span that reaches furthest so far, per writer; an overlap with another writer's reach is a finding
+            std::map<int, uint64_t> reach;
+            for (const Span &sp : v) {
+                for (const auto &other : reach) {
+                    if (other.first != sp.e->rank && other.second > sp.begin &&
+                        told.insert(std::make_tuple(std::min(other.first, sp.e->rank), std::max(other.first, sp.e->rank), sp.e->peer)).second) {
+                        add(FindingKind::AMBIGUOUS_SOURCE, *sp.e,
+                            "ranks " + std::to_string(other.first) + " and " + std::to_string(sp.e->rank) + " both wrote bytes at offset " +
+                                std::to_string(sp.begin) + " of rank " + std::to_string(sp.e->peer) + "'s region in one launch");
+                    }
+                }
+                uint64_t &r = reach[sp.e->rank];
+                r = std::max(r, sp.end);
+            }
         }
     }
     // coverage

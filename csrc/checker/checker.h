@@ -52,6 +52,7 @@ enum class FindingKind {
     UNSUPPORTED_API,
     EVENT_COVERAGE_GAP,
     BUFFER_LIFETIME,
+    AMBIGUOUS_SOURCE,   // two ranks wrote overlapping bytes of one window region in one launch: what a reader finds depends on timing
 };
 const char *FindingName(FindingKind k);
 const char *EventKindName(EventKind k);
@@ -77,6 +78,7 @@ struct Injection {
     bool skipReuseGuard = false;     // a launch overwrites a half a slow peer still reads
     bool corruptOutput = false;      // one output word is flipped
     bool skipEntryMeeting = false;   // zero-copy: a producer writes a peer's own tensor before that peer entered the launch
+    bool sharedSlice = false;        // the last rank stores its first tile into rank 0's slice of rank 1's window (3+ ranks)
 };
 
 struct CheckerCase {

@@ -23,7 +23,7 @@ static void Usage()
               "       [--scheduler serial|round_robin] [--out DIR] [--trace FILE]\n"
               "       [--inject-read-before-copy] [--inject-stale-magic] [--inject-missing-flag] [--inject-peer-user-read]\n"
               "       [--inject-pipe-wait] [--inject-deadlock] [--inject-skip-reuse-guard] [--inject-corrupt-output]\n"
-              "       [--zero-copy] [--inject-skip-entry-meeting]");
+              "       [--zero-copy] [--inject-skip-entry-meeting] [--inject-shared-slice]");
 }
 
 int main(int argc, char **argv)
@@ -61,6 +61,7 @@ int main(int argc, char **argv)
         else if (a == "--inject-deadlock") c.inject.deadlock = true;
         else if (a == "--inject-skip-reuse-guard") c.inject.skipReuseGuard = true;
         else if (a == "--inject-corrupt-output") c.inject.corruptOutput = true;
+        else if (a == "--inject-shared-slice") c.inject.sharedSlice = true;
         else if (a == "--inject-skip-entry-meeting") c.inject.skipEntryMeeting = true;
         else if (a == "--zero-copy") c.zeroCopy = true;
         else if (a == "--help" || a == "-h") {

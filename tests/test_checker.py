@@ -130,3 +130,40 @@ def test_zero_copy_gather_needs_the_entry_meeting():
         ok = subprocess.run([str(cli), "--op", "allgather", "--ranks", "2", "--zero-copy"], capture_output=True, text=True)
         bad = subprocess.run([str(cli), "--op", "allgather", "--ranks", "2", "--zero-copy", "--inject-skip-entry-meeting"], capture_output=True, text=True)
         assert ok.returncode == 0 and bad.returncode != 0 and "BUFFER_LIFETIME" in bad.stdout
+
+
+def test_two_writers_of_the_same_bytes_are_reported():
+    """AMBIGUOUS_SOURCE: ranks 0 and 2 both store into overlapping bytes of rank 1's window in one launch; slices that only
+    touch, other launches and other regions are fine."""
+    import json
+
+    from tilexr_b200.tools import checker
+
+    def ev(i, kind, rank, peer, offset=0, nbytes=0, magic=1, slot=0, role="comm_data"):
+        return {"id": i, "kind": kind, "rank": rank, "peer": peer, "block": 0, "role": role, "slot": slot, "pipe": -1, "magic": magic,
+                "offset": offset, "bytes": nbytes, "satisfied": 1, "source": "test"}
+
+    def run(copies):
+        events = [ev(1, "RankStart", 0, -1, role="none"), ev(2, "RankStart", 2, -1, role="none")]
+        events += [ev(10 + i, "Copy", *c) for i, c in enumerate(copies)]
+        events += [ev(90, "RankEnd", 0, -1, role="none"), ev(91, "RankEnd", 2, -1, role="none")]
+        return [f[0] for f in checker.check_trace("\n".join(json.dumps(e) for e in events) + "\n")]
+
+    assert run([(0, 1, 0, 128), (2, 1, 128, 128)]) == []                               # the slices touch and do not overlap
+    assert run([(0, 1, 0, 128), (2, 1, 64, 128)]) == ["AMBIGUOUS_SOURCE"]
+    assert run([(0, 1, 0, 256), (0, 1, 300, 8), (2, 1, 200, 8)]) == ["AMBIGUOUS_SOURCE"]   # inside an earlier, longer store
+    assert run([(0, 1, 0, 128), (2, 1, 64, 128, 2)]) == []                             # another launch (the other half of the window)
+    assert run([(0, 1, 0, 128), (2, 1, 64, 128, 1, 5)]) == []                          # another region
+    assert run([(0, 1, 0, 128), (0, 1, 64, 128)]) == []                                # one writer may store twice
+    assert run([(0, 1, 0, 128), (2, 1, 64, 128), (2, 1, 100, 8), (0, 1, 90, 8)]) == ["AMBIGUOUS_SOURCE"]   # one finding per pair of writers and owner
+
+
+def test_shared_slice_injection_is_found_in_the_modelled_all_gather():
+    from tilexr_b200.tools import checker
+
+    good = checker.run_case(op="allgather", rank_size=3, count=512, tile_elems=128)
+    assert good["passed"], good["summary"]
+    rep = checker.run_case(op="allgather", rank_size=3, count=512, tile_elems=128, inject_shared_slice=True)
+    assert not rep["passed"] and "AMBIGUOUS_SOURCE" in rep["findings"], rep["summary"]
+    # with two ranks there is no third writer: the switch changes nothing
+    assert checker.run_case(op="allgather", rank_size=2, count=512, tile_elems=128, inject_shared_slice=True)["passed"]

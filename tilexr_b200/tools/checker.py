@@ -17,7 +17,7 @@ import sys
 from .. import _C
 
 INJECTIONS = ("read_before_copy", "stale_magic", "missing_flag", "peer_user_read", "pipe_wait", "deadlock", "skip_reuse_guard",
-              "corrupt_output", "skip_entry_meeting")
+              "corrupt_output", "skip_entry_meeting", "shared_slice")
 
 
 def run_case(**spec) -> dict:
