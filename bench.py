@@ -23,7 +23,6 @@ import json
 import os
 import socket
 import statistics
-import subprocess
 import sys
 import time
 from pathlib import Path

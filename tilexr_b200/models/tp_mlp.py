@@ -17,7 +17,6 @@ src/include/tilexr_types.h:108-125); `tilexr_b200/tools/tp_mlp_perf.py` times th
 from __future__ import annotations
 
 import dataclasses
-from typing import Optional
 
 import torch
 

@@ -16,7 +16,6 @@ reference: src/comm/comm_wrap.cpp:26-149):
 from __future__ import annotations
 
 import contextlib
-import os
 from typing import Callable, List, Optional, Sequence
 
 import torch
