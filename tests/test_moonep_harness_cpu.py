@@ -550,3 +550,32 @@ def test_dispatch_hot_loop_on_host_memory(tmp_path):
     assert len(doc) == 1 and doc[0]["ok"] and doc[0]["case"] == "smoke_r2" and len(doc[0]["ranks"]) == 2
     for rank in doc[0]["ranks"]:
         assert rank["failures"] == [] and rank["device_status"] == 0 and rank["latency_us"]["count"] == 12 and rank["bytes"] > 0
+
+
+def test_route_replay_on_host_memory(tmp_path):
+    """Routes captured from two ranks' routers are replayed by the launcher on a host-memory communicator: the operator
+    sequence of every layer, forward and backward, with the round trip verified."""
+    import json
+    import pathlib
+    import subprocess
+    import sys
+
+    from tilexr_b200.tools.moonep.model_replay import RouteRecorder
+
+    capture = tmp_path / "capture"
+    g = torch.Generator().manual_seed(3)
+    for rank in range(2):
+        rec = RouteRecorder(str(capture), rank, ranks=2, experts=8, prefetch_slots=2, token_padding=4)
+        for layer in range(2):
+            rec.record(f"layers.{layer}.moe", torch.randint(0, 8, (16, 2), generator=g), hidden=64)
+        rec.save()
+    root = pathlib.Path(__file__).resolve().parents[1]
+    out = tmp_path / "replay.json"
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nproc-per-node", "2", "--master-addr", "127.0.0.1", "--master-port", str(free_port()),
+           "-m", "tilexr_b200.tools.moonep.launcher", "--mode", "replay", "--backend", "host", "--capture", str(capture), "--iters", "2", "--json", str(out)]
+    env = dict(os.environ, PYTHONPATH=str(root) + os.pathsep + os.environ.get("PYTHONPATH", ""), MASTER_PORT=str(free_port()))
+    r = subprocess.run(cmd, cwd=str(root), env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    doc = json.loads(out.read_text())
+    assert doc["verified"] and doc["backend"] == "host-memory" and [l["layer"] for l in doc["layers"]] == ["layers.0.moe", "layers.1.moe"]
+    assert set(doc["total_us"]) == {"planning", "dispatch_fwd", "combine_fwd", "dispatch_bwd", "combine_bwd"} and all(v > 0 for v in doc["total_us"].values())

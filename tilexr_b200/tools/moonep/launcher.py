@@ -78,8 +78,8 @@ def main(argv=None) -> int:
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     host = args.backend == "host"
-    if host and args.mode != "correctness":
-        ap.error("--backend host runs the correctness mode only")
+    if host and args.mode not in ("correctness", "replay"):
+        ap.error("--backend host runs the correctness and replay modes only")
     if not host:
         torch.cuda.set_device(local)
     buffer_mb = args.buffer_mb
@@ -105,7 +105,13 @@ def main(argv=None) -> int:
     results = []
     failed = False
     if args.mode == "replay":
-        results = replay(args.capture, comm, iters=max(1, args.iters))
+        if host:
+            from .model_replay import replay_host
+
+            results = replay_host(args.capture, comm, iters=max(1, args.iters))
+            failed |= not results["verified"]
+        else:
+            results = replay(args.capture, comm, iters=max(1, args.iters))
         if rank == 0:
             print(json.dumps(results["total_us"]))
     else:

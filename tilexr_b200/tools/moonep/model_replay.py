@@ -99,6 +99,52 @@ def replay(capture_dir: str, comm, iters: int = 3, layers: Optional[int] = None)
     return {"schema": "tilexr-moonep-replay-result-v1", "ranks": meta["ranks"], "layers": out, "total_us": total}
 
 
+def replay_host(capture_dir: str, comm, iters: int = 3, layers: Optional[int] = None) -> Dict[str, object]:
+    """The same operator sequence on a host-memory communicator (gloo ranks, no GPU): planning from the exchanged routing,
+    dispatch, combine, and both again for the backward pass, through host-memory windows.  Times are wall clock; every
+    layer is also verified: an unweighted combine of what the dispatch delivered returns each token times its number of
+    active routes, exactly."""
+    import time
+
+    from ... import _C
+    from .host_backend import HostMemoryBackend
+    from .planner_reference import dst_local_from_plans, reference_plan
+
+    meta = load_meta(capture_dir)
+    gather = HostMemoryBackend(comm)._all_gather
+    out = []
+    for layer in meta["layers"][: layers or len(meta["layers"])]:
+        case = layer_case(meta, layer)
+        topk = torch.load(pathlib.Path(capture_dir) / f"layer{int(layer['index']):04d}_rank{comm.rank}.pt").to(torch.int32).reshape(case.tokens, case.top_k)
+        g = torch.Generator().manual_seed(int(layer["index"]) * 131 + comm.rank)
+        hidden = torch.randn(case.tokens, case.hidden, generator=g).to(case.torch_dtype()).float().contiguous()
+        weights = torch.rand(case.routes, generator=g)
+        times: Dict[str, List[float]] = {"planning": [], "dispatch_fwd": [], "combine_fwd": [], "dispatch_bwd": [], "combine_bwd": []}
+        verified = True
+        for _ in range(iters):
+            t = [time.perf_counter()]
+            dst = reference_plan(case, gather(topk), comm.rank)["dst"].to(torch.int32).contiguous()
+            dst_local = dst_local_from_plans(case, gather(dst), comm.rank).to(torch.int32)
+            t.append(time.perf_counter())
+            rows, w = _C.host_moon_dispatch(comm, hidden, weights, dst, dst_local, case.top_k)
+            t.append(time.perf_counter())
+            y, wback = _C.host_moon_combine(comm, rows, w, dst, dst_local, case.tokens, case.top_k)
+            t.append(time.perf_counter())
+            grows, _ = _C.host_moon_dispatch(comm, y.contiguous(), None, dst, dst_local, case.top_k)
+            t.append(time.perf_counter())
+            _C.host_moon_combine(comm, grows, None, dst, dst_local, case.tokens, case.top_k)
+            t.append(time.perf_counter())
+            for i, k in enumerate(times):
+                times[k].append((t[i + 1] - t[i]) * 1e6)
+            active = (dst.view(case.tokens, case.top_k) >= 0).sum(1, keepdim=True).float()
+            sent = (dst >= 0).reshape(-1)
+            verified &= bool(torch.equal(y, hidden * active)) and bool(torch.equal(wback.reshape(-1)[sent], weights[sent]))
+        out.append({"layer": layer["name"], "tokens": case.tokens, "verified": verified, "us": {k: statistics.median(v) for k, v in times.items()}})
+    total = {k: sum(l["us"][k] for l in out) for k in out[0]["us"]} if out else {}
+    return {"schema": "tilexr-moonep-replay-result-v1", "ranks": meta["ranks"], "layers": out, "total_us": total, "backend": "host-memory",
+            "verified": all(l["verified"] for l in out)}
+
+
 def compare_replays(a: Dict[str, object], b: Dict[str, object]) -> List[Dict[str, object]]:
     """Per operator: total microseconds of both replays and b's speed-up over a."""
     rows = []
