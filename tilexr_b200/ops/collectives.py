@@ -3,6 +3,9 @@
 Each function issues kernels and returns without synchronising, like the C API
 (csrc/include/tilexr_collectives.h).  Output tensors that live in registered memory
 (``Comm.symm_empty`` / ``Comm.register``) are written by the peers directly.
+
+CPU tensors on a host-memory communicator (``init_from_torch_distributed(host_memory=True)``, the no-GPU plumbing
+mode) take the host kernels instead: the same windows, flags and launch epochs, blocking, sums in fp32 only.
 """
 from __future__ import annotations
 
@@ -21,8 +24,28 @@ class ReduceOp(enum.IntEnum):
     MIN = 3
 
 
+HOST_TILE_BYTES = 16384
+
+
+def _host_sum_only(x: torch.Tensor, op) -> None:
+    if int(op) != int(ReduceOp.SUM) or x.dtype != torch.float32:
+        raise ValueError("host-memory communicators reduce fp32 sums only")
+
+
+def _into(out: Optional[torch.Tensor], value: torch.Tensor) -> torch.Tensor:
+    if out is None:
+        return value
+    out.copy_(value.view_as(out))
+    return out
+
+
 def all_gather(comm, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     x = x.contiguous()
+    if not x.is_cuda:
+        if out is None:
+            out = torch.empty((comm.world_size,) + tuple(x.shape), dtype=x.dtype)
+        _C.host_all_gather(comm, x, out, HOST_TILE_BYTES)
+        return out
     if out is None:
         out = torch.empty((comm.world_size,) + tuple(x.shape), dtype=x.dtype, device=x.device)
     _C.all_gather(comm, x, out)
@@ -32,6 +55,8 @@ def all_gather(comm, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> tor
 def all_to_all(comm, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Equal split along dim 0: chunk p of ``x`` goes to rank p."""
     x = x.contiguous()
+    if not x.is_cuda:
+        return _into(out, _C.host_all_to_all(comm, x, HOST_TILE_BYTES))
     if out is None:
         out = torch.empty_like(x)
     _C.all_to_all(comm, x, out)
@@ -40,6 +65,9 @@ def all_to_all(comm, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> tor
 
 def all_reduce(comm, x: torch.Tensor, op: ReduceOp = ReduceOp.SUM, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     x = x.contiguous()
+    if not x.is_cuda:
+        _host_sum_only(x, op)
+        return _into(out, _C.host_all_reduce(comm, x.reshape(-1)).view_as(x))
     if out is None:
         out = torch.empty_like(x)
     _C.all_reduce(comm, x, out, int(op))
@@ -49,6 +77,11 @@ def all_reduce(comm, x: torch.Tensor, op: ReduceOp = ReduceOp.SUM, out: Optional
 def reduce_scatter(comm, x: torch.Tensor, op: ReduceOp = ReduceOp.SUM, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``x`` holds world_size equal chunks along dim 0; returns the reduction of chunk ``rank``."""
     x = x.contiguous()
+    if not x.is_cuda:
+        _host_sum_only(x, op)
+        shape = list(x.shape)
+        shape[0] //= comm.world_size
+        return _into(out, _C.host_reduce_scatter(comm, x.reshape(-1)).view(shape))
     if out is None:
         shape = list(x.shape)
         shape[0] //= comm.world_size
@@ -58,6 +91,11 @@ def reduce_scatter(comm, x: torch.Tensor, op: ReduceOp = ReduceOp.SUM, out: Opti
 
 
 def broadcast(comm, x: torch.Tensor, root: int = 0) -> torch.Tensor:
+    if not x.is_cuda:
+        if not x.is_contiguous():
+            raise ValueError("broadcast works in place on a contiguous tensor")
+        _C.host_broadcast(comm, x, root, HOST_TILE_BYTES)
+        return x
     _C.broadcast(comm, x, root)
     return x
 

@@ -23,15 +23,16 @@ import torch
 
 
 class HostMemoryOps:
-    """The intra-node collectives on a host-memory communicator (fp32 CPU tensors), for the no-GPU plumbing mode."""
+    """The intra-node collectives on a host-memory communicator (CPU tensors; sums in fp32), for the no-GPU plumbing mode.
+    `tilexr_b200.ops.collectives` takes the same path for CPU tensors; this class only fixes the tile size."""
 
     def __init__(self, tile_bytes: int = 16384):
         self.tile_bytes = tile_bytes
 
     def all_reduce(self, comm, x):
-        from .. import _C
+        from ..ops import collectives
 
-        return _C.host_all_reduce(comm, x.contiguous().reshape(-1)).view_as(x)
+        return collectives.all_reduce(comm, x)
 
     def all_gather(self, comm, x):
         from .. import _C
@@ -41,11 +42,9 @@ class HostMemoryOps:
         return out
 
     def reduce_scatter(self, comm, x):
-        from .. import _C
+        from ..ops import collectives
 
-        shape = list(x.shape)
-        shape[0] //= comm.world_size
-        return _C.host_reduce_scatter(comm, x.contiguous().reshape(-1)).view(shape)
+        return collectives.reduce_scatter(comm, x)
 
     def all_to_all(self, comm, x):
         from .. import _C
