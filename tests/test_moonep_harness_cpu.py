@@ -579,3 +579,32 @@ def test_route_replay_on_host_memory(tmp_path):
     doc = json.loads(out.read_text())
     assert doc["verified"] and doc["backend"] == "host-memory" and [l["layer"] for l in doc["layers"]] == ["layers.0.moe", "layers.1.moe"]
     assert set(doc["total_us"]) == {"planning", "dispatch_fwd", "combine_fwd", "dispatch_bwd", "combine_bwd"} and all(v > 0 for v in doc["total_us"].values())
+
+
+def test_model_flow_on_host_memory(tmp_path):
+    """The operator sequence of a training step (planning, dispatch, prefetch, combine, their backward forms, reduce-grad) issued
+    by the launcher on a host-memory communicator: every operator of every layer timed on both ranks, none skipped."""
+    import json
+    import pathlib
+    import subprocess
+    import sys
+
+    from tilexr_b200.tools.moonep import model_flow as mf
+
+    root = pathlib.Path(__file__).resolve().parents[1]
+    out = tmp_path / "flow.json"
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nproc-per-node", "2", "--master-addr", "127.0.0.1", "--master-port", str(free_port()),
+           "-m", "tilexr_b200.tools.moonep.launcher", "--mode", "model-flow", "--backend", "host", "--cases", "smoke", "--layers", "2", "--iters", "2",
+           "--warmup", "0", "--json", str(out)]
+    env = dict(os.environ, PYTHONPATH=str(root) + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    r = subprocess.run(cmd, cwd=str(root), env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert "| planning | 4 |" in r.stdout and "16750" not in r.stdout            # no published column for the host plumbing
+    doc = mf.load_document(str(out))
+    assert doc["backend"] == "tilexr-host-memory" and len(doc["operator_order"]) == len(mf.operator_order(2)) == 22
+    assert set(doc["ranks"]) == {"0", "1"}
+    for entry in doc["ranks"].values():
+        ops = entry["operators"]
+        assert len(ops) == 22 and not any(o["skipped"] for o in ops) and all(o["latency_us"] > 0 for o in ops)
+    med = mf.stage_medians(doc)
+    assert set(med) == set(mf.FORWARD_STAGES + mf.BACKWARD_STAGES)

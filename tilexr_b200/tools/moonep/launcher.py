@@ -78,8 +78,8 @@ def main(argv=None) -> int:
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     host = args.backend == "host"
-    if host and args.mode not in ("correctness", "replay"):
-        ap.error("--backend host runs the correctness and replay modes only")
+    if host and args.mode not in ("correctness", "replay", "model-flow"):
+        ap.error("--backend host runs the correctness, replay and model-flow modes only")
     if not host:
         torch.cuda.set_device(local)
     buffer_mb = args.buffer_mb
@@ -122,7 +122,10 @@ def main(argv=None) -> int:
             from . import model_flow
 
             for c in cases:
-                doc = model_flow.run_case(comm, c, layers=args.layers, iters=max(1, args.iters), warmup=max(1, args.warmup), recompute=not args.no_recompute)
+                if host:
+                    doc = model_flow.run_case_host(comm, c, layers=args.layers, iters=max(1, args.iters), warmup=max(0, args.warmup), recompute=not args.no_recompute)
+                else:
+                    doc = model_flow.run_case(comm, c, layers=args.layers, iters=max(1, args.iters), warmup=max(1, args.warmup), recompute=not args.no_recompute)
                 if world > 1:
                     docs = [None] * world
                     dist.all_gather_object(docs, doc)

@@ -208,10 +208,10 @@ def performance_document(case: MoonEPCase, rank: int, iterations: List[List[dict
             rec.update(latency_us=med, latency_max_us=max(samples), algorithm_bytes=nbytes,
                        algorithm_bandwidth_GBps=None if not nbytes or med <= 0 else nbytes / med / 1e3, skipped=False)
         operators.append(rec)
-    return {"schema": SCHEMA, "case": case.name, "world_size": case.ranks, "iterations": len(iterations),
+    return {"schema": SCHEMA, "case": case.name, "world_size": case.ranks, "iterations": len(iterations), "backend": backend,
             "shape": {"tokens": case.tokens, "hidden": case.hidden, "top_k": case.top_k, "experts": case.experts,
                       "prefetch_slots": case.prefetch_slots, "token_padding": case.token_padding, "dtype": case.dtype, "ffn": case.ffn},
-            "timing_source": "events on the issuing stream around every operator", "operator_order": [o["stage"] for o in iterations[0]],
+            "timing_source": "wall clock around every (blocking) operator" if "host" in backend else "events on the issuing stream around every operator", "operator_order": [o["stage"] for o in iterations[0]],
             "ranks": {str(rank): {"operators": operators}}}
 
 
@@ -301,6 +301,37 @@ def run_case(comm, case: MoonEPCase, layers: int = 5, iters: int = 5, warmup: in
     return performance_document(case, comm.rank, runs, row_bytes)
 
 
+def run_case_host(comm, case: MoonEPCase, layers: int = 5, iters: int = 2, warmup: int = 0, recompute: bool = True) -> dict:
+    """The same operator sequence on a host-memory communicator (gloo ranks, no GPU): every operator through host-memory
+    windows, timed by wall clock.  The document has the layout of the device run with `backend` = "tilexr-host-memory"."""
+    import types
+
+    from .case_factory import make_inputs, routing
+    from .host_backend import HostStageBuffer
+
+    buf = HostStageBuffer(comm, case)
+    inputs = make_inputs(case, comm.rank)
+    topk = [routing(dataclass_replace_seed(case, case.seed + layer), comm.rank) for layer in range(layers)]
+    projections = grads = None
+    row_bytes = 0
+    if case.ffn > 0:
+        L, B = case.local_experts, case.prefetch_slots
+
+        def slots(src):
+            t = torch.zeros((L + B,) + tuple(src.shape[1:]), dtype=src.dtype)
+            t[:L] = src
+            return t
+
+        projections = types.SimpleNamespace(gate=slots(inputs.gate), up=slots(inputs.up), down=slots(inputs.down))
+        grads = types.SimpleNamespace(gate=inputs.grad_rows.clone().float(), up=None, down=None)
+        row_bytes = 3 * inputs.gate[0].numel() * inputs.gate.element_size()
+    flow = ModelFlow(buf, case, topk, inputs.hidden_sh, inputs.route_weights_sk, projections, grads, recompute=recompute, cuda=False)
+    for _ in range(warmup):
+        flow.run_iteration()
+    runs = [flow.run_iteration() for _ in range(iters)]
+    return performance_document(case, comm.rank, runs, row_bytes, backend="tilexr-host-memory")
+
+
 def dataclass_replace_seed(case: MoonEPCase, seed: int) -> MoonEPCase:
     import dataclasses
 
@@ -311,8 +342,9 @@ def markdown(doc: dict) -> str:
     lines = [f"### {doc['case']}: {len(doc['operator_order'])} operators per step, {doc['iterations']} iterations, {doc['world_size']} ranks", "",
              "| stage | operators | median us (slowest rank) | longest us | GB/s at the median | published Ascend950 EP8 us | ratio |", "|---|---|---|---|---|---|---|"]
     cmp_rows = {r["stage"]: r for r in compare_with_published(doc)}
+    on_device = "host" not in str(doc.get("backend", ""))                 # wall-clock times of the host plumbing compare with nothing published
     for stage, s in stage_medians(doc).items():
-        c = cmp_rows[stage]
+        c = cmp_rows[stage] if on_device else {"speedup": None, "published_us": None}
         gb = "-" if s["median_GBps"] is None else f"{s['median_GBps']:.1f}"
         ratio = "-" if c["speedup"] is None else f"{c['speedup']:.1f}x"
         lines.append(f"| {stage} | {s['operators']} | {s['median_us']:.1f} | {s['max_us']:.1f} | {gb} | {c['published_us'] or '-'} | {ratio} |")
