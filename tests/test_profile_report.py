@@ -77,3 +77,33 @@ def test_groups_diagnostics_and_prompt(tmp_path):
     stage = [e for e in index if "error" not in e][0]["stages"]["local_input_to_ipc"]
     assert stage["GBps_per_block_time"] > 0
     assert profile_report.sanitize(_trace(0, 0, 0, 50_000, 30_000)) == [] and profile_report.expected_launch_ids(7, 3) == [0, 3, 6]
+
+
+def test_clock_offsets_between_hosts_are_estimated_and_removed(tmp_path):
+    """Four ranks on two hosts; host 1's timer runs 5 ms ahead.  Every launch ends on all ranks within a few microseconds, so
+    the estimate recovers the 5 ms and the Perfetto slices of both hosts line up."""
+    skew_ticks = 5_000_000                                    # 5000 us at 1000 ticks per us
+    for rank in range(4):
+        for launch in range(5):
+            d = tmp_path / f"rank{rank}" / f"launch{launch}"
+            d.mkdir(parents=True)
+            start = 100_000 * launch + 500 * rank + (skew_ticks if rank >= 2 else 0)
+            dur = 60_000 - 500 * rank + 700 * (launch % 2) * (rank % 2)          # ends within a microsecond or two of each other
+            t = _trace(rank, launch, start, dur, 20_000)
+            t["rankSize"] = 4
+            (d / "trace.json").write_text(json.dumps(t))
+    assert profile_report.main([str(tmp_path), "--ranks-per-host", "2"]) == 0
+    out = tmp_path / "report"
+    offsets = json.loads((out / "clock_offsets.json").read_text())
+    assert set(offsets) == {"0", "1"} and offsets["0"]["offset_us"] == 0.0 and offsets["0"]["launches"] == 5
+    assert abs(offsets["1"]["offset_us"] - 5000.0) < 2.0 and offsets["1"]["launches"] == 5 and offsets["1"]["spread_us"] < 2.0
+    pf = json.loads((out / "perfetto_trace.json").read_text())
+    first = {}
+    for e in pf["traceEvents"]:
+        if e["ph"] == "X" and e["args"]["launch"] == 3 and e["name"] == "kernel_total":
+            first[e["pid"]] = e["ts"]
+    assert len(first) == 4 and max(first.values()) - min(first.values()) < 5.0          # 5000 us apart before the correction
+    # without the option nothing is shifted and no offsets file is written
+    assert profile_report.main([str(tmp_path), "--out", str(tmp_path / "plain")]) == 0
+    assert not (tmp_path / "plain" / "clock_offsets.json").exists()
+    assert profile_report.estimate_clock_offsets([], 2) == {} and profile_report.estimate_clock_offsets([{"error": "x"}], 0) == {}

@@ -10,10 +10,14 @@
 * ``ai_prompt.md``       the findings as a self-contained question for an assistant (``--ai-prompt``)
 
 Same role as the reference's aggregator (tools/collectives/tilexr_collective_profile_report.py:
-25-1158).  All ranks of one node share the GPU nanosecond timer, so no clock-offset
-compensation is applied; ``--align`` shifts every rank so that its first event starts at zero.
+25-1158).  All ranks of one node share the GPU nanosecond timer; ``--align`` shifts every rank so that its first event
+starts at zero.  Traces from several hosts (two-level jobs, ``--ranks-per-host L``: host = rank // L) carry each host's own
+timer: the offset of a host against host 0 is estimated from the launches that both recorded (a collective ends on all its
+ranks within a few microseconds, so the median difference of the hosts' end times over the launches is the timers'
+difference), written to ``clock_offsets.json`` and taken out of the Perfetto trace.
 
     python -m tilexr_b200.tools.profile_report prof_dir [--out report_dir] [--align] [--measured-iters N --sample-every M] [--ai-prompt]
+                                               [--ranks-per-host L]
 """
 from __future__ import annotations
 
@@ -224,7 +228,37 @@ def analyse(index: List[dict]) -> str:
     return "\n".join(lines) + "\n"
 
 
-def perfetto(traces: List[dict], align: bool) -> dict:
+def estimate_clock_offsets(traces: List[dict], ranks_per_host: int) -> Dict[int, dict]:
+    """{host: {"offset_us", "launches", "spread_us"}}: how far each host's timer is ahead of host 0's, the number of launches
+    the estimate rests on, and the spread (largest minus smallest difference) that says how far to trust it."""
+    if ranks_per_host <= 0:
+        return {}
+    ends: Dict[tuple, Dict[int, float]] = defaultdict(dict)              # (op, launch) -> host -> latest end in us
+    for t in traces:
+        if "error" in t or any(k not in t for k in REQUIRED_KEYS):
+            continue
+        ticks = t.get("ticksPerUs", 1000) or 1000
+        recs = [r for r in t["records"] if r.get("count", 0) > 0]
+        if not recs:
+            continue
+        host = int(t["rank"]) // ranks_per_host
+        end = max(r["lastEnd"] for r in recs) / ticks
+        key = (t["op"], t["launchId"])
+        ends[key][host] = max(ends[key].get(host, end), end)
+    diffs: Dict[int, List[float]] = defaultdict(list)
+    for per_host in ends.values():
+        if 0 not in per_host:
+            continue
+        for host, end in per_host.items():
+            diffs[host].append(end - per_host[0])
+    out = {}
+    for host, d in sorted(diffs.items()):
+        d.sort()
+        out[host] = {"offset_us": 0.0 if host == 0 else d[len(d) // 2], "launches": len(d), "spread_us": d[-1] - d[0]}
+    return out
+
+
+def perfetto(traces: List[dict], align: bool, ranks_per_host: int = 0, offsets: Dict[int, dict] = None) -> dict:
     events = []
     for t in traces:
         if "error" in t or any(k not in t for k in REQUIRED_KEYS):
@@ -233,6 +267,8 @@ def perfetto(traces: List[dict], align: bool) -> dict:
         names = {s["id"]: s["name"] for s in t.get("stages", [])}
         recs = [r for r in t.get("records", []) if r["count"] > 0]
         base = min((r["firstStart"] for r in recs), default=0) if align else 0
+        if not align and ranks_per_host > 0 and offsets:
+            base = offsets.get(int(t["rank"]) // ranks_per_host, {}).get("offset_us", 0.0) * ticks      # this host's timer runs ahead by that much
         for r in recs:
             events.append({
                 "name": names.get(r["stage"], str(r["stage"])), "cat": t["op"], "ph": "X",
@@ -270,8 +306,10 @@ def render_groups(groups: List[dict], diagnostics: List[dict]) -> str:
     return "\n".join(lines) + "\n"
 
 
-def write_report(root: Path, out: Path, align: bool = False, measured_iters: int = 0, sample_every: int = 0, emit_ai_prompt: bool = False) -> dict:
+def write_report(root: Path, out: Path, align: bool = False, measured_iters: int = 0, sample_every: int = 0, emit_ai_prompt: bool = False,
+                 ranks_per_host: int = 0) -> dict:
     traces = load_traces(root)
+    offsets = estimate_clock_offsets(traces, ranks_per_host)
     index = build_index(traces)
     groups = group_launches(index)
     diagnostics = diagnose(traces, index, groups, measured_iters, sample_every)
@@ -281,11 +319,13 @@ def write_report(root: Path, out: Path, align: bool = False, measured_iters: int
     (out / "launch_groups.json").write_text(json.dumps(groups, indent=1))
     (out / "diagnostics.json").write_text(json.dumps(diagnostics, indent=1))
     (out / "analysis.md").write_text(analysis)
-    (out / "perfetto_trace.json").write_text(json.dumps(perfetto(traces, align)))
+    (out / "perfetto_trace.json").write_text(json.dumps(perfetto(traces, align, ranks_per_host, offsets)))
+    if ranks_per_host > 0:
+        (out / "clock_offsets.json").write_text(json.dumps({str(h): v for h, v in offsets.items()}, indent=1))
     (out / "report.html").write_text(render_html(index, analysis))
     if emit_ai_prompt:
         (out / "ai_prompt.md").write_text(ai_prompt(index, groups, diagnostics, analysis))
-    return {"launches": len(index), "groups": len(groups), "problems": len(diagnostics), "out": str(out)}
+    return {"launches": len(index), "groups": len(groups), "problems": len(diagnostics), "out": str(out), "hosts": len(offsets)}
 
 
 def main(argv=None) -> int:
@@ -296,9 +336,10 @@ def main(argv=None) -> int:
     p.add_argument("--measured-iters", type=int, default=0, help="launches of the measured loop (with --sample-every: which launch ids must exist)")
     p.add_argument("--sample-every", type=int, default=0)
     p.add_argument("--ai-prompt", action="store_true", help="also write ai_prompt.md")
+    p.add_argument("--ranks-per-host", type=int, default=0, help="traces come from several hosts of this many ranks: estimate and remove the hosts' timer offsets")
     a = p.parse_args(argv)
     root = Path(a.root)
-    res = write_report(root, Path(a.out) if a.out else root / "report", a.align, a.measured_iters, a.sample_every, a.ai_prompt)
+    res = write_report(root, Path(a.out) if a.out else root / "report", a.align, a.measured_iters, a.sample_every, a.ai_prompt, a.ranks_per_host)
     print(json.dumps(res))
     return 0 if res["launches"] else 1
 
